@@ -1,0 +1,194 @@
+/*
+ * uocr_cuda_moe.h - C ABI of the CUDA (sm_100a) backend for the decoder MoE layer.
+ *
+ * This is the surface a `"cuda"` backend of unlimitedocr.c binds for the MoE layer.
+ * It follows the conventions of the reference's backend headers
+ * (src/backend/metal/uocr_metal.h:170-226, src/backend/cpu_ref/uocr_cpu_ref.h:57-90):
+ *   - plain C types only; every function returns 1 on success and 0 on failure;
+ *   - on failure a NUL-terminated message is written to (error, error_size) when given
+ *     and is also kept in the context (uocr_cuda_context_last_error);
+ *   - nothing on the per-token path allocates: weights are uploaded once by the map
+ *     call, scratch is sized once by the arena call;
+ *   - a context is not re-entrant; distinct contexts may be used from distinct threads
+ *     (the per-engine rule of include/unlimitedocr.h:153-167).
+ * Tensor bytes are exactly those of a .uocr model file (src/model/uocr_format.h:49-99;
+ * expert slabs as laid out by src/unlimitedocr_c/convert.py:966-996).
+ *
+ * "d_" arguments are device pointers valid on the context's device, "h_" arguments
+ * are host pointers.  All work is enqueued on the context's stream.
+ */
+#ifndef UOCR_CUDA_MOE_H
+#define UOCR_CUDA_MOE_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#  define UOCR_CUDA_API __attribute__((visibility("default")))
+#else
+#  define UOCR_CUDA_API
+#endif
+
+/* Tensor storage types; values of uocr_tensor_qtype (src/model/uocr_format.h:40-47). */
+#define UOCR_CUDA_QTYPE_F16  1
+#define UOCR_CUDA_QTYPE_Q8_0 3
+#define UOCR_CUDA_QTYPE_Q4_0 4
+#define UOCR_CUDA_GROUP_SIZE 64u
+
+typedef struct uocr_cuda_context uocr_cuda_context;
+
+/* One projection matrix [rows][cols], input dimension contiguous.
+ * f16: qweight = fp16[rows][cols], qscale unused.
+ * q8_0: qweight = int8[rows][cols], qscale = fp16[rows][cols/64].
+ * q4_0: qweight = uint8[rows][cols/2] (byte j of a 64-group: level[j]+8 low nibble,
+ *       level[j+32]+8 high nibble), qscale = fp16[rows][cols/64]. */
+typedef struct uocr_cuda_matrix {
+    int32_t qtype;
+    uint32_t rows;
+    uint32_t cols;
+    const void *qweight;
+    const void *qscale;
+} uocr_cuda_matrix;
+
+/* One MoE layer as stored in the model file.  The routed experts are one packed-weight
+ * slab and one scale slab, expert-major, each expert holding gate[F][H], up[F][H],
+ * down[H][F]; strides/offsets carry the same meaning as the reference's kernel
+ * parameter block (src/backend/metal/kernels/decode_gemv_q4.metal:15-28): byte counts
+ * for packed weights, value counts for scales.  Zero strides/offsets mean "densely
+ * packed" and are filled in by the library. */
+typedef struct uocr_cuda_moe_layer_desc {
+    uint32_t hidden_size;              /* H, multiple of 64 */
+    uint32_t n_experts;                /* E <= 256 */
+    uint32_t top_k;                    /* K <= 16, K <= E */
+    uint32_t expert_intermediate;      /* F, multiple of 64 */
+    uint32_t shared_intermediate;      /* S, multiple of 64 */
+    float routed_scaling_factor;       /* finite, >= 0; weights are prob * factor, never renormalised */
+    const void *router_weight_f16;     /* fp16 [E][H] */
+    const float *router_logit_bias;    /* optional f32 [E] added to the logits; the model has none,
+                                          synthetic load-skew benchmarks use it */
+    int32_t expert_qtype;
+    const void *expert_qweight;
+    const void *expert_qscale;         /* NULL for f16 */
+    uint64_t expert_stride_bytes;
+    uint64_t up_offset_bytes;
+    uint64_t down_offset_bytes;
+    uint64_t expert_scale_stride_values;
+    uint64_t up_scale_offset_values;
+    uint64_t down_scale_offset_values;
+    uocr_cuda_matrix shared_gate;      /* [S][H] */
+    uocr_cuda_matrix shared_up;        /* [S][H] */
+    uocr_cuda_matrix shared_down;      /* [H][S] */
+} uocr_cuda_moe_layer_desc;
+
+/* Optional extra outputs of a layer call (device pointers, any may be NULL). */
+typedef struct uocr_cuda_moe_debug_outputs {
+    float *d_router_logits;     /* [n][E] */
+    float *d_router_probs;      /* [n][E] */
+    uint32_t *d_top_ids;        /* [n][K], slot order = descending probability */
+    float *d_top_weights;       /* [n][K] */
+} uocr_cuda_moe_debug_outputs;
+
+/* ---- backend and context: counterparts of uocr_metal_is_available, uocr_metal_backend_name,
+ * uocr_metal_context_create/destroy (src/backend/metal/uocr_metal.h:170-176). */
+UOCR_CUDA_API int uocr_cuda_is_available(void);
+UOCR_CUDA_API const char *uocr_cuda_backend_name(void);            /* "cuda" */
+UOCR_CUDA_API int uocr_cuda_device_count(void);
+/* resource_path is accepted for signature parity and ignored (kernels are linked in).
+ * The context binds the CUDA device that is current on the calling thread. */
+UOCR_CUDA_API uocr_cuda_context *uocr_cuda_context_create(const char *resource_path, char *error, size_t error_size);
+UOCR_CUDA_API void uocr_cuda_context_destroy(uocr_cuda_context *ctx);
+UOCR_CUDA_API const char *uocr_cuda_context_last_error(const uocr_cuda_context *ctx);
+/* Use an existing cudaStream_t (passed as void*) instead of the context's own; NULL restores it. */
+UOCR_CUDA_API int uocr_cuda_context_set_stream(uocr_cuda_context *ctx, void *cuda_stream);
+UOCR_CUDA_API int uocr_cuda_context_synchronize(uocr_cuda_context *ctx, char *error, size_t error_size);
+/* Kernels launched by this context since creation (every launch is counted at its call site). */
+UOCR_CUDA_API uint64_t uocr_cuda_context_kernel_launches(const uocr_cuda_context *ctx);
+/* Device bytes held: weights ("model views") and scratch, the two categories the engine's
+ * memory report uses for them (include/unlimitedocr.h:50-63). */
+UOCR_CUDA_API uint64_t uocr_cuda_context_model_view_bytes(const uocr_cuda_context *ctx);
+UOCR_CUDA_API uint64_t uocr_cuda_context_moe_scratch_bytes(const uocr_cuda_context *ctx);
+
+/* ---- model mapping: counterpart of uocr_metal_context_map_model / _unmap_model
+ * (src/backend/metal/uocr_metal.h:178-181).  Metal wraps the mmap'd file without a copy;
+ * here every tensor of the layer is validated and uploaded once.  desc holds HOST pointers.
+ * Layers get consecutive indices starting at 0. */
+UOCR_CUDA_API int uocr_cuda_context_map_moe_layer(uocr_cuda_context *ctx, const uocr_cuda_moe_layer_desc *h_desc,
+                                                  uint32_t *out_layer_index, char *error, size_t error_size);
+UOCR_CUDA_API void uocr_cuda_context_unmap_model(uocr_cuda_context *ctx);
+UOCR_CUDA_API uint32_t uocr_cuda_context_moe_layer_count(const uocr_cuda_context *ctx);
+
+/* ---- scratch: counterpart of uocr_metal_context_allocate_runtime_arenas / _release_runtime_arenas
+ * (src/backend/metal/uocr_metal.h:221-226) restricted to the MoE scratch.  Must be called after the
+ * layers are mapped and before any forward call with n_tokens <= token_capacity. */
+UOCR_CUDA_API int uocr_cuda_context_allocate_runtime_arenas(uocr_cuda_context *ctx, uint32_t batch_slots,
+                                                            uint32_t token_capacity, char *error, size_t error_size);
+UOCR_CUDA_API void uocr_cuda_context_release_runtime_arenas(uocr_cuda_context *ctx);
+/* Bytes the arena call will reserve for a layer of these dimensions (the sizing rule of
+ * src/runtime/uocr_memory.c:480-543 plus this backend's dispatch plan and partial sums). */
+UOCR_CUDA_API uint64_t uocr_cuda_moe_scratch_size(uint32_t hidden_size, uint32_t n_experts, uint32_t top_k,
+                                                  uint32_t expert_intermediate, uint32_t shared_intermediate,
+                                                  uint32_t token_capacity);
+
+/* ---- operators ----------------------------------------------------------------------- */
+
+/* Router: logits = hidden . router^T (fp16 inputs, f32 accumulate) [+ bias], f32 softmax, greedy top-k
+ * with ties to the lower expert id; weight = prob * routed_scaling_factor.  Semantics of
+ * uocr_cpu_ref_moe_router_f32 (src/backend/cpu_ref/uocr_cpu_ref.c:388-466) on the fp16 inputs the GPU
+ * path carries (src/backend/metal/kernels/moe.metal:53-189).  When d_injected_logits is not NULL the dot
+ * products are skipped and those logits are used as they are (bias still added when the layer has one):
+ * softmax, ids and weights are then bit-identical to the CPU function's on the same logits.
+ * d_logits / d_probs may be NULL. */
+UOCR_CUDA_API int uocr_cuda_moe_router(uocr_cuda_context *ctx, uint32_t layer, const void *d_hidden_f16,
+                                       const float *d_injected_logits, uint32_t n_tokens, float *d_logits,
+                                       float *d_probs, uint32_t *d_top_ids, float *d_top_weights, char *error,
+                                       size_t error_size);
+
+/* Token-to-expert permutation.  pair = token * K + slot.  expert_offsets[E+1] is the exclusive prefix sum
+ * of pairs per expert, pair_rows[] lists the pairs grouped by expert in ascending pair order (a stable
+ * counting sort), inverse[pair] is the pair's position in pair_rows (0xffffffff for an id >= E, which is
+ * dropped).  Deterministic form of the reference's bucketing pass
+ * (src/backend/metal/kernels/gemm_q8.metal:462-511). */
+UOCR_CUDA_API int uocr_cuda_moe_dispatch_plan(uocr_cuda_context *ctx, const uint32_t *d_top_ids, uint32_t n_tokens,
+                                              uint32_t top_k, uint32_t n_experts, uint32_t *d_expert_offsets,
+                                              uint32_t *d_pair_rows, uint32_t *d_inverse, char *error,
+                                              size_t error_size);
+
+/* The layer: out[n][H] = fp16( sum_slot weight * expert(hidden) + shared(hidden) [+ residual] ), the
+ * computation of uocr_cpu_ref_moe_swiglu_f32 (src/backend/cpu_ref/uocr_cpu_ref.c:468-579) with the GPU
+ * path's data types: fp16 activations, weights dequantised on the fly and never materialised, f32
+ * accumulation, SwiGLU products stored as fp16, fp16 output with the residual folded into the combine
+ * (call sites src/backend/metal/uocr_metal.m:14433-14497 and :14773-14856).  d_residual_f16 may be NULL.
+ * d_injected_logits as for the router.  The regime (one token, a few tokens, many tokens) is chosen
+ * from n_tokens as the reference does (src/backend/metal/uocr_metal.m:13674). */
+UOCR_CUDA_API int uocr_cuda_moe_layer_forward(uocr_cuda_context *ctx, uint32_t layer, const void *d_hidden_f16,
+                                              const void *d_residual_f16, const float *d_injected_logits,
+                                              uint32_t n_tokens, void *d_out_f16,
+                                              const uocr_cuda_moe_debug_outputs *debug, char *error,
+                                              size_t error_size);
+
+/* A run of consecutive layers first_layer .. first_layer+n_layers-1 chained the way the decoder chains
+ * them with the attention block left out: layer i's input is also its residual, its output feeds layer
+ * i+1.  One call = one decode step through the MoE halves of those layers. */
+UOCR_CUDA_API int uocr_cuda_moe_stack_forward(uocr_cuda_context *ctx, uint32_t first_layer, uint32_t n_layers,
+                                              const void *d_hidden_f16, uint32_t n_tokens, void *d_out_f16,
+                                              char *error, size_t error_size);
+
+/* Host-buffer forms: copy h_hidden (and h_residual) to the device, run, copy the result back and wait.
+ * These are what a host engine without its own device buffers calls. */
+UOCR_CUDA_API int uocr_cuda_moe_layer_forward_host(uocr_cuda_context *ctx, uint32_t layer, const void *h_hidden_f16,
+                                                   const void *h_residual_f16, uint32_t n_tokens, void *h_out_f16,
+                                                   uint32_t *h_top_ids, float *h_top_weights, char *error,
+                                                   size_t error_size);
+UOCR_CUDA_API int uocr_cuda_moe_stack_forward_host(uocr_cuda_context *ctx, uint32_t first_layer, uint32_t n_layers,
+                                                   const void *h_hidden_f16, uint32_t n_tokens, void *h_out_f16,
+                                                   char *error, size_t error_size);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* UOCR_CUDA_MOE_H */

@@ -170,13 +170,34 @@ def synth_layer(rng: np.random.Generator, *, H: int, E: int, K: int, F: int, S: 
     nsc = 0 if expert_qtype == QTYPE_F16 else F * (H // GROUP)
     slab = np.empty(E * 3 * proj, dtype=np.uint8)
     scales = None if expert_qtype == QTYPE_F16 else np.empty(E * 3 * nsc, dtype=np.uint16)
-    for e in range(E):
-        for p, (r, c) in enumerate(((F, H), (F, H), (H, F))):
-            w = rng.standard_normal((r, c), dtype=np.float32) * np.float32(std)
-            qw, qs = quantize(expert_qtype, w)
-            slab[(e * 3 + p) * proj : (e * 3 + p + 1) * proj] = np.ascontiguousarray(qw).view(np.uint8).reshape(-1)
-            if scales is not None:
-                scales[(e * 3 + p) * nsc : (e * 3 + p + 1) * nsc] = np.ascontiguousarray(qs).view(np.uint16).reshape(-1)
+
+    def pack(job):
+        idx, w = job
+        qw, qs = quantize(expert_qtype, w)
+        slab[idx * proj : (idx + 1) * proj] = np.ascontiguousarray(qw).view(np.uint8).reshape(-1)
+        if scales is not None:
+            scales[idx * nsc : (idx + 1) * nsc] = np.ascontiguousarray(qs).view(np.uint16).reshape(-1)
+
+    def draws():   # random draws stay sequential (fixed order); quantisation of each matrix runs on a worker
+        for e in range(E):
+            for p, (r, c) in enumerate(((F, H), (F, H), (H, F))):
+                yield e * 3 + p, rng.standard_normal((r, c), dtype=np.float32) * np.float32(std)
+
+    if E * F * H >= 1 << 22:
+        from concurrent.futures import ThreadPoolExecutor
+        import os
+        workers = min(16, len(os.sched_getaffinity(0)))
+        with ThreadPoolExecutor(workers) as pool:
+            pending = []
+            for job in draws():
+                pending.append(pool.submit(pack, job))
+                if len(pending) > 2 * workers:
+                    pending.pop(0).result()
+            for f in pending:
+                f.result()
+    else:
+        for job in draws():
+            pack(job)
     sg = make_matrix(shared_qtype, rng.standard_normal((S, H), dtype=np.float32) * np.float32(std))
     su = make_matrix(shared_qtype, rng.standard_normal((S, H), dtype=np.float32) * np.float32(std))
     sd = make_matrix(shared_qtype, rng.standard_normal((H, S), dtype=np.float32) * np.float32(std))

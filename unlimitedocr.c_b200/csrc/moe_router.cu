@@ -1,0 +1,220 @@
+// Router and dispatch-plan kernels.
+//
+// Router: per token, logits over the experts (fp16 inputs, f32 accumulation), f32 softmax with the
+// host C library's expf bits, serial f32 denominator in expert order, IEEE division, and greedy
+// top-k with ties to the lower expert id - the arithmetic of uocr_cpu_ref_moe_router_f32
+// (src/backend/cpu_ref/uocr_cpu_ref.c:388-466), so identical logits give identical ids and weights.
+//
+// Dispatch plan: stable counting sort of pair = token*K + slot by expert id.
+#include "expf_compat.h"
+#include "moe_common.cuh"
+
+namespace uocr {
+
+__constant__ uint64_t c_exp_tab[UOCR_EXPF_N];
+static bool g_tab_ready[64] = {false};
+
+static cudaError_t ensure_exp_table() {
+    int dev = 0;
+    cudaError_t err = cudaGetDevice(&dev);
+    if (err != cudaSuccess) return err;
+    if (dev < 64 && g_tab_ready[dev]) return cudaSuccess;
+    uint64_t tab[UOCR_EXPF_N];
+    uocr_expf_table_init(tab);
+    err = cudaMemcpyToSymbol(c_exp_tab, tab, sizeof tab);
+    if (err == cudaSuccess && dev < 64) g_tab_ready[dev] = true;
+    return err;
+}
+
+constexpr int kRouterThreads = 256;
+constexpr int kRouterWarps = kRouterThreads / 32;
+
+// TPB tokens per block.  Shared memory: x[TPB][H] f32, logits[TPB][E] f32, probs[TPB][E] f32.
+template <int TPB>
+__global__ void __launch_bounds__(kRouterThreads)
+router_kernel(const __half *__restrict__ hidden, const __half *__restrict__ router, const float *__restrict__ bias,
+              const float *__restrict__ injected, uint32_t n, uint32_t H, uint32_t E, uint32_t K, float scaling,
+              float *__restrict__ logits_out, float *__restrict__ probs_out, uint32_t *__restrict__ ids_out,
+              float *__restrict__ weights_out, uint32_t *__restrict__ status) {
+    extern __shared__ float smem[];
+    float *xs = smem;                         // [TPB][H]
+    float *ls = xs + (size_t)TPB * H;         // [TPB][E]
+    float *ps = ls + (size_t)TPB * E;         // [TPB][E]
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const uint32_t t0 = blockIdx.x * TPB;
+    const uint32_t nt = min((uint32_t)TPB, n - t0);
+
+    if (injected == nullptr) {
+        for (uint32_t i = tid; i < TPB * H; i += kRouterThreads) {
+            const uint32_t t = i / H;
+            xs[i] = t < nt ? __half2float(hidden[(size_t)(t0 + t) * H + (i - t * H)]) : 0.f;
+        }
+        __syncthreads();
+        for (uint32_t e = warp; e < E; e += kRouterWarps) {
+            float acc[TPB];
+#pragma unroll
+            for (int m = 0; m < TPB; ++m) acc[m] = 0.f;
+            row_dot<UOCR_QT_F16, TPB>(reinterpret_cast<const uint8_t *>(router + (size_t)e * H), nullptr, H, xs, (int)H,
+                                      lane, acc);
+#pragma unroll
+            for (int m = 0; m < TPB; ++m) {
+                const float v = warp_sum(acc[m]);
+                if (lane == 0) ls[m * E + e] = bias ? v + bias[e] : v;
+            }
+        }
+    } else {
+        for (uint32_t i = tid; i < nt * E; i += kRouterThreads) {
+            const uint32_t t = i / E, e = i - t * E;
+            const float v = injected[(size_t)(t0 + t) * E + e];
+            ls[t * E + e] = bias ? v + bias[e] : v;
+        }
+    }
+    __syncthreads();
+
+    // one warp per token: softmax + top-k
+    for (uint32_t t = warp; t < nt; t += kRouterWarps) {
+        const float *l = ls + t * E;
+        float *p = ps + t * E;
+        float mx = -INFINITY;
+        for (uint32_t e = lane; e < E; e += 32) mx = fmaxf(mx, l[e]);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        bool bad = !isfinite(mx);
+        for (uint32_t e = lane; e < E; e += 32) p[e] = uocr_expf_compat(__fsub_rn(l[e], mx), c_exp_tab);
+        __syncwarp();
+        float denom = 0.f;
+        if (lane == 0)
+            for (uint32_t e = 0; e < E; ++e) denom = __fadd_rn(denom, p[e]);   // serial, expert order
+        denom = __shfl_sync(0xffffffffu, denom, 0);
+        bad = bad || !(denom > 0.f) || !isfinite(denom);
+        for (uint32_t e = lane; e < E; e += 32) p[e] = __fdiv_rn(p[e], denom);
+        __syncwarp();
+        const size_t row = (size_t)(t0 + t);
+        if (logits_out) for (uint32_t e = lane; e < E; e += 32) logits_out[row * E + e] = l[e];
+        if (probs_out) for (uint32_t e = lane; e < E; e += 32) probs_out[row * E + e] = p[e];
+
+        // greedy top-k; `taken` bit i of a lane marks expert lane + 32*i as already selected
+        uint32_t taken = 0;
+        for (uint32_t slot = 0; slot < K; ++slot) {
+            float bp = -INFINITY;
+            uint32_t be = 0xffffffffu;
+            for (uint32_t e = lane, i = 0; e < E; e += 32, ++i) {
+                if ((taken >> i) & 1u) continue;
+                const float pe = p[e];
+                if (pe > bp || (pe == bp && e < be)) { bp = pe; be = e; }
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const float op = __shfl_xor_sync(0xffffffffu, bp, o);
+                const uint32_t oe = __shfl_xor_sync(0xffffffffu, be, o);
+                if (op > bp || (op == bp && oe < be)) { bp = op; be = oe; }
+            }
+            if (be == 0xffffffffu || !(bp >= 0.f)) bad = true;
+            if (be != 0xffffffffu && (be & 31u) == (uint32_t)lane) taken |= 1u << (be >> 5);
+            if (lane == 0) {
+                ids_out[row * K + slot] = bad ? 0xffffffffu : be;
+                weights_out[row * K + slot] = bad ? 0.f : __fmul_rn(bp, scaling);
+            }
+        }
+        if (bad && lane == 0) atomicOr(status, 1u);   // the CPU function returns failure here
+    }
+}
+
+cudaError_t launch_router(const DLayer &L, const __half *hidden, const float *injected, uint32_t n, float *logits,
+                          float *probs, uint32_t *ids, float *weights, uint32_t *status, cudaStream_t st,
+                          uint64_t *launches) {
+    if (n <= 32) {
+        const size_t smem = sizeof(float) * ((size_t)L.H + 2 * (size_t)L.E);
+        router_kernel<1><<<n, kRouterThreads, smem, st>>>(hidden, L.router, L.bias, injected, n, L.H, L.E, L.K,
+                                                          L.scaling, logits, probs, ids, weights, status);
+    } else {
+        constexpr int TPB = 8;
+        const size_t smem = sizeof(float) * TPB * ((size_t)L.H + 2 * (size_t)L.E);
+        if (smem > 160 * 1024) return cudaErrorInvalidValue;
+        router_kernel<TPB><<<(n + TPB - 1) / TPB, kRouterThreads, smem, st>>>(
+            hidden, L.router, L.bias, injected, n, L.H, L.E, L.K, L.scaling, logits, probs, ids, weights, status);
+    }
+    ++*launches;
+    return cudaGetLastError();
+}
+
+// ---------------------------------------------------------------------------------- plan
+// One block.  Thread t owns the contiguous pair range [t*seg, (t+1)*seg); per-thread per-expert
+// counts are scanned across threads so that every thread knows where its first pair of each
+// expert lands, then each thread walks its range in order.  The result is the stable sort.
+constexpr int kPlanThreads = 256;
+
+__global__ void __launch_bounds__(kPlanThreads)
+plan_kernel(const uint32_t *__restrict__ ids, uint32_t n_pairs, uint32_t E, uint32_t T, uint32_t *__restrict__ offsets,
+            uint32_t *__restrict__ pair_rows, uint32_t *__restrict__ inverse, uint32_t *__restrict__ active) {
+    extern __shared__ uint32_t cnt[];   // [T][E] then totals [E+1]
+    uint32_t *tot = cnt + (size_t)T * E;
+    const uint32_t tid = threadIdx.x;
+    const uint32_t seg = (n_pairs + T - 1) / T;
+    const uint32_t lo = min(tid * seg, n_pairs), hi = tid < T ? min(lo + seg, n_pairs) : lo;
+    for (uint32_t i = tid; i < T * E; i += kPlanThreads) cnt[i] = 0;
+    __syncthreads();
+    if (tid < T)
+        for (uint32_t p = lo; p < hi; ++p) {
+            const uint32_t e = ids[p];
+            if (e < E) cnt[tid * E + e]++;
+        }
+    __syncthreads();
+    for (uint32_t e = tid; e < E; e += kPlanThreads) {
+        uint32_t run = 0;
+        for (uint32_t t = 0; t < T; ++t) {
+            const uint32_t c = cnt[t * E + e];
+            cnt[t * E + e] = run;
+            run += c;
+        }
+        tot[e] = run;
+    }
+    __syncthreads();
+    if (tid == 0) {
+        uint32_t run = 0, na = 0;
+        for (uint32_t e = 0; e < E; ++e) {
+            const uint32_t c = tot[e];
+            offsets[e] = run;
+            tot[e] = run;
+            if (c) active[1 + na++] = e;
+            run += c;
+        }
+        offsets[E] = run;
+        active[0] = na;
+    }
+    __syncthreads();
+    if (tid < T)
+        for (uint32_t p = lo; p < hi; ++p) {
+            const uint32_t e = ids[p];
+            if (e < E) {
+                const uint32_t pos = tot[e] + cnt[tid * E + e]++;
+                pair_rows[pos] = p;
+                inverse[p] = pos;
+            } else {
+                inverse[p] = 0xffffffffu;
+            }
+        }
+}
+
+// Per-device set-up of this file's kernels; called once when a context is created.
+cudaError_t init_router_kernels() {
+    cudaError_t err = ensure_exp_table();
+    if (err != cudaSuccess) return err;
+    err = cudaFuncSetAttribute(router_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+    if (err != cudaSuccess) return err;
+    return cudaFuncSetAttribute(plan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
+}
+
+cudaError_t launch_dispatch_plan(const uint32_t *ids, uint32_t n, uint32_t K, uint32_t E, uint32_t *offsets,
+                                 uint32_t *pair_rows, uint32_t *inverse, uint32_t *active, cudaStream_t st,
+                                 uint64_t *launches) {
+    uint32_t T = 24576u / E;
+    if (T > (uint32_t)kPlanThreads) T = kPlanThreads;
+    if (T == 0) return cudaErrorInvalidValue;
+    const size_t smem = sizeof(uint32_t) * ((size_t)T * E + E + 1);
+    plan_kernel<<<1, kPlanThreads, smem, st>>>(ids, n * K, E, T, offsets, pair_rows, inverse, active);
+    ++*launches;
+    return cudaGetLastError();
+}
+
+}  // namespace uocr

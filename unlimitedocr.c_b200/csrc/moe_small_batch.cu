@@ -1,0 +1,262 @@
+// Small-batch MoE layer: one to a few dozen tokens per step.  The step is bound by reading the
+// selected experts' packed weights once, so the kernels are matrix-vector products on CUDA cores:
+// one warp per output row, 128-bit loads of the packed row, dequantisation in registers (no
+// dequantised copy of a weight ever exists), per-group scale applied to the group's partial sum,
+// f32 accumulation and a warp-shuffle reduction.
+//
+// Work is grouped per selected expert (dispatch plan), so a weight row is read once per step for
+// all tokens routed to that expert; activations of up to four tokens at a time sit in shared
+// memory as f32.
+//
+//   gate_up : mid[pair][i]   = fp16( silu(gate_e[i].x) * (up_e[i].x) )     (routed and shared)
+//   down    : down_out[pair][h] = down_e[h] . mid[pair]                      (f32 scratch)
+//   combine : out[t][h] = fp16( sum_slot w * down_out + shared_out + residual ), slot order
+//
+// Rounding contract as the reference's GPU kernels (src/backend/metal/kernels/decode_gemv_q4.metal:34-57,
+// :138-224): fp16 activations, scale applied per group partial, fp16 `mid`, f32 routed sum.
+#include "moe_common.cuh"
+
+namespace uocr {
+
+constexpr int kGemvThreads = 256;
+constexpr int kGemvWarps = kGemvThreads / 32;
+constexpr int kMaxM = 4;
+
+struct GroupSource {
+    // routed: rows are the pairs of one active expert; shared: rows are all tokens
+    const uint32_t *active;          // null => shared group
+    const uint32_t *expert_offsets;
+    const uint32_t *pair_rows;
+    uint32_t n_tokens;
+    uint32_t K;
+};
+
+struct GroupRows {
+    uint32_t count;
+    const uint32_t *pairs;   // null => identity (shared)
+    uint32_t expert;
+};
+
+__device__ __forceinline__ bool resolve_group(const GroupSource &g, uint32_t group_index, GroupRows &r) {
+    if (g.active == nullptr) {
+        r.count = g.n_tokens;
+        r.pairs = nullptr;
+        r.expert = 0;
+        return true;
+    }
+    if (group_index >= g.active[0]) return false;
+    r.expert = g.active[1 + group_index];
+    const uint32_t lo = g.expert_offsets[r.expert];
+    r.count = g.expert_offsets[r.expert + 1] - lo;
+    r.pairs = g.pair_rows + lo;
+    return r.count != 0;
+}
+
+template <int QT, int M>
+__device__ __forceinline__ void gate_up_rows(const uint8_t *gw, const __half *gs, const uint8_t *uw, const __half *us,
+                                             uint32_t cols, const float *xs, int lane, float (&g)[M], float (&u)[M]) {
+#pragma unroll
+    for (int m = 0; m < M; ++m) { g[m] = 0.f; u[m] = 0.f; }
+    row_dot<QT, M>(gw, gs, cols, xs, (int)cols, lane, g);
+    row_dot<QT, M>(uw, us, cols, xs, (int)cols, lane, u);
+#pragma unroll
+    for (int m = 0; m < M; ++m) { g[m] = warp_sum(g[m]); u[m] = warp_sum(u[m]); }
+}
+
+// grid.x covers the F (or S) output rows, one per warp; grid.y = group index.
+template <int QT>
+__global__ void __launch_bounds__(kGemvThreads)
+gate_up_kernel(GroupSource src, const __half *__restrict__ hidden, uint32_t H, uint32_t F,
+               const uint8_t *__restrict__ w_base, const __half *__restrict__ s_base, uint64_t expert_stride_bytes,
+               uint64_t up_offset_bytes, uint64_t expert_scale_stride, uint64_t up_scale_offset, uint32_t row_bytes,
+               __half *__restrict__ mid) {
+    extern __shared__ float xs[];   // [kMaxM][H]
+    GroupRows rows;
+    if (!resolve_group(src, blockIdx.y, rows)) return;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const uint32_t i = blockIdx.x * kGemvWarps + warp;          // output row
+    const uint32_t groups = H / UOCR_GROUP;
+    const uint8_t *gw = w_base + rows.expert * expert_stride_bytes + (size_t)i * row_bytes;
+    const uint8_t *uw = gw + up_offset_bytes;
+    const __half *gs = s_base ? s_base + rows.expert * expert_scale_stride + (size_t)i * groups : nullptr;
+    const __half *us = s_base ? gs + up_scale_offset : nullptr;
+
+    for (uint32_t r0 = 0; r0 < rows.count; r0 += kMaxM) {
+        const uint32_t mc = min((uint32_t)kMaxM, rows.count - r0);
+        __syncthreads();
+        for (uint32_t k = tid; k < mc * H; k += kGemvThreads) {
+            const uint32_t m = k / H, c = k - m * H;
+            const uint32_t pair = rows.pairs ? rows.pairs[r0 + m] : (r0 + m);
+            const uint32_t token = rows.pairs ? pair / src.K : pair;
+            xs[k] = __half2float(hidden[(size_t)token * H + c]);
+        }
+        __syncthreads();
+        if (i >= F) continue;
+        float g[kMaxM], u[kMaxM];
+        if (mc == 1) {
+            float g1[1], u1[1];
+            gate_up_rows<QT, 1>(gw, gs, uw, us, H, xs, lane, g1, u1);
+            g[0] = g1[0]; u[0] = u1[0];
+        } else if (mc == 2) {
+            float g2[2], u2[2];
+            gate_up_rows<QT, 2>(gw, gs, uw, us, H, xs, lane, g2, u2);
+            g[0] = g2[0]; u[0] = u2[0]; g[1] = g2[1]; u[1] = u2[1];
+        } else {
+            // rows beyond mc read stale shared memory; their results are not stored
+            gate_up_rows<QT, kMaxM>(gw, gs, uw, us, H, xs, lane, g, u);
+        }
+        if (lane == 0) {
+            for (uint32_t m = 0; m < mc; ++m) {
+                const uint32_t dst_row = rows.pairs ? rows.pairs[r0 + m] : (r0 + m);
+                mid[(size_t)dst_row * F + i] = __float2half_rn(silu_f32(g[m]) * u[m]);
+            }
+        }
+    }
+}
+
+// down: grid.x covers the H output rows (one per warp), grid.y = group; x = mid rows (fp16, global).
+template <int QT>
+__global__ void __launch_bounds__(kGemvThreads)
+down_kernel(GroupSource src, const __half *__restrict__ mid, uint32_t H, uint32_t F,
+            const uint8_t *__restrict__ w_base, const __half *__restrict__ s_base, uint64_t expert_stride_bytes,
+            uint64_t expert_scale_stride, uint32_t row_bytes, float *__restrict__ out) {
+    extern __shared__ float xs[];   // [kMaxM][F]
+    GroupRows rows;
+    if (!resolve_group(src, blockIdx.y, rows)) return;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const uint32_t h = blockIdx.x * kGemvWarps + warp;
+    const uint32_t groups = F / UOCR_GROUP;
+    const uint8_t *dw = w_base + rows.expert * expert_stride_bytes + (size_t)h * row_bytes;
+    const __half *ds = s_base ? s_base + rows.expert * expert_scale_stride + (size_t)h * groups : nullptr;
+
+    for (uint32_t r0 = 0; r0 < rows.count; r0 += kMaxM) {
+        const uint32_t mc = min((uint32_t)kMaxM, rows.count - r0);
+        __syncthreads();
+        for (uint32_t k = tid; k < mc * F; k += kGemvThreads) {
+            const uint32_t m = k / F, c = k - m * F;
+            const uint32_t row = rows.pairs ? rows.pairs[r0 + m] : (r0 + m);
+            xs[k] = __half2float(mid[(size_t)row * F + c]);
+        }
+        __syncthreads();
+        if (h >= H) continue;
+        float acc[kMaxM];
+#pragma unroll
+        for (int m = 0; m < kMaxM; ++m) acc[m] = 0.f;
+        if (mc == 1) {
+            float a1[1] = {0.f};
+            row_dot<QT, 1>(dw, ds, F, xs, (int)F, lane, a1);
+            acc[0] = a1[0];
+        } else if (mc == 2) {
+            float a2[2] = {0.f, 0.f};
+            row_dot<QT, 2>(dw, ds, F, xs, (int)F, lane, a2);
+            acc[0] = a2[0]; acc[1] = a2[1];
+        } else {
+            row_dot<QT, kMaxM>(dw, ds, F, xs, (int)F, lane, acc);
+        }
+#pragma unroll
+        for (int m = 0; m < kMaxM; ++m) acc[m] = warp_sum(acc[m]);
+        if (lane == 0)
+            for (uint32_t m = 0; m < mc; ++m) {
+                const uint32_t row = rows.pairs ? rows.pairs[r0 + m] : (r0 + m);
+                out[(size_t)row * H + h] = acc[m];
+            }
+    }
+}
+
+// out[t][h] = fp16( fma chain over slots of w*down_out, + shared, + residual ): the order of
+// uocr_cpu_ref_moe_swiglu_f32 (src/backend/cpu_ref/uocr_cpu_ref.c:552-576), residual as the GPU
+// layer adds it.  An id >= E contributes nothing.
+__global__ void combine_kernel(const float *__restrict__ down_out, const float *__restrict__ shared_out,
+                               const __half *__restrict__ residual, const uint32_t *__restrict__ ids,
+                               const float *__restrict__ weights, uint32_t n, uint32_t H, uint32_t K, uint32_t E,
+                               __half *__restrict__ out) {
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (size_t)n * H) return;
+    const uint32_t t = (uint32_t)(idx / H), h = (uint32_t)(idx - (size_t)t * H);
+    float acc = 0.f;
+    for (uint32_t s = 0; s < K; ++s) {
+        const uint32_t pair = t * K + s;
+        if (ids[pair] < E) acc = fmaf(weights[pair], down_out[(size_t)pair * H + h], acc);
+    }
+    acc += shared_out[idx];
+    if (residual) acc += __half2float(residual[idx]);
+    out[idx] = __float2half_rn(acc);
+}
+
+template <int QT>
+static void launch_gate_up(const GroupSource &src, uint32_t n_groups, const __half *hidden, uint32_t H, uint32_t F,
+                           const uint8_t *w, const __half *s, uint64_t stride, uint64_t up_off, uint64_t sstride,
+                           uint64_t sup_off, uint32_t row_bytes, __half *mid, cudaStream_t st) {
+    dim3 grid((F + kGemvWarps - 1) / kGemvWarps, n_groups);
+    gate_up_kernel<QT><<<grid, kGemvThreads, sizeof(float) * kMaxM * H, st>>>(src, hidden, H, F, w, s, stride, up_off,
+                                                                              sstride, sup_off, row_bytes, mid);
+}
+
+template <int QT>
+static void launch_down(const GroupSource &src, uint32_t n_groups, const __half *mid, uint32_t H, uint32_t F,
+                        const uint8_t *w, const __half *s, uint64_t stride, uint64_t sstride, uint32_t row_bytes,
+                        float *out, cudaStream_t st) {
+    dim3 grid((H + kGemvWarps - 1) / kGemvWarps, n_groups);
+    down_kernel<QT><<<grid, kGemvThreads, sizeof(float) * kMaxM * F, st>>>(src, mid, H, F, w, s, stride, sstride,
+                                                                           row_bytes, out);
+}
+
+#define UOCR_QT_SWITCH(qt, CALL)                                     \
+    switch (qt) {                                                    \
+        case UOCR_QT_Q4: { constexpr int QT = UOCR_QT_Q4; CALL; } break;  \
+        case UOCR_QT_Q8: { constexpr int QT = UOCR_QT_Q8; CALL; } break;  \
+        default: { constexpr int QT = UOCR_QT_F16; CALL; } break;         \
+    }
+
+static uint32_t packed_row_bytes(int qt, uint32_t cols) {
+    return qt == UOCR_QT_F16 ? cols * 2u : (qt == UOCR_QT_Q8 ? cols : cols / 2u);
+}
+
+cudaError_t init_small_batch_kernels() {
+    // dynamic shared memory stays below 48 KB for every supported shape (4 rows x 2048 f32 = 32 KB)
+    return cudaSuccess;
+}
+
+cudaError_t launch_small_batch_layer(const DLayer &L, const Scratch &S, const __half *hidden, const __half *residual,
+                                     uint32_t n, __half *out, cudaStream_t st, uint64_t *launches) {
+    const uint32_t H = L.H, F = L.F, Sd = L.S, K = L.K, E = L.E;
+    if ((size_t)kMaxM * (H > Sd ? H : Sd) * sizeof(float) > 48 * 1024) return cudaErrorInvalidValue;
+    GroupSource routed{S.active, S.expert_offsets, S.pair_rows, n, K};
+    GroupSource shared{nullptr, nullptr, nullptr, n, K};
+    const uint32_t max_groups = (uint64_t)n * K < E ? n * K : E;
+    const int qt = L.expert_qtype;
+
+    // routed gate/up and shared gate/up
+    UOCR_QT_SWITCH(qt, (launch_gate_up<QT>(routed, max_groups, hidden, H, F, L.expert_w, L.expert_s,
+                                           L.expert_stride_bytes, L.up_offset_bytes, L.expert_scale_stride,
+                                           L.up_scale_offset, packed_row_bytes(qt, H), S.mid, st)));
+    ++*launches;
+    {
+        const DMatrix &g = L.shared_gate, &u = L.shared_up;
+        // gate and up of the shared MLP are separate tensors: express "up" as an offset from "gate"
+        const int64_t up_off = (const uint8_t *)u.w - (const uint8_t *)g.w;
+        const int64_t sup_off = g.s ? (u.s - g.s) : 0;
+        UOCR_QT_SWITCH(g.qtype, (launch_gate_up<QT>(shared, 1, hidden, H, Sd, g.w, g.s, 0, (uint64_t)up_off, 0,
+                                                    (uint64_t)sup_off, g.row_bytes, S.shared_mid, st)));
+        ++*launches;
+    }
+    // down
+    UOCR_QT_SWITCH(qt, (launch_down<QT>(routed, max_groups, S.mid, H, F, L.expert_w + L.down_offset_bytes,
+                                        L.expert_s ? L.expert_s + L.down_scale_offset : nullptr,
+                                        L.expert_stride_bytes, L.expert_scale_stride, packed_row_bytes(qt, F),
+                                        (float *)S.down_out, st)));
+    ++*launches;
+    {
+        const DMatrix &d = L.shared_down;
+        UOCR_QT_SWITCH(d.qtype, (launch_down<QT>(shared, 1, S.shared_mid, H, Sd, d.w, d.s, 0, 0, d.row_bytes,
+                                                 S.shared_out, st)));
+        ++*launches;
+    }
+    const size_t total = (size_t)n * H;
+    combine_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>((const float *)S.down_out, S.shared_out, residual,
+                                                                    S.top_ids, S.top_weights, n, H, K, E, out);
+    ++*launches;
+    return cudaGetLastError();
+}
+
+}  // namespace uocr

@@ -1,0 +1,543 @@
+// Host side of the C ABI in include/uocr_cuda_moe.h: context, weight upload, scratch arena and the
+// per-call dispatch of the MoE layer onto the kernel files.  Plain CUDA runtime; no allocation on
+// the forward path.
+#include "../../include/uocr_cuda_moe.h"
+
+#include <cmath>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <vector>
+
+#include "moe_common.cuh"
+
+namespace uocr {
+cudaError_t init_router_kernels();
+cudaError_t init_small_batch_kernels();
+}  // namespace uocr
+
+using uocr::DLayer;
+using uocr::DMatrix;
+using uocr::Scratch;
+
+struct uocr_cuda_context {
+    int device = 0;
+    cudaStream_t own_stream = nullptr;
+    cudaStream_t stream = nullptr;
+    std::vector<DLayer> layers;
+    std::vector<void *> weight_allocs;
+    uint64_t weight_bytes = 0;
+    // arena
+    uint8_t *arena = nullptr;
+    uint64_t arena_bytes = 0;
+    uint32_t token_capacity = 0;
+    uint32_t *status = nullptr;        // device status word
+    uint32_t *h_status = nullptr;      // pinned mirror
+    __half *h_in = nullptr;            // pinned staging for the host-buffer calls
+    __half *h_res = nullptr;
+    __half *h_out = nullptr;
+    uint32_t *h_ids = nullptr;
+    float *h_wts = nullptr;
+    uint64_t launches = 0;
+    char last_error[1024] = {0};
+};
+
+static thread_local char g_create_error[1024];
+
+static int fail(uocr_cuda_context *ctx, char *error, size_t error_size, const char *fmt, ...) {
+    char buf[1024];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof buf, fmt, ap);
+    va_end(ap);
+    if (ctx) snprintf(ctx->last_error, sizeof ctx->last_error, "%s", buf);
+    else snprintf(g_create_error, sizeof g_create_error, "%s", buf);
+    if (error && error_size) snprintf(error, error_size, "%s", buf);
+    return 0;
+}
+
+#define CU_TRY(ctx, call)                                                                             \
+    do {                                                                                              \
+        cudaError_t e_ = (call);                                                                      \
+        if (e_ != cudaSuccess)                                                                        \
+            return fail(ctx, error, error_size, "%s failed: %s", #call, cudaGetErrorString(e_));      \
+    } while (0)
+
+static uint64_t align_up(uint64_t v, uint64_t a) { return (v + a - 1) / a * a; }
+
+static uint64_t packed_bytes(int qt, uint64_t rows, uint64_t cols) {
+    return qt == UOCR_QT_F16 ? rows * cols * 2 : (qt == UOCR_QT_Q8 ? rows * cols : rows * cols / 2);
+}
+
+static bool qtype_ok(int qt) { return qt == UOCR_QT_F16 || qt == UOCR_QT_Q8 || qt == UOCR_QT_Q4; }
+
+// ------------------------------------------------------------------------------- backend
+extern "C" int uocr_cuda_is_available(void) {
+    int n = 0;
+    return cudaGetDeviceCount(&n) == cudaSuccess && n > 0;
+}
+
+extern "C" const char *uocr_cuda_backend_name(void) { return "cuda"; }
+
+extern "C" int uocr_cuda_device_count(void) {
+    int n = 0;
+    return cudaGetDeviceCount(&n) == cudaSuccess ? n : 0;
+}
+
+extern "C" uocr_cuda_context *uocr_cuda_context_create(const char *resource_path, char *error, size_t error_size) {
+    (void)resource_path;
+    int n = 0;
+    cudaError_t e = cudaGetDeviceCount(&n);
+    if (e != cudaSuccess || n == 0) {
+        fail(nullptr, error, error_size, "no CUDA device available: %s",
+             e == cudaSuccess ? "device count is 0" : cudaGetErrorString(e));
+        return nullptr;
+    }
+    uocr_cuda_context *ctx = new uocr_cuda_context();
+    cudaDeviceProp prop;
+    if ((e = cudaGetDevice(&ctx->device)) != cudaSuccess ||
+        (e = cudaGetDeviceProperties(&prop, ctx->device)) != cudaSuccess) {
+        fail(nullptr, error, error_size, "cannot query the CUDA device: %s", cudaGetErrorString(e));
+        delete ctx;
+        return nullptr;
+    }
+    if (prop.major != 10) {
+        fail(nullptr, error, error_size, "device %d (%s) is compute capability %d.%d; this backend is built for sm_100a only",
+             ctx->device, prop.name, prop.major, prop.minor);
+        delete ctx;
+        return nullptr;
+    }
+    if ((e = cudaStreamCreateWithFlags(&ctx->own_stream, cudaStreamNonBlocking)) != cudaSuccess ||
+        (e = cudaMalloc(&ctx->status, 256)) != cudaSuccess ||
+        (e = cudaMemset(ctx->status, 0, 256)) != cudaSuccess ||
+        (e = cudaMallocHost(&ctx->h_status, 256)) != cudaSuccess ||
+        (e = uocr::init_router_kernels()) != cudaSuccess || (e = uocr::init_small_batch_kernels()) != cudaSuccess) {
+        fail(nullptr, error, error_size, "CUDA context set-up failed: %s", cudaGetErrorString(e));
+        uocr_cuda_context_destroy(ctx);
+        return nullptr;
+    }
+    ctx->stream = ctx->own_stream;
+    return ctx;
+}
+
+extern "C" void uocr_cuda_context_release_runtime_arenas(uocr_cuda_context *ctx) {
+    if (!ctx) return;
+    cudaFree(ctx->arena);
+    ctx->arena = nullptr;
+    ctx->arena_bytes = 0;
+    ctx->token_capacity = 0;
+    cudaFreeHost(ctx->h_in); cudaFreeHost(ctx->h_res); cudaFreeHost(ctx->h_out);
+    cudaFreeHost(ctx->h_ids); cudaFreeHost(ctx->h_wts);
+    ctx->h_in = ctx->h_res = ctx->h_out = nullptr;
+    ctx->h_ids = nullptr;
+    ctx->h_wts = nullptr;
+}
+
+extern "C" void uocr_cuda_context_unmap_model(uocr_cuda_context *ctx) {
+    if (!ctx) return;
+    for (void *p : ctx->weight_allocs) cudaFree(p);
+    ctx->weight_allocs.clear();
+    ctx->layers.clear();
+    ctx->weight_bytes = 0;
+}
+
+extern "C" void uocr_cuda_context_destroy(uocr_cuda_context *ctx) {
+    if (!ctx) return;
+    cudaSetDevice(ctx->device);
+    if (ctx->own_stream) cudaStreamSynchronize(ctx->own_stream);
+    uocr_cuda_context_release_runtime_arenas(ctx);
+    uocr_cuda_context_unmap_model(ctx);
+    cudaFree(ctx->status);
+    cudaFreeHost(ctx->h_status);
+    if (ctx->own_stream) cudaStreamDestroy(ctx->own_stream);
+    delete ctx;
+}
+
+extern "C" const char *uocr_cuda_context_last_error(const uocr_cuda_context *ctx) {
+    return ctx ? ctx->last_error : g_create_error;
+}
+
+extern "C" int uocr_cuda_context_set_stream(uocr_cuda_context *ctx, void *cuda_stream) {
+    if (!ctx) return 0;
+    ctx->stream = cuda_stream ? (cudaStream_t)cuda_stream : ctx->own_stream;
+    return 1;
+}
+
+extern "C" int uocr_cuda_context_synchronize(uocr_cuda_context *ctx, char *error, size_t error_size) {
+    if (!ctx) return fail(nullptr, error, error_size, "null context");
+    CU_TRY(ctx, cudaMemcpyAsync(ctx->h_status, ctx->status, sizeof(uint32_t), cudaMemcpyDeviceToHost, ctx->stream));
+    CU_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+    if (*ctx->h_status != 0) {
+        const uint32_t st = *ctx->h_status;
+        cudaMemsetAsync(ctx->status, 0, sizeof(uint32_t), ctx->stream);
+        return fail(ctx, error, error_size,
+                    "device status 0x%x: %s", st,
+                    (st & 1u) ? "router met a non-finite logit or an empty softmax (the CPU path rejects this input too)"
+                              : "kernel reported an internal error");
+    }
+    return 1;
+}
+
+extern "C" uint64_t uocr_cuda_context_kernel_launches(const uocr_cuda_context *ctx) { return ctx ? ctx->launches : 0; }
+extern "C" uint64_t uocr_cuda_context_model_view_bytes(const uocr_cuda_context *ctx) { return ctx ? ctx->weight_bytes : 0; }
+extern "C" uint64_t uocr_cuda_context_moe_scratch_bytes(const uocr_cuda_context *ctx) { return ctx ? ctx->arena_bytes : 0; }
+extern "C" uint32_t uocr_cuda_context_moe_layer_count(const uocr_cuda_context *ctx) {
+    return ctx ? (uint32_t)ctx->layers.size() : 0;
+}
+
+// ----------------------------------------------------------------------------- map model
+static int upload(uocr_cuda_context *ctx, const void *host, uint64_t bytes, void **out, char *error, size_t error_size) {
+    void *d = nullptr;
+    CU_TRY(ctx, cudaMalloc(&d, bytes));
+    ctx->weight_allocs.push_back(d);
+    CU_TRY(ctx, cudaMemcpy(d, host, bytes, cudaMemcpyHostToDevice));
+    ctx->weight_bytes += bytes;
+    *out = d;
+    return 1;
+}
+
+static int check_matrix(uocr_cuda_context *ctx, const uocr_cuda_matrix &m, uint32_t rows, uint32_t cols, const char *name,
+                        char *error, size_t error_size) {
+    if (!qtype_ok(m.qtype)) return fail(ctx, error, error_size, "%s: unsupported qtype %d", name, m.qtype);
+    if (m.rows != rows || m.cols != cols)
+        return fail(ctx, error, error_size, "%s: shape [%u,%u] does not match the layer ([%u,%u] expected)", name, m.rows,
+                    m.cols, rows, cols);
+    if (!m.qweight) return fail(ctx, error, error_size, "%s: null weight pointer", name);
+    if (m.qtype != UOCR_QT_F16 && !m.qscale) return fail(ctx, error, error_size, "%s: quantised tensor without scales", name);
+    return 1;
+}
+
+extern "C" int uocr_cuda_context_map_moe_layer(uocr_cuda_context *ctx, const uocr_cuda_moe_layer_desc *d,
+                                               uint32_t *out_layer_index, char *error, size_t error_size) {
+    if (!ctx || !d) return fail(ctx, error, error_size, "null context or layer descriptor");
+    const uint32_t H = d->hidden_size, E = d->n_experts, K = d->top_k, F = d->expert_intermediate,
+                   S = d->shared_intermediate;
+    // argument rules of moe_validate_common (src/backend/cpu_ref/uocr_cpu_ref.c:357-377) plus the format's
+    if (H == 0 || E == 0 || K == 0 || F == 0 || S == 0) return fail(ctx, error, error_size, "zero layer dimension");
+    if (K > E) return fail(ctx, error, error_size, "top_k %u exceeds n_experts %u", K, E);
+    if (E > 256 || K > 16) return fail(ctx, error, error_size, "unsupported router size: n_experts %u (max 256), top_k %u (max 16)", E, K);
+    if (!(d->routed_scaling_factor >= 0.0f) || !std::isfinite(d->routed_scaling_factor))
+        return fail(ctx, error, error_size, "routed_scaling_factor must be finite and >= 0");
+    if (H % UOCR_GROUP || F % UOCR_GROUP || S % UOCR_GROUP)
+        return fail(ctx, error, error_size, "hidden (%u), expert (%u) and shared (%u) widths must be multiples of 64", H, F, S);
+    if (H > 2048 || F > 2048 || S > 2048)
+        return fail(ctx, error, error_size, "layer widths above 2048 are not supported (hidden %u, expert %u, shared %u)", H, F, S);
+    if (!d->router_weight_f16) return fail(ctx, error, error_size, "null router weight");
+    if (!qtype_ok(d->expert_qtype)) return fail(ctx, error, error_size, "unsupported expert qtype %d", d->expert_qtype);
+    if (!d->expert_qweight) return fail(ctx, error, error_size, "null expert weight slab");
+    if (d->expert_qtype != UOCR_QT_F16 && !d->expert_qscale) return fail(ctx, error, error_size, "quantised expert slab without scales");
+    if (!check_matrix(ctx, d->shared_gate, S, H, "shared gate", error, error_size) ||
+        !check_matrix(ctx, d->shared_up, S, H, "shared up", error, error_size) ||
+        !check_matrix(ctx, d->shared_down, H, S, "shared down", error, error_size))
+        return 0;
+    if (d->shared_gate.qtype != d->shared_up.qtype)
+        return fail(ctx, error, error_size, "shared gate and up projections must share one qtype");
+
+    const int qt = d->expert_qtype;
+    const uint64_t proj = packed_bytes(qt, F, H);
+    const uint64_t proj_scales = qt == UOCR_QT_F16 ? 0 : (uint64_t)F * (H / UOCR_GROUP);
+    DLayer L{};
+    L.H = H; L.E = E; L.K = K; L.F = F; L.S = S;
+    L.scaling = d->routed_scaling_factor;
+    L.expert_qtype = qt;
+    L.expert_stride_bytes = d->expert_stride_bytes ? d->expert_stride_bytes : 3 * proj;
+    L.up_offset_bytes = d->up_offset_bytes ? d->up_offset_bytes : proj;
+    L.down_offset_bytes = d->down_offset_bytes ? d->down_offset_bytes : 2 * proj;
+    L.expert_scale_stride = d->expert_scale_stride_values ? d->expert_scale_stride_values : 3 * proj_scales;
+    L.up_scale_offset = d->up_scale_offset_values ? d->up_scale_offset_values : proj_scales;
+    L.down_scale_offset = d->down_scale_offset_values ? d->down_scale_offset_values : 2 * proj_scales;
+    // the slab consistency rules the reference host enforces before binding a layer
+    // (src/backend/metal/uocr_metal.m:3037-3154): projections inside the expert stride, 16-byte alignment
+    if (L.up_offset_bytes < proj || L.down_offset_bytes < L.up_offset_bytes + proj ||
+        L.expert_stride_bytes < L.down_offset_bytes + proj || (L.expert_stride_bytes | L.up_offset_bytes | L.down_offset_bytes) % 16)
+        return fail(ctx, error, error_size, "inconsistent expert slab strides");
+    if (qt != UOCR_QT_F16 && (L.up_scale_offset < proj_scales || L.down_scale_offset < L.up_scale_offset + proj_scales ||
+                              L.expert_scale_stride < L.down_scale_offset + proj_scales ||
+                              (L.expert_scale_stride | L.up_scale_offset | L.down_scale_offset) % 8))
+        return fail(ctx, error, error_size, "inconsistent expert scale slab strides");
+
+    CU_TRY(ctx, cudaSetDevice(ctx->device));
+    void *p = nullptr;
+    if (!upload(ctx, d->router_weight_f16, (uint64_t)E * H * 2, &p, error, error_size)) return 0;
+    L.router = (const __half *)p;
+    if (d->router_logit_bias) {
+        if (!upload(ctx, d->router_logit_bias, (uint64_t)E * 4, &p, error, error_size)) return 0;
+        L.bias = (const float *)p;
+    }
+    if (!upload(ctx, d->expert_qweight, (uint64_t)E * L.expert_stride_bytes, &p, error, error_size)) return 0;
+    L.expert_w = (const uint8_t *)p;
+    if (qt != UOCR_QT_F16) {
+        if (!upload(ctx, d->expert_qscale, (uint64_t)E * L.expert_scale_stride * 2, &p, error, error_size)) return 0;
+        L.expert_s = (const __half *)p;
+    }
+    // shared gate and up go into one allocation (gate first) so kernels address "up" as a positive offset
+    {
+        const int sq = d->shared_gate.qtype;
+        const uint64_t wb = packed_bytes(sq, S, H), sb = sq == UOCR_QT_F16 ? 0 : (uint64_t)S * (H / UOCR_GROUP) * 2;
+        uint8_t *dw = nullptr;
+        CU_TRY(ctx, cudaMalloc(&dw, 2 * wb));
+        ctx->weight_allocs.push_back(dw);
+        CU_TRY(ctx, cudaMemcpy(dw, d->shared_gate.qweight, wb, cudaMemcpyHostToDevice));
+        CU_TRY(ctx, cudaMemcpy(dw + wb, d->shared_up.qweight, wb, cudaMemcpyHostToDevice));
+        uint8_t *ds = nullptr;
+        if (sb) {
+            CU_TRY(ctx, cudaMalloc(&ds, 2 * sb));
+            ctx->weight_allocs.push_back(ds);
+            CU_TRY(ctx, cudaMemcpy(ds, d->shared_gate.qscale, sb, cudaMemcpyHostToDevice));
+            CU_TRY(ctx, cudaMemcpy(ds + sb, d->shared_up.qscale, sb, cudaMemcpyHostToDevice));
+        }
+        ctx->weight_bytes += 2 * (wb + sb);
+        const uint32_t rb = (uint32_t)(wb / S);
+        L.shared_gate = DMatrix{dw, (const __half *)ds, S, H, rb, sq};
+        L.shared_up = DMatrix{dw + wb, ds ? (const __half *)(ds + sb) : nullptr, S, H, rb, sq};
+    }
+    {
+        const int sq = d->shared_down.qtype;
+        const uint64_t wb = packed_bytes(sq, H, S), sb = sq == UOCR_QT_F16 ? 0 : (uint64_t)H * (S / UOCR_GROUP) * 2;
+        if (!upload(ctx, d->shared_down.qweight, wb, &p, error, error_size)) return 0;
+        void *ps = nullptr;
+        if (sb && !upload(ctx, d->shared_down.qscale, sb, &ps, error, error_size)) return 0;
+        L.shared_down = DMatrix{(const uint8_t *)p, (const __half *)ps, H, S, (uint32_t)(wb / H), sq};
+    }
+    if (!ctx->layers.empty()) {
+        const DLayer &f = ctx->layers.front();
+        if (f.H != H) return fail(ctx, error, error_size, "all mapped layers must share hidden_size (%u vs %u)", f.H, H);
+    }
+    ctx->layers.push_back(L);
+    if (out_layer_index) *out_layer_index = (uint32_t)ctx->layers.size() - 1;
+    return 1;
+}
+
+// ----------------------------------------------------------------------------------- arena
+struct ArenaLayout {
+    uint64_t logits, probs, ids, weights, offsets, pair_rows, inverse, active, mid, shared_mid, down_out, shared_out,
+        stack0, stack1, d_in, d_res, d_out, total;
+};
+
+// down products are f32 while the call is small enough to take the matrix-vector path, fp16 beyond
+static bool small_batch(uint32_t n) { return n <= 256; }
+
+static ArenaLayout layout_arena(uint32_t H, uint32_t E, uint32_t K, uint32_t F, uint32_t S, uint32_t n) {
+    ArenaLayout a{};
+    uint64_t off = 0;
+    auto take = [&](uint64_t bytes) { uint64_t o = off; off = align_up(off + bytes, 256); return o; };
+    const uint64_t pairs = (uint64_t)n * K;
+    a.logits = take((uint64_t)n * E * 4);
+    a.probs = take((uint64_t)n * E * 4);
+    a.ids = take(pairs * 4);
+    a.weights = take(pairs * 4);
+    a.offsets = take((uint64_t)(E + 1) * 4);
+    a.pair_rows = take(pairs * 4);
+    a.inverse = take(pairs * 4);
+    a.active = take((uint64_t)(E + 1) * 4);
+    a.mid = take(pairs * F * 2);
+    a.shared_mid = take((uint64_t)n * S * 2);
+    a.down_out = take(pairs * H * (small_batch(n) ? 4 : 2));
+    a.shared_out = take((uint64_t)n * H * 4);
+    a.stack0 = take((uint64_t)n * H * 2);
+    a.stack1 = take((uint64_t)n * H * 2);
+    a.d_in = take((uint64_t)n * H * 2);
+    a.d_res = take((uint64_t)n * H * 2);
+    a.d_out = take((uint64_t)n * H * 2);
+    a.total = off;
+    return a;
+}
+
+extern "C" uint64_t uocr_cuda_moe_scratch_size(uint32_t H, uint32_t E, uint32_t K, uint32_t F, uint32_t S,
+                                               uint32_t token_capacity) {
+    if (!H || !E || !K || !F || !S || !token_capacity) return 0;
+    return layout_arena(H, E, K, F, S, token_capacity).total;
+}
+
+struct LayerDims { uint32_t H = 0, E = 0, K = 0, F = 0, S = 0; };
+
+static LayerDims max_dims(const uocr_cuda_context *ctx) {
+    LayerDims m;
+    for (const DLayer &L : ctx->layers) {
+        m.H = L.H > m.H ? L.H : m.H; m.E = L.E > m.E ? L.E : m.E; m.K = L.K > m.K ? L.K : m.K;
+        m.F = L.F > m.F ? L.F : m.F; m.S = L.S > m.S ? L.S : m.S;
+    }
+    return m;
+}
+
+extern "C" int uocr_cuda_context_allocate_runtime_arenas(uocr_cuda_context *ctx, uint32_t batch_slots,
+                                                         uint32_t token_capacity, char *error, size_t error_size) {
+    if (!ctx) return fail(nullptr, error, error_size, "null context");
+    if (batch_slots != 1) return fail(ctx, error, error_size, "batch_slots must be 1 (one request per context, as the reference engine)");
+    if (token_capacity == 0) return fail(ctx, error, error_size, "token_capacity must be positive");
+    if (ctx->layers.empty()) return fail(ctx, error, error_size, "map the model's MoE layers before sizing the arenas");
+    CU_TRY(ctx, cudaSetDevice(ctx->device));
+    uocr_cuda_context_release_runtime_arenas(ctx);
+    const LayerDims m = max_dims(ctx);
+    // both regimes must fit: the largest small-batch call and the full capacity
+    uint64_t bytes = layout_arena(m.H, m.E, m.K, m.F, m.S, token_capacity).total;
+    if (!small_batch(token_capacity)) {
+        const uint64_t b2 = layout_arena(m.H, m.E, m.K, m.F, m.S, 256).total;
+        bytes = b2 > bytes ? b2 : bytes;
+    }
+    CU_TRY(ctx, cudaMalloc(&ctx->arena, bytes));
+    ctx->arena_bytes = bytes;
+    ctx->token_capacity = token_capacity;
+    const size_t act = (size_t)token_capacity * m.H * 2;
+    CU_TRY(ctx, cudaMallocHost(&ctx->h_in, act));
+    CU_TRY(ctx, cudaMallocHost(&ctx->h_res, act));
+    CU_TRY(ctx, cudaMallocHost(&ctx->h_out, act));
+    CU_TRY(ctx, cudaMallocHost(&ctx->h_ids, (size_t)token_capacity * m.K * 4));
+    CU_TRY(ctx, cudaMallocHost(&ctx->h_wts, (size_t)token_capacity * m.K * 4));
+    return 1;
+}
+
+static Scratch carve(const uocr_cuda_context *ctx, const DLayer &L, uint32_t n, ArenaLayout *out_layout = nullptr) {
+    const ArenaLayout a = layout_arena(L.H, L.E, L.K, L.F, L.S, n);
+    uint8_t *b = ctx->arena;
+    Scratch s{};
+    s.logits = (float *)(b + a.logits); s.probs = (float *)(b + a.probs);
+    s.top_ids = (uint32_t *)(b + a.ids); s.top_weights = (float *)(b + a.weights);
+    s.expert_offsets = (uint32_t *)(b + a.offsets); s.pair_rows = (uint32_t *)(b + a.pair_rows);
+    s.inverse = (uint32_t *)(b + a.inverse); s.active = (uint32_t *)(b + a.active);
+    s.mid = (__half *)(b + a.mid); s.shared_mid = (__half *)(b + a.shared_mid);
+    s.down_out = b + a.down_out; s.shared_out = (float *)(b + a.shared_out);
+    s.status = ctx->status;
+    if (out_layout) *out_layout = a;
+    return s;
+}
+
+static int check_call(uocr_cuda_context *ctx, uint32_t layer, uint32_t n, char *error, size_t error_size) {
+    if (!ctx) return fail(nullptr, error, error_size, "null context");
+    if (layer >= ctx->layers.size()) return fail(ctx, error, error_size, "layer index %u out of range (%zu mapped)", layer, ctx->layers.size());
+    if (n == 0) return fail(ctx, error, error_size, "n_tokens must be positive");
+    if (!ctx->arena || n > ctx->token_capacity)
+        return fail(ctx, error, error_size, "n_tokens %u exceeds the arena capacity %u (call uocr_cuda_context_allocate_runtime_arenas)", n, ctx->token_capacity);
+    return 1;
+}
+
+// ------------------------------------------------------------------------------ operators
+extern "C" int uocr_cuda_moe_router(uocr_cuda_context *ctx, uint32_t layer, const void *d_hidden, const float *d_injected,
+                                    uint32_t n, float *d_logits, float *d_probs, uint32_t *d_ids, float *d_weights,
+                                    char *error, size_t error_size) {
+    if (!check_call(ctx, layer, n, error, error_size)) return 0;
+    if ((!d_hidden && !d_injected) || !d_ids || !d_weights) return fail(ctx, error, error_size, "null router argument");
+    const DLayer &L = ctx->layers[layer];
+    CU_TRY(ctx, uocr::launch_router(L, (const __half *)d_hidden, d_injected, n, d_logits, d_probs, d_ids, d_weights,
+                                    ctx->status, ctx->stream, &ctx->launches));
+    return 1;
+}
+
+extern "C" int uocr_cuda_moe_dispatch_plan(uocr_cuda_context *ctx, const uint32_t *d_ids, uint32_t n, uint32_t K, uint32_t E,
+                                           uint32_t *d_offsets, uint32_t *d_pair_rows, uint32_t *d_inverse, char *error,
+                                           size_t error_size) {
+    if (!ctx) return fail(nullptr, error, error_size, "null context");
+    if (!d_ids || !d_offsets || !d_pair_rows || !d_inverse) return fail(ctx, error, error_size, "null dispatch-plan argument");
+    if (n == 0 || K == 0 || E == 0 || E > 256 || K > E) return fail(ctx, error, error_size, "invalid dispatch-plan dimensions");
+    if (!ctx->arena) return fail(ctx, error, error_size, "arenas not allocated");
+    // the list of non-empty experts is an internal by-product; park it in the arena's slot
+    const LayerDims m = max_dims(ctx);
+    if (E > m.E) return fail(ctx, error, error_size, "n_experts %u exceeds the mapped layers' %u", E, m.E);
+    const ArenaLayout a = layout_arena(m.H, m.E, m.K, m.F, m.S, 1);
+    CU_TRY(ctx, uocr::launch_dispatch_plan(d_ids, n, K, E, d_offsets, d_pair_rows, d_inverse,
+                                           (uint32_t *)(ctx->arena + a.active), ctx->stream, &ctx->launches));
+    return 1;
+}
+
+static int layer_forward(uocr_cuda_context *ctx, uint32_t layer, const __half *d_hidden, const __half *d_residual,
+                         const float *d_injected, uint32_t n, __half *d_out, const uocr_cuda_moe_debug_outputs *dbg,
+                         char *error, size_t error_size) {
+    const DLayer &L = ctx->layers[layer];
+    Scratch s = carve(ctx, L, n);
+    float *logits = dbg && dbg->d_router_logits ? dbg->d_router_logits : nullptr;
+    float *probs = dbg && dbg->d_router_probs ? dbg->d_router_probs : nullptr;
+    CU_TRY(ctx, uocr::launch_router(L, d_hidden, d_injected, n, logits, probs, s.top_ids, s.top_weights, ctx->status,
+                                    ctx->stream, &ctx->launches));
+    CU_TRY(ctx, uocr::launch_dispatch_plan(s.top_ids, n, L.K, L.E, s.expert_offsets, s.pair_rows, s.inverse, s.active,
+                                           ctx->stream, &ctx->launches));
+    CU_TRY(ctx, uocr::launch_small_batch_layer(L, s, d_hidden, d_residual, n, d_out, ctx->stream, &ctx->launches));
+    if (dbg && dbg->d_top_ids)
+        CU_TRY(ctx, cudaMemcpyAsync(dbg->d_top_ids, s.top_ids, (size_t)n * L.K * 4, cudaMemcpyDeviceToDevice, ctx->stream));
+    if (dbg && dbg->d_top_weights)
+        CU_TRY(ctx, cudaMemcpyAsync(dbg->d_top_weights, s.top_weights, (size_t)n * L.K * 4, cudaMemcpyDeviceToDevice, ctx->stream));
+    return 1;
+}
+
+extern "C" int uocr_cuda_moe_layer_forward(uocr_cuda_context *ctx, uint32_t layer, const void *d_hidden,
+                                           const void *d_residual, const float *d_injected, uint32_t n, void *d_out,
+                                           const uocr_cuda_moe_debug_outputs *dbg, char *error, size_t error_size) {
+    if (!check_call(ctx, layer, n, error, error_size)) return 0;
+    if (!d_hidden || !d_out) return fail(ctx, error, error_size, "null activation pointer");
+    return layer_forward(ctx, layer, (const __half *)d_hidden, (const __half *)d_residual, d_injected, n, (__half *)d_out,
+                         dbg, error, error_size);
+}
+
+static int stack_forward(uocr_cuda_context *ctx, uint32_t first, uint32_t count, const __half *d_hidden, uint32_t n,
+                         __half *d_out, char *error, size_t error_size) {
+    ArenaLayout a;
+    carve(ctx, ctx->layers[first], n, &a);
+    __half *buf[2] = {(__half *)(ctx->arena + a.stack0), (__half *)(ctx->arena + a.stack1)};
+    const __half *cur = d_hidden;
+    for (uint32_t i = 0; i < count; ++i) {
+        __half *dst = (i + 1 == count) ? d_out : buf[i & 1];
+        if (!layer_forward(ctx, first + i, cur, cur, nullptr, n, dst, nullptr, error, error_size)) return 0;
+        cur = dst;
+    }
+    return 1;
+}
+
+extern "C" int uocr_cuda_moe_stack_forward(uocr_cuda_context *ctx, uint32_t first, uint32_t count, const void *d_hidden,
+                                           uint32_t n, void *d_out, char *error, size_t error_size) {
+    if (!check_call(ctx, first, n, error, error_size)) return 0;
+    if (count == 0 || first + count > ctx->layers.size()) return fail(ctx, error, error_size, "layer range [%u, %u) out of range", first, first + count);
+    if (!d_hidden || !d_out) return fail(ctx, error, error_size, "null activation pointer");
+    for (uint32_t i = 1; i < count; ++i) {
+        const DLayer &A = ctx->layers[first], &B = ctx->layers[first + i];
+        if (A.H != B.H || A.E != B.E || A.K != B.K || A.F != B.F || A.S != B.S)
+            return fail(ctx, error, error_size, "stacked layers must have identical dimensions");
+    }
+    return stack_forward(ctx, first, count, (const __half *)d_hidden, n, (__half *)d_out, error, error_size);
+}
+
+extern "C" int uocr_cuda_moe_layer_forward_host(uocr_cuda_context *ctx, uint32_t layer, const void *h_hidden,
+                                                const void *h_residual, uint32_t n, void *h_out, uint32_t *h_ids,
+                                                float *h_wts, char *error, size_t error_size) {
+    if (!check_call(ctx, layer, n, error, error_size)) return 0;
+    if (!h_hidden || !h_out) return fail(ctx, error, error_size, "null activation pointer");
+    const DLayer &L = ctx->layers[layer];
+    ArenaLayout a;
+    Scratch s = carve(ctx, L, n, &a);
+    const size_t act = (size_t)n * L.H * 2;
+    __half *d_in = (__half *)(ctx->arena + a.d_in), *d_res = (__half *)(ctx->arena + a.d_res),
+           *d_out = (__half *)(ctx->arena + a.d_out);
+    memcpy(ctx->h_in, h_hidden, act);
+    CU_TRY(ctx, cudaMemcpyAsync(d_in, ctx->h_in, act, cudaMemcpyHostToDevice, ctx->stream));
+    if (h_residual) {
+        memcpy(ctx->h_res, h_residual, act);
+        CU_TRY(ctx, cudaMemcpyAsync(d_res, ctx->h_res, act, cudaMemcpyHostToDevice, ctx->stream));
+    }
+    if (!layer_forward(ctx, layer, d_in, h_residual ? d_res : nullptr, nullptr, n, d_out, nullptr, error, error_size)) return 0;
+    CU_TRY(ctx, cudaMemcpyAsync(ctx->h_out, d_out, act, cudaMemcpyDeviceToHost, ctx->stream));
+    if (h_ids) CU_TRY(ctx, cudaMemcpyAsync(ctx->h_ids, s.top_ids, (size_t)n * L.K * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    if (h_wts) CU_TRY(ctx, cudaMemcpyAsync(ctx->h_wts, s.top_weights, (size_t)n * L.K * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    if (!uocr_cuda_context_synchronize(ctx, error, error_size)) return 0;
+    memcpy(h_out, ctx->h_out, act);
+    if (h_ids) memcpy(h_ids, ctx->h_ids, (size_t)n * L.K * 4);
+    if (h_wts) memcpy(h_wts, ctx->h_wts, (size_t)n * L.K * 4);
+    return 1;
+}
+
+extern "C" int uocr_cuda_moe_stack_forward_host(uocr_cuda_context *ctx, uint32_t first, uint32_t count,
+                                                const void *h_hidden, uint32_t n, void *h_out, char *error,
+                                                size_t error_size) {
+    if (!check_call(ctx, first, n, error, error_size)) return 0;
+    if (count == 0 || first + count > ctx->layers.size()) return fail(ctx, error, error_size, "layer range [%u, %u) out of range", first, first + count);
+    if (!h_hidden || !h_out) return fail(ctx, error, error_size, "null activation pointer");
+    const DLayer &L = ctx->layers[first];
+    ArenaLayout a;
+    carve(ctx, L, n, &a);
+    const size_t act = (size_t)n * L.H * 2;
+    __half *d_in = (__half *)(ctx->arena + a.d_in), *d_out = (__half *)(ctx->arena + a.d_out);
+    memcpy(ctx->h_in, h_hidden, act);
+    CU_TRY(ctx, cudaMemcpyAsync(d_in, ctx->h_in, act, cudaMemcpyHostToDevice, ctx->stream));
+    if (!uocr_cuda_moe_stack_forward(ctx, first, count, d_in, n, d_out, error, error_size)) return 0;
+    CU_TRY(ctx, cudaMemcpyAsync(ctx->h_out, d_out, act, cudaMemcpyDeviceToHost, ctx->stream));
+    if (!uocr_cuda_context_synchronize(ctx, error, error_size)) return 0;
+    memcpy(h_out, ctx->h_out, act);
+    return 1;
+}

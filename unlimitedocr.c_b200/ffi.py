@@ -1,0 +1,270 @@
+"""ctypes binding of libuocr_cuda_moe.so, in the style of the reference's own binding
+(src/unlimitedocr_c/ffi.py:252-335: locate the shared library, declare every symbol's
+signature once, wrap handles in small classes that turn status codes into exceptions).
+
+The library is the product; this module only marshals arguments.  There is no fallback:
+if the shared library is missing or the machine has no sm_100 GPU, construction raises.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+from pathlib import Path
+from typing import Any
+
+import numpy as np
+
+QTYPE_F16, QTYPE_Q8_0, QTYPE_Q4_0 = 1, 3, 4
+_ERR = 1024
+
+
+class UocrCudaError(RuntimeError):
+    pass
+
+
+class CMatrix(C.Structure):
+    _fields_ = [("qtype", C.c_int32), ("rows", C.c_uint32), ("cols", C.c_uint32), ("qweight", C.c_void_p),
+                ("qscale", C.c_void_p)]
+
+
+class CLayerDesc(C.Structure):
+    _fields_ = [("hidden_size", C.c_uint32), ("n_experts", C.c_uint32), ("top_k", C.c_uint32),
+                ("expert_intermediate", C.c_uint32), ("shared_intermediate", C.c_uint32),
+                ("routed_scaling_factor", C.c_float), ("router_weight_f16", C.c_void_p),
+                ("router_logit_bias", C.c_void_p), ("expert_qtype", C.c_int32), ("expert_qweight", C.c_void_p),
+                ("expert_qscale", C.c_void_p), ("expert_stride_bytes", C.c_uint64), ("up_offset_bytes", C.c_uint64),
+                ("down_offset_bytes", C.c_uint64), ("expert_scale_stride_values", C.c_uint64),
+                ("up_scale_offset_values", C.c_uint64), ("down_scale_offset_values", C.c_uint64),
+                ("shared_gate", CMatrix), ("shared_up", CMatrix), ("shared_down", CMatrix)]
+
+
+class CDebugOutputs(C.Structure):
+    _fields_ = [("d_router_logits", C.c_void_p), ("d_router_probs", C.c_void_p), ("d_top_ids", C.c_void_p),
+                ("d_top_weights", C.c_void_p)]
+
+
+EXPORTS = (
+    "uocr_cuda_is_available", "uocr_cuda_backend_name", "uocr_cuda_device_count", "uocr_cuda_context_create",
+    "uocr_cuda_context_destroy", "uocr_cuda_context_last_error", "uocr_cuda_context_set_stream",
+    "uocr_cuda_context_synchronize", "uocr_cuda_context_kernel_launches", "uocr_cuda_context_model_view_bytes",
+    "uocr_cuda_context_moe_scratch_bytes", "uocr_cuda_context_map_moe_layer", "uocr_cuda_context_unmap_model",
+    "uocr_cuda_context_moe_layer_count", "uocr_cuda_context_allocate_runtime_arenas",
+    "uocr_cuda_context_release_runtime_arenas", "uocr_cuda_moe_scratch_size", "uocr_cuda_moe_router",
+    "uocr_cuda_moe_dispatch_plan", "uocr_cuda_moe_layer_forward", "uocr_cuda_moe_stack_forward",
+    "uocr_cuda_moe_layer_forward_host", "uocr_cuda_moe_stack_forward_host",
+)
+
+
+def library_path() -> Path:
+    """UOCR_CUDA_LIBRARY_PATH, else the in-tree build next to this file (the reference uses
+    UOCR_LIBRARY_PATH / build/release the same way, src/unlimitedocr_c/ffi.py:283)."""
+    env = os.environ.get("UOCR_CUDA_LIBRARY_PATH")
+    return Path(env) if env else Path(__file__).resolve().parent / "libuocr_cuda_moe.so"
+
+
+_lib = None
+
+
+def load_library() -> C.CDLL:
+    global _lib
+    if _lib is not None:
+        return _lib
+    path = library_path()
+    if not path.exists():
+        raise UocrCudaError(f"{path} not found: build it with `make -C {path.parent / 'csrc'}`; there is no CPU fallback")
+    lib = C.CDLL(str(path))
+    vp, u32, u64, sz, cp = C.c_void_p, C.c_uint32, C.c_uint64, C.c_size_t, C.c_char_p
+    err = [cp, sz]
+    sig = {
+        "uocr_cuda_is_available": (C.c_int, []),
+        "uocr_cuda_backend_name": (cp, []),
+        "uocr_cuda_device_count": (C.c_int, []),
+        "uocr_cuda_context_create": (vp, [cp] + err),
+        "uocr_cuda_context_destroy": (None, [vp]),
+        "uocr_cuda_context_last_error": (cp, [vp]),
+        "uocr_cuda_context_set_stream": (C.c_int, [vp, vp]),
+        "uocr_cuda_context_synchronize": (C.c_int, [vp] + err),
+        "uocr_cuda_context_kernel_launches": (u64, [vp]),
+        "uocr_cuda_context_model_view_bytes": (u64, [vp]),
+        "uocr_cuda_context_moe_scratch_bytes": (u64, [vp]),
+        "uocr_cuda_context_map_moe_layer": (C.c_int, [vp, C.POINTER(CLayerDesc), C.POINTER(u32)] + err),
+        "uocr_cuda_context_unmap_model": (None, [vp]),
+        "uocr_cuda_context_moe_layer_count": (u32, [vp]),
+        "uocr_cuda_context_allocate_runtime_arenas": (C.c_int, [vp, u32, u32] + err),
+        "uocr_cuda_context_release_runtime_arenas": (None, [vp]),
+        "uocr_cuda_moe_scratch_size": (u64, [u32] * 6),
+        "uocr_cuda_moe_router": (C.c_int, [vp, u32, vp, vp, u32, vp, vp, vp, vp] + err),
+        "uocr_cuda_moe_dispatch_plan": (C.c_int, [vp, vp, u32, u32, u32, vp, vp, vp] + err),
+        "uocr_cuda_moe_layer_forward": (C.c_int, [vp, u32, vp, vp, vp, u32, vp, C.POINTER(CDebugOutputs)] + err),
+        "uocr_cuda_moe_stack_forward": (C.c_int, [vp, u32, u32, vp, u32, vp] + err),
+        "uocr_cuda_moe_layer_forward_host": (C.c_int, [vp, u32, vp, vp, u32, vp, vp, vp] + err),
+        "uocr_cuda_moe_stack_forward_host": (C.c_int, [vp, u32, u32, vp, u32, vp] + err),
+    }
+    assert set(sig) == set(EXPORTS)
+    for name, (res, args) in sig.items():
+        fn = getattr(lib, name)
+        fn.restype, fn.argtypes = res, args
+    _lib = lib
+    return lib
+
+
+def _np_ptr(a: np.ndarray | None) -> int | None:
+    if a is None:
+        return None
+    assert a.flags["C_CONTIGUOUS"]
+    return a.ctypes.data
+
+
+def _dev_ptr(t: Any) -> int | None:
+    """Device pointer of a torch CUDA tensor (or an int address, or None)."""
+    if t is None:
+        return None
+    if isinstance(t, int):
+        return t
+    assert t.is_cuda and t.is_contiguous()
+    return t.data_ptr()
+
+
+def make_layer_desc(L: Any) -> tuple[CLayerDesc, list]:
+    """Descriptor over host arrays.  L exposes H, E, K, F, S, scaling, router (uint16 [E,H]),
+    logit_bias (f32 [E] or None), expert_qtype, expert_qweight (uint8), expert_qscale (uint16 or None),
+    shared_gate/up/down with qtype, rows, cols, qweight, qscale.  Returns the struct and the arrays
+    it points into (keep them alive until the map call returns)."""
+    keep = [L.router, L.logit_bias, L.expert_qweight, L.expert_qscale]
+    mats = []
+    for m in (L.shared_gate, L.shared_up, L.shared_down):
+        keep += [m.qweight, m.qscale]
+        mats.append(CMatrix(m.qtype, m.rows, m.cols, _np_ptr(m.qweight), _np_ptr(m.qscale)))
+    d = CLayerDesc(L.H, L.E, L.K, L.F, L.S, L.scaling, _np_ptr(L.router), _np_ptr(L.logit_bias), L.expert_qtype,
+                   _np_ptr(L.expert_qweight), _np_ptr(L.expert_qscale), 0, 0, 0, 0, 0, 0, *mats)
+    return d, keep
+
+
+class Context:
+    """One backend context on the current CUDA device (the reference's Engine plays this role for
+    the whole model; this one holds MoE layers only)."""
+
+    def __init__(self) -> None:
+        self._lib = load_library()
+        self._err = C.create_string_buffer(_ERR)
+        self._h = None
+        if not self._lib.uocr_cuda_is_available():
+            raise UocrCudaError("no CUDA device visible; this backend has no CPU fallback")
+        h = self._lib.uocr_cuda_context_create(None, self._err, _ERR)
+        if not h:
+            raise UocrCudaError(self._err.value.decode())
+        self._h = h
+        self._layer_k: dict[int, int] = {}
+
+    def close(self) -> None:
+        if self._h:
+            self._lib.uocr_cuda_context_destroy(self._h)
+            self._h = None
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        self.close()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def _check(self, ok: int) -> None:
+        if ok != 1:
+            raise UocrCudaError(self._err.value.decode() or self._lib.uocr_cuda_context_last_error(self._h).decode())
+
+    # -- model and arenas
+    def map_layer(self, L: Any) -> int:
+        desc, keep = make_layer_desc(L)
+        idx = self.map_layer_desc(desc)
+        del keep
+        return idx
+
+    def map_layer_desc(self, desc: CLayerDesc) -> int:
+        idx = C.c_uint32(0xFFFFFFFF)
+        self._check(self._lib.uocr_cuda_context_map_moe_layer(self._h, C.byref(desc), C.byref(idx), self._err, _ERR))
+        self._layer_k[idx.value] = desc.top_k
+        return idx.value
+
+    def unmap_model(self) -> None:
+        self._lib.uocr_cuda_context_unmap_model(self._h)
+
+    def allocate_runtime_arenas(self, token_capacity: int, batch_slots: int = 1) -> None:
+        self._check(self._lib.uocr_cuda_context_allocate_runtime_arenas(self._h, batch_slots, token_capacity,
+                                                                        self._err, _ERR))
+
+    def set_stream(self, cuda_stream: int | None) -> None:
+        self._check(self._lib.uocr_cuda_context_set_stream(self._h, cuda_stream))
+
+    def synchronize(self) -> None:
+        self._check(self._lib.uocr_cuda_context_synchronize(self._h, self._err, _ERR))
+
+    @property
+    def layer_count(self) -> int:
+        return self._lib.uocr_cuda_context_moe_layer_count(self._h)
+
+    @property
+    def kernel_launches(self) -> int:
+        return self._lib.uocr_cuda_context_kernel_launches(self._h)
+
+    @property
+    def model_view_bytes(self) -> int:
+        return self._lib.uocr_cuda_context_model_view_bytes(self._h)
+
+    @property
+    def moe_scratch_bytes(self) -> int:
+        return self._lib.uocr_cuda_context_moe_scratch_bytes(self._h)
+
+    # -- operators on device buffers (torch CUDA tensors or raw addresses)
+    def router(self, layer: int, hidden, n_tokens: int, top_ids, top_weights, *, injected_logits=None, logits=None,
+               probs=None) -> None:
+        self._check(self._lib.uocr_cuda_moe_router(self._h, layer, _dev_ptr(hidden), _dev_ptr(injected_logits),
+                                                   n_tokens, _dev_ptr(logits), _dev_ptr(probs), _dev_ptr(top_ids),
+                                                   _dev_ptr(top_weights), self._err, _ERR))
+
+    def dispatch_plan(self, top_ids, n_tokens: int, top_k: int, n_experts: int, expert_offsets, pair_rows,
+                      inverse) -> None:
+        self._check(self._lib.uocr_cuda_moe_dispatch_plan(self._h, _dev_ptr(top_ids), n_tokens, top_k, n_experts,
+                                                          _dev_ptr(expert_offsets), _dev_ptr(pair_rows),
+                                                          _dev_ptr(inverse), self._err, _ERR))
+
+    def layer_forward(self, layer: int, hidden, n_tokens: int, out, *, residual=None, injected_logits=None,
+                      logits=None, probs=None, top_ids=None, top_weights=None) -> None:
+        dbg = None
+        if any(x is not None for x in (logits, probs, top_ids, top_weights)):
+            dbg = C.byref(CDebugOutputs(_dev_ptr(logits), _dev_ptr(probs), _dev_ptr(top_ids), _dev_ptr(top_weights)))
+        self._check(self._lib.uocr_cuda_moe_layer_forward(self._h, layer, _dev_ptr(hidden), _dev_ptr(residual),
+                                                          _dev_ptr(injected_logits), n_tokens, _dev_ptr(out), dbg,
+                                                          self._err, _ERR))
+
+    def stack_forward(self, first_layer: int, n_layers: int, hidden, n_tokens: int, out) -> None:
+        self._check(self._lib.uocr_cuda_moe_stack_forward(self._h, first_layer, n_layers, _dev_ptr(hidden), n_tokens,
+                                                          _dev_ptr(out), self._err, _ERR))
+
+    # -- operators on host buffers (numpy uint16 fp16 bits)
+    def layer_forward_host(self, layer: int, hidden: np.ndarray, residual: np.ndarray | None = None, *,
+                           want_routing: bool = False):
+        hidden = np.ascontiguousarray(hidden, np.uint16)
+        n = hidden.shape[0]
+        out = np.empty_like(hidden)
+        ids = wts = None
+        if want_routing:
+            k = self._layer_k[layer]
+            ids, wts = np.empty((n, k), np.uint32), np.empty((n, k), np.float32)
+        if residual is not None:
+            residual = np.ascontiguousarray(residual, np.uint16)
+        self._check(self._lib.uocr_cuda_moe_layer_forward_host(self._h, layer, _np_ptr(hidden), _np_ptr(residual), n,
+                                                               _np_ptr(out), _np_ptr(ids), _np_ptr(wts), self._err,
+                                                               _ERR))
+        return (out, ids, wts) if want_routing else out
+
+    def stack_forward_host(self, first_layer: int, n_layers: int, hidden: np.ndarray) -> np.ndarray:
+        hidden = np.ascontiguousarray(hidden, np.uint16)
+        out = np.empty_like(hidden)
+        self._check(self._lib.uocr_cuda_moe_stack_forward_host(self._h, first_layer, n_layers, _np_ptr(hidden),
+                                                               hidden.shape[0], _np_ptr(out), self._err, _ERR))
+        return out
