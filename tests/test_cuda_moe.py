@@ -392,3 +392,48 @@ def test_invalid_arguments_are_rejected_with_text(pkg):
         ctx.layer_forward(0, dev(hidden), 4, out)          # and a valid call still works afterwards
         ctx.synchronize()
         assert ctx.model_view_bytes > 0 and ctx.moe_scratch_bytes > 0
+
+
+# ------------------------------------------------------------ persistent decode kernel
+
+@pytest.mark.parametrize("qname", ["q4_0", "q8_0"])
+def test_fused_decode_kernel_agrees_with_the_multi_kernel_path(pkg, port, qname, monkeypatch):
+    """Single-token calls at the model's shapes run in one persistent kernel; the same call with that
+    kernel disabled runs router, plan, gate/up, down and combine kernels.  Both follow one rounding
+    contract, so they agree to f32 summation order, and both match the oracle."""
+    rng = np.random.default_rng(31)
+    layers = [quant.synth_layer(rng, expert_qtype=QT[qname], **FULL) for _ in range(2)]
+    hidden = quant.synth_activations(rng, 1, FULL["H"])
+    outs, launches = {}, {}
+    for mode in ("fused", "generic"):
+        if mode == "generic":
+            monkeypatch.setenv("UOCR_CUDA_DISABLE_FUSED_DECODE", "1")
+        else:
+            monkeypatch.delenv("UOCR_CUDA_DISABLE_FUSED_DECODE", raising=False)
+        with pkg.Context() as ctx:
+            for L in layers:
+                ctx.map_layer(L)
+            ctx.allocate_runtime_arenas(1)
+            before = ctx.kernel_launches
+            outs[mode] = ctx.stack_forward_host(0, 2, hidden).view("<f2").astype(np.float32)
+            launches[mode] = ctx.kernel_launches - before
+            single, ids, wts = ctx.layer_forward_host(0, hidden, hidden, want_routing=True)
+            outs[mode + "_single"] = (single.view("<f2").astype(np.float32), ids, wts)
+    assert launches["fused"] == 1 and launches["generic"] == 14
+    want = port.layer(layers[0], hidden, hidden)
+    for mode in ("fused", "generic"):
+        got, ids, wts = outs[mode + "_single"]
+        assert np.array_equal(ids, want.ids)
+        assert np.max(np.abs(wts - want.weights)) <= 5e-5
+        err, cos = closeness(got, want.out)
+        assert err <= MAX_ABS and cos >= MIN_COS, (mode, err, cos)
+    err, cos = closeness(outs["fused"], outs["generic"])
+    assert err <= 4e-3 and cos >= 0.99999, (err, cos)
+    # repeated calls of the persistent kernel are bit-reproducible (fixed summation orders, no atomics)
+    with pkg.Context() as ctx:
+        for L in layers:
+            ctx.map_layer(L)
+        ctx.allocate_runtime_arenas(1)
+        a = ctx.stack_forward_host(0, 2, hidden)
+        b = ctx.stack_forward_host(0, 2, hidden)
+        assert np.array_equal(a, b)

@@ -6,12 +6,12 @@
 // (src/backend/cpu_ref/uocr_cpu_ref.c:388-466), so identical logits give identical ids and weights.
 //
 // Dispatch plan: stable counting sort of pair = token*K + slot by expert id.
-#include "expf_compat.h"
-#include "moe_common.cuh"
+#include "moe_route.cuh"
 
 namespace uocr {
 
 __constant__ uint64_t c_exp_tab[UOCR_EXPF_N];
+
 static bool g_tab_ready[64] = {false};
 
 static cudaError_t ensure_exp_table() {
@@ -73,49 +73,11 @@ router_kernel(const __half *__restrict__ hidden, const __half *__restrict__ rout
 
     // one warp per token: softmax + top-k
     for (uint32_t t = warp; t < nt; t += kRouterWarps) {
-        const float *l = ls + t * E;
-        float *p = ps + t * E;
-        float mx = -INFINITY;
-        for (uint32_t e = lane; e < E; e += 32) mx = fmaxf(mx, l[e]);
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-        bool bad = !isfinite(mx);
-        for (uint32_t e = lane; e < E; e += 32) p[e] = uocr_expf_compat(__fsub_rn(l[e], mx), c_exp_tab);
-        __syncwarp();
-        float denom = 0.f;
-        if (lane == 0)
-            for (uint32_t e = 0; e < E; ++e) denom = __fadd_rn(denom, p[e]);   // serial, expert order
-        denom = __shfl_sync(0xffffffffu, denom, 0);
-        bad = bad || !(denom > 0.f) || !isfinite(denom);
-        for (uint32_t e = lane; e < E; e += 32) p[e] = __fdiv_rn(p[e], denom);
-        __syncwarp();
         const size_t row = (size_t)(t0 + t);
-        if (logits_out) for (uint32_t e = lane; e < E; e += 32) logits_out[row * E + e] = l[e];
-        if (probs_out) for (uint32_t e = lane; e < E; e += 32) probs_out[row * E + e] = p[e];
-
-        // greedy top-k; `taken` bit i of a lane marks expert lane + 32*i as already selected
-        uint32_t taken = 0;
-        for (uint32_t slot = 0; slot < K; ++slot) {
-            float bp = -INFINITY;
-            uint32_t be = 0xffffffffu;
-            for (uint32_t e = lane, i = 0; e < E; e += 32, ++i) {
-                if ((taken >> i) & 1u) continue;
-                const float pe = p[e];
-                if (pe > bp || (pe == bp && e < be)) { bp = pe; be = e; }
-            }
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) {
-                const float op = __shfl_xor_sync(0xffffffffu, bp, o);
-                const uint32_t oe = __shfl_xor_sync(0xffffffffu, be, o);
-                if (op > bp || (op == bp && oe < be)) { bp = op; be = oe; }
-            }
-            if (be == 0xffffffffu || !(bp >= 0.f)) bad = true;
-            if (be != 0xffffffffu && (be & 31u) == (uint32_t)lane) taken |= 1u << (be >> 5);
-            if (lane == 0) {
-                ids_out[row * K + slot] = bad ? 0xffffffffu : be;
-                weights_out[row * K + slot] = bad ? 0.f : __fmul_rn(bp, scaling);
-            }
-        }
+        const bool bad = route_row_warp(ls + t * E, ps + t * E, E, K, scaling, lane,
+                                        logits_out ? logits_out + row * E : nullptr,
+                                        probs_out ? probs_out + row * E : nullptr, ids_out + row * K,
+                                        weights_out + row * K);
         if (bad && lane == 0) atomicOr(status, 1u);   // the CPU function returns failure here
     }
 }

@@ -6,6 +6,7 @@
 #include <cmath>
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <vector>
 
@@ -14,7 +15,19 @@
 namespace uocr {
 cudaError_t init_router_kernels();
 cudaError_t init_small_batch_kernels();
+cudaError_t init_decode_kernels();
+int decode_grid_size();
+bool decode_supported(const DLayer *layers, uint32_t first, uint32_t count);
+cudaError_t launch_decode_stack(const DLayer *h_layers, const DLayer *d_layers, uint32_t first, uint32_t count,
+                                const __half *hidden, const __half *residual0, int chain_residual,
+                                const float *injected, __half *out, __half *hbuf0, __half *hbuf1, __half *mid,
+                                float *plogits, unsigned long long *bar, unsigned long long *bar_base, uint32_t *status,
+                                float *dbg_logits, float *dbg_probs, uint32_t *ids_out, float *wts_out,
+                                cudaStream_t st, uint64_t *launches);
 }  // namespace uocr
+
+static constexpr uint32_t kMaxLayers = 64;
+static constexpr uint64_t kUploadPad = 256;   // kernels may read an aligned window that ends past a tensor
 
 using uocr::DLayer;
 using uocr::DMatrix;
@@ -25,6 +38,9 @@ struct uocr_cuda_context {
     cudaStream_t own_stream = nullptr;
     cudaStream_t stream = nullptr;
     std::vector<DLayer> layers;
+    DLayer *d_layers = nullptr;        // device copy of `layers`
+    bool fused_decode = true;          // single-token calls use the persistent decode kernel when it fits
+    unsigned long long bar_base = 0;   // value the decode kernel's barrier counter has reached
     std::vector<void *> weight_allocs;
     uint64_t weight_bytes = 0;
     // arena
@@ -111,12 +127,16 @@ extern "C" uocr_cuda_context *uocr_cuda_context_create(const char *resource_path
         (e = cudaMalloc(&ctx->status, 256)) != cudaSuccess ||
         (e = cudaMemset(ctx->status, 0, 256)) != cudaSuccess ||
         (e = cudaMallocHost(&ctx->h_status, 256)) != cudaSuccess ||
-        (e = uocr::init_router_kernels()) != cudaSuccess || (e = uocr::init_small_batch_kernels()) != cudaSuccess) {
+        (e = cudaMalloc(&ctx->d_layers, kMaxLayers * sizeof(DLayer))) != cudaSuccess ||
+        (e = uocr::init_router_kernels()) != cudaSuccess || (e = uocr::init_small_batch_kernels()) != cudaSuccess ||
+        (e = uocr::init_decode_kernels()) != cudaSuccess) {
         fail(nullptr, error, error_size, "CUDA context set-up failed: %s", cudaGetErrorString(e));
         uocr_cuda_context_destroy(ctx);
         return nullptr;
     }
     ctx->stream = ctx->own_stream;
+    const char *off = getenv("UOCR_CUDA_DISABLE_FUSED_DECODE");
+    ctx->fused_decode = !(off && off[0] == '1');
     return ctx;
 }
 
@@ -148,6 +168,7 @@ extern "C" void uocr_cuda_context_destroy(uocr_cuda_context *ctx) {
     uocr_cuda_context_release_runtime_arenas(ctx);
     uocr_cuda_context_unmap_model(ctx);
     cudaFree(ctx->status);
+    cudaFree(ctx->d_layers);
     cudaFreeHost(ctx->h_status);
     if (ctx->own_stream) cudaStreamDestroy(ctx->own_stream);
     delete ctx;
@@ -169,11 +190,15 @@ extern "C" int uocr_cuda_context_synchronize(uocr_cuda_context *ctx, char *error
     CU_TRY(ctx, cudaStreamSynchronize(ctx->stream));
     if (*ctx->h_status != 0) {
         const uint32_t st = *ctx->h_status;
-        cudaMemsetAsync(ctx->status, 0, sizeof(uint32_t), ctx->stream);
+        // clears the status word and the decode kernel's barrier counter (it is off after an abort)
+        cudaMemsetAsync(ctx->status, 0, 256, ctx->stream);
+        ctx->bar_base = 0;
         return fail(ctx, error, error_size,
                     "device status 0x%x: %s", st,
                     (st & 1u) ? "router met a non-finite logit or an empty softmax (the CPU path rejects this input too)"
-                              : "kernel reported an internal error");
+                    : (st & 2u) ? "a grid barrier of the decode kernel timed out"
+                    : (st & 4u) ? "a bulk copy of the decode kernel timed out"
+                                : "kernel reported an internal error");
     }
     return 1;
 }
@@ -188,8 +213,9 @@ extern "C" uint32_t uocr_cuda_context_moe_layer_count(const uocr_cuda_context *c
 // ----------------------------------------------------------------------------- map model
 static int upload(uocr_cuda_context *ctx, const void *host, uint64_t bytes, void **out, char *error, size_t error_size) {
     void *d = nullptr;
-    CU_TRY(ctx, cudaMalloc(&d, bytes));
+    CU_TRY(ctx, cudaMalloc(&d, bytes + kUploadPad));
     ctx->weight_allocs.push_back(d);
+    CU_TRY(ctx, cudaMemset((uint8_t *)d + bytes, 0, kUploadPad));
     CU_TRY(ctx, cudaMemcpy(d, host, bytes, cudaMemcpyHostToDevice));
     ctx->weight_bytes += bytes;
     *out = d;
@@ -275,13 +301,13 @@ extern "C" int uocr_cuda_context_map_moe_layer(uocr_cuda_context *ctx, const uoc
         const int sq = d->shared_gate.qtype;
         const uint64_t wb = packed_bytes(sq, S, H), sb = sq == UOCR_QT_F16 ? 0 : (uint64_t)S * (H / UOCR_GROUP) * 2;
         uint8_t *dw = nullptr;
-        CU_TRY(ctx, cudaMalloc(&dw, 2 * wb));
+        CU_TRY(ctx, cudaMalloc(&dw, 2 * wb + kUploadPad));
         ctx->weight_allocs.push_back(dw);
         CU_TRY(ctx, cudaMemcpy(dw, d->shared_gate.qweight, wb, cudaMemcpyHostToDevice));
         CU_TRY(ctx, cudaMemcpy(dw + wb, d->shared_up.qweight, wb, cudaMemcpyHostToDevice));
         uint8_t *ds = nullptr;
         if (sb) {
-            CU_TRY(ctx, cudaMalloc(&ds, 2 * sb));
+            CU_TRY(ctx, cudaMalloc(&ds, 2 * sb + kUploadPad));
             ctx->weight_allocs.push_back(ds);
             CU_TRY(ctx, cudaMemcpy(ds, d->shared_gate.qscale, sb, cudaMemcpyHostToDevice));
             CU_TRY(ctx, cudaMemcpy(ds + sb, d->shared_up.qscale, sb, cudaMemcpyHostToDevice));
@@ -303,7 +329,9 @@ extern "C" int uocr_cuda_context_map_moe_layer(uocr_cuda_context *ctx, const uoc
         const DLayer &f = ctx->layers.front();
         if (f.H != H) return fail(ctx, error, error_size, "all mapped layers must share hidden_size (%u vs %u)", f.H, H);
     }
+    if (ctx->layers.size() >= kMaxLayers) return fail(ctx, error, error_size, "at most %u layers can be mapped", kMaxLayers);
     ctx->layers.push_back(L);
+    CU_TRY(ctx, cudaMemcpy(ctx->d_layers, ctx->layers.data(), ctx->layers.size() * sizeof(DLayer), cudaMemcpyHostToDevice));
     if (out_layer_index) *out_layer_index = (uint32_t)ctx->layers.size() - 1;
     return 1;
 }
@@ -311,7 +339,7 @@ extern "C" int uocr_cuda_context_map_moe_layer(uocr_cuda_context *ctx, const uoc
 // ----------------------------------------------------------------------------------- arena
 struct ArenaLayout {
     uint64_t logits, probs, ids, weights, offsets, pair_rows, inverse, active, mid, shared_mid, down_out, shared_out,
-        stack0, stack1, d_in, d_res, d_out, total;
+        stack0, stack1, d_in, d_res, d_out, dec_mid, dec_plogits, total;
 };
 
 // down products are f32 while the call is small enough to take the matrix-vector path, fp16 beyond
@@ -339,6 +367,8 @@ static ArenaLayout layout_arena(uint32_t H, uint32_t E, uint32_t K, uint32_t F, 
     a.d_in = take((uint64_t)n * H * 2);
     a.d_res = take((uint64_t)n * H * 2);
     a.d_out = take((uint64_t)n * H * 2);
+    a.dec_mid = take(((uint64_t)K * F + S) * 2);            // single-token decode kernel: SwiGLU products
+    a.dec_plogits = take((uint64_t)1024 * E * 4);           // and per-CTA partial router logits
     a.total = off;
     return a;
 }
@@ -439,18 +469,32 @@ extern "C" int uocr_cuda_moe_dispatch_plan(uocr_cuda_context *ctx, const uint32_
     return 1;
 }
 
+static unsigned long long *barrier_counter(uocr_cuda_context *ctx) {
+    return reinterpret_cast<unsigned long long *>(reinterpret_cast<uint8_t *>(ctx->status) + 64);
+}
+
 static int layer_forward(uocr_cuda_context *ctx, uint32_t layer, const __half *d_hidden, const __half *d_residual,
                          const float *d_injected, uint32_t n, __half *d_out, const uocr_cuda_moe_debug_outputs *dbg,
                          char *error, size_t error_size) {
     const DLayer &L = ctx->layers[layer];
-    Scratch s = carve(ctx, L, n);
+    ArenaLayout a;
+    Scratch s = carve(ctx, L, n, &a);
     float *logits = dbg && dbg->d_router_logits ? dbg->d_router_logits : nullptr;
     float *probs = dbg && dbg->d_router_probs ? dbg->d_router_probs : nullptr;
+    if (n == 1 && ctx->fused_decode && uocr::decode_supported(ctx->layers.data(), layer, 1)) {
+        CU_TRY(ctx, uocr::launch_decode_stack(ctx->layers.data(), ctx->d_layers, layer, 1, d_hidden, d_residual, 0,
+                                              d_injected, d_out, (__half *)(ctx->arena + a.stack0),
+                                              (__half *)(ctx->arena + a.stack1), (__half *)(ctx->arena + a.dec_mid),
+                                              (float *)(ctx->arena + a.dec_plogits), barrier_counter(ctx), &ctx->bar_base,
+                                              ctx->status, logits, probs, s.top_ids, s.top_weights, ctx->stream,
+                                              &ctx->launches));
+    } else {
     CU_TRY(ctx, uocr::launch_router(L, d_hidden, d_injected, n, logits, probs, s.top_ids, s.top_weights, ctx->status,
                                     ctx->stream, &ctx->launches));
     CU_TRY(ctx, uocr::launch_dispatch_plan(s.top_ids, n, L.K, L.E, s.expert_offsets, s.pair_rows, s.inverse, s.active,
                                            ctx->stream, &ctx->launches));
     CU_TRY(ctx, uocr::launch_small_batch_layer(L, s, d_hidden, d_residual, n, d_out, ctx->stream, &ctx->launches));
+    }
     if (dbg && dbg->d_top_ids)
         CU_TRY(ctx, cudaMemcpyAsync(dbg->d_top_ids, s.top_ids, (size_t)n * L.K * 4, cudaMemcpyDeviceToDevice, ctx->stream));
     if (dbg && dbg->d_top_weights)
@@ -470,8 +514,16 @@ extern "C" int uocr_cuda_moe_layer_forward(uocr_cuda_context *ctx, uint32_t laye
 static int stack_forward(uocr_cuda_context *ctx, uint32_t first, uint32_t count, const __half *d_hidden, uint32_t n,
                          __half *d_out, char *error, size_t error_size) {
     ArenaLayout a;
-    carve(ctx, ctx->layers[first], n, &a);
+    Scratch s = carve(ctx, ctx->layers[first], n, &a);
     __half *buf[2] = {(__half *)(ctx->arena + a.stack0), (__half *)(ctx->arena + a.stack1)};
+    if (n == 1 && ctx->fused_decode && uocr::decode_supported(ctx->layers.data(), first, count)) {
+        CU_TRY(ctx, uocr::launch_decode_stack(ctx->layers.data(), ctx->d_layers, first, count, d_hidden, d_hidden, 1,
+                                              nullptr, d_out, buf[0], buf[1], (__half *)(ctx->arena + a.dec_mid),
+                                              (float *)(ctx->arena + a.dec_plogits), barrier_counter(ctx), &ctx->bar_base,
+                                              ctx->status, nullptr, nullptr, s.top_ids, s.top_weights, ctx->stream,
+                                              &ctx->launches));
+        return 1;
+    }
     const __half *cur = d_hidden;
     for (uint32_t i = 0; i < count; ++i) {
         __half *dst = (i + 1 == count) ? d_out : buf[i & 1];
