@@ -102,8 +102,14 @@ UOCR_CUDA_API int uocr_cuda_device_count(void);
 UOCR_CUDA_API uocr_cuda_context *uocr_cuda_context_create(const char *resource_path, char *error, size_t error_size);
 UOCR_CUDA_API void uocr_cuda_context_destroy(uocr_cuda_context *ctx);
 UOCR_CUDA_API const char *uocr_cuda_context_last_error(const uocr_cuda_context *ctx);
-/* Use an existing cudaStream_t (passed as void*) instead of the context's own; NULL restores it. */
+/* Use an existing cudaStream_t (passed as void*) instead of the context's own; NULL restores it.
+ * (The legacy default stream is named by cudaStreamLegacy, not by NULL.) */
 UOCR_CUDA_API int uocr_cuda_context_set_stream(uocr_cuda_context *ctx, void *cuda_stream);
+/* Detail profiling of the single-token stack call, the counterpart of the reference's per-op checkpoints
+ * (UOCR_METAL_DECODER_PROFILE_DETAIL, src/backend/metal/uocr_metal.m:29-31, :14251-14297).  d_trace is a device
+ * buffer of n_layers * 8 uint64: for each layer the SM clock of CTA 0 at layer start, inputs read, routing done,
+ * copies issued, gate/up computed, barrier 1 passed, down computed, barrier 2 passed.  NULL switches it off. */
+UOCR_CUDA_API int uocr_cuda_context_set_profile_detail(uocr_cuda_context *ctx, void *d_trace);
 UOCR_CUDA_API int uocr_cuda_context_synchronize(uocr_cuda_context *ctx, char *error, size_t error_size);
 /* Kernels launched by this context since creation (every launch is counted at its call site). */
 UOCR_CUDA_API uint64_t uocr_cuda_context_kernel_launches(const uocr_cuda_context *ctx);

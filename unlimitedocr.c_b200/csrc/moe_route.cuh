@@ -14,50 +14,87 @@ extern __constant__ uint64_t c_exp_tab[UOCR_EXPF_N];
 // l: logits [E] (shared memory), p: probabilities [E] (shared memory, written).  Results go to
 // ids_out[K] / weights_out[K] (any address space; written by lane 0) and, when not null, to
 // logits_out / probs_out.  Returns true when the row is invalid (non-finite logits, empty softmax).
-__device__ __forceinline__ bool route_row_warp(const float *l, float *p, uint32_t E, uint32_t K, float scaling, int lane,
-                                               float *logits_out, float *probs_out, uint32_t *ids_out,
-                                               float *weights_out) {
+// kPerLane * 32 >= E.  exp_tab is the 32-entry table of expf_compat.h in SHARED memory (lanes index it with
+// different values; constant memory would serialise those reads).  The selection compares probabilities as
+// unsigned integers, which orders non-negative floats exactly as the float comparison does.
+template <int kPerLane>
+__device__ __forceinline__ bool route_row_warp_n(const float *l, float *p, uint32_t E, uint32_t K, float scaling,
+                                                 int lane, const uint64_t *exp_tab, float *logits_out,
+                                                 float *probs_out, uint32_t *ids_out, float *weights_out) {
+    float lv[kPerLane];
     float mx = -INFINITY;
-    for (uint32_t e = lane; e < E; e += 32) mx = fmaxf(mx, l[e]);
+#pragma unroll
+    for (int i = 0; i < kPerLane; ++i) {
+        const uint32_t e = lane + 32 * i;
+        lv[i] = e < E ? l[e] : -INFINITY;
+        mx = fmaxf(mx, lv[i]);
+    }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
     bool bad = !isfinite(mx);
-    for (uint32_t e = lane; e < E; e += 32) p[e] = uocr_expf_compat(__fsub_rn(l[e], mx), c_exp_tab);
+    float pv[kPerLane];
+#pragma unroll
+    for (int i = 0; i < kPerLane; ++i) {
+        const uint32_t e = lane + 32 * i;
+        if (e < E) {
+            pv[i] = uocr_expf_compat(__fsub_rn(lv[i], mx), exp_tab);
+            p[e] = pv[i];
+        } else {
+            pv[i] = 0.f;
+        }
+    }
     __syncwarp();
+    // denominator: one serial chain in expert order; the shared-memory reads are batched ahead of the adds
     float denom = 0.f;
-    if (lane == 0)
-        for (uint32_t e = 0; e < E; ++e) denom = __fadd_rn(denom, p[e]);   // serial, expert order
+    if (lane == 0) {
+        for (uint32_t e0 = 0; e0 < E; e0 += 16) {
+            float t[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) t[i] = e0 + i < E ? p[e0 + i] : 0.f;
+#pragma unroll
+            for (int i = 0; i < 16; ++i)
+                if (e0 + i < E) denom = __fadd_rn(denom, t[i]);
+        }
+    }
     denom = __shfl_sync(0xffffffffu, denom, 0);
     bad = bad || !(denom > 0.f) || !isfinite(denom);
-    for (uint32_t e = lane; e < E; e += 32) p[e] = __fdiv_rn(p[e], denom);
-    __syncwarp();
-    if (logits_out) for (uint32_t e = lane; e < E; e += 32) logits_out[e] = l[e];
-    if (probs_out) for (uint32_t e = lane; e < E; e += 32) probs_out[e] = p[e];
-
-    // `taken` bit i of a lane marks expert lane + 32*i as already selected
+#pragma unroll
+    for (int i = 0; i < kPerLane; ++i) {
+        const uint32_t e = lane + 32 * i;
+        if (e < E) {
+            pv[i] = __fdiv_rn(pv[i], denom);
+            p[e] = pv[i];
+            if (logits_out) logits_out[e] = lv[i];
+            if (probs_out) probs_out[e] = pv[i];
+        }
+    }
+    // greedy top-k: bit i of `taken` marks expert lane + 32*i as selected
     uint32_t taken = 0;
     for (uint32_t slot = 0; slot < K; ++slot) {
-        float bp = -INFINITY;
-        uint32_t be = 0xffffffffu;
-        for (uint32_t e = lane, i = 0; e < E; e += 32, ++i) {
-            if ((taken >> i) & 1u) continue;
-            const float pe = p[e];
-            if (pe > bp || (pe == bp && e < be)) { bp = pe; be = e; }
-        }
+        uint32_t bb = 0, be = 0xffffffffu;       // best probability bits / expert of this lane
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-            const float op = __shfl_xor_sync(0xffffffffu, bp, o);
-            const uint32_t oe = __shfl_xor_sync(0xffffffffu, be, o);
-            if (op > bp || (op == bp && oe < be)) { bp = op; be = oe; }
+        for (int i = 0; i < kPerLane; ++i) {
+            const uint32_t e = lane + 32 * i;
+            const uint32_t bits = __float_as_uint(pv[i]);
+            if (e < E && !((taken >> i) & 1u) && (be == 0xffffffffu || bits > bb)) { bb = bits; be = e; }
         }
-        if (be == 0xffffffffu || !(bp >= 0.f)) bad = true;
-        if (be != 0xffffffffu && (be & 31u) == (uint32_t)lane) taken |= 1u << (be >> 5);
+        const uint32_t top = __reduce_max_sync(0xffffffffu, be == 0xffffffffu ? 0u : bb);
+        const uint32_t win = __reduce_min_sync(0xffffffffu, (be != 0xffffffffu && bb == top) ? be : 0xffffffffu);
+        if (win == 0xffffffffu) bad = true;
+        if (win != 0xffffffffu && (win & 31u) == (uint32_t)lane) taken |= 1u << (win >> 5);
         if (lane == 0) {
-            ids_out[slot] = bad ? 0xffffffffu : be;
-            weights_out[slot] = bad ? 0.f : __fmul_rn(bp, scaling);
+            ids_out[slot] = bad ? 0xffffffffu : win;
+            weights_out[slot] = bad ? 0.f : __fmul_rn(__uint_as_float(top), scaling);
         }
     }
     return bad;
+}
+
+__device__ __forceinline__ bool route_row_warp(const float *l, float *p, uint32_t E, uint32_t K, float scaling, int lane,
+                                               const uint64_t *exp_tab, float *logits_out, float *probs_out,
+                                               uint32_t *ids_out, float *weights_out) {
+    if (E <= 64) return route_row_warp_n<2>(l, p, E, K, scaling, lane, exp_tab, logits_out, probs_out, ids_out, weights_out);
+    return route_row_warp_n<8>(l, p, E, K, scaling, lane, exp_tab, logits_out, probs_out, ids_out, weights_out);
 }
 
 }  // namespace uocr

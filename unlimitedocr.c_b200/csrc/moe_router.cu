@@ -40,6 +40,8 @@ router_kernel(const __half *__restrict__ hidden, const __half *__restrict__ rout
     float *xs = smem;                         // [TPB][H]
     float *ls = xs + (size_t)TPB * H;         // [TPB][E]
     float *ps = ls + (size_t)TPB * E;         // [TPB][E]
+    __shared__ uint64_t s_tab[UOCR_EXPF_N];
+    if (threadIdx.x < UOCR_EXPF_N) s_tab[threadIdx.x] = c_exp_tab[threadIdx.x];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const uint32_t t0 = blockIdx.x * TPB;
     const uint32_t nt = min((uint32_t)TPB, n - t0);
@@ -74,7 +76,7 @@ router_kernel(const __half *__restrict__ hidden, const __half *__restrict__ rout
     // one warp per token: softmax + top-k
     for (uint32_t t = warp; t < nt; t += kRouterWarps) {
         const size_t row = (size_t)(t0 + t);
-        const bool bad = route_row_warp(ls + t * E, ps + t * E, E, K, scaling, lane,
+        const bool bad = route_row_warp(ls + t * E, ps + t * E, E, K, scaling, lane, s_tab,
                                         logits_out ? logits_out + row * E : nullptr,
                                         probs_out ? probs_out + row * E : nullptr, ids_out + row * K,
                                         weights_out + row * K);

@@ -23,7 +23,7 @@ cudaError_t launch_decode_stack(const DLayer *h_layers, const DLayer *d_layers, 
                                 const float *injected, __half *out, __half *hbuf0, __half *hbuf1, __half *mid,
                                 float *plogits, unsigned long long *bar, unsigned long long *bar_base, uint32_t *status,
                                 float *dbg_logits, float *dbg_probs, uint32_t *ids_out, float *wts_out,
-                                cudaStream_t st, uint64_t *launches);
+                                unsigned long long *trace, cudaStream_t st, uint64_t *launches);
 }  // namespace uocr
 
 static constexpr uint32_t kMaxLayers = 64;
@@ -41,6 +41,7 @@ struct uocr_cuda_context {
     DLayer *d_layers = nullptr;        // device copy of `layers`
     bool fused_decode = true;          // single-token calls use the persistent decode kernel when it fits
     unsigned long long bar_base = 0;   // value the decode kernel's barrier counter has reached
+    unsigned long long *decode_trace = nullptr;   // optional device buffer for per-phase clock stamps
     std::vector<void *> weight_allocs;
     uint64_t weight_bytes = 0;
     // arena
@@ -181,6 +182,12 @@ extern "C" const char *uocr_cuda_context_last_error(const uocr_cuda_context *ctx
 extern "C" int uocr_cuda_context_set_stream(uocr_cuda_context *ctx, void *cuda_stream) {
     if (!ctx) return 0;
     ctx->stream = cuda_stream ? (cudaStream_t)cuda_stream : ctx->own_stream;
+    return 1;
+}
+
+extern "C" int uocr_cuda_context_set_profile_detail(uocr_cuda_context *ctx, void *d_trace) {
+    if (!ctx) return 0;
+    ctx->decode_trace = (unsigned long long *)d_trace;
     return 1;
 }
 
@@ -486,7 +493,7 @@ static int layer_forward(uocr_cuda_context *ctx, uint32_t layer, const __half *d
                                               d_injected, d_out, (__half *)(ctx->arena + a.stack0),
                                               (__half *)(ctx->arena + a.stack1), (__half *)(ctx->arena + a.dec_mid),
                                               (float *)(ctx->arena + a.dec_plogits), barrier_counter(ctx), &ctx->bar_base,
-                                              ctx->status, logits, probs, s.top_ids, s.top_weights, ctx->stream,
+                                              ctx->status, logits, probs, s.top_ids, s.top_weights, nullptr, ctx->stream,
                                               &ctx->launches));
     } else {
     CU_TRY(ctx, uocr::launch_router(L, d_hidden, d_injected, n, logits, probs, s.top_ids, s.top_weights, ctx->status,
@@ -520,7 +527,7 @@ static int stack_forward(uocr_cuda_context *ctx, uint32_t first, uint32_t count,
         CU_TRY(ctx, uocr::launch_decode_stack(ctx->layers.data(), ctx->d_layers, first, count, d_hidden, d_hidden, 1,
                                               nullptr, d_out, buf[0], buf[1], (__half *)(ctx->arena + a.dec_mid),
                                               (float *)(ctx->arena + a.dec_plogits), barrier_counter(ctx), &ctx->bar_base,
-                                              ctx->status, nullptr, nullptr, s.top_ids, s.top_weights, ctx->stream,
+                                              ctx->status, nullptr, nullptr, s.top_ids, s.top_weights, ctx->decode_trace, ctx->stream,
                                               &ctx->launches));
         return 1;
     }

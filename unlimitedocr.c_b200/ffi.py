@@ -46,7 +46,7 @@ class CDebugOutputs(C.Structure):
 EXPORTS = (
     "uocr_cuda_is_available", "uocr_cuda_backend_name", "uocr_cuda_device_count", "uocr_cuda_context_create",
     "uocr_cuda_context_destroy", "uocr_cuda_context_last_error", "uocr_cuda_context_set_stream",
-    "uocr_cuda_context_synchronize", "uocr_cuda_context_kernel_launches", "uocr_cuda_context_model_view_bytes",
+    "uocr_cuda_context_set_profile_detail", "uocr_cuda_context_synchronize", "uocr_cuda_context_kernel_launches", "uocr_cuda_context_model_view_bytes",
     "uocr_cuda_context_moe_scratch_bytes", "uocr_cuda_context_map_moe_layer", "uocr_cuda_context_unmap_model",
     "uocr_cuda_context_moe_layer_count", "uocr_cuda_context_allocate_runtime_arenas",
     "uocr_cuda_context_release_runtime_arenas", "uocr_cuda_moe_scratch_size", "uocr_cuda_moe_router",
@@ -83,6 +83,7 @@ def load_library() -> C.CDLL:
         "uocr_cuda_context_destroy": (None, [vp]),
         "uocr_cuda_context_last_error": (cp, [vp]),
         "uocr_cuda_context_set_stream": (C.c_int, [vp, vp]),
+        "uocr_cuda_context_set_profile_detail": (C.c_int, [vp, vp]),
         "uocr_cuda_context_synchronize": (C.c_int, [vp] + err),
         "uocr_cuda_context_kernel_launches": (u64, [vp]),
         "uocr_cuda_context_model_view_bytes": (u64, [vp]),
@@ -198,7 +199,15 @@ class Context:
                                                                         self._err, _ERR))
 
     def set_stream(self, cuda_stream: int | None) -> None:
+        """Run on the given cudaStream_t (e.g. torch.cuda.current_stream().cuda_stream); None restores the
+        context's own stream.  Handle 0 names the legacy default stream and is passed as cudaStreamLegacy."""
+        if cuda_stream == 0:
+            cuda_stream = 1   # cudaStreamLegacy
         self._check(self._lib.uocr_cuda_context_set_stream(self._h, cuda_stream))
+
+    def set_profile_detail(self, trace) -> None:
+        """Device buffer (n_layers * 8 int64) that single-token stack calls fill with per-phase SM clocks."""
+        self._check(self._lib.uocr_cuda_context_set_profile_detail(self._h, _dev_ptr(trace)))
 
     def synchronize(self) -> None:
         self._check(self._lib.uocr_cuda_context_synchronize(self._h, self._err, _ERR))
