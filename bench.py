@@ -167,7 +167,7 @@ def workload_config() -> dict:
     return {"workload": "decode: 1 token x 11 stacked MoE layers, hidden 1280, 64 experts top-6 + shared 1792, "
                         "FFN 896, Q4_0 group-64 experts and shared MLP, seed 1",
             "layers": N_LAYERS, "tokens_per_step": 1, "qtype": "q4_0",
-            "l2": "flushed between timed iterations (256 MiB written, then 256 MiB copied)"}
+            "l2": "flushed between timed iterations (256 MiB written, then 256 MiB read)"}
 
 
 def main() -> None:
@@ -213,13 +213,13 @@ def main() -> None:
     d_hidden = torch.from_numpy(hidden).cuda().view(torch.float16)
     d_out = torch.zeros_like(d_hidden)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
-    flush_sink = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    flush_reader = torch.empty(256 << 20, dtype=torch.uint8, device="cuda").view(torch.int32)
 
     def flush_l2(i: int):
-        # write a buffer larger than L2, then stream a second one through it so that the weights are
+        # write a buffer larger than L2, then read a second one through the cache so that the weights are
         # cold AND the cache is not left full of dirty lines whose write-back would compete with the step
         flush.fill_(i & 0xFF)
-        flush_sink.copy_(flush)
+        flush_reader.max()
 
     def step():
         ctx.stack_forward(0, N_LAYERS, d_hidden, 1, d_out)
