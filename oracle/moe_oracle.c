@@ -270,6 +270,8 @@ typedef struct mo_matrix {
     uint32_t rows, cols;
     const void *qweight;     /* f16: u16[rows][cols]; q8: i8[rows][cols]; q4: u8[rows][cols/2] */
     const uint16_t *qscale;  /* fp16 [rows][cols/64]; unused for f16 */
+    int32_t through_f16;     /* != 0: each dequantised weight is rounded to fp16, the value the reference's tiled
+                                GPU GEMMs feed their MMA (src/backend/metal/kernels/gemm_q4.metal:35-57) */
 } mo_matrix;
 
 static int mo_matrix_ok(const mo_matrix *m) {
@@ -291,6 +293,7 @@ static void mo_dequant_row(const mo_matrix *m, uint32_t r, float *dst) {
     if (m->qtype == MO_QTYPE_Q8_0) {
         const int8_t *src = (const int8_t *)m->qweight + (size_t)r * C;
         for (uint32_t c = 0; c < C; ++c) dst[c] = (float)src[c] * mo_f16_to_f32(sc[c / MO_GROUP]);
+        if (m->through_f16) for (uint32_t c = 0; c < C; ++c) dst[c] = mo_f16_to_f32(mo_f32_to_f16(dst[c]));
         return;
     }
     const uint8_t *src = (const uint8_t *)m->qweight + (size_t)r * (C / 2u);
@@ -302,6 +305,7 @@ static void mo_dequant_row(const mo_matrix *m, uint32_t r, float *dst) {
             dst[g * MO_GROUP + MO_GROUP / 2u + j] = (float)((int)(byte >> 4) - 8) * s;
         }
     }
+    if (m->through_f16) for (uint32_t c = 0; c < C; ++c) dst[c] = mo_f16_to_f32(mo_f32_to_f16(dst[c]));
 }
 
 int mo_dequant_matrix(const mo_matrix *m, float *dst) {
@@ -351,6 +355,7 @@ static void mo_expert_matrices(const mo_layer_weights *L, uint32_t e, mo_matrix 
     const uint8_t *qw = (const uint8_t *)L->expert_qweight + (size_t)e * 3u * proj_bytes;
     const uint16_t *qs = L->expert_qscale ? L->expert_qscale + (size_t)e * 3u * proj_scales : NULL;
     gate->qtype = up->qtype = down->qtype = L->expert_qtype;
+    gate->through_f16 = up->through_f16 = down->through_f16 = L->shared_gate.through_f16;
     gate->rows = up->rows = L->F; gate->cols = up->cols = L->H;
     down->rows = L->H; down->cols = L->F;
     gate->qweight = qw; up->qweight = qw + proj_bytes; down->qweight = qw + 2u * proj_bytes;
@@ -363,10 +368,13 @@ static void mo_expert_matrices(const mo_layer_weights *L, uint32_t e, mo_matrix 
  * f32 layer above, so for any input
  *     mo_layer_slab(...) == mo_layer_f32(dequantised copies ...)   bit for bit.
  * injected_logits (rows x E, may be NULL) replaces the router dot products.
- * round_mid_f16 != 0 additionally rounds the SwiGLU products through fp16,
+ * round_mid_f16 bit 0 additionally rounds the SwiGLU products through fp16,
  * which is the rounding the GPU kernels apply when they store `mid`
- * (src/backend/metal/kernels/decode_gemv_q4.metal:176-179); the reference CPU
- * path itself keeps f32 (round_mid_f16 = 0).
+ * (src/backend/metal/kernels/decode_gemv_q4.metal:176-179); bit 1 rounds every
+ * expert's down product and the shared MLP's output through fp16, as the
+ * reference's many-token GPU path stores them before the combine
+ * (src/backend/metal/kernels/gemm_q8.metal:867-919).  The reference CPU path
+ * itself keeps f32 everywhere (round_mid_f16 = 0).
  * residual (fp16, may be NULL) is added to the f32 result at the end, the place
  * the GPU layer adds it (src/backend/metal/kernels/decode_gemv_q4.metal:221-223).
  * The experts are walked expert-major (each distinct expert is dequantised once
@@ -421,12 +429,13 @@ int mo_layer_slab(const mo_layer_weights *L, const uint16_t *hidden_f16, const u
                 float *mid = expert_ws + (size_t)where[i] * F;
                 for (uint32_t c = 0; c < F; ++c) {
                     float v = mo_silu(g[(size_t)i * F + c]) * u[(size_t)i * F + c];
-                    if (round_mid_f16) v = mo_f16_to_f32(mo_f32_to_f16(v));
+                    if (round_mid_f16 & 1) v = mo_f16_to_f32(mo_f32_to_f16(v));
                     mid[c] = v;
                 }
                 memcpy(xs + (size_t)i * F, mid, sizeof(float) * F);
             }
             mo_matmul_nt(&md, xs, cnt, d, scratch4);
+            if (round_mid_f16 & 2) for (size_t i = 0; i < (size_t)cnt * H; ++i) d[i] = mo_f16_to_f32(mo_f32_to_f16(d[i]));
             for (uint32_t i = 0; i < cnt; ++i) memcpy(down_all + (size_t)where[i] * H, d + (size_t)i * H, sizeof(float) * H);
         }
         if (ok) {
@@ -435,10 +444,11 @@ int mo_layer_slab(const mo_layer_weights *L, const uint16_t *hidden_f16, const u
             mo_matmul_nt(&L->shared_up, x, rows, u, scratch4);
             for (size_t i = 0; i < (size_t)rows * S; ++i) {
                 float v = mo_silu(g[i]) * u[i];
-                if (round_mid_f16) v = mo_f16_to_f32(mo_f32_to_f16(v));
+                if (round_mid_f16 & 1) v = mo_f16_to_f32(mo_f32_to_f16(v));
                 shared_ws[i] = v;
             }
             mo_matmul_nt(&L->shared_down, shared_ws, rows, d, scratch4);
+            if (round_mid_f16 & 2) for (size_t i = 0; i < (size_t)rows * H; ++i) d[i] = mo_f16_to_f32(mo_f32_to_f16(d[i]));
             for (uint32_t r = 0; r < rows; ++r) {
                 float *orow = out + (size_t)r * H;
                 for (uint32_t h = 0; h < H; ++h) orow[h] = 0.0f;

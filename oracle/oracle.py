@@ -40,7 +40,7 @@ def build(force: bool = False) -> None:
 
 class _Matrix(C.Structure):
     _fields_ = [("qtype", C.c_int32), ("rows", C.c_uint32), ("cols", C.c_uint32), ("qweight", C.c_void_p),
-                ("qscale", C.c_void_p)]
+                ("qscale", C.c_void_p), ("through_f16", C.c_int32)]
 
 
 class _Layer(C.Structure):
@@ -54,8 +54,8 @@ def _ptr(a: np.ndarray | None) -> int | None:
     return None if a is None else a.ctypes.data
 
 
-def _cmatrix(m: quant.Matrix) -> _Matrix:
-    return _Matrix(m.qtype, m.rows, m.cols, _ptr(m.qweight), _ptr(m.qscale))
+def _cmatrix(m: quant.Matrix, through_f16: bool = False) -> _Matrix:
+    return _Matrix(m.qtype, m.rows, m.cols, _ptr(m.qweight), _ptr(m.qscale), int(through_f16))
 
 
 class RouterOut:
@@ -148,13 +148,16 @@ class Port:
 
     # -- model-format call
     def layer(self, L: quant.LayerWeights, hidden: np.ndarray, residual: np.ndarray | None = None, *,
-              injected_logits: np.ndarray | None = None, round_mid_f16: bool = False, threads: int = 1) -> LayerOut:
+              injected_logits: np.ndarray | None = None, round_mid_f16: bool | int = False, weights_through_f16: bool = False,
+              threads: int = 1) -> LayerOut:
+        """round_mid_f16: bit 0 rounds the SwiGLU products through fp16, bit 1 the per-expert down products and the
+        shared output; weights_through_f16 rounds every dequantised weight to fp16 (the tiled-GEMM contract)."""
         hidden = np.ascontiguousarray(hidden, np.uint16)
         rows = hidden.shape[0]
         o = LayerOut(rows, L.H, L.E, L.K, L.F, L.S)
         cl = _Layer(L.H, L.E, L.K, L.F, L.S, L.scaling, _ptr(L.router), _ptr(L.logit_bias), L.expert_qtype,
-                    _ptr(L.expert_qweight), _ptr(L.expert_qscale), _cmatrix(L.shared_gate), _cmatrix(L.shared_up),
-                    _cmatrix(L.shared_down))
+                    _ptr(L.expert_qweight), _ptr(L.expert_qscale), _cmatrix(L.shared_gate, weights_through_f16),
+                    _cmatrix(L.shared_up, weights_through_f16), _cmatrix(L.shared_down, weights_through_f16))
         if residual is not None:
             residual = np.ascontiguousarray(residual, np.uint16)
         if injected_logits is not None:

@@ -233,11 +233,14 @@ def test_dispatch_plan_is_the_stable_sort(pkg, port, n, K, E):
 
 # ---------------------------------------------------------------------------- layer output
 
-def check_layer(pkg, port, L, hidden, resid, *, tight=2.5e-3):
-    """Forward with the oracle's logits injected (so both sides route identically) and compare."""
+def check_layer(pkg, port, L, hidden, resid, *, tight=2.5e-3, gemm=False):
+    """Forward with the oracle's logits injected (so both sides route identically) and compare.
+    gemm=True: the call takes the tensor-core path, whose extra roundings (weights, per-expert down
+    products and the shared output pass through fp16, as in the reference's tiled GPU GEMMs) are
+    reproduced by the second oracle run."""
     n = hidden.shape[0]
-    want = port.layer(L, hidden, resid, threads=8)
-    contract = port.layer(L, hidden, resid, round_mid_f16=True, threads=8)
+    want = port.layer(L, hidden, resid, threads=16)
+    contract = port.layer(L, hidden, resid, round_mid_f16=3 if gemm else 1, weights_through_f16=gemm, threads=16)
     L2 = quant.LayerWeights(**{**L.__dict__, "logit_bias": None})
     g = Layer(pkg, L2, n)
     try:
@@ -275,7 +278,31 @@ def test_full_size_decode_layer(pkg, port, qname, shared):
 def test_batched_decode_q8_with_skewed_load(pkg, port, n):
     """Config 3: Q8_0, per-expert logit bias N(0,1)."""
     L, hidden, resid = make(2, FULL, "q8_0", n, bias="normal")
-    check_layer(pkg, port, L, hidden, resid)
+    check_layer(pkg, port, L, hidden, resid, gemm=n >= 5)
+
+
+@pytest.mark.parametrize("qname,shared,n,bias", [("q4_0", None, 200, None), ("f16", None, 96, None),
+                                                 ("q8_0", None, 130, "normal"), ("q4_0", "q8_0", 77, "zipf"),
+                                                 ("q4_0", None, 1024, "zipf"), ("f16", None, 1024, "zipf")])
+def test_prefill_tensor_core_path(pkg, port, qname, shared, n, bias):
+    """Config 4 shapes: many tokens, Zipf-skewed expert popularity, grouped GEMMs on tcgen05."""
+    L, hidden, resid = make(3, FULL, qname, n, bias=bias, shared_qname=shared)
+    check_layer(pkg, port, L, hidden, resid, gemm=True)
+
+
+def test_tensor_core_and_matrix_vector_paths_agree(pkg, port, monkeypatch):
+    """The same 24-token call through the grouped-GEMM path and through the matrix-vector path."""
+    L, hidden, resid = make(8, FULL, "q4_0", 24, bias="normal")
+    outs = {}
+    for mode, min_tokens in (("gemm", "5"), ("gemv", "100000")):
+        monkeypatch.setenv("UOCR_CUDA_GEMM_MIN_TOKENS", min_tokens)
+        with pkg.Context() as ctx:
+            ctx.map_layer(L)
+            ctx.allocate_runtime_arenas(24)
+            outs[mode] = ctx.layer_forward_host(0, hidden, resid, want_routing=True)
+    assert np.array_equal(outs["gemm"][1], outs["gemv"][1])
+    err, cos = closeness(outs["gemm"][0].view("<f2").astype(np.float32), outs["gemv"][0].view("<f2").astype(np.float32))
+    assert err <= 8e-3 and cos >= 0.99999, (err, cos)
 
 
 def test_ragged_sizes_and_scaling(pkg, port):

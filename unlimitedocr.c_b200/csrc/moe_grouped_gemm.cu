@@ -1,0 +1,576 @@
+// Many-token MoE layer: expert-grouped GEMMs on the 5th-generation tensor cores.
+//
+// After the dispatch plan the (token, slot) pairs of one expert are contiguous, so each expert is a
+// dense product.  Both products are computed "weights as rows":
+//     gate/up :  [128 weight rows] x [<=128 tokens]  over K = H,  two accumulators (gate, up) ->
+//                mid[pos][f] = fp16( silu(gate) * up )
+//     down    :  [128 weight rows] x [<=128 tokens]  over K = F (or S) -> down_out[pos][h] = fp16(acc)
+// With the weights on the M side of the MMA a cold expert with a handful of tokens pads its token
+// count to 16, not to 128, which matters under Zipf-skewed routing.
+//
+// One CTA computes one tile; two CTAs share an SM (<= 256 TMEM columns and ~100 KB shared memory
+// each), so one tile's epilogue overlaps the other's main loop.  Per 64-wide K block (= one scale
+// group of the weight formats, = one 128-byte swizzle row of fp16):
+//   warps 0-3  each thread owns one weight row of the tile: loads its packed bytes (32 B for Q4_0) with
+//              128-bit loads, turns them into fp16( level * scale ) in registers and writes the row
+//              into the stage's 128B-swizzled K-major tile; no dequantised copy of a weight ever
+//              reaches global memory.  The same warps run the epilogue.
+//   warp 4     one thread issues the TMA tile load (cp.async.bulk.tensor) of the activation tile.
+//   warp 5     one thread issues tcgen05.mma (kind::f16, fp32 accumulators in TMEM) and commits the
+//              stage back to the producers; the warp also owns the TMEM allocation.
+// Every wait is bounded; on a time-out the CTA raises a status bit, drains and returns.
+#include <cuda.h>
+#include <cudaTypedefs.h>
+
+#include "moe_common.cuh"
+
+namespace uocr {
+
+constexpr int kGemmThreads = 192;
+constexpr int kTileM = 128;          // weight rows per tile = TMEM lanes
+constexpr int kTileN = 128;          // tokens per tile (TMEM columns per accumulator)
+constexpr int kBlockK = 64;          // fp16 elements per K block = 128 bytes = one swizzle row
+constexpr int kTileBytes = kTileM * kBlockK * 2;   // 16 KB: one operand tile of one stage
+constexpr long long kGemmSpinLimit = 4000000000LL;
+constexpr uint32_t kStatusGemm = 8u;
+
+struct GemmParams {
+    const uint8_t *w0, *w1;        // packed weights: gate and up (gate/up mode) or down (w1 unused)
+    const __half *s0, *s1;         // their scales (null for fp16 weights)
+    uint64_t expert_stride_bytes;  // between experts in the packed slab (0 for the shared MLP)
+    uint64_t expert_scale_stride;  // in values
+    uint32_t row_bytes;            // packed bytes of one weight row
+    uint32_t k_dim;                // input width K (multiple of 64)
+    const uint4 *tiles;            // {expert, weight-row tile, first row of the activation matrix, rows}
+    const uint32_t *tile_count;
+    __half *out;                   // mid / down_out, [rows][out_ld]
+    uint32_t out_ld;
+    uint32_t *status;
+};
+
+// ---------------------------------------------------------------------------------- PTX
+__device__ __forceinline__ uint32_t s2u(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void gb_init(uint64_t *bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(s2u(bar)), "r"(count));
+}
+__device__ __forceinline__ void gb_arrive(uint64_t *bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(s2u(bar)) : "memory");
+}
+__device__ __forceinline__ void gb_expect_tx(uint64_t *bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(s2u(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool gb_try(uint64_t *bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(s2u(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait; also gives up as soon as another role of the CTA has raised the abort flag.
+__device__ __forceinline__ bool gb_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag, uint32_t *status) {
+    if (gb_try(bar, parity)) return true;
+    const long long t0 = clock64();
+    uint32_t polls = 0;
+    while (!gb_try(bar, parity)) {
+        if ((++polls & 255u) == 0u) {
+            if (*abort_flag) return false;
+            if (clock64() - t0 > kGemmSpinLimit) {
+                *abort_flag = 1;
+                atomicOr(status, kStatusGemm);
+                return false;
+            }
+        }
+    }
+    return true;
+}
+__device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *map, int x, int y, uint64_t *bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(s2u(dst)), "l"(map), "r"(x), "r"(y), "r"(s2u(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void proxy_fence() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+__device__ __forceinline__ void tc_commit(uint64_t *bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(s2u(bar)) : "memory");
+}
+// D[tmem] (+)= A[smem] * B[smem]^T, fp16 inputs, fp32 accumulate, M = 128, N from the descriptor, K = 16
+__device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// 16 consecutive fp32 columns of this thread's TMEM lane
+__device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t (&v)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+        : "r"(taddr));
+}
+__device__ __forceinline__ void tc_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// K-major operand tile, 128-byte rows, 128B swizzle, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
+    return (uint64_t)((smem_addr >> 4) & 0x3FFFu) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
+}
+// kind::f16 instruction descriptor: fp16 A and B (K-major), fp32 D, M = 128, N = n
+__device__ __forceinline__ uint32_t umma_idesc(uint32_t n) {
+    return (1u << 4) | ((n >> 3) << 17) | ((uint32_t)(kTileM >> 4) << 24);
+}
+
+// ---------------------------------------------------------------------- dequantisation
+// One weight row of one K block -> 64 fp16 values = eight 16-byte chunks, written at their swizzled
+// positions: chunk c of row r lives at r*128 + ((c ^ (r & 7)) << 4).
+__device__ __forceinline__ void store_chunk(uint8_t *tile, int r, int c, uint4 v) {
+    *reinterpret_cast<uint4 *>(tile + r * 128 + ((c ^ (r & 7)) << 4)) = v;
+}
+
+__device__ __forceinline__ uint32_t h2_as_u32(__half2 h) { return *reinterpret_cast<uint32_t *>(&h); }
+
+// four bytes holding values 0..255 in a word -> two half2 (b0,b1), (b2,b3) of (value - bias) * scale, each
+// product rounded to fp16 once: fp16( float(level) * float(scale) ), the value the reference's tiled GEMMs feed
+// their MMA (src/backend/metal/kernels/gemm_q4.metal:35-57, gemm_q8.metal:43-60).
+__device__ __forceinline__ void bytes_to_h2(uint32_t bytes, __half2 bias, __half2 scale, uint32_t &lo, uint32_t &hi) {
+    const uint32_t a = __byte_perm(bytes, 0x64646464u, 0x5140);   // [b0, 0x64, b1, 0x64] = (1024 + b0, 1024 + b1)
+    const uint32_t b = __byte_perm(bytes, 0x64646464u, 0x5342);   // (1024 + b2, 1024 + b3)
+    lo = h2_as_u32(__hmul2(__hsub2(*reinterpret_cast<const __half2 *>(&a), bias), scale));
+    hi = h2_as_u32(__hmul2(__hsub2(*reinterpret_cast<const __half2 *>(&b), bias), scale));
+}
+
+template <int QT> struct PackedBlock;   // packed bytes of one row of one K block, as uint4s
+template <> struct PackedBlock<UOCR_QT_Q4> { static constexpr int kVecs = 2; };
+template <> struct PackedBlock<UOCR_QT_Q8> { static constexpr int kVecs = 4; };
+template <> struct PackedBlock<UOCR_QT_F16> { static constexpr int kVecs = 8; };
+
+template <int QT>
+__device__ __forceinline__ void load_block(const uint8_t *row, uint32_t kb, uint4 (&v)[PackedBlock<QT>::kVecs]) {
+    const uint4 *p = reinterpret_cast<const uint4 *>(row) + (size_t)kb * PackedBlock<QT>::kVecs;
+#pragma unroll
+    for (int i = 0; i < PackedBlock<QT>::kVecs; ++i) v[i] = __ldg(p + i);
+}
+
+template <int QT>
+__device__ __forceinline__ void dequant_row(const uint4 (&v)[PackedBlock<QT>::kVecs], __half scale, uint8_t *tile, int r) {
+    if (QT == UOCR_QT_F16) {
+#pragma unroll
+        for (int c = 0; c < 8; ++c) store_chunk(tile, r, c, v[c]);
+    } else if (QT == UOCR_QT_Q8) {
+        const __half2 s2 = __half2half2(scale), bias = __float2half2_rn(1152.f);   // 1024 + 128
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {          // 16 bytes = 16 weights = chunks 2i, 2i+1
+            const uint32_t w[4] = {v[i].x ^ 0x80808080u, v[i].y ^ 0x80808080u, v[i].z ^ 0x80808080u, v[i].w ^ 0x80808080u};
+            uint4 c0, c1;
+            bytes_to_h2(w[0], bias, s2, c0.x, c0.y);
+            bytes_to_h2(w[1], bias, s2, c0.z, c0.w);
+            bytes_to_h2(w[2], bias, s2, c1.x, c1.y);
+            bytes_to_h2(w[3], bias, s2, c1.z, c1.w);
+            store_chunk(tile, r, 2 * i, c0);
+            store_chunk(tile, r, 2 * i + 1, c1);
+        }
+    } else {
+        // Q4_0 half-split: byte j of the 32 holds column j (low nibble) and column j + 32 (high nibble)
+        const __half2 s2 = __half2half2(scale), bias = __float2half2_rn(1032.f);    // 1024 + 8
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {          // bytes 16i .. 16i+15: low -> chunks 2i, 2i+1; high -> chunks 4+2i, 5+2i
+            const uint32_t w[4] = {v[i].x, v[i].y, v[i].z, v[i].w};
+            uint4 l0, l1, h0, h1;
+            bytes_to_h2(w[0] & 0x0F0F0F0Fu, bias, s2, l0.x, l0.y);
+            bytes_to_h2(w[1] & 0x0F0F0F0Fu, bias, s2, l0.z, l0.w);
+            bytes_to_h2(w[2] & 0x0F0F0F0Fu, bias, s2, l1.x, l1.y);
+            bytes_to_h2(w[3] & 0x0F0F0F0Fu, bias, s2, l1.z, l1.w);
+            bytes_to_h2((w[0] >> 4) & 0x0F0F0F0Fu, bias, s2, h0.x, h0.y);
+            bytes_to_h2((w[1] >> 4) & 0x0F0F0F0Fu, bias, s2, h0.z, h0.w);
+            bytes_to_h2((w[2] >> 4) & 0x0F0F0F0Fu, bias, s2, h1.x, h1.y);
+            bytes_to_h2((w[3] >> 4) & 0x0F0F0F0Fu, bias, s2, h1.z, h1.w);
+            store_chunk(tile, r, 2 * i, l0);
+            store_chunk(tile, r, 2 * i + 1, l1);
+            store_chunk(tile, r, 4 + 2 * i, h0);
+            store_chunk(tile, r, 5 + 2 * i, h1);
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------ kernel
+template <bool GATEUP> struct GemmShape {
+    static constexpr int kATiles = GATEUP ? 2 : 1;                     // weight tiles per stage
+    static constexpr int kStages = GATEUP ? 2 : 3;
+    static constexpr int kStageBytes = (kATiles + 1) * kTileBytes;     // + the activation tile
+    static constexpr int kTmemCols = GATEUP ? 256 : 128;
+    static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment*/ + 256 /*barriers*/;
+};
+
+template <int QT, bool GATEUP>
+__global__ void __launch_bounds__(kGemmThreads, 2)
+grouped_gemm_kernel(const __grid_constant__ CUtensorMap act_map, GemmParams p) {
+    using Sh = GemmShape<GATEUP>;
+    constexpr int kStages = Sh::kStages;
+    if (blockIdx.x >= *p.tile_count) return;
+    const uint4 tile = p.tiles[blockIdx.x];
+    const uint32_t expert = tile.x, mtile = tile.y, row0 = tile.z, nrows = tile.w;
+    const uint32_t n_mma = (nrows + 15u) & ~15u;          // MMA N: multiple of 16, 16..128
+    const uint32_t kblocks = p.k_dim / kBlockK;
+
+    extern __shared__ uint8_t smem_dyn[];
+    uint8_t *stages = reinterpret_cast<uint8_t *>(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(stages + kStages * Sh::kStageBytes);
+    uint64_t *full_a = bars, *full_b = bars + kStages, *empty = bars + 2 * kStages, *acc_full = bars + 3 * kStages;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 3 * kStages + 1);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    if (tid == 0) {
+        for (int s = 0; s < kStages; ++s) { gb_init(&full_a[s], 128); gb_init(&full_b[s], 1); gb_init(&empty[s], 1); }
+        gb_init(acc_full, 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 5) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(s2u(tmem_slot)), "r"((uint32_t)Sh::kTmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp < 4) {
+        // ------------------------------------------------ weight rows -> fp16 swizzled tiles
+        const int r = tid;                                            // row of the tile
+        const size_t grow = (size_t)mtile * kTileM + r;               // row of the matrix
+        const uint8_t *row0p = p.w0 + (size_t)expert * p.expert_stride_bytes + grow * p.row_bytes;
+        const uint8_t *row1p = GATEUP ? p.w1 + (size_t)expert * p.expert_stride_bytes + grow * p.row_bytes : nullptr;
+        const __half *sc0 = QT == UOCR_QT_F16 ? nullptr : p.s0 + (size_t)expert * p.expert_scale_stride + grow * kblocks;
+        const __half *sc1 = (QT == UOCR_QT_F16 || !GATEUP) ? nullptr : p.s1 + (size_t)expert * p.expert_scale_stride + grow * kblocks;
+        uint4 v0[PackedBlock<QT>::kVecs], v1[PackedBlock<QT>::kVecs];
+        load_block<QT>(row0p, 0, v0);
+        if (GATEUP) load_block<QT>(row1p, 0, v1);
+        for (uint32_t kb = 0; kb < kblocks; ++kb) {
+            const int s = kb % kStages;
+            const uint32_t use = kb / kStages;
+            const __half sa = QT == UOCR_QT_F16 ? __ushort_as_half(0) : sc0[kb];
+            const __half sb = (QT == UOCR_QT_F16 || !GATEUP) ? __ushort_as_half(0) : sc1[kb];
+            if (use > 0 && !gb_wait(&empty[s], (use - 1) & 1u, abort_flag, p.status)) break;
+            uint8_t *st = stages + s * Sh::kStageBytes;
+            dequant_row<QT>(v0, sa, st, r);
+            if (GATEUP) dequant_row<QT>(v1, sb, st + kTileBytes, r);
+            if (kb + 1 < kblocks) {                                   // next block's bytes travel while this one is used
+                load_block<QT>(row0p, kb + 1, v0);
+                if (GATEUP) load_block<QT>(row1p, kb + 1, v1);
+            }
+            proxy_fence();                                            // generic-proxy stores -> visible to the MMA's async proxy
+            gb_arrive(&full_a[s]);
+        }
+        // ------------------------------------------------ epilogue: TMEM -> registers -> global
+        if (gb_wait(acc_full, 0, abort_flag, p.status)) {
+            tc_fence_after();
+            const uint32_t lane_base = tmem_base + ((uint32_t)(warp * 32) << 16);
+            const size_t out_col = (size_t)mtile * kTileM + r;
+            for (uint32_t c0 = 0; c0 < nrows; c0 += 16) {
+                uint32_t g[16], u[16];
+                tc_ld16(lane_base + c0, g);
+                if (GATEUP) tc_ld16(lane_base + kTileN + c0, u);
+                tc_ld_wait();
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    if (c0 + j < nrows) {
+                        const float a = __uint_as_float(g[j]);
+                        const float o = GATEUP ? silu_f32(a) * __uint_as_float(u[j]) : a;
+                        p.out[(size_t)(row0 + c0 + j) * p.out_ld + out_col] = __float2half_rn(o);
+                    }
+                }
+            }
+        }
+        tc_fence_before();
+    } else if (warp == 4) {
+        // ------------------------------------------------ activation tiles by TMA
+        if (lane == 0) {
+            for (uint32_t kb = 0; kb < kblocks; ++kb) {
+                const int s = kb % kStages;
+                const uint32_t use = kb / kStages;
+                if (use > 0 && !gb_wait(&empty[s], (use - 1) & 1u, abort_flag, p.status)) break;
+                gb_expect_tx(&full_b[s], kTileBytes);
+                tma_load_2d(stages + s * Sh::kStageBytes + Sh::kATiles * kTileBytes, &act_map, (int)(kb * kBlockK), (int)row0,
+                            &full_b[s]);
+            }
+        }
+    } else {
+        // ------------------------------------------------ MMA issue
+        if (lane == 0) {
+            const uint32_t idesc = umma_idesc(n_mma);
+            bool ok = true;
+            for (uint32_t kb = 0; kb < kblocks && ok; ++kb) {
+                const int s = kb % kStages;
+                const uint32_t ph = (kb / kStages) & 1u;
+                ok = gb_wait(&full_a[s], ph, abort_flag, p.status) && gb_wait(&full_b[s], ph, abort_flag, p.status);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t a_addr = s2u(stages + s * Sh::kStageBytes);
+                const uint32_t b_addr = a_addr + Sh::kATiles * kTileBytes;
+#pragma unroll
+                for (int k = 0; k < kBlockK / 16; ++k) {
+                    const uint32_t acc = (kb > 0 || k > 0) ? 1u : 0u;
+                    const uint64_t bd = umma_desc(b_addr + k * 32);
+                    tc_mma(tmem_base, umma_desc(a_addr + k * 32), bd, idesc, acc);
+                    if (GATEUP) tc_mma(tmem_base + kTileN, umma_desc(a_addr + kTileBytes + k * 32), bd, idesc, acc);
+                }
+                tc_commit(&empty[s]);            // arrives when the MMAs above have read the stage
+            }
+            if (ok) tc_commit(acc_full);
+        }
+        __syncwarp();
+    }
+    __syncthreads();
+    if (*abort_flag) {
+        // a wait gave up: let copies and MMAs that may still be in flight land before the CTA goes away
+        const long long t0 = clock64();
+        while (clock64() - t0 < 2000000LL) {}
+        __syncthreads();
+    }
+    if (warp == 5) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)Sh::kTmemCols) : "memory");
+    }
+}
+
+// --------------------------------------------------------------------- helper kernels
+// Tile lists of the routed GEMMs: for every expert with pairs, one tile per (128 tokens, 128 weight rows).
+// tiles_gu / tiles_dn get {expert, weight-row tile, first sorted position, rows}; counts[0/1] their lengths.
+__global__ void tile_plan_kernel(const uint32_t *__restrict__ expert_offsets, uint32_t E, uint32_t gu_mtiles,
+                                 uint32_t dn_mtiles, uint4 *__restrict__ tiles_gu, uint4 *__restrict__ tiles_dn,
+                                 uint32_t *__restrict__ counts) {
+    __shared__ uint32_t base[257];
+    const uint32_t e = threadIdx.x;
+    uint32_t ttiles = 0;
+    if (e < E) ttiles = (expert_offsets[e + 1] - expert_offsets[e] + kTileN - 1) / kTileN;
+    if (e <= 256) base[e] = 0;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        uint32_t run = 0;
+        for (uint32_t i = 0; i < E; ++i) {
+            const uint32_t t = (expert_offsets[i + 1] - expert_offsets[i] + kTileN - 1) / kTileN;
+            base[i] = run;
+            run += t;
+        }
+        base[E] = run;
+        counts[0] = run * gu_mtiles;
+        counts[1] = run * dn_mtiles;
+    }
+    __syncthreads();
+    if (e < E) {
+        const uint32_t lo = expert_offsets[e], cnt = expert_offsets[e + 1] - lo;
+        for (uint32_t t = 0; t < ttiles; ++t) {
+            const uint32_t r0 = lo + t * kTileN, nr = min((uint32_t)kTileN, cnt - t * kTileN);
+            for (uint32_t m = 0; m < gu_mtiles; ++m) tiles_gu[(size_t)(base[e] + t) * gu_mtiles + m] = make_uint4(e, m, r0, nr);
+            for (uint32_t m = 0; m < dn_mtiles; ++m) tiles_dn[(size_t)(base[e] + t) * dn_mtiles + m] = make_uint4(e, m, r0, nr);
+        }
+    }
+}
+
+// Tile lists of the shared MLP (one "expert", all n tokens).
+__global__ void shared_tile_plan_kernel(uint32_t n, uint32_t gu_mtiles, uint32_t dn_mtiles, uint4 *__restrict__ tiles_gu,
+                                        uint4 *__restrict__ tiles_dn, uint32_t *__restrict__ counts) {
+    const uint32_t ttiles = (n + kTileN - 1) / kTileN;
+    for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < ttiles * max(gu_mtiles, dn_mtiles); i += gridDim.x * blockDim.x) {
+        const uint32_t t = i / max(gu_mtiles, dn_mtiles), m = i % max(gu_mtiles, dn_mtiles);
+        const uint32_t r0 = t * kTileN, nr = min((uint32_t)kTileN, n - r0);
+        if (m < gu_mtiles) tiles_gu[(size_t)t * gu_mtiles + m] = make_uint4(0, m, r0, nr);
+        if (m < dn_mtiles) tiles_dn[(size_t)t * dn_mtiles + m] = make_uint4(0, m, r0, nr);
+    }
+    if (blockIdx.x == 0 && threadIdx.x == 0) { counts[0] = ttiles * gu_mtiles; counts[1] = ttiles * dn_mtiles; }
+}
+
+// x_sorted[pos][:] = hidden[pair_rows[pos] / K][:]  (one warp per row, 16-byte copies)
+__global__ void gather_rows_kernel(const __half *__restrict__ hidden, const uint32_t *__restrict__ pair_rows,
+                                   const uint32_t *__restrict__ expert_offsets, uint32_t E, uint32_t K, uint32_t H,
+                                   __half *__restrict__ x_sorted) {
+    const uint32_t total = expert_offsets[E];
+    const uint32_t warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+    if (warp >= total) return;
+    const uint4 *src = reinterpret_cast<const uint4 *>(hidden + (size_t)(pair_rows[warp] / K) * H);
+    uint4 *dst = reinterpret_cast<uint4 *>(x_sorted + (size_t)warp * H);
+    for (uint32_t i = lane; i < H / 8; i += 32) dst[i] = __ldg(src + i);
+}
+
+// out[t][h] = fp16( fma chain over slots of weight * down_out[inverse[pair]][h], + shared_out[t][h], + residual )
+__global__ void combine_sorted_kernel(const __half *__restrict__ down_out, const __half *__restrict__ shared_out,
+                                      const __half *__restrict__ residual, const uint32_t *__restrict__ inverse,
+                                      const float *__restrict__ weights, uint32_t n, uint32_t H, uint32_t K,
+                                      __half *__restrict__ out) {
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;       // one thread per 8 outputs
+    const uint32_t per_row = H / 8;
+    if (idx >= (size_t)n * per_row) return;
+    const uint32_t t = (uint32_t)(idx / per_row), c = (uint32_t)(idx % per_row) * 8;
+    float acc[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+    for (uint32_t s = 0; s < K; ++s) {
+        const uint32_t pos = inverse[t * K + s];
+        if (pos == 0xffffffffu) continue;
+        const float w = weights[t * K + s];
+        const uint4 v = *reinterpret_cast<const uint4 *>(down_out + (size_t)pos * H + c);
+        const __half2 *h = reinterpret_cast<const __half2 *>(&v);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 f = __half22float2(h[i]);
+            acc[2 * i] = fmaf(w, f.x, acc[2 * i]);
+            acc[2 * i + 1] = fmaf(w, f.y, acc[2 * i + 1]);
+        }
+    }
+    {
+        const uint4 v = *reinterpret_cast<const uint4 *>(shared_out + (size_t)t * H + c);
+        const __half2 *h = reinterpret_cast<const __half2 *>(&v);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 f = __half22float2(h[i]);
+            acc[2 * i] += f.x; acc[2 * i + 1] += f.y;
+        }
+    }
+    if (residual) {
+        const uint4 v = *reinterpret_cast<const uint4 *>(residual + (size_t)t * H + c);
+        const __half2 *h = reinterpret_cast<const __half2 *>(&v);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 f = __half22float2(h[i]);
+            acc[2 * i] += f.x; acc[2 * i + 1] += f.y;
+        }
+    }
+    uint4 o;
+    __half2 *oh = reinterpret_cast<__half2 *>(&o);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) oh[i] = __floats2half2_rn(acc[2 * i], acc[2 * i + 1]);
+    *reinterpret_cast<uint4 *>(out + (size_t)t * H + c) = o;
+}
+
+// ---------------------------------------------------------------------------- host side
+static PFN_cuTensorMapEncodeTiled_v12000 g_encode = nullptr;
+
+cudaError_t init_gemm_kernels() {
+    if (g_encode == nullptr) {
+        void *fn = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        cudaError_t err = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
+        if (err != cudaSuccess) return err;
+        if (qres != cudaDriverEntryPointSuccess || fn == nullptr) return cudaErrorNotSupported;
+        g_encode = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(fn);
+    }
+    cudaError_t err = cudaSuccess;
+#define UOCR_SET_SMEM(QT, GU)                                                                                    \
+    if (err == cudaSuccess)                                                                                      \
+        err = cudaFuncSetAttribute(grouped_gemm_kernel<QT, GU>, cudaFuncAttributeMaxDynamicSharedMemorySize,     \
+                                   GemmShape<GU>::kSmemBytes);
+    UOCR_SET_SMEM(UOCR_QT_Q4, true) UOCR_SET_SMEM(UOCR_QT_Q4, false)
+    UOCR_SET_SMEM(UOCR_QT_Q8, true) UOCR_SET_SMEM(UOCR_QT_Q8, false)
+    UOCR_SET_SMEM(UOCR_QT_F16, true) UOCR_SET_SMEM(UOCR_QT_F16, false)
+#undef UOCR_SET_SMEM
+    return err;
+}
+
+// fp16 matrix [rows][cols] (cols contiguous) viewed as tiles of 128 rows x 64 columns, 128B swizzle, zero fill
+static cudaError_t make_act_map(CUtensorMap *map, const void *base, uint64_t rows, uint64_t cols) {
+    const cuuint64_t dims[2] = {cols, rows};
+    const cuuint64_t strides[1] = {cols * 2};
+    const cuuint32_t box[2] = {kBlockK, kTileN};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void *>(base), dims, strides, box, estr,
+                                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
+}
+
+bool gemm_path_supported(const DLayer &L) {
+    return L.H % 128 == 0 && L.F % 128 == 0 && L.S % 128 == 0 && L.E <= 256 && g_encode != nullptr;
+}
+
+template <bool GU>
+static cudaError_t launch_gemm(int qt, const CUtensorMap &map, const GemmParams &p, uint32_t max_tiles, cudaStream_t st) {
+    if (max_tiles == 0) return cudaSuccess;
+    const size_t smem = GemmShape<GU>::kSmemBytes;
+    switch (qt) {
+        case UOCR_QT_Q4: grouped_gemm_kernel<UOCR_QT_Q4, GU><<<max_tiles, kGemmThreads, smem, st>>>(map, p); break;
+        case UOCR_QT_Q8: grouped_gemm_kernel<UOCR_QT_Q8, GU><<<max_tiles, kGemmThreads, smem, st>>>(map, p); break;
+        default: grouped_gemm_kernel<UOCR_QT_F16, GU><<<max_tiles, kGemmThreads, smem, st>>>(map, p); break;
+    }
+    return cudaGetLastError();
+}
+
+static uint32_t packed_row_bytes_of(int qt, uint32_t cols) {
+    return qt == UOCR_QT_F16 ? cols * 2u : (qt == UOCR_QT_Q8 ? cols : cols / 2u);
+}
+
+// Scratch of the many-token path (all in the context arena).
+struct GemmScratch {
+    __half *x_sorted;       // [n*K][H] activations in expert-sorted order
+    __half *mid_sorted;     // [n*K][F]
+    __half *down_sorted;    // [n*K][H]
+    __half *shared_mid;     // [n][S]
+    __half *shared_out;     // [n][H]
+    uint4 *tiles_gu, *tiles_dn, *stiles_gu, *stiles_dn;
+    uint32_t *counts;       // [4]: routed gate/up, routed down, shared gate/up, shared down
+};
+
+cudaError_t launch_gemm_layer(const DLayer &L, const Scratch &S, const GemmScratch &G, const __half *hidden,
+                              const __half *residual, uint32_t n, __half *out, cudaStream_t st, uint64_t *launches) {
+    const uint32_t H = L.H, F = L.F, Sd = L.S, K = L.K, E = L.E;
+    const uint32_t pairs = n * K;
+    const uint32_t ttiles_max = (pairs + kTileN - 1) / kTileN + E;
+    const uint32_t sttiles = (n + kTileN - 1) / kTileN;
+    cudaError_t err;
+
+    tile_plan_kernel<<<1, 256, 0, st>>>(S.expert_offsets, E, F / kTileM, H / kTileM, G.tiles_gu, G.tiles_dn, G.counts);
+    shared_tile_plan_kernel<<<8, 256, 0, st>>>(n, Sd / kTileM, H / kTileM, G.stiles_gu, G.stiles_dn, G.counts + 2);
+    gather_rows_kernel<<<(pairs * 32 + 255) / 256, 256, 0, st>>>(hidden, S.pair_rows, S.expert_offsets, E, K, H, G.x_sorted);
+    *launches += 3;
+    if ((err = cudaGetLastError()) != cudaSuccess) return err;
+
+    CUtensorMap map_x, map_mid, map_hidden, map_smid;
+    if ((err = make_act_map(&map_x, G.x_sorted, pairs, H)) != cudaSuccess) return err;
+    if ((err = make_act_map(&map_mid, G.mid_sorted, pairs, F)) != cudaSuccess) return err;
+    if ((err = make_act_map(&map_hidden, hidden, n, H)) != cudaSuccess) return err;
+    if ((err = make_act_map(&map_smid, G.shared_mid, n, Sd)) != cudaSuccess) return err;
+
+    const int qt = L.expert_qtype;
+    GemmParams p{};
+    p.status = S.status;
+    // routed gate/up
+    p.w0 = L.expert_w; p.w1 = L.expert_w + L.up_offset_bytes;
+    p.s0 = L.expert_s; p.s1 = L.expert_s ? L.expert_s + L.up_scale_offset : nullptr;
+    p.expert_stride_bytes = L.expert_stride_bytes; p.expert_scale_stride = L.expert_scale_stride;
+    p.row_bytes = packed_row_bytes_of(qt, H); p.k_dim = H;
+    p.tiles = G.tiles_gu; p.tile_count = G.counts; p.out = G.mid_sorted; p.out_ld = F;
+    if ((err = launch_gemm<true>(qt, map_x, p, ttiles_max * (F / kTileM), st)) != cudaSuccess) return err;
+    // shared gate/up
+    p.w0 = L.shared_gate.w; p.w1 = L.shared_up.w; p.s0 = L.shared_gate.s; p.s1 = L.shared_up.s;
+    p.expert_stride_bytes = 0; p.expert_scale_stride = 0;
+    p.row_bytes = L.shared_gate.row_bytes; p.k_dim = H;
+    p.tiles = G.stiles_gu; p.tile_count = G.counts + 2; p.out = G.shared_mid; p.out_ld = Sd;
+    if ((err = launch_gemm<true>(L.shared_gate.qtype, map_hidden, p, sttiles * (Sd / kTileM), st)) != cudaSuccess) return err;
+    // routed down
+    p.w0 = L.expert_w + L.down_offset_bytes; p.w1 = nullptr;
+    p.s0 = L.expert_s ? L.expert_s + L.down_scale_offset : nullptr; p.s1 = nullptr;
+    p.expert_stride_bytes = L.expert_stride_bytes; p.expert_scale_stride = L.expert_scale_stride;
+    p.row_bytes = packed_row_bytes_of(qt, F); p.k_dim = F;
+    p.tiles = G.tiles_dn; p.tile_count = G.counts + 1; p.out = G.down_sorted; p.out_ld = H;
+    if ((err = launch_gemm<false>(qt, map_mid, p, ttiles_max * (H / kTileM), st)) != cudaSuccess) return err;
+    // shared down
+    p.w0 = L.shared_down.w; p.s0 = L.shared_down.s;
+    p.expert_stride_bytes = 0; p.expert_scale_stride = 0;
+    p.row_bytes = L.shared_down.row_bytes; p.k_dim = Sd;
+    p.tiles = G.stiles_dn; p.tile_count = G.counts + 3; p.out = G.shared_out; p.out_ld = H;
+    if ((err = launch_gemm<false>(L.shared_down.qtype, map_smid, p, sttiles * (H / kTileM), st)) != cudaSuccess) return err;
+    *launches += 4;
+
+    const size_t work = (size_t)n * (H / 8);
+    combine_sorted_kernel<<<(unsigned)((work + 255) / 256), 256, 0, st>>>(G.down_sorted, G.shared_out, residual, S.inverse,
+                                                                          S.top_weights, n, H, K, out);
+    ++*launches;
+    return cudaGetLastError();
+}
+
+}  // namespace uocr

@@ -16,6 +16,15 @@ namespace uocr {
 cudaError_t init_router_kernels();
 cudaError_t init_small_batch_kernels();
 cudaError_t init_decode_kernels();
+cudaError_t init_gemm_kernels();
+bool gemm_path_supported(const DLayer &L);
+struct GemmScratch {
+    __half *x_sorted, *mid_sorted, *down_sorted, *shared_mid, *shared_out;
+    uint4 *tiles_gu, *tiles_dn, *stiles_gu, *stiles_dn;
+    uint32_t *counts;
+};
+cudaError_t launch_gemm_layer(const DLayer &L, const Scratch &S, const GemmScratch &G, const __half *hidden,
+                              const __half *residual, uint32_t n, __half *out, cudaStream_t st, uint64_t *launches);
 int decode_grid_size();
 bool decode_supported(const DLayer *layers, uint32_t first, uint32_t count);
 cudaError_t launch_decode_stack(const DLayer *h_layers, const DLayer *d_layers, uint32_t first, uint32_t count,
@@ -40,6 +49,7 @@ struct uocr_cuda_context {
     std::vector<DLayer> layers;
     DLayer *d_layers = nullptr;        // device copy of `layers`
     bool fused_decode = true;          // single-token calls use the persistent decode kernel when it fits
+    uint32_t gemm_min_tokens = 5;      // calls with at least this many tokens take the tensor-core path
     unsigned long long bar_base = 0;   // value the decode kernel's barrier counter has reached
     unsigned long long *decode_trace = nullptr;   // optional device buffer for per-phase clock stamps
     std::vector<void *> weight_allocs;
@@ -130,7 +140,7 @@ extern "C" uocr_cuda_context *uocr_cuda_context_create(const char *resource_path
         (e = cudaMallocHost(&ctx->h_status, 256)) != cudaSuccess ||
         (e = cudaMalloc(&ctx->d_layers, kMaxLayers * sizeof(DLayer))) != cudaSuccess ||
         (e = uocr::init_router_kernels()) != cudaSuccess || (e = uocr::init_small_batch_kernels()) != cudaSuccess ||
-        (e = uocr::init_decode_kernels()) != cudaSuccess) {
+        (e = uocr::init_decode_kernels()) != cudaSuccess || (e = uocr::init_gemm_kernels()) != cudaSuccess) {
         fail(nullptr, error, error_size, "CUDA context set-up failed: %s", cudaGetErrorString(e));
         uocr_cuda_context_destroy(ctx);
         return nullptr;
@@ -138,6 +148,7 @@ extern "C" uocr_cuda_context *uocr_cuda_context_create(const char *resource_path
     ctx->stream = ctx->own_stream;
     const char *off = getenv("UOCR_CUDA_DISABLE_FUSED_DECODE");
     ctx->fused_decode = !(off && off[0] == '1');
+    if (const char *mt = getenv("UOCR_CUDA_GEMM_MIN_TOKENS")) ctx->gemm_min_tokens = (uint32_t)strtoul(mt, nullptr, 10);
     return ctx;
 }
 
@@ -205,6 +216,7 @@ extern "C" int uocr_cuda_context_synchronize(uocr_cuda_context *ctx, char *error
                     (st & 1u) ? "router met a non-finite logit or an empty softmax (the CPU path rejects this input too)"
                     : (st & 2u) ? "a grid barrier of the decode kernel timed out"
                     : (st & 4u) ? "a bulk copy of the decode kernel timed out"
+                    : (st & 8u) ? "a pipeline wait of the grouped GEMM kernel timed out"
                                 : "kernel reported an internal error");
     }
     return 1;
@@ -346,7 +358,8 @@ extern "C" int uocr_cuda_context_map_moe_layer(uocr_cuda_context *ctx, const uoc
 // ----------------------------------------------------------------------------------- arena
 struct ArenaLayout {
     uint64_t logits, probs, ids, weights, offsets, pair_rows, inverse, active, mid, shared_mid, down_out, shared_out,
-        stack0, stack1, d_in, d_res, d_out, dec_mid, dec_plogits, total;
+        stack0, stack1, d_in, d_res, d_out, dec_mid, dec_plogits, x_sorted, tiles_gu, tiles_dn, stiles_gu, stiles_dn,
+        counts, total;
 };
 
 // down products are f32 while the call is small enough to take the matrix-vector path, fp16 beyond
@@ -376,6 +389,15 @@ static ArenaLayout layout_arena(uint32_t H, uint32_t E, uint32_t K, uint32_t F, 
     a.d_out = take((uint64_t)n * H * 2);
     a.dec_mid = take(((uint64_t)K * F + S) * 2);            // single-token decode kernel: SwiGLU products
     a.dec_plogits = take((uint64_t)1024 * E * 4);           // and per-CTA partial router logits
+    {   // tensor-core path: sorted activations and tile lists (128 tokens x 128 weight rows per tile)
+        const uint64_t ttiles = (pairs + 127) / 128 + E, sttiles = ((uint64_t)n + 127) / 128;
+        a.x_sorted = take(pairs * H * 2);
+        a.tiles_gu = take(ttiles * (F / 128 + 1) * 16);
+        a.tiles_dn = take(ttiles * (H / 128 + 1) * 16);
+        a.stiles_gu = take(sttiles * (S / 128 + 1) * 16);
+        a.stiles_dn = take(sttiles * (H / 128 + 1) * 16);
+        a.counts = take(64);
+    }
     a.total = off;
     return a;
 }
@@ -496,11 +518,24 @@ static int layer_forward(uocr_cuda_context *ctx, uint32_t layer, const __half *d
                                               ctx->status, logits, probs, s.top_ids, s.top_weights, nullptr, ctx->stream,
                                               &ctx->launches));
     } else {
-    CU_TRY(ctx, uocr::launch_router(L, d_hidden, d_injected, n, logits, probs, s.top_ids, s.top_weights, ctx->status,
-                                    ctx->stream, &ctx->launches));
-    CU_TRY(ctx, uocr::launch_dispatch_plan(s.top_ids, n, L.K, L.E, s.expert_offsets, s.pair_rows, s.inverse, s.active,
-                                           ctx->stream, &ctx->launches));
-    CU_TRY(ctx, uocr::launch_small_batch_layer(L, s, d_hidden, d_residual, n, d_out, ctx->stream, &ctx->launches));
+        CU_TRY(ctx, uocr::launch_router(L, d_hidden, d_injected, n, logits, probs, s.top_ids, s.top_weights, ctx->status,
+                                        ctx->stream, &ctx->launches));
+        CU_TRY(ctx, uocr::launch_dispatch_plan(s.top_ids, n, L.K, L.E, s.expert_offsets, s.pair_rows, s.inverse,
+                                               s.active, ctx->stream, &ctx->launches));
+        if (n >= ctx->gemm_min_tokens && uocr::gemm_path_supported(L)) {
+            uocr::GemmScratch g{};
+            g.x_sorted = (__half *)(ctx->arena + a.x_sorted);
+            g.mid_sorted = s.mid;
+            g.down_sorted = (__half *)s.down_out;
+            g.shared_mid = s.shared_mid;
+            g.shared_out = (__half *)s.shared_out;
+            g.tiles_gu = (uint4 *)(ctx->arena + a.tiles_gu); g.tiles_dn = (uint4 *)(ctx->arena + a.tiles_dn);
+            g.stiles_gu = (uint4 *)(ctx->arena + a.stiles_gu); g.stiles_dn = (uint4 *)(ctx->arena + a.stiles_dn);
+            g.counts = (uint32_t *)(ctx->arena + a.counts);
+            CU_TRY(ctx, uocr::launch_gemm_layer(L, s, g, d_hidden, d_residual, n, d_out, ctx->stream, &ctx->launches));
+        } else {
+            CU_TRY(ctx, uocr::launch_small_batch_layer(L, s, d_hidden, d_residual, n, d_out, ctx->stream, &ctx->launches));
+        }
     }
     if (dbg && dbg->d_top_ids)
         CU_TRY(ctx, cudaMemcpyAsync(dbg->d_top_ids, s.top_ids, (size_t)n * L.K * 4, cudaMemcpyDeviceToDevice, ctx->stream));
