@@ -163,6 +163,23 @@ UOCR_CUDA_API int uocr_cuda_moe_dispatch_plan(uocr_cuda_context *ctx, const uint
                                               uint32_t *d_pair_rows, uint32_t *d_inverse, char *error,
                                               size_t error_size);
 
+/* The same dispatch plan for callers that must not allocate device memory.  It has no counterpart in the
+ * reference, whose backends own all their buffers.  It needs no context and no arena: the kernel's only scratch
+ * (the list of experts that received a pair) lives in a fixed 1280-byte device array inside this library, which
+ * every process that loads the library holds on each device it uses until it exits.  It exists for hosts that
+ * cannot call cudaMalloc where they need a plan: inside a stream capture, in a decode loop that has frozen its
+ * memory map, or after the engine's memory admission has handed out the whole device budget.
+ * Limits: n_experts <= 256 and n_tokens * top_k <= 1048576; larger sizes are refused with a message.
+ * The first call on a device looks up the array's device address and raises the kernel's shared-memory limit
+ * (no allocation); make that first call before any stream capture.  All calls share the one array, so two calls
+ * whose kernels may overlap on the GPU (different streams without an ordering between them) race on it; calls
+ * on one stream are safe.  Nothing in the array needs clearing: every call rewrites the entries it later reads.
+ * cuda_stream is a cudaStream_t (NULL = the default stream); the current device is used. */
+UOCR_CUDA_API int uocr_cuda_moe_dispatch_plan_noalloc(const uint32_t *d_top_ids, uint32_t n_tokens, uint32_t top_k,
+                                                      uint32_t n_experts, uint32_t *d_expert_offsets,
+                                                      uint32_t *d_pair_rows, uint32_t *d_inverse, void *cuda_stream,
+                                                      char *error, size_t error_size);
+
 /* The layer: out[n][H] = fp16( sum_slot weight * expert(hidden) + shared(hidden) [+ residual] ), the
  * computation of uocr_cpu_ref_moe_swiglu_f32 (src/backend/cpu_ref/uocr_cpu_ref.c:468-579) with the GPU
  * path's data types: fp16 activations, weights dequantised on the fly and never materialised, f32

@@ -182,3 +182,72 @@ cudaError_t launch_dispatch_plan(const uint32_t *ids, uint32_t n, uint32_t K, ui
 }
 
 }  // namespace uocr
+
+namespace uocr {
+// --------------------------------------------------------------------------------------------
+// Dispatch plan for callers that must not allocate device memory.
+//
+// The plan kernel keeps a by-product - the list of experts that received at least one pair - in
+// global memory beside its three outputs.  The regular entry point parks that list in the
+// context's arena, which exists only after cudaMalloc calls.  Some hosts of this library cannot
+// make such calls at the point where they need a plan: code running inside a CUDA-graph stream
+// capture, a real-time decode loop that has frozen its memory map, or an engine whose memory
+// admission control has already handed out the whole device budget (the reference engine refuses
+// work past its budget, src/core/uocr_api.c:1166-1197).  For them the list lives in the fixed
+// array below, which every process that loads this library holds on each device it touches
+// (1280 bytes) until it exits.
+//
+// The array's name is only a host-side handle; the device address comes from
+// cudaGetSymbolAddress, looked up once per device with that device current.
+constexpr uint32_t kNoAllocMaxExperts = 256;
+constexpr uint32_t kNoAllocMaxPairs = 1u << 20;
+static __device__ __align__(256) uint32_t g_plan_scratch[320];   // [0] = count, then up to 256 expert ids
+
+struct NoAllocDeviceState {
+    uint32_t *scratch = nullptr;
+    bool ready = false;
+};
+static NoAllocDeviceState g_noalloc[64];
+
+}  // namespace uocr
+
+#include "../../include/uocr_cuda_moe.h"
+
+#include <cstdio>
+
+extern "C" int uocr_cuda_moe_dispatch_plan_noalloc(const uint32_t *d_top_ids, uint32_t n_tokens, uint32_t top_k,
+                                                   uint32_t n_experts, uint32_t *d_expert_offsets,
+                                                   uint32_t *d_pair_rows, uint32_t *d_inverse, void *cuda_stream,
+                                                   char *error, size_t error_size) {
+    auto fail = [&](const char *msg, const char *detail) {
+        if (error && error_size) snprintf(error, error_size, "%s%s%s", msg, detail ? ": " : "", detail ? detail : "");
+        return 0;
+    };
+    if (!d_top_ids || !d_expert_offsets || !d_pair_rows || !d_inverse) return fail("null dispatch-plan argument", nullptr);
+    if (n_tokens == 0 || top_k == 0 || n_experts == 0 || top_k > n_experts) return fail("invalid dispatch-plan dimensions", nullptr);
+    if (n_experts > uocr::kNoAllocMaxExperts)
+        return fail("n_experts exceeds the 256 experts the allocation-free dispatch plan has scratch for", nullptr);
+    if ((uint64_t)n_tokens * top_k > uocr::kNoAllocMaxPairs)
+        return fail("n_tokens * top_k exceeds the 1048576 pairs the allocation-free dispatch plan accepts", nullptr);
+    int dev = 0;
+    cudaError_t err = cudaGetDevice(&dev);
+    if (err != cudaSuccess) return fail("cudaGetDevice failed", cudaGetErrorString(err));
+    if (dev < 0 || dev >= 64) return fail("device index out of range", nullptr);
+    uocr::NoAllocDeviceState &state = uocr::g_noalloc[dev];
+    if (!state.ready) {
+        // first call on this device: resolve the scratch array's device address and raise the kernel's
+        // dynamic shared-memory limit.  Neither allocates; both must happen outside a stream capture.
+        void *ptr = nullptr;
+        err = cudaGetSymbolAddress(&ptr, uocr::g_plan_scratch);
+        if (err != cudaSuccess) return fail("cudaGetSymbolAddress(plan scratch) failed", cudaGetErrorString(err));
+        err = cudaFuncSetAttribute(uocr::plan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
+        if (err != cudaSuccess) return fail("cudaFuncSetAttribute(plan kernel) failed", cudaGetErrorString(err));
+        state.scratch = static_cast<uint32_t *>(ptr);
+        state.ready = true;
+    }
+    uint64_t launches = 0;
+    err = uocr::launch_dispatch_plan(d_top_ids, n_tokens, top_k, n_experts, d_expert_offsets, d_pair_rows, d_inverse,
+                                     state.scratch, (cudaStream_t)cuda_stream, &launches);
+    if (err != cudaSuccess) return fail("dispatch-plan launch failed", cudaGetErrorString(err));
+    return 1;
+}

@@ -50,7 +50,7 @@ EXPORTS = (
     "uocr_cuda_context_moe_scratch_bytes", "uocr_cuda_context_map_moe_layer", "uocr_cuda_context_unmap_model",
     "uocr_cuda_context_moe_layer_count", "uocr_cuda_context_allocate_runtime_arenas",
     "uocr_cuda_context_release_runtime_arenas", "uocr_cuda_moe_scratch_size", "uocr_cuda_moe_router",
-    "uocr_cuda_moe_dispatch_plan", "uocr_cuda_moe_layer_forward", "uocr_cuda_moe_stack_forward",
+    "uocr_cuda_moe_dispatch_plan", "uocr_cuda_moe_dispatch_plan_noalloc", "uocr_cuda_moe_layer_forward", "uocr_cuda_moe_stack_forward",
     "uocr_cuda_moe_layer_forward_host", "uocr_cuda_moe_stack_forward_host",
 )
 
@@ -96,6 +96,7 @@ def load_library() -> C.CDLL:
         "uocr_cuda_moe_scratch_size": (u64, [u32] * 6),
         "uocr_cuda_moe_router": (C.c_int, [vp, u32, vp, vp, u32, vp, vp, vp, vp] + err),
         "uocr_cuda_moe_dispatch_plan": (C.c_int, [vp, vp, u32, u32, u32, vp, vp, vp] + err),
+        "uocr_cuda_moe_dispatch_plan_noalloc": (C.c_int, [vp, u32, u32, u32, vp, vp, vp, vp] + err),
         "uocr_cuda_moe_layer_forward": (C.c_int, [vp, u32, vp, vp, vp, u32, vp, C.POINTER(CDebugOutputs)] + err),
         "uocr_cuda_moe_stack_forward": (C.c_int, [vp, u32, u32, vp, u32, vp] + err),
         "uocr_cuda_moe_layer_forward_host": (C.c_int, [vp, u32, vp, vp, u32, vp, vp, vp] + err),
@@ -139,6 +140,20 @@ def make_layer_desc(L: Any) -> tuple[CLayerDesc, list]:
     d = CLayerDesc(L.H, L.E, L.K, L.F, L.S, L.scaling, _np_ptr(L.router), _np_ptr(L.logit_bias), L.expert_qtype,
                    _np_ptr(L.expert_qweight), _np_ptr(L.expert_qscale), 0, 0, 0, 0, 0, 0, *mats)
     return d, keep
+
+
+def dispatch_plan_noalloc(top_ids, n_tokens: int, top_k: int, n_experts: int, expert_offsets, pair_rows, inverse,
+                          cuda_stream: int | None = None) -> None:
+    """Dispatch plan without a context, an arena or any device allocation (see the header for who needs this).
+    Arguments are device buffers (torch CUDA tensors or addresses) on the current device."""
+    lib = load_library()
+    err = C.create_string_buffer(_ERR)
+    if cuda_stream == 0:
+        cuda_stream = 1   # cudaStreamLegacy
+    ok = lib.uocr_cuda_moe_dispatch_plan_noalloc(_dev_ptr(top_ids), n_tokens, top_k, n_experts, _dev_ptr(expert_offsets),
+                                                 _dev_ptr(pair_rows), _dev_ptr(inverse), cuda_stream, err, _ERR)
+    if ok != 1:
+        raise UocrCudaError(err.value.decode())
 
 
 class Context:
