@@ -167,7 +167,8 @@ UOCR_CUDA_API int uocr_cuda_moe_dispatch_plan(uocr_cuda_context *ctx, const uint
  * reference, whose backends own all their buffers.  It needs no context and no arena: the kernel's only scratch
  * (the list of experts that received a pair) lives in a fixed 1280-byte device array inside this library, which
  * every process that loads the library holds on each device it uses until it exits.  It exists for hosts that
- * cannot call cudaMalloc where they need a plan: inside a stream capture, in a decode loop that has frozen its
+ * cannot call cudaMalloc where they need a plan: on a hot path guarded against allocation (the reference asserts
+ * this with uocr_alloc_guard, src/core/uocr_alloc.h:21-42), in a decode loop that has frozen its
  * memory map, or after the engine's memory admission has handed out the whole device budget.
  * Limits: n_experts <= 256 and n_tokens * top_k <= 1048576; larger sizes are refused with a message.
  * The first call on a device looks up the array's device address and raises the kernel's shared-memory limit

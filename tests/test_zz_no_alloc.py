@@ -1,7 +1,7 @@
 """The allocation-free dispatch plan (uocr_cuda_moe_dispatch_plan_noalloc).
 
 Some hosts of the library cannot call cudaMalloc at the point where they need the token-to-expert
-permutation: they are inside a stream capture, run a decode loop with a frozen memory map, or their
+permutation: they sit on a hot path guarded against allocation, run a decode loop with a frozen memory map, or their
 engine has already given away the whole device budget.  This entry point needs no context and no arena;
 its scratch is a fixed array inside the library.  The test calls it through the C ABI twice in a row on
 different inputs and compares every output with the regular entry point's (integer data: exact match),

@@ -190,8 +190,8 @@ namespace uocr {
 // The plan kernel keeps a by-product - the list of experts that received at least one pair - in
 // global memory beside its three outputs.  The regular entry point parks that list in the
 // context's arena, which exists only after cudaMalloc calls.  Some hosts of this library cannot
-// make such calls at the point where they need a plan: code running inside a CUDA-graph stream
-// capture, a real-time decode loop that has frozen its memory map, or an engine whose memory
+// make such calls at the point where they need a plan: code on a hot path that is guarded against
+// allocation (the reference asserts this with uocr_alloc_guard, src/core/uocr_alloc.h:21-42), a real-time decode loop that has frozen its memory map, or an engine whose memory
 // admission control has already handed out the whole device budget (the reference engine refuses
 // work past its budget, src/core/uocr_api.c:1166-1197).  For them the list lives in the fixed
 // array below, which every process that loads this library holds on each device it touches
