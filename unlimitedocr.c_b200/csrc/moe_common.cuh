@@ -46,6 +46,7 @@ struct Scratch {
     uint32_t *pair_rows;      // [n*K]
     uint32_t *inverse;        // [n*K]
     uint32_t *active;         // [E+1]: active[0] = count, then expert ids with >= 1 pair, ascending
+    uint32_t *plan_counts;    // [ceil(n*K/2048)][E] per-chunk counts of the many-CTA dispatch plan
     __half *mid;              // routed SwiGLU products [n*K][F], indexed by pair
     __half *shared_mid;       // [n][S]
     void *down_out;           // routed down products [n*K][H], f32 (small n) or fp16
@@ -162,11 +163,11 @@ __device__ __forceinline__ float silu_f32(float v) { return v / (1.0f + __expf(-
 struct LaunchCounter { uint64_t *count; };
 
 cudaError_t launch_router(const DLayer &L, const __half *hidden, const float *injected, uint32_t n, float *logits,
-                          float *probs, uint32_t *ids, float *weights, uint32_t *status, cudaStream_t st,
-                          uint64_t *launches);
+                          float *probs, uint32_t *ids, float *weights, uint32_t *status, float *logits_scratch,
+                          cudaStream_t st, uint64_t *launches);
 cudaError_t launch_dispatch_plan(const uint32_t *ids, uint32_t n, uint32_t K, uint32_t E, uint32_t *offsets,
-                                 uint32_t *pair_rows, uint32_t *inverse, uint32_t *active, cudaStream_t st,
-                                 uint64_t *launches);
+                                 uint32_t *pair_rows, uint32_t *inverse, uint32_t *active, uint32_t *chunk_counts,
+                                 cudaStream_t st, uint64_t *launches);
 cudaError_t launch_small_batch_layer(const DLayer &L, const Scratch &S, const __half *hidden, const __half *residual,
                                      uint32_t n, __half *out, cudaStream_t st, uint64_t *launches);
 

@@ -11,12 +11,12 @@
 // One CTA computes one tile; two CTAs share an SM (<= 256 TMEM columns and ~100 KB shared memory
 // each), so one tile's epilogue overlaps the other's main loop.  Per 64-wide K block (= one scale
 // group of the weight formats, = one 128-byte swizzle row of fp16):
-//   warps 0-3  each thread owns one weight row of the tile: loads its packed bytes (32 B for Q4_0) with
-//              128-bit loads, turns them into fp16( level * scale ) in registers and writes the row
-//              into the stage's 128B-swizzled K-major tile; no dequantised copy of a weight ever
-//              reaches global memory.  The same warps run the epilogue.
-//   warp 4     one thread issues the TMA tile load (cp.async.bulk.tensor) of the activation tile.
-//   warp 5     one thread issues tcgen05.mma (kind::f16, fp32 accumulators in TMEM) and commits the
+//   warps 0-7  two threads per weight row of the tile: each loads its half of the row's packed bytes
+//              (16 B for Q4_0) with 128-bit loads, turns them into fp16( level * scale ) in registers
+//              and writes them into the stage's 128B-swizzled K-major tile; no dequantised copy of a
+//              weight ever reaches global memory.  The same warps run the epilogue.
+//   warp 8     one thread issues the TMA tile load (cp.async.bulk.tensor) of the activation tile.
+//   warp 9     one thread issues tcgen05.mma (kind::f16, fp32 accumulators in TMEM) and commits the
 //              stage back to the producers; the warp also owns the TMEM allocation.
 // Every wait is bounded; on a time-out the CTA raises a status bit, drains and returns.
 #include <cuda.h>
@@ -26,7 +26,8 @@
 
 namespace uocr {
 
-constexpr int kGemmThreads = 192;
+constexpr int kGemmThreads = 320;        // warps 0-7 producers + epilogue, warp 8 TMA, warp 9 MMA
+constexpr int kProducerThreads = 256;
 constexpr int kTileM = 128;          // weight rows per tile = TMEM lanes
 constexpr int kTileN = 128;          // tokens per tile (TMEM columns per accumulator)
 constexpr int kBlockK = 64;          // fp16 elements per K block = 128 bytes = one swizzle row
@@ -144,56 +145,56 @@ __device__ __forceinline__ void bytes_to_h2(uint32_t bytes, __half2 bias, __half
     hi = h2_as_u32(__hmul2(__hsub2(*reinterpret_cast<const __half2 *>(&b), bias), scale));
 }
 
-template <int QT> struct PackedBlock;   // packed bytes of one row of one K block, as uint4s
-template <> struct PackedBlock<UOCR_QT_Q4> { static constexpr int kVecs = 2; };
-template <> struct PackedBlock<UOCR_QT_Q8> { static constexpr int kVecs = 4; };
-template <> struct PackedBlock<UOCR_QT_F16> { static constexpr int kVecs = 8; };
+template <int QT> struct PackedBlock;   // packed bytes of HALF a row of one K block, as uint4s
+template <> struct PackedBlock<UOCR_QT_Q4> { static constexpr int kVecs = 1; };
+template <> struct PackedBlock<UOCR_QT_Q8> { static constexpr int kVecs = 2; };
+template <> struct PackedBlock<UOCR_QT_F16> { static constexpr int kVecs = 4; };
 
+// half = 0 / 1: which half of the row's K block this thread converts
 template <int QT>
-__device__ __forceinline__ void load_block(const uint8_t *row, uint32_t kb, uint4 (&v)[PackedBlock<QT>::kVecs]) {
-    const uint4 *p = reinterpret_cast<const uint4 *>(row) + (size_t)kb * PackedBlock<QT>::kVecs;
+__device__ __forceinline__ void load_block(const uint8_t *row, uint32_t kb, int half, uint4 (&v)[PackedBlock<QT>::kVecs]) {
+    const uint4 *p = reinterpret_cast<const uint4 *>(row) + ((size_t)kb * 2 + half) * PackedBlock<QT>::kVecs;
 #pragma unroll
     for (int i = 0; i < PackedBlock<QT>::kVecs; ++i) v[i] = __ldg(p + i);
 }
 
 template <int QT>
-__device__ __forceinline__ void dequant_row(const uint4 (&v)[PackedBlock<QT>::kVecs], __half scale, uint8_t *tile, int r) {
+__device__ __forceinline__ void dequant_row(const uint4 (&v)[PackedBlock<QT>::kVecs], __half scale, uint8_t *tile, int r,
+                                            int half) {
     if (QT == UOCR_QT_F16) {
 #pragma unroll
-        for (int c = 0; c < 8; ++c) store_chunk(tile, r, c, v[c]);
+        for (int c = 0; c < 4; ++c) store_chunk(tile, r, 4 * half + c, v[c]);
     } else if (QT == UOCR_QT_Q8) {
         const __half2 s2 = __half2half2(scale), bias = __float2half2_rn(1152.f);   // 1024 + 128
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {          // 16 bytes = 16 weights = chunks 2i, 2i+1
+        for (int i = 0; i < 2; ++i) {          // 16 bytes = 16 weights = two chunks
             const uint32_t w[4] = {v[i].x ^ 0x80808080u, v[i].y ^ 0x80808080u, v[i].z ^ 0x80808080u, v[i].w ^ 0x80808080u};
             uint4 c0, c1;
             bytes_to_h2(w[0], bias, s2, c0.x, c0.y);
             bytes_to_h2(w[1], bias, s2, c0.z, c0.w);
             bytes_to_h2(w[2], bias, s2, c1.x, c1.y);
             bytes_to_h2(w[3], bias, s2, c1.z, c1.w);
-            store_chunk(tile, r, 2 * i, c0);
-            store_chunk(tile, r, 2 * i + 1, c1);
+            store_chunk(tile, r, 4 * half + 2 * i, c0);
+            store_chunk(tile, r, 4 * half + 2 * i + 1, c1);
         }
     } else {
-        // Q4_0 half-split: byte j of the 32 holds column j (low nibble) and column j + 32 (high nibble)
+        // Q4_0 half-split: byte j of the 32 holds column j (low nibble) and column j + 32 (high nibble);
+        // this thread has bytes 16*half .. 16*half+15: low -> chunks 2h, 2h+1; high -> chunks 4+2h, 5+2h
         const __half2 s2 = __half2half2(scale), bias = __float2half2_rn(1032.f);    // 1024 + 8
-#pragma unroll
-        for (int i = 0; i < 2; ++i) {          // bytes 16i .. 16i+15: low -> chunks 2i, 2i+1; high -> chunks 4+2i, 5+2i
-            const uint32_t w[4] = {v[i].x, v[i].y, v[i].z, v[i].w};
-            uint4 l0, l1, h0, h1;
-            bytes_to_h2(w[0] & 0x0F0F0F0Fu, bias, s2, l0.x, l0.y);
-            bytes_to_h2(w[1] & 0x0F0F0F0Fu, bias, s2, l0.z, l0.w);
-            bytes_to_h2(w[2] & 0x0F0F0F0Fu, bias, s2, l1.x, l1.y);
-            bytes_to_h2(w[3] & 0x0F0F0F0Fu, bias, s2, l1.z, l1.w);
-            bytes_to_h2((w[0] >> 4) & 0x0F0F0F0Fu, bias, s2, h0.x, h0.y);
-            bytes_to_h2((w[1] >> 4) & 0x0F0F0F0Fu, bias, s2, h0.z, h0.w);
-            bytes_to_h2((w[2] >> 4) & 0x0F0F0F0Fu, bias, s2, h1.x, h1.y);
-            bytes_to_h2((w[3] >> 4) & 0x0F0F0F0Fu, bias, s2, h1.z, h1.w);
-            store_chunk(tile, r, 2 * i, l0);
-            store_chunk(tile, r, 2 * i + 1, l1);
-            store_chunk(tile, r, 4 + 2 * i, h0);
-            store_chunk(tile, r, 5 + 2 * i, h1);
-        }
+        const uint32_t w[4] = {v[0].x, v[0].y, v[0].z, v[0].w};
+        uint4 l0, l1, h0, h1;
+        bytes_to_h2(w[0] & 0x0F0F0F0Fu, bias, s2, l0.x, l0.y);
+        bytes_to_h2(w[1] & 0x0F0F0F0Fu, bias, s2, l0.z, l0.w);
+        bytes_to_h2(w[2] & 0x0F0F0F0Fu, bias, s2, l1.x, l1.y);
+        bytes_to_h2(w[3] & 0x0F0F0F0Fu, bias, s2, l1.z, l1.w);
+        bytes_to_h2((w[0] >> 4) & 0x0F0F0F0Fu, bias, s2, h0.x, h0.y);
+        bytes_to_h2((w[1] >> 4) & 0x0F0F0F0Fu, bias, s2, h0.z, h0.w);
+        bytes_to_h2((w[2] >> 4) & 0x0F0F0F0Fu, bias, s2, h1.x, h1.y);
+        bytes_to_h2((w[3] >> 4) & 0x0F0F0F0Fu, bias, s2, h1.z, h1.w);
+        store_chunk(tile, r, 2 * half, l0);
+        store_chunk(tile, r, 2 * half + 1, l1);
+        store_chunk(tile, r, 4 + 2 * half, h0);
+        store_chunk(tile, r, 5 + 2 * half, h1);
     }
 }
 
@@ -226,12 +227,12 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap act_map, GemmParams p) {
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     if (tid == 0) {
-        for (int s = 0; s < kStages; ++s) { gb_init(&full_a[s], 128); gb_init(&full_b[s], 1); gb_init(&empty[s], 1); }
+        for (int s = 0; s < kStages; ++s) { gb_init(&full_a[s], kProducerThreads); gb_init(&full_b[s], 1); gb_init(&empty[s], 1); }
         gb_init(acc_full, 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 5) {
+    if (warp == 9) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(s2u(tmem_slot)), "r"((uint32_t)Sh::kTmemCols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -240,17 +241,17 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap act_map, GemmParams p) {
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
-    if (warp < 4) {
+    if (warp < 8) {
         // ------------------------------------------------ weight rows -> fp16 swizzled tiles
-        const int r = tid;                                            // row of the tile
+        const int r = tid & 127, half = tid >> 7;                     // row of the tile, half of its K block
         const size_t grow = (size_t)mtile * kTileM + r;               // row of the matrix
         const uint8_t *row0p = p.w0 + (size_t)expert * p.expert_stride_bytes + grow * p.row_bytes;
         const uint8_t *row1p = GATEUP ? p.w1 + (size_t)expert * p.expert_stride_bytes + grow * p.row_bytes : nullptr;
         const __half *sc0 = QT == UOCR_QT_F16 ? nullptr : p.s0 + (size_t)expert * p.expert_scale_stride + grow * kblocks;
         const __half *sc1 = (QT == UOCR_QT_F16 || !GATEUP) ? nullptr : p.s1 + (size_t)expert * p.expert_scale_stride + grow * kblocks;
         uint4 v0[PackedBlock<QT>::kVecs], v1[PackedBlock<QT>::kVecs];
-        load_block<QT>(row0p, 0, v0);
-        if (GATEUP) load_block<QT>(row1p, 0, v1);
+        load_block<QT>(row0p, 0, half, v0);
+        if (GATEUP) load_block<QT>(row1p, 0, half, v1);
         for (uint32_t kb = 0; kb < kblocks; ++kb) {
             const int s = kb % kStages;
             const uint32_t use = kb / kStages;
@@ -258,11 +259,11 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap act_map, GemmParams p) {
             const __half sb = (QT == UOCR_QT_F16 || !GATEUP) ? __ushort_as_half(0) : sc1[kb];
             if (use > 0 && !gb_wait(&empty[s], (use - 1) & 1u, abort_flag, p.status)) break;
             uint8_t *st = stages + s * Sh::kStageBytes;
-            dequant_row<QT>(v0, sa, st, r);
-            if (GATEUP) dequant_row<QT>(v1, sb, st + kTileBytes, r);
+            dequant_row<QT>(v0, sa, st, r, half);
+            if (GATEUP) dequant_row<QT>(v1, sb, st + kTileBytes, r, half);
             if (kb + 1 < kblocks) {                                   // next block's bytes travel while this one is used
-                load_block<QT>(row0p, kb + 1, v0);
-                if (GATEUP) load_block<QT>(row1p, kb + 1, v1);
+                load_block<QT>(row0p, kb + 1, half, v0);
+                if (GATEUP) load_block<QT>(row1p, kb + 1, half, v1);
             }
             proxy_fence();                                            // generic-proxy stores -> visible to the MMA's async proxy
             gb_arrive(&full_a[s]);
@@ -270,9 +271,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap act_map, GemmParams p) {
         // ------------------------------------------------ epilogue: TMEM -> registers -> global
         if (gb_wait(acc_full, 0, abort_flag, p.status)) {
             tc_fence_after();
-            const uint32_t lane_base = tmem_base + ((uint32_t)(warp * 32) << 16);
+            // a warp reads the TMEM lanes 32*(warp % 4)..+31; warps w and w+4 split the 16-column chunks
+            const uint32_t lane_base = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
             const size_t out_col = (size_t)mtile * kTileM + r;
-            for (uint32_t c0 = 0; c0 < nrows; c0 += 16) {
+            for (uint32_t c0 = (uint32_t)half * 16; c0 < nrows; c0 += 32) {
                 uint32_t g[16], u[16];
                 tc_ld16(lane_base + c0, g);
                 if (GATEUP) tc_ld16(lane_base + kTileN + c0, u);
@@ -288,7 +290,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap act_map, GemmParams p) {
             }
         }
         tc_fence_before();
-    } else if (warp == 4) {
+    } else if (warp == 8) {
         // ------------------------------------------------ activation tiles by TMA
         if (lane == 0) {
             for (uint32_t kb = 0; kb < kblocks; ++kb) {
@@ -333,9 +335,108 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap act_map, GemmParams p) {
         while (clock64() - t0 < 2000000LL) {}
         __syncthreads();
     }
-    if (warp == 5) {
+    if (warp == 9) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)Sh::kTmemCols) : "memory");
+    }
+}
+
+// ------------------------------------------------------------------ router logits GEMM
+// logits[n][E] = hidden[n][H] . router[E][H]^T for many tokens: 128 tokens per CTA on the M side, all
+// experts (padded to a multiple of 16, <= 256) on the N side, both operands by TMA, fp32 accumulate in
+// TMEM.  The softmax / top-k kernel then runs on these logits exactly as it does on injected ones.
+constexpr int kRouterGemmThreads = 192;     // warps 0-3 epilogue, warp 4 TMA, warp 5 MMA
+constexpr int kRouterStages = 4;
+
+__host__ __device__ constexpr int router_gemm_stage_bytes(int n_pad) { return kTileBytes + n_pad * 128; }
+
+__global__ void __launch_bounds__(kRouterGemmThreads, 1)
+router_logits_kernel(const __grid_constant__ CUtensorMap hidden_map, const __grid_constant__ CUtensorMap router_map,
+                     uint32_t n, uint32_t E, uint32_t n_pad, uint32_t tmem_cols, uint32_t k_dim, float *__restrict__ logits,
+                     uint32_t *status) {
+    extern __shared__ uint8_t smem_dyn[];
+    uint8_t *stages = reinterpret_cast<uint8_t *>(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
+    const uint32_t b_bytes = (n_pad * 128 + 1023) & ~1023u;
+    const uint32_t stage_bytes = kTileBytes + b_bytes;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(stages + kRouterStages * stage_bytes);
+    uint64_t *full = bars, *empty = bars + kRouterStages, *acc_full = bars + 2 * kRouterStages;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * kRouterStages + 1);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint32_t row0 = blockIdx.x * kTileM;
+    const uint32_t kblocks = k_dim / kBlockK;
+
+    if (tid == 0) {
+        for (int s = 0; s < kRouterStages; ++s) { gb_init(&full[s], 1); gb_init(&empty[s], 1); }
+        gb_init(acc_full, 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 5) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(s2u(tmem_slot)), "r"(tmem_cols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp < 4) {
+        if (gb_wait(acc_full, 0, abort_flag, status)) {
+            tc_fence_after();
+            const uint32_t lane_base = tmem_base + ((uint32_t)(warp * 32) << 16);
+            const uint32_t row = row0 + tid;
+            for (uint32_t c0 = 0; c0 < n_pad; c0 += 16) {
+                uint32_t v[16];
+                tc_ld16(lane_base + c0, v);
+                tc_ld_wait();
+                if (row < n) {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j)
+                        if (c0 + j < E) logits[(size_t)row * E + c0 + j] = __uint_as_float(v[j]);
+                }
+            }
+        }
+        tc_fence_before();
+    } else if (warp == 4) {
+        if (lane == 0) {
+            for (uint32_t kb = 0; kb < kblocks; ++kb) {
+                const int s = kb % kRouterStages;
+                const uint32_t use = kb / kRouterStages;
+                if (use > 0 && !gb_wait(&empty[s], (use - 1) & 1u, abort_flag, status)) break;
+                gb_expect_tx(&full[s], kTileBytes + n_pad * 128);
+                tma_load_2d(stages + s * stage_bytes, &hidden_map, (int)(kb * kBlockK), (int)row0, &full[s]);
+                tma_load_2d(stages + s * stage_bytes + kTileBytes, &router_map, (int)(kb * kBlockK), 0, &full[s]);
+            }
+        }
+    } else {
+        if (lane == 0) {
+            const uint32_t idesc = umma_idesc(n_pad);
+            bool ok = true;
+            for (uint32_t kb = 0; kb < kblocks && ok; ++kb) {
+                const int s = kb % kRouterStages;
+                ok = gb_wait(&full[s], (kb / kRouterStages) & 1u, abort_flag, status);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t a_addr = s2u(stages + s * stage_bytes), b_addr = a_addr + kTileBytes;
+#pragma unroll
+                for (int k = 0; k < kBlockK / 16; ++k)
+                    tc_mma(tmem_base, umma_desc(a_addr + k * 32), umma_desc(b_addr + k * 32), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                tc_commit(&empty[s]);
+            }
+            if (ok) tc_commit(acc_full);
+        }
+        __syncwarp();
+    }
+    __syncthreads();
+    if (*abort_flag) {
+        const long long t0 = clock64();
+        while (clock64() - t0 < 2000000LL) {}
+        __syncthreads();
+    }
+    if (warp == 5) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(tmem_cols) : "memory");
     }
 }
 
@@ -460,7 +561,8 @@ cudaError_t init_gemm_kernels() {
         if (qres != cudaDriverEntryPointSuccess || fn == nullptr) return cudaErrorNotSupported;
         g_encode = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(fn);
     }
-    cudaError_t err = cudaSuccess;
+    cudaError_t err = cudaFuncSetAttribute(router_logits_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           (int)(kRouterStages * (kTileBytes + 32 * 1024) + 1024 + 256));
 #define UOCR_SET_SMEM(QT, GU)                                                                                    \
     if (err == cudaSuccess)                                                                                      \
         err = cudaFuncSetAttribute(grouped_gemm_kernel<QT, GU>, cudaFuncAttributeMaxDynamicSharedMemorySize,     \
@@ -482,6 +584,40 @@ static cudaError_t make_act_map(CUtensorMap *map, const void *base, uint64_t row
                                 CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
+}
+
+static cudaError_t make_map_rows(CUtensorMap *map, const void *base, uint64_t rows, uint64_t cols, uint32_t box_rows) {
+    const cuuint64_t dims[2] = {cols, rows};
+    const cuuint64_t strides[1] = {cols * 2};
+    const cuuint32_t box[2] = {kBlockK, box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void *>(base), dims, strides, box, estr,
+                                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
+}
+
+static size_t router_gemm_smem(uint32_t n_pad) {
+    const size_t b_bytes = ((size_t)n_pad * 128 + 1023) & ~(size_t)1023;
+    return kRouterStages * (kTileBytes + b_bytes) + 1024 + 256;
+}
+
+bool router_gemm_supported(const DLayer &L) { return g_encode != nullptr && L.H % 64 == 0 && L.E <= 256; }
+
+// logits[n][E] (no bias) for n tokens
+cudaError_t launch_router_logits(const DLayer &L, const __half *hidden, uint32_t n, float *logits, uint32_t *status,
+                                 cudaStream_t st, uint64_t *launches) {
+    const uint32_t n_pad = (L.E + 15u) & ~15u;
+    uint32_t cols = 32;
+    while (cols < n_pad) cols <<= 1;
+    CUtensorMap hm, rm;
+    cudaError_t err;
+    if ((err = make_map_rows(&hm, hidden, n, L.H, kTileM)) != cudaSuccess) return err;
+    if ((err = make_map_rows(&rm, L.router, L.E, L.H, n_pad)) != cudaSuccess) return err;
+    router_logits_kernel<<<(n + kTileM - 1) / kTileM, kRouterGemmThreads, router_gemm_smem(n_pad), st>>>(
+        hm, rm, n, L.E, n_pad, cols, L.H, logits, status);
+    ++*launches;
+    return cudaGetLastError();
 }
 
 bool gemm_path_supported(const DLayer &L) {

@@ -84,9 +84,20 @@ router_kernel(const __half *__restrict__ hidden, const __half *__restrict__ rout
     }
 }
 
+bool router_gemm_supported(const DLayer &L);
+cudaError_t launch_router_logits(const DLayer &L, const __half *hidden, uint32_t n, float *logits, uint32_t *status,
+                                 cudaStream_t st, uint64_t *launches);
+
+// logits_scratch: [n][E] floats the many-token path may use for the tensor-core logits (may be null: then the
+// CUDA-core kernel computes them).
 cudaError_t launch_router(const DLayer &L, const __half *hidden, const float *injected, uint32_t n, float *logits,
-                          float *probs, uint32_t *ids, float *weights, uint32_t *status, cudaStream_t st,
-                          uint64_t *launches) {
+                          float *probs, uint32_t *ids, float *weights, uint32_t *status, float *logits_scratch,
+                          cudaStream_t st, uint64_t *launches) {
+    if (injected == nullptr && n > 32 && logits_scratch != nullptr && router_gemm_supported(L)) {
+        cudaError_t err = launch_router_logits(L, hidden, n, logits_scratch, status, st, launches);
+        if (err != cudaSuccess) return err;
+        injected = logits_scratch;      // softmax / top-k on these logits; the bias is added there
+    }
     if (n <= 32) {
         const size_t smem = sizeof(float) * ((size_t)L.H + 2 * (size_t)L.E);
         router_kernel<1><<<n, kRouterThreads, smem, st>>>(hidden, L.router, L.bias, injected, n, L.H, L.E, L.K,
@@ -160,18 +171,135 @@ plan_kernel(const uint32_t *__restrict__ ids, uint32_t n_pairs, uint32_t E, uint
         }
 }
 
+// ---- the same plan with many CTAs, for large token counts -----------------------------------
+// Pairs are cut into chunks of kChunkPairs; chunk b is handled by CTA b.
+//   count   : per-chunk histogram -> chunk_counts[b][E]
+//   scan    : per expert, exclusive prefix over chunks (chunk_counts becomes each chunk's first position
+//             inside the expert's segment); expert offsets and the list of non-empty experts
+//   scatter : inside a chunk, thread t owns kPairsPerThread consecutive pairs; per-thread counts are scanned
+//             so that pairs keep their order -> the stable sort again
+constexpr int kPairsPerThread = 8;
+constexpr int kChunkPairs = kPlanThreads * kPairsPerThread;   // 2048
+
+__global__ void __launch_bounds__(kPlanThreads)
+plan_count_kernel(const uint32_t *__restrict__ ids, uint32_t n_pairs, uint32_t E, uint32_t *__restrict__ chunk_counts) {
+    __shared__ uint32_t hist[256];
+    const uint32_t tid = threadIdx.x, base = blockIdx.x * kChunkPairs;
+    hist[tid] = 0;
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < kPairsPerThread; ++i) {
+        const uint32_t p = base + i * kPlanThreads + tid;      // counting needs no order: coalesced reads
+        if (p < n_pairs) {
+            const uint32_t e = ids[p];
+            if (e < E) atomicAdd(&hist[e], 1u);
+        }
+    }
+    __syncthreads();
+    if (tid < E) chunk_counts[(size_t)blockIdx.x * E + tid] = hist[tid];
+}
+
+__global__ void __launch_bounds__(kPlanThreads)
+plan_scan_kernel(uint32_t *__restrict__ chunk_counts, uint32_t n_chunks, uint32_t E, uint32_t *__restrict__ offsets,
+                 uint32_t *__restrict__ active) {
+    __shared__ uint32_t tot[257];
+    const uint32_t e = threadIdx.x;
+    if (e < E) {
+        uint32_t run = 0;
+        for (uint32_t b = 0; b < n_chunks; ++b) {
+            const uint32_t c = chunk_counts[(size_t)b * E + e];
+            chunk_counts[(size_t)b * E + e] = run;
+            run += c;
+        }
+        tot[e] = run;
+    }
+    __syncthreads();
+    if (e == 0) {
+        uint32_t run = 0, na = 0;
+        for (uint32_t i = 0; i < E; ++i) {
+            const uint32_t c = tot[i];
+            offsets[i] = run;
+            tot[i] = run;
+            if (c) active[1 + na++] = i;
+            run += c;
+        }
+        offsets[E] = run;
+        active[0] = na;
+    }
+    __syncthreads();
+    if (e < E)
+        for (uint32_t b = 0; b < n_chunks; ++b) chunk_counts[(size_t)b * E + e] += tot[e];
+}
+
+__global__ void __launch_bounds__(kPlanThreads)
+plan_scatter_kernel(const uint32_t *__restrict__ ids, uint32_t n_pairs, uint32_t E, const uint32_t *__restrict__ chunk_first,
+                    uint32_t *__restrict__ pair_rows, uint32_t *__restrict__ inverse) {
+    extern __shared__ uint16_t cnt16[];          // [kPlanThreads][E] per-thread counts, then their exclusive prefixes
+    uint32_t *first = reinterpret_cast<uint32_t *>(cnt16 + (size_t)kPlanThreads * E);   // [E]
+    const uint32_t tid = threadIdx.x, lo = blockIdx.x * kChunkPairs + tid * kPairsPerThread;
+    for (uint32_t i = tid; i < kPlanThreads * E / 2; i += kPlanThreads) reinterpret_cast<uint32_t *>(cnt16)[i] = 0;
+    if (tid < E) first[tid] = chunk_first[(size_t)blockIdx.x * E + tid];
+    __syncthreads();
+    uint32_t my[kPairsPerThread];
+#pragma unroll
+    for (int i = 0; i < kPairsPerThread; ++i) {
+        my[i] = lo + i < n_pairs ? ids[lo + i] : 0xffffffffu;
+        if (my[i] < E) cnt16[tid * E + my[i]]++;
+    }
+    __syncthreads();
+    if (tid < E) {                               // exclusive scan over threads, one expert per thread
+        uint32_t run = 0;
+        for (uint32_t t = 0; t < kPlanThreads; ++t) {
+            const uint32_t c = cnt16[t * E + tid];
+            cnt16[t * E + tid] = (uint16_t)run;
+            run += c;
+        }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < kPairsPerThread; ++i) {
+        const uint32_t p = lo + i;
+        if (p >= n_pairs) break;
+        const uint32_t e = my[i];
+        if (e < E) {
+            uint32_t seen = 0;                   // earlier pairs of this thread with the same expert
+#pragma unroll
+            for (int j = 0; j < kPairsPerThread; ++j) seen += (j < i && my[j] == e);
+            const uint32_t pos = first[e] + cnt16[tid * E + e] + seen;
+            pair_rows[pos] = p;
+            inverse[p] = pos;
+        } else {
+            inverse[p] = 0xffffffffu;
+        }
+    }
+}
+
+static size_t plan_scatter_smem(uint32_t E) { return (size_t)kPlanThreads * E * 2 + 4 * E + 16; }
+
 // Per-device set-up of this file's kernels; called once when a context is created.
 cudaError_t init_router_kernels() {
     cudaError_t err = ensure_exp_table();
     if (err != cudaSuccess) return err;
     err = cudaFuncSetAttribute(router_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
     if (err != cudaSuccess) return err;
-    return cudaFuncSetAttribute(plan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
+    err = cudaFuncSetAttribute(plan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
+    if (err != cudaSuccess) return err;
+    return cudaFuncSetAttribute(plan_scatter_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 80 * 1024);
 }
 
+// chunk_counts: scratch of ceil(n*K / 2048) * E words for the many-CTA form (null: one CTA does everything)
 cudaError_t launch_dispatch_plan(const uint32_t *ids, uint32_t n, uint32_t K, uint32_t E, uint32_t *offsets,
-                                 uint32_t *pair_rows, uint32_t *inverse, uint32_t *active, cudaStream_t st,
-                                 uint64_t *launches) {
+                                 uint32_t *pair_rows, uint32_t *inverse, uint32_t *active, uint32_t *chunk_counts,
+                                 cudaStream_t st, uint64_t *launches) {
+    const uint32_t pairs = n * K;
+    if (chunk_counts != nullptr && pairs > 4 * kChunkPairs && E % 2 == 0 && E <= 128) {
+        const uint32_t chunks = (pairs + kChunkPairs - 1) / kChunkPairs;
+        plan_count_kernel<<<chunks, kPlanThreads, 0, st>>>(ids, pairs, E, chunk_counts);
+        plan_scan_kernel<<<1, kPlanThreads, 0, st>>>(chunk_counts, chunks, E, offsets, active);
+        plan_scatter_kernel<<<chunks, kPlanThreads, plan_scatter_smem(E), st>>>(ids, pairs, E, chunk_counts, pair_rows, inverse);
+        *launches += 3;
+        return cudaGetLastError();
+    }
     uint32_t T = 24576u / E;
     if (T > (uint32_t)kPlanThreads) T = kPlanThreads;
     if (T == 0) return cudaErrorInvalidValue;
@@ -247,7 +375,7 @@ extern "C" int uocr_cuda_moe_dispatch_plan_noalloc(const uint32_t *d_top_ids, ui
     }
     uint64_t launches = 0;
     err = uocr::launch_dispatch_plan(d_top_ids, n_tokens, top_k, n_experts, d_expert_offsets, d_pair_rows, d_inverse,
-                                     state.scratch, (cudaStream_t)cuda_stream, &launches);
+                                     state.scratch, nullptr, (cudaStream_t)cuda_stream, &launches);
     if (err != cudaSuccess) return fail("dispatch-plan launch failed", cudaGetErrorString(err));
     return 1;
 }

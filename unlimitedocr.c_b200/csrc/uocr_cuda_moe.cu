@@ -359,7 +359,7 @@ extern "C" int uocr_cuda_context_map_moe_layer(uocr_cuda_context *ctx, const uoc
 struct ArenaLayout {
     uint64_t logits, probs, ids, weights, offsets, pair_rows, inverse, active, mid, shared_mid, down_out, shared_out,
         stack0, stack1, d_in, d_res, d_out, dec_mid, dec_plogits, x_sorted, tiles_gu, tiles_dn, stiles_gu, stiles_dn,
-        counts, total;
+        counts, plan_counts, total;
 };
 
 // down products are f32 while the call is small enough to take the matrix-vector path, fp16 beyond
@@ -397,6 +397,7 @@ static ArenaLayout layout_arena(uint32_t H, uint32_t E, uint32_t K, uint32_t F, 
         a.stiles_gu = take(sttiles * (S / 128 + 1) * 16);
         a.stiles_dn = take(sttiles * (H / 128 + 1) * 16);
         a.counts = take(64);
+        a.plan_counts = take((pairs / 2048 + 2) * E * 4);
     }
     a.total = off;
     return a;
@@ -454,6 +455,7 @@ static Scratch carve(const uocr_cuda_context *ctx, const DLayer &L, uint32_t n, 
     s.top_ids = (uint32_t *)(b + a.ids); s.top_weights = (float *)(b + a.weights);
     s.expert_offsets = (uint32_t *)(b + a.offsets); s.pair_rows = (uint32_t *)(b + a.pair_rows);
     s.inverse = (uint32_t *)(b + a.inverse); s.active = (uint32_t *)(b + a.active);
+    s.plan_counts = (uint32_t *)(b + a.plan_counts);
     s.mid = (__half *)(b + a.mid); s.shared_mid = (__half *)(b + a.shared_mid);
     s.down_out = b + a.down_out; s.shared_out = (float *)(b + a.shared_out);
     s.status = ctx->status;
@@ -478,7 +480,7 @@ extern "C" int uocr_cuda_moe_router(uocr_cuda_context *ctx, uint32_t layer, cons
     if ((!d_hidden && !d_injected) || !d_ids || !d_weights) return fail(ctx, error, error_size, "null router argument");
     const DLayer &L = ctx->layers[layer];
     CU_TRY(ctx, uocr::launch_router(L, (const __half *)d_hidden, d_injected, n, d_logits, d_probs, d_ids, d_weights,
-                                    ctx->status, ctx->stream, &ctx->launches));
+                                    ctx->status, carve(ctx, L, n).logits, ctx->stream, &ctx->launches));
     return 1;
 }
 
@@ -492,9 +494,13 @@ extern "C" int uocr_cuda_moe_dispatch_plan(uocr_cuda_context *ctx, const uint32_
     // the list of non-empty experts is an internal by-product; park it in the arena's slot
     const LayerDims m = max_dims(ctx);
     if (E > m.E) return fail(ctx, error, error_size, "n_experts %u exceeds the mapped layers' %u", E, m.E);
-    const ArenaLayout a = layout_arena(m.H, m.E, m.K, m.F, m.S, 1);
+    // scratch of the plan kernels sits in the arena when the call fits the sizes the arena was laid out for
+    const bool fits = n <= ctx->token_capacity && K <= m.K;
+    const ArenaLayout a = layout_arena(m.H, m.E, m.K, m.F, m.S, fits ? n : 1);
     CU_TRY(ctx, uocr::launch_dispatch_plan(d_ids, n, K, E, d_offsets, d_pair_rows, d_inverse,
-                                           (uint32_t *)(ctx->arena + a.active), ctx->stream, &ctx->launches));
+                                           (uint32_t *)(ctx->arena + a.active),
+                                           fits ? (uint32_t *)(ctx->arena + a.plan_counts) : nullptr, ctx->stream,
+                                           &ctx->launches));
     return 1;
 }
 
@@ -519,9 +525,9 @@ static int layer_forward(uocr_cuda_context *ctx, uint32_t layer, const __half *d
                                               &ctx->launches));
     } else {
         CU_TRY(ctx, uocr::launch_router(L, d_hidden, d_injected, n, logits, probs, s.top_ids, s.top_weights, ctx->status,
-                                        ctx->stream, &ctx->launches));
+                                        s.logits, ctx->stream, &ctx->launches));
         CU_TRY(ctx, uocr::launch_dispatch_plan(s.top_ids, n, L.K, L.E, s.expert_offsets, s.pair_rows, s.inverse,
-                                               s.active, ctx->stream, &ctx->launches));
+                                               s.active, s.plan_counts, ctx->stream, &ctx->launches));
         if (n >= ctx->gemm_min_tokens && uocr::gemm_path_supported(L)) {
             uocr::GemmScratch g{};
             g.x_sorted = (__half *)(ctx->arena + a.x_sorted);
