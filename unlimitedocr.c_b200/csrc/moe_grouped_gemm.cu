@@ -22,14 +22,19 @@
 #include <cuda.h>
 #include <cudaTypedefs.h>
 
+#include <cstdio>
+#include <cstdlib>
+
 #include "moe_common.cuh"
 
 namespace uocr {
 
-constexpr int kGemmThreads = 320;        // warps 0-7 producers + epilogue, warp 8 TMA, warp 9 MMA
-constexpr int kProducerThreads = 256;
+constexpr int kGemmThreads = 576;        // warps 0-15 producers + epilogue, warp 16 TMA, warp 17 MMA
+constexpr int kProducerThreads = 512;
+constexpr int kTmaWarp = 16, kMmaWarp = 17;
 constexpr int kTileM = 128;          // weight rows per tile = TMEM lanes
-constexpr int kTileN = 128;          // tokens per tile (TMEM columns per accumulator)
+constexpr int kTileN = 256;          // tokens per tile of the down product (one accumulator)
+constexpr int kTileNGateUp = 128;    // tokens per tile of the gate/up product (two accumulators)
 constexpr int kBlockK = 64;          // fp16 elements per K block = 128 bytes = one swizzle row
 constexpr int kTileBytes = kTileM * kBlockK * 2;   // 16 KB: one operand tile of one stage
 constexpr long long kGemmSpinLimit = 4000000000LL;
@@ -47,6 +52,8 @@ struct GemmParams {
     __half *out;                   // mid / down_out, [rows][out_ld]
     uint32_t out_ld;
     uint32_t *status;
+    unsigned long long *trace;     // experiments only: clock stamps of one CTA
+    uint32_t debug;                // experiments only: bit 0 skip conversion + tensor-memory stores, bit 1 skip MMAs, bit 2 skip epilogue stores
 };
 
 // ---------------------------------------------------------------------------------- PTX
@@ -127,11 +134,13 @@ __device__ __forceinline__ uint32_t umma_idesc(uint32_t n) {
 }
 
 // ---------------------------------------------------------------------- dequantisation
-// One weight row of one K block -> 64 fp16 values = eight 16-byte chunks, written at their swizzled
-// positions: chunk c of row r lives at r*128 + ((c ^ (r & 7)) << 4).
-__device__ __forceinline__ void store_chunk(uint8_t *tile, int r, int c, uint4 v) {
-    *reinterpret_cast<uint4 *>(tile + r * 128 + ((c ^ (r & 7)) << 4)) = v;
-}
+// The weight operand never touches shared memory: each producer thread converts 16 packed weights of its
+// row to fp16( level * scale ) in registers and writes them straight into tensor memory (tcgen05.st), from
+// where the MMA reads its A operand.  Shared memory then carries only the activation tiles, which keeps its
+// bandwidth below what the tensor cores need.
+//
+// A in tensor memory for kind::f16, M = 128: element (row m, k) sits in lane m, 32-bit column k / 2, the even k
+// in the low half.  A 32-wide K sub-block of one matrix is 16 columns.
 
 __device__ __forceinline__ uint32_t h2_as_u32(__half2 h) { return *reinterpret_cast<uint32_t *>(&h); }
 
@@ -145,94 +154,118 @@ __device__ __forceinline__ void bytes_to_h2(uint32_t bytes, __half2 bias, __half
     hi = h2_as_u32(__hmul2(__hsub2(*reinterpret_cast<const __half2 *>(&b), bias), scale));
 }
 
-template <int QT> struct PackedBlock;   // packed bytes of HALF a row of one K block, as uint4s
-template <> struct PackedBlock<UOCR_QT_Q4> { static constexpr int kVecs = 1; };
-template <> struct PackedBlock<UOCR_QT_Q8> { static constexpr int kVecs = 2; };
-template <> struct PackedBlock<UOCR_QT_F16> { static constexpr int kVecs = 4; };
+// Packed bytes one thread holds per 64-wide K block: it owns K positions [16h, 16h+16) of both 32-wide
+// sub-blocks (h = 0 / 1).  kAhead: how many K blocks of packed bytes a thread keeps in flight from global memory.
+template <int QT> struct PackedBlock;
+template <> struct PackedBlock<UOCR_QT_Q4> { static constexpr int kVecs = 1; static constexpr int kAhead = 4; };
+template <> struct PackedBlock<UOCR_QT_Q8> { static constexpr int kVecs = 2; static constexpr int kAhead = 3; };
+template <> struct PackedBlock<UOCR_QT_F16> { static constexpr int kVecs = 4; static constexpr int kAhead = 2; };
 
-// half = 0 / 1: which half of the row's K block this thread converts
+// Q4_0: bytes 16h..16h+15 of the group's 32 (low nibbles: sub-block 0, high nibbles: sub-block 1).
+// Q8_0: bytes 32j + 16h .. +15 for sub-block j.   fp16: halves 32j + 16h .. +15 for sub-block j.
 template <int QT>
-__device__ __forceinline__ void load_block(const uint8_t *row, uint32_t kb, int half, uint4 (&v)[PackedBlock<QT>::kVecs]) {
-    const uint4 *p = reinterpret_cast<const uint4 *>(row) + ((size_t)kb * 2 + half) * PackedBlock<QT>::kVecs;
-#pragma unroll
-    for (int i = 0; i < PackedBlock<QT>::kVecs; ++i) v[i] = __ldg(p + i);
-}
-
-template <int QT>
-__device__ __forceinline__ void dequant_row(const uint4 (&v)[PackedBlock<QT>::kVecs], __half scale, uint8_t *tile, int r,
-                                            int half) {
-    if (QT == UOCR_QT_F16) {
-#pragma unroll
-        for (int c = 0; c < 4; ++c) store_chunk(tile, r, 4 * half + c, v[c]);
-    } else if (QT == UOCR_QT_Q8) {
-        const __half2 s2 = __half2half2(scale), bias = __float2half2_rn(1152.f);   // 1024 + 128
-#pragma unroll
-        for (int i = 0; i < 2; ++i) {          // 16 bytes = 16 weights = two chunks
-            const uint32_t w[4] = {v[i].x ^ 0x80808080u, v[i].y ^ 0x80808080u, v[i].z ^ 0x80808080u, v[i].w ^ 0x80808080u};
-            uint4 c0, c1;
-            bytes_to_h2(w[0], bias, s2, c0.x, c0.y);
-            bytes_to_h2(w[1], bias, s2, c0.z, c0.w);
-            bytes_to_h2(w[2], bias, s2, c1.x, c1.y);
-            bytes_to_h2(w[3], bias, s2, c1.z, c1.w);
-            store_chunk(tile, r, 4 * half + 2 * i, c0);
-            store_chunk(tile, r, 4 * half + 2 * i + 1, c1);
-        }
+__device__ __forceinline__ void load_block(const uint8_t *row, uint32_t kb, int h, uint4 (&v)[PackedBlock<QT>::kVecs]) {
+    const uint4 *p = reinterpret_cast<const uint4 *>(row);
+    if constexpr (QT == UOCR_QT_Q4) {
+        v[0] = __ldg(p + (size_t)kb * 2 + h);
+    } else if constexpr (QT == UOCR_QT_Q8) {
+        v[0] = __ldg(p + (size_t)kb * 4 + h);
+        v[1] = __ldg(p + (size_t)kb * 4 + 2 + h);
     } else {
-        // Q4_0 half-split: byte j of the 32 holds column j (low nibble) and column j + 32 (high nibble);
-        // this thread has bytes 16*half .. 16*half+15: low -> chunks 2h, 2h+1; high -> chunks 4+2h, 5+2h
-        const __half2 s2 = __half2half2(scale), bias = __float2half2_rn(1032.f);    // 1024 + 8
-        const uint32_t w[4] = {v[0].x, v[0].y, v[0].z, v[0].w};
-        uint4 l0, l1, h0, h1;
-        bytes_to_h2(w[0] & 0x0F0F0F0Fu, bias, s2, l0.x, l0.y);
-        bytes_to_h2(w[1] & 0x0F0F0F0Fu, bias, s2, l0.z, l0.w);
-        bytes_to_h2(w[2] & 0x0F0F0F0Fu, bias, s2, l1.x, l1.y);
-        bytes_to_h2(w[3] & 0x0F0F0F0Fu, bias, s2, l1.z, l1.w);
-        bytes_to_h2((w[0] >> 4) & 0x0F0F0F0Fu, bias, s2, h0.x, h0.y);
-        bytes_to_h2((w[1] >> 4) & 0x0F0F0F0Fu, bias, s2, h0.z, h0.w);
-        bytes_to_h2((w[2] >> 4) & 0x0F0F0F0Fu, bias, s2, h1.x, h1.y);
-        bytes_to_h2((w[3] >> 4) & 0x0F0F0F0Fu, bias, s2, h1.z, h1.w);
-        store_chunk(tile, r, 2 * half, l0);
-        store_chunk(tile, r, 2 * half + 1, l1);
-        store_chunk(tile, r, 4 + 2 * half, h0);
-        store_chunk(tile, r, 5 + 2 * half, h1);
+        v[0] = __ldg(p + (size_t)kb * 8 + 2 * h);
+        v[1] = __ldg(p + (size_t)kb * 8 + 2 * h + 1);
+        v[2] = __ldg(p + (size_t)kb * 8 + 4 + 2 * h);
+        v[3] = __ldg(p + (size_t)kb * 8 + 4 + 2 * h + 1);
     }
 }
 
+// 16 weights of sub-block j -> 8 registers of two fp16 each, in K order
+template <int QT>
+__device__ __forceinline__ void convert_sub(const uint4 (&v)[PackedBlock<QT>::kVecs], int j, __half scale, uint32_t (&out)[8]) {
+    if constexpr (QT == UOCR_QT_F16) {
+        const uint4 a = j ? v[2] : v[0], b = j ? v[3] : v[1];
+        out[0] = a.x; out[1] = a.y; out[2] = a.z; out[3] = a.w; out[4] = b.x; out[5] = b.y; out[6] = b.z; out[7] = b.w;
+    } else if constexpr (QT == UOCR_QT_Q8) {
+        const __half2 s2 = __half2half2(scale), bias = __float2half2_rn(1152.f);   // 1024 + 128
+        const uint4 q = j ? v[1] : v[0];
+        bytes_to_h2(q.x ^ 0x80808080u, bias, s2, out[0], out[1]);
+        bytes_to_h2(q.y ^ 0x80808080u, bias, s2, out[2], out[3]);
+        bytes_to_h2(q.z ^ 0x80808080u, bias, s2, out[4], out[5]);
+        bytes_to_h2(q.w ^ 0x80808080u, bias, s2, out[6], out[7]);
+    } else {
+        const __half2 s2 = __half2half2(scale), bias = __float2half2_rn(1032.f);    // 1024 + 8
+        const uint4 q = v[0];
+        const int sh = 4 * j;
+        bytes_to_h2((q.x >> sh) & 0x0F0F0F0Fu, bias, s2, out[0], out[1]);
+        bytes_to_h2((q.y >> sh) & 0x0F0F0F0Fu, bias, s2, out[2], out[3]);
+        bytes_to_h2((q.z >> sh) & 0x0F0F0F0Fu, bias, s2, out[4], out[5]);
+        bytes_to_h2((q.w >> sh) & 0x0F0F0F0Fu, bias, s2, out[6], out[7]);
+    }
+}
+
+// eight 32-bit columns of this thread's TMEM lane
+__device__ __forceinline__ void tc_st8(uint32_t taddr, const uint32_t (&v)[8]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+                 ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]) : "memory");
+}
+__device__ __forceinline__ void tc_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// D[tmem] (+)= A[tmem] * B[smem]^T
+__device__ __forceinline__ void tc_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+
 // ------------------------------------------------------------------------------ kernel
+// Tensor-memory columns: the accumulators first, then kAStages slots of the weight operand (one 32-wide K
+// sub-block of every weight tile per slot).  Two CTAs share an SM, so a CTA may hold at most 256 columns.
 template <bool GATEUP> struct GemmShape {
-    static constexpr int kATiles = GATEUP ? 2 : 1;                     // weight tiles per stage
-    static constexpr int kStages = GATEUP ? 2 : 3;
-    static constexpr int kStageBytes = (kATiles + 1) * kTileBytes;     // + the activation tile
-    static constexpr int kTmemCols = GATEUP ? 256 : 128;
-    static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment*/ + 256 /*barriers*/;
+    static constexpr int kATiles = GATEUP ? 2 : 1;                     // weight tiles (gate and up, or down)
+    static constexpr int kTileN = GATEUP ? kTileNGateUp : uocr::kTileN;   // tokens per tile = columns per accumulator
+    static constexpr int kAStages = 4;
+    static constexpr int kAccCols = kATiles * kTileN;                  // 256
+    static constexpr int kAStageCols = kATiles * 32;                   // 32 columns = one 64-wide K block per weight tile
+    static constexpr int kTmemCols = 512;
+    static_assert(kAccCols + kAStages * kAStageCols <= kTmemCols, "tensor memory budget");
+    static constexpr int kBStages = GATEUP ? 6 : 4;
+    static constexpr int kBTileBytes = kTileN * kBlockK * 2;           // 16 or 32 KB
+    static constexpr int kMaxKBlocks = 32;                             // K <= 2048
+    static constexpr int kScaleBytes = kATiles * kTileM * kMaxKBlocks * 2;
+    static constexpr int kSmemBytes = kBStages * kBTileBytes + kScaleBytes + 1024 /*alignment*/ + 256 /*barriers*/;
 };
 
 template <int QT, bool GATEUP>
-__global__ void __launch_bounds__(kGemmThreads, 2)
+__global__ void __launch_bounds__(kGemmThreads, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap act_map, GemmParams p) {
     using Sh = GemmShape<GATEUP>;
-    constexpr int kStages = Sh::kStages;
+    constexpr int kAStages = Sh::kAStages, kBStages = Sh::kBStages, kTileN = Sh::kTileN;
     if (blockIdx.x >= *p.tile_count) return;
     const uint4 tile = p.tiles[blockIdx.x];
     const uint32_t expert = tile.x, mtile = tile.y, row0 = tile.z, nrows = tile.w;
-    const uint32_t n_mma = (nrows + 15u) & ~15u;          // MMA N: multiple of 16, 16..128
+    const uint32_t n_mma = (nrows + 15u) & ~15u;          // MMA N: multiple of 16
     const uint32_t kblocks = p.k_dim / kBlockK;
 
     extern __shared__ uint8_t smem_dyn[];
-    uint8_t *stages = reinterpret_cast<uint8_t *>(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
-    uint64_t *bars = reinterpret_cast<uint64_t *>(stages + kStages * Sh::kStageBytes);
-    uint64_t *full_a = bars, *full_b = bars + kStages, *empty = bars + 2 * kStages, *acc_full = bars + 3 * kStages;
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 3 * kStages + 1);
+    uint8_t *b_tiles = reinterpret_cast<uint8_t *>(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
+    __half *s_scales = reinterpret_cast<__half *>(b_tiles + kBStages * Sh::kBTileBytes);   // [kATiles][kblocks][128]
+    uint64_t *bars = reinterpret_cast<uint64_t *>(b_tiles + kBStages * Sh::kBTileBytes + Sh::kScaleBytes);
+    uint64_t *a_full = bars, *a_empty = a_full + kAStages, *b_full = a_empty + kAStages, *b_empty = b_full + kBStages,
+             *acc_full = b_empty + kBStages;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_full + 1);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     if (tid == 0) {
-        for (int s = 0; s < kStages; ++s) { gb_init(&full_a[s], kProducerThreads); gb_init(&full_b[s], 1); gb_init(&empty[s], 1); }
+        for (int s = 0; s < kAStages; ++s) { gb_init(&a_full[s], kProducerThreads / 32); gb_init(&a_empty[s], 1); }
+        for (int s = 0; s < kBStages; ++s) { gb_init(&b_full[s], 1); gb_init(&b_empty[s], 1); }
         gb_init(acc_full, 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 9) {
+    if (warp == kMmaWarp) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(s2u(tmem_slot)), "r"((uint32_t)Sh::kTmemCols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -240,48 +273,89 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap act_map, GemmParams p) {
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    const uint32_t a_base = tmem_base + Sh::kAccCols;       // first column of the weight-operand slots
+    const bool tr = p.trace != nullptr && blockIdx.x == 200;
+    const long long t_begin = clock64();
+    if (tr && tid == 0) p.trace[0] = 0;
 
-    if (warp < 8) {
-        // ------------------------------------------------ weight rows -> fp16 swizzled tiles
-        const int r = tid & 127, half = tid >> 7;                     // row of the tile, half of its K block
+    if (warp < 16) {
+        // ------------------------------------------------ weight rows -> fp16 -> tensor memory
+        // Two groups of 256 threads.  gate/up: group g converts matrix g (gate / up).  down: group g converts
+        // the g-th 32-wide sub-block of every K block.  Inside a group, thread (r, h) owns row r and the K
+        // positions [16h, 16h+16) of a sub-block.
+        const int grp = tid >> 8, r = tid & 127, h = (tid >> 7) & 1;
         const size_t grow = (size_t)mtile * kTileM + r;               // row of the matrix
-        const uint8_t *row0p = p.w0 + (size_t)expert * p.expert_stride_bytes + grow * p.row_bytes;
-        const uint8_t *row1p = GATEUP ? p.w1 + (size_t)expert * p.expert_stride_bytes + grow * p.row_bytes : nullptr;
-        const __half *sc0 = QT == UOCR_QT_F16 ? nullptr : p.s0 + (size_t)expert * p.expert_scale_stride + grow * kblocks;
-        const __half *sc1 = (QT == UOCR_QT_F16 || !GATEUP) ? nullptr : p.s1 + (size_t)expert * p.expert_scale_stride + grow * kblocks;
-        uint4 v0[PackedBlock<QT>::kVecs], v1[PackedBlock<QT>::kVecs];
-        load_block<QT>(row0p, 0, half, v0);
-        if (GATEUP) load_block<QT>(row1p, 0, half, v1);
-        for (uint32_t kb = 0; kb < kblocks; ++kb) {
-            const int s = kb % kStages;
-            const uint32_t use = kb / kStages;
-            const __half sa = QT == UOCR_QT_F16 ? __ushort_as_half(0) : sc0[kb];
-            const __half sb = (QT == UOCR_QT_F16 || !GATEUP) ? __ushort_as_half(0) : sc1[kb];
-            if (use > 0 && !gb_wait(&empty[s], (use - 1) & 1u, abort_flag, p.status)) break;
-            uint8_t *st = stages + s * Sh::kStageBytes;
-            dequant_row<QT>(v0, sa, st, r, half);
-            if (GATEUP) dequant_row<QT>(v1, sb, st + kTileBytes, r, half);
-            if (kb + 1 < kblocks) {                                   // next block's bytes travel while this one is used
-                load_block<QT>(row0p, kb + 1, half, v0);
-                if (GATEUP) load_block<QT>(row1p, kb + 1, half, v1);
-            }
-            proxy_fence();                                            // generic-proxy stores -> visible to the MMA's async proxy
-            gb_arrive(&full_a[s]);
+        const uint8_t *rowp = ((GATEUP && grp) ? p.w1 : p.w0) + (size_t)expert * p.expert_stride_bytes + grow * p.row_bytes;
+        constexpr int kAhead = PackedBlock<QT>::kAhead, kVecs = PackedBlock<QT>::kVecs;
+        const int sm = GATEUP ? grp : 0;                              // which matrix's scales this thread uses
+        // the row's scales go to shared memory once ([matrix][k block][row]): the K loop never waits on a 2-byte load
+        // (all loads are issued before the first store: an unrolled, predicated batch, not a dependent chain)
+        if (QT != UOCR_QT_F16 && h == 0 && (GATEUP || grp == 0)) {
+            const __half *sc = (sm == 0 ? p.s0 : p.s1) + (size_t)expert * p.expert_scale_stride + grow * kblocks;
+            __half t[Sh::kMaxKBlocks];
+#pragma unroll
+            for (int kb = 0; kb < Sh::kMaxKBlocks; ++kb) t[kb] = (uint32_t)kb < kblocks ? sc[kb] : __ushort_as_half(0);
+#pragma unroll
+            for (int kb = 0; kb < Sh::kMaxKBlocks; ++kb)
+                if ((uint32_t)kb < kblocks) s_scales[(sm * kblocks + kb) * kTileM + r] = t[kb];
         }
+        uint4 v[kAhead][kVecs];
+#pragma unroll
+        for (int d = 0; d < kAhead; ++d)
+            if ((uint32_t)d < kblocks) load_block<QT>(rowp, d, h, v[d]);
+        asm volatile("bar.sync 1, %0;" ::"n"(kProducerThreads) : "memory");     // scales visible to every thread of a row
+        if (tr && tid == 0) p.trace[1] = clock64() - t_begin;      // producer setup done
+        long long wait_empty = 0;
+        // this thread's TMEM lane, its 8 columns inside a 16-column sub-block, and its matrix inside a slot
+        const uint32_t lane_addr = ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)h * 8 + (GATEUP ? (uint32_t)grp * 32 : 0u);
+        bool alive = true;
+        for (uint32_t kb0 = 0; kb0 < kblocks && alive; kb0 += kAhead) {
+#pragma unroll
+            for (int d = 0; d < kAhead; ++d) {
+                const uint32_t kb = kb0 + d;
+                if (kb >= kblocks) break;
+                const __half sc = QT == UOCR_QT_F16 ? __ushort_as_half(0) : s_scales[(sm * kblocks + kb) * kTileM + r];
+                const uint32_t slot = kb % kAStages, use = kb / kAStages;
+                // gate/up: both 32-wide sub-blocks of this thread's matrix; down: the group's sub-block
+                uint32_t regs[2][8];
+                if (!(p.debug & 1u)) {
+                    if (GATEUP) { convert_sub<QT>(v[d], 0, sc, regs[0]); convert_sub<QT>(v[d], 1, sc, regs[1]); }
+                    else convert_sub<QT>(v[d], grp, sc, regs[0]);
+                }
+                const long long tw = clock64();
+                if (use > 0 && !gb_wait(&a_empty[slot], (use - 1) & 1u, abort_flag, p.status)) { alive = false; break; }
+                wait_empty += clock64() - tw;
+                __syncwarp();
+                tc_fence_after();
+                if (!(p.debug & 1u)) {
+                    const uint32_t dst = a_base + slot * Sh::kAStageCols + lane_addr;
+                    if (GATEUP) { tc_st8(dst, regs[0]); tc_st8(dst + 16, regs[1]); }
+                    else tc_st8(dst + (uint32_t)grp * 16, regs[0]);
+                    tc_st_wait();
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) gb_arrive(&a_full[slot]);              // one arrival per warp: its stores have all landed
+                if (kb + kAhead < kblocks) load_block<QT>(rowp, kb + kAhead, h, v[d]);
+            }
+        }
+        if (tr && tid == 0) { p.trace[2] = clock64() - t_begin; p.trace[3] = wait_empty; }   // producer loop done
         // ------------------------------------------------ epilogue: TMEM -> registers -> global
-        if (gb_wait(acc_full, 0, abort_flag, p.status)) {
+        const bool have_acc = alive && gb_wait(acc_full, 0, abort_flag, p.status);
+        __syncwarp();
+        if (__all_sync(0xffffffffu, have_acc)) {
             tc_fence_after();
-            // a warp reads the TMEM lanes 32*(warp % 4)..+31; warps w and w+4 split the 16-column chunks
+            // a warp reads the TMEM lanes 32*(warp % 4)..+31; the four warps of a lane quarter split the 16-column chunks
             const uint32_t lane_base = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
             const size_t out_col = (size_t)mtile * kTileM + r;
-            for (uint32_t c0 = (uint32_t)half * 16; c0 < nrows; c0 += 32) {
+            for (uint32_t c0 = (uint32_t)(warp >> 2) * 16; c0 < nrows; c0 += 64) {
                 uint32_t g[16], u[16];
                 tc_ld16(lane_base + c0, g);
                 if (GATEUP) tc_ld16(lane_base + kTileN + c0, u);
                 tc_ld_wait();
 #pragma unroll
                 for (int j = 0; j < 16; ++j) {
-                    if (c0 + j < nrows) {
+                    if (c0 + j < nrows && !(p.debug & 4u)) {
                         const float a = __uint_as_float(g[j]);
                         const float o = GATEUP ? silu_f32(a) * __uint_as_float(u[j]) : a;
                         p.out[(size_t)(row0 + c0 + j) * p.out_ld + out_col] = __float2half_rn(o);
@@ -289,17 +363,17 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap act_map, GemmParams p) {
                 }
             }
         }
+        if (tr && tid == 0) p.trace[4] = clock64() - t_begin;      // epilogue done
         tc_fence_before();
-    } else if (warp == 8) {
+    } else if (warp == kTmaWarp) {
         // ------------------------------------------------ activation tiles by TMA
         if (lane == 0) {
             for (uint32_t kb = 0; kb < kblocks; ++kb) {
-                const int s = kb % kStages;
-                const uint32_t use = kb / kStages;
-                if (use > 0 && !gb_wait(&empty[s], (use - 1) & 1u, abort_flag, p.status)) break;
-                gb_expect_tx(&full_b[s], kTileBytes);
-                tma_load_2d(stages + s * Sh::kStageBytes + Sh::kATiles * kTileBytes, &act_map, (int)(kb * kBlockK), (int)row0,
-                            &full_b[s]);
+                const int s = kb % kBStages;
+                const uint32_t use = kb / kBStages;
+                if (use > 0 && !gb_wait(&b_empty[s], (use - 1) & 1u, abort_flag, p.status)) break;
+                gb_expect_tx(&b_full[s], Sh::kBTileBytes);
+                tma_load_2d(b_tiles + s * Sh::kBTileBytes, &act_map, (int)(kb * kBlockK), (int)row0, &b_full[s]);
             }
         }
     } else {
@@ -307,35 +381,47 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap act_map, GemmParams p) {
         if (lane == 0) {
             const uint32_t idesc = umma_idesc(n_mma);
             bool ok = true;
+            long long wa = 0, wb = 0, t_mma = 0, t_commit = 0;
             for (uint32_t kb = 0; kb < kblocks && ok; ++kb) {
-                const int s = kb % kStages;
-                const uint32_t ph = (kb / kStages) & 1u;
-                ok = gb_wait(&full_a[s], ph, abort_flag, p.status) && gb_wait(&full_b[s], ph, abort_flag, p.status);
+                const uint32_t slot = kb % kAStages, bs = kb % kBStages;
+                long long t0 = clock64();
+                ok = gb_wait(&a_full[slot], (kb / kAStages) & 1u, abort_flag, p.status);
+                long long t1 = clock64();
+                if (ok) ok = gb_wait(&b_full[bs], (kb / kBStages) & 1u, abort_flag, p.status);
+                wa += t1 - t0; wb += clock64() - t1;
+                if (tr && kb == 0) p.trace[5] = clock64() - t_begin;   // first operands ready
                 if (!ok) break;
                 tc_fence_after();
-                const uint32_t a_addr = s2u(stages + s * Sh::kStageBytes);
-                const uint32_t b_addr = a_addr + Sh::kATiles * kTileBytes;
+                const uint32_t b_addr = s2u(b_tiles + bs * Sh::kBTileBytes);
+                const uint32_t a_addr = a_base + slot * Sh::kAStageCols;
+                const long long tm0 = clock64();
 #pragma unroll
                 for (int k = 0; k < kBlockK / 16; ++k) {
                     const uint32_t acc = (kb > 0 || k > 0) ? 1u : 0u;
                     const uint64_t bd = umma_desc(b_addr + k * 32);
-                    tc_mma(tmem_base, umma_desc(a_addr + k * 32), bd, idesc, acc);
-                    if (GATEUP) tc_mma(tmem_base + kTileN, umma_desc(a_addr + kTileBytes + k * 32), bd, idesc, acc);
+                    if (p.debug & 2u) continue;
+                    tc_mma_ts(tmem_base, a_addr + k * 8, bd, idesc, acc);
+                    if (GATEUP) tc_mma_ts(tmem_base + kTileN, a_addr + 32 + k * 8, bd, idesc, acc);
                 }
-                tc_commit(&empty[s]);            // arrives when the MMAs above have read the stage
+                const long long tm1 = clock64();
+                tc_commit(&a_empty[slot]);                // arrives when the MMAs above have read the slot
+                tc_commit(&b_empty[bs]);
+                t_mma += tm1 - tm0; t_commit += clock64() - tm1;
             }
             if (ok) tc_commit(acc_full);
+            if (tr) { p.trace[6] = clock64() - t_begin; p.trace[7] = wa; p.trace[8] = wb; p.trace[10] = t_mma; p.trace[11] = t_commit; }
         }
         __syncwarp();
     }
     __syncthreads();
+    if (tr && tid == 0) p.trace[9] = clock64() - t_begin;
     if (*abort_flag) {
         // a wait gave up: let copies and MMAs that may still be in flight land before the CTA goes away
         const long long t0 = clock64();
         while (clock64() - t0 < 2000000LL) {}
         __syncthreads();
     }
-    if (warp == 9) {
+    if (warp == kMmaWarp) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)Sh::kTmemCols) : "memory");
     }
@@ -441,35 +527,37 @@ router_logits_kernel(const __grid_constant__ CUtensorMap hidden_map, const __gri
 }
 
 // --------------------------------------------------------------------- helper kernels
-// Tile lists of the routed GEMMs: for every expert with pairs, one tile per (128 tokens, 128 weight rows).
-// tiles_gu / tiles_dn get {expert, weight-row tile, first sorted position, rows}; counts[0/1] their lengths.
-__global__ void tile_plan_kernel(const uint32_t *__restrict__ expert_offsets, uint32_t E, uint32_t gu_mtiles,
-                                 uint32_t dn_mtiles, uint4 *__restrict__ tiles_gu, uint4 *__restrict__ tiles_dn,
-                                 uint32_t *__restrict__ counts) {
-    __shared__ uint32_t base[257];
+// Tile lists of the routed GEMMs: for every expert with pairs, gate/up tiles of (64 tokens, 128 weight rows)
+// and down tiles of (128 tokens, 128 weight rows).  Entries are {expert, weight-row tile, first sorted
+// position, rows}; counts[0/1] are the list lengths.
+// Segment e uses the weights of expert expert_base + e % expert_mod (single GPU: base 0, mod E; expert-parallel
+// ranks receive one segment per (source rank, local expert)).
+__global__ void tile_plan_kernel(const uint32_t *__restrict__ expert_offsets, uint32_t E, uint32_t expert_base,
+                                 uint32_t expert_mod, uint32_t gu_mtiles, uint32_t dn_mtiles, uint4 *__restrict__ tiles_gu,
+                                 uint4 *__restrict__ tiles_dn, uint32_t *__restrict__ counts) {
+    __shared__ uint32_t base_gu[257], base_dn[257];
     const uint32_t e = threadIdx.x;
-    uint32_t ttiles = 0;
-    if (e < E) ttiles = (expert_offsets[e + 1] - expert_offsets[e] + kTileN - 1) / kTileN;
-    if (e <= 256) base[e] = 0;
-    __syncthreads();
     if (threadIdx.x == 0) {
-        uint32_t run = 0;
+        uint32_t rg = 0, rd = 0;
         for (uint32_t i = 0; i < E; ++i) {
-            const uint32_t t = (expert_offsets[i + 1] - expert_offsets[i] + kTileN - 1) / kTileN;
-            base[i] = run;
-            run += t;
+            const uint32_t c = expert_offsets[i + 1] - expert_offsets[i];
+            base_gu[i] = rg; base_dn[i] = rd;
+            rg += (c + kTileNGateUp - 1) / kTileNGateUp;
+            rd += (c + kTileN - 1) / kTileN;
         }
-        base[E] = run;
-        counts[0] = run * gu_mtiles;
-        counts[1] = run * dn_mtiles;
+        counts[0] = rg * gu_mtiles;
+        counts[1] = rd * dn_mtiles;
     }
     __syncthreads();
     if (e < E) {
         const uint32_t lo = expert_offsets[e], cnt = expert_offsets[e + 1] - lo;
-        for (uint32_t t = 0; t < ttiles; ++t) {
+        for (uint32_t t = 0; t * kTileNGateUp < cnt; ++t) {
+            const uint32_t r0 = lo + t * kTileNGateUp, nr = min((uint32_t)kTileNGateUp, cnt - t * kTileNGateUp);
+            for (uint32_t m = 0; m < gu_mtiles; ++m) tiles_gu[(size_t)(base_gu[e] + t) * gu_mtiles + m] = make_uint4(expert_base + e % expert_mod, m, r0, nr);
+        }
+        for (uint32_t t = 0; t * kTileN < cnt; ++t) {
             const uint32_t r0 = lo + t * kTileN, nr = min((uint32_t)kTileN, cnt - t * kTileN);
-            for (uint32_t m = 0; m < gu_mtiles; ++m) tiles_gu[(size_t)(base[e] + t) * gu_mtiles + m] = make_uint4(e, m, r0, nr);
-            for (uint32_t m = 0; m < dn_mtiles; ++m) tiles_dn[(size_t)(base[e] + t) * dn_mtiles + m] = make_uint4(e, m, r0, nr);
+            for (uint32_t m = 0; m < dn_mtiles; ++m) tiles_dn[(size_t)(base_dn[e] + t) * dn_mtiles + m] = make_uint4(expert_base + e % expert_mod, m, r0, nr);
         }
     }
 }
@@ -477,14 +565,17 @@ __global__ void tile_plan_kernel(const uint32_t *__restrict__ expert_offsets, ui
 // Tile lists of the shared MLP (one "expert", all n tokens).
 __global__ void shared_tile_plan_kernel(uint32_t n, uint32_t gu_mtiles, uint32_t dn_mtiles, uint4 *__restrict__ tiles_gu,
                                         uint4 *__restrict__ tiles_dn, uint32_t *__restrict__ counts) {
-    const uint32_t ttiles = (n + kTileN - 1) / kTileN;
-    for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < ttiles * max(gu_mtiles, dn_mtiles); i += gridDim.x * blockDim.x) {
-        const uint32_t t = i / max(gu_mtiles, dn_mtiles), m = i % max(gu_mtiles, dn_mtiles);
-        const uint32_t r0 = t * kTileN, nr = min((uint32_t)kTileN, n - r0);
-        if (m < gu_mtiles) tiles_gu[(size_t)t * gu_mtiles + m] = make_uint4(0, m, r0, nr);
-        if (m < dn_mtiles) tiles_dn[(size_t)t * dn_mtiles + m] = make_uint4(0, m, r0, nr);
+    const uint32_t tg = (n + kTileNGateUp - 1) / kTileNGateUp, td = (n + kTileN - 1) / kTileN;
+    const uint32_t stride = gridDim.x * blockDim.x, i0 = blockIdx.x * blockDim.x + threadIdx.x;
+    for (uint32_t i = i0; i < tg * gu_mtiles; i += stride) {
+        const uint32_t t = i / gu_mtiles, m = i % gu_mtiles, r0 = t * kTileNGateUp;
+        tiles_gu[i] = make_uint4(0, m, r0, min((uint32_t)kTileNGateUp, n - r0));
     }
-    if (blockIdx.x == 0 && threadIdx.x == 0) { counts[0] = ttiles * gu_mtiles; counts[1] = ttiles * dn_mtiles; }
+    for (uint32_t i = i0; i < td * dn_mtiles; i += stride) {
+        const uint32_t t = i / dn_mtiles, m = i % dn_mtiles, r0 = t * kTileN;
+        tiles_dn[i] = make_uint4(0, m, r0, min((uint32_t)kTileN, n - r0));
+    }
+    if (i0 == 0) { counts[0] = tg * gu_mtiles; counts[1] = td * dn_mtiles; }
 }
 
 // x_sorted[pos][:] = hidden[pair_rows[pos] / K][:]  (one warp per row, 16-byte copies)
@@ -574,18 +665,7 @@ cudaError_t init_gemm_kernels() {
     return err;
 }
 
-// fp16 matrix [rows][cols] (cols contiguous) viewed as tiles of 128 rows x 64 columns, 128B swizzle, zero fill
-static cudaError_t make_act_map(CUtensorMap *map, const void *base, uint64_t rows, uint64_t cols) {
-    const cuuint64_t dims[2] = {cols, rows};
-    const cuuint64_t strides[1] = {cols * 2};
-    const cuuint32_t box[2] = {kBlockK, kTileN};
-    const cuuint32_t estr[2] = {1, 1};
-    const CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void *>(base), dims, strides, box, estr,
-                                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
-}
-
+// fp16 matrix [rows][cols] (cols contiguous) viewed as tiles of box_rows rows x 64 columns, 128B swizzle, zero fill
 static cudaError_t make_map_rows(CUtensorMap *map, const void *base, uint64_t rows, uint64_t cols, uint32_t box_rows) {
     const cuuint64_t dims[2] = {cols, rows};
     const cuuint64_t strides[1] = {cols * 2};
@@ -621,7 +701,8 @@ cudaError_t launch_router_logits(const DLayer &L, const __half *hidden, uint32_t
 }
 
 bool gemm_path_supported(const DLayer &L) {
-    return L.H % 128 == 0 && L.F % 128 == 0 && L.S % 128 == 0 && L.E <= 256 && g_encode != nullptr;
+    return L.H % 128 == 0 && L.F % 128 == 0 && L.S % 128 == 0 && L.E <= 256 && L.H <= 2048 && L.F <= 2048 &&
+           L.S <= 2048 && g_encode != nullptr;
 }
 
 template <bool GU>
@@ -651,62 +732,106 @@ struct GemmScratch {
     uint32_t *counts;       // [4]: routed gate/up, routed down, shared gate/up, shared down
 };
 
-cudaError_t launch_gemm_layer(const DLayer &L, const Scratch &S, const GemmScratch &G, const __half *hidden,
-                              const __half *residual, uint32_t n, __half *out, cudaStream_t st, uint64_t *launches) {
-    const uint32_t H = L.H, F = L.F, Sd = L.S, K = L.K, E = L.E;
-    const uint32_t pairs = n * K;
-    const uint32_t ttiles_max = (pairs + kTileN - 1) / kTileN + E;
-    const uint32_t sttiles = (n + kTileN - 1) / kTileN;
-    cudaError_t err;
-
-    tile_plan_kernel<<<1, 256, 0, st>>>(S.expert_offsets, E, F / kTileM, H / kTileM, G.tiles_gu, G.tiles_dn, G.counts);
-    shared_tile_plan_kernel<<<8, 256, 0, st>>>(n, Sd / kTileM, H / kTileM, G.stiles_gu, G.stiles_dn, G.counts + 2);
-    gather_rows_kernel<<<(pairs * 32 + 255) / 256, 256, 0, st>>>(hidden, S.pair_rows, S.expert_offsets, E, K, H, G.x_sorted);
-    *launches += 3;
-    if ((err = cudaGetLastError()) != cudaSuccess) return err;
-
-    CUtensorMap map_x, map_mid, map_hidden, map_smid;
-    if ((err = make_act_map(&map_x, G.x_sorted, pairs, H)) != cudaSuccess) return err;
-    if ((err = make_act_map(&map_mid, G.mid_sorted, pairs, F)) != cudaSuccess) return err;
-    if ((err = make_act_map(&map_hidden, hidden, n, H)) != cudaSuccess) return err;
-    if ((err = make_act_map(&map_smid, G.shared_mid, n, Sd)) != cudaSuccess) return err;
-
-    const int qt = L.expert_qtype;
+static GemmParams base_params(const Scratch &S) {
     GemmParams p{};
     p.status = S.status;
-    // routed gate/up
+    if (const char *dbg = getenv("UOCR_CUDA_GEMM_DEBUG")) p.debug = (uint32_t)strtoul(dbg, nullptr, 10);
+    return p;
+}
+
+// Routed experts over rows that are already grouped: segment i (rows seg_offsets[i] .. seg_offsets[i+1]) belongs to
+// expert expert_base + i % expert_mod.  rows_in [rows][H] -> mid [rows][F] -> rows_out [rows][H], all fp16.
+cudaError_t launch_gemm_experts(const DLayer &L, const Scratch &S, const GemmScratch &G, const uint32_t *seg_offsets,
+                                uint32_t n_seg, uint32_t expert_base, uint32_t expert_mod, const __half *rows_in,
+                                uint32_t rows_bound, __half *mid, __half *rows_out, cudaStream_t st, uint64_t *launches) {
+    const uint32_t H = L.H, F = L.F;
+    if (rows_bound == 0) return cudaSuccess;
+    const uint32_t ttiles_gu = (rows_bound + kTileNGateUp - 1) / kTileNGateUp + n_seg;
+    const uint32_t ttiles_dn = (rows_bound + kTileN - 1) / kTileN + n_seg;
+    cudaError_t err;
+    tile_plan_kernel<<<1, 256, 0, st>>>(seg_offsets, n_seg, expert_base, expert_mod, F / kTileM, H / kTileM, G.tiles_gu,
+                                        G.tiles_dn, G.counts);
+    ++*launches;
+    if ((err = cudaGetLastError()) != cudaSuccess) return err;
+    CUtensorMap map_x, map_mid;
+    if ((err = make_map_rows(&map_x, rows_in, rows_bound, H, kTileNGateUp)) != cudaSuccess) return err;
+    if ((err = make_map_rows(&map_mid, mid, rows_bound, F, kTileN)) != cudaSuccess) return err;
+    const int qt = L.expert_qtype;
+    GemmParams p = base_params(S);
     p.w0 = L.expert_w; p.w1 = L.expert_w + L.up_offset_bytes;
     p.s0 = L.expert_s; p.s1 = L.expert_s ? L.expert_s + L.up_scale_offset : nullptr;
     p.expert_stride_bytes = L.expert_stride_bytes; p.expert_scale_stride = L.expert_scale_stride;
     p.row_bytes = packed_row_bytes_of(qt, H); p.k_dim = H;
-    p.tiles = G.tiles_gu; p.tile_count = G.counts; p.out = G.mid_sorted; p.out_ld = F;
-    if ((err = launch_gemm<true>(qt, map_x, p, ttiles_max * (F / kTileM), st)) != cudaSuccess) return err;
-    // shared gate/up
-    p.w0 = L.shared_gate.w; p.w1 = L.shared_up.w; p.s0 = L.shared_gate.s; p.s1 = L.shared_up.s;
-    p.expert_stride_bytes = 0; p.expert_scale_stride = 0;
-    p.row_bytes = L.shared_gate.row_bytes; p.k_dim = H;
-    p.tiles = G.stiles_gu; p.tile_count = G.counts + 2; p.out = G.shared_mid; p.out_ld = Sd;
-    if ((err = launch_gemm<true>(L.shared_gate.qtype, map_hidden, p, sttiles * (Sd / kTileM), st)) != cudaSuccess) return err;
-    // routed down
+    p.tiles = G.tiles_gu; p.tile_count = G.counts; p.out = mid; p.out_ld = F;
+    static unsigned long long *g_trace = nullptr;
+    if (getenv("UOCR_CUDA_GEMM_TRACE")) {
+        if (!g_trace) cudaMalloc(&g_trace, 256);
+        p.trace = g_trace;
+    }
+    if ((err = launch_gemm<true>(qt, map_x, p, ttiles_gu * (F / kTileM), st)) != cudaSuccess) return err;
+    if (p.trace) {
+        unsigned long long h[12];
+        cudaStreamSynchronize(st);
+        cudaMemcpy(h, p.trace, sizeof h, cudaMemcpyDeviceToHost);
+        fprintf(stderr, "gemm trace (cycles): setup %llu  producers done %llu (waiting for free slots %llu)  epilogue done %llu | mma: first operands %llu  "
+                        "done %llu  waited on weights %llu, on activations %llu, issuing mma %llu, commits %llu | cta end %llu\n",
+                h[1], h[2], h[3], h[4], h[5], h[6], h[7], h[8], h[10], h[11], h[9]);
+        p.trace = nullptr;
+    }
     p.w0 = L.expert_w + L.down_offset_bytes; p.w1 = nullptr;
     p.s0 = L.expert_s ? L.expert_s + L.down_scale_offset : nullptr; p.s1 = nullptr;
-    p.expert_stride_bytes = L.expert_stride_bytes; p.expert_scale_stride = L.expert_scale_stride;
     p.row_bytes = packed_row_bytes_of(qt, F); p.k_dim = F;
-    p.tiles = G.tiles_dn; p.tile_count = G.counts + 1; p.out = G.down_sorted; p.out_ld = H;
-    if ((err = launch_gemm<false>(qt, map_mid, p, ttiles_max * (H / kTileM), st)) != cudaSuccess) return err;
-    // shared down
-    p.w0 = L.shared_down.w; p.s0 = L.shared_down.s;
-    p.expert_stride_bytes = 0; p.expert_scale_stride = 0;
+    p.tiles = G.tiles_dn; p.tile_count = G.counts + 1; p.out = rows_out; p.out_ld = H;
+    if ((err = launch_gemm<false>(qt, map_mid, p, ttiles_dn * (H / kTileM), st)) != cudaSuccess) return err;
+    *launches += 2;
+    return cudaSuccess;
+}
+
+// Shared MLP on all n tokens, then out = fp16( sum_slot w * down_rows[inverse[pair]] + shared + residual ).
+cudaError_t launch_gemm_shared_combine(const DLayer &L, const Scratch &S, const GemmScratch &G, const __half *down_rows,
+                                       const __half *hidden, const __half *residual, uint32_t n, __half *out,
+                                       cudaStream_t st, uint64_t *launches) {
+    const uint32_t H = L.H, Sd = L.S, K = L.K;
+    const uint32_t sttiles_gu = (n + kTileNGateUp - 1) / kTileNGateUp, sttiles_dn = (n + kTileN - 1) / kTileN;
+    cudaError_t err;
+    shared_tile_plan_kernel<<<8, 256, 0, st>>>(n, Sd / kTileM, H / kTileM, G.stiles_gu, G.stiles_dn, G.counts + 2);
+    ++*launches;
+    CUtensorMap map_hidden, map_smid;
+    if ((err = make_map_rows(&map_hidden, hidden, n, H, kTileNGateUp)) != cudaSuccess) return err;
+    if ((err = make_map_rows(&map_smid, G.shared_mid, n, Sd, kTileN)) != cudaSuccess) return err;
+    GemmParams p = base_params(S);
+    p.w0 = L.shared_gate.w; p.w1 = L.shared_up.w; p.s0 = L.shared_gate.s; p.s1 = L.shared_up.s;
+    p.row_bytes = L.shared_gate.row_bytes; p.k_dim = H;
+    p.tiles = G.stiles_gu; p.tile_count = G.counts + 2; p.out = G.shared_mid; p.out_ld = Sd;
+    if ((err = launch_gemm<true>(L.shared_gate.qtype, map_hidden, p, sttiles_gu * (Sd / kTileM), st)) != cudaSuccess) return err;
+    p.w0 = L.shared_down.w; p.w1 = nullptr; p.s0 = L.shared_down.s; p.s1 = nullptr;
     p.row_bytes = L.shared_down.row_bytes; p.k_dim = Sd;
     p.tiles = G.stiles_dn; p.tile_count = G.counts + 3; p.out = G.shared_out; p.out_ld = H;
-    if ((err = launch_gemm<false>(L.shared_down.qtype, map_smid, p, sttiles * (H / kTileM), st)) != cudaSuccess) return err;
-    *launches += 4;
-
+    if ((err = launch_gemm<false>(L.shared_down.qtype, map_smid, p, sttiles_dn * (H / kTileM), st)) != cudaSuccess) return err;
     const size_t work = (size_t)n * (H / 8);
-    combine_sorted_kernel<<<(unsigned)((work + 255) / 256), 256, 0, st>>>(G.down_sorted, G.shared_out, residual, S.inverse,
+    combine_sorted_kernel<<<(unsigned)((work + 255) / 256), 256, 0, st>>>(down_rows, G.shared_out, residual, S.inverse,
                                                                           S.top_weights, n, H, K, out);
+    *launches += 3;
+    return cudaGetLastError();
+}
+
+// rows_out[pos][:] = hidden[token of the pos-th pair in expert order][:]
+cudaError_t launch_gather_sorted(const DLayer &L, const Scratch &S, const __half *hidden, uint32_t n, __half *rows_out,
+                                 cudaStream_t st, uint64_t *launches) {
+    const uint32_t pairs = n * L.K;
+    gather_rows_kernel<<<(pairs * 32 + 255) / 256, 256, 0, st>>>(hidden, S.pair_rows, S.expert_offsets, L.E, L.K, L.H, rows_out);
     ++*launches;
     return cudaGetLastError();
+}
+
+// The whole many-token layer on one GPU: gather, routed experts, shared MLP + combine.
+cudaError_t launch_gemm_layer(const DLayer &L, const Scratch &S, const GemmScratch &G, const __half *hidden,
+                              const __half *residual, uint32_t n, __half *out, cudaStream_t st, uint64_t *launches) {
+    cudaError_t err;
+    if ((err = launch_gather_sorted(L, S, hidden, n, G.x_sorted, st, launches)) != cudaSuccess) return err;
+    if ((err = launch_gemm_experts(L, S, G, S.expert_offsets, L.E, 0, L.E, G.x_sorted, n * L.K, G.mid_sorted, G.down_sorted,
+                                   st, launches)) != cudaSuccess) return err;
+    return launch_gemm_shared_combine(L, S, G, G.down_sorted, hidden, residual, n, out, st, launches);
 }
 
 }  // namespace uocr

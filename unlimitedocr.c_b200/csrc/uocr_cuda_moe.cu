@@ -25,6 +25,14 @@ struct GemmScratch {
 };
 cudaError_t launch_gemm_layer(const DLayer &L, const Scratch &S, const GemmScratch &G, const __half *hidden,
                               const __half *residual, uint32_t n, __half *out, cudaStream_t st, uint64_t *launches);
+cudaError_t launch_gather_sorted(const DLayer &L, const Scratch &S, const __half *hidden, uint32_t n, __half *rows_out,
+                                 cudaStream_t st, uint64_t *launches);
+cudaError_t launch_gemm_experts(const DLayer &L, const Scratch &S, const GemmScratch &G, const uint32_t *seg_offsets,
+                                uint32_t n_seg, uint32_t expert_base, uint32_t expert_mod, const __half *rows_in,
+                                uint32_t rows_bound, __half *mid, __half *rows_out, cudaStream_t st, uint64_t *launches);
+cudaError_t launch_gemm_shared_combine(const DLayer &L, const Scratch &S, const GemmScratch &G, const __half *down_rows,
+                                       const __half *hidden, const __half *residual, uint32_t n, __half *out,
+                                       cudaStream_t st, uint64_t *launches);
 int decode_grid_size();
 bool decode_supported(const DLayer *layers, uint32_t first, uint32_t count);
 cudaError_t launch_decode_stack(const DLayer *h_layers, const DLayer *d_layers, uint32_t first, uint32_t count,
@@ -390,11 +398,13 @@ static ArenaLayout layout_arena(uint32_t H, uint32_t E, uint32_t K, uint32_t F, 
     a.dec_mid = take(((uint64_t)K * F + S) * 2);            // single-token decode kernel: SwiGLU products
     a.dec_plogits = take((uint64_t)1024 * E * 4);           // and per-CTA partial router logits
     {   // tensor-core path: sorted activations and tile lists (128 tokens x 128 weight rows per tile)
+        // (gate/up tiles hold 64 tokens, down tiles 128)
         const uint64_t ttiles = (pairs + 127) / 128 + E, sttiles = ((uint64_t)n + 127) / 128;
+        const uint64_t ttiles_gu = (pairs + 63) / 64 + E, sttiles_gu = ((uint64_t)n + 63) / 64;
         a.x_sorted = take(pairs * H * 2);
-        a.tiles_gu = take(ttiles * (F / 128 + 1) * 16);
+        a.tiles_gu = take(ttiles_gu * (F / 128 + 1) * 16);
         a.tiles_dn = take(ttiles * (H / 128 + 1) * 16);
-        a.stiles_gu = take(sttiles * (S / 128 + 1) * 16);
+        a.stiles_gu = take(sttiles_gu * (S / 128 + 1) * 16);
         a.stiles_dn = take(sttiles * (H / 128 + 1) * 16);
         a.counts = take(64);
         a.plan_counts = take((pairs / 2048 + 2) * E * 4);
@@ -442,8 +452,9 @@ extern "C" int uocr_cuda_context_allocate_runtime_arenas(uocr_cuda_context *ctx,
     CU_TRY(ctx, cudaMallocHost(&ctx->h_in, act));
     CU_TRY(ctx, cudaMallocHost(&ctx->h_res, act));
     CU_TRY(ctx, cudaMallocHost(&ctx->h_out, act));
-    CU_TRY(ctx, cudaMallocHost(&ctx->h_ids, (size_t)token_capacity * m.K * 4));
-    CU_TRY(ctx, cudaMallocHost(&ctx->h_wts, (size_t)token_capacity * m.K * 4));
+    const size_t small = (size_t)token_capacity * m.K * 4 > 4096 ? (size_t)token_capacity * m.K * 4 : 4096;
+    CU_TRY(ctx, cudaMallocHost(&ctx->h_ids, small));
+    CU_TRY(ctx, cudaMallocHost(&ctx->h_wts, small));
     return 1;
 }
 
@@ -508,6 +519,19 @@ static unsigned long long *barrier_counter(uocr_cuda_context *ctx) {
     return reinterpret_cast<unsigned long long *>(reinterpret_cast<uint8_t *>(ctx->status) + 64);
 }
 
+static uocr::GemmScratch gemm_scratch(uocr_cuda_context *ctx, const Scratch &s, const ArenaLayout &a) {
+    uocr::GemmScratch g{};
+    g.x_sorted = (__half *)(ctx->arena + a.x_sorted);
+    g.mid_sorted = s.mid;
+    g.down_sorted = (__half *)s.down_out;
+    g.shared_mid = s.shared_mid;
+    g.shared_out = (__half *)s.shared_out;
+    g.tiles_gu = (uint4 *)(ctx->arena + a.tiles_gu); g.tiles_dn = (uint4 *)(ctx->arena + a.tiles_dn);
+    g.stiles_gu = (uint4 *)(ctx->arena + a.stiles_gu); g.stiles_dn = (uint4 *)(ctx->arena + a.stiles_dn);
+    g.counts = (uint32_t *)(ctx->arena + a.counts);
+    return g;
+}
+
 static int layer_forward(uocr_cuda_context *ctx, uint32_t layer, const __half *d_hidden, const __half *d_residual,
                          const float *d_injected, uint32_t n, __half *d_out, const uocr_cuda_moe_debug_outputs *dbg,
                          char *error, size_t error_size) {
@@ -529,15 +553,7 @@ static int layer_forward(uocr_cuda_context *ctx, uint32_t layer, const __half *d
         CU_TRY(ctx, uocr::launch_dispatch_plan(s.top_ids, n, L.K, L.E, s.expert_offsets, s.pair_rows, s.inverse,
                                                s.active, s.plan_counts, ctx->stream, &ctx->launches));
         if (n >= ctx->gemm_min_tokens && uocr::gemm_path_supported(L)) {
-            uocr::GemmScratch g{};
-            g.x_sorted = (__half *)(ctx->arena + a.x_sorted);
-            g.mid_sorted = s.mid;
-            g.down_sorted = (__half *)s.down_out;
-            g.shared_mid = s.shared_mid;
-            g.shared_out = (__half *)s.shared_out;
-            g.tiles_gu = (uint4 *)(ctx->arena + a.tiles_gu); g.tiles_dn = (uint4 *)(ctx->arena + a.tiles_dn);
-            g.stiles_gu = (uint4 *)(ctx->arena + a.stiles_gu); g.stiles_dn = (uint4 *)(ctx->arena + a.stiles_dn);
-            g.counts = (uint32_t *)(ctx->arena + a.counts);
+            const uocr::GemmScratch g = gemm_scratch(ctx, s, a);
             CU_TRY(ctx, uocr::launch_gemm_layer(L, s, g, d_hidden, d_residual, n, d_out, ctx->stream, &ctx->launches));
         } else {
             CU_TRY(ctx, uocr::launch_small_batch_layer(L, s, d_hidden, d_residual, n, d_out, ctx->stream, &ctx->launches));
@@ -639,5 +655,73 @@ extern "C" int uocr_cuda_moe_stack_forward_host(uocr_cuda_context *ctx, uint32_t
     CU_TRY(ctx, cudaMemcpyAsync(ctx->h_out, d_out, act, cudaMemcpyDeviceToHost, ctx->stream));
     if (!uocr_cuda_context_synchronize(ctx, error, error_size)) return 0;
     memcpy(h_out, ctx->h_out, act);
+    return 1;
+}
+
+// ------------------------------------------------------------------ expert-parallel phases
+// The many-token layer cut at its two exchange points, so that a host that shards the experts over several
+// GPUs can put an all-to-all between the phases.  With one GPU the three calls in a row are the layer.
+// Scratch is carved for the context's whole token capacity: a rank may receive more rows than it sends.
+
+extern "C" int uocr_cuda_moe_ep_dispatch(uocr_cuda_context *ctx, uint32_t layer, const void *d_hidden, uint32_t n,
+                                         void *d_sorted_rows, uint32_t *h_expert_counts, char *error, size_t error_size) {
+    if (!check_call(ctx, layer, n, error, error_size)) return 0;
+    if (!d_hidden || !d_sorted_rows || !h_expert_counts) return fail(ctx, error, error_size, "null expert-parallel dispatch argument");
+    const DLayer &L = ctx->layers[layer];
+    if (!uocr::gemm_path_supported(L)) return fail(ctx, error, error_size, "layer shape not supported by the tensor-core path");
+    ArenaLayout a;
+    Scratch s = carve(ctx, L, ctx->token_capacity, &a);
+    CU_TRY(ctx, uocr::launch_router(L, (const __half *)d_hidden, nullptr, n, nullptr, nullptr, s.top_ids, s.top_weights,
+                                    ctx->status, s.logits, ctx->stream, &ctx->launches));
+    CU_TRY(ctx, uocr::launch_dispatch_plan(s.top_ids, n, L.K, L.E, s.expert_offsets, s.pair_rows, s.inverse, s.active,
+                                           s.plan_counts, ctx->stream, &ctx->launches));
+    CU_TRY(ctx, uocr::launch_gather_sorted(L, s, (const __half *)d_hidden, n, (__half *)d_sorted_rows, ctx->stream, &ctx->launches));
+    CU_TRY(ctx, cudaMemcpyAsync(ctx->h_ids, s.expert_offsets, (size_t)(L.E + 1) * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    if (!uocr_cuda_context_synchronize(ctx, error, error_size)) return 0;
+    for (uint32_t e = 0; e < L.E; ++e) h_expert_counts[e] = ctx->h_ids[e + 1] - ctx->h_ids[e];
+    return 1;
+}
+
+extern "C" int uocr_cuda_moe_ep_experts(uocr_cuda_context *ctx, uint32_t layer, uint32_t first_expert, uint32_t n_local_experts,
+                                        uint32_t n_sources, const uint32_t *h_segment_counts, const void *d_rows_in,
+                                        void *d_rows_out, char *error, size_t error_size) {
+    if (!ctx) return fail(nullptr, error, error_size, "null context");
+    if (layer >= ctx->layers.size()) return fail(ctx, error, error_size, "layer index %u out of range", layer);
+    const DLayer &L = ctx->layers[layer];
+    const uint32_t n_seg = n_local_experts * n_sources;
+    if (!h_segment_counts || !d_rows_in || !d_rows_out) return fail(ctx, error, error_size, "null expert-parallel argument");
+    if (n_local_experts == 0 || n_sources == 0 || first_expert + n_local_experts > L.E || n_seg > 256)
+        return fail(ctx, error, error_size, "invalid expert range or segment count");
+    if (!ctx->arena) return fail(ctx, error, error_size, "arenas not allocated");
+    ArenaLayout a;
+    Scratch s = carve(ctx, L, ctx->token_capacity, &a);
+    // segment offsets: host prefix sum through the pinned staging buffer
+    uint64_t run = 0;
+    for (uint32_t i = 0; i < n_seg; ++i) { ctx->h_ids[i] = (uint32_t)run; run += h_segment_counts[i]; }
+    ctx->h_ids[n_seg] = (uint32_t)run;
+    if (run > (uint64_t)ctx->token_capacity * L.K)
+        return fail(ctx, error, error_size, "%llu received rows exceed the arena capacity of %llu rows (token_capacity * top_k)",
+                    (unsigned long long)run, (unsigned long long)ctx->token_capacity * L.K);
+    if (run == 0) return 1;
+    CU_TRY(ctx, cudaMemcpyAsync(s.expert_offsets, ctx->h_ids, (size_t)(n_seg + 1) * 4, cudaMemcpyHostToDevice, ctx->stream));
+    const uocr::GemmScratch g = gemm_scratch(ctx, s, a);
+    CU_TRY(ctx, uocr::launch_gemm_experts(L, s, g, s.expert_offsets, n_seg, first_expert, n_local_experts,
+                                          (const __half *)d_rows_in, (uint32_t)run, g.mid_sorted, (__half *)d_rows_out,
+                                          ctx->stream, &ctx->launches));
+    // the pinned buffer is reused by the next call: wait for the copy that reads it
+    CU_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+    return 1;
+}
+
+extern "C" int uocr_cuda_moe_ep_combine(uocr_cuda_context *ctx, uint32_t layer, const void *d_rows_back, const void *d_hidden,
+                                        const void *d_residual, uint32_t n, void *d_out, char *error, size_t error_size) {
+    if (!check_call(ctx, layer, n, error, error_size)) return 0;
+    if (!d_rows_back || !d_hidden || !d_out) return fail(ctx, error, error_size, "null expert-parallel combine argument");
+    const DLayer &L = ctx->layers[layer];
+    ArenaLayout a;
+    Scratch s = carve(ctx, L, ctx->token_capacity, &a);
+    const uocr::GemmScratch g = gemm_scratch(ctx, s, a);
+    CU_TRY(ctx, uocr::launch_gemm_shared_combine(L, s, g, (const __half *)d_rows_back, (const __half *)d_hidden,
+                                                 (const __half *)d_residual, n, (__half *)d_out, ctx->stream, &ctx->launches));
     return 1;
 }

@@ -52,6 +52,7 @@ EXPORTS = (
     "uocr_cuda_context_release_runtime_arenas", "uocr_cuda_moe_scratch_size", "uocr_cuda_moe_router",
     "uocr_cuda_moe_dispatch_plan", "uocr_cuda_moe_dispatch_plan_noalloc", "uocr_cuda_moe_layer_forward", "uocr_cuda_moe_stack_forward",
     "uocr_cuda_moe_layer_forward_host", "uocr_cuda_moe_stack_forward_host",
+    "uocr_cuda_moe_ep_dispatch", "uocr_cuda_moe_ep_experts", "uocr_cuda_moe_ep_combine",
 )
 
 
@@ -101,6 +102,9 @@ def load_library() -> C.CDLL:
         "uocr_cuda_moe_stack_forward": (C.c_int, [vp, u32, u32, vp, u32, vp] + err),
         "uocr_cuda_moe_layer_forward_host": (C.c_int, [vp, u32, vp, vp, u32, vp, vp, vp] + err),
         "uocr_cuda_moe_stack_forward_host": (C.c_int, [vp, u32, u32, vp, u32, vp] + err),
+        "uocr_cuda_moe_ep_dispatch": (C.c_int, [vp, u32, vp, u32, vp, vp] + err),
+        "uocr_cuda_moe_ep_experts": (C.c_int, [vp, u32, u32, u32, u32, vp, vp, vp] + err),
+        "uocr_cuda_moe_ep_combine": (C.c_int, [vp, u32, vp, vp, vp, u32, vp] + err),
     }
     assert set(sig) == set(EXPORTS)
     for name, (res, args) in sig.items():
@@ -171,6 +175,7 @@ class Context:
             raise UocrCudaError(self._err.value.decode())
         self._h = h
         self._layer_k: dict[int, int] = {}
+        self._layer_e: dict[int, int] = {}
 
     def close(self) -> None:
         if self._h:
@@ -204,6 +209,7 @@ class Context:
         idx = C.c_uint32(0xFFFFFFFF)
         self._check(self._lib.uocr_cuda_context_map_moe_layer(self._h, C.byref(desc), C.byref(idx), self._err, _ERR))
         self._layer_k[idx.value] = desc.top_k
+        self._layer_e[idx.value] = desc.n_experts
         return idx.value
 
     def unmap_model(self) -> None:
@@ -268,6 +274,25 @@ class Context:
     def stack_forward(self, first_layer: int, n_layers: int, hidden, n_tokens: int, out) -> None:
         self._check(self._lib.uocr_cuda_moe_stack_forward(self._h, first_layer, n_layers, _dev_ptr(hidden), n_tokens,
                                                           _dev_ptr(out), self._err, _ERR))
+
+    # -- expert-parallel phases (device buffers)
+    def ep_dispatch(self, layer: int, hidden, n_tokens: int, sorted_rows) -> np.ndarray:
+        """Router, plan and gather; returns the number of pairs per expert (uint32 [E], on the host)."""
+        counts = np.zeros(self._layer_e[layer], np.uint32)
+        self._check(self._lib.uocr_cuda_moe_ep_dispatch(self._h, layer, _dev_ptr(hidden), n_tokens, _dev_ptr(sorted_rows),
+                                                        _np_ptr(counts), self._err, _ERR))
+        return counts
+
+    def ep_experts(self, layer: int, first_expert: int, n_local_experts: int, segment_counts: np.ndarray, rows_in,
+                   rows_out) -> None:
+        """segment_counts: uint32 [n_sources, n_local_experts] rows received per (source, local expert)."""
+        seg = np.ascontiguousarray(segment_counts, np.uint32).reshape(-1, n_local_experts)
+        self._check(self._lib.uocr_cuda_moe_ep_experts(self._h, layer, first_expert, n_local_experts, seg.shape[0],
+                                                       _np_ptr(seg), _dev_ptr(rows_in), _dev_ptr(rows_out), self._err, _ERR))
+
+    def ep_combine(self, layer: int, rows_back, hidden, n_tokens: int, out, *, residual=None) -> None:
+        self._check(self._lib.uocr_cuda_moe_ep_combine(self._h, layer, _dev_ptr(rows_back), _dev_ptr(hidden),
+                                                       _dev_ptr(residual), n_tokens, _dev_ptr(out), self._err, _ERR))
 
     # -- operators on host buffers (numpy uint16 fp16 bits)
     def layer_forward_host(self, layer: int, hidden: np.ndarray, residual: np.ndarray | None = None, *,
