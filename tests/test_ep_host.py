@@ -1,0 +1,134 @@
+"""Host logic of the expert-parallel layer, on CPU: the exchange plan arithmetic, and the real
+ExpertParallelLayer.forward driven over a 2-rank gloo group with a NumPy stand-in for the three library
+phases (dispatch / experts / combine).  The stand-in follows the library's contracts (rows sorted by expert,
+per-expert counts, results returned in dispatch order), so what is tested is everything the host adds:
+owner ranges, count matrices, split sizes, both all-to-alls and the order of the returned rows."""
+import os
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+ROOT = Path(__file__).resolve().parent.parent
+sys.path.insert(0, str(ROOT))
+
+E, K, H = 8, 2, 16
+
+
+def load_ep():
+    import __graft_entry__ as entry
+    return entry.load_package().ep
+
+
+class FakeContext:
+    """CPU stand-in: expert e maps a row x to x * (e + 1) + e; the shared MLP is x * 0.5."""
+
+    def __init__(self, ids, weights):
+        self.ids, self.weights = ids, weights            # [n, K]
+
+    def ep_dispatch(self, layer, hidden, n, sorted_rows):
+        flat = self.ids.reshape(-1)
+        order = np.argsort(flat, kind="stable")
+        self.order = order
+        sorted_rows[: n * K] = hidden[torch.from_numpy(order // K)]
+        return np.bincount(flat, minlength=E).astype(np.uint32)
+
+    def ep_experts(self, layer, first, n_local, seg_counts, rows_in, rows_out):
+        pos = 0
+        for s in range(seg_counts.shape[0]):
+            for e in range(n_local):
+                c = int(seg_counts[s, e])
+                ex = first + e
+                rows_out[pos:pos + c] = rows_in[pos:pos + c] * (ex + 1) + ex
+                pos += c
+
+    def ep_combine(self, layer, rows_back, hidden, n, out, residual=None):
+        inv = np.empty_like(self.order)
+        inv[self.order] = np.arange(self.order.size)
+        acc = hidden.float() * 0.5
+        for t in range(n):
+            for s in range(K):
+                acc[t] += self.weights[t, s] * rows_back[inv[t * K + s]].float()
+        if residual is not None:
+            acc += residual.float()
+        out[:] = acc.half()
+
+
+def reference(hidden, ids, weights, residual=None):
+    acc = hidden.float() * 0.5
+    for t in range(hidden.shape[0]):
+        for s in range(K):
+            e = int(ids[t, s])
+            acc[t] += weights[t, s] * (hidden[t] * (e + 1) + e).float()
+    if residual is not None:
+        acc += residual.float()
+    return acc.half()
+
+
+def make_inputs(rank, n):
+    rng = np.random.default_rng(100 + rank)
+    ids = np.stack([rng.permutation(E)[:K] for _ in range(n)]).astype(np.int64)
+    if rank == 1:
+        ids[:, 0] = 0                                   # skew: everything from rank 1 also hits expert 0 (rank 0's)
+    weights = rng.random((n, K)).astype(np.float32)
+    hidden = torch.from_numpy(rng.integers(-4, 5, (n, H)).astype(np.float16))
+    return hidden, ids, weights
+
+
+def worker(rank, world, port, n_by_rank, results):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        ep = load_ep()
+        hidden, ids, weights = make_inputs(rank, n_by_rank[rank])
+        layer = ep.ExpertParallelLayer(FakeContext(ids, weights), 0, E, K, H, rank=rank, world=world, dist_module=dist,
+                                       device="cpu")
+        out = torch.zeros_like(hidden)
+        plan = layer.forward(hidden, out)
+        ok = torch.equal(out, reference(hidden, ids, weights))
+        # every row this rank received is for one of its own experts, and nothing was lost
+        total_sent = torch.tensor([int(plan.send_counts.sum())])
+        total_recv = torch.tensor([plan.rows_received])
+        dist.all_reduce(total_sent); dist.all_reduce(total_recv)
+        results[rank] = (ok, int(total_sent) == int(total_recv) == sum(n_by_rank) * K, plan.recv_counts.tolist())
+    finally:
+        dist.destroy_process_group()
+
+
+def test_owner_ranges_and_count_matrices():
+    ep = load_ep()
+    assert ep.owner_ranges(64, 8) == [(8 * g, 8 * g + 8) for g in range(8)]
+    with pytest.raises(ValueError):
+        ep.owner_ranges(64, 3)
+    counts = np.arange(8)
+    m = ep.send_counts_from_expert_counts(counts, 4)
+    assert m.tolist() == [[0, 1], [2, 3], [4, 5], [6, 7]]
+    plan = ep.ExchangePlan(m, m.T.copy())
+    assert plan.send_splits == [1, 5, 9, 13] and plan.recv_splits == [6, 22] or plan.rows_received == 28
+    assert np.array_equal(ep.exchange_counts(m[:1]), m[:1])          # one rank: nothing to exchange
+
+
+def test_single_rank_forward_matches_reference():
+    ep = load_ep()
+    hidden, ids, weights = make_inputs(0, 13)
+    layer = ep.ExpertParallelLayer(FakeContext(ids, weights), 0, E, K, H, device="cpu")
+    out = torch.zeros_like(hidden)
+    resid = torch.ones_like(hidden)
+    layer.forward(hidden, out, residual=resid)
+    assert torch.equal(out, reference(hidden, ids, weights, resid))
+
+
+def test_two_rank_gloo_forward_matches_reference():
+    world, n_by_rank = 2, [11, 7]                        # ragged token counts
+    port = 29500 + os.getpid() % 2000
+    manager = mp.get_context("spawn").Manager()
+    results = manager.dict()
+    mp.spawn(worker, args=(world, port, n_by_rank, results), nprocs=world, join=True)
+    assert all(results[r][0] for r in range(world)), "outputs differ from the single-process computation"
+    assert all(results[r][1] for r in range(world)), "rows were lost or duplicated in the exchange"
+    # rank 0 owns expert 0 and must have received one row per rank-1 token for it
+    assert results[0][2][1][0] == n_by_rank[1]

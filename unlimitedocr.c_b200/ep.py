@@ -1,0 +1,127 @@
+"""Expert-parallel MoE layer over the GPUs of one node.
+
+The reference engine runs on a single device; this module is the host side of the new multi-GPU path.
+Rank g of G owns the contiguous expert ids [g*E/G, (g+1)*E/G) and a share of the tokens; router and shared
+MLP are computed where a token lives.  One layer call is
+
+    dispatch (router, plan, rows sorted by expert)           library, local
+    all-to-all of the pair counts, then of the fp16 rows     torch.distributed (NCCL over NVLink)
+    routed experts on the received rows                      library, local
+    all-to-all of the results back to the token owners       torch.distributed
+    shared MLP + weighted combine (+ residual)               library, local
+
+With G = 1 the two exchanges are skipped and the same three library calls run back to back.
+The exchange plan (who sends how many rows to whom, in which order) is plain integer arithmetic kept in
+`ExchangePlan`, so it can be tested without a GPU.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import numpy as np
+
+
+@dataclass
+class ExchangePlan:
+    """Row counts of one layer call seen from one rank.
+
+    send_counts[d, e]   rows this rank sends to rank d for d's e-th local expert
+    recv_counts[s, e]   rows this rank receives from rank s for its own e-th local expert
+    """
+
+    send_counts: np.ndarray
+    recv_counts: np.ndarray
+
+    @property
+    def send_splits(self) -> list[int]:
+        return [int(v) for v in self.send_counts.sum(axis=1)]
+
+    @property
+    def recv_splits(self) -> list[int]:
+        return [int(v) for v in self.recv_counts.sum(axis=1)]
+
+    @property
+    def rows_received(self) -> int:
+        return int(self.recv_counts.sum())
+
+
+def owner_ranges(n_experts: int, world: int) -> list[tuple[int, int]]:
+    """Contiguous expert range of every rank; n_experts must divide evenly."""
+    if n_experts % world != 0:
+        raise ValueError(f"{n_experts} experts do not divide over {world} ranks")
+    per = n_experts // world
+    return [(g * per, (g + 1) * per) for g in range(world)]
+
+
+def send_counts_from_expert_counts(expert_counts: np.ndarray, world: int) -> np.ndarray:
+    """[E] pairs per expert on this rank -> [world, E/world] rows per destination rank and local expert.
+    Rows are already sorted by expert id, so destination d's rows are one contiguous block."""
+    expert_counts = np.asarray(expert_counts, np.int64)
+    return expert_counts.reshape(world, expert_counts.shape[0] // world)
+
+
+def exchange_counts(send_counts: np.ndarray, dist_module=None, group=None, device=None) -> np.ndarray:
+    """All-to-all of the count matrix: recv_counts[s] = what rank s sends to this rank."""
+    world = send_counts.shape[0]
+    if world == 1:
+        return send_counts.copy()
+    import torch
+    t_send = torch.from_numpy(np.ascontiguousarray(send_counts, np.int64))
+    if device is not None:
+        t_send = t_send.to(device)
+    t_recv = torch.empty_like(t_send)
+    dist_module.all_to_all_single(t_recv, t_send, group=group)
+    return t_recv.cpu().numpy()
+
+
+class ExpertParallelLayer:
+    """One mapped MoE layer whose routed experts are sharded over the ranks of a process group.
+    The context must run on the stream the collectives use (ctx.set_stream(torch.cuda.current_stream().cuda_stream))."""
+
+    def __init__(self, ctx, layer: int, n_experts: int, top_k: int, hidden_size: int, *, rank: int = 0, world: int = 1,
+                 dist_module=None, group=None, device: str = "cuda"):
+        import torch
+        self.device = device
+        self.ctx, self.layer = ctx, layer
+        self.E, self.K, self.H = n_experts, top_k, hidden_size
+        self.rank, self.world, self.dist, self.group = rank, world, dist_module, group
+        self.first, self.last = owner_ranges(n_experts, world)[rank]
+        self.torch = torch
+        self._bufs: dict[str, object] = {}
+        self.last_plan: ExchangePlan | None = None
+
+    def _buffer(self, name: str, rows: int):
+        t = self._bufs.get(name)
+        if t is None or t.shape[0] < rows:
+            t = self.torch.empty((max(rows, 1), self.H), dtype=self.torch.float16, device=self.device)
+            self._bufs[name] = t
+        return t
+
+    def reserve(self, n_tokens: int, max_rows_received: int) -> None:
+        """Allocate the exchange buffers up front (so a timed step allocates nothing)."""
+        self._buffer("send", n_tokens * self.K)
+        self._buffer("back", n_tokens * self.K)
+        self._buffer("recv", max_rows_received)
+        self._buffer("done", max_rows_received)
+
+    def forward(self, hidden, out, *, residual=None) -> ExchangePlan:
+        n = hidden.shape[0]
+        send = self._buffer("send", n * self.K)
+        expert_counts = self.ctx.ep_dispatch(self.layer, hidden, n, send)
+        send_counts = send_counts_from_expert_counts(expert_counts, self.world)
+        recv_counts = exchange_counts(send_counts, self.dist, self.group, device=self.device)
+        plan = ExchangePlan(send_counts, recv_counts)
+        self.last_plan = plan
+        if self.world == 1:
+            rows_in, rows_done = send, self._buffer("back", n * self.K)
+            self.ctx.ep_experts(self.layer, self.first, self.last - self.first, recv_counts, rows_in, rows_done)
+            back = rows_done
+        else:
+            r = plan.rows_received
+            rows_in, rows_done = self._buffer("recv", r), self._buffer("done", r)
+            self.dist.all_to_all_single(rows_in[:r], send[: n * self.K], plan.recv_splits, plan.send_splits, group=self.group)
+            self.ctx.ep_experts(self.layer, self.first, self.last - self.first, recv_counts, rows_in, rows_done)
+            back = self._buffer("back", n * self.K)
+            self.dist.all_to_all_single(back[: n * self.K], rows_done[:r], plan.send_splits, plan.recv_splits, group=self.group)
+        self.ctx.ep_combine(self.layer, back, hidden, n, out, residual=residual)
+        return plan
