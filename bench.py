@@ -1,11 +1,16 @@
 #!/usr/bin/env python3
 """Benchmark of the MoE-layer hot path.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload decode]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload decode|prefill|ep]
 
-Prints ONE JSON line on rank 0.  The default workload is the full-size decode stack: one token through
-11 stacked MoE layers (hidden 1280, 64 experts top-6 + shared 1792, FFN 896, Q4_0 group-64 weights,
-seed 1), metric = microseconds per token.  A step is one pass of the token through the 11 layers.
+Prints ONE JSON line on rank 0.  Workloads (seeded synthetic inputs of the benchmark plan's shapes):
+  decode   (default on 1 GPU)  one token through 11 stacked MoE layers (hidden 1280, 64 experts top-6 + shared
+           1792, FFN 896, Q4_0 group-64 weights, seed 1); metric = microseconds per token; a step is one pass
+           of the token through the 11 layers.  On N > 1 GPUs with --workload decode: N independent replicas.
+  prefill  one MoE layer on 4096 tokens, Q4_0, Zipf(1.1)-skewed routing, seed 3; metric = tokens per second.
+  ep       (default on N > 1 GPUs)  one MoE layer on 8 x 2048 = 16384 tokens, Q4_0, Zipf(1.1) routing, seed 4, the 64
+           experts sharded over the N GPUs with all-to-all dispatch/combine; metric = tokens per second of the
+           whole job (fixed total work: strong scaling).  Rank 0 also times the same layer alone (G = 1).
 
   value  device time per step (CUDA events on the launching stream), inputs resident in HBM;
   e2e    wall time of the host-buffer C-ABI call (host->device copy, 11 layers, device->host copy);
@@ -170,38 +175,255 @@ def workload_config() -> dict:
             "l2": "flushed between timed iterations (256 MiB written, then 256 MiB read)"}
 
 
-def main() -> None:
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
-    ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="decode", choices=["decode"])
-    ap.add_argument("--cpu-layers", type=int, default=2, help="layers of the stack the CPU baseline samples")
-    ap.add_argument("--no-cpu-baseline", action="store_true")
-    args = ap.parse_args()
+NOMINAL_BF16_TFLOPS = 2250.0
+FALLBACK_BF16_TFLOPS = 1590.0
+FLOPS_PER_TOKEN = 2 * FULL["E"] * FULL["H"] + FULL["K"] * 3 * 2 * FULL["F"] * FULL["H"] + 3 * 2 * FULL["S"] * FULL["H"]
 
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
 
-    if args.impl == "reference":
-        run_reference_arm(args, rank)
+def measured_tensor_peak() -> tuple[float, str]:
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            return float(json.loads(p.read_text())["bf16_tflops"]), "measured"
+        except Exception:
+            pass
+    return FALLBACK_BF16_TFLOPS, "fallback"
+
+
+def token_workload(kind: str) -> dict:
+    if kind == "prefill":
+        return {"n_tokens": 4096, "seed": 3, "metric": "moe_prefill_tokens_per_s",
+                "workload": "prefill: one MoE layer, 4096 tokens, hidden 1280, 64 experts top-6 + shared 1792, FFN 896, "
+                            "Q4_0, Zipf(1.1)-skewed routing via logit bias, seed 3"}
+    return {"n_tokens": 16384, "seed": 4, "metric": "moe_ep_prefill_tokens_per_s",
+            "workload": "expert-parallel prefill: one MoE layer, 8 requests x 2048 = 16384 tokens, Q4_0, 64 experts sharded "
+                        "evenly over the GPUs, all-to-all dispatch/combine, Zipf(1.1)-skewed routing, seed 4"}
+
+
+def synth_token_layer(seed: int, n_tokens: int, qtype_name: str = "q4_0"):
+    from oracle import quant
+    rng = np.random.default_rng(seed)
+    bias = quant.zipf_logit_bias(rng, FULL["E"])
+    L = quant.synth_layer(rng, expert_qtype=quant.QTYPE_BY_NAME[qtype_name], logit_bias=bias, **FULL)
+    hidden = quant.synth_activations(rng, n_tokens, FULL["H"])
+    resid = quant.synth_activations(rng, n_tokens, FULL["H"])
+    return L, hidden, resid
+
+
+def cpu_tokens_per_s(L, hidden, resid, threads: int, rows_per_thread: int = 4, max_seconds: float = 40.0):
+    """The reference CPU layer function on a seeded subset of the tokens (rows_per_thread per host thread)."""
+    from oracle import oracle as orc
+    try:
+        impl, kind = orc.Ref(), "reference"
+    except FileNotFoundError:
+        impl, kind = orc.Port(), "port"
+    rows = min(hidden.shape[0], threads * rows_per_thread)
+    import dataclasses
+    sub_h, sub_r = hidden[:rows], resid[:rows]
+    if kind == "reference":
+        # the unmodified function has no logit bias input: time it on the same weights without the bias
+        # (routing differs, cost per token does not)
+        plain = dataclasses.replace(L, logit_bias=None)
+        f32 = orc.layer_to_f32(plain)
+        run = lambda: impl.layer(plain, sub_h, sub_r, threads=threads, f32_weights=f32)
+    else:
+        run = lambda: impl.layer(L, sub_h, sub_r, threads=threads)
+    run()
+    t0, done = time.perf_counter(), 0
+    while done < 3 and (done == 0 or time.perf_counter() - t0 < max_seconds):
+        run()
+        done += 1
+    dt = (time.perf_counter() - t0) / done
+    return rows / dt, kind, (f"{rows} of the {hidden.shape[0]} tokens ({rows_per_thread} per host thread, {threads} threads), "
+                             f"{done} passes, f32 dequantised weights; tokens/s extrapolates linearly")
+
+
+def run_reference_tokens(args, rank: int, kind: str) -> None:
+    if rank != 0:
         return
+    from oracle import oracle as orc
+    w = token_workload(kind)
+    threads = orc.host_threads()
+    L, hidden, resid = synth_token_layer(w["seed"], 1024)        # the sample never needs more tokens than this
+    t0 = time.perf_counter()
+    tps, ckind, sample = cpu_tokens_per_s(L, hidden, resid, threads)
+    line = {"impl": "reference", "metric": w["metric"], "value": tps, "unit": "tokens/s", "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": w["n_tokens"] / tps * 1e3, "higher_is_better": True,
+            "scaling": "strong" if kind == "ep" else "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": w["workload"], "tokens_per_step": w["n_tokens"], "qtype": "q4_0"},
+            "cpu_baseline": {"value": tps, "unit": "tokens/s", "cores": threads, "kind": ckind, "sample": sample},
+            "e2e": {"value": tps, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0, "wall_s": time.perf_counter() - t0}
+    print(json.dumps(line), flush=True)
 
+
+def make_flush(torch):
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    reader = torch.empty(256 << 20, dtype=torch.uint8, device="cuda").view(torch.int32)
+
+    def flush_l2(i: int):
+        # write a buffer larger than L2, then read a second one through the cache so that the weights are
+        # cold AND the cache is not left full of dirty lines whose write-back would compete with the step
+        flush.fill_(i & 0xFF)
+        reader.max()
+    return flush_l2
+
+
+def run_tokens(args, kind: str, rank: int, local_rank: int, world: int) -> None:
+    """prefill (one GPU) and expert-parallel prefill (N GPUs): one MoE layer on many tokens."""
     import torch
     import torch.distributed as dist
 
     import __graft_entry__ as entry
-
-    if not torch.cuda.is_available():
-        raise SystemExit("bench.py needs a CUDA device: the library has no CPU path (use --impl reference for the CPU arm)")
-    torch.cuda.set_device(local_rank)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
-    entry.build() if not (entry.PKG_DIR / "libuocr_cuda_moe.so").exists() else None
     pkg = entry.load_package()
+    w = token_workload(kind)
+    n_total = w["n_tokens"]
+    if n_total % world:
+        raise SystemExit(f"{n_total} tokens do not divide over {world} ranks")
+    L, hidden, resid = synth_token_layer(w["seed"], n_total)
+    n_local = n_total // world
+    lo = rank * n_local
+    stream = torch.cuda.current_stream()
+    ctx = pkg.Context()
+    ctx.map_layer(L)
+    # a rank can receive every pair of the job (worst case), and rank 0 also runs the whole job alone
+    ctx.allocate_runtime_arenas(n_total)
+    ctx.set_stream(stream.cuda_stream)
+    flush_l2 = make_flush(torch)
+    h_local = torch.from_numpy(hidden[lo:lo + n_local].copy()).pin_memory()
+    r_local = torch.from_numpy(resid[lo:lo + n_local].copy()).pin_memory()
+    d_h = h_local.cuda().view(torch.float16)
+    d_r = r_local.cuda().view(torch.float16)
+    d_out = torch.zeros_like(d_h)
+    host_out = torch.empty((n_local, FULL["H"]), dtype=torch.float16).pin_memory()
+    layer = pkg.ep.ExpertParallelLayer(ctx, 0, FULL["E"], FULL["K"], FULL["H"], rank=rank, world=world,
+                                       dist_module=dist if world > 1 else None)
+    layer.reserve(n_local, n_total * FULL["K"])
 
+    def step():
+        if kind == "prefill":
+            ctx.layer_forward(0, d_h, n_local, d_out, residual=d_r)
+            return None
+        return layer.forward(d_h, d_out, residual=d_r)
+
+    def timed(fn, steps, warmup):
+        for i in range(warmup):
+            flush_l2(i)
+            fn()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        starts = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+        ends = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+        for i in range(steps):
+            flush_l2(i)
+            if world > 1:
+                dist.barrier()                     # every rank starts the step together; the barrier is not timed
+            starts[i].record(stream)
+            fn()
+            ends[i].record(stream)
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        return [s.elapsed_time(e) for s, e in zip(starts, ends)]
+
+    warm = max(args.warmup, 3)
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    launches0 = ctx.kernel_launches
+    times = timed(step, args.steps, warm)
+    launches = (ctx.kernel_launches - launches0) * args.steps // (args.steps + warm)
+    plan = layer.last_plan
+
+    def e2e_step():
+        d_h.view(torch.uint16).copy_(h_local, non_blocking=True)
+        d_r.view(torch.uint16).copy_(r_local, non_blocking=True)
+        step()
+        host_out.copy_(d_out, non_blocking=True)
+
+    e2e_wall = []
+    for i in range(3 + args.steps):
+        flush_l2(i)
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        t0 = time.perf_counter()
+        e2e_step()
+        torch.cuda.synchronize()
+        e2e_wall.append(time.perf_counter() - t0)
+    e2e_ms = sum(e2e_wall[3:]) / args.steps * 1e3
+    clocks = sampler.stop() if sampler else None
+
+    ms = sum(times) / len(times)
+    t = torch.tensor([ms, e2e_ms, float(plan.rows_received) if plan else float(n_local * FULL["K"])], dtype=torch.float64, device="cuda")
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms, e2e_ms, max_rows = float(t[0]), float(t[1]), float(t[2])
+
+    g1 = None
+    if kind == "ep" and world > 1 and rank == 0:
+        # the same job on one GPU, for the scaling reference (other ranks idle)
+        d_all = torch.from_numpy(hidden).cuda().view(torch.float16)
+        r_all = torch.from_numpy(resid).cuda().view(torch.float16)
+        o_all = torch.zeros_like(d_all)
+        solo = pkg.ep.ExpertParallelLayer(ctx, 0, FULL["E"], FULL["K"], FULL["H"])
+        solo.reserve(n_total, n_total * FULL["K"])
+        ts = []
+        for i in range(3 + 5):
+            flush_l2(i)
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(stream); solo.forward(d_all, o_all, residual=r_all); b.record(stream)
+            torch.cuda.synchronize()
+            ts.append(a.elapsed_time(b))
+        g1 = n_total / (sum(ts[3:]) / 5 * 1e-3)
+        # and the sharded result equals the single-GPU result on this rank's tokens
+        assert torch.equal(o_all[lo:lo + n_local], d_out), "expert-parallel output differs from the single-GPU output"
+    if world > 1:
+        dist.barrier()
+
+    if rank == 0:
+        peak, peak_kind = measured_tensor_peak()
+        flops = n_total * FLOPS_PER_TOKEN
+        achieved = flops / (ms * 1e-3) / 1e12 / world        # per GPU
+        tps = n_total / (ms * 1e-3)
+        line = {
+            "metric": w["metric"], "value": tps, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": warm,
+            "ms_per_step": ms, "higher_is_better": True, "scaling": "strong" if kind == "ep" else "weak", "vs_baseline": None,
+            "dtype": "fp16 tensor-core inputs (weights dequantised from Q4_0 on the fly), f32 accumulate", "data": "synthetic",
+            "config": {"workload": w["workload"], "tokens_per_step": n_total, "qtype": "q4_0",
+                       "parallelism": f"ep{world}" if kind == "ep" else "1 gpu",
+                       "l2": "flushed between timed iterations (256 MiB written, then 256 MiB read)"},
+            "e2e": {"value": n_total / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": 2 * n_local * FULL["H"] * 2,
+                    "d2h_bytes_per_step": n_local * FULL["H"] * 2,
+                    "timer": "host wall clock: pinned H2D of hidden and residual, layer, D2H of the output (per rank, max over ranks)"},
+            "gpu_launches": int(launches),
+            "roofline": {"bound": "tensor", "kernel": "grouped_gemm_kernel (whole layer time used)", "achieved": achieved,
+                         "peak": peak, "peak_kind": f"of {peak_kind}", "unit": "TFLOP/s", "frac": achieved / peak,
+                         "frac_of_nominal_2250": achieved / NOMINAL_BF16_TFLOPS, "algorithmic_flops_per_step": flops,
+                         "traffic": None},
+            "clocks": clocks, "step_ms_min_max": [min(times), max(times)],
+        }
+        if kind == "ep":
+            mean_rows = n_total * FULL["K"] / world
+            line["load"] = {"max_rows_received_per_gpu": max_rows, "mean_rows_per_gpu": mean_rows, "max_over_mean": max_rows / mean_rows}
+            if g1 is not None:
+                line["single_gpu_tokens_per_s_same_job"] = g1
+        if not args.no_cpu_baseline and world == 1:
+            from oracle import oracle as orc
+            cps, ckind, sample = cpu_tokens_per_s(L, hidden, resid, orc.host_threads())
+            line["cpu_baseline"] = {"value": cps, "unit": "tokens/s", "cores": orc.host_threads(), "kind": ckind, "sample": sample}
+        print(json.dumps(line), flush=True)
+    ctx.close()
+
+
+def run_decode(args, rank: int, local_rank: int, world: int) -> None:
+    """One token through the 11-layer stack (N replicas when launched on N GPUs)."""
+    import torch
+    import torch.distributed as dist
+
+    import __graft_entry__ as entry
+    pkg = entry.load_package()
     layers, hidden = synth_stack(N_LAYERS, "q4_0", SEED_DECODE)
     ctx = pkg.Context()
     for L in layers:
@@ -212,14 +434,7 @@ def main() -> None:
 
     d_hidden = torch.from_numpy(hidden).cuda().view(torch.float16)
     d_out = torch.zeros_like(d_hidden)
-    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
-    flush_reader = torch.empty(256 << 20, dtype=torch.uint8, device="cuda").view(torch.int32)
-
-    def flush_l2(i: int):
-        # write a buffer larger than L2, then read a second one through the cache so that the weights are
-        # cold AND the cache is not left full of dirty lines whose write-back would compete with the step
-        flush.fill_(i & 0xFF)
-        flush_reader.max()
+    flush_l2 = make_flush(torch)
 
     def step():
         ctx.stack_forward(0, N_LAYERS, d_hidden, 1, d_out)
@@ -299,6 +514,49 @@ def main() -> None:
             line["cpu_baseline"] = {"value": us, "unit": "us/token", "cores": threads, "kind": kind, "sample": sample}
         print(json.dumps(line), flush=True)
     ctx.close()
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=None)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default=None, choices=["decode", "prefill", "ep"])
+    ap.add_argument("--cpu-layers", type=int, default=2, help="layers of the stack the CPU baseline samples")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    kind = args.workload or ("decode" if max(world, args.gpus) == 1 else "ep")
+    if args.steps is None:
+        args.steps = 50 if kind == "decode" else 20
+
+    if args.impl == "reference":
+        if kind == "decode":
+            run_reference_arm(args, rank)
+        else:
+            run_reference_tokens(args, rank, kind)
+        return
+
+    import torch
+    import torch.distributed as dist
+
+    import __graft_entry__ as entry
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the library has no CPU path (use --impl reference for the CPU arm)")
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    if not (entry.PKG_DIR / "libuocr_cuda_moe.so").exists():
+        entry.build()
+    if kind == "decode":
+        run_decode(args, rank, local_rank, world)
+    else:
+        run_tokens(args, kind, rank, local_rank, world)
     if world > 1:
         dist.destroy_process_group()
 
