@@ -200,10 +200,12 @@ def token_workload(kind: str) -> dict:
                         "evenly over the GPUs, all-to-all dispatch/combine, Zipf(1.1)-skewed routing, seed 4"}
 
 
-def synth_token_layer(seed: int, n_tokens: int, qtype_name: str = "q4_0"):
+def synth_token_layer(seed: int, n_tokens: int, qtype_name: str = "q4_0", routing: str = "zipf"):
     from oracle import quant
     rng = np.random.default_rng(seed)
-    bias = quant.zipf_logit_bias(rng, FULL["E"])
+    bias = quant.zipf_logit_bias(rng, FULL["E"])       # drawn in both cases so that the weights do not depend on the choice
+    if routing == "uniform":
+        bias = None
     L = quant.synth_layer(rng, expert_qtype=quant.QTYPE_BY_NAME[qtype_name], logit_bias=bias, **FULL)
     hidden = quant.synth_activations(rng, n_tokens, FULL["H"])
     resid = quant.synth_activations(rng, n_tokens, FULL["H"])
@@ -280,7 +282,7 @@ def run_tokens(args, kind: str, rank: int, local_rank: int, world: int) -> None:
     n_total = w["n_tokens"]
     if n_total % world:
         raise SystemExit(f"{n_total} tokens do not divide over {world} ranks")
-    L, hidden, resid = synth_token_layer(w["seed"], n_total)
+    L, hidden, resid = synth_token_layer(w["seed"], n_total, routing=args.routing)
     n_local = n_total // world
     lo = rank * n_local
     stream = torch.cuda.current_stream()
@@ -391,7 +393,8 @@ def run_tokens(args, kind: str, rank: int, local_rank: int, world: int) -> None:
             "metric": w["metric"], "value": tps, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": warm,
             "ms_per_step": ms, "higher_is_better": True, "scaling": "strong" if kind == "ep" else "weak", "vs_baseline": None,
             "dtype": "fp16 tensor-core inputs (weights dequantised from Q4_0 on the fly), f32 accumulate", "data": "synthetic",
-            "config": {"workload": w["workload"], "tokens_per_step": n_total, "qtype": "q4_0",
+            "config": {"workload": w["workload"] if args.routing == "zipf" else w["workload"].replace("Zipf(1.1)-skewed", "uniform"),
+                       "tokens_per_step": n_total, "qtype": "q4_0", "routing": args.routing,
                        "parallelism": f"ep{world}" if kind == "ep" else "1 gpu",
                        "l2": "flushed between timed iterations (256 MiB written, then 256 MiB read)"},
             "e2e": {"value": n_total / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": 2 * n_local * FULL["H"] * 2,
@@ -525,6 +528,7 @@ def main() -> None:
     ap.add_argument("--workload", default=None, choices=["decode", "prefill", "ep"])
     ap.add_argument("--cpu-layers", type=int, default=2, help="layers of the stack the CPU baseline samples")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--routing", default="zipf", choices=["zipf", "uniform"], help="expert popularity of the prefill / ep workloads")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))

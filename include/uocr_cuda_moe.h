@@ -216,16 +216,17 @@ UOCR_CUDA_API int uocr_cuda_moe_stack_forward_host(uocr_cuda_context *ctx, uint3
  * these three calls have no counterpart there.  They are the many-token layer cut at its two exchange
  * points: a host that shards the experts over several GPUs (each GPU owning a contiguous range of expert
  * ids and a share of the tokens) runs
- *     dispatch  ->  all-to-all of rows  ->  experts  ->  all-to-all back  ->  combine.
- * On one GPU the three calls in a row, without the exchanges, compute uocr_cuda_moe_layer_forward.
- * All three use scratch sized for the context's token capacity, which must cover the rows a rank can
+ *     dispatch  ->  all-to-all of rows (shared MLP meanwhile)  ->  experts  ->  all-to-all back  ->  combine.
+ * On one GPU the four calls in a row, without the exchanges, compute uocr_cuda_moe_layer_forward.
+ * All of them use scratch sized for the context's token capacity, which must cover the rows a rank can
  * RECEIVE: rows_received <= token_capacity * top_k. */
 
 /* Router + dispatch plan on this rank's n_tokens, then d_sorted_rows[pos][H] = hidden row of the pos-th
  * (token, slot) pair in expert order (fp16, n_tokens * top_k rows; experts ascending, so the rows for each
- * owner GPU are contiguous).  h_expert_counts[E] receives the number of pairs per expert (the call waits). */
+ * owner GPU are contiguous).  d_expert_offsets[E+1] (device) receives the exclusive prefix sum of the pairs per
+ * expert, so that the ranks can exchange their counts without a host round trip.  The call does not wait. */
 UOCR_CUDA_API int uocr_cuda_moe_ep_dispatch(uocr_cuda_context *ctx, uint32_t layer, const void *d_hidden_f16,
-                                            uint32_t n_tokens, void *d_sorted_rows_f16, uint32_t *h_expert_counts,
+                                            uint32_t n_tokens, void *d_sorted_rows_f16, uint32_t *d_expert_offsets,
                                             char *error, size_t error_size);
 /* Routed experts first_expert .. first_expert + n_local_experts - 1 on received rows.  d_rows_in holds, for
  * source 0, 1, ... n_sources - 1 in turn, the rows for each local expert in turn; h_segment_counts
@@ -235,11 +236,15 @@ UOCR_CUDA_API int uocr_cuda_moe_ep_experts(uocr_cuda_context *ctx, uint32_t laye
                                            uint32_t n_local_experts, uint32_t n_sources,
                                            const uint32_t *h_segment_counts, const void *d_rows_in_f16,
                                            void *d_rows_out_f16, char *error, size_t error_size);
+/* Shared MLP of this rank's tokens into the context's scratch.  Independent of the exchange, so a host can
+ * run it while the rows travel.  Must precede the combine call of the same layer call. */
+UOCR_CUDA_API int uocr_cuda_moe_ep_shared(uocr_cuda_context *ctx, uint32_t layer, const void *d_hidden_f16,
+                                          uint32_t n_tokens, char *error, size_t error_size);
 /* d_rows_back[pos][H]: the expert outputs for this rank's pairs, in the order dispatch produced them.
- * out = fp16( sum_slot weight * row + shared MLP(hidden) [+ residual] ) for this rank's tokens. */
+ * out = fp16( sum_slot weight * row + shared MLP output [+ residual] ) for this rank's tokens. */
 UOCR_CUDA_API int uocr_cuda_moe_ep_combine(uocr_cuda_context *ctx, uint32_t layer, const void *d_rows_back_f16,
-                                           const void *d_hidden_f16, const void *d_residual_f16, uint32_t n_tokens,
-                                           void *d_out_f16, char *error, size_t error_size);
+                                           const void *d_residual_f16, uint32_t n_tokens, void *d_out_f16,
+                                           char *error, size_t error_size);
 
 #ifdef __cplusplus
 }

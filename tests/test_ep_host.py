@@ -30,12 +30,13 @@ class FakeContext:
     def __init__(self, ids, weights):
         self.ids, self.weights = ids, weights            # [n, K]
 
-    def ep_dispatch(self, layer, hidden, n, sorted_rows):
+    def ep_dispatch(self, layer, hidden, n, sorted_rows, expert_offsets):
         flat = self.ids.reshape(-1)
         order = np.argsort(flat, kind="stable")
         self.order = order
         sorted_rows[: n * K] = hidden[torch.from_numpy(order // K)]
-        return np.bincount(flat, minlength=E).astype(np.uint32)
+        counts = np.bincount(flat, minlength=E)
+        expert_offsets[:] = torch.from_numpy(np.concatenate([[0], np.cumsum(counts)]).astype(np.int32))
 
     def ep_experts(self, layer, first, n_local, seg_counts, rows_in, rows_out):
         pos = 0
@@ -46,10 +47,13 @@ class FakeContext:
                 rows_out[pos:pos + c] = rows_in[pos:pos + c] * (ex + 1) + ex
                 pos += c
 
-    def ep_combine(self, layer, rows_back, hidden, n, out, residual=None):
+    def ep_shared(self, layer, hidden, n):
+        self.shared = hidden.float() * 0.5
+
+    def ep_combine(self, layer, rows_back, n, out, residual=None):
         inv = np.empty_like(self.order)
         inv[self.order] = np.arange(self.order.size)
-        acc = hidden.float() * 0.5
+        acc = self.shared.clone()
         for t in range(n):
             for s in range(K):
                 acc[t] += self.weights[t, s] * rows_back[inv[t * K + s]].float()
@@ -104,12 +108,15 @@ def test_owner_ranges_and_count_matrices():
     assert ep.owner_ranges(64, 8) == [(8 * g, 8 * g + 8) for g in range(8)]
     with pytest.raises(ValueError):
         ep.owner_ranges(64, 3)
-    counts = np.arange(8)
-    m = ep.send_counts_from_expert_counts(counts, 4)
-    assert m.tolist() == [[0, 1], [2, 3], [4, 5], [6, 7]]
-    plan = ep.ExchangePlan(m, m.T.copy())
-    assert plan.send_splits == [1, 5, 9, 13] and plan.recv_splits == [6, 22] or plan.rows_received == 28
-    assert np.array_equal(ep.exchange_counts(m[:1]), m[:1])          # one rank: nothing to exchange
+    offsets = np.array([[0, 1, 3, 6, 10, 15, 21, 28, 36], [0, 8, 15, 21, 26, 30, 33, 35, 36]])     # two ranks, E = 8
+    counts = ep.counts_from_offsets(offsets)
+    assert counts.tolist() == [[1, 2, 3, 4, 5, 6, 7, 8], [8, 7, 6, 5, 4, 3, 2, 1]]
+    p0, p1 = ep.plan_from_counts(counts, 0), ep.plan_from_counts(counts, 1)
+    assert p0.send_counts.tolist() == [[1, 2, 3, 4], [5, 6, 7, 8]] and p0.recv_counts.tolist() == [[1, 2, 3, 4], [8, 7, 6, 5]]
+    assert p0.send_splits == [10, 26] and p0.recv_splits == [10, 26] and p0.rows_received == 36
+    assert p1.recv_counts.tolist() == [[5, 6, 7, 8], [4, 3, 2, 1]] and p1.send_splits == [26, 10]
+    # what rank a sends to b is what b receives from a
+    assert p0.send_splits[1] == p1.recv_splits[0] and p1.send_splits[0] == p0.recv_splits[1]
 
 
 def test_single_rank_forward_matches_reference():

@@ -787,11 +787,10 @@ cudaError_t launch_gemm_experts(const DLayer &L, const Scratch &S, const GemmScr
     return cudaSuccess;
 }
 
-// Shared MLP on all n tokens, then out = fp16( sum_slot w * down_rows[inverse[pair]] + shared + residual ).
-cudaError_t launch_gemm_shared_combine(const DLayer &L, const Scratch &S, const GemmScratch &G, const __half *down_rows,
-                                       const __half *hidden, const __half *residual, uint32_t n, __half *out,
-                                       cudaStream_t st, uint64_t *launches) {
-    const uint32_t H = L.H, Sd = L.S, K = L.K;
+// Shared MLP on all n tokens: G.shared_out[n][H] = fp16( down( silu(gate x) * up x ) ).
+cudaError_t launch_gemm_shared(const DLayer &L, const Scratch &S, const GemmScratch &G, const __half *hidden, uint32_t n,
+                               cudaStream_t st, uint64_t *launches) {
+    const uint32_t H = L.H, Sd = L.S;
     const uint32_t sttiles_gu = (n + kTileNGateUp - 1) / kTileNGateUp, sttiles_dn = (n + kTileN - 1) / kTileN;
     cudaError_t err;
     shared_tile_plan_kernel<<<8, 256, 0, st>>>(n, Sd / kTileM, H / kTileM, G.stiles_gu, G.stiles_dn, G.counts + 2);
@@ -808,10 +807,17 @@ cudaError_t launch_gemm_shared_combine(const DLayer &L, const Scratch &S, const 
     p.row_bytes = L.shared_down.row_bytes; p.k_dim = Sd;
     p.tiles = G.stiles_dn; p.tile_count = G.counts + 3; p.out = G.shared_out; p.out_ld = H;
     if ((err = launch_gemm<false>(L.shared_down.qtype, map_smid, p, sttiles_dn * (H / kTileM), st)) != cudaSuccess) return err;
-    const size_t work = (size_t)n * (H / 8);
+    *launches += 2;
+    return cudaSuccess;
+}
+
+// out = fp16( sum_slot w * down_rows[inverse[pair]] + shared_out + residual )
+cudaError_t launch_gemm_combine(const DLayer &L, const Scratch &S, const GemmScratch &G, const __half *down_rows,
+                                const __half *residual, uint32_t n, __half *out, cudaStream_t st, uint64_t *launches) {
+    const size_t work = (size_t)n * (L.H / 8);
     combine_sorted_kernel<<<(unsigned)((work + 255) / 256), 256, 0, st>>>(down_rows, G.shared_out, residual, S.inverse,
-                                                                          S.top_weights, n, H, K, out);
-    *launches += 3;
+                                                                          S.top_weights, n, L.H, L.K, out);
+    ++*launches;
     return cudaGetLastError();
 }
 
@@ -831,7 +837,8 @@ cudaError_t launch_gemm_layer(const DLayer &L, const Scratch &S, const GemmScrat
     if ((err = launch_gather_sorted(L, S, hidden, n, G.x_sorted, st, launches)) != cudaSuccess) return err;
     if ((err = launch_gemm_experts(L, S, G, S.expert_offsets, L.E, 0, L.E, G.x_sorted, n * L.K, G.mid_sorted, G.down_sorted,
                                    st, launches)) != cudaSuccess) return err;
-    return launch_gemm_shared_combine(L, S, G, G.down_sorted, hidden, residual, n, out, st, launches);
+    if ((err = launch_gemm_shared(L, S, G, hidden, n, st, launches)) != cudaSuccess) return err;
+    return launch_gemm_combine(L, S, G, G.down_sorted, residual, n, out, st, launches);
 }
 
 }  // namespace uocr

@@ -30,9 +30,10 @@ cudaError_t launch_gather_sorted(const DLayer &L, const Scratch &S, const __half
 cudaError_t launch_gemm_experts(const DLayer &L, const Scratch &S, const GemmScratch &G, const uint32_t *seg_offsets,
                                 uint32_t n_seg, uint32_t expert_base, uint32_t expert_mod, const __half *rows_in,
                                 uint32_t rows_bound, __half *mid, __half *rows_out, cudaStream_t st, uint64_t *launches);
-cudaError_t launch_gemm_shared_combine(const DLayer &L, const Scratch &S, const GemmScratch &G, const __half *down_rows,
-                                       const __half *hidden, const __half *residual, uint32_t n, __half *out,
-                                       cudaStream_t st, uint64_t *launches);
+cudaError_t launch_gemm_shared(const DLayer &L, const Scratch &S, const GemmScratch &G, const __half *hidden, uint32_t n,
+                               cudaStream_t st, uint64_t *launches);
+cudaError_t launch_gemm_combine(const DLayer &L, const Scratch &S, const GemmScratch &G, const __half *down_rows,
+                                const __half *residual, uint32_t n, __half *out, cudaStream_t st, uint64_t *launches);
 int decode_grid_size();
 bool decode_supported(const DLayer *layers, uint32_t first, uint32_t count);
 cudaError_t launch_decode_stack(const DLayer *h_layers, const DLayer *d_layers, uint32_t first, uint32_t count,
@@ -44,6 +45,7 @@ cudaError_t launch_decode_stack(const DLayer *h_layers, const DLayer *d_layers, 
 }  // namespace uocr
 
 static constexpr uint32_t kMaxLayers = 64;
+static constexpr uint32_t kSegSlots = 8;
 static constexpr uint64_t kUploadPad = 256;   // kernels may read an aligned window that ends past a tensor
 
 using uocr::DLayer;
@@ -73,6 +75,9 @@ struct uocr_cuda_context {
     __half *h_out = nullptr;
     uint32_t *h_ids = nullptr;
     float *h_wts = nullptr;
+    uint32_t *h_seg = nullptr;         // pinned ring for the expert-parallel segment offsets
+    cudaEvent_t seg_events[8] = {};
+    uint32_t seg_slot = 0;
     uint64_t launches = 0;
     char last_error[1024] = {0};
 };
@@ -147,12 +152,14 @@ extern "C" uocr_cuda_context *uocr_cuda_context_create(const char *resource_path
         (e = cudaMemset(ctx->status, 0, 256)) != cudaSuccess ||
         (e = cudaMallocHost(&ctx->h_status, 256)) != cudaSuccess ||
         (e = cudaMalloc(&ctx->d_layers, kMaxLayers * sizeof(DLayer))) != cudaSuccess ||
+        (e = cudaMallocHost(&ctx->h_seg, kSegSlots * 260 * sizeof(uint32_t))) != cudaSuccess ||
         (e = uocr::init_router_kernels()) != cudaSuccess || (e = uocr::init_small_batch_kernels()) != cudaSuccess ||
         (e = uocr::init_decode_kernels()) != cudaSuccess || (e = uocr::init_gemm_kernels()) != cudaSuccess) {
         fail(nullptr, error, error_size, "CUDA context set-up failed: %s", cudaGetErrorString(e));
         uocr_cuda_context_destroy(ctx);
         return nullptr;
     }
+    for (uint32_t i = 0; i < kSegSlots; ++i) cudaEventCreateWithFlags(&ctx->seg_events[i], cudaEventDisableTiming);
     ctx->stream = ctx->own_stream;
     const char *off = getenv("UOCR_CUDA_DISABLE_FUSED_DECODE");
     ctx->fused_decode = !(off && off[0] == '1');
@@ -189,6 +196,8 @@ extern "C" void uocr_cuda_context_destroy(uocr_cuda_context *ctx) {
     uocr_cuda_context_unmap_model(ctx);
     cudaFree(ctx->status);
     cudaFree(ctx->d_layers);
+    cudaFreeHost(ctx->h_seg);
+    for (uint32_t i = 0; i < kSegSlots; ++i) if (ctx->seg_events[i]) cudaEventDestroy(ctx->seg_events[i]);
     cudaFreeHost(ctx->h_status);
     if (ctx->own_stream) cudaStreamDestroy(ctx->own_stream);
     delete ctx;
@@ -664,9 +673,9 @@ extern "C" int uocr_cuda_moe_stack_forward_host(uocr_cuda_context *ctx, uint32_t
 // Scratch is carved for the context's whole token capacity: a rank may receive more rows than it sends.
 
 extern "C" int uocr_cuda_moe_ep_dispatch(uocr_cuda_context *ctx, uint32_t layer, const void *d_hidden, uint32_t n,
-                                         void *d_sorted_rows, uint32_t *h_expert_counts, char *error, size_t error_size) {
+                                         void *d_sorted_rows, uint32_t *d_expert_offsets, char *error, size_t error_size) {
     if (!check_call(ctx, layer, n, error, error_size)) return 0;
-    if (!d_hidden || !d_sorted_rows || !h_expert_counts) return fail(ctx, error, error_size, "null expert-parallel dispatch argument");
+    if (!d_hidden || !d_sorted_rows || !d_expert_offsets) return fail(ctx, error, error_size, "null expert-parallel dispatch argument");
     const DLayer &L = ctx->layers[layer];
     if (!uocr::gemm_path_supported(L)) return fail(ctx, error, error_size, "layer shape not supported by the tensor-core path");
     ArenaLayout a;
@@ -676,9 +685,7 @@ extern "C" int uocr_cuda_moe_ep_dispatch(uocr_cuda_context *ctx, uint32_t layer,
     CU_TRY(ctx, uocr::launch_dispatch_plan(s.top_ids, n, L.K, L.E, s.expert_offsets, s.pair_rows, s.inverse, s.active,
                                            s.plan_counts, ctx->stream, &ctx->launches));
     CU_TRY(ctx, uocr::launch_gather_sorted(L, s, (const __half *)d_hidden, n, (__half *)d_sorted_rows, ctx->stream, &ctx->launches));
-    CU_TRY(ctx, cudaMemcpyAsync(ctx->h_ids, s.expert_offsets, (size_t)(L.E + 1) * 4, cudaMemcpyDeviceToHost, ctx->stream));
-    if (!uocr_cuda_context_synchronize(ctx, error, error_size)) return 0;
-    for (uint32_t e = 0; e < L.E; ++e) h_expert_counts[e] = ctx->h_ids[e + 1] - ctx->h_ids[e];
+    CU_TRY(ctx, cudaMemcpyAsync(d_expert_offsets, s.expert_offsets, (size_t)(L.E + 1) * 4, cudaMemcpyDeviceToDevice, ctx->stream));
     return 1;
 }
 
@@ -695,33 +702,48 @@ extern "C" int uocr_cuda_moe_ep_experts(uocr_cuda_context *ctx, uint32_t layer, 
     if (!ctx->arena) return fail(ctx, error, error_size, "arenas not allocated");
     ArenaLayout a;
     Scratch s = carve(ctx, L, ctx->token_capacity, &a);
-    // segment offsets: host prefix sum through the pinned staging buffer
+    // segment offsets: host prefix sum through a pinned staging slot (a ring of slots, each guarded by the event of
+    // the copy that last read it, so the call never has to wait for the stream)
+    const uint32_t slot = ctx->seg_slot++ % kSegSlots;
+    uint32_t *h_seg = ctx->h_seg + (size_t)slot * 260;
+    CU_TRY(ctx, cudaEventSynchronize(ctx->seg_events[slot]));
     uint64_t run = 0;
-    for (uint32_t i = 0; i < n_seg; ++i) { ctx->h_ids[i] = (uint32_t)run; run += h_segment_counts[i]; }
-    ctx->h_ids[n_seg] = (uint32_t)run;
+    for (uint32_t i = 0; i < n_seg; ++i) { h_seg[i] = (uint32_t)run; run += h_segment_counts[i]; }
+    h_seg[n_seg] = (uint32_t)run;
     if (run > (uint64_t)ctx->token_capacity * L.K)
         return fail(ctx, error, error_size, "%llu received rows exceed the arena capacity of %llu rows (token_capacity * top_k)",
                     (unsigned long long)run, (unsigned long long)ctx->token_capacity * L.K);
     if (run == 0) return 1;
-    CU_TRY(ctx, cudaMemcpyAsync(s.expert_offsets, ctx->h_ids, (size_t)(n_seg + 1) * 4, cudaMemcpyHostToDevice, ctx->stream));
+    CU_TRY(ctx, cudaMemcpyAsync(s.expert_offsets, h_seg, (size_t)(n_seg + 1) * 4, cudaMemcpyHostToDevice, ctx->stream));
+    CU_TRY(ctx, cudaEventRecord(ctx->seg_events[slot], ctx->stream));
     const uocr::GemmScratch g = gemm_scratch(ctx, s, a);
     CU_TRY(ctx, uocr::launch_gemm_experts(L, s, g, s.expert_offsets, n_seg, first_expert, n_local_experts,
                                           (const __half *)d_rows_in, (uint32_t)run, g.mid_sorted, (__half *)d_rows_out,
                                           ctx->stream, &ctx->launches));
-    // the pinned buffer is reused by the next call: wait for the copy that reads it
-    CU_TRY(ctx, cudaStreamSynchronize(ctx->stream));
     return 1;
 }
 
-extern "C" int uocr_cuda_moe_ep_combine(uocr_cuda_context *ctx, uint32_t layer, const void *d_rows_back, const void *d_hidden,
-                                        const void *d_residual, uint32_t n, void *d_out, char *error, size_t error_size) {
+extern "C" int uocr_cuda_moe_ep_shared(uocr_cuda_context *ctx, uint32_t layer, const void *d_hidden, uint32_t n, char *error,
+                                       size_t error_size) {
     if (!check_call(ctx, layer, n, error, error_size)) return 0;
-    if (!d_rows_back || !d_hidden || !d_out) return fail(ctx, error, error_size, "null expert-parallel combine argument");
+    if (!d_hidden) return fail(ctx, error, error_size, "null activation pointer");
     const DLayer &L = ctx->layers[layer];
     ArenaLayout a;
     Scratch s = carve(ctx, L, ctx->token_capacity, &a);
     const uocr::GemmScratch g = gemm_scratch(ctx, s, a);
-    CU_TRY(ctx, uocr::launch_gemm_shared_combine(L, s, g, (const __half *)d_rows_back, (const __half *)d_hidden,
-                                                 (const __half *)d_residual, n, (__half *)d_out, ctx->stream, &ctx->launches));
+    CU_TRY(ctx, uocr::launch_gemm_shared(L, s, g, (const __half *)d_hidden, n, ctx->stream, &ctx->launches));
+    return 1;
+}
+
+extern "C" int uocr_cuda_moe_ep_combine(uocr_cuda_context *ctx, uint32_t layer, const void *d_rows_back,
+                                        const void *d_residual, uint32_t n, void *d_out, char *error, size_t error_size) {
+    if (!check_call(ctx, layer, n, error, error_size)) return 0;
+    if (!d_rows_back || !d_out) return fail(ctx, error, error_size, "null expert-parallel combine argument");
+    const DLayer &L = ctx->layers[layer];
+    ArenaLayout a;
+    Scratch s = carve(ctx, L, ctx->token_capacity, &a);
+    const uocr::GemmScratch g = gemm_scratch(ctx, s, a);
+    CU_TRY(ctx, uocr::launch_gemm_combine(L, s, g, (const __half *)d_rows_back, (const __half *)d_residual, n,
+                                          (__half *)d_out, ctx->stream, &ctx->launches));
     return 1;
 }

@@ -8,7 +8,8 @@ MLP are computed where a token lives.  One layer call is
     all-to-all of the pair counts, then of the fp16 rows     torch.distributed (NCCL over NVLink)
     routed experts on the received rows                      library, local
     all-to-all of the results back to the token owners       torch.distributed
-    shared MLP + weighted combine (+ residual)               library, local
+    weighted combine with the shared MLP's output (+ residual)   library, local
+(the shared MLP of the local tokens runs while the first exchange is in flight)
 
 With G = 1 the two exchanges are skipped and the same three library calls run back to back.
 The exchange plan (who sends how many rows to whom, in which order) is plain integer arithmetic kept in
@@ -53,25 +54,19 @@ def owner_ranges(n_experts: int, world: int) -> list[tuple[int, int]]:
     return [(g * per, (g + 1) * per) for g in range(world)]
 
 
-def send_counts_from_expert_counts(expert_counts: np.ndarray, world: int) -> np.ndarray:
-    """[E] pairs per expert on this rank -> [world, E/world] rows per destination rank and local expert.
-    Rows are already sorted by expert id, so destination d's rows are one contiguous block."""
-    expert_counts = np.asarray(expert_counts, np.int64)
-    return expert_counts.reshape(world, expert_counts.shape[0] // world)
+def counts_from_offsets(all_offsets: np.ndarray) -> np.ndarray:
+    """[G, E+1] exclusive prefix sums (one row per rank) -> [G, E] pairs per rank and expert."""
+    return np.diff(np.asarray(all_offsets, np.int64), axis=1)
 
 
-def exchange_counts(send_counts: np.ndarray, dist_module=None, group=None, device=None) -> np.ndarray:
-    """All-to-all of the count matrix: recv_counts[s] = what rank s sends to this rank."""
-    world = send_counts.shape[0]
-    if world == 1:
-        return send_counts.copy()
-    import torch
-    t_send = torch.from_numpy(np.ascontiguousarray(send_counts, np.int64))
-    if device is not None:
-        t_send = t_send.to(device)
-    t_recv = torch.empty_like(t_send)
-    dist_module.all_to_all_single(t_recv, t_send, group=group)
-    return t_recv.cpu().numpy()
+def plan_from_counts(counts: np.ndarray, rank: int) -> ExchangePlan:
+    """counts[g, e]: pairs rank g has for expert e.  Rows are sorted by expert id on every rank, so what a rank
+    sends to destination d is one contiguous block: the experts d owns."""
+    world, n_experts = counts.shape
+    per = n_experts // world
+    send = counts[rank].reshape(world, per)
+    recv = counts[:, rank * per:(rank + 1) * per]
+    return ExchangePlan(np.ascontiguousarray(send), np.ascontiguousarray(recv))
 
 
 class ExpertParallelLayer:
@@ -88,6 +83,8 @@ class ExpertParallelLayer:
         self.first, self.last = owner_ranges(n_experts, world)[rank]
         self.torch = torch
         self._bufs: dict[str, object] = {}
+        self._offsets = None
+        self._all_offsets = None
         self.last_plan: ExchangePlan | None = None
 
     def _buffer(self, name: str, rows: int):
@@ -106,22 +103,35 @@ class ExpertParallelLayer:
 
     def forward(self, hidden, out, *, residual=None) -> ExchangePlan:
         n = hidden.shape[0]
+        torch = self.torch
         send = self._buffer("send", n * self.K)
-        expert_counts = self.ctx.ep_dispatch(self.layer, hidden, n, send)
-        send_counts = send_counts_from_expert_counts(expert_counts, self.world)
-        recv_counts = exchange_counts(send_counts, self.dist, self.group, device=self.device)
-        plan = ExchangePlan(send_counts, recv_counts)
+        if self._offsets is None:
+            self._offsets = torch.zeros(self.E + 1, dtype=torch.int32, device=self.device)
+            self._all_offsets = torch.zeros((self.world, self.E + 1), dtype=torch.int32, device=self.device)
+        self.ctx.ep_dispatch(self.layer, hidden, n, send, self._offsets)
+        if self.world == 1:
+            all_offsets = self._offsets.reshape(1, -1)
+        else:      # one small collective on the device, then ONE host read gives every rank the whole count matrix
+            self.dist.all_gather(list(self._all_offsets.unbind(0)), self._offsets, group=self.group)
+            all_offsets = self._all_offsets
+        plan = plan_from_counts(counts_from_offsets(all_offsets.cpu().numpy()), self.rank)
+        recv_counts = plan.recv_counts
         self.last_plan = plan
         if self.world == 1:
-            rows_in, rows_done = send, self._buffer("back", n * self.K)
-            self.ctx.ep_experts(self.layer, self.first, self.last - self.first, recv_counts, rows_in, rows_done)
+            rows_done = self._buffer("back", n * self.K)
+            self.ctx.ep_shared(self.layer, hidden, n)
+            self.ctx.ep_experts(self.layer, self.first, self.last - self.first, recv_counts, send, rows_done)
             back = rows_done
         else:
             r = plan.rows_received
             rows_in, rows_done = self._buffer("recv", r), self._buffer("done", r)
-            self.dist.all_to_all_single(rows_in[:r], send[: n * self.K], plan.recv_splits, plan.send_splits, group=self.group)
+            # the rows travel on the collective's own stream while the shared MLP runs on the compute stream
+            work = self.dist.all_to_all_single(rows_in[:r], send[: n * self.K], plan.recv_splits, plan.send_splits,
+                                               group=self.group, async_op=True)
+            self.ctx.ep_shared(self.layer, hidden, n)
+            work.wait()
             self.ctx.ep_experts(self.layer, self.first, self.last - self.first, recv_counts, rows_in, rows_done)
             back = self._buffer("back", n * self.K)
             self.dist.all_to_all_single(back[: n * self.K], rows_done[:r], plan.send_splits, plan.recv_splits, group=self.group)
-        self.ctx.ep_combine(self.layer, back, hidden, n, out, residual=residual)
+        self.ctx.ep_combine(self.layer, back, n, out, residual=residual)
         return plan

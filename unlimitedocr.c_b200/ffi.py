@@ -52,7 +52,7 @@ EXPORTS = (
     "uocr_cuda_context_release_runtime_arenas", "uocr_cuda_moe_scratch_size", "uocr_cuda_moe_router",
     "uocr_cuda_moe_dispatch_plan", "uocr_cuda_moe_dispatch_plan_noalloc", "uocr_cuda_moe_layer_forward", "uocr_cuda_moe_stack_forward",
     "uocr_cuda_moe_layer_forward_host", "uocr_cuda_moe_stack_forward_host",
-    "uocr_cuda_moe_ep_dispatch", "uocr_cuda_moe_ep_experts", "uocr_cuda_moe_ep_combine",
+    "uocr_cuda_moe_ep_dispatch", "uocr_cuda_moe_ep_experts", "uocr_cuda_moe_ep_shared", "uocr_cuda_moe_ep_combine",
 )
 
 
@@ -104,7 +104,8 @@ def load_library() -> C.CDLL:
         "uocr_cuda_moe_stack_forward_host": (C.c_int, [vp, u32, u32, vp, u32, vp] + err),
         "uocr_cuda_moe_ep_dispatch": (C.c_int, [vp, u32, vp, u32, vp, vp] + err),
         "uocr_cuda_moe_ep_experts": (C.c_int, [vp, u32, u32, u32, u32, vp, vp, vp] + err),
-        "uocr_cuda_moe_ep_combine": (C.c_int, [vp, u32, vp, vp, vp, u32, vp] + err),
+        "uocr_cuda_moe_ep_shared": (C.c_int, [vp, u32, vp, u32] + err),
+        "uocr_cuda_moe_ep_combine": (C.c_int, [vp, u32, vp, vp, u32, vp] + err),
     }
     assert set(sig) == set(EXPORTS)
     for name, (res, args) in sig.items():
@@ -276,12 +277,10 @@ class Context:
                                                           _dev_ptr(out), self._err, _ERR))
 
     # -- expert-parallel phases (device buffers)
-    def ep_dispatch(self, layer: int, hidden, n_tokens: int, sorted_rows) -> np.ndarray:
-        """Router, plan and gather; returns the number of pairs per expert (uint32 [E], on the host)."""
-        counts = np.zeros(self._layer_e[layer], np.uint32)
+    def ep_dispatch(self, layer: int, hidden, n_tokens: int, sorted_rows, expert_offsets) -> None:
+        """Router, plan and gather; expert_offsets (device int32 [E+1]) gets the prefix sum of pairs per expert."""
         self._check(self._lib.uocr_cuda_moe_ep_dispatch(self._h, layer, _dev_ptr(hidden), n_tokens, _dev_ptr(sorted_rows),
-                                                        _np_ptr(counts), self._err, _ERR))
-        return counts
+                                                        _dev_ptr(expert_offsets), self._err, _ERR))
 
     def ep_experts(self, layer: int, first_expert: int, n_local_experts: int, segment_counts: np.ndarray, rows_in,
                    rows_out) -> None:
@@ -290,9 +289,12 @@ class Context:
         self._check(self._lib.uocr_cuda_moe_ep_experts(self._h, layer, first_expert, n_local_experts, seg.shape[0],
                                                        _np_ptr(seg), _dev_ptr(rows_in), _dev_ptr(rows_out), self._err, _ERR))
 
-    def ep_combine(self, layer: int, rows_back, hidden, n_tokens: int, out, *, residual=None) -> None:
-        self._check(self._lib.uocr_cuda_moe_ep_combine(self._h, layer, _dev_ptr(rows_back), _dev_ptr(hidden),
-                                                       _dev_ptr(residual), n_tokens, _dev_ptr(out), self._err, _ERR))
+    def ep_shared(self, layer: int, hidden, n_tokens: int) -> None:
+        self._check(self._lib.uocr_cuda_moe_ep_shared(self._h, layer, _dev_ptr(hidden), n_tokens, self._err, _ERR))
+
+    def ep_combine(self, layer: int, rows_back, n_tokens: int, out, *, residual=None) -> None:
+        self._check(self._lib.uocr_cuda_moe_ep_combine(self._h, layer, _dev_ptr(rows_back), _dev_ptr(residual), n_tokens,
+                                                       _dev_ptr(out), self._err, _ERR))
 
     # -- operators on host buffers (numpy uint16 fp16 bits)
     def layer_forward_host(self, layer: int, hidden: np.ndarray, residual: np.ndarray | None = None, *,
