@@ -52,8 +52,6 @@ struct GemmParams {
     __half *out;                   // mid / down_out, [rows][out_ld]
     uint32_t out_ld;
     uint32_t *status;
-    unsigned long long *trace;     // experiments only: clock stamps of one CTA
-    uint32_t debug;                // experiments only: bit 0 skip conversion + tensor-memory stores, bit 1 skip MMAs, bit 2 skip epilogue stores
 };
 
 // ---------------------------------------------------------------------------------- PTX
@@ -274,9 +272,6 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap act_map, GemmParams p) {
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     const uint32_t a_base = tmem_base + Sh::kAccCols;       // first column of the weight-operand slots
-    const bool tr = p.trace != nullptr && blockIdx.x == 200;
-    const long long t_begin = clock64();
-    if (tr && tid == 0) p.trace[0] = 0;
 
     if (warp < 16) {
         // ------------------------------------------------ weight rows -> fp16 -> tensor memory
@@ -304,8 +299,6 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap act_map, GemmParams p) {
         for (int d = 0; d < kAhead; ++d)
             if ((uint32_t)d < kblocks) load_block<QT>(rowp, d, h, v[d]);
         asm volatile("bar.sync 1, %0;" ::"n"(kProducerThreads) : "memory");     // scales visible to every thread of a row
-        if (tr && tid == 0) p.trace[1] = clock64() - t_begin;      // producer setup done
-        long long wait_empty = 0;
         // this thread's TMEM lane, its 8 columns inside a 16-column sub-block, and its matrix inside a slot
         const uint32_t lane_addr = ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)h * 8 + (GATEUP ? (uint32_t)grp * 32 : 0u);
         bool alive = true;
@@ -318,28 +311,21 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap act_map, GemmParams p) {
                 const uint32_t slot = kb % kAStages, use = kb / kAStages;
                 // gate/up: both 32-wide sub-blocks of this thread's matrix; down: the group's sub-block
                 uint32_t regs[2][8];
-                if (!(p.debug & 1u)) {
-                    if (GATEUP) { convert_sub<QT>(v[d], 0, sc, regs[0]); convert_sub<QT>(v[d], 1, sc, regs[1]); }
-                    else convert_sub<QT>(v[d], grp, sc, regs[0]);
-                }
-                const long long tw = clock64();
+                if (GATEUP) { convert_sub<QT>(v[d], 0, sc, regs[0]); convert_sub<QT>(v[d], 1, sc, regs[1]); }
+                else convert_sub<QT>(v[d], grp, sc, regs[0]);
                 if (use > 0 && !gb_wait(&a_empty[slot], (use - 1) & 1u, abort_flag, p.status)) { alive = false; break; }
-                wait_empty += clock64() - tw;
                 __syncwarp();
                 tc_fence_after();
-                if (!(p.debug & 1u)) {
-                    const uint32_t dst = a_base + slot * Sh::kAStageCols + lane_addr;
-                    if (GATEUP) { tc_st8(dst, regs[0]); tc_st8(dst + 16, regs[1]); }
-                    else tc_st8(dst + (uint32_t)grp * 16, regs[0]);
-                    tc_st_wait();
-                }
+                const uint32_t dst = a_base + slot * Sh::kAStageCols + lane_addr;
+                if (GATEUP) { tc_st8(dst, regs[0]); tc_st8(dst + 16, regs[1]); }
+                else tc_st8(dst + (uint32_t)grp * 16, regs[0]);
+                tc_st_wait();
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) gb_arrive(&a_full[slot]);              // one arrival per warp: its stores have all landed
                 if (kb + kAhead < kblocks) load_block<QT>(rowp, kb + kAhead, h, v[d]);
             }
         }
-        if (tr && tid == 0) { p.trace[2] = clock64() - t_begin; p.trace[3] = wait_empty; }   // producer loop done
         // ------------------------------------------------ epilogue: TMEM -> registers -> global
         const bool have_acc = alive && gb_wait(acc_full, 0, abort_flag, p.status);
         __syncwarp();
@@ -355,7 +341,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap act_map, GemmParams p) {
                 tc_ld_wait();
 #pragma unroll
                 for (int j = 0; j < 16; ++j) {
-                    if (c0 + j < nrows && !(p.debug & 4u)) {
+                    if (c0 + j < nrows) {
                         const float a = __uint_as_float(g[j]);
                         const float o = GATEUP ? silu_f32(a) * __uint_as_float(u[j]) : a;
                         p.out[(size_t)(row0 + c0 + j) * p.out_ld + out_col] = __float2half_rn(o);
@@ -363,7 +349,6 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap act_map, GemmParams p) {
                 }
             }
         }
-        if (tr && tid == 0) p.trace[4] = clock64() - t_begin;      // epilogue done
         tc_fence_before();
     } else if (warp == kTmaWarp) {
         // ------------------------------------------------ activation tiles by TMA
@@ -381,40 +366,29 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap act_map, GemmParams p) {
         if (lane == 0) {
             const uint32_t idesc = umma_idesc(n_mma);
             bool ok = true;
-            long long wa = 0, wb = 0, t_mma = 0, t_commit = 0;
             for (uint32_t kb = 0; kb < kblocks && ok; ++kb) {
                 const uint32_t slot = kb % kAStages, bs = kb % kBStages;
-                long long t0 = clock64();
                 ok = gb_wait(&a_full[slot], (kb / kAStages) & 1u, abort_flag, p.status);
-                long long t1 = clock64();
                 if (ok) ok = gb_wait(&b_full[bs], (kb / kBStages) & 1u, abort_flag, p.status);
-                wa += t1 - t0; wb += clock64() - t1;
-                if (tr && kb == 0) p.trace[5] = clock64() - t_begin;   // first operands ready
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t b_addr = s2u(b_tiles + bs * Sh::kBTileBytes);
                 const uint32_t a_addr = a_base + slot * Sh::kAStageCols;
-                const long long tm0 = clock64();
 #pragma unroll
                 for (int k = 0; k < kBlockK / 16; ++k) {
                     const uint32_t acc = (kb > 0 || k > 0) ? 1u : 0u;
                     const uint64_t bd = umma_desc(b_addr + k * 32);
-                    if (p.debug & 2u) continue;
                     tc_mma_ts(tmem_base, a_addr + k * 8, bd, idesc, acc);
                     if (GATEUP) tc_mma_ts(tmem_base + kTileN, a_addr + 32 + k * 8, bd, idesc, acc);
                 }
-                const long long tm1 = clock64();
                 tc_commit(&a_empty[slot]);                // arrives when the MMAs above have read the slot
                 tc_commit(&b_empty[bs]);
-                t_mma += tm1 - tm0; t_commit += clock64() - tm1;
             }
             if (ok) tc_commit(acc_full);
-            if (tr) { p.trace[6] = clock64() - t_begin; p.trace[7] = wa; p.trace[8] = wb; p.trace[10] = t_mma; p.trace[11] = t_commit; }
         }
         __syncwarp();
     }
     __syncthreads();
-    if (tr && tid == 0) p.trace[9] = clock64() - t_begin;
     if (*abort_flag) {
         // a wait gave up: let copies and MMAs that may still be in flight land before the CTA goes away
         const long long t0 = clock64();
@@ -735,7 +709,6 @@ struct GemmScratch {
 static GemmParams base_params(const Scratch &S) {
     GemmParams p{};
     p.status = S.status;
-    if (const char *dbg = getenv("UOCR_CUDA_GEMM_DEBUG")) p.debug = (uint32_t)strtoul(dbg, nullptr, 10);
     return p;
 }
 
@@ -763,21 +736,7 @@ cudaError_t launch_gemm_experts(const DLayer &L, const Scratch &S, const GemmScr
     p.expert_stride_bytes = L.expert_stride_bytes; p.expert_scale_stride = L.expert_scale_stride;
     p.row_bytes = packed_row_bytes_of(qt, H); p.k_dim = H;
     p.tiles = G.tiles_gu; p.tile_count = G.counts; p.out = mid; p.out_ld = F;
-    static unsigned long long *g_trace = nullptr;
-    if (getenv("UOCR_CUDA_GEMM_TRACE")) {
-        if (!g_trace) cudaMalloc(&g_trace, 256);
-        p.trace = g_trace;
-    }
     if ((err = launch_gemm<true>(qt, map_x, p, ttiles_gu * (F / kTileM), st)) != cudaSuccess) return err;
-    if (p.trace) {
-        unsigned long long h[12];
-        cudaStreamSynchronize(st);
-        cudaMemcpy(h, p.trace, sizeof h, cudaMemcpyDeviceToHost);
-        fprintf(stderr, "gemm trace (cycles): setup %llu  producers done %llu (waiting for free slots %llu)  epilogue done %llu | mma: first operands %llu  "
-                        "done %llu  waited on weights %llu, on activations %llu, issuing mma %llu, commits %llu | cta end %llu\n",
-                h[1], h[2], h[3], h[4], h[5], h[6], h[7], h[8], h[10], h[11], h[9]);
-        p.trace = nullptr;
-    }
     p.w0 = L.expert_w + L.down_offset_bytes; p.w1 = nullptr;
     p.s0 = L.expert_s ? L.expert_s + L.down_scale_offset : nullptr; p.s1 = nullptr;
     p.row_bytes = packed_row_bytes_of(qt, F); p.k_dim = F;
