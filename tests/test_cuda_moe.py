@@ -423,14 +423,17 @@ def test_invalid_arguments_are_rejected_with_text(pkg):
 
 # ------------------------------------------------------------ persistent decode kernel
 
+@pytest.mark.parametrize("design", ["one-barrier", "two-barrier"])
 @pytest.mark.parametrize("qname", ["q4_0", "q8_0"])
-def test_fused_decode_kernel_agrees_with_the_multi_kernel_path(pkg, port, qname, monkeypatch):
-    """Single-token calls at the model's shapes run in one persistent kernel; the same call with that
-    kernel disabled runs router, plan, gate/up, down and combine kernels.  Both follow one rounding
-    contract, so they agree to f32 summation order, and both match the oracle."""
+def test_fused_decode_kernel_agrees_with_the_multi_kernel_path(pkg, port, qname, design, monkeypatch):
+    """Single-token calls at the model's shapes run in one persistent kernel (two designs: one grid barrier
+    per layer with 64-wide slices of the intermediate dimension per CTA, or the earlier two-barrier form);
+    the same call with that kernel disabled runs router, plan, gate/up, down and combine kernels.  All
+    follow one rounding contract, so they agree to f32 summation order, and all match the oracle."""
     rng = np.random.default_rng(31)
     layers = [quant.synth_layer(rng, expert_qtype=QT[qname], **FULL) for _ in range(2)]
     hidden = quant.synth_activations(rng, 1, FULL["H"])
+    monkeypatch.setenv("UOCR_CUDA_DECODE_DESIGN", design)
     outs, launches = {}, {}
     for mode in ("fused", "generic"):
         if mode == "generic":
@@ -456,11 +459,37 @@ def test_fused_decode_kernel_agrees_with_the_multi_kernel_path(pkg, port, qname,
         assert err <= MAX_ABS and cos >= MIN_COS, (mode, err, cos)
     err, cos = closeness(outs["fused"], outs["generic"])
     assert err <= 4e-3 and cos >= 0.99999, (err, cos)
-    # repeated calls of the persistent kernel are bit-reproducible (fixed summation orders, no atomics)
+    # repeated calls of the persistent kernel are bit-reproducible (fixed summation orders, or order-independent
+    # integer accumulation), also when single-layer and stacked calls alternate on one context
     with pkg.Context() as ctx:
         for L in layers:
             ctx.map_layer(L)
         ctx.allocate_runtime_arenas(1)
         a = ctx.stack_forward_host(0, 2, hidden)
+        singles = [ctx.layer_forward_host(1, hidden, hidden) for _ in range(3)]
         b = ctx.stack_forward_host(0, 2, hidden)
-        assert np.array_equal(a, b)
+        for _ in range(5):
+            singles.append(ctx.layer_forward_host(1, hidden, None))
+            singles.append(ctx.layer_forward_host(1, hidden, hidden))
+        c = ctx.stack_forward_host(0, 2, hidden)
+        assert np.array_equal(a, b) and np.array_equal(a, c)
+        assert all(np.array_equal(singles[0], x) for x in singles[1:3] + singles[4::2])
+        assert all(np.array_equal(singles[3], x) for x in singles[5::2])
+
+
+def test_sliced_decode_kernel_with_injected_logits_with_and_without_residual(pkg, port):
+    """The one-barrier decode kernel on injected logits, once with a residual and once without."""
+    L, hidden, resid = make(6, FULL, "q4_0", 1)
+    want = port.layer(L, hidden, resid)
+    inj = want.logits.copy()
+    g = Layer(pkg, quant.LayerWeights(**{**L.__dict__, "logit_bias": None}), 1)
+    try:
+        out, ids, wts = g.forward(hidden, resid, injected=inj)
+        out2, _, _ = g.forward(hidden, None, injected=inj)
+    finally:
+        g.close()
+    assert np.array_equal(ids, want.ids)
+    err, cos = closeness(out, want.out)
+    assert err <= MAX_ABS and cos >= MIN_COS, (err, cos)
+    err, cos = closeness(out2, port.layer(L, hidden, None).out)
+    assert err <= MAX_ABS and cos >= MIN_COS, (err, cos)

@@ -34,6 +34,9 @@ struct DLayer {
     uint64_t expert_stride_bytes, up_offset_bytes, down_offset_bytes;
     uint64_t expert_scale_stride, up_scale_offset, down_scale_offset;
     DMatrix shared_gate, shared_up, shared_down;
+    // Slice-major copy of the quantised weights for the single-token decode kernel (one contiguous blob per
+    // 64-wide slice of every expert's and the shared MLP's intermediate dimension), or null.
+    const uint8_t *dec_units;
 };
 
 // Scratch carved out of the context arena for one forward call.

@@ -1,0 +1,740 @@
+// Single-token decode, sliced design: a run of MoE layers in ONE persistent kernel with ONE grid-wide
+// barrier per layer.
+//
+// The intermediate dimension of every SwiGLU MLP the token uses is cut into 64-wide slices (one
+// quantisation group of the `down` matrix): K * F/64 routed slices + S/64 shared slices = 112 units for
+// the model's shapes, one CTA each.  The CTA of a slice
+//   1. computes the slice's 64 gate and 64 up pre-activations (128 packed rows of length H, staged in shared
+//      memory by a few large TMA bulk copies) and the 64 SwiGLU products (rounded to fp16),
+//   2. multiplies them straight away with its 64-column slice of `down` (H rows, loaded into registers while
+//      step 1 runs), scales by the routing weight, and
+//   3. adds the H partial outputs to the layer's accumulator in global memory - after the (up to) eight CTAs of
+//      a thread-block cluster have summed their partial outputs through distributed shared memory, which cuts
+//      the number of global reductions eightfold.
+// Nothing crosses CTAs between 1 and 2, so a layer needs a single barrier: after it every CTA reads the H
+// accumulated values, adds the residual, rounds to fp16 and has the next layer's input.
+//
+// Weight layout.  A column slice of `down` in the file layout is 32 bytes out of every 448-byte row, and the
+// 128 gate/up rows of a slice are read 8 bytes per lane: both are poison for DRAM bursts and for the load/store
+// unit (one cache line per row per instruction).  When a layer is mapped, the weights are therefore ALSO stored
+// slice-major ("unit blobs"): everything one CTA needs, contiguous, already in the order the MMA lanes consume
+// it.  The file-layout copy stays for the many-token paths.  Same bytes, no padding: a blob is
+//   gate/up fragments [group 0..19][row block 0..7][lane] | gate/up scales [128][20] | down fragments
+//   [row block 0..79][lane] | down scales [H].
+//
+// The accumulator is 64-bit fixed point (2^-32 units) updated with integer reductions, so the sum does not
+// depend on the order in which CTAs arrive: results are reproducible run to run.  Four accumulator
+// buffers rotate (adds / read / idle / cleared), the rotation continues across launches.
+//
+// Off the critical path: the shared-MLP CTAs do not depend on the routing, so they fetch the NEXT layer's
+// weights while they wait at the barrier; the routed CTAs fetch the next layer's router matrix into
+// registers at the same point and evaluate it (every routed CTA redundantly, no exchange) as soon as the
+// new activations are there.
+//
+// Arithmetic.  Scalar dequantise-and-FMA costs ~3.5 instructions per packed weight and would bound the layer, so
+// the dot products run on the tensor cores as INTEGER MMAs (m16n8k32, s32 accumulate), which take the packed
+// levels as they are (Q8: the int8 words themselves; Q4: one AND per four weights).  The fp16 activations of a
+// 64-wide group are written once per layer as a block-floating-point number: a shared power-of-two scale and
+// 22-bit signed mantissas, exact for every value within 2^11 of the group's largest, 2^-22 of it otherwise (fp32
+// accumulation itself carries 2^-24).  A mantissa is split into three signed bytes, and the three bytes ride in
+// three of the MMA's eight columns, so one MMA yields the group's exact integer dot product with all three.
+// Per group the integers are recombined in f32 and multiplied by (activation scale x the group's fp16 weight
+// scale); Q4's +8 offset is removed with a per-group correction 8 * sum(mantissas).  The router matrix is fp16
+// and runs as fp16 MMAs (m16n8k16) on the activations themselves.
+//
+// Every wait is bounded (see moe_sync.cuh).
+#include <cuda.h>
+
+#include "moe_route.cuh"
+#include "moe_sync.cuh"
+
+namespace uocr {
+
+constexpr int kSlThreads = 512;
+constexpr int kSlH = 1280, kSlF = 896, kSlS = 1792, kSlK = 6, kSlE = 64;
+constexpr int kSlRoutedPerSlot = kSlF / 64;                 // 14
+constexpr int kSlRouted = kSlK * kSlRoutedPerSlot;          // 84
+constexpr int kSlUnits = kSlRouted + kSlS / 64;             // 112 CTAs
+constexpr int kSlGroups = kSlH / 64;                        // 20 quantisation groups along H
+constexpr int kSlChunks = 5;                                // gate/up fragments arrive in 5 copies of 4 groups
+constexpr int kSlAccBuffers = 4;
+constexpr int kSlTracePoints = 8;
+constexpr int kSlMaxLayers = 64;
+constexpr int kSlBlocksPerWarp = kSlH / 16 / 16;            // 5 blocks of 16 output rows per warp
+
+struct SlicedParams {
+    const DLayer *layers;
+    uint32_t first, count;
+    const __half *hidden_in;
+    const __half *residual0;      // residual of the first layer (may be null)
+    int chain_residual;           // layers after the first use their input as residual
+    const float *injected;        // [E] logits for the first layer, or null
+    __half *out;
+    unsigned long long *acc;      // [kSlAccBuffers][H] fixed-point accumulators, all zero between launches except two
+    uint32_t acc_base;            // buffer of the first layer of this launch
+    unsigned long long *bar;
+    unsigned long long bar_base;
+    uint32_t *status;
+    float *dbg_logits, *dbg_probs;
+    uint32_t *ids_out;            // [K] routing of the last layer run
+    float *wts_out;
+    unsigned long long *trace;    // optional [CTA][count][kSlTracePoints] SM-clock stamps
+};
+
+// ---------------------------------------------------------------- packed formats and the unit blob
+template <int QT> struct SlFmt;
+template <> struct SlFmt<UOCR_QT_Q4> {
+    static constexpr int kGroupBytes = 32, kLaneBytes = 8;             // of one row: per 64-wide group, per lane of a quad
+    static constexpr int kRowBytesH = kSlH / 2;
+};
+template <> struct SlFmt<UOCR_QT_Q8> {
+    static constexpr int kGroupBytes = 64, kLaneBytes = 16;
+    static constexpr int kRowBytesH = kSlH;
+};
+template <int QT> struct SlBlob {
+    static constexpr int kGu = 0;                                           // gate/up fragments
+    static constexpr int kGuBytes = 128 * SlFmt<QT>::kRowBytesH;
+    static constexpr int kGuSc = kGu + kGuBytes;                            // gate scales [64][20], up scales [64][20]
+    static constexpr int kGuScBytes = 2 * 64 * kSlGroups * 2;
+    static constexpr int kDn = kGuSc + kGuScBytes;                          // down fragments
+    static constexpr int kDnBytes = kSlH * SlFmt<QT>::kGroupBytes;
+    static constexpr int kDnSc = kDn + kDnBytes;                            // down scales [H]
+    static constexpr int kBytes = kDnSc + kSlH * 2;                         // Q4: 130560, Q8: 253440 (multiples of 256)
+};
+
+__device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                         uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ void imma_u8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                 : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void imma_s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                 : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// One 64-wide group of two weight rows (lo: MMA rows 0-7, hi: MMA rows 8-15; this lane holds its 16 levels of
+// each) against the group's activation bytes xb: two MMAs.  Which column sits in which k slot follows from the
+// packing; limb_column() below arranges the activation bytes to match.  Column n of the result is the dot
+// product with mantissa byte n (lanes of a quad hold columns 2t and 2t + 1).
+__device__ __forceinline__ void group_imma(int (&c)[4], const uint2 &lo, const uint2 &hi, const uint4 &xb) {   // Q4_0
+    constexpr uint32_t M = 0x0F0F0F0Fu;
+    imma_u8(c, lo.x & M, hi.x & M, lo.y & M, hi.y & M, xb.x, xb.y);                                  // low nibbles
+    imma_u8(c, (lo.x >> 4) & M, (hi.x >> 4) & M, (lo.y >> 4) & M, (hi.y >> 4) & M, xb.z, xb.w);      // high nibbles
+}
+__device__ __forceinline__ void group_imma(int (&c)[4], const uint4 &lo, const uint4 &hi, const uint4 &xb) {   // Q8_0
+    imma_s8(c, lo.x, hi.x, lo.y, hi.y, xb.x, xb.y);
+    imma_s8(c, lo.z, hi.z, lo.w, hi.w, xb.z, xb.w);
+}
+// first of the four consecutive columns (inside the group) behind activation word p = 4 t + 2 j + r of a group:
+// lane-in-quad t, MMA j of the group, B register r
+template <int QT>
+__device__ __forceinline__ int limb_column(int p) {
+    const int t = p >> 2, j = (p >> 1) & 1, r = p & 1;
+    return QT == UOCR_QT_Q4 ? 32 * j + 8 * t + 4 * r : 16 * t + 8 * j + 4 * r;
+}
+
+// Block-floating-point form of 64-wide groups of fp16 values, written by 16 consecutive lanes per group (this
+// thread: word p = idx % 16 of group idx / 16).  dst: [group][3 mantissa bytes][16 words]; scale[group] = 2^(e - 21);
+// ncorr[group] = -8 * sum(mantissas) for Q4 (0 for Q8), ncorr[ngroups_stride + group] = 0 (read by the lanes
+// that hold the high mantissa byte).
+template <int QT>
+__device__ __forceinline__ void write_limbs(const __half *src, int idx, uint32_t *dst, float *scale, float *ncorr, int zero_off) {
+    const int G = idx >> 4, p = idx & 15;
+    const uint2 raw = *reinterpret_cast<const uint2 *>(src + G * 64 + limb_column<QT>(p));
+    const float2 f01 = __half22float2(*reinterpret_cast<const __half2 *>(&raw.x));
+    const float2 f23 = __half22float2(*reinterpret_cast<const __half2 *>(&raw.y));
+    const float x[4] = {f01.x, f01.y, f23.x, f23.y};
+    float amax = fmaxf(fmaxf(fabsf(x[0]), fabsf(x[1])), fmaxf(fabsf(x[2]), fabsf(x[3])));
+#pragma unroll
+    for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o, 16));
+    // amax = 1.f * 2^e (fp16 values: e in [-24, 15]); up = 2^(21 - e), down = 2^(e - 21); a group of zeros gets 0
+    const int e = (int)(__float_as_uint(amax) >> 23) - 127;
+    const bool live = amax > 0.f && amax < INFINITY;
+    const float up = live ? __uint_as_float((uint32_t)(127 + 21 - e) << 23) : 0.f;
+    int msum = 0;
+    uint32_t w[3] = {0u, 0u, 0u};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int m = __float2int_rn(x[i] * up);          // |m| < 2^22
+        msum += m;
+        const int l0 = (int)((uint32_t)m << 24) >> 24, m1 = (m - l0) >> 8, l1 = (int)((uint32_t)m1 << 24) >> 24, l2 = (m1 - l1) >> 8;
+        w[0] |= (uint32_t)(l0 & 0xff) << (8 * i);
+        w[1] |= (uint32_t)(l1 & 0xff) << (8 * i);
+        w[2] |= (uint32_t)(l2 & 0xff) << (8 * i);
+    }
+#pragma unroll
+    for (int o = 8; o > 0; o >>= 1) msum += __shfl_xor_sync(0xffffffffu, msum, o, 16);
+#pragma unroll
+    for (int L = 0; L < 3; ++L) dst[(G * 3 + L) * 16 + p] = w[L];
+    if (p == 0) {
+        scale[G] = live ? __uint_as_float((uint32_t)(127 - 21 + e) << 23) : 0.f;
+        ncorr[G] = QT == UOCR_QT_Q4 ? -8.f * (float)msum : 0.f;
+        ncorr[zero_off + G] = 0.f;
+    }
+}
+
+__device__ __forceinline__ unsigned long long ldcg_u64(const unsigned long long *p) {
+    unsigned long long v;
+    asm volatile("ld.global.cg.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void red_add_u64(unsigned long long *p, unsigned long long v) {
+    asm volatile("red.relaxed.gpu.global.add.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ uint32_t cluster_size() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r));
+    return r;
+}
+// address of the same shared-memory variable in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t cluster_addr(const void *local, uint32_t rank) {
+    uint32_t a;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(a) : "r"(smem_u32(local)), "r"(rank));
+    return a;
+}
+__device__ __forceinline__ float ld_cluster_f32(uint32_t addr) {
+    float v;
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");
+    return v;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t remote_bar) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(remote_bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t *bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+
+// Shared-memory layout (byte offsets); the layer table comes last.
+template <int QT> struct SlSmem {
+    static constexpr int kW = 0;                                        // gate/up fragments as in the blob
+    static constexpr int kSc = kW + SlBlob<QT>::kGuBytes;               // gate scales [64][20], up scales [64][20] (fp16)
+    static constexpr int kX = kSc + SlBlob<QT>::kGuScBytes;             // activations, fp16 natural order
+    static constexpr int kXf = kX + kSlH * 2;                           // activation mantissa bytes [20][3][16 words]
+    static constexpr int kXs = kXf + kSlGroups * 3 * 16 * 4;            // [20] group scales, then [2][20] negated corrections
+    static constexpr int kGu = kXs + 256;                               // [2][128] partial gate / up sums of the two group parities
+    static constexpr int kMid = kGu + 2 * 128 * 4;                      // [64] fp16 SwiGLU products
+    static constexpr int kMidf = kMid + 128;                            // their mantissa bytes [3][16 words], scale, corrections
+    static constexpr int kPart = kMidf + 256;                           // [H] this CTA's partial outputs (read by its cluster)
+    static constexpr int kRp = kPart + kSlH * 4;                        // [4][64] partial router logits
+    static constexpr int kLogits = kRp + 4 * 64 * 4;                    // [64]
+    static constexpr int kProbs = kLogits + 256;                        // [64]
+    static constexpr int kIds = kProbs + 256;                           // ids [8], weights [8], flags [2], mid correction
+    static constexpr int kBars = kIds + 128;                            // kSlChunks copy barriers, scale barrier, cluster barrier
+    static constexpr int kLayers = kBars + 8 * 8;                       // DLayer table
+    static constexpr int kTotal = kLayers + kSlMaxLayers * (int)sizeof(DLayer);
+};
+
+// ---------------------------------------------------------------- the kernel
+template <int QT>
+__global__ void __launch_bounds__(kSlThreads, 1) decode_sliced_kernel(SlicedParams prm) {
+    using Bl = SlBlob<QT>;
+    using Sm = SlSmem<QT>;
+    constexpr int H = kSlH, K = kSlK, E = kSlE;
+    constexpr int kChunkBytes = Bl::kGuBytes / kSlChunks;
+
+    extern __shared__ __align__(128) uint8_t smem[];
+    const uint4 *s_w4 = reinterpret_cast<const uint4 *>(smem + Sm::kW);
+    __half *s_sc = reinterpret_cast<__half *>(smem + Sm::kSc);
+    __half *s_x = reinterpret_cast<__half *>(smem + Sm::kX);
+    uint32_t *s_xf = reinterpret_cast<uint32_t *>(smem + Sm::kXf);
+    float *s_xs = reinterpret_cast<float *>(smem + Sm::kXs);             // [20] scales
+    float *s_ncorr = s_xs + kSlGroups;                                   // [2][20]: real corrections, zeros
+    float *s_gu = reinterpret_cast<float *>(smem + Sm::kGu);
+    __half *s_mid = reinterpret_cast<__half *>(smem + Sm::kMid);
+    uint32_t *s_midf = reinterpret_cast<uint32_t *>(smem + Sm::kMidf);   // [3][16 words]
+    float *s_mscale = reinterpret_cast<float *>(s_midf + 48);            // scale, then corrections [2]
+    float *s_part = reinterpret_cast<float *>(smem + Sm::kPart);
+    float *s_rp = reinterpret_cast<float *>(smem + Sm::kRp);
+    float *s_logits = reinterpret_cast<float *>(smem + Sm::kLogits);
+    float *s_probs = reinterpret_cast<float *>(smem + Sm::kProbs);
+    uint32_t *s_ids = reinterpret_cast<uint32_t *>(smem + Sm::kIds);
+    float *s_wts = reinterpret_cast<float *>(s_ids + 8);
+    int *s_flag = reinterpret_cast<int *>(s_ids + 16);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + Sm::kBars);     // [0, kSlChunks) copies, then scales, then cluster
+    uint64_t *sc_bar = bars + kSlChunks, *cl_bar = bars + kSlChunks + 1;
+    DLayer *s_layers = reinterpret_cast<DLayer *>(smem + Sm::kLayers);
+    __shared__ uint64_t s_tab[UOCR_EXPF_N];
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int g = lane >> 2, t = lane & 3;                              // MMA row group / lane in quad
+    const uint32_t G = gridDim.x, cta = blockIdx.x;
+    const bool routed = cta < (uint32_t)kSlRouted;
+    const uint32_t slot = routed ? cta / kSlRoutedPerSlot : (uint32_t)K;
+    const uint32_t fg = routed ? cta % kSlRoutedPerSlot : cta - kSlRouted;     // 64-wide slice of F (of S)
+    unsigned long long bar_target = prm.bar_base;
+    uint32_t *status = prm.status;
+    const uint32_t crank = cluster_rank(), csize = cluster_size();
+    const int cols_per_cta = H / (int)csize;                           // columns of the cluster's sum this CTA sends on
+
+    if (tid < UOCR_EXPF_N) s_tab[tid] = c_exp_tab[tid];
+    if (tid == 0) {
+        s_flag[0] = 1; s_flag[1] = 0;
+        for (int i = 0; i <= kSlChunks; ++i) mbar_init(&bars[i], 1);
+        mbar_init(cl_bar, csize);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    // every CTA of the cluster has initialised its barriers before any peer arrives on them
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+    {
+        const uint32_t words = prm.count * (uint32_t)(sizeof(DLayer) / 4);
+        const uint32_t *src = reinterpret_cast<const uint32_t *>(prm.layers + prm.first);
+        uint32_t *dst = reinterpret_cast<uint32_t *>(s_layers);
+        for (uint32_t i = tid; i < words; i += kSlThreads) dst[i] = src[i];
+    }
+    // the first layer's input, and its residual in registers
+    for (int h = tid; h < H; h += kSlThreads) s_x[h] = prm.hidden_in[h];
+    float res0[3] = {0.f, 0.f, 0.f};
+    if (prm.residual0 != nullptr) {
+#pragma unroll
+        for (int i = 0; i < 3; ++i)
+            if (tid + i * kSlThreads < H) res0[i] = __half2float(prm.residual0[tid + i * kSlThreads]);
+    }
+    __syncthreads();
+
+    // ---- helpers --------------------------------------------------------------------------------------
+    // fragments and offset corrections of the activations in s_x
+    auto build_x_frags = [&]() {
+        if (tid < kSlGroups * 16) write_limbs<QT>(s_x, tid, s_xf, s_xs, s_ncorr, kSlGroups);     // 16 lanes per group
+    };
+    // what each lane does with its two result columns (2t, 2t + 1) of a group: columns 0 and 1 (t = 0) are the low
+    // and middle mantissa bytes, column 2 (t = 1) the high byte; the other columns are unused
+    const int limb_mul = t == 0 ? 256 : 0;                              // integer: c[col 2t] + limb_mul * c[col 2t + 1]
+    const float limb_f = t == 0 ? 1.f : (t == 1 ? 65536.f : 0.f);
+    const int corr_row = t == 0 ? 0 : 1;                                // lanes other than t = 0 read zeros as correction
+    const int limb_of_lane = g < 2 ? g : 2;                             // mantissa byte this lane feeds in as MMA column g
+    // Register file shared by two prefetches that are never live together: the router matrix as MMA A
+    // fragments (routed CTAs, requested while waiting at the barrier, used right after it) and this warp's
+    // 5 blocks of 16 `down` rows, the unit's 64 columns of each.
+    uint4 rw[10][2];
+    __half dslo[kSlBlocksPerWarp], dshi[kSlBlocksPerWarp];
+    // everything of one unit: bulk copies of the gate/up fragments (chunk c completes barrier c) and scales into
+    // shared memory, plain loads of the down fragments and scales into registers
+    auto fetch_unit = [&](const uint8_t *blob) {
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        if (tid < kSlChunks) {
+            mbar_expect_tx(&bars[tid], kChunkBytes);
+            bulk_g2s(smem + Sm::kW + tid * kChunkBytes, blob + Bl::kGu + (size_t)tid * kChunkBytes, kChunkBytes, &bars[tid]);
+        } else if (tid == kSlChunks) {
+            mbar_expect_tx(sc_bar, Bl::kGuScBytes);
+            bulk_g2s(s_sc, blob + Bl::kGuSc, Bl::kGuScBytes, sc_bar);
+        }
+        const uint4 *dn = reinterpret_cast<const uint4 *>(blob + Bl::kDn);
+        const __half *dsc = reinterpret_cast<const __half *>(blob + Bl::kDnSc);
+#pragma unroll
+        for (int bi = 0; bi < kSlBlocksPerWarp; ++bi) {
+            const int blk = warp + 16 * bi;
+            if (QT == UOCR_QT_Q8) {
+                rw[bi][0] = __ldg(dn + (blk * 2) * 32 + lane);
+                rw[bi][1] = __ldg(dn + (blk * 2 + 1) * 32 + lane);
+            } else {
+                rw[bi][0] = __ldg(dn + blk * 32 + lane);          // rows g: .x .y, rows g + 8: .z .w
+            }
+            dslo[bi] = dsc[16 * blk + g];
+            dshi[bi] = dsc[16 * blk + 8 + g];
+        }
+    };
+    // router matrix [64][H] fp16 as MMA A fragments: warp (mb, kq) holds rows 16 mb .. +15, columns 320 kq .. +319
+    const int mb = warp & 3, kq = warp >> 2;
+    auto load_router = [&](const DLayer &L) {
+        const __half *r0 = L.router + (size_t)(16 * mb + g) * H + kq * 320 + 8 * t;
+#pragma unroll
+        for (int i = 0; i < 10; ++i) {
+            rw[i][0] = __ldg(reinterpret_cast<const uint4 *>(r0 + i * 32));
+            rw[i][1] = __ldg(reinterpret_cast<const uint4 *>(r0 + 8 * H + i * 32));
+        }
+    };
+
+#define UOCR_SL_TRACE(point)                                                                              \
+    do {                                                                                                  \
+        if (prm.trace != nullptr && tid == 0)                                                             \
+            prm.trace[((size_t)cta * prm.count + li) * kSlTracePoints + (point)] = clock64();             \
+    } while (0)
+
+    // ---- prologue: everything the first layer can fetch before its activations are arranged
+    uint32_t copy_phase = 0;
+    if (routed) load_router(s_layers[0]);
+    else fetch_unit(s_layers[0].dec_units + (size_t)(kSlE * kSlRoutedPerSlot + fg) * Bl::kBytes);
+    build_x_frags();
+    __syncthreads();
+
+    for (uint32_t li = 0; li < prm.count; ++li) {
+        const DLayer &L = s_layers[li];
+        const bool last = li + 1 == prm.count;
+        unsigned long long *acc = prm.acc + (size_t)((prm.acc_base + li) % kSlAccBuffers) * H;
+        UOCR_SL_TRACE(0);     // activations of this layer arranged
+        bool valid = true;
+        float weight = 1.0f;
+
+        if (routed) {
+            // ---- router: logits of all experts, evaluated by every routed CTA for itself
+            if (li == 0 && prm.injected != nullptr) {
+                if (tid < E) s_logits[tid] = prm.injected[tid] + (L.bias ? L.bias[tid] : 0.f);
+            } else {
+                float c[4] = {0.f, 0.f, 0.f, 0.f}, d[4] = {0.f, 0.f, 0.f, 0.f};      // two chains of MMAs
+                const __half *xq = s_x + kq * 320 + 8 * t;
+#pragma unroll
+                for (int i = 0; i < 10; ++i) {
+                    const uint4 xv = *reinterpret_cast<const uint4 *>(xq + i * 32);
+                    mma16816(c, rw[i][0].x, rw[i][1].x, rw[i][0].y, rw[i][1].y, xv.x, xv.y);
+                    mma16816(d, rw[i][0].z, rw[i][1].z, rw[i][0].w, rw[i][1].w, xv.z, xv.w);
+                }
+                if (t == 0) { s_rp[kq * 64 + 16 * mb + g] = c[0] + d[0]; s_rp[kq * 64 + 16 * mb + 8 + g] = c[2] + d[2]; }
+                __syncthreads();
+                if (tid < E) {
+                    const float v = ((s_rp[tid] + s_rp[64 + tid]) + s_rp[128 + tid]) + s_rp[192 + tid];
+                    s_logits[tid] = L.bias ? v + L.bias[tid] : v;
+                }
+            }
+            __syncthreads();
+            if (warp == 0) {
+                const bool dbg = cta == 0 && li == 0;
+                const bool bad = route_row_warp(s_logits, s_probs, E, K, L.scaling, lane, s_tab, dbg ? prm.dbg_logits : nullptr,
+                                                dbg ? prm.dbg_probs : nullptr, s_ids, s_wts);
+                if (bad && lane == 0 && cta == 0) atomicOr(status, kStatusRouter);
+            }
+            __syncthreads();
+            UOCR_SL_TRACE(1);     // routing
+            if (cta == 0 && last && tid < K) { prm.ids_out[tid] = s_ids[tid]; prm.wts_out[tid] = s_wts[tid]; }
+            const uint32_t ex = s_ids[slot];
+            valid = ex < (uint32_t)E;         // an invalid expert id contributes zeros
+            weight = s_wts[slot];
+            if (valid) fetch_unit(L.dec_units + (size_t)(ex * kSlRoutedPerSlot + fg) * Bl::kBytes);
+        } else {
+            UOCR_SL_TRACE(1);
+        }
+        UOCR_SL_TRACE(2);         // weight fetches issued
+
+        if (valid) {
+            // ---- gate / up: warp (rb, kh) multiplies rows 8 rb .. +7 of both matrices with the groups of parity kh,
+            // chunk by chunk as the copies land
+            const int rb = warp & 7, kh = warp >> 3;
+            bool got = mbar_wait(sc_bar, copy_phase, status, s_flag);
+            float sg = 0.f, su = 0.f;
+            {
+                const __half *scg = s_sc + (8 * rb + g) * kSlGroups;
+                const __half *scu = scg + 64 * kSlGroups;
+                // straight-line code: chunk c holds groups 4c .. 4c + 3, this warp takes the two of its parity
+#pragma unroll
+                for (int ch = 0; ch < kSlChunks; ++ch) {
+                    got = mbar_wait(&bars[ch], copy_phase, status, s_flag) && got;
+                    if (ch == 0) UOCR_SL_TRACE(3);     // first chunk is in shared memory
+#pragma unroll
+                    for (int q = 0; q < 2; ++q) {
+                        const int Gi = 4 * ch + 2 * q + kh;
+                        const uint4 xb = *reinterpret_cast<const uint4 *>(s_xf + ((Gi * 3 + limb_of_lane) * 4 + t) * 4);
+                        int c[4] = {0, 0, 0, 0};
+                        if (QT == UOCR_QT_Q8) {
+                            const uint4 a = s_w4[((Gi * 8 + rb) * 2) * 32 + lane], b = s_w4[((Gi * 8 + rb) * 2 + 1) * 32 + lane];
+                            group_imma(c, a, b, xb);
+                        } else {
+                            const uint4 v = s_w4[(Gi * 8 + rb) * 32 + lane];       // gate: .x .y, up: .z .w
+                            group_imma(c, make_uint2(v.x, v.y), make_uint2(v.z, v.w), xb);
+                        }
+                        const float xs = s_xs[Gi], nc = s_ncorr[corr_row * kSlGroups + Gi];
+                        sg = fmaf(fmaf((float)(c[1] * limb_mul + c[0]), limb_f, nc), __half2float(scg[Gi]) * xs, sg);
+                        su = fmaf(fmaf((float)(c[3] * limb_mul + c[2]), limb_f, nc), __half2float(scu[Gi]) * xs, su);
+                    }
+                }
+                if (!got) { sg = 0.f; su = 0.f; }
+            }
+            // the lanes of a quad hold the parts of different mantissa bytes
+            sg += __shfl_xor_sync(0xffffffffu, sg, 1); su += __shfl_xor_sync(0xffffffffu, su, 1);
+            if (t == 0) { s_gu[kh * 128 + 8 * rb + g] = sg; s_gu[kh * 128 + 64 + 8 * rb + g] = su; }
+            __syncthreads();
+            if (tid < 64) {
+                const float gate = s_gu[tid] + s_gu[128 + tid], up = s_gu[64 + tid] + s_gu[192 + tid];
+                s_mid[tid] = __float2half_rn(silu_f32(gate) * up);
+            }
+            __syncthreads();
+            if (warp == 0) write_limbs<QT>(s_mid, lane & 15, s_midf, s_mscale, s_mscale + 1, 1);    // both half-warps write the same
+            __syncthreads();
+            copy_phase ^= 1u;
+            UOCR_SL_TRACE(4);     // SwiGLU products of the slice
+
+            // ---- down: H rows x the slice's 64 columns, straight from registers; partial outputs to shared memory
+            {
+                const uint4 mbf = *reinterpret_cast<const uint4 *>(s_midf + (limb_of_lane * 4 + t) * 4);
+                const float ms = s_mscale[0] * weight, nc = s_mscale[1 + corr_row];
+#pragma unroll
+                for (int bi = 0; bi < kSlBlocksPerWarp; ++bi) {
+                    int c[4] = {0, 0, 0, 0};
+                    if (QT == UOCR_QT_Q8) group_imma(c, rw[bi][0], rw[bi][1], mbf);
+                    else group_imma(c, make_uint2(rw[bi][0].x, rw[bi][0].y), make_uint2(rw[bi][0].z, rw[bi][0].w), mbf);
+                    float v0 = fmaf((float)(c[1] * limb_mul + c[0]), limb_f, nc) * (__half2float(dslo[bi]) * ms);
+                    float v1 = fmaf((float)(c[3] * limb_mul + c[2]), limb_f, nc) * (__half2float(dshi[bi]) * ms);
+                    v0 += __shfl_xor_sync(0xffffffffu, v0, 1);
+                    v1 += __shfl_xor_sync(0xffffffffu, v1, 1);
+                    if (t == 0) {
+                        const uint32_t r0 = 16u * (warp + 16 * bi) + g;
+                        s_part[r0] = v0;
+                        s_part[r0 + 8] = v1;
+                    }
+                }
+            }
+        } else {
+            UOCR_SL_TRACE(3);
+            UOCR_SL_TRACE(4);
+            for (int h = tid; h < H; h += kSlThreads) s_part[h] = 0.f;
+        }
+        UOCR_SL_TRACE(5);         // partial outputs of this CTA
+        // ---- sum over the cluster (fixed order), then one integer reduction per column into the accumulator
+        __syncthreads();
+        if ((uint32_t)tid < csize) mbar_arrive_cluster(cluster_addr(cl_bar, (uint32_t)tid));
+        if (tid == 0) {
+            int ok = 1;
+            if (!mbar_try_wait_cluster(cl_bar, li & 1u)) {
+                const long long t0 = clock64();
+                while (!mbar_try_wait_cluster(cl_bar, li & 1u)) {
+                    if (clock64() - t0 > kSpinLimit) { atomicOr(status, kStatusBarrier); ok = 0; break; }
+                }
+            }
+            s_flag[0] = ok;
+        }
+        __syncthreads();
+        if (s_flag[0] != 0 && tid < cols_per_cta) {
+            const int h = (int)crank * cols_per_cta + tid;
+            float pv[8];
+#pragma unroll
+            for (uint32_t r = 0; r < 8; ++r) pv[r] = r < csize ? ld_cluster_f32(cluster_addr(s_part + h, r)) : 0.f;
+            float v = 0.f;
+#pragma unroll
+            for (uint32_t r = 0; r < 8; ++r) v += pv[r];
+            if (!(fabsf(v) < 1.0e9f)) atomicOr(status, kStatusRange);      // also true for NaN
+            red_add_u64(acc + h, (unsigned long long)__float2ll_rn(v * 4294967296.f));
+        }
+        UOCR_SL_TRACE(6);         // cluster sum sent
+
+        // ---- barrier; while it is pending, the work for later layers that does not need this layer's result
+        grid_arrive(prm.bar);
+        if (cta == G - 1) {       // clear the accumulator that the layer after next will add to
+            unsigned long long *z = prm.acc + (size_t)((prm.acc_base + li + 2) % kSlAccBuffers) * H;
+            for (int h = tid; h < H; h += kSlThreads) z[h] = 0ull;
+        }
+        if (!last) {
+            if (routed) load_router(s_layers[li + 1]);
+            else fetch_unit(s_layers[li + 1].dec_units + (size_t)(kSlE * kSlRoutedPerSlot + fg) * Bl::kBytes);
+        }
+        bar_target += G;
+        if (!grid_wait(prm.bar, bar_target, status, s_flag)) return;
+        UOCR_SL_TRACE(7);         // barrier passed
+
+        // ---- the layer's output = next layer's input: accumulator + residual, rounded to fp16
+#pragma unroll
+        for (int i = 0; i < 3; ++i) {
+            const int h = tid + i * kSlThreads;
+            if (h < H) {
+                float v = (float)(long long)ldcg_u64(acc + h) * (1.0f / 4294967296.f);
+                if (li == 0) v += res0[i];
+                else if (prm.chain_residual) v += __half2float(s_x[h]);
+                s_x[h] = __float2half_rn(v);
+            }
+        }
+        __syncthreads();
+        if (last) {
+            if (cta == 0)
+                for (int h = tid; h < H; h += kSlThreads) prm.out[h] = s_x[h];
+        } else {
+            build_x_frags();
+            __syncthreads();
+        }
+    }
+#undef UOCR_SL_TRACE
+}
+
+// ---------------------------------------------------------------- building the unit blobs
+struct RepackSrc {
+    const uint8_t *gate_w, *up_w, *down_w;      // first matrix of each kind (file layout)
+    const __half *gate_s, *up_s, *down_s;
+    uint64_t mat_stride_w;                      // bytes / values from one expert to the next (unused for one matrix set)
+    uint64_t mat_stride_s;
+    uint32_t inter;                             // F or S: rows of gate / up, columns of down
+};
+
+// One CTA per unit: gathers the unit's pieces from the file layout into the blob, 16 bytes at a time.
+template <int QT>
+__global__ void repack_units_kernel(RepackSrc src, uint8_t *out) {
+    using Fm = SlFmt<QT>;
+    using Bl = SlBlob<QT>;
+    const uint32_t per = src.inter / 64, unit = blockIdx.x, m = unit / per, fg = unit % per;
+    const uint8_t *gw = src.gate_w + (size_t)m * src.mat_stride_w + (size_t)fg * 64 * Fm::kRowBytesH;
+    const uint8_t *uw = src.up_w + (size_t)m * src.mat_stride_w + (size_t)fg * 64 * Fm::kRowBytesH;
+    const uint8_t *dw = src.down_w + (size_t)m * src.mat_stride_w + (size_t)fg * Fm::kGroupBytes;
+    const __half *gs = src.gate_s + (size_t)m * src.mat_stride_s + (size_t)fg * 64 * kSlGroups;
+    const __half *us = src.up_s + (size_t)m * src.mat_stride_s + (size_t)fg * 64 * kSlGroups;
+    const __half *ds = src.down_s + (size_t)m * src.mat_stride_s + fg;
+    const uint32_t down_row_bytes = QT == UOCR_QT_Q4 ? src.inter / 2 : src.inter;
+    uint8_t *blob = out + (size_t)unit * Bl::kBytes;
+    uint4 *gu = reinterpret_cast<uint4 *>(blob + Bl::kGu), *dn = reinterpret_cast<uint4 *>(blob + Bl::kDn);
+    __half *gusc = reinterpret_cast<__half *>(blob + Bl::kGuSc), *dnsc = reinterpret_cast<__half *>(blob + Bl::kDnSc);
+
+    for (uint32_t p = threadIdx.x; p < (uint32_t)Bl::kGuBytes / 16; p += blockDim.x) {
+        const uint32_t lane = p & 31, g = lane >> 2, t = lane & 3;
+        if (QT == UOCR_QT_Q4) {           // [group][row block][lane]: 8 bytes of the gate row, 8 of the up row
+            const uint32_t rb = (p >> 5) & 7, Gi = p >> 8;
+            const size_t off = (size_t)(8 * rb + g) * Fm::kRowBytesH + Gi * 32 + 8 * t;
+            const uint2 a = *reinterpret_cast<const uint2 *>(gw + off), b = *reinterpret_cast<const uint2 *>(uw + off);
+            gu[p] = make_uint4(a.x, a.y, b.x, b.y);
+        } else {                          // [group][row block][gate, up][lane]: 16 bytes of the row
+            const uint32_t mm = (p >> 5) & 1, rb = (p >> 6) & 7, Gi = p >> 9;
+            const size_t off = (size_t)(8 * rb + g) * Fm::kRowBytesH + Gi * 64 + 16 * t;
+            gu[p] = *reinterpret_cast<const uint4 *>((mm ? uw : gw) + off);
+        }
+    }
+    for (uint32_t i = threadIdx.x; i < 64u * kSlGroups; i += blockDim.x) { gusc[i] = gs[i]; gusc[64 * kSlGroups + i] = us[i]; }
+    for (uint32_t p = threadIdx.x; p < (uint32_t)Bl::kDnBytes / 16; p += blockDim.x) {
+        const uint32_t lane = p & 31, g = lane >> 2, t = lane & 3;
+        if (QT == UOCR_QT_Q4) {           // [row block][lane]: 8 bytes of row g, 8 of row g + 8
+            const uint32_t blk = p >> 5;
+            const uint8_t *r0 = dw + (size_t)(16 * blk + g) * down_row_bytes + 8 * t;
+            const uint2 a = *reinterpret_cast<const uint2 *>(r0), b = *reinterpret_cast<const uint2 *>(r0 + (size_t)8 * down_row_bytes);
+            dn[p] = make_uint4(a.x, a.y, b.x, b.y);
+        } else {                          // [row block][rows g, rows g + 8][lane]: 16 bytes of the row
+            const uint32_t hi = (p >> 5) & 1, blk = p >> 6;
+            dn[p] = *reinterpret_cast<const uint4 *>(dw + (size_t)(16 * blk + 8 * hi + g) * down_row_bytes + 16 * t);
+        }
+    }
+    for (uint32_t h = threadIdx.x; h < (uint32_t)kSlH; h += blockDim.x) dnsc[h] = ds[(size_t)h * per];
+}
+
+// ---------------------------------------------------------------- host side
+static int g_sliced_cluster[64] = {0};      // cluster size the kernel is launched with on a device, 0: cannot run there
+
+// The shapes and formats this kernel is built for (the model's).
+bool decode_sliced_layer_ok(const DLayer &L) {
+    const bool q = L.expert_qtype == UOCR_QT_Q4 || L.expert_qtype == UOCR_QT_Q8;
+    return q && L.shared_gate.qtype == L.expert_qtype && L.shared_up.qtype == L.expert_qtype &&
+           L.shared_down.qtype == L.expert_qtype && L.H == (uint32_t)kSlH && L.F == (uint32_t)kSlF &&
+           L.S == (uint32_t)kSlS && L.K == (uint32_t)kSlK && L.E == (uint32_t)kSlE;
+}
+
+size_t decode_units_bytes(const DLayer &L) {
+    const size_t units = (size_t)kSlE * kSlRoutedPerSlot + kSlS / 64;
+    return units * (L.expert_qtype == UOCR_QT_Q4 ? SlBlob<UOCR_QT_Q4>::kBytes : SlBlob<UOCR_QT_Q8>::kBytes);
+}
+
+// Fills `out` (decode_units_bytes(L) bytes of device memory) from the layer's file-layout weights.
+cudaError_t build_decode_units(const DLayer &L, uint8_t *out, cudaStream_t st) {
+    RepackSrc ex{}, sh{};
+    ex.gate_w = L.expert_w; ex.up_w = L.expert_w + L.up_offset_bytes; ex.down_w = L.expert_w + L.down_offset_bytes;
+    ex.gate_s = L.expert_s; ex.up_s = L.expert_s + L.up_scale_offset; ex.down_s = L.expert_s + L.down_scale_offset;
+    ex.mat_stride_w = L.expert_stride_bytes; ex.mat_stride_s = L.expert_scale_stride; ex.inter = L.F;
+    sh.gate_w = L.shared_gate.w; sh.up_w = L.shared_up.w; sh.down_w = L.shared_down.w;
+    sh.gate_s = L.shared_gate.s; sh.up_s = L.shared_up.s; sh.down_s = L.shared_down.s;
+    sh.inter = L.S;
+    const uint32_t routed_units = kSlE * kSlRoutedPerSlot, shared_units = kSlS / 64;
+    if (L.expert_qtype == UOCR_QT_Q4) {
+        repack_units_kernel<UOCR_QT_Q4><<<routed_units, 256, 0, st>>>(ex, out);
+        repack_units_kernel<UOCR_QT_Q4><<<shared_units, 256, 0, st>>>(sh, out + (size_t)routed_units * SlBlob<UOCR_QT_Q4>::kBytes);
+    } else {
+        repack_units_kernel<UOCR_QT_Q8><<<routed_units, 256, 0, st>>>(ex, out);
+        repack_units_kernel<UOCR_QT_Q8><<<shared_units, 256, 0, st>>>(sh, out + (size_t)routed_units * SlBlob<UOCR_QT_Q8>::kBytes);
+    }
+    return cudaGetLastError();
+}
+
+template <int QT>
+static void launch_config(cudaLaunchConfig_t *cfg, cudaLaunchAttribute *attrs, int cluster, cudaStream_t st) {
+    *cfg = cudaLaunchConfig_t{};
+    cfg->gridDim = dim3(kSlUnits); cfg->blockDim = dim3(kSlThreads);
+    cfg->dynamicSmemBytes = SlSmem<QT>::kTotal; cfg->stream = st;
+    attrs[0].id = cudaLaunchAttributeCooperative; attrs[0].val.cooperative = 1;
+    attrs[1].id = cudaLaunchAttributeClusterDimension;
+    attrs[1].val.clusterDim.x = (unsigned)cluster; attrs[1].val.clusterDim.y = 1; attrs[1].val.clusterDim.z = 1;
+    cfg->attrs = attrs; cfg->numAttrs = 2;
+}
+
+// largest cluster size (at most `limit`: 8, 4, 2 or 1) with which all CTAs are resident at once
+template <int QT>
+static cudaError_t prepare_sliced(int limit, int *cluster) {
+    auto kern = decode_sliced_kernel<QT>;
+    cudaError_t err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SlSmem<QT>::kTotal);
+    if (err != cudaSuccess) return err;
+    *cluster = 0;
+    for (int cs = limit; cs >= 1 && *cluster == 0; cs >>= 1) {
+        cudaLaunchConfig_t cfg;
+        cudaLaunchAttribute attrs[2];
+        launch_config<QT>(&cfg, attrs, cs, nullptr);
+        int clusters = 0;
+        if (cudaOccupancyMaxActiveClusters(&clusters, kern, &cfg) == cudaSuccess && clusters * cs >= kSlUnits) *cluster = cs;
+        else (void)cudaGetLastError();
+    }
+    return cudaSuccess;
+}
+
+// cluster_limit: 8, 4, 2 or 1
+cudaError_t init_decode_sliced_kernels(int cluster_limit) {
+    int dev = 0;
+    cudaError_t err = cudaGetDevice(&dev);
+    if (err != cudaSuccess) return err;
+    int c4 = 0, c8 = 0;
+    if ((err = prepare_sliced<UOCR_QT_Q4>(cluster_limit, &c4)) != cudaSuccess) return err;
+    if ((err = prepare_sliced<UOCR_QT_Q8>(cluster_limit, &c8)) != cudaSuccess) return err;
+    if (dev < 64) g_sliced_cluster[dev] = c4 < c8 ? c4 : c8;
+    return cudaSuccess;
+}
+
+size_t decode_sliced_acc_bytes() { return (size_t)kSlAccBuffers * kSlH * sizeof(unsigned long long); }
+
+bool decode_sliced_supported(const DLayer *layers, uint32_t first, uint32_t count) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev >= 64 || g_sliced_cluster[dev] == 0) return false;
+    if (count == 0 || count > (uint32_t)kSlMaxLayers) return false;
+    for (uint32_t i = 0; i < count; ++i) {
+        const DLayer &L = layers[first + i];
+        if (!decode_sliced_layer_ok(L) || L.dec_units == nullptr || L.expert_qtype != layers[first].expert_qtype) return false;
+    }
+    return true;
+}
+
+// acc: decode_sliced_acc_bytes() of device memory, zero before the first launch; *acc_base and *bar_base carry the
+// accumulator rotation and the barrier count from launch to launch (reset both, and clear acc, after a failed launch).
+cudaError_t launch_decode_sliced(const DLayer *h_layers, const DLayer *d_layers, uint32_t first, uint32_t count,
+                                 const __half *hidden, const __half *residual0, int chain_residual, const float *injected,
+                                 __half *out, unsigned long long *acc, uint32_t *acc_base, unsigned long long *bar,
+                                 unsigned long long *bar_base, uint32_t *status, float *dbg_logits, float *dbg_probs,
+                                 uint32_t *ids_out, float *wts_out, unsigned long long *trace, cudaStream_t st,
+                                 uint64_t *launches) {
+    int dev = 0;
+    cudaError_t err = cudaGetDevice(&dev);
+    if (err != cudaSuccess) return err;
+    if (dev >= 64 || g_sliced_cluster[dev] == 0) return cudaErrorNotSupported;
+    SlicedParams prm{};
+    prm.layers = d_layers; prm.first = first; prm.count = count;
+    prm.hidden_in = hidden; prm.residual0 = residual0; prm.chain_residual = chain_residual;
+    prm.injected = injected; prm.out = out; prm.acc = acc; prm.acc_base = *acc_base;
+    prm.bar = bar; prm.bar_base = *bar_base; prm.status = status;
+    prm.dbg_logits = dbg_logits; prm.dbg_probs = dbg_probs; prm.ids_out = ids_out; prm.wts_out = wts_out; prm.trace = trace;
+    cudaLaunchConfig_t cfg;
+    cudaLaunchAttribute attrs[2];
+    if (h_layers[first].expert_qtype == UOCR_QT_Q4) {
+        launch_config<UOCR_QT_Q4>(&cfg, attrs, g_sliced_cluster[dev], st);
+        err = cudaLaunchKernelEx(&cfg, decode_sliced_kernel<UOCR_QT_Q4>, prm);
+    } else {
+        launch_config<UOCR_QT_Q8>(&cfg, attrs, g_sliced_cluster[dev], st);
+        err = cudaLaunchKernelEx(&cfg, decode_sliced_kernel<UOCR_QT_Q8>, prm);
+    }
+    if (err != cudaSuccess) return err;
+    *bar_base += (unsigned long long)kSlUnits * count;       // one barrier per layer
+    *acc_base = (*acc_base + count) % kSlAccBuffers;
+    ++*launches;
+    return cudaSuccess;
+}
+
+}  // namespace uocr

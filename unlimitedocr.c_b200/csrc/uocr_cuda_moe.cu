@@ -16,6 +16,7 @@ namespace uocr {
 cudaError_t init_router_kernels();
 cudaError_t init_small_batch_kernels();
 cudaError_t init_decode_kernels();
+cudaError_t init_decode_sliced_kernels(int cluster_limit);
 cudaError_t init_gemm_kernels();
 bool gemm_path_supported(const DLayer &L);
 struct GemmScratch {
@@ -36,6 +37,17 @@ cudaError_t launch_gemm_combine(const DLayer &L, const Scratch &S, const GemmScr
                                 const __half *residual, uint32_t n, __half *out, cudaStream_t st, uint64_t *launches);
 int decode_grid_size();
 bool decode_supported(const DLayer *layers, uint32_t first, uint32_t count);
+bool decode_sliced_layer_ok(const DLayer &L);
+size_t decode_units_bytes(const DLayer &L);
+cudaError_t build_decode_units(const DLayer &L, uint8_t *out, cudaStream_t st);
+size_t decode_sliced_acc_bytes();
+bool decode_sliced_supported(const DLayer *layers, uint32_t first, uint32_t count);
+cudaError_t launch_decode_sliced(const DLayer *h_layers, const DLayer *d_layers, uint32_t first, uint32_t count,
+                                 const __half *hidden, const __half *residual0, int chain_residual, const float *injected,
+                                 __half *out, unsigned long long *acc, uint32_t *acc_base, unsigned long long *bar,
+                                 unsigned long long *bar_base, uint32_t *status, float *dbg_logits, float *dbg_probs,
+                                 uint32_t *ids_out, float *wts_out, unsigned long long *trace, cudaStream_t st,
+                                 uint64_t *launches);
 cudaError_t launch_decode_stack(const DLayer *h_layers, const DLayer *d_layers, uint32_t first, uint32_t count,
                                 const __half *hidden, const __half *residual0, int chain_residual,
                                 const float *injected, __half *out, __half *hbuf0, __half *hbuf1, __half *mid,
@@ -60,7 +72,10 @@ struct uocr_cuda_context {
     DLayer *d_layers = nullptr;        // device copy of `layers`
     bool fused_decode = true;          // single-token calls use the persistent decode kernel when it fits
     uint32_t gemm_min_tokens = 5;      // calls with at least this many tokens take the tensor-core path
+    bool sliced_decode = true;         // ... in its one-barrier-per-layer form when the shapes allow it
     unsigned long long bar_base = 0;   // value the decode kernel's barrier counter has reached
+    uint32_t acc_base = 0;             // accumulator buffer the next sliced decode launch starts with
+    size_t status_bytes = 0;           // status word, barrier counter and the decode accumulators
     unsigned long long *decode_trace = nullptr;   // optional device buffer for per-phase clock stamps
     std::vector<void *> weight_allocs;
     uint64_t weight_bytes = 0;
@@ -124,6 +139,13 @@ extern "C" int uocr_cuda_device_count(void) {
     return cudaGetDeviceCount(&n) == cudaSuccess ? n : 0;
 }
 
+// UOCR_CUDA_DECODE_CLUSTER = 1, 2, 4 or 8 (default 8): CTAs per thread-block cluster of the one-barrier decode kernel
+static int decode_cluster_limit() {
+    const char *v = getenv("UOCR_CUDA_DECODE_CLUSTER");
+    const int c = v ? atoi(v) : 8;
+    return (c == 1 || c == 2 || c == 4 || c == 8) ? c : 8;
+}
+
 extern "C" uocr_cuda_context *uocr_cuda_context_create(const char *resource_path, char *error, size_t error_size) {
     (void)resource_path;
     int n = 0;
@@ -148,13 +170,14 @@ extern "C" uocr_cuda_context *uocr_cuda_context_create(const char *resource_path
         return nullptr;
     }
     if ((e = cudaStreamCreateWithFlags(&ctx->own_stream, cudaStreamNonBlocking)) != cudaSuccess ||
-        (e = cudaMalloc(&ctx->status, 256)) != cudaSuccess ||
-        (e = cudaMemset(ctx->status, 0, 256)) != cudaSuccess ||
+        (e = cudaMalloc(&ctx->status, ctx->status_bytes = 256 + uocr::decode_sliced_acc_bytes())) != cudaSuccess ||
+        (e = cudaMemset(ctx->status, 0, ctx->status_bytes)) != cudaSuccess ||
         (e = cudaMallocHost(&ctx->h_status, 256)) != cudaSuccess ||
         (e = cudaMalloc(&ctx->d_layers, kMaxLayers * sizeof(DLayer))) != cudaSuccess ||
         (e = cudaMallocHost(&ctx->h_seg, kSegSlots * 260 * sizeof(uint32_t))) != cudaSuccess ||
         (e = uocr::init_router_kernels()) != cudaSuccess || (e = uocr::init_small_batch_kernels()) != cudaSuccess ||
-        (e = uocr::init_decode_kernels()) != cudaSuccess || (e = uocr::init_gemm_kernels()) != cudaSuccess) {
+        (e = uocr::init_decode_kernels()) != cudaSuccess ||
+        (e = uocr::init_decode_sliced_kernels(decode_cluster_limit())) != cudaSuccess || (e = uocr::init_gemm_kernels()) != cudaSuccess) {
         fail(nullptr, error, error_size, "CUDA context set-up failed: %s", cudaGetErrorString(e));
         uocr_cuda_context_destroy(ctx);
         return nullptr;
@@ -163,6 +186,8 @@ extern "C" uocr_cuda_context *uocr_cuda_context_create(const char *resource_path
     ctx->stream = ctx->own_stream;
     const char *off = getenv("UOCR_CUDA_DISABLE_FUSED_DECODE");
     ctx->fused_decode = !(off && off[0] == '1');
+    const char *design = getenv("UOCR_CUDA_DECODE_DESIGN");      // "two-barrier": the earlier persistent kernel
+    ctx->sliced_decode = !(design && strcmp(design, "two-barrier") == 0);   // (then no slice-major weight copy is made)
     if (const char *mt = getenv("UOCR_CUDA_GEMM_MIN_TOKENS")) ctx->gemm_min_tokens = (uint32_t)strtoul(mt, nullptr, 10);
     return ctx;
 }
@@ -225,15 +250,17 @@ extern "C" int uocr_cuda_context_synchronize(uocr_cuda_context *ctx, char *error
     CU_TRY(ctx, cudaStreamSynchronize(ctx->stream));
     if (*ctx->h_status != 0) {
         const uint32_t st = *ctx->h_status;
-        // clears the status word and the decode kernel's barrier counter (it is off after an abort)
-        cudaMemsetAsync(ctx->status, 0, 256, ctx->stream);
+        // clears the status word, the decode kernels' barrier counter and accumulators (they are off after an abort)
+        cudaMemsetAsync(ctx->status, 0, ctx->status_bytes, ctx->stream);
         ctx->bar_base = 0;
+        ctx->acc_base = 0;
         return fail(ctx, error, error_size,
                     "device status 0x%x: %s", st,
                     (st & 1u) ? "router met a non-finite logit or an empty softmax (the CPU path rejects this input too)"
                     : (st & 2u) ? "a grid barrier of the decode kernel timed out"
                     : (st & 4u) ? "a bulk copy of the decode kernel timed out"
                     : (st & 8u) ? "a pipeline wait of the grouped GEMM kernel timed out"
+                    : (st & 16u) ? "the decode kernel met a non-finite or out-of-range partial output"
                                 : "kernel reported an internal error");
     }
     return 1;
@@ -360,6 +387,17 @@ extern "C" int uocr_cuda_context_map_moe_layer(uocr_cuda_context *ctx, const uoc
         void *ps = nullptr;
         if (sb && !upload(ctx, d->shared_down.qscale, sb, &ps, error, error_size)) return 0;
         L.shared_down = DMatrix{(const uint8_t *)p, (const __half *)ps, H, S, (uint32_t)(wb / H), sq};
+    }
+    // slice-major copy of the weights for the one-barrier decode kernel (model shapes, quantised, kernel enabled)
+    if (ctx->fused_decode && ctx->sliced_decode && uocr::decode_sliced_layer_ok(L)) {
+        const size_t bytes = uocr::decode_units_bytes(L);
+        uint8_t *units = nullptr;
+        CU_TRY(ctx, cudaMalloc(&units, bytes + kUploadPad));
+        ctx->weight_allocs.push_back(units);
+        ctx->weight_bytes += bytes;
+        CU_TRY(ctx, uocr::build_decode_units(L, units, ctx->own_stream));
+        CU_TRY(ctx, cudaStreamSynchronize(ctx->own_stream));
+        L.dec_units = units;
     }
     if (!ctx->layers.empty()) {
         const DLayer &f = ctx->layers.front();
@@ -527,6 +565,9 @@ extern "C" int uocr_cuda_moe_dispatch_plan(uocr_cuda_context *ctx, const uint32_
 static unsigned long long *barrier_counter(uocr_cuda_context *ctx) {
     return reinterpret_cast<unsigned long long *>(reinterpret_cast<uint8_t *>(ctx->status) + 64);
 }
+static unsigned long long *decode_accumulators(uocr_cuda_context *ctx) {
+    return reinterpret_cast<unsigned long long *>(reinterpret_cast<uint8_t *>(ctx->status) + 256);
+}
 
 static uocr::GemmScratch gemm_scratch(uocr_cuda_context *ctx, const Scratch &s, const ArenaLayout &a) {
     uocr::GemmScratch g{};
@@ -549,7 +590,12 @@ static int layer_forward(uocr_cuda_context *ctx, uint32_t layer, const __half *d
     Scratch s = carve(ctx, L, n, &a);
     float *logits = dbg && dbg->d_router_logits ? dbg->d_router_logits : nullptr;
     float *probs = dbg && dbg->d_router_probs ? dbg->d_router_probs : nullptr;
-    if (n == 1 && ctx->fused_decode && uocr::decode_supported(ctx->layers.data(), layer, 1)) {
+    if (n == 1 && ctx->fused_decode && ctx->sliced_decode && uocr::decode_sliced_supported(ctx->layers.data(), layer, 1)) {
+        CU_TRY(ctx, uocr::launch_decode_sliced(ctx->layers.data(), ctx->d_layers, layer, 1, d_hidden, d_residual, 0,
+                                               d_injected, d_out, decode_accumulators(ctx), &ctx->acc_base,
+                                               barrier_counter(ctx), &ctx->bar_base, ctx->status, logits, probs, s.top_ids,
+                                               s.top_weights, nullptr, ctx->stream, &ctx->launches));
+    } else if (n == 1 && ctx->fused_decode && uocr::decode_supported(ctx->layers.data(), layer, 1)) {
         CU_TRY(ctx, uocr::launch_decode_stack(ctx->layers.data(), ctx->d_layers, layer, 1, d_hidden, d_residual, 0,
                                               d_injected, d_out, (__half *)(ctx->arena + a.stack0),
                                               (__half *)(ctx->arena + a.stack1), (__half *)(ctx->arena + a.dec_mid),
@@ -589,6 +635,13 @@ static int stack_forward(uocr_cuda_context *ctx, uint32_t first, uint32_t count,
     ArenaLayout a;
     Scratch s = carve(ctx, ctx->layers[first], n, &a);
     __half *buf[2] = {(__half *)(ctx->arena + a.stack0), (__half *)(ctx->arena + a.stack1)};
+    if (n == 1 && ctx->fused_decode && ctx->sliced_decode && uocr::decode_sliced_supported(ctx->layers.data(), first, count)) {
+        CU_TRY(ctx, uocr::launch_decode_sliced(ctx->layers.data(), ctx->d_layers, first, count, d_hidden, d_hidden, 1, nullptr,
+                                               d_out, decode_accumulators(ctx), &ctx->acc_base, barrier_counter(ctx),
+                                               &ctx->bar_base, ctx->status, nullptr, nullptr, s.top_ids, s.top_weights,
+                                               ctx->decode_trace, ctx->stream, &ctx->launches));
+        return 1;
+    }
     if (n == 1 && ctx->fused_decode && uocr::decode_supported(ctx->layers.data(), first, count)) {
         CU_TRY(ctx, uocr::launch_decode_stack(ctx->layers.data(), ctx->d_layers, first, count, d_hidden, d_hidden, 1,
                                               nullptr, d_out, buf[0], buf[1], (__half *)(ctx->arena + a.dec_mid),
