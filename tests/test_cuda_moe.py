@@ -493,3 +493,27 @@ def test_sliced_decode_kernel_with_injected_logits_with_and_without_residual(pkg
     assert err <= MAX_ABS and cos >= MIN_COS, (err, cos)
     err, cos = closeness(out2, port.layer(L, hidden, None).out)
     assert err <= MAX_ABS and cos >= MIN_COS, (err, cos)
+
+
+def test_sliced_decode_when_distinct_logits_share_a_probability(pkg, port):
+    """The one-barrier decode kernel picks each slot's expert from the logit order first and checks it against the
+    exact softmax / top-k afterwards.  The two orders differ only where distinct logits round to one probability:
+    here all but four experts underflow to probability 0, so the exact rule fills the last two slots with the
+    lowest ids while the logit order would take the largest of the tiny logits."""
+    L, hidden, resid = make(7, FULL, "q4_0", 1)
+    rng = np.random.default_rng(70)
+    inj = (-150.0 - rng.permutation(64).astype(np.float32)).reshape(1, 64)      # distinct, all exp() == 0 after the shift
+    inj[0, [9, 21, 40, 63]] = [3.0, 2.5, 2.0, 1.5]
+    want = port.layer(L, hidden, resid, injected_logits=inj)
+    assert list(want.ids[0]) == [9, 21, 40, 63, 0, 1]
+    by_logit = np.argsort(-inj[0], kind="stable")[:6]
+    assert list(by_logit[:4]) == [9, 21, 40, 63] and set(by_logit[4:]) != {0, 1}
+    g = Layer(pkg, quant.LayerWeights(**{**L.__dict__, "logit_bias": None}), 1)
+    try:
+        out, ids, wts = g.forward(hidden, resid, injected=inj)
+    finally:
+        g.close()
+    assert np.array_equal(ids, want.ids)
+    assert np.array_equal(wts.view(np.uint32), want.weights.view(np.uint32))
+    err, cos = closeness(out, want.out)
+    assert err <= MAX_ABS and cos >= MIN_COS, (err, cos)

@@ -8,9 +8,9 @@
 //      memory by a few large TMA bulk copies) and the 64 SwiGLU products (rounded to fp16),
 //   2. multiplies them straight away with its 64-column slice of `down` (H rows, loaded into registers while
 //      step 1 runs), scales by the routing weight, and
-//   3. adds the H partial outputs to the layer's accumulator in global memory - after the (up to) eight CTAs of
-//      a thread-block cluster have summed their partial outputs through distributed shared memory, which cuts
-//      the number of global reductions eightfold.
+//   3. adds the H partial outputs to the layer's accumulator in global memory - after the four CTAs of a
+//      thread-block cluster have summed their partial outputs through distributed shared memory, which cuts the
+//      number of global reductions fourfold.
 // Nothing crosses CTAs between 1 and 2, so a layer needs a single barrier: after it every CTA reads the H
 // accumulated values, adds the residual, rounds to fp16 and has the next layer's input.
 //
@@ -28,8 +28,9 @@
 //
 // Off the critical path: the shared-MLP CTAs do not depend on the routing, so they fetch the NEXT layer's
 // weights while they wait at the barrier; the routed CTAs fetch the next layer's router matrix into
-// registers at the same point and evaluate it (every routed CTA redundantly, no exchange) as soon as the
-// new activations are there.
+// registers at the same point - each CTA of a cluster of four a quarter of it (16 experts) - and evaluate it as
+// soon as the new activations are there; the four quarters of the logits are exchanged through distributed
+// shared memory.  The softmax / top-k itself is taken off the path as well: see "routing" in the kernel.
 //
 // Arithmetic.  Scalar dequantise-and-FMA costs ~3.5 instructions per packed weight and would bound the layer, so
 // the dot products run on the tensor cores as INTEGER MMAs (m16n8k32, s32 accumulate), which take the packed
@@ -56,6 +57,7 @@ constexpr int kSlRoutedPerSlot = kSlF / 64;                 // 14
 constexpr int kSlRouted = kSlK * kSlRoutedPerSlot;          // 84
 constexpr int kSlUnits = kSlRouted + kSlS / 64;             // 112 CTAs
 constexpr int kSlGroups = kSlH / 64;                        // 20 quantisation groups along H
+constexpr int kSlCluster = 4;                               // CTAs per cluster: they share the router and pre-sum their outputs
 constexpr int kSlChunks = 5;                                // gate/up fragments arrive in 5 copies of 4 groups
 constexpr int kSlAccBuffers = 4;
 constexpr int kSlTracePoints = 8;
@@ -232,11 +234,11 @@ template <int QT> struct SlSmem {
     static constexpr int kMid = kGu + 2 * 128 * 4;                      // [64] fp16 SwiGLU products
     static constexpr int kMidf = kMid + 128;                            // their mantissa bytes [3][16 words], scale, corrections
     static constexpr int kPart = kMidf + 256;                           // [H] this CTA's partial outputs (read by its cluster)
-    static constexpr int kRp = kPart + kSlH * 4;                        // [4][64] partial router logits
+    static constexpr int kRp = kPart + kSlH * 4;                        // [16 warps][16 experts] partial router logits
     static constexpr int kLogits = kRp + 4 * 64 * 4;                    // [64]
     static constexpr int kProbs = kLogits + 256;                        // [64]
     static constexpr int kIds = kProbs + 256;                           // ids [8], weights [8], flags [2], mid correction
-    static constexpr int kBars = kIds + 128;                            // kSlChunks copy barriers, scale barrier, cluster barrier
+    static constexpr int kBars = kIds + 128;                            // kSlChunks copy barriers, scale barrier, two cluster barriers
     static constexpr int kLayers = kBars + 8 * 8;                       // DLayer table
     static constexpr int kTotal = kLayers + kSlMaxLayers * (int)sizeof(DLayer);
 };
@@ -268,7 +270,7 @@ __global__ void __launch_bounds__(kSlThreads, 1) decode_sliced_kernel(SlicedPara
     float *s_wts = reinterpret_cast<float *>(s_ids + 8);
     int *s_flag = reinterpret_cast<int *>(s_ids + 16);
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem + Sm::kBars);     // [0, kSlChunks) copies, then scales, then cluster
-    uint64_t *sc_bar = bars + kSlChunks, *cl_bar = bars + kSlChunks + 1;
+    uint64_t *sc_bar = bars + kSlChunks, *cl_bar = bars + kSlChunks + 1, *lg_bar = bars + kSlChunks + 2;
     DLayer *s_layers = reinterpret_cast<DLayer *>(smem + Sm::kLayers);
     __shared__ uint64_t s_tab[UOCR_EXPF_N];
 
@@ -288,6 +290,8 @@ __global__ void __launch_bounds__(kSlThreads, 1) decode_sliced_kernel(SlicedPara
         s_flag[0] = 1; s_flag[1] = 0;
         for (int i = 0; i <= kSlChunks; ++i) mbar_init(&bars[i], 1);
         mbar_init(cl_bar, csize);
+        mbar_init(lg_bar, csize);
+        s_ids[7] = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     // every CTA of the cluster has initialised its barriers before any peer arrives on them
@@ -319,10 +323,10 @@ __global__ void __launch_bounds__(kSlThreads, 1) decode_sliced_kernel(SlicedPara
     const float limb_f = t == 0 ? 1.f : (t == 1 ? 65536.f : 0.f);
     const int corr_row = t == 0 ? 0 : 1;                                // lanes other than t = 0 read zeros as correction
     const int limb_of_lane = g < 2 ? g : 2;                             // mantissa byte this lane feeds in as MMA column g
-    // Register file shared by two prefetches that are never live together: the router matrix as MMA A
-    // fragments (routed CTAs, requested while waiting at the barrier, used right after it) and this warp's
-    // 5 blocks of 16 `down` rows, the unit's 64 columns of each.
-    uint4 rw[10][2];
+    // Prefetched into registers: this warp's 5 blocks of 16 `down` rows (the unit's 64 columns of each), and the
+    // CTA's part of the next layer's router matrix (requested while waiting at the barrier, used right after it).
+    uint4 dwn[kSlBlocksPerWarp][2];
+    uint2 rtr[5][2];
     __half dslo[kSlBlocksPerWarp], dshi[kSlBlocksPerWarp];
     // everything of one unit: bulk copies of the gate/up fragments (chunk c completes barrier c) and scales into
     // shared memory, plain loads of the down fragments and scales into registers
@@ -341,25 +345,26 @@ __global__ void __launch_bounds__(kSlThreads, 1) decode_sliced_kernel(SlicedPara
         for (int bi = 0; bi < kSlBlocksPerWarp; ++bi) {
             const int blk = warp + 16 * bi;
             if (QT == UOCR_QT_Q8) {
-                rw[bi][0] = __ldg(dn + (blk * 2) * 32 + lane);
-                rw[bi][1] = __ldg(dn + (blk * 2 + 1) * 32 + lane);
+                dwn[bi][0] = __ldg(dn + (blk * 2) * 32 + lane);
+                dwn[bi][1] = __ldg(dn + (blk * 2 + 1) * 32 + lane);
             } else {
-                rw[bi][0] = __ldg(dn + blk * 32 + lane);          // rows g: .x .y, rows g + 8: .z .w
+                dwn[bi][0] = __ldg(dn + blk * 32 + lane);         // rows g: .x .y, rows g + 8: .z .w
             }
             dslo[bi] = dsc[16 * blk + g];
             dshi[bi] = dsc[16 * blk + 8 + g];
         }
     };
-    // router matrix [64][H] fp16 as MMA A fragments: warp (mb, kq) holds rows 16 mb .. +15, columns 320 kq .. +319
-    const int mb = warp & 3, kq = warp >> 2;
+    // This CTA's quarter of the router matrix (experts 16 crank .. +15, fp16 [E][H]) as MMA A fragments: warp w holds
+    // columns 80 w .. 80 w + 79 (five k steps), lane (g, t) the columns 4t .. 4t + 3 of each step for rows g and g + 8.
     auto load_router = [&](const DLayer &L) {
-        const __half *r0 = L.router + (size_t)(16 * mb + g) * H + kq * 320 + 8 * t;
+        const __half *r0 = L.router + (size_t)(16 * crank + g) * H + 80 * warp + 4 * t;
 #pragma unroll
-        for (int i = 0; i < 10; ++i) {
-            rw[i][0] = __ldg(reinterpret_cast<const uint4 *>(r0 + i * 32));
-            rw[i][1] = __ldg(reinterpret_cast<const uint4 *>(r0 + 8 * H + i * 32));
+        for (int i = 0; i < 5; ++i) {
+            rtr[i][0] = __ldg(reinterpret_cast<const uint2 *>(r0 + 16 * i));
+            rtr[i][1] = __ldg(reinterpret_cast<const uint2 *>(r0 + 8 * H + 16 * i));
         }
     };
+    uint32_t lg_phase = 0;
 
 #define UOCR_SL_TRACE(point)                                                                              \
     do {                                                                                                  \
@@ -383,45 +388,81 @@ __global__ void __launch_bounds__(kSlThreads, 1) decode_sliced_kernel(SlicedPara
         float weight = 1.0f;
 
         if (routed) {
-            // ---- router: logits of all experts, evaluated by every routed CTA for itself
+            // ---- router: this CTA's 16 logits, then the exchange with the three other CTAs of the cluster
             if (li == 0 && prm.injected != nullptr) {
                 if (tid < E) s_logits[tid] = prm.injected[tid] + (L.bias ? L.bias[tid] : 0.f);
             } else {
                 float c[4] = {0.f, 0.f, 0.f, 0.f}, d[4] = {0.f, 0.f, 0.f, 0.f};      // two chains of MMAs
-                const __half *xq = s_x + kq * 320 + 8 * t;
+                const __half *xq = s_x + 80 * warp + 4 * t;
 #pragma unroll
-                for (int i = 0; i < 10; ++i) {
-                    const uint4 xv = *reinterpret_cast<const uint4 *>(xq + i * 32);
-                    mma16816(c, rw[i][0].x, rw[i][1].x, rw[i][0].y, rw[i][1].y, xv.x, xv.y);
-                    mma16816(d, rw[i][0].z, rw[i][1].z, rw[i][0].w, rw[i][1].w, xv.z, xv.w);
+                for (int i = 0; i < 5; ++i) {
+                    const uint2 xv = *reinterpret_cast<const uint2 *>(xq + 16 * i);
+                    if (i & 1) mma16816(d, rtr[i][0].x, rtr[i][1].x, rtr[i][0].y, rtr[i][1].y, xv.x, xv.y);
+                    else mma16816(c, rtr[i][0].x, rtr[i][1].x, rtr[i][0].y, rtr[i][1].y, xv.x, xv.y);
                 }
-                if (t == 0) { s_rp[kq * 64 + 16 * mb + g] = c[0] + d[0]; s_rp[kq * 64 + 16 * mb + 8 + g] = c[2] + d[2]; }
+                if (t == 0) { s_rp[warp * 16 + g] = c[0] + d[0]; s_rp[warp * 16 + 8 + g] = c[2] + d[2]; }
                 __syncthreads();
-                if (tid < E) {
-                    const float v = ((s_rp[tid] + s_rp[64 + tid]) + s_rp[128 + tid]) + s_rp[192 + tid];
-                    s_logits[tid] = L.bias ? v + L.bias[tid] : v;
+                if (warp == 0) {
+                    if (lane < 16) {          // one logit per lane, summed over the warps in a fixed order, sent to the whole cluster
+                        float v = 0.f;
+#pragma unroll
+                        for (int w = 0; w < 16; ++w) v += s_rp[w * 16 + lane];
+                        const uint32_t e = 16u * crank + (uint32_t)lane;
+                        if (L.bias) v += L.bias[e];
+                        for (uint32_t r = 0; r < csize; ++r)
+                            asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(cluster_addr(s_logits + e, r)), "f"(v) : "memory");
+                    }
+                    __syncwarp();
+                    if ((uint32_t)lane < csize) mbar_arrive_cluster(cluster_addr(lg_bar, (uint32_t)lane));
+                    if (lane == 0) {
+                        int ok = 1;
+                        if (!mbar_try_wait_cluster(lg_bar, lg_phase)) {
+                            const long long t0 = clock64();
+                            while (!mbar_try_wait_cluster(lg_bar, lg_phase)) {
+                                if (clock64() - t0 > kSpinLimit) { atomicOr(status, kStatusBarrier); s_flag[1] = 1; ok = 0; break; }
+                            }
+                        }
+                        (void)ok;
+                    }
                 }
+                lg_phase ^= 1u;
             }
             __syncthreads();
-            if (warp == 0) {
+            // ---- routing.  The softmax is monotonic, so the slot's expert is (except for two logits that round to one
+            // probability) the one whose logit ranks slot-th: eight threads per expert count the logits that beat
+            // it.  Every warp but one goes on to fetch that expert's weights, while warp 1 runs the exact softmax /
+            // top-k; the result is checked after the gate/up products and the rare mismatch is redone.
+            {
+                const int e = tid >> 3, part = tid & 7;
+                const float mine = s_logits[e];
+                int beats = 0;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const int o = 8 * part + j;
+                    const float v = s_logits[o];
+                    beats += (v > mine || (v == mine && o < e)) ? 1 : 0;
+                }
+                beats += __shfl_xor_sync(0xffffffffu, beats, 1);
+                beats += __shfl_xor_sync(0xffffffffu, beats, 2);
+                beats += __shfl_xor_sync(0xffffffffu, beats, 4);
+                if (part == 0 && beats == (int)slot) s_ids[7] = (uint32_t)e;
+            }
+            __syncthreads();
+            if (warp == 1) {
                 const bool dbg = cta == 0 && li == 0;
                 const bool bad = route_row_warp(s_logits, s_probs, E, K, L.scaling, lane, s_tab, dbg ? prm.dbg_logits : nullptr,
                                                 dbg ? prm.dbg_probs : nullptr, s_ids, s_wts);
                 if (bad && lane == 0 && cta == 0) atomicOr(status, kStatusRouter);
             }
-            __syncthreads();
-            UOCR_SL_TRACE(1);     // routing
-            if (cta == 0 && last && tid < K) { prm.ids_out[tid] = s_ids[tid]; prm.wts_out[tid] = s_wts[tid]; }
-            const uint32_t ex = s_ids[slot];
-            valid = ex < (uint32_t)E;         // an invalid expert id contributes zeros
-            weight = s_wts[slot];
-            if (valid) fetch_unit(L.dec_units + (size_t)(ex * kSlRoutedPerSlot + fg) * Bl::kBytes);
+            UOCR_SL_TRACE(1);     // expert of this CTA's slot chosen
         } else {
             UOCR_SL_TRACE(1);
         }
+        uint32_t ex = routed ? s_ids[7] : 0u;       // expert whose weights this CTA fetches
+      for (;;) {
+        if (routed) fetch_unit(L.dec_units + (size_t)(ex * kSlRoutedPerSlot + fg) * Bl::kBytes);
         UOCR_SL_TRACE(2);         // weight fetches issued
-
-        if (valid) {
+        {
             // ---- gate / up: warp (rb, kh) multiplies rows 8 rb .. +7 of both matrices with the groups of parity kh,
             // chunk by chunk as the copies land
             const int rb = warp & 7, kh = warp >> 3;
@@ -458,6 +499,20 @@ __global__ void __launch_bounds__(kSlThreads, 1) decode_sliced_kernel(SlicedPara
             sg += __shfl_xor_sync(0xffffffffu, sg, 1); su += __shfl_xor_sync(0xffffffffu, su, 1);
             if (t == 0) { s_gu[kh * 128 + 8 * rb + g] = sg; s_gu[kh * 128 + 64 + 8 * rb + g] = su; }
             __syncthreads();
+            copy_phase ^= 1u;
+            if (routed) {            // the exact routing is in shared memory by now
+                const uint32_t exact = s_ids[slot];
+                if (exact != ex) {
+                    if (exact < (uint32_t)E) { ex = exact; __syncthreads(); continue; }
+                    valid = false;          // an invalid expert id contributes zeros
+                }
+                weight = s_wts[slot];
+                if (cta == 0 && last && tid < K) { prm.ids_out[tid] = s_ids[tid]; prm.wts_out[tid] = s_wts[tid]; }
+            }
+            break;
+        }
+      }
+        if (valid) {
             if (tid < 64) {
                 const float gate = s_gu[tid] + s_gu[128 + tid], up = s_gu[64 + tid] + s_gu[192 + tid];
                 s_mid[tid] = __float2half_rn(silu_f32(gate) * up);
@@ -465,7 +520,6 @@ __global__ void __launch_bounds__(kSlThreads, 1) decode_sliced_kernel(SlicedPara
             __syncthreads();
             if (warp == 0) write_limbs<QT>(s_mid, lane & 15, s_midf, s_mscale, s_mscale + 1, 1);    // both half-warps write the same
             __syncthreads();
-            copy_phase ^= 1u;
             UOCR_SL_TRACE(4);     // SwiGLU products of the slice
 
             // ---- down: H rows x the slice's 64 columns, straight from registers; partial outputs to shared memory
@@ -475,8 +529,8 @@ __global__ void __launch_bounds__(kSlThreads, 1) decode_sliced_kernel(SlicedPara
 #pragma unroll
                 for (int bi = 0; bi < kSlBlocksPerWarp; ++bi) {
                     int c[4] = {0, 0, 0, 0};
-                    if (QT == UOCR_QT_Q8) group_imma(c, rw[bi][0], rw[bi][1], mbf);
-                    else group_imma(c, make_uint2(rw[bi][0].x, rw[bi][0].y), make_uint2(rw[bi][0].z, rw[bi][0].w), mbf);
+                    if (QT == UOCR_QT_Q8) group_imma(c, dwn[bi][0], dwn[bi][1], mbf);
+                    else group_imma(c, make_uint2(dwn[bi][0].x, dwn[bi][0].y), make_uint2(dwn[bi][0].z, dwn[bi][0].w), mbf);
                     float v0 = fmaf((float)(c[1] * limb_mul + c[0]), limb_f, nc) * (__half2float(dslo[bi]) * ms);
                     float v1 = fmaf((float)(c[3] * limb_mul + c[2]), limb_f, nc) * (__half2float(dshi[bi]) * ms);
                     v0 += __shfl_xor_sync(0xffffffffu, v0, 1);
@@ -660,33 +714,29 @@ static void launch_config(cudaLaunchConfig_t *cfg, cudaLaunchAttribute *attrs, i
     cfg->attrs = attrs; cfg->numAttrs = 2;
 }
 
-// largest cluster size (at most `limit`: 8, 4, 2 or 1) with which all CTAs are resident at once
+// 1 when all CTAs can be resident at once in clusters of kSlCluster, else 0
 template <int QT>
-static cudaError_t prepare_sliced(int limit, int *cluster) {
+static cudaError_t prepare_sliced(int *ok) {
     auto kern = decode_sliced_kernel<QT>;
     cudaError_t err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SlSmem<QT>::kTotal);
     if (err != cudaSuccess) return err;
-    *cluster = 0;
-    for (int cs = limit; cs >= 1 && *cluster == 0; cs >>= 1) {
-        cudaLaunchConfig_t cfg;
-        cudaLaunchAttribute attrs[2];
-        launch_config<QT>(&cfg, attrs, cs, nullptr);
-        int clusters = 0;
-        if (cudaOccupancyMaxActiveClusters(&clusters, kern, &cfg) == cudaSuccess && clusters * cs >= kSlUnits) *cluster = cs;
-        else (void)cudaGetLastError();
-    }
+    cudaLaunchConfig_t cfg;
+    cudaLaunchAttribute attrs[2];
+    launch_config<QT>(&cfg, attrs, kSlCluster, nullptr);
+    int clusters = 0;
+    if (cudaOccupancyMaxActiveClusters(&clusters, kern, &cfg) != cudaSuccess) { (void)cudaGetLastError(); clusters = 0; }
+    *ok = clusters * kSlCluster >= kSlUnits ? 1 : 0;
     return cudaSuccess;
 }
 
-// cluster_limit: 8, 4, 2 or 1
-cudaError_t init_decode_sliced_kernels(int cluster_limit) {
+cudaError_t init_decode_sliced_kernels() {
     int dev = 0;
     cudaError_t err = cudaGetDevice(&dev);
     if (err != cudaSuccess) return err;
-    int c4 = 0, c8 = 0;
-    if ((err = prepare_sliced<UOCR_QT_Q4>(cluster_limit, &c4)) != cudaSuccess) return err;
-    if ((err = prepare_sliced<UOCR_QT_Q8>(cluster_limit, &c8)) != cudaSuccess) return err;
-    if (dev < 64) g_sliced_cluster[dev] = c4 < c8 ? c4 : c8;
+    int ok4 = 0, ok8 = 0;
+    if ((err = prepare_sliced<UOCR_QT_Q4>(&ok4)) != cudaSuccess) return err;
+    if ((err = prepare_sliced<UOCR_QT_Q8>(&ok8)) != cudaSuccess) return err;
+    if (dev < 64) g_sliced_cluster[dev] = (ok4 && ok8) ? kSlCluster : 0;
     return cudaSuccess;
 }
 

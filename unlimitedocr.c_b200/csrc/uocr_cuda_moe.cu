@@ -16,7 +16,7 @@ namespace uocr {
 cudaError_t init_router_kernels();
 cudaError_t init_small_batch_kernels();
 cudaError_t init_decode_kernels();
-cudaError_t init_decode_sliced_kernels(int cluster_limit);
+cudaError_t init_decode_sliced_kernels();
 cudaError_t init_gemm_kernels();
 bool gemm_path_supported(const DLayer &L);
 struct GemmScratch {
@@ -139,13 +139,6 @@ extern "C" int uocr_cuda_device_count(void) {
     return cudaGetDeviceCount(&n) == cudaSuccess ? n : 0;
 }
 
-// UOCR_CUDA_DECODE_CLUSTER = 1, 2, 4 or 8 (default 8): CTAs per thread-block cluster of the one-barrier decode kernel
-static int decode_cluster_limit() {
-    const char *v = getenv("UOCR_CUDA_DECODE_CLUSTER");
-    const int c = v ? atoi(v) : 8;
-    return (c == 1 || c == 2 || c == 4 || c == 8) ? c : 8;
-}
-
 extern "C" uocr_cuda_context *uocr_cuda_context_create(const char *resource_path, char *error, size_t error_size) {
     (void)resource_path;
     int n = 0;
@@ -177,7 +170,7 @@ extern "C" uocr_cuda_context *uocr_cuda_context_create(const char *resource_path
         (e = cudaMallocHost(&ctx->h_seg, kSegSlots * 260 * sizeof(uint32_t))) != cudaSuccess ||
         (e = uocr::init_router_kernels()) != cudaSuccess || (e = uocr::init_small_batch_kernels()) != cudaSuccess ||
         (e = uocr::init_decode_kernels()) != cudaSuccess ||
-        (e = uocr::init_decode_sliced_kernels(decode_cluster_limit())) != cudaSuccess || (e = uocr::init_gemm_kernels()) != cudaSuccess) {
+        (e = uocr::init_decode_sliced_kernels()) != cudaSuccess || (e = uocr::init_gemm_kernels()) != cudaSuccess) {
         fail(nullptr, error, error_size, "CUDA context set-up failed: %s", cudaGetErrorString(e));
         uocr_cuda_context_destroy(ctx);
         return nullptr;
