@@ -37,7 +37,7 @@ constexpr int kTileN = 256;          // tokens per tile of the down product (one
 constexpr int kTileNGateUp = 128;    // tokens per tile of the gate/up product (two accumulators)
 constexpr int kBlockK = 64;          // fp16 elements per K block = 128 bytes = one swizzle row
 constexpr int kTileBytes = kTileM * kBlockK * 2;   // 16 KB: one operand tile of one stage
-constexpr long long kGemmSpinLimit = 4000000000LL;
+constexpr long long kGemmSpinLimit = 400000000LL;    // cycles (~0.2 s): no legitimate wait comes near
 constexpr uint32_t kStatusGemm = 8u;
 
 struct GemmParams {
@@ -217,6 +217,9 @@ __device__ __forceinline__ void tc_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint
         ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
 }
 
+// silu with the fast exponential and reciprocal (about 2 ulp; the result is rounded to fp16 anyway)
+__device__ __forceinline__ float silu_fast(float v) { return __fdividef(v, 1.0f + __expf(-v)); }
+
 // ------------------------------------------------------------------------------ kernel
 // Tensor-memory columns: the accumulators first, then kAStages slots of the weight operand (one 32-wide K
 // sub-block of every weight tile per slot).  Two CTAs share an SM, so a CTA may hold at most 256 columns.
@@ -302,6 +305,14 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap act_map, GemmParams p) {
         // this thread's TMEM lane, its 8 columns inside a 16-column sub-block, and its matrix inside a slot
         const uint32_t lane_addr = ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)h * 8 + (GATEUP ? (uint32_t)grp * 32 : 0u);
         bool alive = true;
+        int pending = -1;       // slot whose tensor-memory stores are in flight: published one block later, so that
+                                // the stores' latency hides behind the next block's conversion
+        auto publish = [&]() {
+            tc_st_wait();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) gb_arrive(&a_full[pending]);              // one arrival per warp: its stores have all landed
+        };
         for (uint32_t kb0 = 0; kb0 < kblocks && alive; kb0 += kAhead) {
 #pragma unroll
             for (int d = 0; d < kAhead; ++d) {
@@ -313,38 +324,49 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap act_map, GemmParams p) {
                 uint32_t regs[2][8];
                 if (GATEUP) { convert_sub<QT>(v[d], 0, sc, regs[0]); convert_sub<QT>(v[d], 1, sc, regs[1]); }
                 else convert_sub<QT>(v[d], grp, sc, regs[0]);
-                if (use > 0 && !gb_wait(&a_empty[slot], (use - 1) & 1u, abort_flag, p.status)) { alive = false; break; }
+                if (kb + kAhead < kblocks) load_block<QT>(rowp, kb + kAhead, h, v[d]);
+                if (pending >= 0) publish();
+                if (use > 0 && !gb_wait(&a_empty[slot], (use - 1) & 1u, abort_flag, p.status)) { alive = false; pending = -1; break; }
                 __syncwarp();
                 tc_fence_after();
                 const uint32_t dst = a_base + slot * Sh::kAStageCols + lane_addr;
                 if (GATEUP) { tc_st8(dst, regs[0]); tc_st8(dst + 16, regs[1]); }
                 else tc_st8(dst + (uint32_t)grp * 16, regs[0]);
-                tc_st_wait();
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) gb_arrive(&a_full[slot]);              // one arrival per warp: its stores have all landed
-                if (kb + kAhead < kblocks) load_block<QT>(rowp, kb + kAhead, h, v[d]);
+                pending = (int)slot;
             }
         }
+        if (pending >= 0) publish();
         // ------------------------------------------------ epilogue: TMEM -> registers -> global
         const bool have_acc = alive && gb_wait(acc_full, 0, abort_flag, p.status);
         __syncwarp();
         if (__all_sync(0xffffffffu, have_acc)) {
             tc_fence_after();
-            // a warp reads the TMEM lanes 32*(warp % 4)..+31; the four warps of a lane quarter split the 16-column chunks
+            // a warp reads the TMEM lanes 32*(warp % 4)..+31; the four warps of a lane quarter split the 16-column
+            // chunks.  All of a warp's chunks are requested before the first is used.
+            constexpr int kChunks = kTileN / 64;
             const uint32_t lane_base = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
             const size_t out_col = (size_t)mtile * kTileM + r;
-            for (uint32_t c0 = (uint32_t)(warp >> 2) * 16; c0 < nrows; c0 += 64) {
-                uint32_t g[16], u[16];
-                tc_ld16(lane_base + c0, g);
-                if (GATEUP) tc_ld16(lane_base + kTileN + c0, u);
-                tc_ld_wait();
+            const uint32_t cbase = (uint32_t)(warp >> 2) * 16;
+            uint32_t g[kChunks][16], u[GATEUP ? kChunks : 1][16];
 #pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                    if (c0 + j < nrows) {
-                        const float a = __uint_as_float(g[j]);
-                        const float o = GATEUP ? silu_f32(a) * __uint_as_float(u[j]) : a;
-                        p.out[(size_t)(row0 + c0 + j) * p.out_ld + out_col] = __float2half_rn(o);
+            for (int i = 0; i < kChunks; ++i) {
+                if (cbase + 64 * i < nrows) {
+                    tc_ld16(lane_base + cbase + 64 * i, g[i]);
+                    if (GATEUP) tc_ld16(lane_base + kTileN + cbase + 64 * i, u[i]);
+                }
+            }
+            tc_ld_wait();
+#pragma unroll
+            for (int i = 0; i < kChunks; ++i) {
+                const uint32_t c0 = cbase + 64 * i;
+                if (c0 < nrows) {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        if (c0 + j < nrows) {
+                            const float a = __uint_as_float(g[i][j]);
+                            const float o = GATEUP ? silu_fast(a) * __uint_as_float(u[GATEUP ? i : 0][j]) : a;
+                            p.out[(size_t)(row0 + c0 + j) * p.out_ld + out_col] = __float2half_rn(o);
+                        }
                     }
                 }
             }
@@ -787,17 +809,6 @@ cudaError_t launch_gather_sorted(const DLayer &L, const Scratch &S, const __half
     gather_rows_kernel<<<(pairs * 32 + 255) / 256, 256, 0, st>>>(hidden, S.pair_rows, S.expert_offsets, L.E, L.K, L.H, rows_out);
     ++*launches;
     return cudaGetLastError();
-}
-
-// The whole many-token layer on one GPU: gather, routed experts, shared MLP + combine.
-cudaError_t launch_gemm_layer(const DLayer &L, const Scratch &S, const GemmScratch &G, const __half *hidden,
-                              const __half *residual, uint32_t n, __half *out, cudaStream_t st, uint64_t *launches) {
-    cudaError_t err;
-    if ((err = launch_gather_sorted(L, S, hidden, n, G.x_sorted, st, launches)) != cudaSuccess) return err;
-    if ((err = launch_gemm_experts(L, S, G, S.expert_offsets, L.E, 0, L.E, G.x_sorted, n * L.K, G.mid_sorted, G.down_sorted,
-                                   st, launches)) != cudaSuccess) return err;
-    if ((err = launch_gemm_shared(L, S, G, hidden, n, st, launches)) != cudaSuccess) return err;
-    return launch_gemm_combine(L, S, G, G.down_sorted, residual, n, out, st, launches);
 }
 
 }  // namespace uocr

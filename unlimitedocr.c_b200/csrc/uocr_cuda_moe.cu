@@ -24,8 +24,6 @@ struct GemmScratch {
     uint4 *tiles_gu, *tiles_dn, *stiles_gu, *stiles_dn;
     uint32_t *counts;
 };
-cudaError_t launch_gemm_layer(const DLayer &L, const Scratch &S, const GemmScratch &G, const __half *hidden,
-                              const __half *residual, uint32_t n, __half *out, cudaStream_t st, uint64_t *launches);
 cudaError_t launch_gather_sorted(const DLayer &L, const Scratch &S, const __half *hidden, uint32_t n, __half *rows_out,
                                  cudaStream_t st, uint64_t *launches);
 cudaError_t launch_gemm_experts(const DLayer &L, const Scratch &S, const GemmScratch &G, const uint32_t *seg_offsets,
@@ -92,6 +90,8 @@ struct uocr_cuda_context {
     float *h_wts = nullptr;
     uint32_t *h_seg = nullptr;         // pinned ring for the expert-parallel segment offsets
     cudaEvent_t seg_events[8] = {};
+    cudaStream_t side_stream = nullptr;   // the shared MLP of a many-token call runs here, beside routing and the routed experts
+    cudaEvent_t fork_event = nullptr, join_event = nullptr;
     uint32_t seg_slot = 0;
     uint64_t launches = 0;
     char last_error[1024] = {0};
@@ -176,6 +176,13 @@ extern "C" uocr_cuda_context *uocr_cuda_context_create(const char *resource_path
         return nullptr;
     }
     for (uint32_t i = 0; i < kSegSlots; ++i) cudaEventCreateWithFlags(&ctx->seg_events[i], cudaEventDisableTiming);
+    if ((e = cudaStreamCreateWithFlags(&ctx->side_stream, cudaStreamNonBlocking)) != cudaSuccess ||
+        (e = cudaEventCreateWithFlags(&ctx->fork_event, cudaEventDisableTiming)) != cudaSuccess ||
+        (e = cudaEventCreateWithFlags(&ctx->join_event, cudaEventDisableTiming)) != cudaSuccess) {
+        fail(nullptr, error, error_size, "CUDA context set-up failed: %s", cudaGetErrorString(e));
+        uocr_cuda_context_destroy(ctx);
+        return nullptr;
+    }
     ctx->stream = ctx->own_stream;
     const char *off = getenv("UOCR_CUDA_DISABLE_FUSED_DECODE");
     ctx->fused_decode = !(off && off[0] == '1');
@@ -218,6 +225,9 @@ extern "C" void uocr_cuda_context_destroy(uocr_cuda_context *ctx) {
     for (uint32_t i = 0; i < kSegSlots; ++i) if (ctx->seg_events[i]) cudaEventDestroy(ctx->seg_events[i]);
     cudaFreeHost(ctx->h_status);
     if (ctx->own_stream) cudaStreamDestroy(ctx->own_stream);
+    if (ctx->side_stream) { cudaStreamSynchronize(ctx->side_stream); cudaStreamDestroy(ctx->side_stream); }
+    if (ctx->fork_event) cudaEventDestroy(ctx->fork_event);
+    if (ctx->join_event) cudaEventDestroy(ctx->join_event);
     delete ctx;
 }
 
@@ -595,17 +605,29 @@ static int layer_forward(uocr_cuda_context *ctx, uint32_t layer, const __half *d
                                               (float *)(ctx->arena + a.dec_plogits), barrier_counter(ctx), &ctx->bar_base,
                                               ctx->status, logits, probs, s.top_ids, s.top_weights, nullptr, ctx->stream,
                                               &ctx->launches));
+    } else if (n >= ctx->gemm_min_tokens && uocr::gemm_path_supported(L)) {
+        // The shared MLP needs neither the routing nor the permutation: it runs on a second stream beside the router,
+        // the dispatch plan, the gather and the routed experts, whose small kernels leave most SMs idle.
+        const uocr::GemmScratch g = gemm_scratch(ctx, s, a);
+        CU_TRY(ctx, cudaEventRecord(ctx->fork_event, ctx->stream));
+        CU_TRY(ctx, cudaStreamWaitEvent(ctx->side_stream, ctx->fork_event, 0));
+        CU_TRY(ctx, uocr::launch_gemm_shared(L, s, g, d_hidden, n, ctx->side_stream, &ctx->launches));
+        CU_TRY(ctx, cudaEventRecord(ctx->join_event, ctx->side_stream));
+        CU_TRY(ctx, uocr::launch_router(L, d_hidden, d_injected, n, logits, probs, s.top_ids, s.top_weights, ctx->status,
+                                        s.logits, ctx->stream, &ctx->launches));
+        CU_TRY(ctx, uocr::launch_dispatch_plan(s.top_ids, n, L.K, L.E, s.expert_offsets, s.pair_rows, s.inverse,
+                                               s.active, s.plan_counts, ctx->stream, &ctx->launches));
+        CU_TRY(ctx, uocr::launch_gather_sorted(L, s, d_hidden, n, g.x_sorted, ctx->stream, &ctx->launches));
+        CU_TRY(ctx, uocr::launch_gemm_experts(L, s, g, s.expert_offsets, L.E, 0, L.E, g.x_sorted, n * L.K, g.mid_sorted,
+                                              g.down_sorted, ctx->stream, &ctx->launches));
+        CU_TRY(ctx, cudaStreamWaitEvent(ctx->stream, ctx->join_event, 0));
+        CU_TRY(ctx, uocr::launch_gemm_combine(L, s, g, g.down_sorted, d_residual, n, d_out, ctx->stream, &ctx->launches));
     } else {
         CU_TRY(ctx, uocr::launch_router(L, d_hidden, d_injected, n, logits, probs, s.top_ids, s.top_weights, ctx->status,
                                         s.logits, ctx->stream, &ctx->launches));
         CU_TRY(ctx, uocr::launch_dispatch_plan(s.top_ids, n, L.K, L.E, s.expert_offsets, s.pair_rows, s.inverse,
                                                s.active, s.plan_counts, ctx->stream, &ctx->launches));
-        if (n >= ctx->gemm_min_tokens && uocr::gemm_path_supported(L)) {
-            const uocr::GemmScratch g = gemm_scratch(ctx, s, a);
-            CU_TRY(ctx, uocr::launch_gemm_layer(L, s, g, d_hidden, d_residual, n, d_out, ctx->stream, &ctx->launches));
-        } else {
-            CU_TRY(ctx, uocr::launch_small_batch_layer(L, s, d_hidden, d_residual, n, d_out, ctx->stream, &ctx->launches));
-        }
+        CU_TRY(ctx, uocr::launch_small_batch_layer(L, s, d_hidden, d_residual, n, d_out, ctx->stream, &ctx->launches));
     }
     if (dbg && dbg->d_top_ids)
         CU_TRY(ctx, cudaMemcpyAsync(dbg->d_top_ids, s.top_ids, (size_t)n * L.K * 4, cudaMemcpyDeviceToDevice, ctx->stream));
