@@ -1,5 +1,5 @@
-// Single-token decode, sliced design: a run of MoE layers in ONE persistent kernel with ONE grid-wide
-// barrier per layer.
+// Single-token decode, sliced design: a run of MoE layers in ONE persistent kernel whose only exchange
+// between CTAs per layer is the layer's output vector.
 //
 // The intermediate dimension of every SwiGLU MLP the token uses is cut into 64-wide slices (one
 // quantisation group of the `down` matrix): K * F/64 routed slices + S/64 shared slices = 112 units for
@@ -8,11 +8,9 @@
 //      memory by a few large TMA bulk copies) and the 64 SwiGLU products (rounded to fp16),
 //   2. multiplies them straight away with its 64-column slice of `down` (H rows, loaded into registers while
 //      step 1 runs), scales by the routing weight, and
-//   3. adds the H partial outputs to the layer's accumulator in global memory - after the four CTAs of a
-//      thread-block cluster have summed their partial outputs through distributed shared memory, which cuts the
-//      number of global reductions fourfold.
-// Nothing crosses CTAs between 1 and 2, so a layer needs a single barrier: after it every CTA reads the H
-// accumulated values, adds the residual, rounds to fp16 and has the next layer's input.
+//   3. adds the H partial outputs to the layer's accumulator in global memory.
+// Nothing crosses CTAs between 1 and 2.  Every CTA then reads the H accumulated values, adds the residual, rounds to
+// fp16 and has the next layer's input.
 //
 // Weight layout.  A column slice of `down` in the file layout is 32 bytes out of every 448-byte row, and the
 // 128 gate/up rows of a slice are read 8 bytes per lane: both are poison for DRAM bursts and for the load/store
@@ -22,9 +20,13 @@
 //   gate/up fragments [group 0..19][row block 0..7][lane] | gate/up scales [128][20] | down fragments
 //   [row block 0..79][lane] | down scales [H].
 //
-// The accumulator is 64-bit fixed point (2^-32 units) updated with integer reductions, so the sum does not
-// depend on the order in which CTAs arrive: results are reproducible run to run.  Four accumulator
-// buffers rotate (adds / read / idle / cleared), the rotation continues across launches.
+// The accumulator is 64-bit fixed point (2^-28 units) updated with integer reductions, so the sum does not
+// depend on the order in which CTAs arrive: results are reproducible run to run.  The top byte of a word counts
+// the CTAs that have added to it - every CTA adds to every word exactly once per layer - so a reader that sees
+// the full count holds the final value: no grid barrier, no fence, one L2 round trip less per layer.  Four
+// accumulator buffers rotate (adds / read / idle / cleared); the rotation continues across launches, and the data
+// dependency itself (nobody can start layer l + 1 before everybody has finished reading layer l - 1) keeps the
+// clearing safe.
 //
 // Off the critical path: the shared-MLP CTAs do not depend on the routing, so they fetch the NEXT layer's
 // weights while they wait at the barrier; the routed CTAs fetch the next layer's router matrix into
@@ -60,6 +62,11 @@ constexpr int kSlGroups = kSlH / 64;                        // 20 quantisation g
 constexpr int kSlCluster = 4;                               // CTAs per cluster: they share the router and pre-sum their outputs
 constexpr int kSlChunks = 5;                                // gate/up fragments arrive in 5 copies of 4 groups
 constexpr int kSlAccBuffers = 4;
+// accumulator word: bits 56-63 count the CTAs that have added, bits 0-55 hold the sum of (value * 2^28 + 2^47)
+constexpr unsigned long long kSlAccOne = 1ull << 56;
+constexpr long long kSlAccBias = 1ll << 47;
+constexpr float kSlAccScale = 268435456.f;       // 2^28
+constexpr float kSlAccRange = 262144.f;          // |partial output| must stay below 2^18
 constexpr int kSlTracePoints = 8;
 constexpr int kSlMaxLayers = 64;
 constexpr int kSlBlocksPerWarp = kSlH / 16 / 16;            // 5 blocks of 16 output rows per warp
@@ -74,8 +81,6 @@ struct SlicedParams {
     __half *out;
     unsigned long long *acc;      // [kSlAccBuffers][H] fixed-point accumulators, all zero between launches except two
     uint32_t acc_base;            // buffer of the first layer of this launch
-    unsigned long long *bar;
-    unsigned long long bar_base;
     uint32_t *status;
     float *dbg_logits, *dbg_probs;
     uint32_t *ids_out;            // [K] routing of the last layer run
@@ -181,11 +186,6 @@ __device__ __forceinline__ void write_limbs(const __half *src, int idx, uint32_t
     }
 }
 
-__device__ __forceinline__ unsigned long long ldcg_u64(const unsigned long long *p) {
-    unsigned long long v;
-    asm volatile("ld.global.cg.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
-    return v;
-}
 __device__ __forceinline__ void red_add_u64(unsigned long long *p, unsigned long long v) {
     asm volatile("red.relaxed.gpu.global.add.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
 }
@@ -204,11 +204,6 @@ __device__ __forceinline__ uint32_t cluster_addr(const void *local, uint32_t ran
     uint32_t a;
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(a) : "r"(smem_u32(local)), "r"(rank));
     return a;
-}
-__device__ __forceinline__ float ld_cluster_f32(uint32_t addr) {
-    float v;
-    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");
-    return v;
 }
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t remote_bar) {
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(remote_bar) : "memory");
@@ -270,7 +265,7 @@ __global__ void __launch_bounds__(kSlThreads, 1) decode_sliced_kernel(SlicedPara
     float *s_wts = reinterpret_cast<float *>(s_ids + 8);
     int *s_flag = reinterpret_cast<int *>(s_ids + 16);
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem + Sm::kBars);     // [0, kSlChunks) copies, then scales, then cluster
-    uint64_t *sc_bar = bars + kSlChunks, *cl_bar = bars + kSlChunks + 1, *lg_bar = bars + kSlChunks + 2;
+    uint64_t *sc_bar = bars + kSlChunks, *lg_bar = bars + kSlChunks + 1;
     DLayer *s_layers = reinterpret_cast<DLayer *>(smem + Sm::kLayers);
     __shared__ uint64_t s_tab[UOCR_EXPF_N];
 
@@ -280,16 +275,13 @@ __global__ void __launch_bounds__(kSlThreads, 1) decode_sliced_kernel(SlicedPara
     const bool routed = cta < (uint32_t)kSlRouted;
     const uint32_t slot = routed ? cta / kSlRoutedPerSlot : (uint32_t)K;
     const uint32_t fg = routed ? cta % kSlRoutedPerSlot : cta - kSlRouted;     // 64-wide slice of F (of S)
-    unsigned long long bar_target = prm.bar_base;
     uint32_t *status = prm.status;
     const uint32_t crank = cluster_rank(), csize = cluster_size();
-    const int cols_per_cta = H / (int)csize;                           // columns of the cluster's sum this CTA sends on
 
     if (tid < UOCR_EXPF_N) s_tab[tid] = c_exp_tab[tid];
     if (tid == 0) {
         s_flag[0] = 1; s_flag[1] = 0;
         for (int i = 0; i <= kSlChunks; ++i) mbar_init(&bars[i], 1);
-        mbar_init(cl_bar, csize);
         mbar_init(lg_bar, csize);
         s_ids[7] = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -376,7 +368,7 @@ __global__ void __launch_bounds__(kSlThreads, 1) decode_sliced_kernel(SlicedPara
     uint32_t copy_phase = 0;
     if (routed) load_router(s_layers[0]);
     else fetch_unit(s_layers[0].dec_units + (size_t)(kSlE * kSlRoutedPerSlot + fg) * Bl::kBytes);
-    build_x_frags();
+    if (!routed) build_x_frags();      // routed CTAs arrange their activations while their weights are on the way
     __syncthreads();
 
     for (uint32_t li = 0; li < prm.count; ++li) {
@@ -459,8 +451,11 @@ __global__ void __launch_bounds__(kSlThreads, 1) decode_sliced_kernel(SlicedPara
             UOCR_SL_TRACE(1);
         }
         uint32_t ex = routed ? s_ids[7] : 0u;       // expert whose weights this CTA fetches
-      for (;;) {
-        if (routed) fetch_unit(L.dec_units + (size_t)(ex * kSlRoutedPerSlot + fg) * Bl::kBytes);
+      for (bool first = true;; first = false) {
+        if (routed) {
+            fetch_unit(L.dec_units + (size_t)(ex * kSlRoutedPerSlot + fg) * Bl::kBytes);
+            if (first) { build_x_frags(); __syncthreads(); }
+        }
         UOCR_SL_TRACE(2);         // weight fetches issued
         {
             // ---- gate / up: warp (rb, kh) multiplies rows 8 rb .. +7 of both matrices with the groups of parity kh,
@@ -548,63 +543,82 @@ __global__ void __launch_bounds__(kSlThreads, 1) decode_sliced_kernel(SlicedPara
             for (int h = tid; h < H; h += kSlThreads) s_part[h] = 0.f;
         }
         UOCR_SL_TRACE(5);         // partial outputs of this CTA
-        // ---- sum over the cluster (fixed order), then one integer reduction per column into the accumulator
+        // ---- one integer reduction per column into the accumulator.  A word carries the number of CTAs that have
+        // added to it in its top byte (every CTA adds to every word exactly once per layer), so readers need no
+        // separate barrier: a word whose count is complete is complete.
         __syncthreads();
-        if ((uint32_t)tid < csize) mbar_arrive_cluster(cluster_addr(cl_bar, (uint32_t)tid));
-        if (tid == 0) {
-            int ok = 1;
-            if (!mbar_try_wait_cluster(cl_bar, li & 1u)) {
-                const long long t0 = clock64();
-                while (!mbar_try_wait_cluster(cl_bar, li & 1u)) {
-                    if (clock64() - t0 > kSpinLimit) { atomicOr(status, kStatusBarrier); ok = 0; break; }
+        {
+            bool range_ok = true;
+#pragma unroll
+            for (int i = 0; i < 3; ++i) {
+                const int h = tid + i * kSlThreads;
+                if (h < H) {
+                    float v = s_part[h];
+                    if (!(fabsf(v) < kSlAccRange)) { range_ok = false; v = 0.f; }      // NaN too: the count must stay intact
+                    red_add_u64(acc + h, kSlAccOne + (unsigned long long)(__float2ll_rn(v * kSlAccScale) + kSlAccBias));
                 }
             }
-            s_flag[0] = ok;
+            if (!range_ok) atomicOr(status, kStatusRange);
         }
-        __syncthreads();
-        if (s_flag[0] != 0 && tid < cols_per_cta) {
-            const int h = (int)crank * cols_per_cta + tid;
-            float pv[8];
-#pragma unroll
-            for (uint32_t r = 0; r < 8; ++r) pv[r] = r < csize ? ld_cluster_f32(cluster_addr(s_part + h, r)) : 0.f;
-            float v = 0.f;
-#pragma unroll
-            for (uint32_t r = 0; r < 8; ++r) v += pv[r];
-            if (!(fabsf(v) < 1.0e9f)) atomicOr(status, kStatusRange);      // also true for NaN
-            red_add_u64(acc + h, (unsigned long long)__float2ll_rn(v * 4294967296.f));
-        }
-        UOCR_SL_TRACE(6);         // cluster sum sent
+        UOCR_SL_TRACE(6);         // partial outputs sent
 
-        // ---- barrier; while it is pending, the work for later layers that does not need this layer's result
-        grid_arrive(prm.bar);
-        if (cta == G - 1) {       // clear the accumulator that the layer after next will add to
+        // ---- while the other CTAs finish: the work for later layers that does not need this layer's result
+        if (cta == G - 1) {       // clear the accumulator that the layer after next will add to; the clearing is
+                                  // ordered before this CTA's next additions, which every later reader waits for
             unsigned long long *z = prm.acc + (size_t)((prm.acc_base + li + 2) % kSlAccBuffers) * H;
             for (int h = tid; h < H; h += kSlThreads) z[h] = 0ull;
+            __threadfence();
         }
         if (!last) {
             if (routed) load_router(s_layers[li + 1]);
             else fetch_unit(s_layers[li + 1].dec_units + (size_t)(kSlE * kSlRoutedPerSlot + fg) * Bl::kBytes);
         }
-        bar_target += G;
-        if (!grid_wait(prm.bar, bar_target, status, s_flag)) return;
-        UOCR_SL_TRACE(7);         // barrier passed
 
-        // ---- the layer's output = next layer's input: accumulator + residual, rounded to fp16
+        // ---- the layer's output = next layer's input: every accumulator word once all G CTAs have added to it,
+        // + residual, rounded to fp16.  The poll is bounded; a CTA that gives up raises the status word, which
+        // the others check while they wait.
+        {
+            unsigned long long w[3] = {0ull, 0ull, 0ull};
+            bool have = true;
+            const long long t0 = clock64();
+            const unsigned long long full = (unsigned long long)G;
+            for (uint32_t polls = 1;; ++polls) {
+                bool all = true;           // the thread's (up to) three words are requested together: one round trip per poll
 #pragma unroll
-        for (int i = 0; i < 3; ++i) {
-            const int h = tid + i * kSlThreads;
-            if (h < H) {
-                float v = (float)(long long)ldcg_u64(acc + h) * (1.0f / 4294967296.f);
-                if (li == 0) v += res0[i];
-                else if (prm.chain_residual) v += __half2float(s_x[h]);
-                s_x[h] = __float2half_rn(v);
+                for (int i = 0; i < 3; ++i) {
+                    const int h = tid + i * kSlThreads;
+                    if (h < H && (w[i] >> 56) != full) w[i] = ld_relaxed_u64(acc + h);
+                }
+#pragma unroll
+                for (int i = 0; i < 3; ++i) {
+                    const int h = tid + i * kSlThreads;
+                    if (h < H && (w[i] >> 56) != full) all = false;
+                }
+                if (all) break;
+                if ((polls & 15u) == 0u) {
+                    if (ld_volatile_u32(status) & (kStatusBarrier | kStatusCopy)) { have = false; break; }
+                    if (clock64() - t0 > kSpinLimit) { atomicOr(status, kStatusBarrier); have = false; break; }
+                }
+            }
+            if (__syncthreads_or(!have || s_flag[1] != 0)) return;
+            UOCR_SL_TRACE(7);         // every partial output is in
+#pragma unroll
+            for (int i = 0; i < 3; ++i) {
+                const int h = tid + i * kSlThreads;
+                if (h < H) {
+                    const long long sum = (long long)(w[i] & (kSlAccOne - 1ull)) - (long long)G * kSlAccBias;
+                    float v = (float)sum * (1.0f / kSlAccScale);
+                    if (li == 0) v += res0[i];
+                    else if (prm.chain_residual) v += __half2float(s_x[h]);
+                    s_x[h] = __float2half_rn(v);
+                }
             }
         }
         __syncthreads();
         if (last) {
             if (cta == 0)
                 for (int h = tid; h < H; h += kSlThreads) prm.out[h] = s_x[h];
-        } else {
+        } else if (!routed) {
             build_x_frags();
             __syncthreads();
         }
@@ -753,14 +767,13 @@ bool decode_sliced_supported(const DLayer *layers, uint32_t first, uint32_t coun
     return true;
 }
 
-// acc: decode_sliced_acc_bytes() of device memory, zero before the first launch; *acc_base and *bar_base carry the
-// accumulator rotation and the barrier count from launch to launch (reset both, and clear acc, after a failed launch).
+// acc: decode_sliced_acc_bytes() of device memory, zero before the first launch; *acc_base carries the accumulator
+// rotation from launch to launch (reset it, and clear acc, after a failed launch).
 cudaError_t launch_decode_sliced(const DLayer *h_layers, const DLayer *d_layers, uint32_t first, uint32_t count,
                                  const __half *hidden, const __half *residual0, int chain_residual, const float *injected,
-                                 __half *out, unsigned long long *acc, uint32_t *acc_base, unsigned long long *bar,
-                                 unsigned long long *bar_base, uint32_t *status, float *dbg_logits, float *dbg_probs,
-                                 uint32_t *ids_out, float *wts_out, unsigned long long *trace, cudaStream_t st,
-                                 uint64_t *launches) {
+                                 __half *out, unsigned long long *acc, uint32_t *acc_base, uint32_t *status,
+                                 float *dbg_logits, float *dbg_probs, uint32_t *ids_out, float *wts_out,
+                                 unsigned long long *trace, cudaStream_t st, uint64_t *launches) {
     int dev = 0;
     cudaError_t err = cudaGetDevice(&dev);
     if (err != cudaSuccess) return err;
@@ -769,7 +782,7 @@ cudaError_t launch_decode_sliced(const DLayer *h_layers, const DLayer *d_layers,
     prm.layers = d_layers; prm.first = first; prm.count = count;
     prm.hidden_in = hidden; prm.residual0 = residual0; prm.chain_residual = chain_residual;
     prm.injected = injected; prm.out = out; prm.acc = acc; prm.acc_base = *acc_base;
-    prm.bar = bar; prm.bar_base = *bar_base; prm.status = status;
+    prm.status = status;
     prm.dbg_logits = dbg_logits; prm.dbg_probs = dbg_probs; prm.ids_out = ids_out; prm.wts_out = wts_out; prm.trace = trace;
     cudaLaunchConfig_t cfg;
     cudaLaunchAttribute attrs[2];
@@ -781,7 +794,6 @@ cudaError_t launch_decode_sliced(const DLayer *h_layers, const DLayer *d_layers,
         err = cudaLaunchKernelEx(&cfg, decode_sliced_kernel<UOCR_QT_Q8>, prm);
     }
     if (err != cudaSuccess) return err;
-    *bar_base += (unsigned long long)kSlUnits * count;       // one barrier per layer
     *acc_base = (*acc_base + count) % kSlAccBuffers;
     ++*launches;
     return cudaSuccess;

@@ -42,10 +42,9 @@ size_t decode_sliced_acc_bytes();
 bool decode_sliced_supported(const DLayer *layers, uint32_t first, uint32_t count);
 cudaError_t launch_decode_sliced(const DLayer *h_layers, const DLayer *d_layers, uint32_t first, uint32_t count,
                                  const __half *hidden, const __half *residual0, int chain_residual, const float *injected,
-                                 __half *out, unsigned long long *acc, uint32_t *acc_base, unsigned long long *bar,
-                                 unsigned long long *bar_base, uint32_t *status, float *dbg_logits, float *dbg_probs,
-                                 uint32_t *ids_out, float *wts_out, unsigned long long *trace, cudaStream_t st,
-                                 uint64_t *launches);
+                                 __half *out, unsigned long long *acc, uint32_t *acc_base, uint32_t *status,
+                                 float *dbg_logits, float *dbg_probs, uint32_t *ids_out, float *wts_out,
+                                 unsigned long long *trace, cudaStream_t st, uint64_t *launches);
 cudaError_t launch_decode_stack(const DLayer *h_layers, const DLayer *d_layers, uint32_t first, uint32_t count,
                                 const __half *hidden, const __half *residual0, int chain_residual,
                                 const float *injected, __half *out, __half *hbuf0, __half *hbuf1, __half *mid,
@@ -595,9 +594,9 @@ static int layer_forward(uocr_cuda_context *ctx, uint32_t layer, const __half *d
     float *probs = dbg && dbg->d_router_probs ? dbg->d_router_probs : nullptr;
     if (n == 1 && ctx->fused_decode && ctx->sliced_decode && uocr::decode_sliced_supported(ctx->layers.data(), layer, 1)) {
         CU_TRY(ctx, uocr::launch_decode_sliced(ctx->layers.data(), ctx->d_layers, layer, 1, d_hidden, d_residual, 0,
-                                               d_injected, d_out, decode_accumulators(ctx), &ctx->acc_base,
-                                               barrier_counter(ctx), &ctx->bar_base, ctx->status, logits, probs, s.top_ids,
-                                               s.top_weights, nullptr, ctx->stream, &ctx->launches));
+                                               d_injected, d_out, decode_accumulators(ctx), &ctx->acc_base, ctx->status,
+                                               logits, probs, s.top_ids, s.top_weights, nullptr, ctx->stream,
+                                               &ctx->launches));
     } else if (n == 1 && ctx->fused_decode && uocr::decode_supported(ctx->layers.data(), layer, 1)) {
         CU_TRY(ctx, uocr::launch_decode_stack(ctx->layers.data(), ctx->d_layers, layer, 1, d_hidden, d_residual, 0,
                                               d_injected, d_out, (__half *)(ctx->arena + a.stack0),
@@ -652,9 +651,9 @@ static int stack_forward(uocr_cuda_context *ctx, uint32_t first, uint32_t count,
     __half *buf[2] = {(__half *)(ctx->arena + a.stack0), (__half *)(ctx->arena + a.stack1)};
     if (n == 1 && ctx->fused_decode && ctx->sliced_decode && uocr::decode_sliced_supported(ctx->layers.data(), first, count)) {
         CU_TRY(ctx, uocr::launch_decode_sliced(ctx->layers.data(), ctx->d_layers, first, count, d_hidden, d_hidden, 1, nullptr,
-                                               d_out, decode_accumulators(ctx), &ctx->acc_base, barrier_counter(ctx),
-                                               &ctx->bar_base, ctx->status, nullptr, nullptr, s.top_ids, s.top_weights,
-                                               ctx->decode_trace, ctx->stream, &ctx->launches));
+                                               d_out, decode_accumulators(ctx), &ctx->acc_base, ctx->status, nullptr,
+                                               nullptr, s.top_ids, s.top_weights, ctx->decode_trace, ctx->stream,
+                                               &ctx->launches));
         return 1;
     }
     if (n == 1 && ctx->fused_decode && uocr::decode_supported(ctx->layers.data(), first, count)) {
