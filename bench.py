@@ -404,7 +404,10 @@ def run_tokens(args, kind: str, rank: int, local_rank: int, world: int) -> None:
             "roofline": {"bound": "tensor", "kernel": "grouped_gemm_kernel (whole layer time used)", "achieved": achieved,
                          "peak": peak, "peak_kind": f"of {peak_kind}", "unit": "TFLOP/s", "frac": achieved / peak,
                          "frac_of_nominal_2250": achieved / NOMINAL_BF16_TFLOPS, "algorithmic_flops_per_step": flops,
-                         "traffic": None},
+                         # DRAM bytes of the dominant launch (routed gate/up GEMM) from one ncu capture of the 4096-token workload
+                         "traffic": 159.2e6 if (kind == "prefill" and args.routing == "zipf") else None,
+                         "traffic_source": "dram__bytes_read.sum + dram__bytes_write.sum of the routed gate/up launch "
+                                           "(profiles/grouped_gemm_kernel__prefill_q4_4096.md)"},
             "clocks": clocks, "step_ms_min_max": [min(times), max(times)],
         }
         if kind == "ep":
@@ -502,11 +505,11 @@ def run_decode(args, rank: int, local_rank: int, world: int) -> None:
             "e2e": {"value": e2e_ms * 1e3 / world, "unit": "us/token", "h2d_bytes_per_step": FULL["H"] * 2,
                     "d2h_bytes_per_step": FULL["H"] * 2, "timer": "host wall clock around uocr_cuda_moe_stack_forward_host"},
             "gpu_launches": int(launches),
-            "roofline": {"bound": "hbm", "kernel": "decode_stack_kernel (one launch = one step when the persistent kernel runs)", "achieved": achieved,
+            "roofline": {"bound": "hbm", "kernel": "decode_sliced_kernel (one launch = one step)", "achieved": achieved,
                          "peak": peak, "peak_kind": f"of {peak_kind}", "unit": "GB/s", "frac": achieved / peak,
                          "frac_of_nominal_8TBs": achieved / NOMINAL_HBM_GBS, "algorithmic_bytes_per_step": step_bytes,
-                         "traffic": 167.9e6, "traffic_source": "dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture "
-                         "of this kernel on this workload (profiles/decode_stack_kernel__decode_q4_11layers.md)"},
+                         "traffic": 165.4e6, "traffic_source": "dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture "
+                         "of this kernel on this workload (profiles/decode_sliced_kernel__decode_q4_11layers.md)"},
             "clocks": clocks,
             "per_layer_us": ms_per_step * 1e3 / N_LAYERS,
             "step_ms_min_max": [min(times_ms), max(times_ms)],
