@@ -2,22 +2,23 @@
 //
 // After the dispatch plan the (token, slot) pairs of one expert are contiguous, so each expert is a
 // dense product.  Both products are computed "weights as rows":
-//     gate/up :  [128 weight rows] x [<=128 tokens]  over K = H,  two accumulators (gate, up) ->
+//     gate/up :  [2 x 128 weight rows] x [<=128 tokens]  over K = H,  two accumulators (gate, up) ->
 //                mid[pos][f] = fp16( silu(gate) * up )
-//     down    :  [128 weight rows] x [<=128 tokens]  over K = F (or S) -> down_out[pos][h] = fp16(acc)
+//     down    :  [128 weight rows] x [<=256 tokens]  over K = F (or S) -> down_out[pos][h] = fp16(acc)
 // With the weights on the M side of the MMA a cold expert with a handful of tokens pads its token
 // count to 16, not to 128, which matters under Zipf-skewed routing.
 //
-// One CTA computes one tile; two CTAs share an SM (<= 256 TMEM columns and ~100 KB shared memory
-// each), so one tile's epilogue overlaps the other's main loop.  Per 64-wide K block (= one scale
-// group of the weight formats, = one 128-byte swizzle row of fp16):
-//   warps 0-7  two threads per weight row of the tile: each loads its half of the row's packed bytes
-//              (16 B for Q4_0) with 128-bit loads, turns them into fp16( level * scale ) in registers
-//              and writes them into the stage's 128B-swizzled K-major tile; no dequantised copy of a
-//              weight ever reaches global memory.  The same warps run the epilogue.
-//   warp 8     one thread issues the TMA tile load (cp.async.bulk.tensor) of the activation tile.
-//   warp 9     one thread issues tcgen05.mma (kind::f16, fp32 accumulators in TMEM) and commits the
-//              stage back to the producers; the warp also owns the TMEM allocation.
+// One CTA (576 threads, one per SM: it owns all 512 tensor-memory columns) computes one tile.  Per 64-wide K
+// block (= one scale group of the weight formats, = one 128-byte swizzle row of fp16):
+//   warps 0-15 two threads per weight row and matrix: each loads its share of the row's packed bytes with 128-bit
+//              loads (several K blocks ahead), turns them into fp16( level * scale ) in registers and stores
+//              them with tcgen05.st straight into a ring of tensor-memory slots, the A operand of the MMA:
+//              no dequantised weight ever reaches shared or global memory.  A slot is published one block late,
+//              so the stores' latency hides behind the next conversion.  The same warps run the epilogue
+//              (tcgen05.ld, SwiGLU with the fast exponential, fp16 stores).
+//   warp 16    one thread issues the TMA tile loads (cp.async.bulk.tensor) of the activation tile.
+//   warp 17    one thread issues tcgen05.mma (kind::f16, A from tensor memory, B from shared memory, fp32
+//              accumulators in tensor memory) and commits the slots back; the warp also owns the TMEM allocation.
 // Every wait is bounded; on a time-out the CTA raises a status bit, drains and returns.
 #include <cuda.h>
 #include <cudaTypedefs.h>
