@@ -322,15 +322,21 @@ __global__ void __launch_bounds__(kSlThreads, 1) decode_sliced_kernel(SlicedPara
     __half dslo[kSlBlocksPerWarp], dshi[kSlBlocksPerWarp];
     // everything of one unit: bulk copies of the gate/up fragments (chunk c completes barrier c) and scales into
     // shared memory, plain loads of the down fragments and scales into registers
-    auto fetch_unit = [&](const uint8_t *blob) {
+    // (one thread issues the copies in the order they are needed, and a routed CTA asks for its down fragments only
+    // once the first chunk is there: all routed CTAs fetch at the same moment and HBM serves what was asked first)
+    auto fetch_gate_up = [&](const uint8_t *blob) {
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        if (tid < kSlChunks) {
-            mbar_expect_tx(&bars[tid], kChunkBytes);
-            bulk_g2s(smem + Sm::kW + tid * kChunkBytes, blob + Bl::kGu + (size_t)tid * kChunkBytes, kChunkBytes, &bars[tid]);
-        } else if (tid == kSlChunks) {
+        if (tid == 0) {
             mbar_expect_tx(sc_bar, Bl::kGuScBytes);
             bulk_g2s(s_sc, blob + Bl::kGuSc, Bl::kGuScBytes, sc_bar);
+#pragma unroll
+            for (int c = 0; c < kSlChunks; ++c) {
+                mbar_expect_tx(&bars[c], kChunkBytes);
+                bulk_g2s(smem + Sm::kW + c * kChunkBytes, blob + Bl::kGu + (size_t)c * kChunkBytes, kChunkBytes, &bars[c]);
+            }
         }
+    };
+    auto fetch_down = [&](const uint8_t *blob) {
         const uint4 *dn = reinterpret_cast<const uint4 *>(blob + Bl::kDn);
         const __half *dsc = reinterpret_cast<const __half *>(blob + Bl::kDnSc);
 #pragma unroll
@@ -346,6 +352,7 @@ __global__ void __launch_bounds__(kSlThreads, 1) decode_sliced_kernel(SlicedPara
             dshi[bi] = dsc[16 * blk + 8 + g];
         }
     };
+    auto fetch_unit = [&](const uint8_t *blob) { fetch_gate_up(blob); fetch_down(blob); };
     // This CTA's quarter of the router matrix (experts 16 crank .. +15, fp16 [E][H]) as MMA A fragments: warp w holds
     // columns 80 w .. 80 w + 79 (five k steps), lane (g, t) the columns 4t .. 4t + 3 of each step for rows g and g + 8.
     auto load_router = [&](const DLayer &L) {
@@ -452,8 +459,9 @@ __global__ void __launch_bounds__(kSlThreads, 1) decode_sliced_kernel(SlicedPara
         }
         uint32_t ex = routed ? s_ids[7] : 0u;       // expert whose weights this CTA fetches
       for (bool first = true;; first = false) {
+        const uint8_t *blob = L.dec_units + (size_t)(ex * kSlRoutedPerSlot + fg) * Bl::kBytes;
         if (routed) {
-            fetch_unit(L.dec_units + (size_t)(ex * kSlRoutedPerSlot + fg) * Bl::kBytes);
+            fetch_gate_up(blob);
             if (first) { build_x_frags(); __syncthreads(); }
         }
         UOCR_SL_TRACE(2);         // weight fetches issued
@@ -470,7 +478,10 @@ __global__ void __launch_bounds__(kSlThreads, 1) decode_sliced_kernel(SlicedPara
 #pragma unroll
                 for (int ch = 0; ch < kSlChunks; ++ch) {
                     got = mbar_wait(&bars[ch], copy_phase, status, s_flag) && got;
-                    if (ch == 0) UOCR_SL_TRACE(3);     // first chunk is in shared memory
+                    if (ch == 0) {
+                        UOCR_SL_TRACE(3);              // first chunk is in shared memory
+                        if (routed) fetch_down(blob);
+                    }
 #pragma unroll
                     for (int q = 0; q < 2; ++q) {
                         const int Gi = 4 * ch + 2 * q + kh;
