@@ -80,6 +80,24 @@ class ClockSampler:
         except OSError:
             self.proc = None
 
+    def samples(self) -> int:
+        try:
+            return sum(1 for r in Path(self.file.name).read_text().splitlines() if r.count(",") >= 8)
+        except OSError:
+            return 0
+
+    def hold(self, step, minimum: int = 2, limit_s: float = 4.0) -> None:
+        """Keep the same load running (untimed) until nvidia-smi has delivered `minimum` samples: a timed region of a
+        few milliseconds is over before its first sample."""
+        if self.proc is None:
+            return
+        import torch
+        t0 = time.perf_counter()
+        while self.samples() < minimum and time.perf_counter() - t0 < limit_s:
+            for _ in range(20):
+                step()
+            torch.cuda.synchronize()
+
     def stop(self) -> dict:
         out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
         if self.proc is None:
@@ -336,6 +354,13 @@ def run_tokens(args, kind: str, rank: int, local_rank: int, world: int) -> None:
     launches0 = ctx.kernel_launches
     times = timed(step, args.steps, warm)
     launches = (ctx.kernel_launches - launches0) * args.steps // (args.steps + warm)
+    if world == 1:
+        if sampler:
+            sampler.hold(step)
+    else:                      # the same number of extra steps on every rank (the step holds collectives)
+        for _ in range(300):
+            step()
+        torch.cuda.synchronize()
     plan = layer.last_plan
 
     def e2e_step():
@@ -468,6 +493,8 @@ def run_decode(args, rank: int, local_rank: int, world: int) -> None:
     torch.cuda.synchronize()
     launches = ctx.kernel_launches - launches0
     times_ms = [s.elapsed_time(e) for s, e in zip(starts, ends)]
+    if sampler:
+        sampler.hold(step)
     ms_per_step = sum(times_ms) / len(times_ms)
     ctx.synchronize()
 
