@@ -1,5 +1,5 @@
 // Waiting primitives shared by the persistent single-token decode kernels: mbarrier and bulk-copy wrappers,
-// and a grid-wide barrier over a monotonic counter.  Every wait is bounded: after ~2 s it sets a bit in the
+// relaxed / acquire loads for polling, and a grid-wide barrier over a monotonic counter.  Every wait is bounded: after ~2 s it sets a bit in the
 // device status word, every CTA sees the bit at its next wait and returns.
 #pragma once
 
@@ -92,34 +92,6 @@ __device__ __forceinline__ bool grid_barrier(unsigned long long *ctr, unsigned l
         }
         __threadfence();
         if (s_flag[1] != 0) ok = 0;     // a bulk copy of this CTA timed out: leave; the others time out in turn
-        *s_flag = ok;
-    }
-    __syncthreads();
-    return *s_flag != 0;
-}
-
-// The same barrier in two halves, for work that should overlap the wait: grid_arrive() publishes the CTA's writes
-// and counts it in; grid_wait() returns once `target` arrivals are there (false: timed out or another CTA failed).
-__device__ __forceinline__ void grid_arrive(unsigned long long *ctr) {
-    __syncthreads();
-    if (threadIdx.x == 0) red_release_add_u64(ctr, 1ULL);
-}
-__device__ __forceinline__ bool grid_wait(const unsigned long long *ctr, unsigned long long target, uint32_t *status,
-                                          int *s_flag) {
-    if (threadIdx.x == 0) {
-        int ok = 1;
-        if (ld_relaxed_u64(ctr) < target) {
-            const long long t0 = clock64();
-            uint32_t polls = 0;
-            while (ld_relaxed_u64(ctr) < target) {
-                if ((++polls & 63u) == 0u) {
-                    if (ld_volatile_u32(status) & (kStatusBarrier | kStatusCopy)) { ok = 0; break; }
-                    if (clock64() - t0 > kSpinLimit) { atomicOr(status, kStatusBarrier); ok = 0; break; }
-                }
-            }
-        }
-        __threadfence();
-        if (s_flag[1] != 0) ok = 0;
         *s_flag = ok;
     }
     __syncthreads();
