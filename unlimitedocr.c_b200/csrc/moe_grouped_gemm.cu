@@ -287,6 +287,11 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap act_map, GemmParams p) {
         const uint8_t *rowp = ((GATEUP && grp) ? p.w1 : p.w0) + (size_t)expert * p.expert_stride_bytes + grow * p.row_bytes;
         constexpr int kAhead = PackedBlock<QT>::kAhead, kVecs = PackedBlock<QT>::kVecs;
         const int sm = GATEUP ? grp : 0;                              // which matrix's scales this thread uses
+        // the first packed blocks are requested before the scales are waited for: one memory latency, not two
+        uint4 v[kAhead][kVecs];
+#pragma unroll
+        for (int d = 0; d < kAhead; ++d)
+            if ((uint32_t)d < kblocks) load_block<QT>(rowp, d, h, v[d]);
         // the row's scales go to shared memory once ([matrix][k block][row]): the K loop never waits on a 2-byte load
         // (all loads are issued before the first store: an unrolled, predicated batch, not a dependent chain)
         if (QT != UOCR_QT_F16 && h == 0 && (GATEUP || grp == 0)) {
@@ -298,10 +303,6 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap act_map, GemmParams p) {
             for (int kb = 0; kb < Sh::kMaxKBlocks; ++kb)
                 if ((uint32_t)kb < kblocks) s_scales[(sm * kblocks + kb) * kTileM + r] = t[kb];
         }
-        uint4 v[kAhead][kVecs];
-#pragma unroll
-        for (int d = 0; d < kAhead; ++d)
-            if ((uint32_t)d < kblocks) load_block<QT>(rowp, d, h, v[d]);
         asm volatile("bar.sync 1, %0;" ::"n"(kProducerThreads) : "memory");     // scales visible to every thread of a row
         // this thread's TMEM lane, its 8 columns inside a 16-column sub-block, and its matrix inside a slot
         const uint32_t lane_addr = ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)h * 8 + (GATEUP ? (uint32_t)grp * 32 : 0u);
