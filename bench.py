@@ -316,9 +316,27 @@ def run_tokens(args, kind: str, rank: int, local_rank: int, world: int) -> None:
     d_r = r_local.cuda().view(torch.float16)
     d_out = torch.zeros_like(d_h)
     host_out = torch.empty((n_local, FULL["H"]), dtype=torch.float16).pin_memory()
-    layer = pkg.ep.ExpertParallelLayer(ctx, 0, FULL["E"], FULL["K"], FULL["H"], rank=rank, world=world,
-                                       dist_module=dist if world > 1 else None)
-    layer.reserve(n_local, n_total * FULL["K"])
+    # the exchange: fused into the library's kernels over peer memory (default), or NCCL all-to-all between its phases
+    exchange, layer = "nccl all_to_all_single", None
+    if kind == "ep" and world > 1 and args.exchange == "peer":
+        why = ""
+        try:
+            layer = pkg.ep.PeerExpertParallelLayer(ctx, 0, FULL["E"], FULL["K"], FULL["H"], row_capacity=n_total * FULL["K"],
+                                                   rank=rank, world=world, dist_module=dist)
+            exchange = "peer memory (CUDA IPC over NVLink), fused into gather and combine"
+        except Exception as e:      # e.g. no peer access between the devices: every rank must then take the other path
+            why = str(e)[:200]
+        ok = torch.tensor([1 if layer is not None else 0], device="cuda")
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        if int(ok.item()) == 0:
+            if layer is not None:
+                layer.close()
+            layer = None
+            exchange = f"nccl all_to_all_single (peer-memory set-up failed on a rank: {why})"
+    if layer is None:
+        layer = pkg.ep.ExpertParallelLayer(ctx, 0, FULL["E"], FULL["K"], FULL["H"], rank=rank, world=world,
+                                           dist_module=dist if world > 1 else None)
+        layer.reserve(n_local, n_total * FULL["K"])
 
     def step():
         if kind == "prefill":
@@ -421,6 +439,7 @@ def run_tokens(args, kind: str, rank: int, local_rank: int, world: int) -> None:
             "config": {"workload": w["workload"] if args.routing == "zipf" else w["workload"].replace("Zipf(1.1)-skewed", "uniform"),
                        "tokens_per_step": n_total, "qtype": "q4_0", "routing": args.routing,
                        "parallelism": f"ep{world}" if kind == "ep" else "1 gpu",
+                       **({"exchange": exchange} if kind == "ep" and world > 1 else {}),
                        "l2": "flushed between timed iterations (256 MiB written, then 256 MiB read)"},
             "e2e": {"value": n_total / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": 2 * n_local * FULL["H"] * 2,
                     "d2h_bytes_per_step": n_local * FULL["H"] * 2,
@@ -560,6 +579,7 @@ def main() -> None:
     ap.add_argument("--cpu-layers", type=int, default=2, help="layers of the stack the CPU baseline samples")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--routing", default="zipf", choices=["zipf", "uniform"], help="expert popularity of the prefill / ep workloads")
+    ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"], help="ep workload: how rows travel between the GPUs")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))

@@ -239,8 +239,10 @@ UOCR_CUDA_API int uocr_cuda_moe_ep_experts(uocr_cuda_context *ctx, uint32_t laye
                                            uint32_t n_local_experts, uint32_t n_sources,
                                            const uint32_t *h_segment_counts, const void *d_rows_in_f16,
                                            void *d_rows_out_f16, char *error, size_t error_size);
-/* Shared MLP of this rank's tokens into the context's scratch.  Independent of the exchange, so a host can
- * run it while the rows travel.  Must precede the combine call of the same layer call. */
+/* Shared MLP of this rank's tokens into the context's scratch.  Independent of the exchange: it is queued on a
+ * second stream of the context (after everything queued so far on the context's stream) and runs beside whatever
+ * the caller queues next; the combine call of the same layer call waits for it.  d_hidden_f16 must stay unchanged
+ * until then.  Must precede the combine call of the same layer call. */
 UOCR_CUDA_API int uocr_cuda_moe_ep_shared(uocr_cuda_context *ctx, uint32_t layer, const void *d_hidden_f16,
                                           uint32_t n_tokens, char *error, size_t error_size);
 /* d_rows_back[pos][H]: the expert outputs for this rank's pairs, in the order dispatch produced them.
@@ -248,6 +250,41 @@ UOCR_CUDA_API int uocr_cuda_moe_ep_shared(uocr_cuda_context *ctx, uint32_t layer
 UOCR_CUDA_API int uocr_cuda_moe_ep_combine(uocr_cuda_context *ctx, uint32_t layer, const void *d_rows_back_f16,
                                            const void *d_residual_f16, uint32_t n_tokens, void *d_out_f16,
                                            char *error, size_t error_size);
+
+/* ---- expert parallelism over peer memory (no reference counterpart) --------------------------------------------
+ * The same layer call with the exchange fused into the library's kernels: every rank (one process per GPU of one
+ * node) owns two buffers of row_capacity rows x hidden fp16, "received rows" and "expert outputs", and maps the
+ * other ranks' buffers through CUDA IPC.  The gather then writes each pair's row straight into the owner's
+ * buffer and the combine reads each pair's output row straight from it, over NVLink, so no separate all-to-all
+ * runs.  What the caller provides: the per-rank counts (one small all_gather of d_expert_offsets), and two
+ * barriers over the group per call (after scatter: all rows have landed; after experts: all outputs are
+ * written).  With one rank the calls reproduce uocr_cuda_moe_layer_forward.
+ *
+ * create:   allocates this rank's buffers; handles_out receives 128 bytes (two CUDA IPC handles) to be gathered.
+ * open:     all_handles = the world x 128 bytes of every rank, in rank order.  At most 16 ranks.
+ * dispatch: router + dispatch plan on this rank's tokens; d_expert_offsets[E+1] as in uocr_cuda_moe_ep_dispatch.
+ * scatter:  h_dst_row0[E]: for every expert, the row of ITS OWNER's "received rows" buffer where this rank's
+ *           rows start.  The owner of expert e is rank e / (E / world); its buffer holds, for source rank 0, 1, ...
+ *           in turn, the rows of each of its experts in turn.
+ * experts:  this rank's experts on its received rows -> its "expert outputs", same row order;
+ *           h_segment_counts[world][E / world] as in uocr_cuda_moe_ep_experts.
+ * combine:  out = fp16( sum_slot weight * output row of the pair (read from its owner) + shared MLP [+ residual] );
+ *           uocr_cuda_moe_ep_shared must have run for these tokens.
+ * A row index outside the buffers (inconsistent counts) is never dereferenced: it raises a status bit that
+ * uocr_cuda_context_synchronize reports. */
+UOCR_CUDA_API int uocr_cuda_moe_ep_peer_create(uocr_cuda_context *ctx, uint32_t hidden_size, uint64_t row_capacity,
+                                               void *handles_out, char *error, size_t error_size);
+UOCR_CUDA_API int uocr_cuda_moe_ep_peer_open(uocr_cuda_context *ctx, uint32_t world, uint32_t rank, const void *all_handles,
+                                             char *error, size_t error_size);
+UOCR_CUDA_API void uocr_cuda_moe_ep_peer_destroy(uocr_cuda_context *ctx);
+UOCR_CUDA_API int uocr_cuda_moe_ep_peer_dispatch(uocr_cuda_context *ctx, uint32_t layer, const void *d_hidden_f16,
+                                                 uint32_t n_tokens, uint32_t *d_expert_offsets, char *error, size_t error_size);
+UOCR_CUDA_API int uocr_cuda_moe_ep_peer_scatter(uocr_cuda_context *ctx, uint32_t layer, const void *d_hidden_f16,
+                                                uint32_t n_tokens, const uint32_t *h_dst_row0, char *error, size_t error_size);
+UOCR_CUDA_API int uocr_cuda_moe_ep_peer_experts(uocr_cuda_context *ctx, uint32_t layer, uint32_t n_sources,
+                                                const uint32_t *h_segment_counts, char *error, size_t error_size);
+UOCR_CUDA_API int uocr_cuda_moe_ep_peer_combine(uocr_cuda_context *ctx, uint32_t layer, const void *d_residual_f16,
+                                                uint32_t n_tokens, void *d_out_f16, char *error, size_t error_size);
 
 #ifdef __cplusplus
 }

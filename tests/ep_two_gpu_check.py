@@ -46,6 +46,17 @@ def main():
         torch.cuda.synchronize()
         same = torch.equal(out, want[lo:hi])
         diff = float((out.float() - want[lo:hi].float()).abs().max())
+        # the same layer with the exchange over peer memory (CUDA IPC mappings of the other ranks' buffers)
+        peer = pkg.ep.PeerExpertParallelLayer(ctx, 0, dims["E"], dims["K"], dims["H"], row_capacity=n_total * dims["K"],
+                                              rank=rank, world=world, dist_module=dist)
+        for _ in range(2):
+            out2 = torch.zeros_like(mine)
+            plan2 = peer.forward(mine, out2, residual=r_all[lo:hi].contiguous())
+            ctx.synchronize()
+            torch.cuda.synchronize()
+            same = same and torch.equal(out2, want[lo:hi]) and plan2.rows_received == plan.rows_received
+        dist.barrier()
+        peer.close()
         print(f"rank {rank}: rows received {plan.rows_received}, max diff {diff:.3e}, {'EP_OK' if same else 'EP_MISMATCH'}", flush=True)
     dist.barrier()
     dist.destroy_process_group()

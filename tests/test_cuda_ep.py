@@ -61,6 +61,37 @@ def test_phases_on_one_gpu_equal_the_layer_call(pkg, port, qname, n):
     assert np.max(np.abs(got[same] - o.out[same])) <= 2e-2
 
 
+def test_peer_memory_phases_on_one_gpu_equal_the_layer_call(pkg):
+    """The peer-memory form of the phases with a group of one rank: the scatter writes into this rank's own exchange
+    buffer and the combine reads from it; the result equals uocr_cuda_moe_layer_forward bit for bit, twice in a row."""
+    rng = np.random.default_rng(43)
+    n = 300
+    L = quant.synth_layer(rng, expert_qtype=quant.QTYPE_Q4_0, logit_bias=quant.zipf_logit_bias(rng, 64), **FULL)
+    hidden = quant.synth_activations(rng, n, FULL["H"])
+    resid = quant.synth_activations(rng, n, FULL["H"])
+    with pkg.Context() as ctx:
+        ctx.map_layer(L)
+        ctx.allocate_runtime_arenas(n)
+        ctx.set_stream(torch.cuda.current_stream().cuda_stream)
+        d_h = torch.from_numpy(hidden).cuda().view(torch.float16)
+        d_r = torch.from_numpy(resid).cuda().view(torch.float16)
+        want = torch.zeros_like(d_h)
+        ctx.layer_forward(0, d_h, n, want, residual=d_r)
+        layer = pkg.ep.PeerExpertParallelLayer(ctx, 0, FULL["E"], FULL["K"], FULL["H"], row_capacity=n * FULL["K"])
+        for _ in range(2):
+            got = torch.zeros_like(d_h)
+            plan = layer.forward(d_h, got, residual=d_r)
+            ctx.synchronize()
+            assert plan.rows_received == n * FULL["K"]
+            assert torch.equal(got, want)
+        # offsets that point outside the buffer are refused on the device, not dereferenced
+        ctx.ep_peer_dispatch(0, d_h, n, layer._offsets)
+        ctx.ep_peer_scatter(0, d_h, n, np.full(64, n * FULL["K"], np.uint32))
+        with pytest.raises(pkg.UocrCudaError, match="exchange buffers"):
+            ctx.synchronize()
+        layer.close()
+
+
 def test_experts_phase_rejects_more_rows_than_the_arena_holds(pkg):
     rng = np.random.default_rng(42)
     L = quant.synth_layer(rng, expert_qtype=quant.QTYPE_Q8_0, **FULL)
@@ -79,7 +110,7 @@ def test_experts_phase_rejects_more_rows_than_the_arena_holds(pkg):
 def test_two_gpu_expert_parallel_equals_single_gpu(pkg):
     n_gpus = torch.cuda.device_count()
     if n_gpus < 2:
-        pytest.skip("needs two GPUs (run under gpurun --gpus 2)")
+        pytest.skip("needs two GPUs")
     world = 2
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr", "127.0.0.1",
            "--master-port", str(29600 + os.getpid() % 1000), str(ROOT / "tests" / "ep_two_gpu_check.py")]

@@ -139,3 +139,29 @@ def test_two_rank_gloo_forward_matches_reference():
     assert all(results[r][1] for r in range(world)), "rows were lost or duplicated in the exchange"
     # rank 0 owns expert 0 and must have received one row per rank-1 token for it
     assert results[0][2][1][0] == n_by_rank[1]
+
+
+def test_peer_scatter_offsets_match_the_owner_side_row_order():
+    """dst_rows_from_counts: where a rank's rows for an expert start in the owner's buffer.  Simulated exchange: every
+    rank writes row labels at its offsets; each owner must then hold, source by source and expert by expert, exactly
+    the segments plan_from_counts announces, with no gap and no overlap."""
+    ep = load_ep()
+    rng = np.random.default_rng(5)
+    world, n_experts = 4, 64
+    per = n_experts // world
+    counts = rng.integers(0, 40, size=(world, n_experts))
+    counts[2, 5] = 0
+    buffers = [dict() for _ in range(world)]
+    for r in range(world):
+        dst = ep.dst_rows_from_counts(counts, r)
+        for e in range(n_experts):
+            for i in range(counts[r, e]):
+                row = int(dst[e]) + i
+                assert row not in buffers[e // per]
+                buffers[e // per][row] = (r, e)
+    for owner in range(world):
+        plan = ep.plan_from_counts(counts, owner)
+        assert sorted(buffers[owner]) == list(range(plan.rows_received))
+        want = [(s, owner * per + e) for s in range(world) for e in range(per) for _ in range(plan.recv_counts[s, e])]
+        assert [buffers[owner][i] for i in range(plan.rows_received)] == want
+

@@ -162,6 +162,10 @@ __device__ __forceinline__ void row_dot(const uint8_t *wrow, const __half *srow,
 
 __device__ __forceinline__ float silu_f32(float v) { return v / (1.0f + __expf(-v)); }
 
+// One buffer per rank of an expert-parallel group on one node (this rank's own and the peers' mapped ones).
+constexpr int kMaxPeers = 16;
+struct PeerBuffers { __half *p[kMaxPeers]; };
+
 // ---- launch interface (implemented in the kernel files, called by the host API) ----------
 struct LaunchCounter { uint64_t *count; };
 

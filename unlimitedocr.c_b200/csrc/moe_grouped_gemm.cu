@@ -638,6 +638,100 @@ __global__ void combine_sorted_kernel(const __half *__restrict__ down_out, const
     *reinterpret_cast<uint4 *>(out + (size_t)t * H + c) = o;
 }
 
+// ---------------------------------------------------------------- peer-memory exchange (expert parallelism)
+// One node, one process per GPU: every rank has mapped the other ranks' "received rows" and "expert outputs"
+// buffers (CUDA IPC).  The two kernels below are the gather and the combine with the exchange fused in: rows are
+// written straight into the owner's buffer, and read back straight from it, over NVLink, with plain stores and
+// loads (no TMA multicast, no library kernel on peer memory).
+//
+// Expert e is owned by rank e / experts_per_rank.  dst_row0[e]: row of the owner's buffer where this rank's rows
+// for expert e start (the host derives it from the gathered per-rank counts).
+constexpr uint32_t kStatusPeerRange = 32u;
+
+// peer.p[owner][row][:] = hidden[token of the pos-th pair in expert order][:]
+__global__ void scatter_rows_peer_kernel(const __half *__restrict__ hidden, const uint32_t *__restrict__ pair_rows,
+                                         const uint32_t *__restrict__ expert_offsets, uint32_t E, uint32_t K, uint32_t H,
+                                         uint32_t experts_per_rank, const uint32_t *__restrict__ dst_row0, PeerBuffers peer,
+                                         unsigned long long row_capacity, uint32_t *status) {
+    const uint32_t total = expert_offsets[E];
+    const uint32_t pos = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+    if (pos >= total) return;
+    uint32_t lo = 0, hi = E;                    // the expert whose range [offsets[e], offsets[e + 1]) holds pos
+    while (hi - lo > 1) {
+        const uint32_t mid = (lo + hi) >> 1;
+        if (expert_offsets[mid] <= pos) lo = mid; else hi = mid;
+    }
+    const uint32_t e = lo;
+    const unsigned long long row = (unsigned long long)dst_row0[e] + (pos - expert_offsets[e]);
+    if (row >= row_capacity) {                  // never write outside a peer's buffer
+        if (lane == 0) atomicOr(status, kStatusPeerRange);
+        return;
+    }
+    const uint4 *src = reinterpret_cast<const uint4 *>(hidden + (size_t)(pair_rows[pos] / K) * H);
+    uint4 *dst = reinterpret_cast<uint4 *>(peer.p[e / experts_per_rank] + (size_t)row * H);
+    for (uint32_t i = lane; i < H / 8; i += 32) dst[i] = __ldg(src + i);
+}
+
+__device__ __forceinline__ uint4 ld_volatile_v4(const uint4 *p) {
+    uint4 v;
+    asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+
+// out[t][h] = fp16( fma chain over slots of weight * (owner's output row of the pair)[h] + shared_out[t][h] + residual )
+__global__ void combine_peer_kernel(PeerBuffers peer, const __half *__restrict__ shared_out, const __half *__restrict__ residual,
+                                    const uint32_t *__restrict__ inverse, const uint32_t *__restrict__ top_ids,
+                                    const float *__restrict__ weights, const uint32_t *__restrict__ expert_offsets,
+                                    const uint32_t *__restrict__ dst_row0, uint32_t experts_per_rank, uint32_t E, uint32_t n,
+                                    uint32_t H, uint32_t K, unsigned long long row_capacity, uint32_t *status,
+                                    __half *__restrict__ out) {
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;       // one thread per 8 outputs
+    const uint32_t per_row = H / 8;
+    if (idx >= (size_t)n * per_row) return;
+    const uint32_t t = (uint32_t)(idx / per_row), c = (uint32_t)(idx % per_row) * 8;
+    float acc[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+    for (uint32_t s = 0; s < K; ++s) {
+        const uint32_t pos = inverse[t * K + s], e = top_ids[t * K + s];
+        if (pos == 0xffffffffu || e >= E) continue;
+        const unsigned long long row = (unsigned long long)dst_row0[e] + (pos - expert_offsets[e]);
+        if (row >= row_capacity) { atomicOr(status, kStatusPeerRange); continue; }
+        const float w = weights[t * K + s];
+        const uint4 v = ld_volatile_v4(reinterpret_cast<const uint4 *>(peer.p[e / experts_per_rank] + (size_t)row * H + c));
+        const __half2 *h = reinterpret_cast<const __half2 *>(&v);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 f = __half22float2(h[i]);
+            acc[2 * i] = fmaf(w, f.x, acc[2 * i]);
+            acc[2 * i + 1] = fmaf(w, f.y, acc[2 * i + 1]);
+        }
+    }
+    {
+        const uint4 v = *reinterpret_cast<const uint4 *>(shared_out + (size_t)t * H + c);
+        const __half2 *h = reinterpret_cast<const __half2 *>(&v);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 f = __half22float2(h[i]);
+            acc[2 * i] += f.x; acc[2 * i + 1] += f.y;
+        }
+    }
+    if (residual) {
+        const uint4 v = *reinterpret_cast<const uint4 *>(residual + (size_t)t * H + c);
+        const __half2 *h = reinterpret_cast<const __half2 *>(&v);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 f = __half22float2(h[i]);
+            acc[2 * i] += f.x; acc[2 * i + 1] += f.y;
+        }
+    }
+    uint4 o;
+    __half2 *oh = reinterpret_cast<__half2 *>(&o);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) oh[i] = __floats2half2_rn(acc[2 * i], acc[2 * i + 1]);
+    *reinterpret_cast<uint4 *>(out + (size_t)t * H + c) = o;
+}
+
 // ---------------------------------------------------------------------------- host side
 static PFN_cuTensorMapEncodeTiled_v12000 g_encode = nullptr;
 
@@ -809,6 +903,29 @@ cudaError_t launch_gather_sorted(const DLayer &L, const Scratch &S, const __half
                                  cudaStream_t st, uint64_t *launches) {
     const uint32_t pairs = n * L.K;
     gather_rows_kernel<<<(pairs * 32 + 255) / 256, 256, 0, st>>>(hidden, S.pair_rows, S.expert_offsets, L.E, L.K, L.H, rows_out);
+    ++*launches;
+    return cudaGetLastError();
+}
+
+// rows of this rank's pairs -> the owners' "received rows" buffers
+cudaError_t launch_scatter_peer(const DLayer &L, const Scratch &S, const __half *hidden, uint32_t n, uint32_t experts_per_rank,
+                                const uint32_t *dst_row0, const PeerBuffers &recv, unsigned long long row_capacity,
+                                cudaStream_t st, uint64_t *launches) {
+    const uint32_t pairs = n * L.K;
+    scatter_rows_peer_kernel<<<(pairs * 32 + 255) / 256, 256, 0, st>>>(hidden, S.pair_rows, S.expert_offsets, L.E, L.K, L.H,
+                                                                       experts_per_rank, dst_row0, recv, row_capacity, S.status);
+    ++*launches;
+    return cudaGetLastError();
+}
+
+// combine that reads the pairs' expert outputs from the owners' buffers
+cudaError_t launch_combine_peer(const DLayer &L, const Scratch &S, const GemmScratch &G, const PeerBuffers &done,
+                                uint32_t experts_per_rank, const uint32_t *dst_row0, unsigned long long row_capacity,
+                                const __half *residual, uint32_t n, __half *out, cudaStream_t st, uint64_t *launches) {
+    const size_t work = (size_t)n * (L.H / 8);
+    combine_peer_kernel<<<(unsigned)((work + 255) / 256), 256, 0, st>>>(done, G.shared_out, residual, S.inverse, S.top_ids,
+                                                                        S.top_weights, S.expert_offsets, dst_row0,
+                                                                        experts_per_rank, L.E, n, L.H, L.K, row_capacity, S.status, out);
     ++*launches;
     return cudaGetLastError();
 }

@@ -24,6 +24,12 @@ struct GemmScratch {
     uint4 *tiles_gu, *tiles_dn, *stiles_gu, *stiles_dn;
     uint32_t *counts;
 };
+cudaError_t launch_scatter_peer(const DLayer &L, const Scratch &S, const __half *hidden, uint32_t n, uint32_t experts_per_rank,
+                                const uint32_t *dst_row0, const PeerBuffers &recv, unsigned long long row_capacity,
+                                cudaStream_t st, uint64_t *launches);
+cudaError_t launch_combine_peer(const DLayer &L, const Scratch &S, const GemmScratch &G, const PeerBuffers &done,
+                                uint32_t experts_per_rank, const uint32_t *dst_row0, unsigned long long row_capacity,
+                                const __half *residual, uint32_t n, __half *out, cudaStream_t st, uint64_t *launches);
 cudaError_t launch_gather_sorted(const DLayer &L, const Scratch &S, const __half *hidden, uint32_t n, __half *rows_out,
                                  cudaStream_t st, uint64_t *launches);
 cudaError_t launch_gemm_experts(const DLayer &L, const Scratch &S, const GemmScratch &G, const uint32_t *seg_offsets,
@@ -89,8 +95,18 @@ struct uocr_cuda_context {
     float *h_wts = nullptr;
     uint32_t *h_seg = nullptr;         // pinned ring for the expert-parallel segment offsets
     cudaEvent_t seg_events[8] = {};
+    // peer-memory exchange of an expert-parallel group (uocr_cuda_moe_ep_peer_*)
+    struct {
+        uint32_t world = 0, rank = 0, hidden = 0;
+        uint64_t row_capacity = 0;
+        __half *recv = nullptr, *done = nullptr;        // this rank's buffers
+        uocr::PeerBuffers recv_all{}, done_all{};      // every rank's (own pointers + mapped peers)
+        uint32_t *d_dst_row0 = nullptr;                // [256] device copy of the scatter offsets of the current call
+        bool opened = false;
+    } peer;
     cudaStream_t side_stream = nullptr;   // the shared MLP of a many-token call runs here, beside routing and the routed experts
     cudaEvent_t fork_event = nullptr, join_event = nullptr;
+    bool shared_pending = false;          // an expert-parallel shared-MLP call is running on the second stream
     uint32_t seg_slot = 0;
     uint64_t launches = 0;
     char last_error[1024] = {0};
@@ -212,10 +228,13 @@ extern "C" void uocr_cuda_context_unmap_model(uocr_cuda_context *ctx) {
     ctx->weight_bytes = 0;
 }
 
+extern "C" void uocr_cuda_moe_ep_peer_destroy(uocr_cuda_context *ctx);
+
 extern "C" void uocr_cuda_context_destroy(uocr_cuda_context *ctx) {
     if (!ctx) return;
     cudaSetDevice(ctx->device);
     if (ctx->own_stream) cudaStreamSynchronize(ctx->own_stream);
+    uocr_cuda_moe_ep_peer_destroy(ctx);
     uocr_cuda_context_release_runtime_arenas(ctx);
     uocr_cuda_context_unmap_model(ctx);
     cudaFree(ctx->status);
@@ -263,6 +282,7 @@ extern "C" int uocr_cuda_context_synchronize(uocr_cuda_context *ctx, char *error
                     : (st & 4u) ? "a bulk copy of the decode kernel timed out"
                     : (st & 8u) ? "a pipeline wait of the grouped GEMM kernel timed out"
                     : (st & 16u) ? "the decode kernel met a non-finite or out-of-range partial output"
+                    : (st & 32u) ? "a row index left the expert-parallel exchange buffers (inconsistent counts between the ranks)"
                                 : "kernel reported an internal error");
     }
     return 1;
@@ -416,7 +436,7 @@ extern "C" int uocr_cuda_context_map_moe_layer(uocr_cuda_context *ctx, const uoc
 struct ArenaLayout {
     uint64_t logits, probs, ids, weights, offsets, pair_rows, inverse, active, mid, shared_mid, down_out, shared_out,
         stack0, stack1, d_in, d_res, d_out, dec_mid, dec_plogits, x_sorted, tiles_gu, tiles_dn, stiles_gu, stiles_dn,
-        counts, plan_counts, total;
+        counts, plan_counts, seg_offsets, total;
 };
 
 // down products are f32 while the call is small enough to take the matrix-vector path, fp16 beyond
@@ -456,6 +476,7 @@ static ArenaLayout layout_arena(uint32_t H, uint32_t E, uint32_t K, uint32_t F, 
         a.stiles_gu = take(sttiles_gu * (S / 128 + 1) * 16);
         a.stiles_dn = take(sttiles * (H / 128 + 1) * 16);
         a.counts = take(64);
+        a.seg_offsets = take(260 * 4);        // expert-parallel experts phase: offsets of the received segments
         a.plan_counts = take((pairs / 2048 + 2) * E * 4);
     }
     a.total = off;
@@ -781,10 +802,12 @@ extern "C" int uocr_cuda_moe_ep_experts(uocr_cuda_context *ctx, uint32_t layer, 
         return fail(ctx, error, error_size, "%llu received rows exceed the arena capacity of %llu rows (token_capacity * top_k)",
                     (unsigned long long)run, (unsigned long long)ctx->token_capacity * L.K);
     if (run == 0) return 1;
-    CU_TRY(ctx, cudaMemcpyAsync(s.expert_offsets, h_seg, (size_t)(n_seg + 1) * 4, cudaMemcpyHostToDevice, ctx->stream));
+    // (its own array: the plan of this rank's tokens in s.expert_offsets is still needed by a peer-memory combine)
+    uint32_t *d_seg = (uint32_t *)(ctx->arena + a.seg_offsets);
+    CU_TRY(ctx, cudaMemcpyAsync(d_seg, h_seg, (size_t)(n_seg + 1) * 4, cudaMemcpyHostToDevice, ctx->stream));
     CU_TRY(ctx, cudaEventRecord(ctx->seg_events[slot], ctx->stream));
     const uocr::GemmScratch g = gemm_scratch(ctx, s, a);
-    CU_TRY(ctx, uocr::launch_gemm_experts(L, s, g, s.expert_offsets, n_seg, first_expert, n_local_experts,
+    CU_TRY(ctx, uocr::launch_gemm_experts(L, s, g, d_seg, n_seg, first_expert, n_local_experts,
                                           (const __half *)d_rows_in, (uint32_t)run, g.mid_sorted, (__half *)d_rows_out,
                                           ctx->stream, &ctx->launches));
     return 1;
@@ -798,7 +821,20 @@ extern "C" int uocr_cuda_moe_ep_shared(uocr_cuda_context *ctx, uint32_t layer, c
     ArenaLayout a;
     Scratch s = carve(ctx, L, ctx->token_capacity, &a);
     const uocr::GemmScratch g = gemm_scratch(ctx, s, a);
-    CU_TRY(ctx, uocr::launch_gemm_shared(L, s, g, (const __half *)d_hidden, n, ctx->stream, &ctx->launches));
+    // on the second stream, beside whatever the caller queues next (exchange, routed experts); the combine joins it
+    CU_TRY(ctx, cudaEventRecord(ctx->fork_event, ctx->stream));
+    CU_TRY(ctx, cudaStreamWaitEvent(ctx->side_stream, ctx->fork_event, 0));
+    CU_TRY(ctx, uocr::launch_gemm_shared(L, s, g, (const __half *)d_hidden, n, ctx->side_stream, &ctx->launches));
+    CU_TRY(ctx, cudaEventRecord(ctx->join_event, ctx->side_stream));
+    ctx->shared_pending = true;
+    return 1;
+}
+
+static int join_shared(uocr_cuda_context *ctx, char *error, size_t error_size) {
+    if (ctx->shared_pending) {
+        CU_TRY(ctx, cudaStreamWaitEvent(ctx->stream, ctx->join_event, 0));
+        ctx->shared_pending = false;
+    }
     return 1;
 }
 
@@ -810,7 +846,148 @@ extern "C" int uocr_cuda_moe_ep_combine(uocr_cuda_context *ctx, uint32_t layer, 
     ArenaLayout a;
     Scratch s = carve(ctx, L, ctx->token_capacity, &a);
     const uocr::GemmScratch g = gemm_scratch(ctx, s, a);
+    if (!join_shared(ctx, error, error_size)) return 0;
     CU_TRY(ctx, uocr::launch_gemm_combine(L, s, g, (const __half *)d_rows_back, (const __half *)d_residual, n,
                                           (__half *)d_out, ctx->stream, &ctx->launches));
+    return 1;
+}
+
+// ------------------------------------------------------------ expert parallelism over peer memory
+// The exchange fused into the gather and the combine: see scatter_rows_peer_kernel / combine_peer_kernel.
+
+extern "C" void uocr_cuda_moe_ep_peer_destroy(uocr_cuda_context *ctx) {
+    if (!ctx) return;
+    auto &P = ctx->peer;
+    if (P.opened) {
+        for (uint32_t g = 0; g < P.world; ++g) {
+            if (g == P.rank) continue;
+            if (P.recv_all.p[g]) cudaIpcCloseMemHandle(P.recv_all.p[g]);
+            if (P.done_all.p[g]) cudaIpcCloseMemHandle(P.done_all.p[g]);
+        }
+    }
+    cudaFree(P.recv); cudaFree(P.done); cudaFree(P.d_dst_row0);
+    P = {};
+}
+
+extern "C" int uocr_cuda_moe_ep_peer_create(uocr_cuda_context *ctx, uint32_t hidden_size, uint64_t row_capacity,
+                                            void *handles_out, char *error, size_t error_size) {
+    if (!ctx || !handles_out) return fail(ctx, error, error_size, "null argument");
+    if (hidden_size == 0 || hidden_size % 8 || row_capacity == 0) return fail(ctx, error, error_size, "invalid exchange buffer shape");
+    uocr_cuda_moe_ep_peer_destroy(ctx);
+    CU_TRY(ctx, cudaSetDevice(ctx->device));
+    auto &P = ctx->peer;
+    const size_t bytes = (size_t)row_capacity * hidden_size * 2;
+    CU_TRY(ctx, cudaMalloc(&P.recv, bytes));
+    CU_TRY(ctx, cudaMalloc(&P.done, bytes));
+    CU_TRY(ctx, cudaMalloc(&P.d_dst_row0, 256 * sizeof(uint32_t)));
+    P.hidden = hidden_size; P.row_capacity = row_capacity;
+    cudaIpcMemHandle_t h[2];
+    CU_TRY(ctx, cudaIpcGetMemHandle(&h[0], P.recv));
+    CU_TRY(ctx, cudaIpcGetMemHandle(&h[1], P.done));
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size is part of the ABI");
+    memcpy(handles_out, h, sizeof h);
+    return 1;
+}
+
+extern "C" int uocr_cuda_moe_ep_peer_open(uocr_cuda_context *ctx, uint32_t world, uint32_t rank, const void *all_handles,
+                                          char *error, size_t error_size) {
+    if (!ctx || !all_handles) return fail(ctx, error, error_size, "null argument");
+    auto &P = ctx->peer;
+    if (!P.recv) return fail(ctx, error, error_size, "create the exchange buffers first");
+    if (P.opened) return fail(ctx, error, error_size, "exchange already opened");
+    if (world == 0 || world > (uint32_t)uocr::kMaxPeers || rank >= world) return fail(ctx, error, error_size, "invalid group: rank %u of %u (at most %d ranks)", rank, world, uocr::kMaxPeers);
+    CU_TRY(ctx, cudaSetDevice(ctx->device));
+    const cudaIpcMemHandle_t *h = (const cudaIpcMemHandle_t *)all_handles;
+    P.world = world; P.rank = rank;
+    for (uint32_t g = 0; g < world; ++g) {
+        if (g == rank) { P.recv_all.p[g] = P.recv; P.done_all.p[g] = P.done; continue; }
+        void *a = nullptr, *b = nullptr;
+        CU_TRY(ctx, cudaIpcOpenMemHandle(&a, h[2 * g], cudaIpcMemLazyEnablePeerAccess));
+        P.recv_all.p[g] = (__half *)a;
+        P.opened = true;
+        CU_TRY(ctx, cudaIpcOpenMemHandle(&b, h[2 * g + 1], cudaIpcMemLazyEnablePeerAccess));
+        P.done_all.p[g] = (__half *)b;
+    }
+    P.opened = true;
+    return 1;
+}
+
+static int peer_ready(uocr_cuda_context *ctx, const DLayer &L, char *error, size_t error_size) {
+    const auto &P = ctx->peer;
+    if (!P.opened) return fail(ctx, error, error_size, "peer exchange not opened");
+    if (P.hidden != L.H) return fail(ctx, error, error_size, "exchange buffers were created for hidden size %u, the layer has %u", P.hidden, L.H);
+    if (L.E % P.world) return fail(ctx, error, error_size, "%u experts do not divide over %u ranks", L.E, P.world);
+    return 1;
+}
+
+extern "C" int uocr_cuda_moe_ep_peer_dispatch(uocr_cuda_context *ctx, uint32_t layer, const void *d_hidden, uint32_t n,
+                                              uint32_t *d_expert_offsets, char *error, size_t error_size) {
+    if (!check_call(ctx, layer, n, error, error_size)) return 0;
+    if (!d_hidden || !d_expert_offsets) return fail(ctx, error, error_size, "null expert-parallel dispatch argument");
+    const DLayer &L = ctx->layers[layer];
+    if (!uocr::gemm_path_supported(L)) return fail(ctx, error, error_size, "layer shape not supported by the tensor-core path");
+    if (!peer_ready(ctx, L, error, error_size)) return 0;
+    ArenaLayout a;
+    Scratch s = carve(ctx, L, ctx->token_capacity, &a);
+    CU_TRY(ctx, uocr::launch_router(L, (const __half *)d_hidden, nullptr, n, nullptr, nullptr, s.top_ids, s.top_weights,
+                                    ctx->status, s.logits, ctx->stream, &ctx->launches));
+    CU_TRY(ctx, uocr::launch_dispatch_plan(s.top_ids, n, L.K, L.E, s.expert_offsets, s.pair_rows, s.inverse, s.active,
+                                           s.plan_counts, ctx->stream, &ctx->launches));
+    CU_TRY(ctx, cudaMemcpyAsync(d_expert_offsets, s.expert_offsets, (size_t)(L.E + 1) * 4, cudaMemcpyDeviceToDevice, ctx->stream));
+    return 1;
+}
+
+extern "C" int uocr_cuda_moe_ep_peer_scatter(uocr_cuda_context *ctx, uint32_t layer, const void *d_hidden, uint32_t n,
+                                             const uint32_t *h_dst_row0, char *error, size_t error_size) {
+    if (!check_call(ctx, layer, n, error, error_size)) return 0;
+    if (!d_hidden || !h_dst_row0) return fail(ctx, error, error_size, "null expert-parallel scatter argument");
+    const DLayer &L = ctx->layers[layer];
+    if (!peer_ready(ctx, L, error, error_size)) return 0;
+    auto &P = ctx->peer;
+    ArenaLayout a;
+    Scratch s = carve(ctx, L, ctx->token_capacity, &a);
+    const uint32_t slot = ctx->seg_slot++ % kSegSlots;
+    uint32_t *h_stage = ctx->h_seg + (size_t)slot * 260;
+    CU_TRY(ctx, cudaEventSynchronize(ctx->seg_events[slot]));
+    memcpy(h_stage, h_dst_row0, (size_t)L.E * 4);
+    CU_TRY(ctx, cudaMemcpyAsync(P.d_dst_row0, h_stage, (size_t)L.E * 4, cudaMemcpyHostToDevice, ctx->stream));
+    CU_TRY(ctx, cudaEventRecord(ctx->seg_events[slot], ctx->stream));
+    CU_TRY(ctx, uocr::launch_scatter_peer(L, s, (const __half *)d_hidden, n, L.E / P.world, P.d_dst_row0, P.recv_all,
+                                          P.row_capacity, ctx->stream, &ctx->launches));
+    return 1;
+}
+
+extern "C" int uocr_cuda_moe_ep_experts(uocr_cuda_context *ctx, uint32_t layer, uint32_t first_expert, uint32_t n_local_experts,
+                                        uint32_t n_sources, const uint32_t *h_segment_counts, const void *d_rows_in,
+                                        void *d_rows_out, char *error, size_t error_size);
+
+extern "C" int uocr_cuda_moe_ep_peer_experts(uocr_cuda_context *ctx, uint32_t layer, uint32_t n_sources,
+                                             const uint32_t *h_segment_counts, char *error, size_t error_size) {
+    if (!ctx) return fail(nullptr, error, error_size, "null context");
+    if (layer >= ctx->layers.size()) return fail(ctx, error, error_size, "layer index %u out of range", layer);
+    const DLayer &L = ctx->layers[layer];
+    if (!peer_ready(ctx, L, error, error_size)) return 0;
+    auto &P = ctx->peer;
+    if (n_sources != P.world || !h_segment_counts) return fail(ctx, error, error_size, "segment counts of all %u ranks are needed", P.world);
+    const uint32_t per = L.E / P.world;
+    uint64_t rows = 0;
+    for (uint32_t i = 0; i < n_sources * per; ++i) rows += h_segment_counts[i];
+    if (rows > P.row_capacity) return fail(ctx, error, error_size, "%llu received rows exceed the exchange buffers' %llu rows", (unsigned long long)rows, (unsigned long long)P.row_capacity);
+    return uocr_cuda_moe_ep_experts(ctx, layer, P.rank * per, per, n_sources, h_segment_counts, P.recv, P.done, error, error_size);
+}
+
+extern "C" int uocr_cuda_moe_ep_peer_combine(uocr_cuda_context *ctx, uint32_t layer, const void *d_residual, uint32_t n,
+                                             void *d_out, char *error, size_t error_size) {
+    if (!check_call(ctx, layer, n, error, error_size)) return 0;
+    if (!d_out) return fail(ctx, error, error_size, "null expert-parallel combine argument");
+    const DLayer &L = ctx->layers[layer];
+    if (!peer_ready(ctx, L, error, error_size)) return 0;
+    auto &P = ctx->peer;
+    ArenaLayout a;
+    Scratch s = carve(ctx, L, ctx->token_capacity, &a);
+    const uocr::GemmScratch g = gemm_scratch(ctx, s, a);
+    if (!join_shared(ctx, error, error_size)) return 0;
+    CU_TRY(ctx, uocr::launch_combine_peer(L, s, g, P.done_all, L.E / P.world, P.d_dst_row0, P.row_capacity,
+                                          (const __half *)d_residual, n, (__half *)d_out, ctx->stream, &ctx->launches));
     return 1;
 }

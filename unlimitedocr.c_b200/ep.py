@@ -9,7 +9,7 @@ MLP are computed where a token lives.  One layer call is
     routed experts on the received rows                      library, local
     all-to-all of the results back to the token owners       torch.distributed
     weighted combine with the shared MLP's output (+ residual)   library, local
-(the shared MLP of the local tokens runs while the first exchange is in flight)
+(the shared MLP of the local tokens runs on the context's second stream beside the exchange and the routed experts)
 
 With G = 1 the two exchanges are skipped and the same three library calls run back to back.
 The exchange plan (who sends how many rows to whom, in which order) is plain integer arithmetic kept in
@@ -69,6 +69,21 @@ def plan_from_counts(counts: np.ndarray, rank: int) -> ExchangePlan:
     return ExchangePlan(np.ascontiguousarray(send), np.ascontiguousarray(recv))
 
 
+def dst_rows_from_counts(counts: np.ndarray, rank: int) -> np.ndarray:
+    """counts[g, e]: pairs rank g has for expert e.  For this rank and every expert e: the row of the OWNER's receive
+    buffer where this rank's rows for e start.  An owner's buffer holds, for source rank 0, 1, ... in turn, the rows
+    of each of its experts in turn (the order uocr_cuda_moe_ep_experts expects)."""
+    counts = np.asarray(counts, np.int64)
+    world, n_experts = counts.shape
+    per = n_experts // world
+    out = np.zeros(n_experts, np.int64)
+    for owner in range(world):
+        block = counts[:, owner * per:(owner + 1) * per]            # [source][local expert]
+        before = int(block[:rank].sum())                             # everything the lower ranks send to this owner
+        out[owner * per:(owner + 1) * per] = before + np.concatenate(([0], np.cumsum(block[rank])[:-1]))
+    return out.astype(np.uint32)
+
+
 class ExpertParallelLayer:
     """One mapped MoE layer whose routed experts are sharded over the ranks of a process group.
     The context must run on the stream the collectives use (ctx.set_stream(torch.cuda.current_stream().cuda_stream))."""
@@ -109,6 +124,7 @@ class ExpertParallelLayer:
             self._offsets = torch.zeros(self.E + 1, dtype=torch.int32, device=self.device)
             self._all_offsets = torch.zeros((self.world, self.E + 1), dtype=torch.int32, device=self.device)
         self.ctx.ep_dispatch(self.layer, hidden, n, send, self._offsets)
+        self.ctx.ep_shared(self.layer, hidden, n)       # on the context's second stream, beside all that follows
         if self.world == 1:
             all_offsets = self._offsets.reshape(1, -1)
         else:      # one small collective on the device, then ONE host read gives every rank the whole count matrix
@@ -119,19 +135,71 @@ class ExpertParallelLayer:
         self.last_plan = plan
         if self.world == 1:
             rows_done = self._buffer("back", n * self.K)
-            self.ctx.ep_shared(self.layer, hidden, n)
             self.ctx.ep_experts(self.layer, self.first, self.last - self.first, recv_counts, send, rows_done)
             back = rows_done
         else:
             r = plan.rows_received
             rows_in, rows_done = self._buffer("recv", r), self._buffer("done", r)
-            # the rows travel on the collective's own stream while the shared MLP runs on the compute stream
-            work = self.dist.all_to_all_single(rows_in[:r], send[: n * self.K], plan.recv_splits, plan.send_splits,
-                                               group=self.group, async_op=True)
-            self.ctx.ep_shared(self.layer, hidden, n)
-            work.wait()
+            self.dist.all_to_all_single(rows_in[:r], send[: n * self.K], plan.recv_splits, plan.send_splits, group=self.group)
             self.ctx.ep_experts(self.layer, self.first, self.last - self.first, recv_counts, rows_in, rows_done)
             back = self._buffer("back", n * self.K)
             self.dist.all_to_all_single(back[: n * self.K], rows_done[:r], plan.send_splits, plan.recv_splits, group=self.group)
         self.ctx.ep_combine(self.layer, back, n, out, residual=residual)
         return plan
+
+
+class PeerExpertParallelLayer:
+    """The same layer with the exchange fused into the library's kernels: each rank's gather writes its rows straight
+    into the owners' buffers and its combine reads the outputs straight from them over NVLink (CUDA IPC mappings, one
+    process per GPU of one node), so no all-to-all runs.  torch.distributed carries only the IPC handles (once), the
+    per-rank counts and two barriers per call."""
+
+    def __init__(self, ctx, layer: int, n_experts: int, top_k: int, hidden_size: int, *, row_capacity: int, rank: int = 0,
+                 world: int = 1, dist_module=None, group=None, device: str = "cuda"):
+        import torch
+        self.torch, self.device = torch, device
+        self.ctx, self.layer = ctx, layer
+        self.E, self.K, self.H = n_experts, top_k, hidden_size
+        self.rank, self.world, self.dist, self.group = rank, world, dist_module, group
+        owner_ranges(n_experts, world)                       # raises when the experts do not divide
+        mine = ctx.ep_peer_create(hidden_size, row_capacity)
+        if world > 1:
+            t = torch.frombuffer(bytearray(mine), dtype=torch.uint8).to(device)
+            every = torch.empty((world, 128), dtype=torch.uint8, device=device)
+            self.dist.all_gather(list(every.unbind(0)), t, group=group)
+            blob = every.cpu().numpy().tobytes()
+        else:
+            blob = mine
+        ctx.ep_peer_open(world, rank, blob)
+        self._offsets = torch.zeros(n_experts + 1, dtype=torch.int32, device=device)
+        self._all_offsets = torch.zeros((world, n_experts + 1), dtype=torch.int32, device=device)
+        self._token = torch.zeros(1, dtype=torch.int32, device=device)
+        self.last_plan: ExchangePlan | None = None
+
+    def _barrier(self) -> None:
+        """Everything every rank has queued so far is done (a tiny all-reduce on the compute stream)."""
+        if self.world > 1:
+            self.dist.all_reduce(self._token, group=self.group)
+
+    def forward(self, hidden, out, *, residual=None) -> ExchangePlan:
+        n = hidden.shape[0]
+        self.ctx.ep_peer_dispatch(self.layer, hidden, n, self._offsets)
+        self.ctx.ep_shared(self.layer, hidden, n)            # on the context's second stream, beside all that follows
+        if self.world == 1:
+            all_offsets = self._offsets.reshape(1, -1)
+        else:
+            self.dist.all_gather(list(self._all_offsets.unbind(0)), self._offsets, group=self.group)
+            all_offsets = self._all_offsets
+        counts = counts_from_offsets(all_offsets.cpu().numpy())
+        plan = plan_from_counts(counts, self.rank)
+        self.last_plan = plan
+        self.ctx.ep_peer_scatter(self.layer, hidden, n, dst_rows_from_counts(counts, self.rank))
+        self._barrier()                                      # every rank's rows are in the owners' buffers
+        self.ctx.ep_peer_experts(self.layer, plan.recv_counts)
+        self._barrier()                                      # every owner's outputs are written
+        self.ctx.ep_peer_combine(self.layer, n, out, residual=residual)
+        return plan
+
+    def close(self) -> None:
+        self.ctx.ep_peer_destroy()
+

@@ -53,6 +53,9 @@ EXPORTS = (
     "uocr_cuda_moe_dispatch_plan", "uocr_cuda_moe_dispatch_plan_noalloc", "uocr_cuda_moe_layer_forward", "uocr_cuda_moe_stack_forward",
     "uocr_cuda_moe_layer_forward_host", "uocr_cuda_moe_stack_forward_host",
     "uocr_cuda_moe_ep_dispatch", "uocr_cuda_moe_ep_experts", "uocr_cuda_moe_ep_shared", "uocr_cuda_moe_ep_combine",
+    "uocr_cuda_moe_ep_peer_create", "uocr_cuda_moe_ep_peer_open", "uocr_cuda_moe_ep_peer_destroy",
+    "uocr_cuda_moe_ep_peer_dispatch", "uocr_cuda_moe_ep_peer_scatter", "uocr_cuda_moe_ep_peer_experts",
+    "uocr_cuda_moe_ep_peer_combine",
 )
 
 
@@ -106,6 +109,13 @@ def load_library() -> C.CDLL:
         "uocr_cuda_moe_ep_experts": (C.c_int, [vp, u32, u32, u32, u32, vp, vp, vp] + err),
         "uocr_cuda_moe_ep_shared": (C.c_int, [vp, u32, vp, u32] + err),
         "uocr_cuda_moe_ep_combine": (C.c_int, [vp, u32, vp, vp, u32, vp] + err),
+        "uocr_cuda_moe_ep_peer_create": (C.c_int, [vp, u32, C.c_uint64, vp] + err),
+        "uocr_cuda_moe_ep_peer_open": (C.c_int, [vp, u32, u32, vp] + err),
+        "uocr_cuda_moe_ep_peer_destroy": (None, [vp]),
+        "uocr_cuda_moe_ep_peer_dispatch": (C.c_int, [vp, u32, vp, u32, vp] + err),
+        "uocr_cuda_moe_ep_peer_scatter": (C.c_int, [vp, u32, vp, u32, vp] + err),
+        "uocr_cuda_moe_ep_peer_experts": (C.c_int, [vp, u32, u32, vp] + err),
+        "uocr_cuda_moe_ep_peer_combine": (C.c_int, [vp, u32, vp, u32, vp] + err),
     }
     assert set(sig) == set(EXPORTS)
     for name, (res, args) in sig.items():
@@ -296,6 +306,37 @@ class Context:
     def ep_combine(self, layer: int, rows_back, n_tokens: int, out, *, residual=None) -> None:
         self._check(self._lib.uocr_cuda_moe_ep_combine(self._h, layer, _dev_ptr(rows_back), _dev_ptr(residual), n_tokens,
                                                        _dev_ptr(out), self._err, _ERR))
+
+    # -- expert-parallel phases with the exchange over peer memory
+    def ep_peer_create(self, hidden_size: int, row_capacity: int) -> bytes:
+        """Allocates this rank's exchange buffers; returns the 128 bytes of IPC handles to gather over the group."""
+        buf = C.create_string_buffer(128)
+        self._check(self._lib.uocr_cuda_moe_ep_peer_create(self._h, hidden_size, row_capacity, buf, self._err, _ERR))
+        return buf.raw
+
+    def ep_peer_open(self, world: int, rank: int, all_handles: bytes) -> None:
+        if len(all_handles) != 128 * world:
+            raise ValueError("all_handles must hold 128 bytes per rank")
+        self._check(self._lib.uocr_cuda_moe_ep_peer_open(self._h, world, rank, C.c_char_p(all_handles), self._err, _ERR))
+
+    def ep_peer_destroy(self) -> None:
+        self._lib.uocr_cuda_moe_ep_peer_destroy(self._h)
+
+    def ep_peer_dispatch(self, layer: int, hidden, n_tokens: int, expert_offsets) -> None:
+        self._check(self._lib.uocr_cuda_moe_ep_peer_dispatch(self._h, layer, _dev_ptr(hidden), n_tokens, _dev_ptr(expert_offsets),
+                                                             self._err, _ERR))
+
+    def ep_peer_scatter(self, layer: int, hidden, n_tokens: int, dst_row0: np.ndarray) -> None:
+        d = np.ascontiguousarray(dst_row0, np.uint32)
+        self._check(self._lib.uocr_cuda_moe_ep_peer_scatter(self._h, layer, _dev_ptr(hidden), n_tokens, _np_ptr(d), self._err, _ERR))
+
+    def ep_peer_experts(self, layer: int, segment_counts: np.ndarray) -> None:
+        seg = np.ascontiguousarray(segment_counts, np.uint32)
+        self._check(self._lib.uocr_cuda_moe_ep_peer_experts(self._h, layer, seg.shape[0], _np_ptr(seg), self._err, _ERR))
+
+    def ep_peer_combine(self, layer: int, n_tokens: int, out, *, residual=None) -> None:
+        self._check(self._lib.uocr_cuda_moe_ep_peer_combine(self._h, layer, _dev_ptr(residual), n_tokens, _dev_ptr(out),
+                                                            self._err, _ERR))
 
     # -- operators on host buffers (numpy uint16 fp16 bits)
     def layer_forward_host(self, layer: int, hidden: np.ndarray, residual: np.ndarray | None = None, *,
