@@ -29,8 +29,8 @@
 // clearing safe.
 //
 // Off the critical path: the shared-MLP CTAs do not depend on the routing, so they fetch the NEXT layer's
-// weights while they wait at the barrier; the routed CTAs fetch the next layer's router matrix into
-// registers at the same point - each CTA of a cluster of four a quarter of it (16 experts) - and evaluate it as
+// weights while they wait for the layer's output to be complete; the routed CTAs fetch the next layer's router
+// matrix into registers at the same point - each CTA of a cluster of four a quarter of it (16 experts) - and evaluate it as
 // soon as the new activations are there; the four quarters of the logits are exchanged through distributed
 // shared memory.  The softmax / top-k itself is taken off the path as well: see "routing" in the kernel.
 //
@@ -59,7 +59,7 @@ constexpr int kSlRoutedPerSlot = kSlF / 64;                 // 14
 constexpr int kSlRouted = kSlK * kSlRoutedPerSlot;          // 84
 constexpr int kSlUnits = kSlRouted + kSlS / 64;             // 112 CTAs
 constexpr int kSlGroups = kSlH / 64;                        // 20 quantisation groups along H
-constexpr int kSlCluster = 4;                               // CTAs per cluster: they share the router and pre-sum their outputs
+constexpr int kSlCluster = 4;                               // CTAs per cluster: each evaluates a quarter of the router
 constexpr int kSlChunks = 5;                                // gate/up fragments arrive in 5 copies of 4 groups
 constexpr int kSlAccBuffers = 4;
 // accumulator word: bits 56-63 count the CTAs that have added, bits 0-55 hold the sum of (value * 2^28 + 2^47)
