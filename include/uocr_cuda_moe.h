@@ -205,7 +205,9 @@ UOCR_CUDA_API int uocr_cuda_moe_stack_forward(uocr_cuda_context *ctx, uint32_t f
                                               char *error, size_t error_size);
 
 /* Host-buffer forms: copy h_hidden (and h_residual) to the device, run, copy the result back and wait.
- * These are what a host engine without its own device buffers calls. */
+ * These are what a host engine without its own device buffers calls.  The stack form with one token issues no
+ * copies when the single-token decode kernel serves it: the activations travel in the launch parameters, the
+ * kernel writes the result and its status word into mapped pinned host memory, and the call waits for the stream. */
 UOCR_CUDA_API int uocr_cuda_moe_layer_forward_host(uocr_cuda_context *ctx, uint32_t layer, const void *h_hidden_f16,
                                                    const void *h_residual_f16, uint32_t n_tokens, void *h_out_f16,
                                                    uint32_t *h_top_ids, float *h_top_weights, char *error,

@@ -384,6 +384,14 @@ def test_stack_of_layers_matches_layer_by_layer(pkg, port):
         assert torch.equal(stacked, chain[-1])
         host = ctx.stack_forward_host(0, 3, hidden)
         assert np.array_equal(host, stacked.cpu().numpy().view(np.uint16))
+        # the host-buffer call of one token issues no copies (activations in the launch parameters, result and
+        # status word written to mapped host memory): a rejected input must still be reported, and the next call work
+        bad = hidden.copy()
+        bad[0, 5] = 0x7C00                                   # +inf
+        with pytest.raises(pkg.UocrCudaError, match="non-finite"):
+            ctx.stack_forward_host(0, 3, bad)
+        again = ctx.stack_forward_host(0, 3, hidden)
+        assert np.array_equal(again, host)
 
 
 # --------------------------------------------------------------------------- invalid input

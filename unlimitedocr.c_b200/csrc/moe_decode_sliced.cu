@@ -86,6 +86,9 @@ struct SlicedParams {
     uint32_t *ids_out;            // [K] routing of the last layer run
     float *wts_out;
     unsigned long long *trace;    // optional [CTA][count][kSlTracePoints] SM-clock stamps
+    uint32_t *host_status;        // optional word in mapped host memory: receives the status word after `out` is written
+    int inline_input;             // 1: the first layer's input (and, with chain_residual, its residual) is inline_x
+    uint4 inline_x[kSlH * 2 / 16];  // fp16 activations carried in the launch parameters: a host-buffer call needs no copy
 };
 
 // ---------------------------------------------------------------- packed formats and the unit blob
@@ -240,7 +243,7 @@ template <int QT> struct SlSmem {
 
 // ---------------------------------------------------------------- the kernel
 template <int QT>
-__global__ void __launch_bounds__(kSlThreads, 1) decode_sliced_kernel(SlicedParams prm) {
+__global__ void __launch_bounds__(kSlThreads, 1) decode_sliced_kernel(const __grid_constant__ SlicedParams prm) {
     using Bl = SlBlob<QT>;
     using Sm = SlSmem<QT>;
     constexpr int H = kSlH, K = kSlK, E = kSlE;
@@ -295,12 +298,16 @@ __global__ void __launch_bounds__(kSlThreads, 1) decode_sliced_kernel(SlicedPara
         for (uint32_t i = tid; i < words; i += kSlThreads) dst[i] = src[i];
     }
     // the first layer's input, and its residual in registers
-    for (int h = tid; h < H; h += kSlThreads) s_x[h] = prm.hidden_in[h];
     float res0[3] = {0.f, 0.f, 0.f};
-    if (prm.residual0 != nullptr) {
+    {
+        const __half *xin = prm.inline_input ? reinterpret_cast<const __half *>(prm.inline_x) : prm.hidden_in;
+        const __half *rin = prm.inline_input ? (prm.chain_residual ? xin : nullptr) : prm.residual0;
+        for (int h = tid; h < H; h += kSlThreads) s_x[h] = xin[h];
+        if (rin != nullptr) {
 #pragma unroll
-        for (int i = 0; i < 3; ++i)
-            if (tid + i * kSlThreads < H) res0[i] = __half2float(prm.residual0[tid + i * kSlThreads]);
+            for (int i = 0; i < 3; ++i)
+                if (tid + i * kSlThreads < H) res0[i] = __half2float(rin[tid + i * kSlThreads]);
+        }
     }
     __syncthreads();
 
@@ -559,17 +566,19 @@ __global__ void __launch_bounds__(kSlThreads, 1) decode_sliced_kernel(SlicedPara
         // separate barrier: a word whose count is complete is complete.
         __syncthreads();
         {
-            bool range_ok = true;
 #pragma unroll
             for (int i = 0; i < 3; ++i) {
                 const int h = tid + i * kSlThreads;
                 if (h < H) {
                     float v = s_part[h];
-                    if (!(fabsf(v) < kSlAccRange)) { range_ok = false; v = 0.f; }      // NaN too: the count must stay intact
+                    if (!(fabsf(v) < kSlAccRange)) {      // NaN too: the count must stay intact
+                        atomicOr(status, kStatusRange);   // visible before the addition below: whoever sees the full
+                        __threadfence();                  // count and then reads the status word sees this bit
+                        v = 0.f;
+                    }
                     red_add_u64(acc + h, kSlAccOne + (unsigned long long)(__float2ll_rn(v * kSlAccScale) + kSlAccBias));
                 }
             }
-            if (!range_ok) atomicOr(status, kStatusRange);
         }
         UOCR_SL_TRACE(6);         // partial outputs sent
 
@@ -627,8 +636,14 @@ __global__ void __launch_bounds__(kSlThreads, 1) decode_sliced_kernel(SlicedPara
         }
         __syncthreads();
         if (last) {
-            if (cta == 0)
+            if (cta == 0) {
                 for (int h = tid; h < H; h += kSlThreads) prm.out[h] = s_x[h];
+                if (prm.host_status != nullptr) {       // ordered after this CTA saw every contribution of the launch
+                    __threadfence();
+                    __syncthreads();
+                    if (tid == 0) *prm.host_status = ld_volatile_u32(status);
+                }
+            }
         } else if (!routed) {
             build_x_frags();
             __syncthreads();
@@ -779,10 +794,14 @@ bool decode_sliced_supported(const DLayer *layers, uint32_t first, uint32_t coun
 }
 
 // acc: decode_sliced_acc_bytes() of device memory, zero before the first launch; *acc_base carries the accumulator
-// rotation from launch to launch (reset it, and clear acc, after a failed launch).
+// rotation from launch to launch (reset it, and clear acc, after a failed launch).  host_status: device address of a
+// word in mapped host memory that receives the status word once `out` is complete, or null.  h_inline: host pointer to the H
+// fp16 activations, copied into the launch parameters (hidden and residual0 are then unused; the first layer's
+// residual is the input itself when chain_residual is set), or null.
 cudaError_t launch_decode_sliced(const DLayer *h_layers, const DLayer *d_layers, uint32_t first, uint32_t count,
-                                 const __half *hidden, const __half *residual0, int chain_residual, const float *injected,
-                                 __half *out, unsigned long long *acc, uint32_t *acc_base, uint32_t *status,
+                                 const __half *hidden, const __half *residual0, const void *h_inline, int chain_residual,
+                                 const float *injected,
+                                 __half *out, uint32_t *host_status, unsigned long long *acc, uint32_t *acc_base, uint32_t *status,
                                  float *dbg_logits, float *dbg_probs, uint32_t *ids_out, float *wts_out,
                                  unsigned long long *trace, cudaStream_t st, uint64_t *launches) {
     int dev = 0;
@@ -793,7 +812,8 @@ cudaError_t launch_decode_sliced(const DLayer *h_layers, const DLayer *d_layers,
     prm.layers = d_layers; prm.first = first; prm.count = count;
     prm.hidden_in = hidden; prm.residual0 = residual0; prm.chain_residual = chain_residual;
     prm.injected = injected; prm.out = out; prm.acc = acc; prm.acc_base = *acc_base;
-    prm.status = status;
+    prm.status = status; prm.host_status = host_status;
+    if (h_inline != nullptr) { prm.inline_input = 1; memcpy(prm.inline_x, h_inline, sizeof(prm.inline_x)); }
     prm.dbg_logits = dbg_logits; prm.dbg_probs = dbg_probs; prm.ids_out = ids_out; prm.wts_out = wts_out; prm.trace = trace;
     cudaLaunchConfig_t cfg;
     cudaLaunchAttribute attrs[2];

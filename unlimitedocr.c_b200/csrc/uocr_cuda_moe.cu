@@ -47,8 +47,9 @@ cudaError_t build_decode_units(const DLayer &L, uint8_t *out, cudaStream_t st);
 size_t decode_sliced_acc_bytes();
 bool decode_sliced_supported(const DLayer *layers, uint32_t first, uint32_t count);
 cudaError_t launch_decode_sliced(const DLayer *h_layers, const DLayer *d_layers, uint32_t first, uint32_t count,
-                                 const __half *hidden, const __half *residual0, int chain_residual, const float *injected,
-                                 __half *out, unsigned long long *acc, uint32_t *acc_base, uint32_t *status,
+                                 const __half *hidden, const __half *residual0, const void *h_inline, int chain_residual,
+                                 const float *injected, __half *out, uint32_t *host_status, unsigned long long *acc,
+                                 uint32_t *acc_base, uint32_t *status,
                                  float *dbg_logits, float *dbg_probs, uint32_t *ids_out, float *wts_out,
                                  unsigned long long *trace, cudaStream_t st, uint64_t *launches);
 cudaError_t launch_decode_stack(const DLayer *h_layers, const DLayer *d_layers, uint32_t first, uint32_t count,
@@ -91,6 +92,8 @@ struct uocr_cuda_context {
     __half *h_in = nullptr;            // pinned staging for the host-buffer calls
     __half *h_res = nullptr;
     __half *h_out = nullptr;
+    __half *h_out_dev = nullptr;       // device addresses of h_out and h_status (mapped host memory), or null
+    uint32_t *h_status_dev = nullptr;
     uint32_t *h_ids = nullptr;
     float *h_wts = nullptr;
     uint32_t *h_seg = nullptr;         // pinned ring for the expert-parallel segment offsets
@@ -216,6 +219,7 @@ extern "C" void uocr_cuda_context_release_runtime_arenas(uocr_cuda_context *ctx)
     cudaFreeHost(ctx->h_in); cudaFreeHost(ctx->h_res); cudaFreeHost(ctx->h_out);
     cudaFreeHost(ctx->h_ids); cudaFreeHost(ctx->h_wts);
     ctx->h_in = ctx->h_res = ctx->h_out = nullptr;
+    ctx->h_out_dev = nullptr; ctx->h_status_dev = nullptr;
     ctx->h_ids = nullptr;
     ctx->h_wts = nullptr;
 }
@@ -522,6 +526,16 @@ extern "C" int uocr_cuda_context_allocate_runtime_arenas(uocr_cuda_context *ctx,
     CU_TRY(ctx, cudaMallocHost(&ctx->h_in, act));
     CU_TRY(ctx, cudaMallocHost(&ctx->h_res, act));
     CU_TRY(ctx, cudaMallocHost(&ctx->h_out, act));
+    {   // pinned memory is mapped into the device's address space where addressing is unified; else the copies stay
+        void *dp = nullptr, *ds = nullptr;
+        if (cudaHostGetDevicePointer(&dp, ctx->h_out, 0) == cudaSuccess && ctx->h_status &&
+            cudaHostGetDevicePointer(&ds, ctx->h_status, 0) == cudaSuccess) {
+            ctx->h_out_dev = (__half *)dp;
+            ctx->h_status_dev = (uint32_t *)ds;
+        } else {
+            (void)cudaGetLastError();
+        }
+    }
     const size_t small = (size_t)token_capacity * m.K * 4 > 4096 ? (size_t)token_capacity * m.K * 4 : 4096;
     CU_TRY(ctx, cudaMallocHost(&ctx->h_ids, small));
     CU_TRY(ctx, cudaMallocHost(&ctx->h_wts, small));
@@ -614,8 +628,8 @@ static int layer_forward(uocr_cuda_context *ctx, uint32_t layer, const __half *d
     float *logits = dbg && dbg->d_router_logits ? dbg->d_router_logits : nullptr;
     float *probs = dbg && dbg->d_router_probs ? dbg->d_router_probs : nullptr;
     if (n == 1 && ctx->fused_decode && ctx->sliced_decode && uocr::decode_sliced_supported(ctx->layers.data(), layer, 1)) {
-        CU_TRY(ctx, uocr::launch_decode_sliced(ctx->layers.data(), ctx->d_layers, layer, 1, d_hidden, d_residual, 0,
-                                               d_injected, d_out, decode_accumulators(ctx), &ctx->acc_base, ctx->status,
+        CU_TRY(ctx, uocr::launch_decode_sliced(ctx->layers.data(), ctx->d_layers, layer, 1, d_hidden, d_residual, nullptr, 0,
+                                               d_injected, d_out, nullptr, decode_accumulators(ctx), &ctx->acc_base, ctx->status,
                                                logits, probs, s.top_ids, s.top_weights, nullptr, ctx->stream,
                                                &ctx->launches));
     } else if (n == 1 && ctx->fused_decode && uocr::decode_supported(ctx->layers.data(), layer, 1)) {
@@ -665,14 +679,20 @@ extern "C" int uocr_cuda_moe_layer_forward(uocr_cuda_context *ctx, uint32_t laye
                          dbg, error, error_size);
 }
 
+static bool stack_uses_sliced_decode(const uocr_cuda_context *ctx, uint32_t first, uint32_t count, uint32_t n) {
+    return n == 1 && ctx->fused_decode && ctx->sliced_decode && uocr::decode_sliced_supported(ctx->layers.data(), first, count);
+}
+
+// h_inline / host_status: only with the sliced decode kernel (see launch_decode_sliced); null otherwise
 static int stack_forward(uocr_cuda_context *ctx, uint32_t first, uint32_t count, const __half *d_hidden, uint32_t n,
-                         __half *d_out, char *error, size_t error_size) {
+                         __half *d_out, char *error, size_t error_size, const void *h_inline = nullptr,
+                         uint32_t *host_status = nullptr) {
     ArenaLayout a;
     Scratch s = carve(ctx, ctx->layers[first], n, &a);
     __half *buf[2] = {(__half *)(ctx->arena + a.stack0), (__half *)(ctx->arena + a.stack1)};
-    if (n == 1 && ctx->fused_decode && ctx->sliced_decode && uocr::decode_sliced_supported(ctx->layers.data(), first, count)) {
-        CU_TRY(ctx, uocr::launch_decode_sliced(ctx->layers.data(), ctx->d_layers, first, count, d_hidden, d_hidden, 1, nullptr,
-                                               d_out, decode_accumulators(ctx), &ctx->acc_base, ctx->status, nullptr,
+    if (stack_uses_sliced_decode(ctx, first, count, n)) {
+        CU_TRY(ctx, uocr::launch_decode_sliced(ctx->layers.data(), ctx->d_layers, first, count, d_hidden, d_hidden, h_inline, 1,
+                                               nullptr, d_out, host_status, decode_accumulators(ctx), &ctx->acc_base, ctx->status, nullptr,
                                                nullptr, s.top_ids, s.top_weights, ctx->decode_trace, ctx->stream,
                                                &ctx->launches));
         return 1;
@@ -746,6 +766,19 @@ extern "C" int uocr_cuda_moe_stack_forward_host(uocr_cuda_context *ctx, uint32_t
     carve(ctx, L, n, &a);
     const size_t act = (size_t)n * L.H * 2;
     __half *d_in = (__half *)(ctx->arena + a.d_in), *d_out = (__half *)(ctx->arena + a.d_out);
+    if (ctx->h_out_dev && ctx->h_status_dev && stack_uses_sliced_decode(ctx, first, count, n)) {
+        // one token through the decode kernel: the activations ride in the launch parameters, and the kernel writes
+        // the result and its status word straight into mapped host memory, so the call issues no copy at all
+        *ctx->h_status = 0xffffffffu;
+        if (!stack_forward(ctx, first, count, d_in, n, ctx->h_out_dev, error, error_size, h_hidden, ctx->h_status_dev)) return 0;
+        CU_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+        if (*(volatile uint32_t *)ctx->h_status != 0) {       // the kernel gave up, or flagged something: read the device word
+            if (!uocr_cuda_context_synchronize(ctx, error, error_size)) return 0;
+            return fail(ctx, error, error_size, "the decode kernel ended without writing its result");
+        }
+        memcpy(h_out, ctx->h_out, act);
+        return 1;
+    }
     memcpy(ctx->h_in, h_hidden, act);
     CU_TRY(ctx, cudaMemcpyAsync(d_in, ctx->h_in, act, cudaMemcpyHostToDevice, ctx->stream));
     if (!uocr_cuda_moe_stack_forward(ctx, first, count, d_in, n, d_out, error, error_size)) return 0;
