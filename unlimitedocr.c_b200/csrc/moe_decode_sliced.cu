@@ -208,8 +208,10 @@ __device__ __forceinline__ uint32_t cluster_addr(const void *local, uint32_t ran
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(a) : "r"(smem_u32(local)), "r"(rank));
     return a;
 }
-__device__ __forceinline__ void mbar_arrive_cluster(uint32_t remote_bar) {
-    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(remote_bar) : "memory");
+// one fp32 value into another CTA's shared memory; its arrival counts 4 bytes on that CTA's barrier
+__device__ __forceinline__ void st_async_f32(uint32_t remote_addr, float v, uint32_t remote_bar) {
+    asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.b32 [%0], %1, [%2];"
+                 ::"r"(remote_addr), "r"(__float_as_uint(v)), "r"(remote_bar) : "memory");
 }
 __device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t *bar, uint32_t parity) {
     uint32_t ok;
@@ -285,7 +287,7 @@ __global__ void __launch_bounds__(kSlThreads, 1) decode_sliced_kernel(const __gr
     if (tid == 0) {
         s_flag[0] = 1; s_flag[1] = 0;
         for (int i = 0; i <= kSlChunks; ++i) mbar_init(&bars[i], 1);
-        mbar_init(lg_bar, csize);
+        mbar_init(lg_bar, 1);
         s_ids[7] = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -415,13 +417,13 @@ __global__ void __launch_bounds__(kSlThreads, 1) decode_sliced_kernel(const __gr
                         for (int w = 0; w < 16; ++w) v += s_rp[w * 16 + lane];
                         const uint32_t e = 16u * crank + (uint32_t)lane;
                         if (L.bias) v += L.bias[e];
-                        for (uint32_t r = 0; r < csize; ++r)
-                            asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(cluster_addr(s_logits + e, r)), "f"(v) : "memory");
+                        // each store carries its own completion count to the receiver's barrier: no release /
+                        // acquire round between the data and a separate arrival
+                        for (uint32_t r = 0; r < csize; ++r) st_async_f32(cluster_addr(s_logits + e, r), v, cluster_addr(lg_bar, r));
                     }
-                    __syncwarp();
-                    if ((uint32_t)lane < csize) mbar_arrive_cluster(cluster_addr(lg_bar, (uint32_t)lane));
                     if (lane == 0) {
                         int ok = 1;
+                        mbar_expect_tx(lg_bar, 16u * 4u * csize);       // this phase: 16 logits from each CTA of the cluster
                         if (!mbar_try_wait_cluster(lg_bar, lg_phase)) {
                             const long long t0 = clock64();
                             while (!mbar_try_wait_cluster(lg_bar, lg_phase)) {
