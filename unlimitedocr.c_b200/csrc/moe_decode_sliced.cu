@@ -315,8 +315,10 @@ __global__ void __launch_bounds__(kSlThreads, 1) decode_sliced_kernel(const __gr
 
     // ---- helpers --------------------------------------------------------------------------------------
     // fragments and offset corrections of the activations in s_x
+    // (by warps 0 and 2 .. 10: warp 1 of a routed CTA is busy with the exact routing at that time)
     auto build_x_frags = [&]() {
-        if (tid < kSlGroups * 16) write_limbs<QT>(s_x, tid, s_xf, s_xs, s_ncorr, kSlGroups);     // 16 lanes per group
+        const int bi = warp == 0 ? tid : tid - 32;
+        if (warp != 1 && bi < kSlGroups * 16) write_limbs<QT>(s_x, bi, s_xf, s_xs, s_ncorr, kSlGroups);     // 16 lanes per group
     };
     // what each lane does with its two result columns (2t, 2t + 1) of a group: columns 0 and 1 (t = 0) are the low
     // and middle mantissa bytes, column 2 (t = 1) the high byte; the other columns are unused
@@ -456,12 +458,6 @@ __global__ void __launch_bounds__(kSlThreads, 1) decode_sliced_kernel(const __gr
                 if (part == 0 && beats == (int)slot) s_ids[7] = (uint32_t)e;
             }
             __syncthreads();
-            if (warp == 1) {
-                const bool dbg = cta == 0 && li == 0;
-                const bool bad = route_row_warp(s_logits, s_probs, E, K, L.scaling, lane, s_tab, dbg ? prm.dbg_logits : nullptr,
-                                                dbg ? prm.dbg_probs : nullptr, s_ids, s_wts);
-                if (bad && lane == 0 && cta == 0) atomicOr(status, kStatusRouter);
-            }
             UOCR_SL_TRACE(1);     // expert of this CTA's slot chosen
         } else {
             UOCR_SL_TRACE(1);
@@ -471,7 +467,24 @@ __global__ void __launch_bounds__(kSlThreads, 1) decode_sliced_kernel(const __gr
         const uint8_t *blob = L.dec_units + (size_t)(ex * kSlRoutedPerSlot + fg) * Bl::kBytes;
         if (routed) {
             fetch_gate_up(blob);
-            if (first) { build_x_frags(); __syncthreads(); }
+            if (first) {
+                // Warp 1 computes the exact routing (about 1.5 us: the C library's expf in double precision, a serial
+                // sum, K selection rounds) while the other fifteen arrange the activations and start on the gate / up
+                // products; nobody waits for it before the check after those products.  Barrier 1: the fifteen
+                // announce the arranged activations and warp 1 waits for them; barrier 2: the fifteen among themselves.
+                if (warp == 1) {
+                    const bool dbg = cta == 0 && li == 0;
+                    const bool bad = route_row_warp(s_logits, s_probs, E, K, L.scaling, lane, s_tab, dbg ? prm.dbg_logits : nullptr,
+                                                    dbg ? prm.dbg_probs : nullptr, s_ids, s_wts);
+                    if (bad && lane == 0 && cta == 0) atomicOr(status, kStatusRouter);
+                    asm volatile("bar.sync 1, %0;" ::"n"(kSlThreads) : "memory");
+                } else {
+                    build_x_frags();
+                    __threadfence_block();
+                    asm volatile("bar.arrive 1, %0;" ::"n"(kSlThreads) : "memory");
+                    asm volatile("bar.sync 2, %0;" ::"n"(kSlThreads - 32) : "memory");
+                }
+            }
         }
         UOCR_SL_TRACE(2);         // weight fetches issued
         {
