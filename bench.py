@@ -555,7 +555,8 @@ def run_decode(args, rank: int, local_rank: int, world: int) -> None:
                          "peak": peak, "peak_kind": f"of {peak_kind}", "unit": "GB/s", "frac": achieved / peak,
                          "frac_of_nominal_8TBs": achieved / NOMINAL_HBM_GBS, "algorithmic_bytes_per_step": step_bytes,
                          "traffic": 165.4e6, "traffic_source": "dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture "
-                         "of this kernel on this workload (profiles/decode_sliced_kernel__decode_q4_11layers.md)"},
+                         "of this kernel on this workload, taken before its latest changes, which read the same bytes "
+                         "(profiles/decode_sliced_kernel__decode_q4_11layers.md)"},
             "clocks": clocks,
             "per_layer_us": ms_per_step * 1e3 / N_LAYERS,
             "step_ms_min_max": [min(times_ms), max(times_ms)],
