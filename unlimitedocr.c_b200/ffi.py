@@ -356,6 +356,8 @@ class Context:
         return (out, ids, wts) if want_routing else out
 
     def stack_forward_host(self, first_layer: int, n_layers: int, hidden: np.ndarray) -> np.ndarray:
+        """Host buffers in and out (fp16 bits).  One token through the decode kernel issues no copies: the
+        activations travel in the launch parameters and the kernel writes result and status into mapped host memory."""
         hidden = np.ascontiguousarray(hidden, np.uint16)
         out = np.empty_like(hidden)
         self._check(self._lib.uocr_cuda_moe_stack_forward_host(self._h, first_layer, n_layers, _np_ptr(hidden),
