@@ -32,7 +32,9 @@
 // weights while they wait for the layer's output to be complete; the routed CTAs fetch the next layer's router
 // matrix into registers at the same point - each CTA of a cluster of four a quarter of it (16 experts) - and evaluate it as
 // soon as the new activations are there; the four quarters of the logits are exchanged through distributed
-// shared memory.  The softmax / top-k itself is taken off the path as well: see "routing" in the kernel.
+// shared memory (st.async stores that count bytes on the receiver's mbarrier: one hop, no separate arrival).
+// The softmax / top-k itself is taken off the path as well (one warp, which the others do not wait for): see
+// "routing" in the kernel.
 //
 // Arithmetic.  Scalar dequantise-and-FMA costs ~3.5 instructions per packed weight and would bound the layer, so
 // the dot products run on the tensor cores as INTEGER MMAs (m16n8k32, s32 accumulate), which take the packed
