@@ -330,7 +330,7 @@ def run_tokens(args, kind: str, rank: int, local_rank: int, world: int) -> None:
         dist.all_reduce(ok, op=dist.ReduceOp.MIN)
         if int(ok.item()) == 0:
             if layer is not None:
-                layer.close()
+                layer.close(group_barrier=False)      # nothing has run on the exchange buffers yet
             layer = None
             exchange = f"nccl all_to_all_single (peer-memory set-up failed on a rank: {why})"
     if layer is None:

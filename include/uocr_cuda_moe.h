@@ -184,6 +184,17 @@ UOCR_CUDA_API int uocr_cuda_moe_dispatch_plan_noalloc(const uint32_t *d_top_ids,
                                                       uint32_t *d_pair_rows, uint32_t *d_inverse, void *cuda_stream,
                                                       char *error, size_t error_size);
 
+/* Bring-up and test aid: the value the kernels give every weight of one projection matrix, so that the in-register
+ * dequantisers can be compared with the format definition (level * fp16 scale, src/model/uocr_format.h:49-99; the
+ * reference pins its packed bytes in tests/test_convert.py:192-218 and unpacks them on the CPU only).
+ *   matrix  0 / 1 / 2: gate [F][H] / up [F][H] / down [H][F] of routed expert `expert`; 3 / 4 / 5: the shared MLP's.
+ *   path    0: the matrix-vector kernels (row_dot on one-hot activations): f32 level * float(scale), exact;
+ *           1: the grouped GEMM's producer: fp16( float(level) * float(scale) ), the value the reference's tiled
+ *              GEMMs feed their MMAs (src/backend/metal/kernels/gemm_q4.metal:35-57, gemm_q8.metal:43-60).
+ * d_out: f32 [rows][cols] on the device.  path 1 needs cols to be a multiple of 64. */
+UOCR_CUDA_API int uocr_cuda_moe_debug_dequantize(uocr_cuda_context *ctx, uint32_t layer, uint32_t matrix, uint32_t expert,
+                                                 uint32_t path, float *d_out, char *error, size_t error_size);
+
 /* The layer: out[n][H] = fp16( sum_slot weight * expert(hidden) + shared(hidden) [+ residual] ), the
  * computation of uocr_cpu_ref_moe_swiglu_f32 (src/backend/cpu_ref/uocr_cpu_ref.c:468-579) with the GPU
  * path's data types: fp16 activations, weights dequantised on the fly and never materialised, f32
@@ -273,7 +284,10 @@ UOCR_CUDA_API int uocr_cuda_moe_ep_combine(uocr_cuda_context *ctx, uint32_t laye
  * combine:  out = fp16( sum_slot weight * output row of the pair (read from its owner) + shared MLP [+ residual] );
  *           uocr_cuda_moe_ep_shared must have run for these tokens.
  * A row index outside the buffers (inconsistent counts) is never dereferenced: it raises a status bit that
- * uocr_cuda_context_synchronize reports. */
+ * uocr_cuda_context_synchronize reports.
+ * destroy:  unmaps the peers' buffers and frees this rank's.  The caller must make sure that NO rank still has a
+ *           scatter or combine kernel in flight (every rank waits for its stream, then a barrier over the group):
+ *           a peer that touches a freed buffer faults on its own GPU. */
 UOCR_CUDA_API int uocr_cuda_moe_ep_peer_create(uocr_cuda_context *ctx, uint32_t hidden_size, uint64_t row_capacity,
                                                void *handles_out, char *error, size_t error_size);
 UOCR_CUDA_API int uocr_cuda_moe_ep_peer_open(uocr_cuda_context *ctx, uint32_t world, uint32_t rank, const void *all_handles,

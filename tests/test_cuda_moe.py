@@ -525,3 +525,235 @@ def test_sliced_decode_when_distinct_logits_share_a_probability(pkg, port):
     assert np.array_equal(wts.view(np.uint32), want.weights.view(np.uint32))
     err, cos = closeness(out, want.out)
     assert err <= MAX_ABS and cos >= MIN_COS, (err, cos)
+
+
+# ------------------------------------------------------------ bounded waits (time-out path)
+
+def test_decode_wait_runs_out_and_the_context_recovers(pkg, monkeypatch):
+    """A wait between CTAs of the decode kernel that can never be satisfied ends at its limit: the kernel raises its
+    status word and returns, the call reports a time-out as text, and the next call on the same context works.
+    The hooks (read when the context is created) shorten the limit to ~1 ms and make ONE launch wait for one
+    contribution more than there are CTAs; nothing faults or traps."""
+    rng = np.random.default_rng(41)
+    layers = [quant.synth_layer(rng, expert_qtype=quant.QTYPE_Q4_0, **FULL) for _ in range(2)]
+    hidden = quant.synth_activations(rng, 1, FULL["H"])
+    with pkg.Context() as ctx:                      # an undisturbed context gives the expected result
+        for L in layers:
+            ctx.map_layer(L)
+        ctx.allocate_runtime_arenas(1)
+        want = ctx.stack_forward_host(0, 2, hidden)
+    monkeypatch.setenv("UOCR_CUDA_TEST_SPIN_LIMIT_CYCLES", "2000000")
+    monkeypatch.setenv("UOCR_CUDA_TEST_DECODE_STALL_ONCE", "1")
+    with pkg.Context() as ctx:
+        for L in layers:
+            ctx.map_layer(L)
+        ctx.allocate_runtime_arenas(1)
+        with pytest.raises(pkg.UocrCudaError, match="timed out"):
+            ctx.stack_forward_host(0, 2, hidden)
+        assert np.array_equal(ctx.stack_forward_host(0, 2, hidden), want)       # same context, next call
+        assert np.array_equal(ctx.stack_forward_host(0, 2, hidden), want)
+    monkeypatch.setenv("UOCR_CUDA_TEST_DECODE_STALL_ONCE", "1")
+    with pkg.Context() as ctx:                      # the same through the device-buffer entry point
+        for L in layers:
+            ctx.map_layer(L)
+        ctx.allocate_runtime_arenas(1)
+        ctx.set_stream(torch.cuda.current_stream().cuda_stream)
+        d_in = dev(hidden).view(torch.float16)
+        d_out = torch.zeros_like(d_in)
+        ctx.stack_forward(0, 2, d_in, 1, d_out)
+        with pytest.raises(pkg.UocrCudaError, match="timed out"):
+            ctx.synchronize()
+        ctx.stack_forward(0, 2, d_in, 1, d_out)
+        ctx.synchronize()
+        assert np.array_equal(d_out.cpu().numpy().view(np.uint16), want)
+
+
+# ------------------------------------------------------------ exact dequantisation
+
+def _expected_producer_values(m):
+    """fp16( float(level) * float(fp16 scale) ): what the reference's tiled GEMMs feed their MMAs."""
+    return m.to_f32().astype(np.float16).astype(np.float32)
+
+
+@pytest.mark.parametrize("qname", ["q4_0", "q8_0", "f16"])
+def test_gpu_dequantisers_are_exact(pkg, qname):
+    """Every weight as the kernels see it equals level * float(fp16 scale) of the packed bytes (the format the
+    reference pins in tests/test_convert.py:192-218), including an all-zero group, groups whose largest element is
+    negative / positive (Q4_0's signed maximum) and the extreme levels."""
+    dims = dict(H=256, E=4, K=2, F=128, S=192)
+    rng = np.random.default_rng(5)
+    L = quant.synth_layer(rng, expert_qtype=QT[qname], **dims)
+    w = (rng.standard_normal((dims["S"], dims["H"])) * 0.02).astype(np.float32)
+    w[3, 64:128] = 0.0                                   # all-zero group
+    w[4, 0:64] = np.abs(w[4, 0:64]); w[4, 7] = -0.5      # largest magnitude negative: level -8 ... +7 range in use
+    w[5, 0:64] = -np.abs(w[5, 0:64]); w[5, 9] = 0.5      # largest magnitude positive
+    w[6, 128:192] = np.linspace(-1, 1, 64)               # every level of both formats
+    L.shared_gate = quant.make_matrix(QT[qname], w)
+    mats = {3: L.shared_gate, 4: L.shared_up, 5: L.shared_down}
+    with pkg.Context() as ctx:
+        ctx.map_layer(L)
+        ctx.allocate_runtime_arenas(1)
+        ctx.set_stream(torch.cuda.current_stream().cuda_stream)
+
+        def probe(matrix, expert, rows, cols, path):
+            out = torch.full((rows, cols), float("nan"), dtype=torch.float32, device="cuda")
+            ctx.debug_dequantize(0, matrix, expert, path, out)
+            ctx.synchronize()
+            return out.cpu().numpy()
+
+        for matrix, m in mats.items():
+            want = m.to_f32()
+            assert np.array_equal(probe(matrix, 0, m.rows, m.cols, 0), want), (matrix, "matrix-vector path")
+            assert np.array_equal(probe(matrix, 0, m.rows, m.cols, 1), _expected_producer_values(m)), (matrix, "producer")
+        for e in (0, dims["E"] - 1):
+            for matrix, want in enumerate(L.expert_f32(e)):
+                rows, cols = want.shape
+                assert np.array_equal(probe(matrix, e, rows, cols, 0), want), (e, matrix)
+                assert np.array_equal(probe(matrix, e, rows, cols, 1), want.astype(np.float16).astype(np.float32)), (e, matrix)
+        with pytest.raises(pkg.UocrCudaError, match="out of range"):
+            ctx.debug_dequantize(0, 6, 0, 0, torch.zeros(4, device="cuda"))
+        with pytest.raises(pkg.UocrCudaError, match="out of range"):
+            ctx.debug_dequantize(0, 0, dims["E"], 0, torch.zeros(4, device="cuda"))
+
+
+# ------------------------------------------------------------ slabs that are not densely packed
+
+def padded_slab_layer(L, pad_bytes=48, pad_scales=24):
+    """The same layer with gaps between the projections and the experts of its slabs (strides as the model file's
+    tensor table may give them, src/backend/metal/uocr_metal.m:3037-3154)."""
+    qt = L.expert_qtype
+    proj = L.F * quant.packed_row_bytes(qt, L.H)
+    nsc = 0 if qt == quant.QTYPE_F16 else L.F * (L.H // 64)
+    stride_w, stride_s = 3 * (proj + pad_bytes) + 16, 3 * (nsc + pad_scales) + 8
+    slab = np.full(L.E * stride_w, 0xA5, np.uint8)
+    scales = None if qt == quant.QTYPE_F16 else np.full(L.E * stride_s, 0x3C00, np.uint16)
+    for e in range(L.E):
+        for p in range(3):
+            slab[e * stride_w + p * (proj + pad_bytes):][:proj] = L.expert_qweight[(e * 3 + p) * proj:][:proj]
+            if scales is not None:
+                scales[e * stride_s + p * (nsc + pad_scales):][:nsc] = L.expert_qscale[(e * 3 + p) * nsc:][:nsc]
+    strides = dict(expert_stride_bytes=stride_w, up_offset_bytes=proj + pad_bytes, down_offset_bytes=2 * (proj + pad_bytes))
+    if scales is not None:
+        strides.update(expert_scale_stride_values=stride_s, up_scale_offset_values=nsc + pad_scales,
+                       down_scale_offset_values=2 * (nsc + pad_scales))
+    return quant.LayerWeights(**{**L.__dict__, "expert_qweight": slab, "expert_qscale": scales, "meta": {"strides": strides}})
+
+
+@pytest.mark.parametrize("qname,n", [("q4_0", 1), ("q8_0", 1), ("q4_0", 3), ("q4_0", 64), ("f16", 40)])
+def test_slab_with_gaps_between_projections(pkg, port, qname, n):
+    """Expert strides and projection offsets larger than the dense ones: every regime (decode kernel with its
+    slice-major copy, matrix-vector kernels, grouped GEMM) must address the slab through them."""
+    L, hidden, resid = make(9, FULL, qname, n)
+    want = port.layer(L, hidden, resid, threads=16)
+    g = Layer(pkg, quant.LayerWeights(**{**padded_slab_layer(L).__dict__, "logit_bias": None}), n)
+    try:
+        out, ids, _ = g.forward(hidden, resid, injected=want.logits)
+    finally:
+        g.close()
+    assert np.array_equal(ids, want.ids)
+    err, cos = closeness(out, want.out)
+    assert err <= MAX_ABS and cos >= MIN_COS, (err, cos)
+
+
+def test_inconsistent_slab_strides_are_refused(pkg):
+    L, _, _ = make(9, TINY, "q8_0", 1)
+    proj = L.F * L.H
+    with pkg.Context() as ctx:
+        for strides in (dict(up_offset_bytes=proj - 16), dict(down_offset_bytes=proj), dict(expert_stride_bytes=3 * proj - 16),
+                        dict(up_offset_bytes=proj + 8)):
+            with pytest.raises(pkg.UocrCudaError, match="inconsistent"):
+                ctx.map_layer(quant.LayerWeights(**{**L.__dict__, "meta": {"strides": strides}}))
+
+
+# ------------------------------------------------------------ many tokens off the tensor-core path
+
+@pytest.mark.parametrize("dims,n", [(TINY, 300), (TINY, 1000), (dict(H=192, E=5, K=3, F=128, S=320), 300)])
+def test_matrix_vector_path_beyond_256_tokens(pkg, port, dims, n):
+    """Shapes the grouped GEMM does not take (widths that are not multiples of 128) stay on the matrix-vector
+    kernels however many tokens a call has; its f32 scratch must be sized for that."""
+    L, hidden, resid = make(13, dims, "q8_0", n)
+    check_layer(pkg, port, L, hidden, resid)
+
+
+def test_expert_parallel_phases_refuse_shapes_off_the_tensor_core_path(pkg):
+    L, hidden, _ = make(14, TINY, "q8_0", 8)
+    with pkg.Context() as ctx:
+        ctx.map_layer(L)
+        ctx.allocate_runtime_arenas(8)
+        rows = torch.zeros((16, 128), dtype=torch.float16, device="cuda")
+        with pytest.raises(pkg.UocrCudaError, match="not supported by the tensor-core path"):
+            ctx.ep_experts(0, 0, 8, np.full((1, 8), 2, np.uint32), rows, rows.clone())
+        with pytest.raises(pkg.UocrCudaError, match="not supported by the tensor-core path"):
+            ctx.ep_shared(0, dev(hidden), 8)
+
+
+# ------------------------------------------------------------ the benchmark plan's large configurations
+
+def _oracle_logits(port, L, hidden, threads=16):
+    """Router logits of every token from the CPU path's serial f32 chain (+ bias), computed in row slices."""
+    from concurrent.futures import ThreadPoolExecutor
+    x = port.f16_to_f32(hidden)
+    w = L.router.view("<f2").astype(np.float32)
+    bounds = np.linspace(0, x.shape[0], threads + 1).astype(int)
+
+    def run(i):
+        st, r = port.router_f32(np.ascontiguousarray(x[bounds[i]:bounds[i + 1]]), w, L.K, L.scaling)
+        assert st == 1
+        return r.logits
+
+    with ThreadPoolExecutor(threads) as pool:
+        logits = np.concatenate(list(pool.map(run, range(threads))))
+    return logits + (L.logit_bias if L.logit_bias is not None else 0)
+
+
+def _spread_rows(rng, ids, E, per_expert=5, minimum=256):
+    """Token rows that cover every expert that received tokens, hot and cold alike."""
+    rows = set()
+    for e in range(E):
+        hit = np.flatnonzero(np.any(ids == e, axis=1))
+        rows.update(rng.choice(hit, size=min(per_expert, hit.size), replace=False).tolist())
+    n = ids.shape[0]
+    rows.update([0, n - 1])
+    while len(rows) < min(minimum, n):
+        rows.add(int(rng.integers(n)))
+    return np.array(sorted(rows))
+
+
+@pytest.mark.parametrize("n,seed,qname,routing", [(4096, 3, "q4_0", "zipf"), (4096, 3, "f16", "zipf"),
+                                                  (16384, 4, "q4_0", "uniform"), (16384, 4, "q4_0", "zipf")])
+def test_large_prefill_configs(pkg, port, n, seed, qname, routing):
+    """Configs 4 and 5 at full size (the inputs bench.py times): routing ids, weights and the permutation of EVERY
+    token bit-exact against the CPU path on identical logits; layer output of a seeded subset of >= 256 rows that
+    covers every expert within the stated tolerance; every other row finite."""
+    import bench
+    L, hidden, resid = bench.synth_token_layer(seed, n, qname, routing)
+    logits = _oracle_logits(port, L, hidden).astype(np.float32)
+    st, want_r = port.route_from_logits(logits, L.K, L.scaling)
+    assert st == 1
+    g = Layer(pkg, quant.LayerWeights(**{**L.__dict__, "logit_bias": None}), n)
+    try:
+        out, ids, wts = g.forward(hidden, resid, injected=logits)
+        off = torch.zeros(L.E + 1, dtype=torch.int32).cuda()
+        rows_t = torch.full((n * L.K,), -1, dtype=torch.int32).cuda()
+        inv = torch.zeros(n * L.K, dtype=torch.int32).cuda()
+        g.ctx.dispatch_plan(dev(ids.view(np.int32)), n, L.K, L.E, off, rows_t, inv)
+        g.ctx.synchronize()
+    finally:
+        g.close()
+    assert np.array_equal(ids, want_r.ids)
+    assert np.array_equal(wts.view(np.uint32), want_r.weights.view(np.uint32))
+    want_off, want_rows, want_inv = port.dispatch_plan(want_r.ids, L.E)
+    assert np.array_equal(off.cpu().numpy().view(np.uint32), want_off)
+    assert np.array_equal(rows_t.cpu().numpy().view(np.uint32), want_rows)
+    assert np.array_equal(inv.cpu().numpy().view(np.uint32), want_inv)
+    counts = np.diff(want_off.astype(np.int64))
+    if routing == "zipf":
+        assert counts.max() > 8 * max(1, counts.min())          # the skew is really there
+    sub = _spread_rows(np.random.default_rng(seed), want_r.ids, L.E)
+    assert sub.size >= 256
+    plain = quant.LayerWeights(**{**L.__dict__, "logit_bias": None})       # the bias is already inside the logits
+    want = port.layer(plain, hidden[sub], resid[sub], injected_logits=logits[sub], threads=16)
+    assert np.array_equal(want.ids, want_r.ids[sub])
+    err, cos = closeness(out[sub], want.out)
+    assert err <= MAX_ABS and cos >= MIN_COS, (err, cos)
+    assert np.all(np.isfinite(out))

@@ -166,6 +166,14 @@ __device__ __forceinline__ float silu_f32(float v) { return v / (1.0f + __expf(-
 constexpr int kMaxPeers = 16;
 struct PeerBuffers { __half *p[kMaxPeers]; };
 
+// Run-time settings of the single-token decode kernel (a context reads them from the environment when it is created).
+struct SlicedKnobs {
+    uint32_t replicas = 1;            // copies of the layer accumulator the CTAs spread their additions over (1, 2 or 4)
+    long long spin_limit_cycles = 0;  // limit of a wait between CTAs; 0: the built-in limit (about two seconds)
+    uint32_t expect_extra = 0;        // test hook: the wait for a layer's output expects this many contributions
+                                      // more than there are CTAs, so it runs into its limit
+};
+
 // ---- launch interface (implemented in the kernel files, called by the host API) ----------
 struct LaunchCounter { uint64_t *count; };
 

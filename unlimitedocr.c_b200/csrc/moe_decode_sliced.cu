@@ -23,7 +23,9 @@
 // The accumulator is 64-bit fixed point (2^-28 units) updated with integer reductions, so the sum does not
 // depend on the order in which CTAs arrive: results are reproducible run to run.  The top byte of a word counts
 // the CTAs that have added to it - every CTA adds to every word exactly once per layer - so a reader that sees
-// the full count holds the final value: no grid barrier, no fence, one L2 round trip less per layer.  Four
+// the full count holds the final value: no grid barrier, no fence, one L2 round trip less per layer.  The
+// accumulator may be kept in 1, 2 or 4 replicas (CTA c adds to replica c % R, readers add the replicas up), which
+// spreads the 112 additions per word over more L2 lines.  Four
 // accumulator buffers rotate (adds / read / idle / cleared); the rotation continues across launches, and the data
 // dependency itself (nobody can start layer l + 1 before everybody has finished reading layer l - 1) keeps the
 // clearing safe.
@@ -40,15 +42,20 @@
 // the dot products run on the tensor cores as INTEGER MMAs (m16n8k32, s32 accumulate), which take the packed
 // levels as they are (Q8: the int8 words themselves; Q4: one AND per four weights).  The fp16 activations of a
 // 64-wide group are written once per layer as a block-floating-point number: a shared power-of-two scale and
-// 22-bit signed mantissas, exact for every value within 2^11 of the group's largest, 2^-22 of it otherwise (fp32
-// accumulation itself carries 2^-24).  A mantissa is split into three signed bytes, and the three bytes ride in
-// three of the MMA's eight columns, so one MMA yields the group's exact integer dot product with all three.
-// Per group the integers are recombined in f32 and multiplied by (activation scale x the group's fp16 weight
-// scale); Q4's +8 offset is removed with a per-group correction 8 * sum(mantissas).  The router matrix is fp16
-// and runs as fp16 MMAs (m16n8k16) on the activations themselves.
+// signed 15-bit mantissas, exact for every value within a factor 8 of the group's largest and rounded to 2^-14 of
+// the largest's power of two otherwise (far below the fp16 rounding of the SwiGLU products that the data path
+// carries anyway).  A mantissa is split into two signed bytes, and the two bytes ride in two of the MMA's eight
+// columns.  Which two depends on the group (columns 2 (G % 4) and 2 (G % 4) + 1), so four consecutive groups
+// accumulate into one set of MMA registers and the per-group work - recombine the two bytes, multiply by
+// (activation scale x the group's fp16 weight scale), remove Q4's +8 offset with the correction 8 * sum(mantissas)
+// - runs once per four groups with every lane holding one group's result.  The `down` product uses the same trick
+// over four 16-row blocks.  The router matrix is fp16 and runs as fp16 MMAs (m16n8k16) on the activations
+// themselves.
 //
 // Every wait is bounded (see moe_sync.cuh).
 #include <cuda.h>
+
+#include <atomic>
 
 #include "moe_route.cuh"
 #include "moe_sync.cuh"
@@ -64,6 +71,7 @@ constexpr int kSlGroups = kSlH / 64;                        // 20 quantisation g
 constexpr int kSlCluster = 4;                               // CTAs per cluster: each evaluates a quarter of the router
 constexpr int kSlChunks = 5;                                // gate/up fragments arrive in 5 copies of 4 groups
 constexpr int kSlAccBuffers = 4;
+constexpr int kSlMaxReplicas = 4;
 // accumulator word: bits 56-63 count the CTAs that have added, bits 0-55 hold the sum of (value * 2^28 + 2^47)
 constexpr unsigned long long kSlAccOne = 1ull << 56;
 constexpr long long kSlAccBias = 1ll << 47;
@@ -74,6 +82,7 @@ constexpr int kSlMaxLayers = 64;
 constexpr int kSlBlocksPerWarp = kSlH / 16 / 16;            // 5 blocks of 16 output rows per warp
 
 struct SlicedParams {
+    static constexpr bool kInline = false;
     const DLayer *layers;
     uint32_t first, count;
     const __half *hidden_in;
@@ -81,16 +90,24 @@ struct SlicedParams {
     int chain_residual;           // layers after the first use their input as residual
     const float *injected;        // [E] logits for the first layer, or null
     __half *out;
-    unsigned long long *acc;      // [kSlAccBuffers][H] fixed-point accumulators, all zero between launches except two
+    unsigned long long *acc;      // [kSlAccBuffers][kSlMaxReplicas][H] fixed-point accumulators, all zero between launches except two buffers
     uint32_t acc_base;            // buffer of the first layer of this launch
+    uint32_t replicas;            // accumulator replicas in use (1, 2 or 4): CTA c adds to replica c % replicas
     uint32_t *status;
     float *dbg_logits, *dbg_probs;
     uint32_t *ids_out;            // [K] routing of the last layer run
     float *wts_out;
     unsigned long long *trace;    // optional [CTA][count][kSlTracePoints] SM-clock stamps
     uint32_t *host_status;        // optional word in mapped host memory: receives the status word after `out` is written
-    int inline_input;             // 1: the first layer's input (and, with chain_residual, its residual) is inline_x
-    uint4 inline_x[kSlH * 2 / 16];  // fp16 activations carried in the launch parameters: a host-buffer call needs no copy
+    long long spin_limit;         // cycles a wait for other CTAs may take before the kernel gives up
+    uint32_t expect_extra;        // test hook: contributions the poll expects beyond the CTAs there are (0 in production)
+};
+// The same with the first layer's input (and, with chain_residual, its residual) carried in the launch parameters:
+// a host-buffer call then needs no copy.  A kernel instantiation of its own, so that calls on device buffers keep a
+// small parameter block.
+struct SlicedParamsInline : SlicedParams {
+    static constexpr bool kInline = true;
+    uint4 inline_x[kSlH * 2 / 16];  // fp16 activations
 };
 
 // ---------------------------------------------------------------- packed formats and the unit blob
@@ -131,17 +148,17 @@ __device__ __forceinline__ void imma_s8(int (&c)[4], uint32_t a0, uint32_t a1, u
 }
 
 // One 64-wide group of two weight rows (lo: MMA rows 0-7, hi: MMA rows 8-15; this lane holds its 16 levels of
-// each) against the group's activation bytes xb: two MMAs.  Which column sits in which k slot follows from the
-// packing; limb_column() below arranges the activation bytes to match.  Column n of the result is the dot
-// product with mantissa byte n (lanes of a quad hold columns 2t and 2t + 1).
-__device__ __forceinline__ void group_imma(int (&c)[4], const uint2 &lo, const uint2 &hi, const uint4 &xb) {   // Q4_0
+// each) against the group's activation bytes xb: two MMAs, the first 32 columns of the group into accumulator a,
+// the other 32 into accumulator b, so that consecutive groups form two independent chains.  Which column sits in
+// which k slot follows from the packing; limb_column() below arranges the activation bytes to match.
+__device__ __forceinline__ void group_imma(int (&ca)[4], int (&cb)[4], const uint2 &lo, const uint2 &hi, const uint4 &xb) {   // Q4_0
     constexpr uint32_t M = 0x0F0F0F0Fu;
-    imma_u8(c, lo.x & M, hi.x & M, lo.y & M, hi.y & M, xb.x, xb.y);                                  // low nibbles
-    imma_u8(c, (lo.x >> 4) & M, (hi.x >> 4) & M, (lo.y >> 4) & M, (hi.y >> 4) & M, xb.z, xb.w);      // high nibbles
+    imma_u8(ca, lo.x & M, hi.x & M, lo.y & M, hi.y & M, xb.x, xb.y);                                  // low nibbles
+    imma_u8(cb, (lo.x >> 4) & M, (hi.x >> 4) & M, (lo.y >> 4) & M, (hi.y >> 4) & M, xb.z, xb.w);      // high nibbles
 }
-__device__ __forceinline__ void group_imma(int (&c)[4], const uint4 &lo, const uint4 &hi, const uint4 &xb) {   // Q8_0
-    imma_s8(c, lo.x, hi.x, lo.y, hi.y, xb.x, xb.y);
-    imma_s8(c, lo.z, hi.z, lo.w, hi.w, xb.z, xb.w);
+__device__ __forceinline__ void group_imma(int (&ca)[4], int (&cb)[4], const uint4 &lo, const uint4 &hi, const uint4 &xb) {   // Q8_0
+    imma_s8(ca, lo.x, hi.x, lo.y, hi.y, xb.x, xb.y);
+    imma_s8(cb, lo.z, hi.z, lo.w, hi.w, xb.z, xb.w);
 }
 // first of the four consecutive columns (inside the group) behind activation word p = 4 t + 2 j + r of a group:
 // lane-in-quad t, MMA j of the group, B register r
@@ -151,44 +168,42 @@ __device__ __forceinline__ int limb_column(int p) {
     return QT == UOCR_QT_Q4 ? 32 * j + 8 * t + 4 * r : 16 * t + 8 * j + 4 * r;
 }
 
-// Block-floating-point form of 64-wide groups of fp16 values, written by 16 consecutive lanes per group (this
-// thread: word p = idx % 16 of group idx / 16).  dst: [group][3 mantissa bytes][16 words]; scale[group] = 2^(e - 21);
-// ncorr[group] = -8 * sum(mantissas) for Q4 (0 for Q8), ncorr[ngroups_stride + group] = 0 (read by the lanes
-// that hold the high mantissa byte).
+// Block-floating-point form of one 64-wide group of fp16 values, computed by 16 consecutive lanes (this lane: the
+// four values behind word p): a shared power-of-two scale 2^(e - 13) and signed 15-bit mantissas (exact for every
+// value within a factor 8 of the group's largest, rounded to 2^-14 of the largest's power of two otherwise), each
+// split into a signed low byte and a signed high byte (|high| <= 64).  msum is the sum of the group's mantissas.
+struct GroupLimbs {
+    uint32_t lo, hi;      // the low / high bytes of this lane's four values
+    float scale;
+    int msum;
+};
 template <int QT>
-__device__ __forceinline__ void write_limbs(const __half *src, int idx, uint32_t *dst, float *scale, float *ncorr, int zero_off) {
-    const int G = idx >> 4, p = idx & 15;
-    const uint2 raw = *reinterpret_cast<const uint2 *>(src + G * 64 + limb_column<QT>(p));
+__device__ __forceinline__ GroupLimbs group_limbs(const __half *group, int p) {
+    const uint2 raw = *reinterpret_cast<const uint2 *>(group + limb_column<QT>(p));
     const float2 f01 = __half22float2(*reinterpret_cast<const __half2 *>(&raw.x));
     const float2 f23 = __half22float2(*reinterpret_cast<const __half2 *>(&raw.y));
     const float x[4] = {f01.x, f01.y, f23.x, f23.y};
     float amax = fmaxf(fmaxf(fabsf(x[0]), fabsf(x[1])), fmaxf(fabsf(x[2]), fabsf(x[3])));
 #pragma unroll
     for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o, 16));
-    // amax = 1.f * 2^e (fp16 values: e in [-24, 15]); up = 2^(21 - e), down = 2^(e - 21); a group of zeros gets 0
+    // amax = 1.f * 2^e (fp16 values: e in [-24, 15]); up = 2^(13 - e), scale = 2^(e - 13); a group of zeros gets 0
     const int e = (int)(__float_as_uint(amax) >> 23) - 127;
     const bool live = amax > 0.f && amax < INFINITY;
-    const float up = live ? __uint_as_float((uint32_t)(127 + 21 - e) << 23) : 0.f;
-    int msum = 0;
-    uint32_t w[3] = {0u, 0u, 0u};
+    const float up = live ? __uint_as_float((uint32_t)(127 + 13 - e) << 23) : 0.f;
+    GroupLimbs out;
+    out.lo = 0u; out.hi = 0u; out.msum = 0;
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-        const int m = __float2int_rn(x[i] * up);          // |m| < 2^22
-        msum += m;
-        const int l0 = (int)((uint32_t)m << 24) >> 24, m1 = (m - l0) >> 8, l1 = (int)((uint32_t)m1 << 24) >> 24, l2 = (m1 - l1) >> 8;
-        w[0] |= (uint32_t)(l0 & 0xff) << (8 * i);
-        w[1] |= (uint32_t)(l1 & 0xff) << (8 * i);
-        w[2] |= (uint32_t)(l2 & 0xff) << (8 * i);
+        const int m = __float2int_rn(x[i] * up);          // |m| < 2^14
+        out.msum += m;
+        const int l0 = (int)((uint32_t)m << 24) >> 24, l1 = (m - l0) >> 8;
+        out.lo |= (uint32_t)(l0 & 0xff) << (8 * i);
+        out.hi |= (uint32_t)(l1 & 0xff) << (8 * i);
     }
 #pragma unroll
-    for (int o = 8; o > 0; o >>= 1) msum += __shfl_xor_sync(0xffffffffu, msum, o, 16);
-#pragma unroll
-    for (int L = 0; L < 3; ++L) dst[(G * 3 + L) * 16 + p] = w[L];
-    if (p == 0) {
-        scale[G] = live ? __uint_as_float((uint32_t)(127 - 21 + e) << 23) : 0.f;
-        ncorr[G] = QT == UOCR_QT_Q4 ? -8.f * (float)msum : 0.f;
-        ncorr[zero_off + G] = 0.f;
-    }
+    for (int o = 8; o > 0; o >>= 1) out.msum += __shfl_xor_sync(0xffffffffu, out.msum, o, 16);
+    out.scale = live ? __uint_as_float((uint32_t)(127 - 13 + e) << 23) : 0.f;
+    return out;
 }
 
 __device__ __forceinline__ void red_add_u64(unsigned long long *p, unsigned long long v) {
@@ -226,28 +241,38 @@ __device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t *bar, uint32_t pa
 }
 
 // Shared-memory layout (byte offsets); the layer table comes last.
+//
+// Activation bytes for the MMAs' B operand are kept "by column": [group][MMA column 0..7][16 words].  Group G puts
+// its low mantissa bytes in column 2 (G % 4), its high bytes in column 2 (G % 4) + 1 and leaves the other six
+// columns zero (written once at kernel start).  Four consecutive groups can then be accumulated into ONE set of MMA
+// accumulators: group q only touches result columns 2q and 2q + 1, i.e. the two registers of lane-in-quad q.
+// After the four groups every lane of a quad holds one group's two integer dot products for its rows, and the
+// per-group scaling runs once per four groups with all 32 lanes busy.  The SwiGLU products use the same layout
+// four times ([q][column][16 words], their bytes in columns 2q, 2q + 1) so that four 16-row blocks of `down`
+// share an accumulator set in the same way.
 template <int QT> struct SlSmem {
     static constexpr int kW = 0;                                        // gate/up fragments as in the blob
     static constexpr int kSc = kW + SlBlob<QT>::kGuBytes;               // gate scales [64][20], up scales [64][20] (fp16)
     static constexpr int kX = kSc + SlBlob<QT>::kGuScBytes;             // activations, fp16 natural order
-    static constexpr int kXf = kX + kSlH * 2;                           // activation mantissa bytes [20][3][16 words]
-    static constexpr int kXs = kXf + kSlGroups * 3 * 16 * 4;            // [20] group scales, then [2][20] negated corrections
-    static constexpr int kGu = kXs + 256;                               // [2][128] partial gate / up sums of the two group parities
+    static constexpr int kXf = kX + kSlH * 2;                           // activation bytes [20][8][16 words]
+    static constexpr int kXs = kXf + kSlGroups * 8 * 16 * 4;            // [20] {group scale, offset correction}
+    static constexpr int kGu = kXs + 256;                               // [2][128] partial gate / up sums of the two warp halves
     static constexpr int kMid = kGu + 2 * 128 * 4;                      // [64] fp16 SwiGLU products
-    static constexpr int kMidf = kMid + 128;                            // their mantissa bytes [3][16 words], scale, corrections
-    static constexpr int kPart = kMidf + 256;                           // [H] this CTA's partial outputs (read by its cluster)
-    static constexpr int kRp = kPart + kSlH * 4;                        // [16 warps][16 experts] partial router logits
+    static constexpr int kMidf = kMid + 128;                            // their bytes [4][8][16 words], then scale, correction
+    static constexpr int kRp = kMidf + 4 * 8 * 16 * 4 + 64;             // [16 warps][16 experts] partial router logits
     static constexpr int kLogits = kRp + 4 * 64 * 4;                    // [64]
     static constexpr int kProbs = kLogits + 256;                        // [64]
-    static constexpr int kIds = kProbs + 256;                           // ids [8], weights [8], flags [2], mid correction
-    static constexpr int kBars = kIds + 128;                            // kSlChunks copy barriers, scale barrier, two cluster barriers
+    static constexpr int kIds = kProbs + 256;                           // ids [8], weights [8], flags [2]
+    static constexpr int kBars = kIds + 128;                            // kSlChunks copy barriers, scale barrier, cluster barrier
     static constexpr int kLayers = kBars + 8 * 8;                       // DLayer table
     static constexpr int kTotal = kLayers + kSlMaxLayers * (int)sizeof(DLayer);
 };
 
+template <int N> struct SlInt { static constexpr int value = N; };
+
 // ---------------------------------------------------------------- the kernel
-template <int QT>
-__global__ void __launch_bounds__(kSlThreads, 1) decode_sliced_kernel(const __grid_constant__ SlicedParams prm) {
+template <int QT, class Params>
+__global__ void __launch_bounds__(kSlThreads, 1) decode_sliced_kernel(const __grid_constant__ Params prm) {
     using Bl = SlBlob<QT>;
     using Sm = SlSmem<QT>;
     constexpr int H = kSlH, K = kSlK, E = kSlE;
@@ -258,13 +283,11 @@ __global__ void __launch_bounds__(kSlThreads, 1) decode_sliced_kernel(const __gr
     __half *s_sc = reinterpret_cast<__half *>(smem + Sm::kSc);
     __half *s_x = reinterpret_cast<__half *>(smem + Sm::kX);
     uint32_t *s_xf = reinterpret_cast<uint32_t *>(smem + Sm::kXf);
-    float *s_xs = reinterpret_cast<float *>(smem + Sm::kXs);             // [20] scales
-    float *s_ncorr = s_xs + kSlGroups;                                   // [2][20]: real corrections, zeros
+    float2 *s_xsnc = reinterpret_cast<float2 *>(smem + Sm::kXs);         // [20] {scale, -8 * sum of mantissas (Q4_0) or 0}
     float *s_gu = reinterpret_cast<float *>(smem + Sm::kGu);
     __half *s_mid = reinterpret_cast<__half *>(smem + Sm::kMid);
-    uint32_t *s_midf = reinterpret_cast<uint32_t *>(smem + Sm::kMidf);   // [3][16 words]
-    float *s_mscale = reinterpret_cast<float *>(s_midf + 48);            // scale, then corrections [2]
-    float *s_part = reinterpret_cast<float *>(smem + Sm::kPart);
+    uint32_t *s_midf = reinterpret_cast<uint32_t *>(smem + Sm::kMidf);   // [4][8][16 words]
+    float *s_mscale = reinterpret_cast<float *>(s_midf + 4 * 8 * 16);    // scale, correction
     float *s_rp = reinterpret_cast<float *>(smem + Sm::kRp);
     float *s_logits = reinterpret_cast<float *>(smem + Sm::kLogits);
     float *s_probs = reinterpret_cast<float *>(smem + Sm::kProbs);
@@ -277,13 +300,15 @@ __global__ void __launch_bounds__(kSlThreads, 1) decode_sliced_kernel(const __gr
     __shared__ uint64_t s_tab[UOCR_EXPF_N];
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int g = lane >> 2, t = lane & 3;                              // MMA row group / lane in quad
+    const int g = lane >> 2, t = lane & 3;                              // MMA row group = B column / lane in quad
     const uint32_t G = gridDim.x, cta = blockIdx.x;
     const bool routed = cta < (uint32_t)kSlRouted;
     const uint32_t slot = routed ? cta / kSlRoutedPerSlot : (uint32_t)K;
     const uint32_t fg = routed ? cta % kSlRoutedPerSlot : cta - kSlRouted;     // 64-wide slice of F (of S)
     uint32_t *status = prm.status;
     const uint32_t crank = cluster_rank(), csize = cluster_size();
+    const uint32_t R = prm.replicas;                                    // accumulator replicas (1, 2 or 4)
+    const long long spin_limit = prm.spin_limit;
 
     if (tid < UOCR_EXPF_N) s_tab[tid] = c_exp_tab[tid];
     if (tid == 0) {
@@ -300,12 +325,17 @@ __global__ void __launch_bounds__(kSlThreads, 1) decode_sliced_kernel(const __gr
         const uint32_t *src = reinterpret_cast<const uint32_t *>(prm.layers + prm.first);
         uint32_t *dst = reinterpret_cast<uint32_t *>(s_layers);
         for (uint32_t i = tid; i < words; i += kSlThreads) dst[i] = src[i];
+        for (int i = tid; i < kSlGroups * 8 * 16; i += kSlThreads) s_xf[i] = 0u;      // the columns no group writes
+        for (int i = tid; i < 4 * 8 * 16; i += kSlThreads) s_midf[i] = 0u;
     }
     // the first layer's input, and its residual in registers
     float res0[3] = {0.f, 0.f, 0.f};
     {
-        const __half *xin = prm.inline_input ? reinterpret_cast<const __half *>(prm.inline_x) : prm.hidden_in;
-        const __half *rin = prm.inline_input ? (prm.chain_residual ? xin : nullptr) : prm.residual0;
+        const __half *xin = prm.hidden_in, *rin = prm.residual0;
+        if constexpr (Params::kInline) {
+            xin = reinterpret_cast<const __half *>(prm.inline_x);
+            rin = prm.chain_residual ? xin : nullptr;
+        }
         for (int h = tid; h < H; h += kSlThreads) s_x[h] = xin[h];
         if (rin != nullptr) {
 #pragma unroll
@@ -316,27 +346,29 @@ __global__ void __launch_bounds__(kSlThreads, 1) decode_sliced_kernel(const __gr
     __syncthreads();
 
     // ---- helpers --------------------------------------------------------------------------------------
-    // fragments and offset corrections of the activations in s_x
+    // mantissa bytes and offset corrections of the activations in s_x
     // (by warps 0 and 2 .. 10: warp 1 of a routed CTA is busy with the exact routing at that time)
     auto build_x_frags = [&]() {
         const int bi = warp == 0 ? tid : tid - 32;
-        if (warp != 1 && bi < kSlGroups * 16) write_limbs<QT>(s_x, bi, s_xf, s_xs, s_ncorr, kSlGroups);     // 16 lanes per group
+        if (warp != 1 && bi < kSlGroups * 16) {                         // 16 lanes per group
+            const int Gi = bi >> 4, p = bi & 15;
+            const GroupLimbs L = group_limbs<QT>(s_x + Gi * 64, p);
+            uint32_t *d = s_xf + (Gi * 8 + 2 * (Gi & 3)) * 16 + p;
+            d[0] = L.lo;
+            d[16] = L.hi;
+            if (p == 0) s_xsnc[Gi] = make_float2(L.scale, QT == UOCR_QT_Q4 ? -8.f * (float)L.msum : 0.f);
+        }
     };
-    // what each lane does with its two result columns (2t, 2t + 1) of a group: columns 0 and 1 (t = 0) are the low
-    // and middle mantissa bytes, column 2 (t = 1) the high byte; the other columns are unused
-    const int limb_mul = t == 0 ? 256 : 0;                              // integer: c[col 2t] + limb_mul * c[col 2t + 1]
-    const float limb_f = t == 0 ? 1.f : (t == 1 ? 65536.f : 0.f);
-    const int corr_row = t == 0 ? 0 : 1;                                // lanes other than t = 0 read zeros as correction
-    const int limb_of_lane = g < 2 ? g : 2;                             // mantissa byte this lane feeds in as MMA column g
-    // Prefetched into registers: this warp's 5 blocks of 16 `down` rows (the unit's 64 columns of each), and the
-    // CTA's part of the next layer's router matrix (requested while waiting at the barrier, used right after it).
+    // Prefetched into registers: this warp's 5 blocks of 16 `down` rows (the unit's 64 columns of each) with the
+    // scales of the rows this lane finishes, and the CTA's part of the next layer's router matrix (requested while
+    // waiting for the layer's output, used right after it).
     uint4 dwn[kSlBlocksPerWarp][2];
     uint2 rtr[5][2];
-    __half dslo[kSlBlocksPerWarp], dshi[kSlBlocksPerWarp];
+    __half dsc4[4];
     // everything of one unit: bulk copies of the gate/up fragments (chunk c completes barrier c) and scales into
     // shared memory, plain loads of the down fragments and scales into registers
     // (one thread issues the copies in the order they are needed, and a routed CTA asks for its down fragments only
-    // once the first chunk is there: all routed CTAs fetch at the same moment and HBM serves what was asked first)
+    // once its first chunk is there: all routed CTAs fetch at the same moment and HBM serves what was asked first)
     auto fetch_gate_up = [&](const uint8_t *blob) {
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         if (tid == 0) {
@@ -349,6 +381,9 @@ __global__ void __launch_bounds__(kSlThreads, 1) decode_sliced_kernel(const __gr
             }
         }
     };
+    // Blocks warp + 16 bi (bi = 0 .. 4).  Blocks 0 .. 3 share one accumulator set, whose results for block bi end up
+    // in lane-in-quad bi (rows g and g + 8 of the block): each lane keeps the scales of exactly those two rows, and
+    // of its two rows of block 4.
     auto fetch_down = [&](const uint8_t *blob) {
         const uint4 *dn = reinterpret_cast<const uint4 *>(blob + Bl::kDn);
         const __half *dsc = reinterpret_cast<const __half *>(blob + Bl::kDnSc);
@@ -361,9 +396,11 @@ __global__ void __launch_bounds__(kSlThreads, 1) decode_sliced_kernel(const __gr
             } else {
                 dwn[bi][0] = __ldg(dn + blk * 32 + lane);         // rows g: .x .y, rows g + 8: .z .w
             }
-            dslo[bi] = dsc[16 * blk + g];
-            dshi[bi] = dsc[16 * blk + 8 + g];
         }
+        dsc4[0] = dsc[16 * (warp + 16 * t) + g];
+        dsc4[1] = dsc[16 * (warp + 16 * t) + 8 + g];
+        dsc4[2] = dsc[16 * (warp + 64) + g];
+        dsc4[3] = dsc[16 * (warp + 64) + 8 + g];
     };
     auto fetch_unit = [&](const uint8_t *blob) { fetch_gate_up(blob); fetch_down(blob); };
     // This CTA's quarter of the router matrix (experts 16 crank .. +15, fp16 [E][H]) as MMA A fragments: warp w holds
@@ -394,7 +431,8 @@ __global__ void __launch_bounds__(kSlThreads, 1) decode_sliced_kernel(const __gr
     for (uint32_t li = 0; li < prm.count; ++li) {
         const DLayer &L = s_layers[li];
         const bool last = li + 1 == prm.count;
-        unsigned long long *acc = prm.acc + (size_t)((prm.acc_base + li) % kSlAccBuffers) * H;
+        // the layer's accumulator: R replicas of H words; this CTA adds to replica cta % R, readers sum all R
+        unsigned long long *acc = prm.acc + (size_t)((prm.acc_base + li) % kSlAccBuffers) * kSlMaxReplicas * H;
         UOCR_SL_TRACE(0);     // activations of this layer arranged
         bool valid = true;
         float weight = 1.0f;
@@ -426,15 +464,13 @@ __global__ void __launch_bounds__(kSlThreads, 1) decode_sliced_kernel(const __gr
                         for (uint32_t r = 0; r < csize; ++r) st_async_f32(cluster_addr(s_logits + e, r), v, cluster_addr(lg_bar, r));
                     }
                     if (lane == 0) {
-                        int ok = 1;
                         mbar_expect_tx(lg_bar, 16u * 4u * csize);       // this phase: 16 logits from each CTA of the cluster
                         if (!mbar_try_wait_cluster(lg_bar, lg_phase)) {
                             const long long t0 = clock64();
                             while (!mbar_try_wait_cluster(lg_bar, lg_phase)) {
-                                if (clock64() - t0 > kSpinLimit) { atomicOr(status, kStatusBarrier); s_flag[1] = 1; ok = 0; break; }
+                                if (clock64() - t0 > spin_limit) { atomicOr(status, kStatusBarrier); s_flag[1] = 1; break; }
                             }
                         }
-                        (void)ok;
                     }
                 }
                 lg_phase ^= 1u;
@@ -490,43 +526,63 @@ __global__ void __launch_bounds__(kSlThreads, 1) decode_sliced_kernel(const __gr
         }
         UOCR_SL_TRACE(2);         // weight fetches issued
         {
-            // ---- gate / up: warp (rb, kh) multiplies rows 8 rb .. +7 of both matrices with the groups of parity kh,
-            // chunk by chunk as the copies land
+            // ---- gate / up.  Warp (rb, kh) multiplies rows 8 rb .. +7 of both matrices with half of the groups, four
+            // groups (= one chunk of the copy) per accumulator set, as the copies land: warps kh = 0 take chunks 0 and
+            // 2, warps kh = 1 chunks 1 and 3, and the last chunk is split between them so that all sixteen work on it.
             const int rb = warp & 7, kh = warp >> 3;
             bool got = mbar_wait(sc_bar, copy_phase, status, s_flag);
             float sg = 0.f, su = 0.f;
-            {
-                const __half *scg = s_sc + (8 * rb + g) * kSlGroups;
-                const __half *scu = scg + 64 * kSlGroups;
-                // straight-line code: chunk c holds groups 4c .. 4c + 3, this warp takes the two of its parity
+            const __half *scg = s_sc + (8 * rb + g) * kSlGroups;
+            const __half *scu = scg + 64 * kSlGroups;
+            // groups G0 + QLO .. G0 + QHI - 1 (G0 a multiple of 4) into one accumulator set; lane-in-quad q then
+            // holds group G0 + q: its low-byte and high-byte dot products with gate row g (c[0], c[1]) and up row g
+            // (c[2], c[3])
+            auto quad = [&](int G0, auto qlo, auto qhi) {
+                constexpr int QLO = decltype(qlo)::value, QHI = decltype(qhi)::value;
+                int ca[4] = {0, 0, 0, 0}, cb[4] = {0, 0, 0, 0};
 #pragma unroll
-                for (int ch = 0; ch < kSlChunks; ++ch) {
-                    got = mbar_wait(&bars[ch], copy_phase, status, s_flag) && got;
-                    if (ch == 0) {
-                        UOCR_SL_TRACE(3);              // first chunk is in shared memory
-                        if (routed) fetch_down(blob);
-                    }
-#pragma unroll
-                    for (int q = 0; q < 2; ++q) {
-                        const int Gi = 4 * ch + 2 * q + kh;
-                        const uint4 xb = *reinterpret_cast<const uint4 *>(s_xf + ((Gi * 3 + limb_of_lane) * 4 + t) * 4);
-                        int c[4] = {0, 0, 0, 0};
-                        if (QT == UOCR_QT_Q8) {
-                            const uint4 a = s_w4[((Gi * 8 + rb) * 2) * 32 + lane], b = s_w4[((Gi * 8 + rb) * 2 + 1) * 32 + lane];
-                            group_imma(c, a, b, xb);
-                        } else {
-                            const uint4 v = s_w4[(Gi * 8 + rb) * 32 + lane];       // gate: .x .y, up: .z .w
-                            group_imma(c, make_uint2(v.x, v.y), make_uint2(v.z, v.w), xb);
-                        }
-                        const float xs = s_xs[Gi], nc = s_ncorr[corr_row * kSlGroups + Gi];
-                        sg = fmaf(fmaf((float)(c[1] * limb_mul + c[0]), limb_f, nc), __half2float(scg[Gi]) * xs, sg);
-                        su = fmaf(fmaf((float)(c[3] * limb_mul + c[2]), limb_f, nc), __half2float(scu[Gi]) * xs, su);
+                for (int q = QLO; q < QHI; ++q) {
+                    const int Gi = G0 + q;
+                    const uint4 xb = *reinterpret_cast<const uint4 *>(s_xf + ((Gi * 8 + g) * 4 + t) * 4);
+                    if (QT == UOCR_QT_Q8) {
+                        const uint4 a = s_w4[((Gi * 8 + rb) * 2) * 32 + lane], b = s_w4[((Gi * 8 + rb) * 2 + 1) * 32 + lane];
+                        group_imma(ca, cb, a, b, xb);
+                    } else {
+                        const uint4 v = s_w4[(Gi * 8 + rb) * 32 + lane];       // gate: .x .y, up: .z .w
+                        group_imma(ca, cb, make_uint2(v.x, v.y), make_uint2(v.z, v.w), xb);
                     }
                 }
-                if (!got) { sg = 0.f; su = 0.f; }
+                if (t >= QLO && t < QHI) {
+                    const int Gi = G0 + t;
+                    const float2 xc = s_xsnc[Gi];
+                    const float vg = (float)(ca[0] + cb[0] + ((ca[1] + cb[1]) * 256)) + xc.y;
+                    const float vu = (float)(ca[2] + cb[2] + ((ca[3] + cb[3]) * 256)) + xc.y;
+                    sg = fmaf(vg, __half2float(scg[Gi]) * xc.x, sg);
+                    su = fmaf(vu, __half2float(scu[Gi]) * xc.x, su);
+                }
+            };
+            if (kh == 0) {
+                got = mbar_wait(&bars[0], copy_phase, status, s_flag) && got;
+                UOCR_SL_TRACE(3);              // first chunk is in shared memory
+                if (routed) fetch_down(blob);
+                quad(0, SlInt<0>{}, SlInt<4>{});
+                got = mbar_wait(&bars[2], copy_phase, status, s_flag) && got;
+                quad(8, SlInt<0>{}, SlInt<4>{});
+                got = mbar_wait(&bars[4], copy_phase, status, s_flag) && got;
+                quad(16, SlInt<0>{}, SlInt<2>{});
+            } else {
+                got = mbar_wait(&bars[1], copy_phase, status, s_flag) && got;
+                if (routed) fetch_down(blob);
+                quad(4, SlInt<0>{}, SlInt<4>{});
+                got = mbar_wait(&bars[3], copy_phase, status, s_flag) && got;
+                quad(12, SlInt<0>{}, SlInt<4>{});
+                got = mbar_wait(&bars[4], copy_phase, status, s_flag) && got;
+                quad(16, SlInt<2>{}, SlInt<4>{});
             }
-            // the lanes of a quad hold the parts of different mantissa bytes
+            if (!got) { sg = 0.f; su = 0.f; }
+            // the lanes of a quad hold different groups
             sg += __shfl_xor_sync(0xffffffffu, sg, 1); su += __shfl_xor_sync(0xffffffffu, su, 1);
+            sg += __shfl_xor_sync(0xffffffffu, sg, 2); su += __shfl_xor_sync(0xffffffffu, su, 2);
             if (t == 0) { s_gu[kh * 128 + 8 * rb + g] = sg; s_gu[kh * 128 + 64 + 8 * rb + g] = su; }
             __syncthreads();
             copy_phase ^= 1u;
@@ -542,58 +598,68 @@ __global__ void __launch_bounds__(kSlThreads, 1) decode_sliced_kernel(const __gr
             break;
         }
       }
+        // ---- down: H rows x the slice's 64 columns, straight from registers.  Blocks 0 .. 3 of the warp share one
+        // accumulator set (block bi ends up in lane-in-quad bi), block 4 uses a second one (lane-in-quad 0).
+        float v[4] = {0.f, 0.f, 0.f, 0.f};
         if (valid) {
             if (tid < 64) {
                 const float gate = s_gu[tid] + s_gu[128 + tid], up = s_gu[64 + tid] + s_gu[192 + tid];
                 s_mid[tid] = __float2half_rn(silu_f32(gate) * up);
             }
             __syncthreads();
-            if (warp == 0) write_limbs<QT>(s_mid, lane & 15, s_midf, s_mscale, s_mscale + 1, 1);    // both half-warps write the same
+            if (warp == 0) {          // both half-warps compute the same bytes; each writes two of the four copies
+                const int p = lane & 15, q0 = (lane >> 4) * 2;
+                const GroupLimbs M = group_limbs<QT>(s_mid, p);
+#pragma unroll
+                for (int q = q0; q < q0 + 2; ++q) {
+                    uint32_t *d = s_midf + (q * 8 + 2 * q) * 16 + p;
+                    d[0] = M.lo;
+                    d[16] = M.hi;
+                }
+                if (lane == 0) { s_mscale[0] = M.scale; s_mscale[1] = QT == UOCR_QT_Q4 ? -8.f * (float)M.msum : 0.f; }
+            }
             __syncthreads();
             UOCR_SL_TRACE(4);     // SwiGLU products of the slice
-
-            // ---- down: H rows x the slice's 64 columns, straight from registers; partial outputs to shared memory
-            {
-                const uint4 mbf = *reinterpret_cast<const uint4 *>(s_midf + (limb_of_lane * 4 + t) * 4);
-                const float ms = s_mscale[0] * weight, nc = s_mscale[1 + corr_row];
+            const float ms = s_mscale[0] * weight, nc = s_mscale[1];
+            int ca[4] = {0, 0, 0, 0}, cb[4] = {0, 0, 0, 0}, cc[4] = {0, 0, 0, 0}, cd[4] = {0, 0, 0, 0};
 #pragma unroll
-                for (int bi = 0; bi < kSlBlocksPerWarp; ++bi) {
-                    int c[4] = {0, 0, 0, 0};
-                    if (QT == UOCR_QT_Q8) group_imma(c, dwn[bi][0], dwn[bi][1], mbf);
-                    else group_imma(c, make_uint2(dwn[bi][0].x, dwn[bi][0].y), make_uint2(dwn[bi][0].z, dwn[bi][0].w), mbf);
-                    float v0 = fmaf((float)(c[1] * limb_mul + c[0]), limb_f, nc) * (__half2float(dslo[bi]) * ms);
-                    float v1 = fmaf((float)(c[3] * limb_mul + c[2]), limb_f, nc) * (__half2float(dshi[bi]) * ms);
-                    v0 += __shfl_xor_sync(0xffffffffu, v0, 1);
-                    v1 += __shfl_xor_sync(0xffffffffu, v1, 1);
-                    if (t == 0) {
-                        const uint32_t r0 = 16u * (warp + 16 * bi) + g;
-                        s_part[r0] = v0;
-                        s_part[r0 + 8] = v1;
-                    }
+            for (int bi = 0; bi < kSlBlocksPerWarp; ++bi) {
+                const int q = bi & 3;
+                const uint4 mbf = *reinterpret_cast<const uint4 *>(s_midf + ((q * 8 + g) * 4 + t) * 4);
+                if (bi < 4) {
+                    if (QT == UOCR_QT_Q8) group_imma(ca, cb, dwn[bi][0], dwn[bi][1], mbf);
+                    else group_imma(ca, cb, make_uint2(dwn[bi][0].x, dwn[bi][0].y), make_uint2(dwn[bi][0].z, dwn[bi][0].w), mbf);
+                } else {
+                    if (QT == UOCR_QT_Q8) group_imma(cc, cd, dwn[bi][0], dwn[bi][1], mbf);
+                    else group_imma(cc, cd, make_uint2(dwn[bi][0].x, dwn[bi][0].y), make_uint2(dwn[bi][0].z, dwn[bi][0].w), mbf);
                 }
             }
+            v[0] = ((float)(ca[0] + cb[0] + ((ca[1] + cb[1]) * 256)) + nc) * (__half2float(dsc4[0]) * ms);
+            v[1] = ((float)(ca[2] + cb[2] + ((ca[3] + cb[3]) * 256)) + nc) * (__half2float(dsc4[1]) * ms);
+            v[2] = ((float)(cc[0] + cd[0] + ((cc[1] + cd[1]) * 256)) + nc) * (__half2float(dsc4[2]) * ms);
+            v[3] = ((float)(cc[2] + cd[2] + ((cc[3] + cd[3]) * 256)) + nc) * (__half2float(dsc4[3]) * ms);
         } else {
             UOCR_SL_TRACE(3);
             UOCR_SL_TRACE(4);
-            for (int h = tid; h < H; h += kSlThreads) s_part[h] = 0.f;
         }
         UOCR_SL_TRACE(5);         // partial outputs of this CTA
-        // ---- one integer reduction per column into the accumulator.  A word carries the number of CTAs that have
-        // added to it in its top byte (every CTA adds to every word exactly once per layer), so readers need no
-        // separate barrier: a word whose count is complete is complete.
-        __syncthreads();
+        // ---- one integer reduction per output row into the accumulator, straight from the lane that holds it.  A
+        // word carries the number of CTAs that have added to it in its top byte (every CTA adds to every row exactly
+        // once per layer), so readers need no separate barrier: a row whose count is complete is complete.
         {
+            unsigned long long *mine = acc + (size_t)(cta % R) * H;
+            const uint32_t rows[4] = {16u * (warp + 16 * t) + g, 16u * (warp + 16 * t) + 8u + g,
+                                      16u * (warp + 64) + g, 16u * (warp + 64) + 8u + g};
 #pragma unroll
-            for (int i = 0; i < 3; ++i) {
-                const int h = tid + i * kSlThreads;
-                if (h < H) {
-                    float v = s_part[h];
-                    if (!(fabsf(v) < kSlAccRange)) {      // NaN too: the count must stay intact
+            for (int i = 0; i < 4; ++i) {
+                if (i < 2 || t == 0) {
+                    float x = v[i];
+                    if (!(fabsf(x) < kSlAccRange)) {      // NaN too: the count must stay intact
                         atomicOr(status, kStatusRange);   // visible before the addition below: whoever sees the full
                         __threadfence();                  // count and then reads the status word sees this bit
-                        v = 0.f;
+                        x = 0.f;
                     }
-                    red_add_u64(acc + h, kSlAccOne + (unsigned long long)(__float2ll_rn(v * kSlAccScale) + kSlAccBias));
+                    red_add_u64(mine + rows[i], kSlAccOne + (unsigned long long)(__float2ll_rn(x * kSlAccScale) + kSlAccBias));
                 }
             }
         }
@@ -602,8 +668,8 @@ __global__ void __launch_bounds__(kSlThreads, 1) decode_sliced_kernel(const __gr
         // ---- while the other CTAs finish: the work for later layers that does not need this layer's result
         if (cta == G - 1) {       // clear the accumulator that the layer after next will add to; the clearing is
                                   // ordered before this CTA's next additions, which every later reader waits for
-            unsigned long long *z = prm.acc + (size_t)((prm.acc_base + li + 2) % kSlAccBuffers) * H;
-            for (int h = tid; h < H; h += kSlThreads) z[h] = 0ull;
+            unsigned long long *z = prm.acc + (size_t)((prm.acc_base + li + 2) % kSlAccBuffers) * kSlMaxReplicas * H;
+            for (uint32_t h = tid; h < R * (uint32_t)H; h += kSlThreads) z[h] = 0ull;
             __threadfence();
         }
         if (!last) {
@@ -611,30 +677,39 @@ __global__ void __launch_bounds__(kSlThreads, 1) decode_sliced_kernel(const __gr
             else fetch_unit(s_layers[li + 1].dec_units + (size_t)(kSlE * kSlRoutedPerSlot + fg) * Bl::kBytes);
         }
 
-        // ---- the layer's output = next layer's input: every accumulator word once all G CTAs have added to it,
+        // ---- the layer's output = next layer's input: every accumulator row once all G CTAs have added to it,
         // + residual, rounded to fp16.  The poll is bounded; a CTA that gives up raises the status word, which
         // the others check while they wait.
         {
             unsigned long long w[3] = {0ull, 0ull, 0ull};
             bool have = true;
             const long long t0 = clock64();
-            const unsigned long long full = (unsigned long long)G;
+            const unsigned long long full = (unsigned long long)G + prm.expect_extra;
             for (uint32_t polls = 1;; ++polls) {
-                bool all = true;           // the thread's (up to) three words are requested together: one round trip per poll
+                bool all = true;           // the thread's (up to) three rows are requested together: one round trip per poll
+                unsigned long long nw[3][kSlMaxReplicas];
 #pragma unroll
                 for (int i = 0; i < 3; ++i) {
                     const int h = tid + i * kSlThreads;
-                    if (h < H && (w[i] >> 56) != full) w[i] = ld_relaxed_u64(acc + h);
+                    const bool need = h < H && (w[i] >> 56) != full;
+#pragma unroll
+                    for (int r = 0; r < kSlMaxReplicas; ++r) nw[i][r] = (need && (uint32_t)r < R) ? ld_relaxed_u64(acc + (size_t)r * H + h) : 0ull;
                 }
 #pragma unroll
                 for (int i = 0; i < 3; ++i) {
                     const int h = tid + i * kSlThreads;
-                    if (h < H && (w[i] >> 56) != full) all = false;
+                    if (h < H && (w[i] >> 56) != full) {
+                        unsigned long long s = 0ull;         // counts and sums add up without carrying into each other
+#pragma unroll
+                        for (int r = 0; r < kSlMaxReplicas; ++r) s += nw[i][r];
+                        w[i] = s;
+                        if ((s >> 56) != full) all = false;
+                    }
                 }
                 if (all) break;
                 if ((polls & 15u) == 0u) {
                     if (ld_volatile_u32(status) & (kStatusBarrier | kStatusCopy)) { have = false; break; }
-                    if (clock64() - t0 > kSpinLimit) { atomicOr(status, kStatusBarrier); have = false; break; }
+                    if (clock64() - t0 > spin_limit) { atomicOr(status, kStatusBarrier); have = false; break; }
                 }
             }
             if (__syncthreads_or(!have || s_flag[1] != 0)) return;
@@ -644,10 +719,10 @@ __global__ void __launch_bounds__(kSlThreads, 1) decode_sliced_kernel(const __gr
                 const int h = tid + i * kSlThreads;
                 if (h < H) {
                     const long long sum = (long long)(w[i] & (kSlAccOne - 1ull)) - (long long)G * kSlAccBias;
-                    float v = (float)sum * (1.0f / kSlAccScale);
-                    if (li == 0) v += res0[i];
-                    else if (prm.chain_residual) v += __half2float(s_x[h]);
-                    s_x[h] = __float2half_rn(v);
+                    float o = (float)sum * (1.0f / kSlAccScale);
+                    if (li == 0) o += res0[i];
+                    else if (prm.chain_residual) o += __half2float(s_x[h]);
+                    s_x[h] = __float2half_rn(o);
                 }
             }
         }
@@ -725,7 +800,9 @@ __global__ void repack_units_kernel(RepackSrc src, uint8_t *out) {
 }
 
 // ---------------------------------------------------------------- host side
-static int g_sliced_cluster[64] = {0};      // cluster size the kernel is launched with on a device, 0: cannot run there
+// cluster size the kernel is launched with on a device, 0: cannot run there (written when a context is created,
+// possibly by several threads at once: same value every time)
+static std::atomic<int> g_sliced_cluster[64];
 
 // The shapes and formats this kernel is built for (the model's).
 bool decode_sliced_layer_ok(const DLayer &L) {
@@ -774,15 +851,19 @@ static void launch_config(cudaLaunchConfig_t *cfg, cudaLaunchAttribute *attrs, i
 // 1 when all CTAs can be resident at once in clusters of kSlCluster, else 0
 template <int QT>
 static cudaError_t prepare_sliced(int *ok) {
-    auto kern = decode_sliced_kernel<QT>;
-    cudaError_t err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SlSmem<QT>::kTotal);
+    cudaError_t err = cudaFuncSetAttribute(decode_sliced_kernel<QT, SlicedParams>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           (int)SlSmem<QT>::kTotal);
+    if (err != cudaSuccess) return err;
+    err = cudaFuncSetAttribute(decode_sliced_kernel<QT, SlicedParamsInline>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               (int)SlSmem<QT>::kTotal);
     if (err != cudaSuccess) return err;
     cudaLaunchConfig_t cfg;
     cudaLaunchAttribute attrs[2];
     launch_config<QT>(&cfg, attrs, kSlCluster, nullptr);
-    int clusters = 0;
-    if (cudaOccupancyMaxActiveClusters(&clusters, kern, &cfg) != cudaSuccess) { (void)cudaGetLastError(); clusters = 0; }
-    *ok = clusters * kSlCluster >= kSlUnits ? 1 : 0;
+    int clusters = 0, clusters_inline = 0;
+    if (cudaOccupancyMaxActiveClusters(&clusters, decode_sliced_kernel<QT, SlicedParams>, &cfg) != cudaSuccess) { (void)cudaGetLastError(); clusters = 0; }
+    if (cudaOccupancyMaxActiveClusters(&clusters_inline, decode_sliced_kernel<QT, SlicedParamsInline>, &cfg) != cudaSuccess) { (void)cudaGetLastError(); clusters_inline = 0; }
+    *ok = (clusters * kSlCluster >= kSlUnits && clusters_inline * kSlCluster >= kSlUnits) ? 1 : 0;
     return cudaSuccess;
 }
 
@@ -793,15 +874,15 @@ cudaError_t init_decode_sliced_kernels() {
     int ok4 = 0, ok8 = 0;
     if ((err = prepare_sliced<UOCR_QT_Q4>(&ok4)) != cudaSuccess) return err;
     if ((err = prepare_sliced<UOCR_QT_Q8>(&ok8)) != cudaSuccess) return err;
-    if (dev < 64) g_sliced_cluster[dev] = (ok4 && ok8) ? kSlCluster : 0;
+    if (dev >= 0 && dev < 64) g_sliced_cluster[dev] = (ok4 && ok8) ? kSlCluster : 0;
     return cudaSuccess;
 }
 
-size_t decode_sliced_acc_bytes() { return (size_t)kSlAccBuffers * kSlH * sizeof(unsigned long long); }
+size_t decode_sliced_acc_bytes() { return (size_t)kSlAccBuffers * kSlMaxReplicas * kSlH * sizeof(unsigned long long); }
 
 bool decode_sliced_supported(const DLayer *layers, uint32_t first, uint32_t count) {
     int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev >= 64 || g_sliced_cluster[dev] == 0) return false;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64 || g_sliced_cluster[dev] == 0) return false;
     if (count == 0 || count > (uint32_t)kSlMaxLayers) return false;
     for (uint32_t i = 0; i < count; ++i) {
         const DLayer &L = layers[first + i];
@@ -810,36 +891,47 @@ bool decode_sliced_supported(const DLayer *layers, uint32_t first, uint32_t coun
     return true;
 }
 
+template <int QT, class Params>
+static cudaError_t launch_one(const Params &prm, int cluster, cudaStream_t st) {
+    cudaLaunchConfig_t cfg;
+    cudaLaunchAttribute attrs[2];
+    launch_config<QT>(&cfg, attrs, cluster, st);
+    return cudaLaunchKernelEx(&cfg, decode_sliced_kernel<QT, Params>, prm);
+}
+
 // acc: decode_sliced_acc_bytes() of device memory, zero before the first launch; *acc_base carries the accumulator
 // rotation from launch to launch (reset it, and clear acc, after a failed launch).  host_status: device address of a
 // word in mapped host memory that receives the status word once `out` is complete, or null.  h_inline: host pointer to the H
 // fp16 activations, copied into the launch parameters (hidden and residual0 are then unused; the first layer's
-// residual is the input itself when chain_residual is set), or null.
+// residual is the input itself when chain_residual is set), or null.  knobs: accumulator replicas, the limit of the
+// waits between CTAs, and the test hook that makes the first wait run out.
 cudaError_t launch_decode_sliced(const DLayer *h_layers, const DLayer *d_layers, uint32_t first, uint32_t count,
                                  const __half *hidden, const __half *residual0, const void *h_inline, int chain_residual,
                                  const float *injected,
                                  __half *out, uint32_t *host_status, unsigned long long *acc, uint32_t *acc_base, uint32_t *status,
                                  float *dbg_logits, float *dbg_probs, uint32_t *ids_out, float *wts_out,
-                                 unsigned long long *trace, cudaStream_t st, uint64_t *launches) {
+                                 unsigned long long *trace, const SlicedKnobs &knobs, cudaStream_t st, uint64_t *launches) {
     int dev = 0;
     cudaError_t err = cudaGetDevice(&dev);
     if (err != cudaSuccess) return err;
-    if (dev >= 64 || g_sliced_cluster[dev] == 0) return cudaErrorNotSupported;
-    SlicedParams prm{};
+    if (dev < 0 || dev >= 64 || g_sliced_cluster[dev] == 0) return cudaErrorNotSupported;
+    const int cluster = g_sliced_cluster[dev];
+    SlicedParamsInline prm{};
     prm.layers = d_layers; prm.first = first; prm.count = count;
     prm.hidden_in = hidden; prm.residual0 = residual0; prm.chain_residual = chain_residual;
     prm.injected = injected; prm.out = out; prm.acc = acc; prm.acc_base = *acc_base;
+    prm.replicas = (knobs.replicas == 1 || knobs.replicas == 2 || knobs.replicas == 4) ? knobs.replicas : 1u;
     prm.status = status; prm.host_status = host_status;
-    if (h_inline != nullptr) { prm.inline_input = 1; memcpy(prm.inline_x, h_inline, sizeof(prm.inline_x)); }
+    prm.spin_limit = knobs.spin_limit_cycles > 0 ? knobs.spin_limit_cycles : kSpinLimit;
+    prm.expect_extra = knobs.expect_extra;
     prm.dbg_logits = dbg_logits; prm.dbg_probs = dbg_probs; prm.ids_out = ids_out; prm.wts_out = wts_out; prm.trace = trace;
-    cudaLaunchConfig_t cfg;
-    cudaLaunchAttribute attrs[2];
-    if (h_layers[first].expert_qtype == UOCR_QT_Q4) {
-        launch_config<UOCR_QT_Q4>(&cfg, attrs, g_sliced_cluster[dev], st);
-        err = cudaLaunchKernelEx(&cfg, decode_sliced_kernel<UOCR_QT_Q4>, prm);
+    const bool q4 = h_layers[first].expert_qtype == UOCR_QT_Q4;
+    if (h_inline != nullptr) {
+        memcpy(prm.inline_x, h_inline, sizeof(prm.inline_x));
+        err = q4 ? launch_one<UOCR_QT_Q4, SlicedParamsInline>(prm, cluster, st) : launch_one<UOCR_QT_Q8, SlicedParamsInline>(prm, cluster, st);
     } else {
-        launch_config<UOCR_QT_Q8>(&cfg, attrs, g_sliced_cluster[dev], st);
-        err = cudaLaunchKernelEx(&cfg, decode_sliced_kernel<UOCR_QT_Q8>, prm);
+        const SlicedParams &base = prm;
+        err = q4 ? launch_one<UOCR_QT_Q4, SlicedParams>(base, cluster, st) : launch_one<UOCR_QT_Q8, SlicedParams>(base, cluster, st);
     }
     if (err != cudaSuccess) return err;
     *acc_base = (*acc_base + count) % kSlAccBuffers;

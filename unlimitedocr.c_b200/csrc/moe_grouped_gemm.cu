@@ -23,6 +23,7 @@
 #include <cuda.h>
 #include <cudaTypedefs.h>
 
+#include <atomic>
 #include <cstdio>
 #include <cstdlib>
 
@@ -733,16 +734,16 @@ __global__ void combine_peer_kernel(PeerBuffers peer, const __half *__restrict__
 }
 
 // ---------------------------------------------------------------------------- host side
-static PFN_cuTensorMapEncodeTiled_v12000 g_encode = nullptr;
+static std::atomic<PFN_cuTensorMapEncodeTiled_v12000> g_encode{nullptr};    // process-wide, the same value from every thread
 
 cudaError_t init_gemm_kernels() {
-    if (g_encode == nullptr) {
+    if (g_encode.load() == nullptr) {
         void *fn = nullptr;
         cudaDriverEntryPointQueryResult qres;
         cudaError_t err = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
         if (err != cudaSuccess) return err;
         if (qres != cudaDriverEntryPointSuccess || fn == nullptr) return cudaErrorNotSupported;
-        g_encode = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(fn);
+        g_encode.store(reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(fn));
     }
     cudaError_t err = cudaFuncSetAttribute(router_logits_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                            (int)(kRouterStages * (kTileBytes + 32 * 1024) + 1024 + 256));
@@ -763,7 +764,7 @@ static cudaError_t make_map_rows(CUtensorMap *map, const void *base, uint64_t ro
     const cuuint64_t strides[1] = {cols * 2};
     const cuuint32_t box[2] = {kBlockK, box_rows};
     const cuuint32_t estr[2] = {1, 1};
-    const CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void *>(base), dims, strides, box, estr,
+    const CUresult r = g_encode.load()(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void *>(base), dims, strides, box, estr,
                                 CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
@@ -774,7 +775,7 @@ static size_t router_gemm_smem(uint32_t n_pad) {
     return kRouterStages * (kTileBytes + b_bytes) + 1024 + 256;
 }
 
-bool router_gemm_supported(const DLayer &L) { return g_encode != nullptr && L.H % 64 == 0 && L.E <= 256; }
+bool router_gemm_supported(const DLayer &L) { return g_encode.load() != nullptr && L.H % 64 == 0 && L.E <= 256; }
 
 // logits[n][E] (no bias) for n tokens
 cudaError_t launch_router_logits(const DLayer &L, const __half *hidden, uint32_t n, float *logits, uint32_t *status,
@@ -794,7 +795,7 @@ cudaError_t launch_router_logits(const DLayer &L, const __half *hidden, uint32_t
 
 bool gemm_path_supported(const DLayer &L) {
     return L.H % 128 == 0 && L.F % 128 == 0 && L.S % 128 == 0 && L.E <= 256 && L.H <= 2048 && L.F <= 2048 &&
-           L.S <= 2048 && g_encode != nullptr;
+           L.S <= 2048 && g_encode.load() != nullptr;
 }
 
 template <bool GU>
@@ -926,6 +927,46 @@ cudaError_t launch_combine_peer(const DLayer &L, const Scratch &S, const GemmScr
     combine_peer_kernel<<<(unsigned)((work + 255) / 256), 256, 0, st>>>(done, G.shared_out, residual, S.inverse, S.top_ids,
                                                                         S.top_weights, S.expert_offsets, dst_row0,
                                                                         experts_per_rank, L.E, n, L.H, L.K, row_capacity, S.status, out);
+    ++*launches;
+    return cudaGetLastError();
+}
+
+// ---- dequantisation probe ------------------------------------------------------------------------------------
+// out[row][col] = the fp16 value (widened to f32) the grouped GEMM's producer threads store into tensor memory for
+// weight (row, col): the same load_block / convert_sub pair, one thread per (row, 64-wide K block, half h).
+template <int QT>
+__global__ void producer_probe_kernel(const uint8_t *__restrict__ w, const __half *__restrict__ s, uint32_t rows, uint32_t cols,
+                                      uint32_t row_bytes, float *__restrict__ out) {
+    const uint32_t kblocks = cols / kBlockK;
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (size_t)rows * kblocks * 2) return;
+    const int h = (int)(idx & 1);
+    const uint32_t kb = (uint32_t)((idx >> 1) % kblocks), row = (uint32_t)((idx >> 1) / kblocks);
+    uint4 v[PackedBlock<QT>::kVecs];
+    load_block<QT>(w + (size_t)row * row_bytes, kb, h, v);
+    const __half sc = QT == UOCR_QT_F16 ? __ushort_as_half(0) : s[(size_t)row * kblocks + kb];
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+        uint32_t regs[8];
+        convert_sub<QT>(v, j, sc, regs);
+        float *dst = out + (size_t)row * cols + (size_t)kb * kBlockK + 32 * j + 16 * h;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&regs[i]));
+            dst[2 * i] = f.x;
+            dst[2 * i + 1] = f.y;
+        }
+    }
+}
+
+cudaError_t launch_producer_probe(const DMatrix &m, float *out, cudaStream_t st, uint64_t *launches) {
+    const size_t work = (size_t)m.rows * (m.cols / kBlockK) * 2;
+    const unsigned blocks = (unsigned)((work + 255) / 256);
+    switch (m.qtype) {
+        case UOCR_QT_Q4: producer_probe_kernel<UOCR_QT_Q4><<<blocks, 256, 0, st>>>(m.w, m.s, m.rows, m.cols, m.row_bytes, out); break;
+        case UOCR_QT_Q8: producer_probe_kernel<UOCR_QT_Q8><<<blocks, 256, 0, st>>>(m.w, m.s, m.rows, m.cols, m.row_bytes, out); break;
+        default: producer_probe_kernel<UOCR_QT_F16><<<blocks, 256, 0, st>>>(m.w, m.s, m.rows, m.cols, m.row_bytes, out); break;
+    }
     ++*launches;
     return cudaGetLastError();
 }

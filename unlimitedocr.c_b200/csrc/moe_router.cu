@@ -6,23 +6,28 @@
 // (src/backend/cpu_ref/uocr_cpu_ref.c:388-466), so identical logits give identical ids and weights.
 //
 // Dispatch plan: stable counting sort of pair = token*K + slot by expert id.
+#include <mutex>
+
 #include "moe_route.cuh"
 
 namespace uocr {
 
 __constant__ uint64_t c_exp_tab[UOCR_EXPF_N];
 
+// Per-device, set up once; contexts may be created from several threads at the same time.
+static std::mutex g_tab_mutex;
 static bool g_tab_ready[64] = {false};
 
 static cudaError_t ensure_exp_table() {
     int dev = 0;
     cudaError_t err = cudaGetDevice(&dev);
     if (err != cudaSuccess) return err;
-    if (dev < 64 && g_tab_ready[dev]) return cudaSuccess;
+    std::lock_guard<std::mutex> lock(g_tab_mutex);
+    if (dev >= 0 && dev < 64 && g_tab_ready[dev]) return cudaSuccess;
     uint64_t tab[UOCR_EXPF_N];
     uocr_expf_table_init(tab);
     err = cudaMemcpyToSymbol(c_exp_tab, tab, sizeof tab);
-    if (err == cudaSuccess && dev < 64) g_tab_ready[dev] = true;
+    if (err == cudaSuccess && dev >= 0 && dev < 64) g_tab_ready[dev] = true;
     return err;
 }
 
@@ -336,6 +341,7 @@ struct NoAllocDeviceState {
     bool ready = false;
 };
 static NoAllocDeviceState g_noalloc[64];
+static std::mutex g_noalloc_mutex;      // first calls from two host threads must not both run the set-up
 
 }  // namespace uocr
 
@@ -362,7 +368,10 @@ extern "C" int uocr_cuda_moe_dispatch_plan_noalloc(const uint32_t *d_top_ids, ui
     if (err != cudaSuccess) return fail("cudaGetDevice failed", cudaGetErrorString(err));
     if (dev < 0 || dev >= 64) return fail("device index out of range", nullptr);
     uocr::NoAllocDeviceState &state = uocr::g_noalloc[dev];
-    if (!state.ready) {
+    uint32_t *scratch = nullptr;
+    {
+      std::lock_guard<std::mutex> lock(uocr::g_noalloc_mutex);
+      if (!state.ready) {
         // first call on this device: resolve the scratch array's device address and raise the kernel's
         // dynamic shared-memory limit.  Neither allocates; both must happen outside a stream capture.
         void *ptr = nullptr;
@@ -372,10 +381,12 @@ extern "C" int uocr_cuda_moe_dispatch_plan_noalloc(const uint32_t *d_top_ids, ui
         if (err != cudaSuccess) return fail("cudaFuncSetAttribute(plan kernel) failed", cudaGetErrorString(err));
         state.scratch = static_cast<uint32_t *>(ptr);
         state.ready = true;
+      }
+      scratch = state.scratch;
     }
     uint64_t launches = 0;
     err = uocr::launch_dispatch_plan(d_top_ids, n_tokens, top_k, n_experts, d_expert_offsets, d_pair_rows, d_inverse,
-                                     state.scratch, nullptr, (cudaStream_t)cuda_stream, &launches);
+                                     scratch, nullptr, (cudaStream_t)cuda_stream, &launches);
     if (err != cudaSuccess) return fail("dispatch-plan launch failed", cudaGetErrorString(err));
     return 1;
 }

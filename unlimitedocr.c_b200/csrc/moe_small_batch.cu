@@ -259,4 +259,41 @@ cudaError_t launch_small_batch_layer(const DLayer &L, const Scratch &S, const __
     return cudaGetLastError();
 }
 
+// ---- dequantisation probe ------------------------------------------------------------------------------------
+// out[row][col] = the f32 value the matrix-vector kernels give weight (row, col): the row is multiplied, through the
+// same row_dot() the layer kernels use, with a one-hot activation vector per column, which leaves level * scale.
+// One CTA per row, one activation buffer per warp.
+constexpr int kProbeWarps = 4;
+
+template <int QT>
+__global__ void __launch_bounds__(kProbeWarps * 32)
+dequant_probe_kernel(const uint8_t *__restrict__ w, const __half *__restrict__ s, uint32_t cols, uint32_t row_bytes,
+                     float *__restrict__ out) {
+    extern __shared__ float xs[];   // [kProbeWarps][cols]
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const uint32_t row = blockIdx.x, groups = cols / UOCR_GROUP;
+    float *x = xs + (size_t)warp * cols;
+    for (uint32_t c = lane; c < cols; c += 32) x[c] = 0.f;
+    __syncwarp();
+    const uint8_t *wrow = w + (size_t)row * row_bytes;
+    const __half *srow = s ? s + (size_t)row * groups : nullptr;
+    for (uint32_t c = warp; c < cols; c += kProbeWarps) {
+        if (lane == 0) x[c] = 1.f;
+        __syncwarp();
+        float acc[1] = {0.f};
+        row_dot<QT, 1>(wrow, srow, cols, x, (int)cols, lane, acc);
+        const float v = warp_sum(acc[0]);
+        if (lane == 0) { out[(size_t)row * cols + c] = v; x[c] = 0.f; }
+        __syncwarp();
+    }
+}
+
+cudaError_t launch_dequant_probe(const DMatrix &m, float *out, cudaStream_t st, uint64_t *launches) {
+    const size_t smem = sizeof(float) * kProbeWarps * m.cols;
+    if (smem > 48 * 1024) return cudaErrorInvalidValue;
+    UOCR_QT_SWITCH(m.qtype, (dequant_probe_kernel<QT><<<m.rows, kProbeWarps * 32, smem, st>>>(m.w, m.s, m.cols, m.row_bytes, out)));
+    ++*launches;
+    return cudaGetLastError();
+}
+
 }  // namespace uocr

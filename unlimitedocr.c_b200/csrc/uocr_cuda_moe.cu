@@ -39,6 +39,8 @@ cudaError_t launch_gemm_shared(const DLayer &L, const Scratch &S, const GemmScra
                                cudaStream_t st, uint64_t *launches);
 cudaError_t launch_gemm_combine(const DLayer &L, const Scratch &S, const GemmScratch &G, const __half *down_rows,
                                 const __half *residual, uint32_t n, __half *out, cudaStream_t st, uint64_t *launches);
+cudaError_t launch_dequant_probe(const DMatrix &m, float *out, cudaStream_t st, uint64_t *launches);
+cudaError_t launch_producer_probe(const DMatrix &m, float *out, cudaStream_t st, uint64_t *launches);
 int decode_grid_size();
 bool decode_supported(const DLayer *layers, uint32_t first, uint32_t count);
 bool decode_sliced_layer_ok(const DLayer &L);
@@ -51,7 +53,7 @@ cudaError_t launch_decode_sliced(const DLayer *h_layers, const DLayer *d_layers,
                                  const float *injected, __half *out, uint32_t *host_status, unsigned long long *acc,
                                  uint32_t *acc_base, uint32_t *status,
                                  float *dbg_logits, float *dbg_probs, uint32_t *ids_out, float *wts_out,
-                                 unsigned long long *trace, cudaStream_t st, uint64_t *launches);
+                                 unsigned long long *trace, const SlicedKnobs &knobs, cudaStream_t st, uint64_t *launches);
 cudaError_t launch_decode_stack(const DLayer *h_layers, const DLayer *d_layers, uint32_t first, uint32_t count,
                                 const __half *hidden, const __half *residual0, int chain_residual,
                                 const float *injected, __half *out, __half *hbuf0, __half *hbuf1, __half *mid,
@@ -79,6 +81,8 @@ struct uocr_cuda_context {
     bool sliced_decode = true;         // ... in its one-barrier-per-layer form when the shapes allow it
     unsigned long long bar_base = 0;   // value the decode kernel's barrier counter has reached
     uint32_t acc_base = 0;             // accumulator buffer the next sliced decode launch starts with
+    uocr::SlicedKnobs decode_knobs;    // replicas of the decode accumulator, wait limit
+    bool test_stall_once = false;      // test hook: the next sliced decode launch waits for a contribution nobody makes
     size_t status_bytes = 0;           // status word, barrier counter and the decode accumulators
     unsigned long long *decode_trace = nullptr;   // optional device buffer for per-phase clock stamps
     std::vector<void *> weight_allocs;
@@ -207,6 +211,12 @@ extern "C" uocr_cuda_context *uocr_cuda_context_create(const char *resource_path
     const char *design = getenv("UOCR_CUDA_DECODE_DESIGN");      // "two-barrier": the earlier persistent kernel
     ctx->sliced_decode = !(design && strcmp(design, "two-barrier") == 0);   // (then no slice-major weight copy is made)
     if (const char *mt = getenv("UOCR_CUDA_GEMM_MIN_TOKENS")) ctx->gemm_min_tokens = (uint32_t)strtoul(mt, nullptr, 10);
+    if (const char *r = getenv("UOCR_CUDA_DECODE_REPLICAS")) ctx->decode_knobs.replicas = (uint32_t)strtoul(r, nullptr, 10);
+    // Test hooks for the time-out path of the decode kernel's waits: a shorter limit (in SM cycles), and one launch
+    // whose wait for the layer output expects one contribution more than there are CTAs.  Nothing faults: the wait
+    // runs into its limit, the kernel raises its status word and returns.
+    if (const char *c = getenv("UOCR_CUDA_TEST_SPIN_LIMIT_CYCLES")) ctx->decode_knobs.spin_limit_cycles = strtoll(c, nullptr, 10);
+    if (const char *c = getenv("UOCR_CUDA_TEST_DECODE_STALL_ONCE")) ctx->test_stall_once = c[0] == '1';
     return ctx;
 }
 
@@ -443,9 +453,6 @@ struct ArenaLayout {
         counts, plan_counts, seg_offsets, total;
 };
 
-// down products are f32 while the call is small enough to take the matrix-vector path, fp16 beyond
-static bool small_batch(uint32_t n) { return n <= 256; }
-
 static ArenaLayout layout_arena(uint32_t H, uint32_t E, uint32_t K, uint32_t F, uint32_t S, uint32_t n) {
     ArenaLayout a{};
     uint64_t off = 0;
@@ -461,7 +468,9 @@ static ArenaLayout layout_arena(uint32_t H, uint32_t E, uint32_t K, uint32_t F, 
     a.active = take((uint64_t)(E + 1) * 4);
     a.mid = take(pairs * F * 2);
     a.shared_mid = take((uint64_t)n * S * 2);
-    a.down_out = take(pairs * H * (small_batch(n) ? 4 : 2));
+    // routed down products: f32 on the matrix-vector path, fp16 on the tensor-core path.  Which path a call takes
+    // depends on the layer's shapes and on a run-time threshold, so the slot always has room for f32.
+    a.down_out = take(pairs * H * 4);
     a.shared_out = take((uint64_t)n * H * 4);
     a.stack0 = take((uint64_t)n * H * 2);
     a.stack1 = take((uint64_t)n * H * 2);
@@ -513,12 +522,7 @@ extern "C" int uocr_cuda_context_allocate_runtime_arenas(uocr_cuda_context *ctx,
     CU_TRY(ctx, cudaSetDevice(ctx->device));
     uocr_cuda_context_release_runtime_arenas(ctx);
     const LayerDims m = max_dims(ctx);
-    // both regimes must fit: the largest small-batch call and the full capacity
-    uint64_t bytes = layout_arena(m.H, m.E, m.K, m.F, m.S, token_capacity).total;
-    if (!small_batch(token_capacity)) {
-        const uint64_t b2 = layout_arena(m.H, m.E, m.K, m.F, m.S, 256).total;
-        bytes = b2 > bytes ? b2 : bytes;
-    }
+    const uint64_t bytes = layout_arena(m.H, m.E, m.K, m.F, m.S, token_capacity).total;
     CU_TRY(ctx, cudaMalloc(&ctx->arena, bytes));
     ctx->arena_bytes = bytes;
     ctx->token_capacity = token_capacity;
@@ -599,6 +603,40 @@ extern "C" int uocr_cuda_moe_dispatch_plan(uocr_cuda_context *ctx, const uint32_
     return 1;
 }
 
+// settings of the next sliced decode launch (the stall hook applies to one launch only)
+static uocr::SlicedKnobs take_decode_knobs(uocr_cuda_context *ctx) {
+    uocr::SlicedKnobs k = ctx->decode_knobs;
+    if (ctx->test_stall_once) { k.expect_extra = 1; ctx->test_stall_once = false; }
+    return k;
+}
+
+extern "C" int uocr_cuda_moe_debug_dequantize(uocr_cuda_context *ctx, uint32_t layer, uint32_t matrix, uint32_t expert,
+                                              uint32_t path, float *d_out, char *error, size_t error_size) {
+    if (!ctx) return fail(nullptr, error, error_size, "null context");
+    if (layer >= ctx->layers.size()) return fail(ctx, error, error_size, "layer index %u out of range (%zu mapped)", layer, ctx->layers.size());
+    if (!d_out) return fail(ctx, error, error_size, "null output pointer");
+    const DLayer &L = ctx->layers[layer];
+    DMatrix m{};
+    if (matrix < 3) {          // gate, up, down of one routed expert, addressed exactly as the layer kernels address them
+        if (expert >= L.E) return fail(ctx, error, error_size, "expert %u out of range (%u experts)", expert, L.E);
+        const uint32_t rows = matrix == 2 ? L.H : L.F, cols = matrix == 2 ? L.F : L.H;
+        const uint64_t woff = matrix == 0 ? 0 : (matrix == 1 ? L.up_offset_bytes : L.down_offset_bytes);
+        const uint64_t soff = matrix == 0 ? 0 : (matrix == 1 ? L.up_scale_offset : L.down_scale_offset);
+        m.w = L.expert_w + (size_t)expert * L.expert_stride_bytes + woff;
+        m.s = L.expert_s ? L.expert_s + (size_t)expert * L.expert_scale_stride + soff : nullptr;
+        m.rows = rows; m.cols = cols; m.qtype = L.expert_qtype;
+        m.row_bytes = (uint32_t)packed_bytes(L.expert_qtype, 1, cols);
+    } else if (matrix < 6) {
+        m = matrix == 3 ? L.shared_gate : (matrix == 4 ? L.shared_up : L.shared_down);
+    } else {
+        return fail(ctx, error, error_size, "matrix selector %u out of range (0-2 routed gate/up/down, 3-5 shared)", matrix);
+    }
+    if (path == 0) CU_TRY(ctx, uocr::launch_dequant_probe(m, d_out, ctx->stream, &ctx->launches));
+    else if (path == 1) CU_TRY(ctx, uocr::launch_producer_probe(m, d_out, ctx->stream, &ctx->launches));
+    else return fail(ctx, error, error_size, "path selector %u out of range (0 matrix-vector kernels, 1 tensor-core producer)", path);
+    return 1;
+}
+
 static unsigned long long *barrier_counter(uocr_cuda_context *ctx) {
     return reinterpret_cast<unsigned long long *>(reinterpret_cast<uint8_t *>(ctx->status) + 64);
 }
@@ -630,7 +668,7 @@ static int layer_forward(uocr_cuda_context *ctx, uint32_t layer, const __half *d
     if (n == 1 && ctx->fused_decode && ctx->sliced_decode && uocr::decode_sliced_supported(ctx->layers.data(), layer, 1)) {
         CU_TRY(ctx, uocr::launch_decode_sliced(ctx->layers.data(), ctx->d_layers, layer, 1, d_hidden, d_residual, nullptr, 0,
                                                d_injected, d_out, nullptr, decode_accumulators(ctx), &ctx->acc_base, ctx->status,
-                                               logits, probs, s.top_ids, s.top_weights, nullptr, ctx->stream,
+                                               logits, probs, s.top_ids, s.top_weights, nullptr, take_decode_knobs(ctx), ctx->stream,
                                                &ctx->launches));
     } else if (n == 1 && ctx->fused_decode && uocr::decode_supported(ctx->layers.data(), layer, 1)) {
         CU_TRY(ctx, uocr::launch_decode_stack(ctx->layers.data(), ctx->d_layers, layer, 1, d_hidden, d_residual, 0,
@@ -693,7 +731,7 @@ static int stack_forward(uocr_cuda_context *ctx, uint32_t first, uint32_t count,
     if (stack_uses_sliced_decode(ctx, first, count, n)) {
         CU_TRY(ctx, uocr::launch_decode_sliced(ctx->layers.data(), ctx->d_layers, first, count, d_hidden, d_hidden, h_inline, 1,
                                                nullptr, d_out, host_status, decode_accumulators(ctx), &ctx->acc_base, ctx->status, nullptr,
-                                               nullptr, s.top_ids, s.top_weights, ctx->decode_trace, ctx->stream,
+                                               nullptr, s.top_ids, s.top_weights, ctx->decode_trace, take_decode_knobs(ctx), ctx->stream,
                                                &ctx->launches));
         return 1;
     }
@@ -817,6 +855,7 @@ extern "C" int uocr_cuda_moe_ep_experts(uocr_cuda_context *ctx, uint32_t layer, 
     if (layer >= ctx->layers.size()) return fail(ctx, error, error_size, "layer index %u out of range", layer);
     const DLayer &L = ctx->layers[layer];
     const uint32_t n_seg = n_local_experts * n_sources;
+    if (!uocr::gemm_path_supported(L)) return fail(ctx, error, error_size, "layer shape not supported by the tensor-core path");
     if (!h_segment_counts || !d_rows_in || !d_rows_out) return fail(ctx, error, error_size, "null expert-parallel argument");
     if (n_local_experts == 0 || n_sources == 0 || first_expert + n_local_experts > L.E || n_seg > 256)
         return fail(ctx, error, error_size, "invalid expert range or segment count");
@@ -851,6 +890,7 @@ extern "C" int uocr_cuda_moe_ep_shared(uocr_cuda_context *ctx, uint32_t layer, c
     if (!check_call(ctx, layer, n, error, error_size)) return 0;
     if (!d_hidden) return fail(ctx, error, error_size, "null activation pointer");
     const DLayer &L = ctx->layers[layer];
+    if (!uocr::gemm_path_supported(L)) return fail(ctx, error, error_size, "layer shape not supported by the tensor-core path");
     ArenaLayout a;
     Scratch s = carve(ctx, L, ctx->token_capacity, &a);
     const uocr::GemmScratch g = gemm_scratch(ctx, s, a);

@@ -200,6 +200,16 @@ class PeerExpertParallelLayer:
         self.ctx.ep_peer_combine(self.layer, n, out, residual=residual)
         return plan
 
-    def close(self) -> None:
-        self.ctx.ep_peer_destroy()
+    def close(self, *, group_barrier: bool = True) -> None:
+        """Unmap the peers' buffers and free this rank's.  A peer's scatter or combine kernel may still be reading or
+        writing this rank's buffers, so first this rank's own work is awaited, then every rank's (group barrier on
+        the compute stream, then a host wait), and only then is anything freed.  Every rank of the group must call
+        this together; group_barrier=False is for a rank that knows that no forward call has run yet."""
+        try:
+            self.ctx.synchronize()
+        finally:
+            if group_barrier:
+                self._barrier()
+            self.torch.cuda.synchronize()
+            self.ctx.ep_peer_destroy()
 

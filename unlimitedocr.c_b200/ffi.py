@@ -50,7 +50,7 @@ EXPORTS = (
     "uocr_cuda_context_moe_scratch_bytes", "uocr_cuda_context_map_moe_layer", "uocr_cuda_context_unmap_model",
     "uocr_cuda_context_moe_layer_count", "uocr_cuda_context_allocate_runtime_arenas",
     "uocr_cuda_context_release_runtime_arenas", "uocr_cuda_moe_scratch_size", "uocr_cuda_moe_router",
-    "uocr_cuda_moe_dispatch_plan", "uocr_cuda_moe_dispatch_plan_noalloc", "uocr_cuda_moe_layer_forward", "uocr_cuda_moe_stack_forward",
+    "uocr_cuda_moe_dispatch_plan", "uocr_cuda_moe_dispatch_plan_noalloc", "uocr_cuda_moe_debug_dequantize", "uocr_cuda_moe_layer_forward", "uocr_cuda_moe_stack_forward",
     "uocr_cuda_moe_layer_forward_host", "uocr_cuda_moe_stack_forward_host",
     "uocr_cuda_moe_ep_dispatch", "uocr_cuda_moe_ep_experts", "uocr_cuda_moe_ep_shared", "uocr_cuda_moe_ep_combine",
     "uocr_cuda_moe_ep_peer_create", "uocr_cuda_moe_ep_peer_open", "uocr_cuda_moe_ep_peer_destroy",
@@ -101,6 +101,7 @@ def load_library() -> C.CDLL:
         "uocr_cuda_moe_router": (C.c_int, [vp, u32, vp, vp, u32, vp, vp, vp, vp] + err),
         "uocr_cuda_moe_dispatch_plan": (C.c_int, [vp, vp, u32, u32, u32, vp, vp, vp] + err),
         "uocr_cuda_moe_dispatch_plan_noalloc": (C.c_int, [vp, u32, u32, u32, vp, vp, vp, vp] + err),
+        "uocr_cuda_moe_debug_dequantize": (C.c_int, [vp, u32, u32, u32, u32, vp] + err),
         "uocr_cuda_moe_layer_forward": (C.c_int, [vp, u32, vp, vp, vp, u32, vp, C.POINTER(CDebugOutputs)] + err),
         "uocr_cuda_moe_stack_forward": (C.c_int, [vp, u32, u32, vp, u32, vp] + err),
         "uocr_cuda_moe_layer_forward_host": (C.c_int, [vp, u32, vp, vp, u32, vp, vp, vp] + err),
@@ -145,15 +146,19 @@ def _dev_ptr(t: Any) -> int | None:
 def make_layer_desc(L: Any) -> tuple[CLayerDesc, list]:
     """Descriptor over host arrays.  L exposes H, E, K, F, S, scaling, router (uint16 [E,H]),
     logit_bias (f32 [E] or None), expert_qtype, expert_qweight (uint8), expert_qscale (uint16 or None),
-    shared_gate/up/down with qtype, rows, cols, qweight, qscale.  Returns the struct and the arrays
+    shared_gate/up/down with qtype, rows, cols, qweight, qscale; L.meta["strides"] may give the six slab strides
+    and offsets of a slab that is not densely packed.  Returns the struct and the arrays
     it points into (keep them alive until the map call returns)."""
     keep = [L.router, L.logit_bias, L.expert_qweight, L.expert_qscale]
     mats = []
     for m in (L.shared_gate, L.shared_up, L.shared_down):
         keep += [m.qweight, m.qscale]
         mats.append(CMatrix(m.qtype, m.rows, m.cols, _np_ptr(m.qweight), _np_ptr(m.qscale)))
+    st = (getattr(L, "meta", None) or {}).get("strides", {})      # absent: densely packed (zeros)
     d = CLayerDesc(L.H, L.E, L.K, L.F, L.S, L.scaling, _np_ptr(L.router), _np_ptr(L.logit_bias), L.expert_qtype,
-                   _np_ptr(L.expert_qweight), _np_ptr(L.expert_qscale), 0, 0, 0, 0, 0, 0, *mats)
+                   _np_ptr(L.expert_qweight), _np_ptr(L.expert_qscale), st.get("expert_stride_bytes", 0),
+                   st.get("up_offset_bytes", 0), st.get("down_offset_bytes", 0), st.get("expert_scale_stride_values", 0),
+                   st.get("up_scale_offset_values", 0), st.get("down_scale_offset_values", 0), *mats)
     return d, keep
 
 
@@ -273,6 +278,11 @@ class Context:
         self._check(self._lib.uocr_cuda_moe_dispatch_plan(self._h, _dev_ptr(top_ids), n_tokens, top_k, n_experts,
                                                           _dev_ptr(expert_offsets), _dev_ptr(pair_rows),
                                                           _dev_ptr(inverse), self._err, _ERR))
+
+    def debug_dequantize(self, layer: int, matrix: int, expert: int, path: int, out) -> None:
+        """Weights of one projection as the kernels see them (f32 [rows, cols] device tensor); see the header."""
+        self._check(self._lib.uocr_cuda_moe_debug_dequantize(self._h, layer, matrix, expert, path, _dev_ptr(out),
+                                                             self._err, _ERR))
 
     def layer_forward(self, layer: int, hidden, n_tokens: int, out, *, residual=None, injected_logits=None,
                       logits=None, probs=None, top_ids=None, top_weights=None) -> None:
