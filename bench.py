@@ -1,16 +1,22 @@
 #!/usr/bin/env python3
 """Benchmark of the MoE-layer hot path.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload decode|prefill|ep]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--workload decode|prefill|ep|batched] [--extras all|none]
 
 Prints ONE JSON line on rank 0.  Workloads (seeded synthetic inputs of the benchmark plan's shapes):
-  decode   (default on 1 GPU)  one token through 11 stacked MoE layers (hidden 1280, 64 experts top-6 + shared
-           1792, FFN 896, Q4_0 group-64 weights, seed 1); metric = microseconds per token; a step is one pass
-           of the token through the 11 layers.  On N > 1 GPUs with --workload decode: N independent replicas.
-  prefill  one MoE layer on 4096 tokens, Q4_0, Zipf(1.1)-skewed routing, seed 3; metric = tokens per second.
-  ep       (default on N > 1 GPUs)  one MoE layer on 8 x 2048 = 16384 tokens, Q4_0, Zipf(1.1) routing, seed 4, the 64
-           experts sharded over the N GPUs with all-to-all dispatch/combine; metric = tokens per second of the
-           whole job (fixed total work: strong scaling).  Rank 0 also times the same layer alone (G = 1).
+  decode   (default, the headline)  one token through 11 stacked MoE layers (hidden 1280, 64 experts top-6 + shared
+           1792, FFN 896, Q4_0 group-64 weights, seed 1); metric = microseconds per token; a step is one pass of
+           the token through the 11 layers.  On N > 1 GPUs: N independent replicas (the path does not shard for one
+           token), value = step time / N.
+  prefill  one MoE layer on 4096 tokens, Q4_0 (or --qtype f16), Zipf(1.1)-skewed routing, seed 3; tokens per second.
+  batched  one MoE layer on 8 / 32 / 64 tokens, Q8_0, per-expert logit bias N(0,1), seed 2; microseconds per step and
+           the fraction of the HBM roofline for the bytes of the experts the step really selects.
+  ep       one MoE layer on 8 x 2048 = 16384 tokens, Q4_0, Zipf(1.1) and uniform routing, seed 4, the 64 experts
+           sharded over the N GPUs with the exchange over peer memory (or NCCL all-to-all); tokens per second of the
+           whole job (fixed total work: strong scaling).  Every rank checks its shard against the single-GPU layer.
+With --extras all (default) the headline line also carries short timed passes of the other workloads under the keys
+"prefill", "batched_decode" (one GPU only) and "ep" (every N, with an explicit scaling_efficiency).
 
   value  device time per step (CUDA events on the launching stream), inputs resident in HBM;
   e2e    wall time of the host-buffer C-ABI call (host->device copy, 11 layers, device->host copy);
@@ -23,8 +29,10 @@ With --impl reference the reference's CPU path alone is timed on the same worklo
 from __future__ import annotations
 
 import argparse
+import hashlib
 import json
 import os
+import re
 import statistics
 import subprocess
 import sys
@@ -42,6 +50,10 @@ N_LAYERS = 11
 SEED_DECODE = 1
 NOMINAL_HBM_GBS = 8000.0
 FALLBACK_HBM_GBS = 6650.0
+NOMINAL_BF16_TFLOPS = 2250.0
+FALLBACK_BF16_TFLOPS = 1590.0
+FLOPS_PER_TOKEN = 2 * FULL["E"] * FULL["H"] + FULL["K"] * 3 * 2 * FULL["F"] * FULL["H"] + 3 * 2 * FULL["S"] * FULL["H"]
+L2_NOTE = "flushed between timed iterations (256 MiB written, then 256 MiB read)"
 
 
 def layer_bytes(qtype_name: str, n_tokens: int = 1, distinct_experts: int = 6) -> int:
@@ -54,14 +66,38 @@ def layer_bytes(qtype_name: str, n_tokens: int = 1, distinct_experts: int = 6) -
     return E * H * 2 + distinct_experts * expert + shared + n_tokens * H * 2 * 3
 
 
-def measured_peaks() -> tuple[float, str]:
+def _peak(key: str, fallback: float) -> tuple[float, str]:
     p = ROOT / "MEASURED_PEAKS.json"
     if p.exists():
         try:
-            return float(json.loads(p.read_text())["hbm_gbs"]), "measured"
+            return float(json.loads(p.read_text())[key]), "measured"
         except Exception:
             pass
-    return FALLBACK_HBM_GBS, "fallback"
+    return fallback, "fallback"
+
+
+def measured_peaks() -> tuple[float, str]:
+    return _peak("hbm_gbs", FALLBACK_HBM_GBS)
+
+
+def measured_tensor_peak() -> tuple[float, str]:
+    return _peak("bf16_tflops", FALLBACK_BF16_TFLOPS)
+
+
+def captured_traffic(summary: str, kernel_source: str) -> tuple[float | None, str]:
+    """DRAM bytes per launch from the ncu summary under profiles/, valid only for the kernel source it was taken on:
+    the summary carries a line `dram_bytes_per_launch: <bytes> source_sha16: <first 16 hex of the sha256 of the .cu file>`."""
+    path = ROOT / "profiles" / summary
+    src = ROOT / "unlimitedocr.c_b200" / "csrc" / kernel_source
+    if not path.exists() or not src.exists():
+        return None, f"no ncu capture on record (profiles/{summary})"
+    m = re.search(r"^dram_bytes_per_launch:\s*(\d+)\s+source_sha16:\s*([0-9a-f]{16})", path.read_text(), re.M)
+    if not m:
+        return None, f"profiles/{summary} holds no ncu capture of the kernel as it is now (see the summary for why)"
+    sha = hashlib.sha256(src.read_bytes()).hexdigest()[:16]
+    if m.group(2) != sha:
+        return None, f"the capture in profiles/{summary} is of an earlier version of {kernel_source}"
+    return float(m.group(1)), f"dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture (profiles/{summary})"
 
 
 class ClockSampler:
@@ -86,7 +122,7 @@ class ClockSampler:
         except OSError:
             return 0
 
-    def hold(self, step, minimum: int = 2, limit_s: float = 4.0) -> None:
+    def hold(self, step, minimum: int = 6, limit_s: float = 4.0) -> None:
         """Keep the same load running (untimed) until nvidia-smi has delivered `minimum` samples: a timed region of a
         few milliseconds is over before its first sample."""
         if self.proc is None:
@@ -132,7 +168,16 @@ def synth_stack(n_layers: int, qtype_name: str, seed: int):
     return layers, hidden
 
 
-def run_reference_arm(args, rank: int) -> None:
+def workload_config(world: int = 1) -> dict:
+    return {"workload": "decode: 1 token x 11 stacked MoE layers, hidden 1280, 64 experts top-6 + shared 1792, "
+                        "FFN 896, Q4_0 group-64 experts and shared MLP, seed 1",
+            "layers": N_LAYERS, "tokens_per_step": 1, "qtype": "q4_0",
+            "parallelism": "replicas only" if world > 1 else "1 gpu", "l2": L2_NOTE}
+
+
+# ------------------------------------------------------------------------------------------ the CPU arm
+
+def run_reference_arm(args, rank: int, world: int) -> None:
     if rank != 0:
         return
     from oracle import oracle as orc
@@ -145,7 +190,7 @@ def run_reference_arm(args, rank: int) -> None:
         "impl": "reference", "metric": "moe_decode_us_per_token", "value": us, "unit": "us/token", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": us * threads / 1000.0, "higher_is_better": False,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": workload_config(),
+        "config": workload_config(max(world, args.gpus)),
         "cpu_baseline": {"value": us, "unit": "us/token", "cores": threads, "kind": kind, "sample": sample},
         "e2e": {"value": us, "unit": "us/token", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0, "wall_s": time.perf_counter() - t0,
@@ -184,28 +229,6 @@ def _cpu_arm(sampled_layers, hidden, args, threads):
     sample = (f"{threads} tokens in parallel (one per host thread) through {len(sampled_layers)} of the {N_LAYERS} "
               f"layers, {done} passes, scaled x{N_LAYERS}/{len(sampled_layers)}; f32 dequantised weights")
     return us, kind, sample
-
-
-def workload_config() -> dict:
-    return {"workload": "decode: 1 token x 11 stacked MoE layers, hidden 1280, 64 experts top-6 + shared 1792, "
-                        "FFN 896, Q4_0 group-64 experts and shared MLP, seed 1",
-            "layers": N_LAYERS, "tokens_per_step": 1, "qtype": "q4_0",
-            "l2": "flushed between timed iterations (256 MiB written, then 256 MiB read)"}
-
-
-NOMINAL_BF16_TFLOPS = 2250.0
-FALLBACK_BF16_TFLOPS = 1590.0
-FLOPS_PER_TOKEN = 2 * FULL["E"] * FULL["H"] + FULL["K"] * 3 * 2 * FULL["F"] * FULL["H"] + 3 * 2 * FULL["S"] * FULL["H"]
-
-
-def measured_tensor_peak() -> tuple[float, str]:
-    p = ROOT / "MEASURED_PEAKS.json"
-    if p.exists():
-        try:
-            return float(json.loads(p.read_text())["bf16_tflops"]), "measured"
-        except Exception:
-            pass
-    return FALLBACK_BF16_TFLOPS, "fallback"
 
 
 def token_workload(kind: str) -> dict:
@@ -277,6 +300,8 @@ def run_reference_tokens(args, rank: int, kind: str) -> None:
     print(json.dumps(line), flush=True)
 
 
+# ------------------------------------------------------------------------------------------ GPU helpers
+
 def make_flush(torch):
     flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
     reader = torch.empty(256 << 20, dtype=torch.uint8, device="cuda").view(torch.int32)
@@ -289,191 +314,248 @@ def make_flush(torch):
     return flush_l2
 
 
-def run_tokens(args, kind: str, rank: int, local_rank: int, world: int) -> None:
-    """prefill (one GPU) and expert-parallel prefill (N GPUs): one MoE layer on many tokens."""
-    import torch
-    import torch.distributed as dist
+def timed_steps(torch, dist, world, stream, flush_l2, fn, steps: int, warmup: int) -> list[float]:
+    """W untimed steps, then K steps each between two CUDA events on the launching stream (ms per step)."""
+    for i in range(warmup):
+        flush_l2(i)
+        fn()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    starts = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+    ends = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+    for i in range(steps):
+        flush_l2(i)
+        if world > 1:
+            dist.barrier()                     # every rank starts the step together; the barrier is not timed
+        starts[i].record(stream)
+        fn()
+        ends[i].record(stream)
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    return [s.elapsed_time(e) for s, e in zip(starts, ends)]
 
-    import __graft_entry__ as entry
-    pkg = entry.load_package()
-    w = token_workload(kind)
+
+def tensor_roofline(n_tokens: int, ms: float, world: int = 1) -> dict:
+    peak, peak_kind = measured_tensor_peak()
+    flops = n_tokens * FLOPS_PER_TOKEN
+    achieved = flops / (ms * 1e-3) / 1e12 / world        # per GPU
+    return {"bound": "tensor", "kernel": "grouped_gemm_kernel (whole layer time used)", "achieved": achieved, "peak": peak,
+            "peak_kind": f"of {peak_kind}", "unit": "TFLOP/s", "frac": achieved / peak,
+            "frac_of_nominal_2250": achieved / NOMINAL_BF16_TFLOPS, "algorithmic_flops_per_step": flops}
+
+
+# ------------------------------------------------------------------------------------------ prefill (one GPU)
+
+def measure_prefill(pkg, torch, flush_l2, qtype_name: str, steps: int, warmup: int, with_e2e: bool = True) -> dict:
+    """One MoE layer on 4096 tokens (benchmark plan config 4): device time per call and the call with pinned
+    host-to-device / device-to-host copies of the activations."""
+    w = token_workload("prefill")
+    n = w["n_tokens"]
+    L, hidden, resid = synth_token_layer(w["seed"], n, qtype_name)
+    stream = torch.cuda.current_stream()
+    with pkg.Context() as ctx:
+        ctx.map_layer(L)
+        ctx.allocate_runtime_arenas(n)
+        ctx.set_stream(stream.cuda_stream)
+        h_host = torch.from_numpy(hidden.copy()).pin_memory()
+        r_host = torch.from_numpy(resid.copy()).pin_memory()
+        d_h, d_r = h_host.cuda().view(torch.float16), r_host.cuda().view(torch.float16)
+        d_out = torch.zeros_like(d_h)
+        host_out = torch.empty((n, FULL["H"]), dtype=torch.float16).pin_memory()
+        launches0 = ctx.kernel_launches
+        times = timed_steps(torch, None, 1, stream, flush_l2, lambda: ctx.layer_forward(0, d_h, n, d_out, residual=d_r), steps, warmup)
+        launches = (ctx.kernel_launches - launches0) // (steps + warmup)
+        ms = sum(times) / len(times)
+        out = {"workload": w["workload"].replace("Q4_0", qtype_name.upper()), "qtype": qtype_name, "tokens_per_step": n,
+               "tokens_per_s": n / (ms * 1e-3), "ms_per_step": ms, "step_ms_min_max": [min(times), max(times)],
+               "gpu_launches_per_step": int(launches), "roofline": tensor_roofline(n, ms)}
+        if with_e2e:
+            wall = []
+            for i in range(3 + steps):
+                flush_l2(i)
+                torch.cuda.synchronize()
+                t0 = time.perf_counter()
+                d_h.view(torch.uint16).copy_(h_host, non_blocking=True)
+                d_r.view(torch.uint16).copy_(r_host, non_blocking=True)
+                ctx.layer_forward(0, d_h, n, d_out, residual=d_r)
+                host_out.copy_(d_out, non_blocking=True)
+                torch.cuda.synchronize()
+                wall.append(time.perf_counter() - t0)
+            e2e_ms = sum(wall[3:]) / steps * 1e3
+            out["e2e"] = {"value": n / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": 2 * n * FULL["H"] * 2,
+                          "d2h_bytes_per_step": n * FULL["H"] * 2}
+        ctx.synchronize()
+    return out
+
+
+# ------------------------------------------------------------------------------------------ batched decode (one GPU)
+
+def measure_batched_decode(pkg, torch, flush_l2, steps: int, warmup: int) -> dict:
+    """One Q8_0 layer on 8 / 32 / 64 tokens with a per-expert logit bias N(0,1) (benchmark plan config 3).  The step is
+    bound by reading the weights of the experts it selects: bytes = router + U distinct experts + shared MLP +
+    activations, against the measured copy bandwidth."""
+    from oracle import quant
+    rng = np.random.default_rng(2)
+    bias = rng.standard_normal(FULL["E"]).astype(np.float32)
+    L = quant.synth_layer(rng, expert_qtype=quant.QTYPE_Q8_0, logit_bias=bias, **FULL)
+    peak, peak_kind = measured_peaks()
+    stream = torch.cuda.current_stream()
+    out = {"workload": "batched decode: one MoE layer, Q8_0, per-expert logit bias N(0,1), seed 2", "qtype": "q8_0",
+           "peak_gbs": peak, "peak_kind": f"of {peak_kind}", "l2": L2_NOTE, "tokens": {}}
+    with pkg.Context() as ctx:
+        ctx.map_layer(L)
+        ctx.allocate_runtime_arenas(64)
+        ctx.set_stream(stream.cuda_stream)
+        for n in (8, 32, 64):
+            hidden = quant.synth_activations(rng, n, FULL["H"])
+            d_h = torch.from_numpy(hidden).cuda().view(torch.float16)
+            d_out = torch.zeros_like(d_h)
+            d_ids = torch.zeros((n, FULL["K"]), dtype=torch.int32, device="cuda")
+            ctx.layer_forward(0, d_h, n, d_out, residual=d_h, top_ids=d_ids)
+            ctx.synchronize()
+            distinct = int(np.unique(d_ids.cpu().numpy()).size)
+            launches0 = ctx.kernel_launches
+            times = timed_steps(torch, None, 1, stream, flush_l2, lambda: ctx.layer_forward(0, d_h, n, d_out, residual=d_h), steps, warmup)
+            launches = (ctx.kernel_launches - launches0) // (steps + warmup)
+            ms = sum(times) / len(times)
+            nbytes = layer_bytes("q8_0", n, distinct)
+            achieved = nbytes / (ms * 1e-3) / 1e9
+            out["tokens"][str(n)] = {"us_per_step": ms * 1e3, "us_per_token": ms * 1e3 / n, "distinct_experts": distinct,
+                                     "algorithmic_bytes_per_step": nbytes, "achieved_gbs": achieved, "frac": achieved / peak,
+                                     "frac_of_nominal_8TBs": achieved / NOMINAL_HBM_GBS, "gpu_launches_per_step": int(launches),
+                                     "served_by": ctx.regime_name(0, n)}
+    return out
+
+
+# ------------------------------------------------------------------------------------------ expert parallelism
+
+def measure_ep(pkg, torch, dist, rank: int, world: int, flush_l2, steps: int, warmup: int, exchange_kind: str,
+               routings=("zipf", "uniform"), with_e2e: bool = True) -> dict:
+    """One Q4_0 MoE layer on 16384 tokens (benchmark plan config 5), its experts sharded over the ranks; for each
+    routing: tokens/s of the whole job, the same job on one GPU (rank 0), every rank's shard checked bit for bit
+    against the single-GPU output, and the rows the busiest rank received."""
+    import dataclasses
+    w = token_workload("ep")
     n_total = w["n_tokens"]
     if n_total % world:
         raise SystemExit(f"{n_total} tokens do not divide over {world} ranks")
-    L, hidden, resid = synth_token_layer(w["seed"], n_total, routing=args.routing)
-    n_local = n_total // world
-    lo = rank * n_local
+    n_local, lo = n_total // world, rank * (n_total // world)
+    H, E, K = FULL["H"], FULL["E"], FULL["K"]
+    L, hidden, resid = synth_token_layer(w["seed"], n_total, routing="zipf")
     stream = torch.cuda.current_stream()
     ctx = pkg.Context()
-    ctx.map_layer(L)
-    # a rank can receive every pair of the job (worst case), and rank 0 also runs the whole job alone
-    ctx.allocate_runtime_arenas(n_total)
+    layer_of = {"zipf": ctx.map_layer(L), "uniform": ctx.map_layer(dataclasses.replace(L, logit_bias=None))}
+    ctx.allocate_runtime_arenas(n_total)     # a rank can receive every pair of the job, and every rank also runs the whole job alone
     ctx.set_stream(stream.cuda_stream)
-    flush_l2 = make_flush(torch)
+    d_all = torch.from_numpy(hidden).cuda().view(torch.float16)
+    r_all = torch.from_numpy(resid).cuda().view(torch.float16)
     h_local = torch.from_numpy(hidden[lo:lo + n_local].copy()).pin_memory()
     r_local = torch.from_numpy(resid[lo:lo + n_local].copy()).pin_memory()
-    d_h = h_local.cuda().view(torch.float16)
-    d_r = r_local.cuda().view(torch.float16)
+    d_h, d_r = d_all[lo:lo + n_local].clone(), r_all[lo:lo + n_local].clone()
     d_out = torch.zeros_like(d_h)
-    host_out = torch.empty((n_local, FULL["H"]), dtype=torch.float16).pin_memory()
-    # the exchange: fused into the library's kernels over peer memory (default), or NCCL all-to-all between its phases
-    exchange, layer = "nccl all_to_all_single", None
-    if kind == "ep" and world > 1 and args.exchange == "peer":
-        why = ""
-        try:
-            layer = pkg.ep.PeerExpertParallelLayer(ctx, 0, FULL["E"], FULL["K"], FULL["H"], row_capacity=n_total * FULL["K"],
-                                                   rank=rank, world=world, dist_module=dist)
-            exchange = "peer memory (CUDA IPC over NVLink), fused into gather and combine"
-        except Exception as e:      # e.g. no peer access between the devices: every rank must then take the other path
-            why = str(e)[:200]
-        ok = torch.tensor([1 if layer is not None else 0], device="cuda")
-        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
-        if int(ok.item()) == 0:
-            if layer is not None:
-                layer.close(group_barrier=False)      # nothing has run on the exchange buffers yet
-            layer = None
-            exchange = f"nccl all_to_all_single (peer-memory set-up failed on a rank: {why})"
-    if layer is None:
-        layer = pkg.ep.ExpertParallelLayer(ctx, 0, FULL["E"], FULL["K"], FULL["H"], rank=rank, world=world,
-                                           dist_module=dist if world > 1 else None)
-        layer.reserve(n_local, n_total * FULL["K"])
-
-    def step():
-        if kind == "prefill":
-            ctx.layer_forward(0, d_h, n_local, d_out, residual=d_r)
-            return None
-        return layer.forward(d_h, d_out, residual=d_r)
-
-    def timed(fn, steps, warmup):
-        for i in range(warmup):
-            flush_l2(i)
-            fn()
-        torch.cuda.synchronize()
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-        starts = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
-        ends = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
-        for i in range(steps):
-            flush_l2(i)
-            if world > 1:
-                dist.barrier()                     # every rank starts the step together; the barrier is not timed
-            starts[i].record(stream)
-            fn()
-            ends[i].record(stream)
-        torch.cuda.synchronize()
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-        return [s.elapsed_time(e) for s, e in zip(starts, ends)]
-
-    warm = max(args.warmup, 3)
-    sampler = ClockSampler(local_rank) if rank == 0 else None
-    launches0 = ctx.kernel_launches
-    times = timed(step, args.steps, warm)
-    launches = (ctx.kernel_launches - launches0) * args.steps // (args.steps + warm)
-    if world == 1:
-        if sampler:
-            sampler.hold(step)
-    else:                      # the same number of extra steps on every rank (the step holds collectives)
-        for _ in range(300):
-            step()
-        torch.cuda.synchronize()
-    plan = layer.last_plan
-
-    def e2e_step():
-        d_h.view(torch.uint16).copy_(h_local, non_blocking=True)
-        d_r.view(torch.uint16).copy_(r_local, non_blocking=True)
-        step()
-        host_out.copy_(d_out, non_blocking=True)
-
-    e2e_wall = []
-    for i in range(3 + args.steps):
-        flush_l2(i)
-        torch.cuda.synchronize()
-        if world > 1:
-            dist.barrier()
-        t0 = time.perf_counter()
-        e2e_step()
-        torch.cuda.synchronize()
-        e2e_wall.append(time.perf_counter() - t0)
-    e2e_ms = sum(e2e_wall[3:]) / args.steps * 1e3
-    clocks = sampler.stop() if sampler else None
-
-    ms = sum(times) / len(times)
-    t = torch.tensor([ms, e2e_ms, float(plan.rows_received) if plan else float(n_local * FULL["K"])], dtype=torch.float64, device="cuda")
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms, e2e_ms, max_rows = float(t[0]), float(t[1]), float(t[2])
-
-    g1 = None
-    if kind == "ep" and world > 1 and rank == 0:
-        # the same job on one GPU, for the scaling reference (other ranks idle)
-        d_all = torch.from_numpy(hidden).cuda().view(torch.float16)
-        r_all = torch.from_numpy(resid).cuda().view(torch.float16)
-        o_all = torch.zeros_like(d_all)
-        solo = pkg.ep.ExpertParallelLayer(ctx, 0, FULL["E"], FULL["K"], FULL["H"])
-        solo.reserve(n_total, n_total * FULL["K"])
+    o_all = torch.zeros_like(d_all)
+    host_out = torch.empty((n_local, H), dtype=torch.float16).pin_memory()
+    result = {"workload": w["workload"].replace("Zipf(1.1)-skewed routing", "Zipf(1.1)-skewed and uniform routing"),
+              "tokens_per_step": n_total, "qtype": "q4_0", "n_gpus": world, "parallelism": f"ep{world}", "l2": L2_NOTE}
+    exchange = "none (one GPU)"
+    for routing in routings:
+        li = layer_of[routing]
+        layer = None
+        if world > 1 and exchange_kind == "peer":
+            why = ""
+            try:
+                layer = pkg.ep.PeerExpertParallelLayer(ctx, li, E, K, H, row_capacity=n_total * K, rank=rank, world=world,
+                                                       dist_module=dist)
+                exchange = "peer memory (CUDA IPC over NVLink), fused into gather and combine"
+            except Exception as e:      # e.g. no peer access between the devices: every rank must then take the other path
+                why = str(e)[:200]
+            ok = torch.tensor([1 if layer is not None else 0], device="cuda")
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+            if int(ok.item()) == 0:
+                if layer is not None:
+                    layer.close(group_barrier=False)      # nothing has run on the exchange buffers yet
+                layer = None
+                exchange = f"nccl all_to_all_single (peer-memory set-up failed on a rank: {why})"
+        if layer is None:
+            if world > 1 and exchange_kind != "peer":
+                exchange = "nccl all_to_all_single"
+            layer = pkg.ep.ExpertParallelLayer(ctx, li, E, K, H, rank=rank, world=world, dist_module=dist if world > 1 else None)
+            layer.reserve(n_local, n_total * K)
+        step = lambda: layer.forward(d_h, d_out, residual=d_r)
+        launches0 = ctx.kernel_launches
+        times = timed_steps(torch, dist, world, stream, flush_l2, step, steps, warmup)
+        launches = (ctx.kernel_launches - launches0) // (steps + warmup)
+        plan = layer.last_plan
+        e2e_ms = 0.0
+        if with_e2e:
+            wall = []
+            for i in range(2 + steps):
+                flush_l2(i)
+                torch.cuda.synchronize()
+                if world > 1:
+                    dist.barrier()
+                t0 = time.perf_counter()
+                d_h.view(torch.uint16).copy_(h_local, non_blocking=True)
+                d_r.view(torch.uint16).copy_(r_local, non_blocking=True)
+                step()
+                host_out.copy_(d_out, non_blocking=True)
+                torch.cuda.synchronize()
+                wall.append(time.perf_counter() - t0)
+            e2e_ms = sum(wall[2:]) / steps * 1e3
+        ms = sum(times) / len(times)
+        # the same job on one GPU: every rank runs it once (the check), rank 0 also times it (the scaling reference)
+        solo = pkg.ep.ExpertParallelLayer(ctx, li, E, K, H)
+        solo.reserve(n_total, n_total * K)
         ts = []
-        for i in range(3 + 5):
+        for i in range(1 + (3 + 5 if rank == 0 else 0)):
             flush_l2(i)
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             a.record(stream); solo.forward(d_all, o_all, residual=r_all); b.record(stream)
             torch.cuda.synchronize()
             ts.append(a.elapsed_time(b))
-        g1 = n_total / (sum(ts[3:]) / 5 * 1e-3)
-        # and the sharded result equals the single-GPU result on this rank's tokens
-        assert torch.equal(o_all[lo:lo + n_local], d_out), "expert-parallel output differs from the single-GPU output"
-    if world > 1:
-        dist.barrier()
-
-    if rank == 0:
-        peak, peak_kind = measured_tensor_peak()
-        flops = n_total * FLOPS_PER_TOKEN
-        achieved = flops / (ms * 1e-3) / 1e12 / world        # per GPU
+        if world > 1:
+            dist.barrier()
+        step()                                   # the sharded result once more, after the single-GPU run
+        torch.cuda.synchronize()
+        mismatch = 0 if torch.equal(o_all[lo:lo + n_local], d_out) else 1
+        t = torch.tensor([ms, e2e_ms, float(plan.rows_received) if plan else float(n_local * K), float(mismatch)],
+                         dtype=torch.float64, device="cuda")
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, e2e_ms, max_rows, mismatches = float(t[0]), float(t[1]), float(t[2]), int(t[3])
+        if mismatches:
+            raise SystemExit(f"expert-parallel output differs from the single-GPU output on at least one rank ({routing} routing)")
         tps = n_total / (ms * 1e-3)
-        line = {
-            "metric": w["metric"], "value": tps, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": warm,
-            "ms_per_step": ms, "higher_is_better": True, "scaling": "strong" if kind == "ep" else "weak", "vs_baseline": None,
-            "dtype": "fp16 tensor-core inputs (weights dequantised from Q4_0 on the fly), f32 accumulate", "data": "synthetic",
-            "config": {"workload": w["workload"] if args.routing == "zipf" else w["workload"].replace("Zipf(1.1)-skewed", "uniform"),
-                       "tokens_per_step": n_total, "qtype": "q4_0", "routing": args.routing,
-                       "parallelism": f"ep{world}" if kind == "ep" else "1 gpu",
-                       **({"exchange": exchange} if kind == "ep" and world > 1 else {}),
-                       "l2": "flushed between timed iterations (256 MiB written, then 256 MiB read)"},
-            "e2e": {"value": n_total / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": 2 * n_local * FULL["H"] * 2,
-                    "d2h_bytes_per_step": n_local * FULL["H"] * 2,
-                    "timer": "host wall clock: pinned H2D of hidden and residual, layer, D2H of the output (per rank, max over ranks)"},
-            "gpu_launches": int(launches),
-            "roofline": {"bound": "tensor", "kernel": "grouped_gemm_kernel (whole layer time used)", "achieved": achieved,
-                         "peak": peak, "peak_kind": f"of {peak_kind}", "unit": "TFLOP/s", "frac": achieved / peak,
-                         "frac_of_nominal_2250": achieved / NOMINAL_BF16_TFLOPS, "algorithmic_flops_per_step": flops,
-                         # DRAM bytes of the dominant launch (routed gate/up GEMM) from one ncu capture of the 4096-token workload
-                         "traffic": 159.2e6 if (kind == "prefill" and args.routing == "zipf") else None,
-                         "traffic_source": "dram__bytes_read.sum + dram__bytes_write.sum of the routed gate/up launch "
-                                           "(profiles/grouped_gemm_kernel__prefill_q4_4096.md)"},
-            "clocks": clocks, "step_ms_min_max": [min(times), max(times)],
-        }
-        if kind == "ep":
-            mean_rows = n_total * FULL["K"] / world
-            line["load"] = {"max_rows_received_per_gpu": max_rows, "mean_rows_per_gpu": mean_rows, "max_over_mean": max_rows / mean_rows}
-            if g1 is not None:
-                line["single_gpu_tokens_per_s_same_job"] = g1
-        if not args.no_cpu_baseline and world == 1:
-            from oracle import oracle as orc
-            cps, ckind, sample = cpu_tokens_per_s(L, hidden, resid, orc.host_threads())
-            line["cpu_baseline"] = {"value": cps, "unit": "tokens/s", "cores": orc.host_threads(), "kind": ckind, "sample": sample}
-        print(json.dumps(line), flush=True)
+        mean_rows = n_total * K / world
+        r = {"tokens_per_s": tps, "ms_per_step": ms, "step_ms_min_max": [min(times), max(times)],
+             "gpu_launches_per_step": int(launches), "roofline": tensor_roofline(n_total, ms, world),
+             "all_ranks_equal_single_gpu_bit_for_bit": True,
+             "load": {"max_rows_received_per_gpu": max_rows, "mean_rows_per_gpu": mean_rows, "max_over_mean": max_rows / mean_rows}}
+        if with_e2e:
+            r["e2e"] = {"value": n_total / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": 2 * n_local * H * 2,
+                        "d2h_bytes_per_step": n_local * H * 2,
+                        "timer": "host wall clock: pinned H2D of hidden and residual, layer, D2H of the output (per rank, max over ranks)"}
+        if rank == 0:
+            g1 = n_total / (sum(ts[-5:]) / 5 * 1e-3)
+            r["single_gpu_tokens_per_s_same_job"] = g1
+            r["scaling_efficiency"] = tps / g1 / world
+        result[routing] = r
+        if isinstance(layer, pkg.ep.PeerExpertParallelLayer):
+            layer.close()                          # every rank together: waits for all ranks' kernels before freeing
+    result["exchange"] = exchange
+    ctx.synchronize()
     ctx.close()
+    return result
 
 
-def run_decode(args, rank: int, local_rank: int, world: int) -> None:
+# ------------------------------------------------------------------------------------------ decode (headline)
+
+def measure_decode(pkg, torch, dist, rank: int, local_rank: int, world: int, flush_l2, args) -> dict | None:
     """One token through the 11-layer stack (N replicas when launched on N GPUs)."""
-    import torch
-    import torch.distributed as dist
-
-    import __graft_entry__ as entry
-    pkg = entry.load_package()
     layers, hidden = synth_stack(N_LAYERS, "q4_0", SEED_DECODE)
     ctx = pkg.Context()
     for L in layers:
@@ -481,37 +563,17 @@ def run_decode(args, rank: int, local_rank: int, world: int) -> None:
     ctx.allocate_runtime_arenas(1)
     stream = torch.cuda.current_stream()
     ctx.set_stream(stream.cuda_stream)
-
     d_hidden = torch.from_numpy(hidden).cuda().view(torch.float16)
     d_out = torch.zeros_like(d_hidden)
-    flush_l2 = make_flush(torch)
+    warm = max(args.warmup, 3)
 
     def step():
         ctx.stack_forward(0, N_LAYERS, d_hidden, 1, d_out)
 
-    for _ in range(max(args.warmup, 3)):
-        flush_l2(1)
-        step()
-    torch.cuda.synchronize()
-    if world > 1:
-        dist.barrier()
-    torch.cuda.synchronize()
-
     sampler = ClockSampler(local_rank) if rank == 0 else None
     launches0 = ctx.kernel_launches
-    starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
-    ends = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
-    for i in range(args.steps):
-        flush_l2(i)
-        starts[i].record(stream)
-        step()
-        ends[i].record(stream)
-    torch.cuda.synchronize()
-    if world > 1:
-        dist.barrier()
-    torch.cuda.synchronize()
-    launches = ctx.kernel_launches - launches0
-    times_ms = [s.elapsed_time(e) for s, e in zip(starts, ends)]
+    times_ms = timed_steps(torch, dist, world, stream, flush_l2, step, args.steps, warm)
+    launches = (ctx.kernel_launches - launches0) * args.steps // (args.steps + warm)
     if sampler:
         sampler.hold(step)
     ms_per_step = sum(times_ms) / len(times_ms)
@@ -534,40 +596,39 @@ def run_decode(args, rank: int, local_rank: int, world: int) -> None:
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms_per_step, e2e_ms = float(t[0]), float(t[1])
-
-    if rank == 0:
-        peak, peak_kind = measured_peaks()
-        step_bytes = N_LAYERS * layer_bytes("q4_0")
-        achieved = step_bytes / (ms_per_step * 1e-3) / 1e9
-        if achieved > 1.25 * peak:
-            raise SystemExit(f"implausible timing: {achieved:.0f} GB/s against a measured peak of {peak:.0f}; "
-                             "the timed stream did not carry the kernels")
-        us_per_token = ms_per_step * 1e3 / world          # N replicas: job-level time per token
-        line = {
-            "metric": "moe_decode_us_per_token", "value": us_per_token, "unit": "us/token", "n_gpus": world,
-            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": False,
-            "scaling": "weak", "vs_baseline": None, "dtype": "f32 accumulate over fp16 activations and Q4_0 weights",
-            "data": "synthetic", "config": {**workload_config(), "parallelism": "replicas only" if world > 1 else "1 gpu"},
-            "e2e": {"value": e2e_ms * 1e3 / world, "unit": "us/token", "h2d_bytes_per_step": FULL["H"] * 2,
-                    "d2h_bytes_per_step": FULL["H"] * 2, "timer": "host wall clock around uocr_cuda_moe_stack_forward_host"},
-            "gpu_launches": int(launches),
-            "roofline": {"bound": "hbm", "kernel": "decode_sliced_kernel (one launch = one step)", "achieved": achieved,
-                         "peak": peak, "peak_kind": f"of {peak_kind}", "unit": "GB/s", "frac": achieved / peak,
-                         "frac_of_nominal_8TBs": achieved / NOMINAL_HBM_GBS, "algorithmic_bytes_per_step": step_bytes,
-                         "traffic": 165.4e6, "traffic_source": "dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture "
-                         "of this kernel on this workload, taken before its latest changes, which read the same bytes "
-                         "(profiles/decode_sliced_kernel__decode_q4_11layers.md)"},
-            "clocks": clocks,
-            "per_layer_us": ms_per_step * 1e3 / N_LAYERS,
-            "step_ms_min_max": [min(times_ms), max(times_ms)],
-        }
-        if not args.no_cpu_baseline:
-            from oracle import oracle as orc
-            threads = orc.host_threads()
-            us, kind, sample = _cpu_arm(layers[: args.cpu_layers], hidden, argparse.Namespace(steps=3, warmup=1), threads)
-            line["cpu_baseline"] = {"value": us, "unit": "us/token", "cores": threads, "kind": kind, "sample": sample}
-        print(json.dumps(line), flush=True)
     ctx.close()
+    if rank != 0:
+        return None
+    peak, peak_kind = measured_peaks()
+    step_bytes = N_LAYERS * layer_bytes("q4_0")
+    achieved = step_bytes / (ms_per_step * 1e-3) / 1e9
+    if achieved > 1.25 * peak:
+        raise SystemExit(f"implausible timing: {achieved:.0f} GB/s against a measured peak of {peak:.0f}; "
+                         "the timed stream did not carry the kernels")
+    traffic, traffic_source = captured_traffic("decode_sliced_kernel__decode_q4_11layers.md", "moe_decode_sliced.cu")
+    us_per_token = ms_per_step * 1e3 / world          # N replicas: job-level time per token
+    line = {
+        "metric": "moe_decode_us_per_token", "value": us_per_token, "unit": "us/token", "n_gpus": world,
+        "steps": args.steps, "warmup": warm, "ms_per_step": ms_per_step, "higher_is_better": False,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32 accumulate over fp16 activations and Q4_0 weights",
+        "data": "synthetic", "config": workload_config(world),
+        "e2e": {"value": e2e_ms * 1e3 / world, "unit": "us/token", "h2d_bytes_per_step": FULL["H"] * 2,
+                "d2h_bytes_per_step": FULL["H"] * 2, "timer": "host wall clock around uocr_cuda_moe_stack_forward_host"},
+        "gpu_launches": int(launches),
+        "roofline": {"bound": "hbm", "kernel": "decode_sliced_kernel (one launch = one step)", "achieved": achieved,
+                     "peak": peak, "peak_kind": f"of {peak_kind}", "unit": "GB/s", "frac": achieved / peak,
+                     "frac_of_nominal_8TBs": achieved / NOMINAL_HBM_GBS, "algorithmic_bytes_per_step": step_bytes,
+                     "traffic": traffic, "traffic_source": traffic_source},
+        "clocks": clocks,
+        "per_layer_us": ms_per_step * 1e3 / N_LAYERS,
+        "step_ms_min_max": [min(times_ms), max(times_ms)],
+    }
+    if not args.no_cpu_baseline:
+        from oracle import oracle as orc
+        threads = orc.host_threads()
+        us, kind, sample = _cpu_arm(layers[: args.cpu_layers], hidden, argparse.Namespace(steps=3, warmup=1), threads)
+        line["cpu_baseline"] = {"value": us, "unit": "us/token", "cores": threads, "kind": kind, "sample": sample}
+    return line
 
 
 def main() -> None:
@@ -576,23 +637,26 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=None)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default=None, choices=["decode", "prefill", "ep"])
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "ep", "batched"])
+    ap.add_argument("--extras", default="all", choices=["all", "none"],
+                    help="decode workload: also time short passes of the other workloads and append them to the line")
+    ap.add_argument("--qtype", default="q4_0", choices=["q4_0", "f16", "q8_0"], help="prefill workload: weight format")
     ap.add_argument("--cpu-layers", type=int, default=2, help="layers of the stack the CPU baseline samples")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--routing", default="zipf", choices=["zipf", "uniform"], help="expert popularity of the prefill / ep workloads")
+    ap.add_argument("--routing", default="both", choices=["both", "zipf", "uniform"], help="ep workload: expert popularity")
     ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"], help="ep workload: how rows travel between the GPUs")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
-    kind = args.workload or ("decode" if max(world, args.gpus) == 1 else "ep")
+    kind = args.workload
     if args.steps is None:
         args.steps = 50 if kind == "decode" else 20
 
     if args.impl == "reference":
-        if kind == "decode":
-            run_reference_arm(args, rank)
+        if kind in ("decode", "batched"):
+            run_reference_arm(args, rank, world)
         else:
             run_reference_tokens(args, rank, kind)
         return
@@ -609,11 +673,81 @@ def main() -> None:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     if not (entry.PKG_DIR / "libuocr_cuda_moe.so").exists():
         entry.build()
+    pkg = entry.load_package()
+    flush_l2 = make_flush(torch)
+    routings = ("zipf", "uniform") if args.routing == "both" else (args.routing,)
+    short = max(5, min(args.steps, 10))
+    line = None
+
     if kind == "decode":
-        run_decode(args, rank, local_rank, world)
+        line = measure_decode(pkg, torch, dist, rank, local_rank, world, flush_l2, args)
+        if args.extras == "all":
+            t0 = time.perf_counter()
+            extras = {}
+            if world == 1:
+                extras["prefill"] = {q: measure_prefill(pkg, torch, flush_l2, q, short, 3) for q in ("q4_0", "f16")}
+                extras["batched_decode"] = measure_batched_decode(pkg, torch, flush_l2, short, 3)
+            extras["ep"] = measure_ep(pkg, torch, dist, rank, world, flush_l2, short, 3, args.exchange, routings)
+            if rank == 0:
+                line.update(extras)
+                line["extras_wall_s"] = time.perf_counter() - t0
+    elif kind == "prefill":
+        if world > 1:
+            raise SystemExit("the prefill workload runs on one GPU (use --workload ep for several)")
+        sampler = ClockSampler(local_rank)
+        r = measure_prefill(pkg, torch, flush_l2, args.qtype, args.steps, max(args.warmup, 3))
+        w = token_workload("prefill")
+        line = {"metric": w["metric"], "value": r["tokens_per_s"], "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
+                "warmup": max(args.warmup, 3), "ms_per_step": r["ms_per_step"], "higher_is_better": True, "scaling": "weak",
+                "vs_baseline": None, "dtype": "fp16 tensor-core inputs (weights dequantised on the fly), f32 accumulate",
+                "data": "synthetic", "config": {"workload": r["workload"], "tokens_per_step": r["tokens_per_step"],
+                                                "qtype": args.qtype, "parallelism": "1 gpu", "l2": L2_NOTE},
+                "e2e": r["e2e"], "gpu_launches": r["gpu_launches_per_step"] * args.steps, "roofline": r["roofline"],
+                "clocks": sampler.stop(), "step_ms_min_max": r["step_ms_min_max"]}
+        traffic, source = captured_traffic("grouped_gemm_kernel__prefill_q4_4096.md", "moe_grouped_gemm.cu")
+        line["roofline"].update(traffic=traffic if args.qtype == "q4_0" else None, traffic_source=source)
+        if not args.no_cpu_baseline:
+            from oracle import oracle as orc
+            L, hidden, resid = synth_token_layer(w["seed"], 1024, args.qtype)
+            cps, ckind, sample = cpu_tokens_per_s(L, hidden, resid, orc.host_threads())
+            line["cpu_baseline"] = {"value": cps, "unit": "tokens/s", "cores": orc.host_threads(), "kind": ckind, "sample": sample}
+    elif kind == "batched":
+        if world > 1:
+            raise SystemExit("the batched-decode workload runs on one GPU")
+        r = measure_batched_decode(pkg, torch, flush_l2, args.steps, max(args.warmup, 3))
+        t64 = r["tokens"]["64"]
+        line = {"metric": "moe_batched_decode_us_per_step", "value": t64["us_per_step"], "unit": "us/step (64 tokens)", "n_gpus": 1,
+                "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": t64["us_per_step"] / 1e3,
+                "higher_is_better": False, "scaling": "weak", "vs_baseline": None,
+                "dtype": "f32 accumulate over fp16 activations and Q8_0 weights", "data": "synthetic",
+                "config": {"workload": r["workload"], "tokens_per_step": 64, "qtype": "q8_0", "l2": L2_NOTE},
+                "gpu_launches": t64["gpu_launches_per_step"] * args.steps,
+                "roofline": {"bound": "hbm", "achieved": t64["achieved_gbs"], "peak": r["peak_gbs"], "peak_kind": r["peak_kind"],
+                             "unit": "GB/s", "frac": t64["frac"], "traffic": None}, "batched_decode": r}
     else:
-        run_tokens(args, kind, rank, local_rank, world)
+        sampler = ClockSampler(local_rank) if rank == 0 else None
+        ep = measure_ep(pkg, torch, dist, rank, world, flush_l2, args.steps, max(args.warmup, 3), args.exchange, routings)
+        clocks = sampler.stop() if sampler else None
+        if rank == 0:
+            w = token_workload("ep")
+            first = ep[routings[0]]
+            line = {"metric": w["metric"], "value": first["tokens_per_s"], "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+                    "warmup": max(args.warmup, 3), "ms_per_step": first["ms_per_step"], "higher_is_better": True, "scaling": "strong",
+                    "vs_baseline": None, "dtype": "fp16 tensor-core inputs (weights dequantised from Q4_0 on the fly), f32 accumulate",
+                    "data": "synthetic", "config": {"workload": ep["workload"], "tokens_per_step": ep["tokens_per_step"], "qtype": "q4_0",
+                                                    "routing": routings[0], "parallelism": ep["parallelism"], "exchange": ep["exchange"],
+                                                    "l2": L2_NOTE},
+                    "e2e": first.get("e2e"), "gpu_launches": first["gpu_launches_per_step"] * args.steps, "roofline": first["roofline"],
+                    "clocks": clocks, "ep": ep}
+            if not args.no_cpu_baseline:
+                from oracle import oracle as orc
+                L, hidden, resid = synth_token_layer(w["seed"], 1024)
+                cps, ckind, sample = cpu_tokens_per_s(L, hidden, resid, orc.host_threads())
+                line["cpu_baseline"] = {"value": cps, "unit": "tokens/s", "cores": orc.host_threads(), "kind": ckind, "sample": sample}
+    if rank == 0 and line is not None:
+        print(json.dumps(line), flush=True)
     if world > 1:
+        dist.barrier()
         dist.destroy_process_group()
 
 

@@ -107,11 +107,13 @@ UOCR_CUDA_API const char *uocr_cuda_context_last_error(const uocr_cuda_context *
 UOCR_CUDA_API int uocr_cuda_context_set_stream(uocr_cuda_context *ctx, void *cuda_stream);
 /* Detail profiling of the single-token stack call, the counterpart of the reference's per-op checkpoints
  * (UOCR_METAL_DECODER_PROFILE_DETAIL, src/backend/metal/uocr_metal.m:29-31, :14251-14297).  d_trace is a device
- * buffer of 128 * n_layers * 8 uint64: the SM clock of CTA c in layer l at point p sits at [(c * n_layers + l) * 8 + p].
- * One-barrier decode kernel (112 CTAs): activations arranged, routing done, weight fetches issued, first weight
- * chunk in shared memory, SwiGLU products ready, partial outputs ready, partial sums sent, barrier passed.
- * Two-barrier decode kernel (CTA 0 only): layer start, inputs read, routing done, copies issued, gate/up computed,
- * barrier 1 passed, down computed, barrier 2 passed.  NULL switches it off. */
+ * buffer of 128 * n_layers * 16 uint64: the SM clock of CTA c in layer l at point p sits at [(c * n_layers + l) * 16 + p].
+ * One-barrier decode kernel (112 CTAs): 0 activations arranged, 1 routing done, 2 weight fetches issued, 3 first weight
+ * chunk in shared memory, 4 SwiGLU products ready, 5 partial outputs ready, 6 partial sums sent, 7 layer output
+ * complete; 8 own router logits, 9 logits exchanged, 10-13 gate / up products of the first warp chunk by chunk,
+ * 14 its sums, 15 every warp's sums; CTA slot 127 holds the clock of CTA 0 at kernel entry ([0]) and exit ([1]).
+ * Two-barrier decode kernel (CTA 0 only, 8 points per layer at stride 8): layer start, inputs read, routing done,
+ * copies issued, gate/up computed, barrier 1 passed, down computed, barrier 2 passed.  NULL switches it off. */
 UOCR_CUDA_API int uocr_cuda_context_set_profile_detail(uocr_cuda_context *ctx, void *d_trace);
 UOCR_CUDA_API int uocr_cuda_context_synchronize(uocr_cuda_context *ctx, char *error, size_t error_size);
 /* Kernels launched by this context since creation (every launch is counted at its call site). */

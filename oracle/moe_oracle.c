@@ -368,13 +368,19 @@ static void mo_expert_matrices(const mo_layer_weights *L, uint32_t e, mo_matrix 
  * f32 layer above, so for any input
  *     mo_layer_slab(...) == mo_layer_f32(dequantised copies ...)   bit for bit.
  * injected_logits (rows x E, may be NULL) replaces the router dot products.
- * round_mid_f16 bit 0 additionally rounds the SwiGLU products through fp16,
- * which is the rounding the GPU kernels apply when they store `mid`
- * (src/backend/metal/kernels/decode_gemv_q4.metal:176-179); bit 1 rounds every
- * expert's down product and the shared MLP's output through fp16, as the
- * reference's many-token GPU path stores them before the combine
- * (src/backend/metal/kernels/gemm_q8.metal:867-919).  The reference CPU path
- * itself keeps f32 everywhere (round_mid_f16 = 0).
+ * round_mid_f16 is a set of bits, each an fp16 rounding of the reference's GPU
+ * or NumPy fp16 contracts; the reference CPU path itself keeps f32 everywhere
+ * (round_mid_f16 = 0):
+ *   1  the SwiGLU products, as the GPU kernels store `mid`
+ *      (src/backend/metal/kernels/decode_gemv_q4.metal:176-179;
+ *      src/unlimitedocr_c/golden.py:476-477, :624-625);
+ *   2  every expert's down product, as the many-token GPU path stores it
+ *      before the combine (src/backend/metal/kernels/gemm_q8.metal:867-919);
+ *   4  the shared MLP's output (same GPU path; golden.py:481 with a zero
+ *      residual, :640-648);
+ *   8  the weighted sum of the routed experts before the shared output is
+ *      added (golden.py:627-628, :663-665).
+ * 1|2|4 is the tiled-GEMM contract, 1|4|8 the NumPy fp16 contract.
  * residual (fp16, may be NULL) is added to the f32 result at the end, the place
  * the GPU layer adds it (src/backend/metal/kernels/decode_gemv_q4.metal:221-223).
  * The experts are walked expert-major (each distinct expert is dequantised once
@@ -448,7 +454,7 @@ int mo_layer_slab(const mo_layer_weights *L, const uint16_t *hidden_f16, const u
                 shared_ws[i] = v;
             }
             mo_matmul_nt(&L->shared_down, shared_ws, rows, d, scratch4);
-            if (round_mid_f16 & 2) for (size_t i = 0; i < (size_t)rows * H; ++i) d[i] = mo_f16_to_f32(mo_f32_to_f16(d[i]));
+            if (round_mid_f16 & 4) for (size_t i = 0; i < (size_t)rows * H; ++i) d[i] = mo_f16_to_f32(mo_f32_to_f16(d[i]));
             for (uint32_t r = 0; r < rows; ++r) {
                 float *orow = out + (size_t)r * H;
                 for (uint32_t h = 0; h < H; ++h) orow[h] = 0.0f;
@@ -457,6 +463,7 @@ int mo_layer_slab(const mo_layer_weights *L, const uint16_t *hidden_f16, const u
                     const float *dn = down_all + ((size_t)r * K + s) * H;
                     for (uint32_t h = 0; h < H; ++h) orow[h] = fmaf(w, dn[h], orow[h]);
                 }
+                if (round_mid_f16 & 8) for (uint32_t h = 0; h < H; ++h) orow[h] = mo_f16_to_f32(mo_f32_to_f16(orow[h]));
                 for (uint32_t h = 0; h < H; ++h) orow[h] += d[(size_t)r * H + h];
                 if (residual_f16)
                     for (uint32_t h = 0; h < H; ++h) orow[h] += mo_f16_to_f32(residual_f16[(size_t)r * H + h]);

@@ -150,8 +150,9 @@ class Port:
     def layer(self, L: quant.LayerWeights, hidden: np.ndarray, residual: np.ndarray | None = None, *,
               injected_logits: np.ndarray | None = None, round_mid_f16: bool | int = False, weights_through_f16: bool = False,
               threads: int = 1) -> LayerOut:
-        """round_mid_f16: bit 0 rounds the SwiGLU products through fp16, bit 1 the per-expert down products and the
-        shared output; weights_through_f16 rounds every dequantised weight to fp16 (the tiled-GEMM contract)."""
+        """round_mid_f16: bits selecting fp16 roundings: 1 the SwiGLU products, 2 the per-expert down products,
+        4 the shared MLP's output, 8 the weighted routed sum (1|2|4: the tiled-GEMM contract, 1|4|8: the
+        reference's NumPy fp16 contract); weights_through_f16 rounds every dequantised weight to fp16."""
         hidden = np.ascontiguousarray(hidden, np.uint16)
         rows = hidden.shape[0]
         o = LayerOut(rows, L.H, L.E, L.K, L.F, L.S)

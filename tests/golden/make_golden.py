@@ -3,9 +3,10 @@
 
 Run where the reference checkout is available:
 
-    python tests/golden/make_golden.py [--reference /path/to/unlimitedocr.c]
+    python tests/golden/make_golden.py --reference /path/to/unlimitedocr.c
+    (or set UOCR_REFERENCE_ROOT)
 
-It writes three small files next to itself; the tests only read those files.
+It writes four small files next to itself; the tests only read those files.
 
 cpu_ref_tiny_moe.json
     The MoE and dense-SwiGLU golden vectors the reference's own unit test
@@ -22,11 +23,19 @@ ref_layers.npz
     oracle/_ref) on seeded inputs: the tiny 16-token Q8_0 layer of the benchmark
     plan, a Q4_0 and an fp16 variant, plus the router on hand-made tie cases.
     Inputs are regenerated from the seed by oracle/quant.py; only outputs are stored.
+f16_contract.npz
+    Outputs of the reference's NumPy fp16-contract layer (src/unlimitedocr_c/golden.py:
+    _moe_router_f16 :544-562 and _moe_layer_f16_bits_with_router :649-666, which rounds the SwiGLU
+    products, the routed sum and the shared output to fp16) on a seeded full-size fp16 layer.  The
+    functions read their weights by tensor name from a checkpoint folder; here the module's reader
+    is replaced by one that serves the synthetic arrays under the same names, nothing else changes.
+    Inputs are regenerated from the seed; only outputs are stored.
 """
 from __future__ import annotations
 
 import argparse
 import json
+import os
 import re
 import sys
 import types
@@ -62,10 +71,45 @@ TINY = dict(H=128, E=8, K=2, F=64, S=64)
 TINY_ROWS = 16
 
 
+FULL = dict(H=1280, E=64, K=6, F=896, S=1792)
+F16_CONTRACT_SEED, F16_CONTRACT_ROWS, F16_CONTRACT_LAYER = 50, 6, 1
+
+
+def f16_contract_inputs():
+    """Seeded full-size fp16 layer, activations and residual of the fp16-contract fixture."""
+    from oracle import quant
+    rng = np.random.default_rng(F16_CONTRACT_SEED)
+    L = quant.synth_layer(rng, expert_qtype=quant.QTYPE_F16, **FULL)
+    hidden = quant.synth_activations(rng, F16_CONTRACT_ROWS, FULL["H"])
+    resid = quant.synth_activations(rng, F16_CONTRACT_ROWS, FULL["H"])
+    return L, hidden, resid
+
+
+def f16_contract_tensor_names(L, layer: int) -> dict:
+    """The layer's fp16 tensors under the checkpoint names the reference's NumPy functions ask for."""
+    H, E, F, S = L.H, L.E, L.F, L.S
+    prefix = f"model.layers.{layer}.mlp"
+    out = {f"{prefix}.gate.weight": L.router.reshape(E, H)}
+    slab = L.expert_qweight.view(np.uint16)
+    proj = F * H
+    for e in range(E):
+        base = e * 3 * proj
+        out[f"{prefix}.experts.{e}.gate_proj.weight"] = slab[base:base + proj].reshape(F, H)
+        out[f"{prefix}.experts.{e}.up_proj.weight"] = slab[base + proj:base + 2 * proj].reshape(F, H)
+        out[f"{prefix}.experts.{e}.down_proj.weight"] = slab[base + 2 * proj:base + 3 * proj].reshape(H, F)
+    for key, m in (("gate_proj", L.shared_gate), ("up_proj", L.shared_up), ("down_proj", L.shared_down)):
+        out[f"{prefix}.shared_experts.{key}.weight"] = m.qweight.view(np.uint16).reshape(m.rows, m.cols)
+    return out
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
-    ref_root = Path(ap.parse_args().reference)
+    ap.add_argument("--reference", default=os.environ.get("UOCR_REFERENCE_ROOT"),
+                    help="checkout of the reference project (or set UOCR_REFERENCE_ROOT)")
+    args = ap.parse_args()
+    if not args.reference:
+        ap.error("give --reference or set UOCR_REFERENCE_ROOT")
+    ref_root = Path(args.reference)
 
     # 1. the reference's golden header, as data
     hdr = parse_header(ref_root / "tests/fixtures/cpu_ref_tiny_golden.h", ("UOCR_TINY_MOE_", "UOCR_TINY_SWIGLU_"))
@@ -122,6 +166,23 @@ def main() -> None:
         store[f"ties_k{k}_weights"] = o.weights
     store["ties_logits"] = ties
     np.savez_compressed(HERE / "ref_layers.npz", **store)
+
+    # 4. the reference's NumPy fp16 contract on a synthetic full-size fp16 layer
+    from unlimitedocr_c import golden as ref_golden  # type: ignore
+
+    L, hidden, resid = f16_contract_inputs()
+    names = f16_contract_tensor_names(L, layer=F16_CONTRACT_LAYER)
+
+    def fake_reader(hf_dir, name, expected_shape=None):
+        t = names[name]
+        assert expected_shape is None or tuple(expected_shape) == t.shape, (name, expected_shape, t.shape)
+        return t
+
+    ref_golden.read_bf16_tensor_as_f16_bits = fake_reader
+    probs, r_ids, r_w = ref_golden._moe_router_f16(hidden, names[f"model.layers.{F16_CONTRACT_LAYER}.mlp.gate.weight"])
+    out_bits, ids, wts = ref_golden._moe_layer_f16_bits_with_router(hidden, resid, "synthetic", layer=F16_CONTRACT_LAYER)
+    assert np.array_equal(ids, r_ids) and np.array_equal(wts, r_w)
+    np.savez_compressed(HERE / "f16_contract.npz", probs=probs, ids=ids, weights=wts, out_bits=out_bits)
     print("wrote", [p.name for p in sorted(HERE.glob("*.json")) + sorted(HERE.glob("*.npz"))])
 
 

@@ -240,7 +240,7 @@ def check_layer(pkg, port, L, hidden, resid, *, tight=2.5e-3, gemm=False):
     reproduced by the second oracle run."""
     n = hidden.shape[0]
     want = port.layer(L, hidden, resid, threads=16)
-    contract = port.layer(L, hidden, resid, round_mid_f16=3 if gemm else 1, weights_through_f16=gemm, threads=16)
+    contract = port.layer(L, hidden, resid, round_mid_f16=7 if gemm else 1, weights_through_f16=gemm, threads=16)
     L2 = quant.LayerWeights(**{**L.__dict__, "logit_bias": None})
     g = Layer(pkg, L2, n)
     try:

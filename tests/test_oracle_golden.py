@@ -279,3 +279,31 @@ def test_dispatch_plan_is_the_stable_sort(port):
             seg = pr[off[e]:off[e + 1]]
             assert np.all(flat[seg] == e) and np.all(np.diff(seg.astype(np.int64)) > 0)
         assert off[E] == np.count_nonzero(flat < E)
+
+
+def test_fp16_contract_mode_matches_the_reference_numpy_layer(port, golden_dir):
+    """The oracle's fp16 roundings (SwiGLU products, routed sum, shared output: round_mid_f16 = 1|4|8) against
+    the reference's own NumPy fp16-contract layer (src/unlimitedocr_c/golden.py:544-562, :649-666), whose stored
+    outputs tests/golden/make_golden.py produced on the same seeded full-size fp16 layer.  The two sum in different
+    orders (serial f32 chains here, BLAS there), so logits-dependent values are compared at the reference's own
+    router threshold and a few outputs differ by one fp16 step of an intermediate."""
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("make_golden", golden_dir / "make_golden.py")
+    mg = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mg)
+    L, hidden, resid = mg.f16_contract_inputs()
+    z = np.load(golden_dir / "f16_contract.npz")
+    got = port.layer(L, hidden, resid, round_mid_f16=1 | 4 | 8, threads=6)
+    assert np.array_equal(got.ids, z["ids"])
+    assert np.max(np.abs(got.weights - z["weights"])) <= 5e-5        # src/unlimitedocr_c/parity_thresholds.py:66-70
+    assert np.max(np.abs(got.probs - z["probs"])) <= 5e-5
+    got_bits = port.f32_to_f16(got.out)
+    want_bits = z["out_bits"]
+    # a differing element comes from ONE fp16 step of the routed sum or the shared output (both below 2 in magnitude:
+    # a step of at most 2^-10) carried through the final rounding of an output below 4 (half a step of 2^-8)
+    assert np.max(np.abs(port.f16_to_f32(got_bits) - port.f16_to_f32(want_bits))) <= 2.0 ** -9
+    assert np.max(np.abs(port.f16_to_f32(want_bits))) < 8.0
+    assert np.mean(got_bits == want_bits) >= 0.97
+    # and the mode matters: without the roundings the bits differ far more often
+    plain = port.f32_to_f16(port.layer(L, hidden, resid, threads=6).out)
+    assert np.mean(plain == want_bits) < np.mean(got_bits == want_bits)

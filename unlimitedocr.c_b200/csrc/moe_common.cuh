@@ -170,6 +170,7 @@ struct PeerBuffers { __half *p[kMaxPeers]; };
 struct SlicedKnobs {
     uint32_t replicas = 1;            // copies of the layer accumulator the CTAs spread their additions over (1, 2 or 4)
     long long spin_limit_cycles = 0;  // limit of a wait between CTAs; 0: the built-in limit (about two seconds)
+    uint32_t poll_sleep_ns = 0;       // pause between two polls of the layer accumulator
     uint32_t expect_extra = 0;        // test hook: the wait for a layer's output expects this many contributions
                                       // more than there are CTAs, so it runs into its limit
 };

@@ -56,6 +56,8 @@
 #include <cuda.h>
 
 #include <atomic>
+#include <cstdlib>
+#include <cstring>
 
 #include "moe_route.cuh"
 #include "moe_sync.cuh"
@@ -77,7 +79,7 @@ constexpr unsigned long long kSlAccOne = 1ull << 56;
 constexpr long long kSlAccBias = 1ll << 47;
 constexpr float kSlAccScale = 268435456.f;       // 2^28
 constexpr float kSlAccRange = 262144.f;          // |partial output| must stay below 2^18
-constexpr int kSlTracePoints = 8;
+constexpr int kSlTracePoints = 16;
 constexpr int kSlMaxLayers = 64;
 constexpr int kSlBlocksPerWarp = kSlH / 16 / 16;            // 5 blocks of 16 output rows per warp
 
@@ -100,6 +102,7 @@ struct SlicedParams {
     unsigned long long *trace;    // optional [CTA][count][kSlTracePoints] SM-clock stamps
     uint32_t *host_status;        // optional word in mapped host memory: receives the status word after `out` is written
     long long spin_limit;         // cycles a wait for other CTAs may take before the kernel gives up
+    uint32_t poll_sleep_ns;       // pause between two polls of the layer accumulator (0: none)
     uint32_t expect_extra;        // test hook: contributions the poll expects beyond the CTAs there are (0 in production)
 };
 // The same with the first layer's input (and, with chain_residual, its residual) carried in the launch parameters:
@@ -310,6 +313,7 @@ __global__ void __launch_bounds__(kSlThreads, 1) decode_sliced_kernel(const __gr
     const uint32_t R = prm.replicas;                                    // accumulator replicas (1, 2 or 4)
     const long long spin_limit = prm.spin_limit;
 
+    if (prm.trace != nullptr && tid == 0 && cta == 0) prm.trace[(size_t)127 * prm.count * kSlTracePoints] = clock64();     // kernel entry
     if (tid < UOCR_EXPF_N) s_tab[tid] = c_exp_tab[tid];
     if (tid == 0) {
         s_flag[0] = 1; s_flag[1] = 0;
@@ -452,6 +456,7 @@ __global__ void __launch_bounds__(kSlThreads, 1) decode_sliced_kernel(const __gr
                 }
                 if (t == 0) { s_rp[warp * 16 + g] = c[0] + d[0]; s_rp[warp * 16 + 8 + g] = c[2] + d[2]; }
                 __syncthreads();
+                UOCR_SL_TRACE(8);     // this CTA's partial logits
                 if (warp == 0) {
                     if (lane < 16) {          // one logit per lane, summed over the warps in a fixed order, sent to the whole cluster
                         float v = 0.f;
@@ -476,6 +481,7 @@ __global__ void __launch_bounds__(kSlThreads, 1) decode_sliced_kernel(const __gr
                 lg_phase ^= 1u;
             }
             __syncthreads();
+            UOCR_SL_TRACE(9);         // all 64 logits exchanged
             // ---- routing.  The softmax is monotonic, so the slot's expert is (except for two logits that round to one
             // probability) the one whose logit ranks slot-th: eight threads per expert count the logits that beat
             // it.  Every warp but one goes on to fetch that expert's weights, while warp 1 runs the exact softmax /
@@ -566,9 +572,13 @@ __global__ void __launch_bounds__(kSlThreads, 1) decode_sliced_kernel(const __gr
                 UOCR_SL_TRACE(3);              // first chunk is in shared memory
                 if (routed) fetch_down(blob);
                 quad(0, SlInt<0>{}, SlInt<4>{});
+                UOCR_SL_TRACE(10);
                 got = mbar_wait(&bars[2], copy_phase, status, s_flag) && got;
+                UOCR_SL_TRACE(11);
                 quad(8, SlInt<0>{}, SlInt<4>{});
+                UOCR_SL_TRACE(12);
                 got = mbar_wait(&bars[4], copy_phase, status, s_flag) && got;
+                UOCR_SL_TRACE(13);
                 quad(16, SlInt<0>{}, SlInt<2>{});
             } else {
                 got = mbar_wait(&bars[1], copy_phase, status, s_flag) && got;
@@ -584,7 +594,9 @@ __global__ void __launch_bounds__(kSlThreads, 1) decode_sliced_kernel(const __gr
             sg += __shfl_xor_sync(0xffffffffu, sg, 1); su += __shfl_xor_sync(0xffffffffu, su, 1);
             sg += __shfl_xor_sync(0xffffffffu, sg, 2); su += __shfl_xor_sync(0xffffffffu, su, 2);
             if (t == 0) { s_gu[kh * 128 + 8 * rb + g] = sg; s_gu[kh * 128 + 64 + 8 * rb + g] = su; }
+            UOCR_SL_TRACE(14);        // this warp's gate / up sums
             __syncthreads();
+            UOCR_SL_TRACE(15);        // every warp's
             copy_phase ^= 1u;
             if (routed) {            // the exact routing is in shared memory by now
                 const uint32_t exact = s_ids[slot];
@@ -707,6 +719,7 @@ __global__ void __launch_bounds__(kSlThreads, 1) decode_sliced_kernel(const __gr
                     }
                 }
                 if (all) break;
+                if (prm.poll_sleep_ns != 0u) __nanosleep(prm.poll_sleep_ns);
                 if ((polls & 15u) == 0u) {
                     if (ld_volatile_u32(status) & (kStatusBarrier | kStatusCopy)) { have = false; break; }
                     if (clock64() - t0 > spin_limit) { atomicOr(status, kStatusBarrier); have = false; break; }
@@ -741,6 +754,7 @@ __global__ void __launch_bounds__(kSlThreads, 1) decode_sliced_kernel(const __gr
             __syncthreads();
         }
     }
+    if (prm.trace != nullptr && tid == 0 && cta == 0) prm.trace[(size_t)127 * prm.count * kSlTracePoints + 1] = clock64();   // kernel exit
 #undef UOCR_SL_TRACE
 }
 
@@ -803,6 +817,10 @@ __global__ void repack_units_kernel(RepackSrc src, uint8_t *out) {
 // cluster size the kernel is launched with on a device, 0: cannot run there (written when a context is created,
 // possibly by several threads at once: same value every time)
 static std::atomic<int> g_sliced_cluster[64];
+// Co-residency of all CTAs is what the waits between them rely on; a cooperative launch guarantees it.  The
+// environment variable UOCR_CUDA_DECODE_COOPERATIVE=0 drops the attribute (measurement only: the grid is smaller
+// than the machine, and every wait is bounded, so a launch that is not co-resident ends with an error status).
+static std::atomic<int> g_sliced_cooperative{1};
 
 // The shapes and formats this kernel is built for (the model's).
 bool decode_sliced_layer_ok(const DLayer &L) {
@@ -842,10 +860,10 @@ static void launch_config(cudaLaunchConfig_t *cfg, cudaLaunchAttribute *attrs, i
     *cfg = cudaLaunchConfig_t{};
     cfg->gridDim = dim3(kSlUnits); cfg->blockDim = dim3(kSlThreads);
     cfg->dynamicSmemBytes = SlSmem<QT>::kTotal; cfg->stream = st;
-    attrs[0].id = cudaLaunchAttributeCooperative; attrs[0].val.cooperative = 1;
-    attrs[1].id = cudaLaunchAttributeClusterDimension;
-    attrs[1].val.clusterDim.x = (unsigned)cluster; attrs[1].val.clusterDim.y = 1; attrs[1].val.clusterDim.z = 1;
-    cfg->attrs = attrs; cfg->numAttrs = 2;
+    attrs[0].id = cudaLaunchAttributeClusterDimension;
+    attrs[0].val.clusterDim.x = (unsigned)cluster; attrs[0].val.clusterDim.y = 1; attrs[0].val.clusterDim.z = 1;
+    attrs[1].id = cudaLaunchAttributeCooperative; attrs[1].val.cooperative = 1;
+    cfg->attrs = attrs; cfg->numAttrs = g_sliced_cooperative.load() ? 2 : 1;
 }
 
 // 1 when all CTAs can be resident at once in clusters of kSlCluster, else 0
@@ -871,6 +889,7 @@ cudaError_t init_decode_sliced_kernels() {
     int dev = 0;
     cudaError_t err = cudaGetDevice(&dev);
     if (err != cudaSuccess) return err;
+    if (const char *c = getenv("UOCR_CUDA_DECODE_COOPERATIVE")) g_sliced_cooperative = c[0] == '0' ? 0 : 1;
     int ok4 = 0, ok8 = 0;
     if ((err = prepare_sliced<UOCR_QT_Q4>(&ok4)) != cudaSuccess) return err;
     if ((err = prepare_sliced<UOCR_QT_Q8>(&ok8)) != cudaSuccess) return err;
@@ -924,6 +943,7 @@ cudaError_t launch_decode_sliced(const DLayer *h_layers, const DLayer *d_layers,
     prm.status = status; prm.host_status = host_status;
     prm.spin_limit = knobs.spin_limit_cycles > 0 ? knobs.spin_limit_cycles : kSpinLimit;
     prm.expect_extra = knobs.expect_extra;
+    prm.poll_sleep_ns = knobs.poll_sleep_ns;
     prm.dbg_logits = dbg_logits; prm.dbg_probs = dbg_probs; prm.ids_out = ids_out; prm.wts_out = wts_out; prm.trace = trace;
     const bool q4 = h_layers[first].expert_qtype == UOCR_QT_Q4;
     if (h_inline != nullptr) {

@@ -212,6 +212,7 @@ extern "C" uocr_cuda_context *uocr_cuda_context_create(const char *resource_path
     ctx->sliced_decode = !(design && strcmp(design, "two-barrier") == 0);   // (then no slice-major weight copy is made)
     if (const char *mt = getenv("UOCR_CUDA_GEMM_MIN_TOKENS")) ctx->gemm_min_tokens = (uint32_t)strtoul(mt, nullptr, 10);
     if (const char *r = getenv("UOCR_CUDA_DECODE_REPLICAS")) ctx->decode_knobs.replicas = (uint32_t)strtoul(r, nullptr, 10);
+    if (const char *r = getenv("UOCR_CUDA_DECODE_POLL_SLEEP_NS")) ctx->decode_knobs.poll_sleep_ns = (uint32_t)strtoul(r, nullptr, 10);
     // Test hooks for the time-out path of the decode kernel's waits: a shorter limit (in SM cycles), and one launch
     // whose wait for the layer output expects one contribution more than there are CTAs.  Nothing faults: the wait
     // runs into its limit, the kernel raises its status word and returns.

@@ -243,8 +243,9 @@ class Context:
         self._check(self._lib.uocr_cuda_context_set_stream(self._h, cuda_stream))
 
     def set_profile_detail(self, trace) -> None:
-        """Device buffer (128 * n_layers * 8 int64) that single-token stack calls fill with per-phase SM clocks:
-        CTA c, layer l, point p at [(c * n_layers + l) * 8 + p] (the two-barrier kernel writes CTA 0 only)."""
+        """Device buffer (128 * n_layers * 16 int64) that single-token stack calls fill with per-phase SM clocks:
+        CTA c, layer l, point p at [(c * n_layers + l) * 16 + p] (see the header for the points; the two-barrier
+        kernel writes CTA 0 only, 8 points per layer at stride 8)."""
         self._check(self._lib.uocr_cuda_context_set_profile_detail(self._h, _dev_ptr(trace)))
 
     def synchronize(self) -> None:
