@@ -210,6 +210,10 @@ UOCR_CUDA_API int uocr_cuda_moe_layer_forward(uocr_cuda_context *ctx, uint32_t l
                                               const uocr_cuda_moe_debug_outputs *debug, char *error,
                                               size_t error_size);
 
+/* Which of the regimes a layer call with n_tokens would take (a static string naming the kernels; "" for invalid
+ * arguments).  The reference switches on n_tokens > 1 in the same place (src/backend/metal/uocr_metal.m:13674). */
+UOCR_CUDA_API const char *uocr_cuda_moe_regime_name(const uocr_cuda_context *ctx, uint32_t layer, uint32_t n_tokens);
+
 /* A run of consecutive layers first_layer .. first_layer+n_layers-1 chained the way the decoder chains
  * them with the attention block left out: layer i's input is also its residual, its output feeds layer
  * i+1.  One call = one decode step through the MoE halves of those layers. */

@@ -276,9 +276,23 @@ def test_full_size_decode_layer(pkg, port, qname, shared):
 
 @pytest.mark.parametrize("n", [2, 8, 32, 64])
 def test_batched_decode_q8_with_skewed_load(pkg, port, n):
-    """Config 3: Q8_0, per-expert logit bias N(0,1)."""
+    """Config 3: Q8_0, per-expert logit bias N(0,1).  Served by the weight-streaming batched decode kernel, which
+    follows the single-token kernel's rounding contract (fp16 SwiGLU products, f32 everywhere else)."""
     L, hidden, resid = make(2, FULL, "q8_0", n, bias="normal")
-    check_layer(pkg, port, L, hidden, resid, gemm=n >= 5)
+    with pkg.Context() as ctx:
+        ctx.map_layer(L)
+        assert "decode_batched_kernel" in ctx.regime_name(0, n)
+    check_layer(pkg, port, L, hidden, resid)
+
+
+@pytest.mark.parametrize("qname,n,bias", [("q4_0", 5, None), ("q4_0", 17, "zipf"), ("q4_0", 64, "zipf"), ("q8_0", 33, "zipf"),
+                                          ("q8_0", 64, None)])
+def test_batched_decode_kernel_ragged_and_hot_experts(pkg, port, qname, n, bias):
+    """The batched decode kernel on token counts that are not multiples of its 4-token MMA blocks or 16-token passes,
+    and under Zipf-skewed routing, where one expert receives more tokens than one pass holds."""
+    L, hidden, resid = make(12, FULL, qname, n, bias=bias)
+    check_layer(pkg, port, L, hidden, resid)
+    check_layer(pkg, port, L, hidden, None)
 
 
 @pytest.mark.parametrize("qname,shared,n,bias", [("q4_0", None, 200, None), ("f16", None, 96, None),
@@ -290,19 +304,23 @@ def test_prefill_tensor_core_path(pkg, port, qname, shared, n, bias):
     check_layer(pkg, port, L, hidden, resid, gemm=True)
 
 
-def test_tensor_core_and_matrix_vector_paths_agree(pkg, port, monkeypatch):
-    """The same 24-token call through the grouped-GEMM path and through the matrix-vector path."""
+def test_the_three_few_token_paths_agree(pkg, port, monkeypatch):
+    """The same 24-token call through the batched decode kernel, the grouped-GEMM path and the matrix-vector path."""
     L, hidden, resid = make(8, FULL, "q4_0", 24, bias="normal")
     outs = {}
-    for mode, min_tokens in (("gemm", "5"), ("gemv", "100000")):
+    for mode, batched_off, min_tokens, kernel in (("batched", "0", "5", "decode_batched_kernel"), ("gemm", "1", "5", "grouped_gemm_kernel"),
+                                                   ("gemv", "1", "100000", "gate_up_kernel")):
+        monkeypatch.setenv("UOCR_CUDA_DISABLE_BATCHED_DECODE", batched_off)
         monkeypatch.setenv("UOCR_CUDA_GEMM_MIN_TOKENS", min_tokens)
         with pkg.Context() as ctx:
             ctx.map_layer(L)
             ctx.allocate_runtime_arenas(24)
+            assert kernel in ctx.regime_name(0, 24)
             outs[mode] = ctx.layer_forward_host(0, hidden, resid, want_routing=True)
-    assert np.array_equal(outs["gemm"][1], outs["gemv"][1])
-    err, cos = closeness(outs["gemm"][0].view("<f2").astype(np.float32), outs["gemv"][0].view("<f2").astype(np.float32))
-    assert err <= 8e-3 and cos >= 0.99999, (err, cos)
+    assert np.array_equal(outs["gemm"][1], outs["gemv"][1]) and np.array_equal(outs["batched"][1], outs["gemv"][1])
+    for a, b, tol in (("gemm", "gemv", 8e-3), ("batched", "gemv", 4e-3)):
+        err, cos = closeness(outs[a][0].view("<f2").astype(np.float32), outs[b][0].view("<f2").astype(np.float32))
+        assert err <= tol and cos >= 0.99999, (a, b, err, cos)
 
 
 def test_ragged_sizes_and_scaling(pkg, port):
@@ -639,10 +657,10 @@ def padded_slab_layer(L, pad_bytes=48, pad_scales=24):
     return quant.LayerWeights(**{**L.__dict__, "expert_qweight": slab, "expert_qscale": scales, "meta": {"strides": strides}})
 
 
-@pytest.mark.parametrize("qname,n", [("q4_0", 1), ("q8_0", 1), ("q4_0", 3), ("q4_0", 64), ("f16", 40)])
+@pytest.mark.parametrize("qname,n", [("q4_0", 1), ("q8_0", 1), ("q4_0", 3), ("q4_0", 64), ("q4_0", 200), ("f16", 40)])
 def test_slab_with_gaps_between_projections(pkg, port, qname, n):
-    """Expert strides and projection offsets larger than the dense ones: every regime (decode kernel with its
-    slice-major copy, matrix-vector kernels, grouped GEMM) must address the slab through them."""
+    """Expert strides and projection offsets larger than the dense ones: every regime (the decode kernels with their
+    slice-major copy, grouped GEMM on the file layout) must address the slab through them."""
     L, hidden, resid = make(9, FULL, qname, n)
     want = port.layer(L, hidden, resid, threads=16)
     g = Layer(pkg, quant.LayerWeights(**{**padded_slab_layer(L).__dict__, "logit_bias": None}), n)

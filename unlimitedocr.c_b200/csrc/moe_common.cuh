@@ -161,6 +161,9 @@ __device__ __forceinline__ void row_dot(const uint8_t *wrow, const __half *srow,
 }
 
 __device__ __forceinline__ float silu_f32(float v) { return v / (1.0f + __expf(-v)); }
+// the same with the fast reciprocal (about 2 ulp; the result is rounded to fp16 anyway): an IEEE division is a
+// subroutine of a few hundred cycles, which a latency-bound kernel cannot hide
+__device__ __forceinline__ float silu_fast_f32(float v) { return __fdividef(v, 1.0f + __expf(-v)); }
 
 // One buffer per rank of an expert-parallel group on one node (this rank's own and the peers' mapped ones).
 constexpr int kMaxPeers = 16;
@@ -168,7 +171,7 @@ struct PeerBuffers { __half *p[kMaxPeers]; };
 
 // Run-time settings of the single-token decode kernel (a context reads them from the environment when it is created).
 struct SlicedKnobs {
-    uint32_t replicas = 1;            // copies of the layer accumulator the CTAs spread their additions over (1, 2 or 4)
+    uint32_t replicas = 2;            // copies of the layer accumulator the CTAs spread their additions over (1, 2 or 4)
     long long spin_limit_cycles = 0;  // limit of a wait between CTAs; 0: the built-in limit (about two seconds)
     uint32_t poll_sleep_ns = 0;       // pause between two polls of the layer accumulator
     uint32_t expect_extra = 0;        // test hook: the wait for a layer's output expects this many contributions

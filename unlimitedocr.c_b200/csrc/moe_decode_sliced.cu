@@ -59,17 +59,15 @@
 #include <cstdlib>
 #include <cstring>
 
+#include "moe_decode_units.cuh"
 #include "moe_route.cuh"
 #include "moe_sync.cuh"
 
 namespace uocr {
 
 constexpr int kSlThreads = 512;
-constexpr int kSlH = 1280, kSlF = 896, kSlS = 1792, kSlK = 6, kSlE = 64;
-constexpr int kSlRoutedPerSlot = kSlF / 64;                 // 14
 constexpr int kSlRouted = kSlK * kSlRoutedPerSlot;          // 84
 constexpr int kSlUnits = kSlRouted + kSlS / 64;             // 112 CTAs
-constexpr int kSlGroups = kSlH / 64;                        // 20 quantisation groups along H
 constexpr int kSlCluster = 4;                               // CTAs per cluster: each evaluates a quarter of the router
 constexpr int kSlChunks = 5;                                // gate/up fragments arrive in 5 copies of 4 groups
 constexpr int kSlAccBuffers = 4;
@@ -112,102 +110,6 @@ struct SlicedParamsInline : SlicedParams {
     static constexpr bool kInline = true;
     uint4 inline_x[kSlH * 2 / 16];  // fp16 activations
 };
-
-// ---------------------------------------------------------------- packed formats and the unit blob
-template <int QT> struct SlFmt;
-template <> struct SlFmt<UOCR_QT_Q4> {
-    static constexpr int kGroupBytes = 32, kLaneBytes = 8;             // of one row: per 64-wide group, per lane of a quad
-    static constexpr int kRowBytesH = kSlH / 2;
-};
-template <> struct SlFmt<UOCR_QT_Q8> {
-    static constexpr int kGroupBytes = 64, kLaneBytes = 16;
-    static constexpr int kRowBytesH = kSlH;
-};
-template <int QT> struct SlBlob {
-    static constexpr int kGu = 0;                                           // gate/up fragments
-    static constexpr int kGuBytes = 128 * SlFmt<QT>::kRowBytesH;
-    static constexpr int kGuSc = kGu + kGuBytes;                            // gate scales [64][20], up scales [64][20]
-    static constexpr int kGuScBytes = 2 * 64 * kSlGroups * 2;
-    static constexpr int kDn = kGuSc + kGuScBytes;                          // down fragments
-    static constexpr int kDnBytes = kSlH * SlFmt<QT>::kGroupBytes;
-    static constexpr int kDnSc = kDn + kDnBytes;                            // down scales [H]
-    static constexpr int kBytes = kDnSc + kSlH * 2;                         // Q4: 130560, Q8: 253440 (multiples of 256)
-};
-
-__device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
-                                         uint32_t b1) {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
-                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-
-__device__ __forceinline__ void imma_u8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
-    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
-                 : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-__device__ __forceinline__ void imma_s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
-    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
-                 : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-
-// One 64-wide group of two weight rows (lo: MMA rows 0-7, hi: MMA rows 8-15; this lane holds its 16 levels of
-// each) against the group's activation bytes xb: two MMAs, the first 32 columns of the group into accumulator a,
-// the other 32 into accumulator b, so that consecutive groups form two independent chains.  Which column sits in
-// which k slot follows from the packing; limb_column() below arranges the activation bytes to match.
-__device__ __forceinline__ void group_imma(int (&ca)[4], int (&cb)[4], const uint2 &lo, const uint2 &hi, const uint4 &xb) {   // Q4_0
-    constexpr uint32_t M = 0x0F0F0F0Fu;
-    imma_u8(ca, lo.x & M, hi.x & M, lo.y & M, hi.y & M, xb.x, xb.y);                                  // low nibbles
-    imma_u8(cb, (lo.x >> 4) & M, (hi.x >> 4) & M, (lo.y >> 4) & M, (hi.y >> 4) & M, xb.z, xb.w);      // high nibbles
-}
-__device__ __forceinline__ void group_imma(int (&ca)[4], int (&cb)[4], const uint4 &lo, const uint4 &hi, const uint4 &xb) {   // Q8_0
-    imma_s8(ca, lo.x, hi.x, lo.y, hi.y, xb.x, xb.y);
-    imma_s8(cb, lo.z, hi.z, lo.w, hi.w, xb.z, xb.w);
-}
-// first of the four consecutive columns (inside the group) behind activation word p = 4 t + 2 j + r of a group:
-// lane-in-quad t, MMA j of the group, B register r
-template <int QT>
-__device__ __forceinline__ int limb_column(int p) {
-    const int t = p >> 2, j = (p >> 1) & 1, r = p & 1;
-    return QT == UOCR_QT_Q4 ? 32 * j + 8 * t + 4 * r : 16 * t + 8 * j + 4 * r;
-}
-
-// Block-floating-point form of one 64-wide group of fp16 values, computed by 16 consecutive lanes (this lane: the
-// four values behind word p): a shared power-of-two scale 2^(e - 13) and signed 15-bit mantissas (exact for every
-// value within a factor 8 of the group's largest, rounded to 2^-14 of the largest's power of two otherwise), each
-// split into a signed low byte and a signed high byte (|high| <= 64).  msum is the sum of the group's mantissas.
-struct GroupLimbs {
-    uint32_t lo, hi;      // the low / high bytes of this lane's four values
-    float scale;
-    int msum;
-};
-template <int QT>
-__device__ __forceinline__ GroupLimbs group_limbs(const __half *group, int p) {
-    const uint2 raw = *reinterpret_cast<const uint2 *>(group + limb_column<QT>(p));
-    const float2 f01 = __half22float2(*reinterpret_cast<const __half2 *>(&raw.x));
-    const float2 f23 = __half22float2(*reinterpret_cast<const __half2 *>(&raw.y));
-    const float x[4] = {f01.x, f01.y, f23.x, f23.y};
-    float amax = fmaxf(fmaxf(fabsf(x[0]), fabsf(x[1])), fmaxf(fabsf(x[2]), fabsf(x[3])));
-#pragma unroll
-    for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o, 16));
-    // amax = 1.f * 2^e (fp16 values: e in [-24, 15]); up = 2^(13 - e), scale = 2^(e - 13); a group of zeros gets 0
-    const int e = (int)(__float_as_uint(amax) >> 23) - 127;
-    const bool live = amax > 0.f && amax < INFINITY;
-    const float up = live ? __uint_as_float((uint32_t)(127 + 13 - e) << 23) : 0.f;
-    GroupLimbs out;
-    out.lo = 0u; out.hi = 0u; out.msum = 0;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const int m = __float2int_rn(x[i] * up);          // |m| < 2^14
-        out.msum += m;
-        const int l0 = (int)((uint32_t)m << 24) >> 24, l1 = (m - l0) >> 8;
-        out.lo |= (uint32_t)(l0 & 0xff) << (8 * i);
-        out.hi |= (uint32_t)(l1 & 0xff) << (8 * i);
-    }
-#pragma unroll
-    for (int o = 8; o > 0; o >>= 1) out.msum += __shfl_xor_sync(0xffffffffu, out.msum, o, 16);
-    out.scale = live ? __uint_as_float((uint32_t)(127 - 13 + e) << 23) : 0.f;
-    return out;
-}
 
 __device__ __forceinline__ void red_add_u64(unsigned long long *p, unsigned long long v) {
     asm volatile("red.relaxed.gpu.global.add.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
@@ -258,10 +160,10 @@ template <int QT> struct SlSmem {
     static constexpr int kSc = kW + SlBlob<QT>::kGuBytes;               // gate scales [64][20], up scales [64][20] (fp16)
     static constexpr int kX = kSc + SlBlob<QT>::kGuScBytes;             // activations, fp16 natural order
     static constexpr int kXf = kX + kSlH * 2;                           // activation bytes [20][8][16 words]
-    static constexpr int kXs = kXf + kSlGroups * 8 * 16 * 4;            // [20] {group scale, offset correction}
+    static constexpr int kXs = kXf + kSlGroups * 8 * 16 * 4;            // [20] group scales (Q4_0: with the 1/16 of the level bytes)
     static constexpr int kGu = kXs + 256;                               // [2][128] partial gate / up sums of the two warp halves
     static constexpr int kMid = kGu + 2 * 128 * 4;                      // [64] fp16 SwiGLU products
-    static constexpr int kMidf = kMid + 128;                            // their bytes [4][8][16 words], then scale, correction
+    static constexpr int kMidf = kMid + 128;                            // their bytes [4][8][16 words], then the scale
     static constexpr int kRp = kMidf + 4 * 8 * 16 * 4 + 64;             // [16 warps][16 experts] partial router logits
     static constexpr int kLogits = kRp + 4 * 64 * 4;                    // [64]
     static constexpr int kProbs = kLogits + 256;                        // [64]
@@ -286,11 +188,10 @@ __global__ void __launch_bounds__(kSlThreads, 1) decode_sliced_kernel(const __gr
     __half *s_sc = reinterpret_cast<__half *>(smem + Sm::kSc);
     __half *s_x = reinterpret_cast<__half *>(smem + Sm::kX);
     uint32_t *s_xf = reinterpret_cast<uint32_t *>(smem + Sm::kXf);
-    float2 *s_xsnc = reinterpret_cast<float2 *>(smem + Sm::kXs);         // [20] {scale, -8 * sum of mantissas (Q4_0) or 0}
+    float *s_xs = reinterpret_cast<float *>(smem + Sm::kXs);             // [20] group scales
     float *s_gu = reinterpret_cast<float *>(smem + Sm::kGu);
-    __half *s_mid = reinterpret_cast<__half *>(smem + Sm::kMid);
     uint32_t *s_midf = reinterpret_cast<uint32_t *>(smem + Sm::kMidf);   // [4][8][16 words]
-    float *s_mscale = reinterpret_cast<float *>(s_midf + 4 * 8 * 16);    // scale, correction
+    float *s_mscale = reinterpret_cast<float *>(s_midf + 4 * 8 * 16);    // scale
     float *s_rp = reinterpret_cast<float *>(smem + Sm::kRp);
     float *s_logits = reinterpret_cast<float *>(smem + Sm::kLogits);
     float *s_probs = reinterpret_cast<float *>(smem + Sm::kProbs);
@@ -356,11 +257,13 @@ __global__ void __launch_bounds__(kSlThreads, 1) decode_sliced_kernel(const __gr
         const int bi = warp == 0 ? tid : tid - 32;
         if (warp != 1 && bi < kSlGroups * 16) {                         // 16 lanes per group
             const int Gi = bi >> 4, p = bi & 15;
-            const GroupLimbs L = group_limbs<QT>(s_x + Gi * 64, p);
+            float xv[4];
+            load_word_values<QT>(s_x + Gi * 64, p, xv);
+            const GroupLimbs L = group_limbs(xv);
             uint32_t *d = s_xf + (Gi * 8 + 2 * (Gi & 3)) * 16 + p;
             d[0] = L.lo;
             d[16] = L.hi;
-            if (p == 0) s_xsnc[Gi] = make_float2(L.scale, QT == UOCR_QT_Q4 ? -8.f * (float)L.msum : 0.f);
+            if (p == 0) s_xs[Gi] = QT == UOCR_QT_Q4 ? L.scale * kQ4LevelScale : L.scale;
         }
     };
     // Prefetched into registers: this warp's 5 blocks of 16 `down` rows (the unit's 64 columns of each) with the
@@ -376,12 +279,14 @@ __global__ void __launch_bounds__(kSlThreads, 1) decode_sliced_kernel(const __gr
     auto fetch_gate_up = [&](const uint8_t *blob) {
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         if (tid == 0) {
-            mbar_expect_tx(sc_bar, Bl::kGuScBytes);
-            bulk_g2s(s_sc, blob + Bl::kGuSc, Bl::kGuScBytes, sc_bar);
 #pragma unroll
             for (int c = 0; c < kSlChunks; ++c) {
                 mbar_expect_tx(&bars[c], kChunkBytes);
                 bulk_g2s(smem + Sm::kW + c * kChunkBytes, blob + Bl::kGu + (size_t)c * kChunkBytes, kChunkBytes, &bars[c]);
+                if (c == 1) {          // the scales are first needed after the MMAs of the first two chunks
+                    mbar_expect_tx(sc_bar, Bl::kGuScBytes);
+                    bulk_g2s(s_sc, blob + Bl::kGuSc, Bl::kGuScBytes, sc_bar);
+                }
             }
         }
     };
@@ -536,58 +441,59 @@ __global__ void __launch_bounds__(kSlThreads, 1) decode_sliced_kernel(const __gr
             // groups (= one chunk of the copy) per accumulator set, as the copies land: warps kh = 0 take chunks 0 and
             // 2, warps kh = 1 chunks 1 and 3, and the last chunk is split between them so that all sixteen work on it.
             const int rb = warp & 7, kh = warp >> 3;
-            bool got = mbar_wait(sc_bar, copy_phase, status, s_flag);
+            bool got = true;
             float sg = 0.f, su = 0.f;
             const __half *scg = s_sc + (8 * rb + g) * kSlGroups;
             const __half *scu = scg + 64 * kSlGroups;
-            // groups G0 + QLO .. G0 + QHI - 1 (G0 a multiple of 4) into one accumulator set; lane-in-quad q then
-            // holds group G0 + q: its low-byte and high-byte dot products with gate row g (c[0], c[1]) and up row g
-            // (c[2], c[3])
-            auto quad = [&](int G0, auto qlo, auto qhi) {
+            // groups G0 + QLO .. G0 + QHI - 1 (G0 a multiple of 4) into one accumulator set (four accumulators: chains
+            // of at most two dependent MMAs); lane-in-quad q then holds group G0 + q: its low-byte and high-byte dot
+            // products with gate row g (c[0], c[1]) and up row g (c[2], c[3])
+            auto quad = [&](int G0, auto qlo, auto qhi, bool wait_scales) {
                 constexpr int QLO = decltype(qlo)::value, QHI = decltype(qhi)::value;
-                int ca[4] = {0, 0, 0, 0}, cb[4] = {0, 0, 0, 0};
+                int ca[2][4] = {{0, 0, 0, 0}, {0, 0, 0, 0}}, cb[2][4] = {{0, 0, 0, 0}, {0, 0, 0, 0}};
 #pragma unroll
                 for (int q = QLO; q < QHI; ++q) {
                     const int Gi = G0 + q;
                     const uint4 xb = *reinterpret_cast<const uint4 *>(s_xf + ((Gi * 8 + g) * 4 + t) * 4);
                     if (QT == UOCR_QT_Q8) {
                         const uint4 a = s_w4[((Gi * 8 + rb) * 2) * 32 + lane], b = s_w4[((Gi * 8 + rb) * 2 + 1) * 32 + lane];
-                        group_imma(ca, cb, a, b, xb);
+                        group_imma(ca[q & 1], cb[q & 1], a, b, xb);
                     } else {
                         const uint4 v = s_w4[(Gi * 8 + rb) * 32 + lane];       // gate: .x .y, up: .z .w
-                        group_imma(ca, cb, make_uint2(v.x, v.y), make_uint2(v.z, v.w), xb);
+                        group_imma(ca[q & 1], cb[q & 1], make_uint2(v.x, v.y), make_uint2(v.z, v.w), xb);
                     }
                 }
+                if (wait_scales) got = mbar_wait(sc_bar, copy_phase, status, s_flag) && got;
                 if (t >= QLO && t < QHI) {
                     const int Gi = G0 + t;
-                    const float2 xc = s_xsnc[Gi];
-                    const float vg = (float)(ca[0] + cb[0] + ((ca[1] + cb[1]) * 256)) + xc.y;
-                    const float vu = (float)(ca[2] + cb[2] + ((ca[3] + cb[3]) * 256)) + xc.y;
-                    sg = fmaf(vg, __half2float(scg[Gi]) * xc.x, sg);
-                    su = fmaf(vu, __half2float(scu[Gi]) * xc.x, su);
+                    const float xs = s_xs[Gi];
+                    const float vg = (float)(ca[0][0] + cb[0][0] + ca[1][0] + cb[1][0] + (ca[0][1] + cb[0][1] + ca[1][1] + cb[1][1]) * 256);
+                    const float vu = (float)(ca[0][2] + cb[0][2] + ca[1][2] + cb[1][2] + (ca[0][3] + cb[0][3] + ca[1][3] + cb[1][3]) * 256);
+                    sg = fmaf(vg, __half2float(scg[Gi]) * xs, sg);
+                    su = fmaf(vu, __half2float(scu[Gi]) * xs, su);
                 }
             };
             if (kh == 0) {
                 got = mbar_wait(&bars[0], copy_phase, status, s_flag) && got;
                 UOCR_SL_TRACE(3);              // first chunk is in shared memory
                 if (routed) fetch_down(blob);
-                quad(0, SlInt<0>{}, SlInt<4>{});
+                quad(0, SlInt<0>{}, SlInt<4>{}, true);
                 UOCR_SL_TRACE(10);
                 got = mbar_wait(&bars[2], copy_phase, status, s_flag) && got;
                 UOCR_SL_TRACE(11);
-                quad(8, SlInt<0>{}, SlInt<4>{});
+                quad(8, SlInt<0>{}, SlInt<4>{}, false);
                 UOCR_SL_TRACE(12);
                 got = mbar_wait(&bars[4], copy_phase, status, s_flag) && got;
                 UOCR_SL_TRACE(13);
-                quad(16, SlInt<0>{}, SlInt<2>{});
+                quad(16, SlInt<0>{}, SlInt<2>{}, false);
             } else {
                 got = mbar_wait(&bars[1], copy_phase, status, s_flag) && got;
                 if (routed) fetch_down(blob);
-                quad(4, SlInt<0>{}, SlInt<4>{});
+                quad(4, SlInt<0>{}, SlInt<4>{}, true);
                 got = mbar_wait(&bars[3], copy_phase, status, s_flag) && got;
-                quad(12, SlInt<0>{}, SlInt<4>{});
+                quad(12, SlInt<0>{}, SlInt<4>{}, false);
                 got = mbar_wait(&bars[4], copy_phase, status, s_flag) && got;
-                quad(16, SlInt<2>{}, SlInt<4>{});
+                quad(16, SlInt<2>{}, SlInt<4>{}, false);
             }
             if (!got) { sg = 0.f; su = 0.f; }
             // the lanes of a quad hold different groups
@@ -614,42 +520,46 @@ __global__ void __launch_bounds__(kSlThreads, 1) decode_sliced_kernel(const __gr
         // accumulator set (block bi ends up in lane-in-quad bi), block 4 uses a second one (lane-in-quad 0).
         float v[4] = {0.f, 0.f, 0.f, 0.f};
         if (valid) {
-            if (tid < 64) {
-                const float gate = s_gu[tid] + s_gu[128 + tid], up = s_gu[64 + tid] + s_gu[192 + tid];
-                s_mid[tid] = __float2half_rn(silu_f32(gate) * up);
-            }
-            __syncthreads();
-            if (warp == 0) {          // both half-warps compute the same bytes; each writes two of the four copies
-                const int p = lane & 15, q0 = (lane >> 4) * 2;
-                const GroupLimbs M = group_limbs<QT>(s_mid, p);
+            // SwiGLU products and their bytes in one step by warp 0: lane p % 16 takes the four values behind word p
+            // (both half-warps compute the same; each writes two of the four copies)
+            if (warp == 0) {
+                const int p = lane & 15, q0 = (lane >> 4) * 2, c0 = limb_column<QT>(p);
+                const float4 g0 = *reinterpret_cast<const float4 *>(s_gu + c0), g1 = *reinterpret_cast<const float4 *>(s_gu + 128 + c0);
+                const float4 u0 = *reinterpret_cast<const float4 *>(s_gu + 64 + c0), u1 = *reinterpret_cast<const float4 *>(s_gu + 192 + c0);
+                const float gate[4] = {g0.x + g1.x, g0.y + g1.y, g0.z + g1.z, g0.w + g1.w};
+                const float up[4] = {u0.x + u1.x, u0.y + u1.y, u0.z + u1.z, u0.w + u1.w};
+                float mv[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) mv[i] = __half2float(__float2half_rn(silu_fast_f32(gate[i]) * up[i]));    // fp16, as every path stores them
+                const GroupLimbs M = group_limbs(mv);
 #pragma unroll
                 for (int q = q0; q < q0 + 2; ++q) {
                     uint32_t *d = s_midf + (q * 8 + 2 * q) * 16 + p;
                     d[0] = M.lo;
                     d[16] = M.hi;
                 }
-                if (lane == 0) { s_mscale[0] = M.scale; s_mscale[1] = QT == UOCR_QT_Q4 ? -8.f * (float)M.msum : 0.f; }
+                if (lane == 0) s_mscale[0] = QT == UOCR_QT_Q4 ? M.scale * kQ4LevelScale : M.scale;
             }
             __syncthreads();
             UOCR_SL_TRACE(4);     // SwiGLU products of the slice
-            const float ms = s_mscale[0] * weight, nc = s_mscale[1];
-            int ca[4] = {0, 0, 0, 0}, cb[4] = {0, 0, 0, 0}, cc[4] = {0, 0, 0, 0}, cd[4] = {0, 0, 0, 0};
+            const float ms = s_mscale[0] * weight;
+            int ca[2][4] = {{0, 0, 0, 0}, {0, 0, 0, 0}}, cb[2][4] = {{0, 0, 0, 0}, {0, 0, 0, 0}}, cc[4] = {0, 0, 0, 0}, cd[4] = {0, 0, 0, 0};
 #pragma unroll
             for (int bi = 0; bi < kSlBlocksPerWarp; ++bi) {
                 const int q = bi & 3;
                 const uint4 mbf = *reinterpret_cast<const uint4 *>(s_midf + ((q * 8 + g) * 4 + t) * 4);
                 if (bi < 4) {
-                    if (QT == UOCR_QT_Q8) group_imma(ca, cb, dwn[bi][0], dwn[bi][1], mbf);
-                    else group_imma(ca, cb, make_uint2(dwn[bi][0].x, dwn[bi][0].y), make_uint2(dwn[bi][0].z, dwn[bi][0].w), mbf);
+                    if (QT == UOCR_QT_Q8) group_imma(ca[bi & 1], cb[bi & 1], dwn[bi][0], dwn[bi][1], mbf);
+                    else group_imma(ca[bi & 1], cb[bi & 1], make_uint2(dwn[bi][0].x, dwn[bi][0].y), make_uint2(dwn[bi][0].z, dwn[bi][0].w), mbf);
                 } else {
                     if (QT == UOCR_QT_Q8) group_imma(cc, cd, dwn[bi][0], dwn[bi][1], mbf);
                     else group_imma(cc, cd, make_uint2(dwn[bi][0].x, dwn[bi][0].y), make_uint2(dwn[bi][0].z, dwn[bi][0].w), mbf);
                 }
             }
-            v[0] = ((float)(ca[0] + cb[0] + ((ca[1] + cb[1]) * 256)) + nc) * (__half2float(dsc4[0]) * ms);
-            v[1] = ((float)(ca[2] + cb[2] + ((ca[3] + cb[3]) * 256)) + nc) * (__half2float(dsc4[1]) * ms);
-            v[2] = ((float)(cc[0] + cd[0] + ((cc[1] + cd[1]) * 256)) + nc) * (__half2float(dsc4[2]) * ms);
-            v[3] = ((float)(cc[2] + cd[2] + ((cc[3] + cd[3]) * 256)) + nc) * (__half2float(dsc4[3]) * ms);
+            v[0] = (float)(ca[0][0] + cb[0][0] + ca[1][0] + cb[1][0] + (ca[0][1] + cb[0][1] + ca[1][1] + cb[1][1]) * 256) * (__half2float(dsc4[0]) * ms);
+            v[1] = (float)(ca[0][2] + cb[0][2] + ca[1][2] + cb[1][2] + (ca[0][3] + cb[0][3] + ca[1][3] + cb[1][3]) * 256) * (__half2float(dsc4[1]) * ms);
+            v[2] = (float)(cc[0] + cd[0] + (cc[1] + cd[1]) * 256) * (__half2float(dsc4[2]) * ms);
+            v[3] = (float)(cc[2] + cd[2] + (cc[3] + cd[3]) * 256) * (__half2float(dsc4[3]) * ms);
         } else {
             UOCR_SL_TRACE(3);
             UOCR_SL_TRACE(4);

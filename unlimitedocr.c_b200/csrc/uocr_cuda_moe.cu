@@ -39,6 +39,13 @@ cudaError_t launch_gemm_shared(const DLayer &L, const Scratch &S, const GemmScra
                                cudaStream_t st, uint64_t *launches);
 cudaError_t launch_gemm_combine(const DLayer &L, const Scratch &S, const GemmScratch &G, const __half *down_rows,
                                 const __half *residual, uint32_t n, __half *out, cudaStream_t st, uint64_t *launches);
+cudaError_t init_decode_batched_kernels();
+uint32_t decode_batched_max_tokens();
+size_t decode_batched_routed_part_bytes(uint32_t n, uint32_t K);
+size_t decode_batched_shared_part_bytes(uint32_t n);
+bool decode_batched_supported(const DLayer &L, uint32_t n);
+cudaError_t launch_decode_batched(const DLayer &L, const Scratch &S, const __half *hidden, const __half *residual, uint32_t n,
+                                  float *routed_part, float *shared_part, __half *out, cudaStream_t st, uint64_t *launches);
 cudaError_t launch_dequant_probe(const DMatrix &m, float *out, cudaStream_t st, uint64_t *launches);
 cudaError_t launch_producer_probe(const DMatrix &m, float *out, cudaStream_t st, uint64_t *launches);
 int decode_grid_size();
@@ -79,6 +86,7 @@ struct uocr_cuda_context {
     bool fused_decode = true;          // single-token calls use the persistent decode kernel when it fits
     uint32_t gemm_min_tokens = 5;      // calls with at least this many tokens take the tensor-core path
     bool sliced_decode = true;         // ... in its one-barrier-per-layer form when the shapes allow it
+    bool batched_decode = true;        // calls of a few tokens (up to 64) at the model's shapes use the weight-streaming kernel
     unsigned long long bar_base = 0;   // value the decode kernel's barrier counter has reached
     uint32_t acc_base = 0;             // accumulator buffer the next sliced decode launch starts with
     uocr::SlicedKnobs decode_knobs;    // replicas of the decode accumulator, wait limit
@@ -192,7 +200,8 @@ extern "C" uocr_cuda_context *uocr_cuda_context_create(const char *resource_path
         (e = cudaMallocHost(&ctx->h_seg, kSegSlots * 260 * sizeof(uint32_t))) != cudaSuccess ||
         (e = uocr::init_router_kernels()) != cudaSuccess || (e = uocr::init_small_batch_kernels()) != cudaSuccess ||
         (e = uocr::init_decode_kernels()) != cudaSuccess ||
-        (e = uocr::init_decode_sliced_kernels()) != cudaSuccess || (e = uocr::init_gemm_kernels()) != cudaSuccess) {
+        (e = uocr::init_decode_sliced_kernels()) != cudaSuccess || (e = uocr::init_decode_batched_kernels()) != cudaSuccess ||
+        (e = uocr::init_gemm_kernels()) != cudaSuccess) {
         fail(nullptr, error, error_size, "CUDA context set-up failed: %s", cudaGetErrorString(e));
         uocr_cuda_context_destroy(ctx);
         return nullptr;
@@ -210,6 +219,7 @@ extern "C" uocr_cuda_context *uocr_cuda_context_create(const char *resource_path
     ctx->fused_decode = !(off && off[0] == '1');
     const char *design = getenv("UOCR_CUDA_DECODE_DESIGN");      // "two-barrier": the earlier persistent kernel
     ctx->sliced_decode = !(design && strcmp(design, "two-barrier") == 0);   // (then no slice-major weight copy is made)
+    if (const char *b = getenv("UOCR_CUDA_DISABLE_BATCHED_DECODE")) ctx->batched_decode = !(b[0] == '1');
     if (const char *mt = getenv("UOCR_CUDA_GEMM_MIN_TOKENS")) ctx->gemm_min_tokens = (uint32_t)strtoul(mt, nullptr, 10);
     if (const char *r = getenv("UOCR_CUDA_DECODE_REPLICAS")) ctx->decode_knobs.replicas = (uint32_t)strtoul(r, nullptr, 10);
     if (const char *r = getenv("UOCR_CUDA_DECODE_POLL_SLEEP_NS")) ctx->decode_knobs.poll_sleep_ns = (uint32_t)strtoul(r, nullptr, 10);
@@ -451,7 +461,7 @@ extern "C" int uocr_cuda_context_map_moe_layer(uocr_cuda_context *ctx, const uoc
 struct ArenaLayout {
     uint64_t logits, probs, ids, weights, offsets, pair_rows, inverse, active, mid, shared_mid, down_out, shared_out,
         stack0, stack1, d_in, d_res, d_out, dec_mid, dec_plogits, x_sorted, tiles_gu, tiles_dn, stiles_gu, stiles_dn,
-        counts, plan_counts, seg_offsets, total;
+        counts, plan_counts, seg_offsets, bt_routed, bt_shared, total;
 };
 
 static ArenaLayout layout_arena(uint32_t H, uint32_t E, uint32_t K, uint32_t F, uint32_t S, uint32_t n) {
@@ -492,6 +502,11 @@ static ArenaLayout layout_arena(uint32_t H, uint32_t E, uint32_t K, uint32_t F, 
         a.counts = take(64);
         a.seg_offsets = take(260 * 4);        // expert-parallel experts phase: offsets of the received segments
         a.plan_counts = take((pairs / 2048 + 2) * E * 4);
+    }
+    {   // batched decode kernel: per-part partial outputs of the routed experts and the shared MLP (calls of up to 64 tokens)
+        const uint32_t nb = n < uocr::decode_batched_max_tokens() ? n : uocr::decode_batched_max_tokens();
+        a.bt_routed = take(uocr::decode_batched_routed_part_bytes(nb, K));
+        a.bt_shared = take(uocr::decode_batched_shared_part_bytes(nb));
     }
     a.total = off;
     return a;
@@ -678,6 +693,15 @@ static int layer_forward(uocr_cuda_context *ctx, uint32_t layer, const __half *d
                                               (float *)(ctx->arena + a.dec_plogits), barrier_counter(ctx), &ctx->bar_base,
                                               ctx->status, logits, probs, s.top_ids, s.top_weights, nullptr, ctx->stream,
                                               &ctx->launches));
+    } else if (n >= 2 && ctx->batched_decode && uocr::decode_batched_supported(L, n)) {
+        // a few tokens at the model's shapes: router, plan, then ONE weight-streaming kernel for the routed experts and
+        // the shared MLP, and the combine
+        CU_TRY(ctx, uocr::launch_router(L, d_hidden, d_injected, n, logits, probs, s.top_ids, s.top_weights, ctx->status,
+                                        s.logits, ctx->stream, &ctx->launches));
+        CU_TRY(ctx, uocr::launch_dispatch_plan(s.top_ids, n, L.K, L.E, s.expert_offsets, s.pair_rows, s.inverse,
+                                               s.active, nullptr, ctx->stream, &ctx->launches));
+        CU_TRY(ctx, uocr::launch_decode_batched(L, s, d_hidden, d_residual, n, (float *)(ctx->arena + a.bt_routed),
+                                                (float *)(ctx->arena + a.bt_shared), d_out, ctx->stream, &ctx->launches));
     } else if (n >= ctx->gemm_min_tokens && uocr::gemm_path_supported(L)) {
         // The shared MLP needs neither the routing nor the permutation: it runs on a second stream beside the router,
         // the dispatch plan, the gather and the routed experts, whose small kernels leave most SMs idle.
@@ -707,6 +731,19 @@ static int layer_forward(uocr_cuda_context *ctx, uint32_t layer, const __half *d
     if (dbg && dbg->d_top_weights)
         CU_TRY(ctx, cudaMemcpyAsync(dbg->d_top_weights, s.top_weights, (size_t)n * L.K * 4, cudaMemcpyDeviceToDevice, ctx->stream));
     return 1;
+}
+
+extern "C" const char *uocr_cuda_moe_regime_name(const uocr_cuda_context *ctx, uint32_t layer, uint32_t n) {
+    if (!ctx || layer >= ctx->layers.size() || n == 0) return "";
+    const DLayer &L = ctx->layers[layer];
+    if (n == 1 && ctx->fused_decode && ctx->sliced_decode && uocr::decode_sliced_supported(ctx->layers.data(), layer, 1))
+        return "single-token decode kernel (decode_sliced_kernel)";
+    if (n == 1 && ctx->fused_decode && uocr::decode_supported(ctx->layers.data(), layer, 1))
+        return "single-token decode kernel, two-barrier form (decode_stack_kernel)";
+    if (n >= 2 && ctx->batched_decode && uocr::decode_batched_supported(L, n))
+        return "weight-streaming batched decode kernel (decode_batched_kernel)";
+    if (n >= ctx->gemm_min_tokens && uocr::gemm_path_supported(L)) return "grouped GEMM on tensor cores (grouped_gemm_kernel)";
+    return "matrix-vector kernels (gate_up_kernel, down_kernel)";
 }
 
 extern "C" int uocr_cuda_moe_layer_forward(uocr_cuda_context *ctx, uint32_t layer, const void *d_hidden,

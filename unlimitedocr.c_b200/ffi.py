@@ -50,7 +50,7 @@ EXPORTS = (
     "uocr_cuda_context_moe_scratch_bytes", "uocr_cuda_context_map_moe_layer", "uocr_cuda_context_unmap_model",
     "uocr_cuda_context_moe_layer_count", "uocr_cuda_context_allocate_runtime_arenas",
     "uocr_cuda_context_release_runtime_arenas", "uocr_cuda_moe_scratch_size", "uocr_cuda_moe_router",
-    "uocr_cuda_moe_dispatch_plan", "uocr_cuda_moe_dispatch_plan_noalloc", "uocr_cuda_moe_debug_dequantize", "uocr_cuda_moe_layer_forward", "uocr_cuda_moe_stack_forward",
+    "uocr_cuda_moe_dispatch_plan", "uocr_cuda_moe_dispatch_plan_noalloc", "uocr_cuda_moe_debug_dequantize", "uocr_cuda_moe_regime_name", "uocr_cuda_moe_layer_forward", "uocr_cuda_moe_stack_forward",
     "uocr_cuda_moe_layer_forward_host", "uocr_cuda_moe_stack_forward_host",
     "uocr_cuda_moe_ep_dispatch", "uocr_cuda_moe_ep_experts", "uocr_cuda_moe_ep_shared", "uocr_cuda_moe_ep_combine",
     "uocr_cuda_moe_ep_peer_create", "uocr_cuda_moe_ep_peer_open", "uocr_cuda_moe_ep_peer_destroy",
@@ -102,6 +102,7 @@ def load_library() -> C.CDLL:
         "uocr_cuda_moe_dispatch_plan": (C.c_int, [vp, vp, u32, u32, u32, vp, vp, vp] + err),
         "uocr_cuda_moe_dispatch_plan_noalloc": (C.c_int, [vp, u32, u32, u32, vp, vp, vp, vp] + err),
         "uocr_cuda_moe_debug_dequantize": (C.c_int, [vp, u32, u32, u32, u32, vp] + err),
+        "uocr_cuda_moe_regime_name": (cp, [vp, u32, u32]),
         "uocr_cuda_moe_layer_forward": (C.c_int, [vp, u32, vp, vp, vp, u32, vp, C.POINTER(CDebugOutputs)] + err),
         "uocr_cuda_moe_stack_forward": (C.c_int, [vp, u32, u32, vp, u32, vp] + err),
         "uocr_cuda_moe_layer_forward_host": (C.c_int, [vp, u32, vp, vp, u32, vp, vp, vp] + err),
@@ -284,6 +285,10 @@ class Context:
         """Weights of one projection as the kernels see them (f32 [rows, cols] device tensor); see the header."""
         self._check(self._lib.uocr_cuda_moe_debug_dequantize(self._h, layer, matrix, expert, path, _dev_ptr(out),
                                                              self._err, _ERR))
+
+    def regime_name(self, layer: int, n_tokens: int) -> str:
+        """The kernels a layer call with n_tokens tokens would run."""
+        return self._lib.uocr_cuda_moe_regime_name(self._h, layer, n_tokens).decode()
 
     def layer_forward(self, layer: int, hidden, n_tokens: int, out, *, residual=None, injected_logits=None,
                       logits=None, probs=None, top_ids=None, top_weights=None) -> None:
