@@ -178,6 +178,9 @@ struct SlicedKnobs {
                                       // more than there are CTAs, so it runs into its limit
 };
 
+// Byte offsets inside the scratch region of the batched decode path.
+struct BatchedScratchLayout { size_t routed_part, shared_part, x_limbs, x_scales, total; };
+
 // ---- launch interface (implemented in the kernel files, called by the host API) ----------
 struct LaunchCounter { uint64_t *count; };
 

@@ -1,26 +1,33 @@
-// Batched decode: a handful to a few dozen tokens per step (5 .. 64) at the model's shapes, Q4_0 / Q8_0.
+// Batched decode: a few to a few dozen tokens per step (2 .. 64) at the model's shapes, Q4_0 / Q8_0.
 //
-// Such a step is bound by reading the weights of the experts it selects, once each, so the kernel is
-// weight-stationary on the slice-major "unit blobs" of the single-token decode kernel: one CTA takes two
-// consecutive 64-wide slices of the intermediate dimension of ONE selected expert (or of the shared MLP) and
-// multiplies them with all tokens routed to that expert, 16 tokens per pass:
-//   1. the pass's activations are written as block-floating-point bytes (two signed bytes per value, one scale per
-//      token and 64-wide group), the B operand of the integer MMAs;
-//   2. per slice the 128 gate / up rows stream through a four-stage ring of bulk copies (one chunk = four
-//      quantisation groups), each chunk multiplied with up to 16 tokens: a token occupies two of the MMA's eight
-//      columns, so one MMA covers four tokens;
-//   3. the SwiGLU products never leave the SM: they are rounded to fp16, rewritten as bytes, and multiplied with the
-//      slice's 64 columns of `down` (held in registers);
-//   4. the slice's partial outputs go to a per-part buffer ([part][row][H], f32; the CTA's second slice adds to its
-//      first), and the combine kernel adds the parts in a fixed order, applies the routing weights in slot order, adds
-//      the shared MLP and the residual and rounds to fp16: bit-reproducible, no atomics.
-// An expert with more than 16 tokens is processed in several passes (its weights then come from L2).
+// Such a step is bound by reading the weights of the experts it selects, once each.  Three launches:
+//
+// 1. route_small_kernel, one CTA per token: the 64 router logits (all loads of a warp's eight experts in flight at
+//    once), the exact softmax / top-k, and the token's activations rewritten as block-floating-point bytes (two
+//    signed bytes per value, one scale per 64-wide group) - the B operand of the integer MMAs, computed once per
+//    token instead of once per expert that uses it.  The CTA that finishes last builds the dispatch plan (a stable
+//    counting sort of the at most 384 pairs).
+// 2. decode_batched_kernel, weight-stationary on the slice-major "unit blobs" of the single-token decode kernel.  A
+//    work item is (expert, 16-token pass, two consecutive 64-wide slices of the intermediate dimension); the shared
+//    MLP counts as two more experts that every token selects.  Items are listed hottest expert first and dealt
+//    round-robin to one CTA per SM.  Per item the pass's activation bytes are copied into shared memory, then per slice
+//    the 128 gate / up rows stream through a four-stage ring of bulk copies (one chunk = four quantisation groups) and
+//    are multiplied with up to 16 tokens (a token occupies two of the MMA's eight columns, so one MMA covers four
+//    tokens); the SwiGLU products never leave the SM: rounded to fp16, rewritten as bytes, multiplied with the
+//    slice's 64 columns of `down` (held in registers).  The slice's partial outputs go to a per-part buffer
+//    ([part][row][H], f32; the item's second slice adds to its first).
+// 3. combine_batched_kernel adds the parts in a fixed order, applies the routing weights in slot order, adds the shared
+//    MLP and the residual and rounds to fp16.  No atomics on data: results are bit-reproducible.
+//
 // Rounding contract as the single-token kernel: fp16 activations, scale applied per group partial, fp16 SwiGLU
 // products, f32 routed sum (src/backend/metal/kernels/decode_gemv_q8.metal:166-251).
 // Every wait is bounded (moe_sync.cuh).
 #include <cuda.h>
 
+#include <atomic>
+
 #include "moe_decode_units.cuh"
+#include "moe_route.cuh"
 #include "moe_sync.cuh"
 
 namespace uocr {
@@ -28,24 +35,161 @@ namespace uocr {
 constexpr int kBtConsumers = 512;                              // 16 warps compute
 constexpr int kBtThreads = kBtConsumers + 32;                  // + one warp that issues the bulk copies
 constexpr int kBtTokens = 16;                                  // tokens per pass
-constexpr int kBtSlices = 2;                                   // consecutive slices per CTA
-constexpr int kBtRoutedParts = kSlRoutedPerSlot / kBtSlices;   // 7 CTAs per selected expert
-constexpr int kBtSharedParts = kSlS / 64 / kBtSlices;          // 14 CTAs for the shared MLP
+constexpr int kBtSlices = 2;                                   // consecutive slices per item
+constexpr int kBtParts = kSlRoutedPerSlot / kBtSlices;         // 7 items per (expert, pass)
+constexpr int kBtSharedHalves = kSlS / 64 / kSlRoutedPerSlot;  // the shared MLP as 2 pseudo-experts of 14 slices
+constexpr int kBtEntries = kSlE + kBtSharedHalves;             // 66
 constexpr int kBtStages = 4;
 constexpr int kBtChunks = 5;                                   // chunks of four groups per slice
 constexpr int kBtMaxTokens = 64;
 constexpr int kBtBlocksPerWarp = kSlH / 16 / 16;               // 5 blocks of 16 `down` rows per warp
+constexpr int kBtTokenLimbBytes = kSlGroups * 2 * 64;          // 2560: a token's activation bytes [20][2][16 words]
 
-struct BatchedParams {
-    const uint8_t *units;             // slice-major weights of the layer
-    const __half *hidden;             // [n][H]
+// ---------------------------------------------------------------- 1. routing, activation bytes, dispatch plan
+constexpr int kRsThreads = 256;
+
+struct RouteSmallParams {
+    const __half *hidden;           // [n][H]
+    const __half *router;           // [E][H]
+    const float *bias;              // [E] or null
+    const float *injected;          // [n][E] logits to use instead of the dot products, or null
     uint32_t n, K;
-    uint32_t max_groups;              // selected experts the grid has CTAs for
+    float scaling;
+    float *logits_out, *probs_out;  // optional [n][E]
+    uint32_t *ids;                  // [n][K]
+    float *weights;                 // [n][K]
+    uint32_t *x_limbs;              // [n][20][2][16 words]
+    float *x_scales;                // [n][20]
+    uint32_t *offsets, *pair_rows, *inverse, *active;      // the dispatch plan
+    uint32_t *ticket;               // zero between launches
+    uint32_t *status;
+};
+
+template <int QT>
+__global__ void __launch_bounds__(kRsThreads) route_small_kernel(const RouteSmallParams prm) {
+    constexpr int H = kSlH, E = kSlE;
+    __shared__ __align__(16) __half s_x[H];
+    __shared__ float s_logits[E], s_probs[E];
+    __shared__ uint64_t s_tab[UOCR_EXPF_N];
+    __shared__ uint32_t s_last;
+    __shared__ uint32_t s_ids[kBtMaxTokens * 16];            // the plan: every pair's expert (K <= 16)
+    __shared__ uint32_t s_cnt[E + 1];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const uint32_t token = blockIdx.x, K = prm.K;
+    if (tid < UOCR_EXPF_N) s_tab[tid] = c_exp_tab[tid];
+    if (tid < H / 8) reinterpret_cast<uint4 *>(s_x)[tid] = __ldg(reinterpret_cast<const uint4 *>(prm.hidden + (size_t)token * H) + tid);
+    __syncthreads();
+
+    if (prm.injected != nullptr) {
+        if (tid < E) s_logits[tid] = prm.injected[(size_t)token * E + tid] + (prm.bias ? prm.bias[tid] : 0.f);
+    } else {
+        // warp w: experts 8w .. 8w + 7, four at a time; lane: the 16-byte chunks lane, lane + 32, ... of every row, all
+        // 20 loads of a batch in flight before the first is used
+        float xv[5][8];
+#pragma unroll
+        for (int i = 0; i < 5; ++i) {
+            const uint4 xr = reinterpret_cast<const uint4 *>(s_x)[lane + 32 * i];
+            const __half2 *xh = reinterpret_cast<const __half2 *>(&xr);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) { const float2 f = __half22float2(xh[k]); xv[i][2 * k] = f.x; xv[i][2 * k + 1] = f.y; }
+        }
+#pragma unroll
+        for (int b = 0; b < 2; ++b) {
+            uint4 wv[4][5];
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+#pragma unroll
+                for (int i = 0; i < 5; ++i)
+                    wv[j][i] = __ldg(reinterpret_cast<const uint4 *>(prm.router + (size_t)(8 * warp + 4 * b + j) * H) + lane + 32 * i);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                float acc = 0.f;
+#pragma unroll
+                for (int i = 0; i < 5; ++i) {
+                    const __half2 *wh = reinterpret_cast<const __half2 *>(&wv[j][i]);
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        const float2 f = __half22float2(wh[k]);
+                        acc = fmaf(f.x, xv[i][2 * k], acc);
+                        acc = fmaf(f.y, xv[i][2 * k + 1], acc);
+                    }
+                }
+                acc = warp_sum(acc);
+                const int e = 8 * warp + 4 * b + j;
+                if (lane == 0) s_logits[e] = prm.bias ? acc + prm.bias[e] : acc;
+            }
+        }
+    }
+    __syncthreads();
+    if (warp == 0) {
+        const bool bad = route_row_warp(s_logits, s_probs, E, K, prm.scaling, lane, s_tab,
+                                        prm.logits_out ? prm.logits_out + (size_t)token * E : nullptr,
+                                        prm.probs_out ? prm.probs_out + (size_t)token * E : nullptr, prm.ids + (size_t)token * K,
+                                        prm.weights + (size_t)token * K);
+        if (bad && lane == 0) atomicOr(prm.status, 1u);
+    } else {
+        // the token's activations as bytes: 16 lanes per group, warps 1 .. 7 (14 half-warps) over the 20 groups
+        for (int Gi = (warp - 1) * 2 + (lane >> 4); Gi < kSlGroups; Gi += 14) {
+            const int p = lane & 15;
+            float xv[4];
+            load_word_values<QT>(s_x + Gi * 64, p, xv);
+            const GroupLimbs L = group_limbs16(xv, (lane & 16) ? 0xffff0000u : 0x0000ffffu);
+            uint32_t *d = prm.x_limbs + ((size_t)token * kSlGroups + Gi) * 32 + p;
+            d[0] = L.lo;
+            d[16] = L.hi;
+            if (p == 0) prm.x_scales[(size_t)token * kSlGroups + Gi] = QT == UOCR_QT_Q4 ? L.scale * kQ4LevelScale : L.scale;
+        }
+    }
+    // ---- the CTA that finishes last builds the dispatch plan
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) s_last = atomicAdd(prm.ticket, 1u) == prm.n - 1u ? 1u : 0u;
+    __syncthreads();
+    if (s_last == 0u) return;
+    __threadfence();
+    const uint32_t pairs = prm.n * K;
+    for (uint32_t p = tid; p < pairs; p += kRsThreads) s_ids[p] = __ldcg(prm.ids + p);
+    __syncthreads();
+    if (tid < E) {
+        uint32_t c = 0;
+        for (uint32_t p = 0; p < pairs; ++p) c += s_ids[p] == (uint32_t)tid ? 1u : 0u;
+        s_cnt[tid] = c;
+    }
+    __syncthreads();
+    if (tid == 0) {
+        uint32_t run = 0, na = 0;
+        for (int e = 0; e < E; ++e) {
+            const uint32_t c = s_cnt[e];
+            s_cnt[e] = run;
+            prm.offsets[e] = run;
+            if (c) prm.active[1 + na++] = (uint32_t)e;
+            run += c;
+        }
+        prm.offsets[E] = run;
+        prm.active[0] = na;
+        *prm.ticket = 0u;
+    }
+    __syncthreads();
+    if (tid < E) {                              // expert e lists its pairs in ascending order: the stable sort
+        uint32_t pos = s_cnt[tid];
+        for (uint32_t p = 0; p < pairs; ++p)
+            if (s_ids[p] == (uint32_t)tid) { prm.pair_rows[pos] = p; prm.inverse[p] = pos; ++pos; }
+    }
+    for (uint32_t p = tid; p < pairs; p += kRsThreads)
+        if (s_ids[p] >= (uint32_t)E) prm.inverse[p] = 0xffffffffu;
+}
+
+// ---------------------------------------------------------------- 2. routed experts and shared MLP
+struct BatchedParams {
+    const uint8_t *units;             // slice-major weights of the layer: unit = expert * 14 + slice (shared MLP: experts 64, 65)
+    const uint32_t *x_limbs;          // [n][20][2][16 words]
+    const float *x_scales;            // [n][20]
+    uint32_t n, K;
     const uint32_t *active;           // [0] = number of experts with at least one pair, then their ids
     const uint32_t *expert_offsets;   // [E + 1]
     const uint32_t *pair_rows;        // pairs grouped by expert
-    float *routed_part;               // [kBtRoutedParts][n * K][H], row = position in pair_rows
-    float *shared_part;               // [kBtSharedParts][n][H]
+    float *routed_part;               // [kBtParts][n * K][H], row = position in pair_rows
+    float *shared_part;               // [kBtSharedHalves * kBtParts][n][H]
     uint32_t *status;
 };
 
@@ -54,12 +198,14 @@ template <int QT> struct BtSmem {
     static constexpr int kRing = 0;
     static constexpr int kSc = kRing + kBtStages * kChunkBytes;             // two buffers of gate / up scales
     static constexpr int kXf = kSc + 2 * SlBlob<QT>::kGuScBytes;            // activation bytes [16 tok][20][2][16 words]
-    static constexpr int kXs = kXf + kBtTokens * kSlGroups * 2 * 64;        // their scales [16 tok][20]
+    static constexpr int kXs = kXf + kBtTokens * kBtTokenLimbBytes;         // their scales [16 tok][20]
     static constexpr int kMid = kXs + kBtTokens * kSlGroups * 4;            // SwiGLU products [16 tok][64] fp16
     static constexpr int kMidf = kMid + kBtTokens * 64 * 2;                 // their bytes [16 tok][2][16 words]
     static constexpr int kMs = kMidf + kBtTokens * 2 * 64;                  // their scales [16]
     static constexpr int kTok = kMs + 64;                                   // token of each slot of the pass [16]
-    static constexpr int kBars = kTok + 64;                                 // full[4], empty[4], sc_full[2], sc_empty[2], flags
+    static constexpr int kEntry = kTok + 64;                                // entries (expert ids), most tokens first [66]
+    static constexpr int kFirst = kEntry + 68 * 4;                          // first (entry, pass) index of each entry [67]
+    static constexpr int kBars = kFirst + 68 * 4;                           // full[4], empty[4], sc_full[2], sc_empty[2], flags
     static constexpr int kTotal = kBars + 128;
 };
 
@@ -67,6 +213,11 @@ __device__ __forceinline__ void bt_sync() { asm volatile("bar.sync 1, %0;" ::"n"
 __device__ __forceinline__ void bt_arrive(uint64_t *bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
+
+// one work item: an entry (expert or shared half), a 16-token pass, a part (two slices)
+struct BtItem {
+    uint32_t expert, part, row0, p0, T;
+};
 
 template <int QT>
 __global__ void __launch_bounds__(kBtThreads, 1) decode_batched_kernel(const __grid_constant__ BatchedParams prm) {
@@ -82,36 +233,16 @@ __global__ void __launch_bounds__(kBtThreads, 1) decode_batched_kernel(const __g
     uint32_t *s_midf = reinterpret_cast<uint32_t *>(smem + Sm::kMidf);
     float *s_ms = reinterpret_cast<float *>(smem + Sm::kMs);
     uint32_t *s_tok = reinterpret_cast<uint32_t *>(smem + Sm::kTok);
+    uint32_t *s_entry = reinterpret_cast<uint32_t *>(smem + Sm::kEntry);
+    uint32_t *s_first = reinterpret_cast<uint32_t *>(smem + Sm::kFirst);
     uint64_t *full = reinterpret_cast<uint64_t *>(smem + Sm::kBars), *empty = full + kBtStages, *sc_full = empty + kBtStages,
              *sc_empty = sc_full + 2;
     int *s_flag = reinterpret_cast<int *>(sc_empty + 2);
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
-
-    // ---- which unit: (selected expert, part) or (shared MLP, part)
-    const uint32_t routed_ctas = prm.max_groups * kBtRoutedParts;
-    const bool routed = blockIdx.x < routed_ctas;
-    uint32_t expert = 0, part, cnt, row0, rows_total;
-    if (routed) {
-        const uint32_t group = blockIdx.x / kBtRoutedParts;
-        part = blockIdx.x % kBtRoutedParts;
-        if (group >= prm.active[0]) return;                       // fewer distinct experts than the grid allows for
-        expert = prm.active[1 + group];
-        row0 = prm.expert_offsets[expert];
-        cnt = prm.expert_offsets[expert + 1] - row0;
-        rows_total = prm.n * prm.K;
-    } else {
-        part = blockIdx.x - routed_ctas;
-        row0 = 0;
-        cnt = prm.n;
-        rows_total = prm.n;
-    }
-    if (cnt == 0) return;
-    const uint32_t first_unit = routed ? expert * kSlRoutedPerSlot + part * kBtSlices
-                                       : (uint32_t)kSlE * kSlRoutedPerSlot + part * kBtSlices;
-    float *out_base = (routed ? prm.routed_part : prm.shared_part) + (size_t)part * rows_total * H;
-    const uint32_t passes = (cnt + kBtTokens - 1) / kBtTokens;
+    const uint32_t n_active = prm.active[0];
+    const uint32_t n_entries = n_active + kBtSharedHalves;
 
     if (tid == 0) {
         for (int i = 0; i < kBtStages; ++i) { mbar_init(&full[i], 1); mbar_init(&empty[i], kBtConsumers / 32); }
@@ -119,13 +250,49 @@ __global__ void __launch_bounds__(kBtThreads, 1) decode_batched_kernel(const __g
         s_flag[0] = 1; s_flag[1] = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
+    // the entries ordered by their number of tokens, most first (the shared halves lead: every token takes them; then
+    // the selected experts, ties by id): rank by counting
+    auto entry_count = [&](uint32_t e) { return e >= (uint32_t)kSlE ? prm.n : prm.expert_offsets[e + 1] - prm.expert_offsets[e]; };
+    if ((uint32_t)tid < n_entries) {
+        const uint32_t e = (uint32_t)tid < (uint32_t)kBtSharedHalves ? (uint32_t)kSlE + tid : prm.active[1 + tid - kBtSharedHalves];
+        const uint32_t c = entry_count(e);
+        uint32_t rank = 0;
+        for (uint32_t j = 0; j < n_entries; ++j) {
+            const uint32_t e2 = j < (uint32_t)kBtSharedHalves ? (uint32_t)kSlE + j : prm.active[1 + j - kBtSharedHalves];
+            const uint32_t c2 = entry_count(e2);
+            rank += (c2 > c || (c2 == c && (e2 >= (uint32_t)kSlE ? e2 - kSlE : e2 + kBtSharedHalves) < (e >= (uint32_t)kSlE ? e - kSlE : e + kBtSharedHalves))) ? 1u : 0u;
+        }
+        s_entry[rank] = e;
+    }
     __syncthreads();
+    if (tid == 0) {
+        uint32_t run = 0;
+        for (uint32_t k = 0; k < n_entries; ++k) { s_first[k] = run; run += (entry_count(s_entry[k]) + kBtTokens - 1) / kBtTokens; }
+        s_first[n_entries] = run;
+    }
+    __syncthreads();
+    const uint32_t n_items = s_first[n_entries] * kBtParts;
+    if (blockIdx.x >= n_items) return;
+    auto resolve = [&](uint32_t item) {
+        BtItem it;
+        const uint32_t ep = item / kBtParts;
+        it.part = item % kBtParts;
+        uint32_t k = 0;
+        while (s_first[k + 1] <= ep) ++k;
+        it.expert = s_entry[k];
+        it.p0 = (ep - s_first[k]) * kBtTokens;
+        it.row0 = it.expert >= (uint32_t)kSlE ? 0u : prm.expert_offsets[it.expert];
+        it.T = min((uint32_t)kBtTokens, entry_count(it.expert) - it.p0);
+        return it;
+    };
 
     if (warp == kBtConsumers / 32) {
-        // ---- producer: the gate / up fragments of every (pass, slice), chunk by chunk through the ring, and their scales
+        // ---- producer: the gate / up fragments of every (item, slice), chunk by chunk through the ring, and their scales
         if (lane == 0) {
             uint32_t seq = 0, slices_done = 0;
-            for (uint32_t ps = 0; ps < passes; ++ps) {
+            for (uint32_t item = blockIdx.x; item < n_items; item += gridDim.x) {
+                const BtItem it = resolve(item);
+                const uint32_t first_unit = it.expert * kSlRoutedPerSlot + it.part * kBtSlices;
                 for (int sl = 0; sl < kBtSlices; ++sl, ++slices_done) {
                     const uint8_t *blob = prm.units + (size_t)(first_unit + sl) * Bl::kBytes;
                     const uint32_t sb = slices_done & 1u;
@@ -149,30 +316,35 @@ __global__ void __launch_bounds__(kBtThreads, 1) decode_batched_kernel(const __g
     // ---- consumers
     const int rb = warp & 7, nh = warp >> 3;       // gate / up: row block, and which n-blocks (nh, nh + 2) of the pass
     uint32_t seq = 0, slices_done = 0;
-    for (uint32_t ps = 0; ps < passes; ++ps) {
-        const uint32_t p0 = ps * kBtTokens;
-        const uint32_t T = min((uint32_t)kBtTokens, cnt - p0), NB = (T + 3u) / 4u;
+    for (uint32_t item = blockIdx.x; item < n_items; item += gridDim.x) {
+        const BtItem it = resolve(item);
+        const bool shared = it.expert >= (uint32_t)kSlE;
+        const uint32_t T = it.T, NB = (T + 3u) / 4u;
+        const uint32_t first_unit = it.expert * kSlRoutedPerSlot + it.part * kBtSlices;
+        float *out_base = shared ? prm.shared_part + (size_t)((it.expert - kSlE) * kBtParts + it.part) * prm.n * H
+                                 : prm.routed_part + (size_t)it.part * prm.n * prm.K * H;
         if (tid < kBtTokens)
-            s_tok[tid] = (uint32_t)tid < T ? (routed ? prm.pair_rows[row0 + p0 + tid] / prm.K : p0 + tid) : 0xffffffffu;
+            s_tok[tid] = (uint32_t)tid < T ? (shared ? it.p0 + tid : prm.pair_rows[it.row0 + it.p0 + tid] / prm.K) : 0xffffffffu;
         bt_sync();
-        // 1. activation bytes of the pass's tokens: 16 lanes per (token, group); slots beyond T hold zeros
-#pragma unroll 2
-        for (int r = 0; r < kBtTokens * kSlGroups * 16 / kBtConsumers; ++r) {
-            const int idx = r * kBtConsumers + tid, task = idx >> 4, p = idx & 15;
-            const int tok = task / kSlGroups, Gi = task - tok * kSlGroups;
-            float xv[4] = {0.f, 0.f, 0.f, 0.f};
-            const uint32_t token = s_tok[tok];
-            if (token != 0xffffffffu) {
-                const uint2 raw = __ldg(reinterpret_cast<const uint2 *>(prm.hidden + (size_t)token * H + Gi * 64 + limb_column<QT>(p)));
-                const float2 f01 = __half22float2(*reinterpret_cast<const __half2 *>(&raw.x));
-                const float2 f23 = __half22float2(*reinterpret_cast<const __half2 *>(&raw.y));
-                xv[0] = f01.x; xv[1] = f01.y; xv[2] = f23.x; xv[3] = f23.y;
+        // 1. the pass's activation bytes and scales (slots beyond T: zeros), all loads of a thread in flight together
+        {
+            constexpr int kVecsPerToken = kBtTokenLimbBytes / 16;            // 160
+            constexpr int kPerThread = kBtTokens * kVecsPerToken / kBtConsumers;     // 5
+            uint4 v[kPerThread];
+#pragma unroll
+            for (int i = 0; i < kPerThread; ++i) {
+                const int idx = i * kBtConsumers + tid, tok = idx / kVecsPerToken, w = idx - tok * kVecsPerToken;
+                const uint32_t token = s_tok[tok];
+                v[i] = token != 0xffffffffu ? __ldg(reinterpret_cast<const uint4 *>(prm.x_limbs + (size_t)token * (kBtTokenLimbBytes / 4)) + w)
+                                            : make_uint4(0u, 0u, 0u, 0u);
             }
-            const GroupLimbs L = group_limbs(xv);
-            uint32_t *d = s_xf + ((tok * kSlGroups + Gi) * 2) * 16 + p;
-            d[0] = L.lo;
-            d[16] = L.hi;
-            if (p == 0) s_xs[tok * kSlGroups + Gi] = QT == UOCR_QT_Q4 ? L.scale * kQ4LevelScale : L.scale;
+#pragma unroll
+            for (int i = 0; i < kPerThread; ++i) reinterpret_cast<uint4 *>(s_xf)[i * kBtConsumers + tid] = v[i];
+            if (tid < kBtTokens * kSlGroups) {
+                const int tok = tid / kSlGroups, Gi = tid - tok * kSlGroups;
+                const uint32_t token = s_tok[tok];
+                s_xs[tid] = token != 0xffffffffu ? prm.x_scales[(size_t)token * kSlGroups + Gi] : 0.f;
+            }
         }
         bt_sync();
 
@@ -208,25 +380,27 @@ __global__ void __launch_bounds__(kBtThreads, 1) decode_batched_kernel(const __g
                 got = mbar_wait(&full[s], (seq / kBtStages) & 1u, prm.status, s_flag) && got;
                 if (c == 0) got = mbar_wait(&sc_full[sb], (slices_done >> 1) & 1u, prm.status, s_flag) && got;
                 const uint4 *w4 = s_ring4 + (size_t)s * (Sm::kChunkBytes / 16);
+                if ((uint32_t)nh < NB) {
 #pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    const int Gi = 4 * c + q;
-                    uint4 wa, wb;
-                    if (QT == UOCR_QT_Q8) { wa = w4[((q * 8 + rb) * 2) * 32 + lane]; wb = w4[((q * 8 + rb) * 2 + 1) * 32 + lane]; }
-                    else { wa = w4[(q * 8 + rb) * 32 + lane]; wb = wa; }
-                    const float sg = __half2float(scg[Gi]), su = __half2float(scu[Gi]);
+                    for (int q = 0; q < 4; ++q) {
+                        const int Gi = 4 * c + q;
+                        uint4 wa, wb;
+                        if (QT == UOCR_QT_Q8) { wa = w4[((q * 8 + rb) * 2) * 32 + lane]; wb = w4[((q * 8 + rb) * 2 + 1) * 32 + lane]; }
+                        else { wa = w4[(q * 8 + rb) * 32 + lane]; wb = wa; }
+                        const float sg = __half2float(scg[Gi]), su = __half2float(scu[Gi]);
 #pragma unroll
-                    for (int i = 0; i < 2; ++i) {
-                        const uint32_t nb = (uint32_t)nh + 2u * i;
-                        if (nb < NB) {
-                            const int tokl = 4 * (int)nb + (g >> 1);
-                            const uint4 xb = *reinterpret_cast<const uint4 *>(s_xf + (((tokl * kSlGroups + Gi) * 2 + (g & 1)) * 4 + t) * 4);
-                            int ca[4] = {0, 0, 0, 0}, cb[4] = {0, 0, 0, 0};
-                            if (QT == UOCR_QT_Q8) group_imma(ca, cb, wa, wb, xb);
-                            else group_imma(ca, cb, make_uint2(wa.x, wa.y), make_uint2(wa.z, wa.w), xb);
-                            const float xs = s_xs[(4 * (int)nb + t) * kSlGroups + Gi];
-                            ag[i] = fmaf((float)(ca[0] + cb[0] + (ca[1] + cb[1]) * 256), sg * xs, ag[i]);
-                            au[i] = fmaf((float)(ca[2] + cb[2] + (ca[3] + cb[3]) * 256), su * xs, au[i]);
+                        for (int i = 0; i < 2; ++i) {
+                            const uint32_t nb = (uint32_t)nh + 2u * i;
+                            if (nb < NB) {
+                                const int tokl = 4 * (int)nb + (g >> 1);
+                                const uint4 xb = *reinterpret_cast<const uint4 *>(s_xf + (((tokl * kSlGroups + Gi) * 2 + (g & 1)) * 4 + t) * 4);
+                                int ca[4] = {0, 0, 0, 0}, cb[4] = {0, 0, 0, 0};
+                                if (QT == UOCR_QT_Q8) group_imma(ca, cb, wa, wb, xb);
+                                else group_imma(ca, cb, make_uint2(wa.x, wa.y), make_uint2(wa.z, wa.w), xb);
+                                const float xs = s_xs[(4 * (int)nb + t) * kSlGroups + Gi];
+                                ag[i] = fmaf((float)(ca[0] + cb[0] + (ca[1] + cb[1]) * 256), sg * xs, ag[i]);
+                                au[i] = fmaf((float)(ca[2] + cb[2] + (ca[3] + cb[3]) * 256), su * xs, au[i]);
+                            }
                         }
                     }
                 }
@@ -242,11 +416,11 @@ __global__ void __launch_bounds__(kBtThreads, 1) decode_batched_kernel(const __g
                 if (nb < NB) s_mid[(4 * nb + t) * 64 + 8 * rb + g] = __float2half_rn(got ? silu_fast_f32(ag[i]) * au[i] : 0.f);
             }
             bt_sync();
-            if (tid < kBtTokens * 16) {                // the products as bytes: 16 lanes per token
+            if ((uint32_t)tid < 4u * NB * 16u) {                // the products as bytes: 16 lanes per token
                 const int tok = tid >> 4, p = tid & 15;
-                float mv[4] = {0.f, 0.f, 0.f, 0.f};
-                if ((uint32_t)tok < 4u * NB) load_word_values<QT>(s_mid + tok * 64, p, mv);
-                const GroupLimbs M = group_limbs(mv);
+                float mv[4];
+                load_word_values<QT>(s_mid + tok * 64, p, mv);
+                const GroupLimbs M = group_limbs16(mv, (lane & 16) ? 0xffff0000u : 0x0000ffffu);
                 uint32_t *d = s_midf + (tok * 2) * 16 + p;
                 d[0] = M.lo;
                 d[16] = M.hi;
@@ -258,18 +432,28 @@ __global__ void __launch_bounds__(kBtThreads, 1) decode_batched_kernel(const __g
                 const uint4 mbf = *reinterpret_cast<const uint4 *>(s_midf + (((4 * nb + (g >> 1)) * 2 + (g & 1)) * 4 + t) * 4);
                 const uint32_t tokc = 4u * nb + t;
                 const float ms = s_ms[tokc];
-                float *dst = out_base + (size_t)(row0 + p0 + tokc) * H;
+                float *dst = out_base + (size_t)(it.row0 + it.p0 + tokc) * H;
+                float prev[kBtBlocksPerWarp][2];
+                if (sl != 0 && tokc < T) {                    // the first slice's values of this thread: all loads in flight together
+#pragma unroll
+                    for (int bi = 0; bi < kBtBlocksPerWarp; ++bi) {
+                        const uint32_t r = 16u * (warp + 16 * bi) + g;
+                        prev[bi][0] = dst[r];
+                        prev[bi][1] = dst[r + 8];
+                    }
+                }
 #pragma unroll
                 for (int bi = 0; bi < kBtBlocksPerWarp; ++bi) {
                     int ca[4] = {0, 0, 0, 0}, cb[4] = {0, 0, 0, 0};
                     if (QT == UOCR_QT_Q8) group_imma(ca, cb, dwn[bi][0], dwn[bi][1], mbf);
                     else group_imma(ca, cb, make_uint2(dwn[bi][0].x, dwn[bi][0].y), make_uint2(dwn[bi][0].z, dwn[bi][0].w), mbf);
                     if (tokc < T) {
-                        const float v0 = (float)(ca[0] + cb[0] + (ca[1] + cb[1]) * 256) * (__half2float(dslo[bi]) * ms);
-                        const float v1 = (float)(ca[2] + cb[2] + (ca[3] + cb[3]) * 256) * (__half2float(dshi[bi]) * ms);
+                        float v0 = (float)(ca[0] + cb[0] + (ca[1] + cb[1]) * 256) * (__half2float(dslo[bi]) * ms);
+                        float v1 = (float)(ca[2] + cb[2] + (ca[3] + cb[3]) * 256) * (__half2float(dshi[bi]) * ms);
+                        if (sl != 0) { v0 += prev[bi][0]; v1 += prev[bi][1]; }     // same thread, same address as for the first slice
                         const uint32_t r = 16u * (warp + 16 * bi) + g;
-                        if (sl == 0) { dst[r] = v0; dst[r + 8] = v1; }
-                        else { dst[r] += v0; dst[r + 8] += v1; }          // same thread, same address as for the first slice
+                        dst[r] = v0;
+                        dst[r + 8] = v1;
                     }
                 }
             }
@@ -278,37 +462,53 @@ __global__ void __launch_bounds__(kBtThreads, 1) decode_batched_kernel(const __g
     }
 }
 
-// out[t][h] = fp16( fma chain over slots of w * (sum of the routed parts) + (sum of the shared parts) + residual )
-__global__ void combine_batched_kernel(const float *__restrict__ routed_part, const float *__restrict__ shared_part,
-                                       const __half *__restrict__ residual, const uint32_t *__restrict__ inverse,
-                                       const float *__restrict__ weights, uint32_t n, uint32_t H, uint32_t K,
-                                       __half *__restrict__ out) {
+// ---------------------------------------------------------------- 3. combine
+// out[t][h] = fp16( fma chain over slots of w * (sum of the pair's parts) + (sum of the shared parts) + residual )
+__global__ void __launch_bounds__(256) combine_batched_kernel(const float *__restrict__ routed_part, const float *__restrict__ shared_part,
+                                                              const __half *__restrict__ residual, const uint32_t *__restrict__ inverse,
+                                                              const float *__restrict__ weights, uint32_t n, uint32_t H, uint32_t K,
+                                                              __half *__restrict__ out) {
     const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;       // one thread per 4 outputs
     const uint32_t per_row = H / 4;
     if (idx >= (size_t)n * per_row) return;
     const uint32_t tkn = (uint32_t)(idx / per_row), c = (uint32_t)(idx % per_row) * 4;
     const size_t routed_stride = (size_t)n * K * H, shared_stride = (size_t)n * H;
+    // the shared parts first in flight, summed last (the order of the CPU path: routed slots, then shared, then residual)
+    float4 sh[kBtSharedHalves * kBtParts];
+#pragma unroll
+    for (int p = 0; p < kBtSharedHalves * kBtParts; ++p)
+        sh[p] = *reinterpret_cast<const float4 *>(shared_part + p * shared_stride + (size_t)tkn * H + c);
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
-    for (uint32_t s = 0; s < K; ++s) {
-        const uint32_t pos = inverse[tkn * K + s];
-        if (pos == 0xffffffffu) continue;
-        const float w = weights[tkn * K + s];
-        float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+    // three slots at a time: their 21 loads are issued before the first is used
+    for (uint32_t s0 = 0; s0 < K; s0 += 3) {
+        uint32_t pos[3];
+        float w[3];
+        float4 v[3][kBtParts];
 #pragma unroll
-        for (int p = 0; p < kBtRoutedParts; ++p) {
-            const float4 v = *reinterpret_cast<const float4 *>(routed_part + p * routed_stride + (size_t)pos * H + c);
-            sum.x += v.x; sum.y += v.y; sum.z += v.z; sum.w += v.w;
+        for (int j = 0; j < 3; ++j) {
+            pos[j] = s0 + j < K ? inverse[tkn * K + s0 + j] : 0xffffffffu;
+            w[j] = s0 + j < K ? weights[tkn * K + s0 + j] : 0.f;
         }
-        acc[0] = fmaf(w, sum.x, acc[0]); acc[1] = fmaf(w, sum.y, acc[1]);
-        acc[2] = fmaf(w, sum.z, acc[2]); acc[3] = fmaf(w, sum.w, acc[3]);
-    }
-    float4 sh = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-    for (int p = 0; p < kBtSharedParts; ++p) {
-        const float4 v = *reinterpret_cast<const float4 *>(shared_part + p * shared_stride + (size_t)tkn * H + c);
-        sh.x += v.x; sh.y += v.y; sh.z += v.z; sh.w += v.w;
+        for (int j = 0; j < 3; ++j)
+#pragma unroll
+            for (int p = 0; p < kBtParts; ++p)
+                v[j][p] = pos[j] != 0xffffffffu ? *reinterpret_cast<const float4 *>(routed_part + p * routed_stride + (size_t)pos[j] * H + c)
+                                                 : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int j = 0; j < 3; ++j) {
+            if (pos[j] == 0xffffffffu) continue;
+            float4 sum = v[j][0];
+#pragma unroll
+            for (int p = 1; p < kBtParts; ++p) { sum.x += v[j][p].x; sum.y += v[j][p].y; sum.z += v[j][p].z; sum.w += v[j][p].w; }
+            acc[0] = fmaf(w[j], sum.x, acc[0]); acc[1] = fmaf(w[j], sum.y, acc[1]);
+            acc[2] = fmaf(w[j], sum.z, acc[2]); acc[3] = fmaf(w[j], sum.w, acc[3]);
+        }
     }
-    acc[0] += sh.x; acc[1] += sh.y; acc[2] += sh.z; acc[3] += sh.w;
+    float4 ssum = sh[0];
+#pragma unroll
+    for (int p = 1; p < kBtSharedHalves * kBtParts; ++p) { ssum.x += sh[p].x; ssum.y += sh[p].y; ssum.z += sh[p].z; ssum.w += sh[p].w; }
+    acc[0] += ssum.x; acc[1] += ssum.y; acc[2] += ssum.z; acc[3] += ssum.w;
     if (residual) {
         const uint2 rv = *reinterpret_cast<const uint2 *>(residual + (size_t)tkn * H + c);
         const float2 r01 = __half22float2(*reinterpret_cast<const __half2 *>(&rv.x));
@@ -333,31 +533,71 @@ cudaError_t init_decode_batched_kernels() {
 }
 
 uint32_t decode_batched_max_tokens() { return kBtMaxTokens; }
-size_t decode_batched_routed_part_bytes(uint32_t n, uint32_t K) { return (size_t)kBtRoutedParts * n * K * kSlH * sizeof(float); }
-size_t decode_batched_shared_part_bytes(uint32_t n) { return (size_t)kBtSharedParts * n * kSlH * sizeof(float); }
 
-// The model's shapes in Q4_0 / Q8_0 with the slice-major copy present, and a token count this kernel is built for.
-bool decode_batched_supported(const DLayer &L, uint32_t n) {
-    return n >= 2 && n <= (uint32_t)kBtMaxTokens && decode_sliced_layer_ok(L) && L.dec_units != nullptr;
+// Scratch of a call with n tokens (n <= decode_batched_max_tokens()): the parts of the routed experts and of the shared
+// MLP, the tokens' activation bytes and scales.
+BatchedScratchLayout decode_batched_scratch(uint32_t n, uint32_t K) {
+    BatchedScratchLayout l{};
+    size_t off = 0;
+    auto take = [&](size_t bytes) { const size_t o = off; off = (off + bytes + 255) / 256 * 256; return o; };
+    l.routed_part = take((size_t)kBtParts * n * K * kSlH * sizeof(float));
+    l.shared_part = take((size_t)kBtSharedHalves * kBtParts * n * kSlH * sizeof(float));
+    l.x_limbs = take((size_t)n * kBtTokenLimbBytes);
+    l.x_scales = take((size_t)n * kSlGroups * sizeof(float));
+    l.total = off;
+    return l;
 }
 
-// Routed experts and shared MLP of n tokens whose routing and dispatch plan are in S; then the combine.
-cudaError_t launch_decode_batched(const DLayer &L, const Scratch &S, const __half *hidden, const __half *residual, uint32_t n,
-                                  float *routed_part, float *shared_part, __half *out, cudaStream_t st, uint64_t *launches) {
-    BatchedParams p{};
-    p.units = L.dec_units; p.hidden = hidden; p.n = n; p.K = L.K;
-    p.max_groups = (uint64_t)n * L.K < L.E ? n * L.K : L.E;
-    p.active = S.active; p.expert_offsets = S.expert_offsets; p.pair_rows = S.pair_rows;
-    p.routed_part = routed_part; p.shared_part = shared_part; p.status = S.status;
-    const uint32_t grid = p.max_groups * kBtRoutedParts + kBtSharedParts;
-    if (L.expert_qtype == UOCR_QT_Q4) decode_batched_kernel<UOCR_QT_Q4><<<grid, kBtThreads, BtSmem<UOCR_QT_Q4>::kTotal, st>>>(p);
-    else decode_batched_kernel<UOCR_QT_Q8><<<grid, kBtThreads, BtSmem<UOCR_QT_Q8>::kTotal, st>>>(p);
-    cudaError_t err = cudaGetLastError();
+// The model's shapes in Q4_0 / Q8_0 with the slice-major copy present, and a token count this path is built for.
+bool decode_batched_supported(const DLayer &L, uint32_t n) {
+    return n >= 2 && n <= (uint32_t)kBtMaxTokens && L.K <= 16 && decode_sliced_layer_ok(L) && L.dec_units != nullptr;
+}
+
+static std::atomic<int> g_bt_sms[64];
+
+// The whole layer for n tokens: routing (results in S), dispatch plan (in S), experts, combine.  scratch: a region of
+// decode_batched_scratch(n, K).total bytes; ticket: a word that is zero before the first call (every call leaves it zero).
+cudaError_t launch_decode_batched(const DLayer &L, const Scratch &S, const __half *hidden, const __half *residual,
+                                  const float *injected, uint32_t n, float *logits, float *probs, uint8_t *scratch,
+                                  uint32_t *ticket, __half *out, cudaStream_t st, uint64_t *launches) {
+    int dev = 0;
+    cudaError_t err = cudaGetDevice(&dev);
     if (err != cudaSuccess) return err;
+    int sms = (dev >= 0 && dev < 64) ? g_bt_sms[dev].load() : 0;
+    if (sms == 0) {
+        if ((err = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return err;
+        if (dev >= 0 && dev < 64) g_bt_sms[dev] = sms;
+    }
+    const BatchedScratchLayout lay = decode_batched_scratch(n, L.K);
+    RouteSmallParams r{};
+    r.hidden = hidden; r.router = L.router; r.bias = L.bias; r.injected = injected; r.n = n; r.K = L.K; r.scaling = L.scaling;
+    r.logits_out = logits; r.probs_out = probs; r.ids = S.top_ids; r.weights = S.top_weights;
+    r.x_limbs = reinterpret_cast<uint32_t *>(scratch + lay.x_limbs); r.x_scales = reinterpret_cast<float *>(scratch + lay.x_scales);
+    r.offsets = S.expert_offsets; r.pair_rows = S.pair_rows; r.inverse = S.inverse; r.active = S.active;
+    r.ticket = ticket; r.status = S.status;
+    const bool q4 = L.expert_qtype == UOCR_QT_Q4;
+    if (q4) route_small_kernel<UOCR_QT_Q4><<<n, kRsThreads, 0, st>>>(r);
+    else route_small_kernel<UOCR_QT_Q8><<<n, kRsThreads, 0, st>>>(r);
+    if ((err = cudaGetLastError()) != cudaSuccess) return err;
+
+    BatchedParams p{};
+    p.units = L.dec_units; p.x_limbs = r.x_limbs; p.x_scales = r.x_scales; p.n = n; p.K = L.K;
+    p.active = S.active; p.expert_offsets = S.expert_offsets; p.pair_rows = S.pair_rows;
+    p.routed_part = reinterpret_cast<float *>(scratch + lay.routed_part);
+    p.shared_part = reinterpret_cast<float *>(scratch + lay.shared_part);
+    p.status = S.status;
+    // at most one item per (selected expert or shared half, pass, part); one CTA per SM, items dealt round-robin
+    const uint64_t pairs = (uint64_t)n * L.K;
+    const uint64_t max_entry_passes = (pairs < L.E ? pairs : L.E) + pairs / kBtTokens + kBtSharedHalves * ((n + kBtTokens - 1) / kBtTokens);
+    const uint64_t max_items = max_entry_passes * kBtParts;
+    const uint32_t grid = (uint32_t)(max_items < (uint64_t)sms ? max_items : (uint64_t)sms);
+    if (q4) decode_batched_kernel<UOCR_QT_Q4><<<grid, kBtThreads, BtSmem<UOCR_QT_Q4>::kTotal, st>>>(p);
+    else decode_batched_kernel<UOCR_QT_Q8><<<grid, kBtThreads, BtSmem<UOCR_QT_Q8>::kTotal, st>>>(p);
+    if ((err = cudaGetLastError()) != cudaSuccess) return err;
     const size_t work = (size_t)n * (L.H / 4);
-    combine_batched_kernel<<<(unsigned)((work + 255) / 256), 256, 0, st>>>(routed_part, shared_part, residual, S.inverse,
+    combine_batched_kernel<<<(unsigned)((work + 255) / 256), 256, 0, st>>>(p.routed_part, p.shared_part, residual, S.inverse,
                                                                            S.top_weights, n, L.H, L.K, out);
-    *launches += 2;
+    *launches += 3;
     return cudaGetLastError();
 }
 

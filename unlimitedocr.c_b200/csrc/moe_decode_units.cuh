@@ -82,10 +82,11 @@ struct GroupLimbs {
     uint32_t lo, hi;      // the low / high bytes of this lane's four values
     float scale;
 };
-__device__ __forceinline__ GroupLimbs group_limbs(const float (&x)[4]) {
+// mask: the lanes that take part (the caller's half-warp of 16 lanes, or the whole warp when both halves do)
+__device__ __forceinline__ GroupLimbs group_limbs16(const float (&x)[4], uint32_t mask) {
     float amax = fmaxf(fmaxf(fabsf(x[0]), fabsf(x[1])), fmaxf(fabsf(x[2]), fabsf(x[3])));
 #pragma unroll
-    for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o, 16));
+    for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(mask, amax, o, 16));
     // amax = 1.f * 2^e (fp16 values: e in [-24, 15]); up = 2^(13 - e), scale = 2^(e - 13); a group of zeros gets 0
     const int e = (int)(__float_as_uint(amax) >> 23) - 127;
     const bool live = amax > 0.f && amax < INFINITY;
@@ -102,6 +103,7 @@ __device__ __forceinline__ GroupLimbs group_limbs(const float (&x)[4]) {
     out.scale = live ? __uint_as_float((uint32_t)(127 - 13 + e) << 23) : 0.f;
     return out;
 }
+__device__ __forceinline__ GroupLimbs group_limbs(const float (&x)[4]) { return group_limbs16(x, 0xffffffffu); }
 // the four fp16 values behind word p of a group in shared memory
 template <int QT>
 __device__ __forceinline__ void load_word_values(const __half *group, int p, float (&x)[4]) {

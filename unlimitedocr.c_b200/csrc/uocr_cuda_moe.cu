@@ -41,11 +41,11 @@ cudaError_t launch_gemm_combine(const DLayer &L, const Scratch &S, const GemmScr
                                 const __half *residual, uint32_t n, __half *out, cudaStream_t st, uint64_t *launches);
 cudaError_t init_decode_batched_kernels();
 uint32_t decode_batched_max_tokens();
-size_t decode_batched_routed_part_bytes(uint32_t n, uint32_t K);
-size_t decode_batched_shared_part_bytes(uint32_t n);
+BatchedScratchLayout decode_batched_scratch(uint32_t n, uint32_t K);
 bool decode_batched_supported(const DLayer &L, uint32_t n);
-cudaError_t launch_decode_batched(const DLayer &L, const Scratch &S, const __half *hidden, const __half *residual, uint32_t n,
-                                  float *routed_part, float *shared_part, __half *out, cudaStream_t st, uint64_t *launches);
+cudaError_t launch_decode_batched(const DLayer &L, const Scratch &S, const __half *hidden, const __half *residual,
+                                  const float *injected, uint32_t n, float *logits, float *probs, uint8_t *scratch,
+                                  uint32_t *ticket, __half *out, cudaStream_t st, uint64_t *launches);
 cudaError_t launch_dequant_probe(const DMatrix &m, float *out, cudaStream_t st, uint64_t *launches);
 cudaError_t launch_producer_probe(const DMatrix &m, float *out, cudaStream_t st, uint64_t *launches);
 int decode_grid_size();
@@ -461,7 +461,7 @@ extern "C" int uocr_cuda_context_map_moe_layer(uocr_cuda_context *ctx, const uoc
 struct ArenaLayout {
     uint64_t logits, probs, ids, weights, offsets, pair_rows, inverse, active, mid, shared_mid, down_out, shared_out,
         stack0, stack1, d_in, d_res, d_out, dec_mid, dec_plogits, x_sorted, tiles_gu, tiles_dn, stiles_gu, stiles_dn,
-        counts, plan_counts, seg_offsets, bt_routed, bt_shared, total;
+        counts, plan_counts, seg_offsets, bt_routed, total;
 };
 
 static ArenaLayout layout_arena(uint32_t H, uint32_t E, uint32_t K, uint32_t F, uint32_t S, uint32_t n) {
@@ -503,10 +503,9 @@ static ArenaLayout layout_arena(uint32_t H, uint32_t E, uint32_t K, uint32_t F, 
         a.seg_offsets = take(260 * 4);        // expert-parallel experts phase: offsets of the received segments
         a.plan_counts = take((pairs / 2048 + 2) * E * 4);
     }
-    {   // batched decode kernel: per-part partial outputs of the routed experts and the shared MLP (calls of up to 64 tokens)
+    {   // batched decode path (calls of up to 64 tokens): per-part partial outputs, the tokens' activation bytes
         const uint32_t nb = n < uocr::decode_batched_max_tokens() ? n : uocr::decode_batched_max_tokens();
-        a.bt_routed = take(uocr::decode_batched_routed_part_bytes(nb, K));
-        a.bt_shared = take(uocr::decode_batched_shared_part_bytes(nb));
+        a.bt_routed = take(uocr::decode_batched_scratch(nb, K).total);
     }
     a.total = off;
     return a;
@@ -656,6 +655,10 @@ extern "C" int uocr_cuda_moe_debug_dequantize(uocr_cuda_context *ctx, uint32_t l
 static unsigned long long *barrier_counter(uocr_cuda_context *ctx) {
     return reinterpret_cast<unsigned long long *>(reinterpret_cast<uint8_t *>(ctx->status) + 64);
 }
+// ticket word of the batched decode path's routing kernel: in the context's status block, zero between calls
+static uint32_t *batched_ticket(uocr_cuda_context *ctx) {
+    return reinterpret_cast<uint32_t *>(reinterpret_cast<uint8_t *>(ctx->status) + 128);
+}
 static unsigned long long *decode_accumulators(uocr_cuda_context *ctx) {
     return reinterpret_cast<unsigned long long *>(reinterpret_cast<uint8_t *>(ctx->status) + 256);
 }
@@ -694,14 +697,10 @@ static int layer_forward(uocr_cuda_context *ctx, uint32_t layer, const __half *d
                                               ctx->status, logits, probs, s.top_ids, s.top_weights, nullptr, ctx->stream,
                                               &ctx->launches));
     } else if (n >= 2 && ctx->batched_decode && uocr::decode_batched_supported(L, n)) {
-        // a few tokens at the model's shapes: router, plan, then ONE weight-streaming kernel for the routed experts and
-        // the shared MLP, and the combine
-        CU_TRY(ctx, uocr::launch_router(L, d_hidden, d_injected, n, logits, probs, s.top_ids, s.top_weights, ctx->status,
-                                        s.logits, ctx->stream, &ctx->launches));
-        CU_TRY(ctx, uocr::launch_dispatch_plan(s.top_ids, n, L.K, L.E, s.expert_offsets, s.pair_rows, s.inverse,
-                                               s.active, nullptr, ctx->stream, &ctx->launches));
-        CU_TRY(ctx, uocr::launch_decode_batched(L, s, d_hidden, d_residual, n, (float *)(ctx->arena + a.bt_routed),
-                                                (float *)(ctx->arena + a.bt_shared), d_out, ctx->stream, &ctx->launches));
+        // a few tokens at the model's shapes: routing + plan, ONE weight-streaming kernel for the routed experts and the
+        // shared MLP, and the combine
+        CU_TRY(ctx, uocr::launch_decode_batched(L, s, d_hidden, d_residual, d_injected, n, logits, probs, ctx->arena + a.bt_routed,
+                                                batched_ticket(ctx), d_out, ctx->stream, &ctx->launches));
     } else if (n >= ctx->gemm_min_tokens && uocr::gemm_path_supported(L)) {
         // The shared MLP needs neither the routing nor the permutation: it runs on a second stream beside the router,
         // the dispatch plan, the gather and the routed experts, whose small kernels leave most SMs idle.
