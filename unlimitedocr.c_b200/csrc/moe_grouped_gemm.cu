@@ -236,7 +236,7 @@ template <bool GATEUP> struct GemmShape {
     static constexpr int kBStages = GATEUP ? 6 : 4;
     static constexpr int kBTileBytes = kTileN * kBlockK * 2;           // 16 or 32 KB
     static constexpr int kMaxKBlocks = 32;                             // K <= 2048
-    static constexpr int kScaleBytes = kATiles * kTileM * kMaxKBlocks * 2;
+    static constexpr int kScaleBytes = 2 * kATiles * kTileM * kMaxKBlocks * 2;    // two tiles' worth: [tile parity][matrix][row][k block]
     static constexpr int kSmemBytes = kBStages * kBTileBytes + kScaleBytes + 1024 /*alignment*/ + 256 /*barriers*/;
 };
 
@@ -245,15 +245,16 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap act_map, GemmParams p) {
     using Sh = GemmShape<GATEUP>;
     constexpr int kAStages = Sh::kAStages, kBStages = Sh::kBStages, kTileN = Sh::kTileN;
-    if (blockIdx.x >= *p.tile_count) return;
-    const uint4 tile = p.tiles[blockIdx.x];
-    const uint32_t expert = tile.x, mtile = tile.y, row0 = tile.z, nrows = tile.w;
-    const uint32_t n_mma = (nrows + 15u) & ~15u;          // MMA N: multiple of 16
+    // Persistent: the grid has at most one CTA per SM, and CTA b takes tiles b, b + gridDim.x, ... of the list (hottest
+    // expert first).  Barriers and tensor memory are set up once; the rings' phases run on across tiles, and the
+    // activation loader works ahead into the next tile while the other warps finish the current one.
+    const uint32_t n_tiles = *p.tile_count;
+    if (blockIdx.x >= n_tiles) return;
     const uint32_t kblocks = p.k_dim / kBlockK;
 
     extern __shared__ uint8_t smem_dyn[];
     uint8_t *b_tiles = reinterpret_cast<uint8_t *>(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
-    __half *s_scales = reinterpret_cast<__half *>(b_tiles + kBStages * Sh::kBTileBytes);   // [kATiles][kblocks][128]
+    __half *s_scales = reinterpret_cast<__half *>(b_tiles + kBStages * Sh::kBTileBytes);   // [tile parity][kATiles][128][kMaxKBlocks]
     uint64_t *bars = reinterpret_cast<uint64_t *>(b_tiles + kBStages * Sh::kBTileBytes + Sh::kScaleBytes);
     uint64_t *a_full = bars, *a_empty = a_full + kAStages, *b_full = a_empty + kAStages, *b_empty = b_full + kBStages,
              *acc_full = b_empty + kBStages;
@@ -279,137 +280,156 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap act_map, GemmParams p) {
     const uint32_t a_base = tmem_base + Sh::kAccCols;       // first column of the weight-operand slots
 
     if (warp < 16) {
-        // ------------------------------------------------ weight rows -> fp16 -> tensor memory
+        // ------------------------------------------------ weight rows -> fp16 -> tensor memory, then the epilogue
         // Two groups of 256 threads.  gate/up: group g converts matrix g (gate / up).  down: group g converts
         // the g-th 32-wide sub-block of every K block.  Inside a group, thread (r, h) owns row r and the K
         // positions [16h, 16h+16) of a sub-block.
         const int grp = tid >> 8, r = tid & 127, h = (tid >> 7) & 1;
-        const size_t grow = (size_t)mtile * kTileM + r;               // row of the matrix
-        const uint8_t *rowp = ((GATEUP && grp) ? p.w1 : p.w0) + (size_t)expert * p.expert_stride_bytes + grow * p.row_bytes;
         constexpr int kAhead = PackedBlock<QT>::kAhead, kVecs = PackedBlock<QT>::kVecs;
         const int sm = GATEUP ? grp : 0;                              // which matrix's scales this thread uses
-        // the first packed blocks are requested before the scales are waited for: one memory latency, not two
-        uint4 v[kAhead][kVecs];
-#pragma unroll
-        for (int d = 0; d < kAhead; ++d)
-            if ((uint32_t)d < kblocks) load_block<QT>(rowp, d, h, v[d]);
-        // the row's scales go to shared memory once ([matrix][k block][row]): the K loop never waits on a 2-byte load
-        // (all loads are issued before the first store: an unrolled, predicated batch, not a dependent chain)
-        if (QT != UOCR_QT_F16 && h == 0 && (GATEUP || grp == 0)) {
-            const __half *sc = (sm == 0 ? p.s0 : p.s1) + (size_t)expert * p.expert_scale_stride + grow * kblocks;
-            __half t[Sh::kMaxKBlocks];
-#pragma unroll
-            for (int kb = 0; kb < Sh::kMaxKBlocks; ++kb) t[kb] = (uint32_t)kb < kblocks ? sc[kb] : __ushort_as_half(0);
-#pragma unroll
-            for (int kb = 0; kb < Sh::kMaxKBlocks; ++kb)
-                if ((uint32_t)kb < kblocks) s_scales[(sm * kblocks + kb) * kTileM + r] = t[kb];
-        }
-        asm volatile("bar.sync 1, %0;" ::"n"(kProducerThreads) : "memory");     // scales visible to every thread of a row
         // this thread's TMEM lane, its 8 columns inside a 16-column sub-block, and its matrix inside a slot
         const uint32_t lane_addr = ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)h * 8 + (GATEUP ? (uint32_t)grp * 32 : 0u);
         bool alive = true;
-        int pending = -1;       // slot whose tensor-memory stores are in flight: published one block later, so that
-                                // the stores' latency hides behind the next block's conversion
-        auto publish = [&]() {
-            tc_st_wait();
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) gb_arrive(&a_full[pending]);              // one arrival per warp: its stores have all landed
-        };
-        for (uint32_t kb0 = 0; kb0 < kblocks && alive; kb0 += kAhead) {
+        uint32_t kbase = 0, it = 0;                                   // K blocks and tiles this CTA has gone through
+#pragma unroll 1
+        for (uint32_t tile_idx = blockIdx.x; tile_idx < n_tiles && alive; tile_idx += gridDim.x, kbase += kblocks, ++it) {
+            const uint4 tile = p.tiles[tile_idx];
+            const uint32_t expert = tile.x, mtile = tile.y, row0 = tile.z, nrows = tile.w;
+            const size_t grow = (size_t)mtile * kTileM + r;               // row of the matrix
+            const uint8_t *rowp = ((GATEUP && grp) ? p.w1 : p.w0) + (size_t)expert * p.expert_stride_bytes + grow * p.row_bytes;
+            // the first packed blocks are requested before the scales are waited for: one memory latency, not two
+            uint4 v[kAhead][kVecs];
 #pragma unroll
-            for (int d = 0; d < kAhead; ++d) {
-                const uint32_t kb = kb0 + d;
-                if (kb >= kblocks) break;
-                const __half sc = QT == UOCR_QT_F16 ? __ushort_as_half(0) : s_scales[(sm * kblocks + kb) * kTileM + r];
-                const uint32_t slot = kb % kAStages, use = kb / kAStages;
-                // gate/up: both 32-wide sub-blocks of this thread's matrix; down: the group's sub-block
-                uint32_t regs[2][8];
-                if (GATEUP) { convert_sub<QT>(v[d], 0, sc, regs[0]); convert_sub<QT>(v[d], 1, sc, regs[1]); }
-                else convert_sub<QT>(v[d], grp, sc, regs[0]);
-                if (kb + kAhead < kblocks) load_block<QT>(rowp, kb + kAhead, h, v[d]);
-                if (pending >= 0) publish();
-                if (use > 0 && !gb_wait(&a_empty[slot], (use - 1) & 1u, abort_flag, p.status)) { alive = false; pending = -1; break; }
-                __syncwarp();
-                tc_fence_after();
-                const uint32_t dst = a_base + slot * Sh::kAStageCols + lane_addr;
-                if (GATEUP) { tc_st8(dst, regs[0]); tc_st8(dst + 16, regs[1]); }
-                else tc_st8(dst + (uint32_t)grp * 16, regs[0]);
-                pending = (int)slot;
+            for (int d = 0; d < kAhead; ++d)
+                if ((uint32_t)d < kblocks) load_block<QT>(rowp, d, h, v[d]);
+            // The row's scales go to shared memory once ([matrix][row][k block], one buffer per tile parity, so the
+            // previous tile's readers need not be waited for): the K loop never waits on a 2-byte global load.  A row's
+            // scales are contiguous: 4-byte loads, all issued before the first store.
+            __half *tile_scales = s_scales + (size_t)(it & 1u) * (Sh::kATiles * kTileM * Sh::kMaxKBlocks);
+            if (QT != UOCR_QT_F16 && h == 0 && (GATEUP || grp == 0)) {
+                // (K is a multiple of 128, so a row holds an even number of scales and starts on a 4-byte boundary)
+                const uint32_t *sc = reinterpret_cast<const uint32_t *>((sm == 0 ? p.s0 : p.s1) + (size_t)expert * p.expert_scale_stride + grow * kblocks);
+                uint32_t *dst = reinterpret_cast<uint32_t *>(tile_scales + ((size_t)sm * kTileM + r) * Sh::kMaxKBlocks);
+                uint32_t t[Sh::kMaxKBlocks / 2];
+#pragma unroll
+                for (int i = 0; i < Sh::kMaxKBlocks / 2; ++i) t[i] = (uint32_t)(2 * i) < kblocks ? __ldg(sc + i) : 0u;
+#pragma unroll
+                for (int i = 0; i < Sh::kMaxKBlocks / 2; ++i)
+                    if ((uint32_t)(2 * i) < kblocks) dst[i] = t[i];
             }
-        }
-        if (pending >= 0) publish();
-        // ------------------------------------------------ epilogue: TMEM -> registers -> global
-        const bool have_acc = alive && gb_wait(acc_full, 0, abort_flag, p.status);
-        __syncwarp();
-        if (__all_sync(0xffffffffu, have_acc)) {
-            tc_fence_after();
-            // a warp reads the TMEM lanes 32*(warp % 4)..+31; the four warps of a lane quarter split the 16-column
-            // chunks.  All of a warp's chunks are requested before the first is used.
-            constexpr int kChunks = kTileN / 64;
-            const uint32_t lane_base = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
-            const size_t out_col = (size_t)mtile * kTileM + r;
-            const uint32_t cbase = (uint32_t)(warp >> 2) * 16;
-            uint32_t g[kChunks][16], u[GATEUP ? kChunks : 1][16];
+            asm volatile("bar.sync 1, %0;" ::"n"(kProducerThreads) : "memory");     // scales visible to every thread of a row
+            const __half *my_scales = tile_scales + ((size_t)sm * kTileM + r) * Sh::kMaxKBlocks;
+            int pending = -1;       // slot whose tensor-memory stores are in flight: published one block later, so that
+                                    // the stores' latency hides behind the next block's conversion
+            auto publish = [&]() {
+                tc_st_wait();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) gb_arrive(&a_full[pending]);              // one arrival per warp: its stores have all landed
+            };
+            for (uint32_t kb0 = 0; kb0 < kblocks && alive; kb0 += kAhead) {
 #pragma unroll
-            for (int i = 0; i < kChunks; ++i) {
-                if (cbase + 64 * i < nrows) {
-                    tc_ld16(lane_base + cbase + 64 * i, g[i]);
-                    if (GATEUP) tc_ld16(lane_base + kTileN + cbase + 64 * i, u[i]);
+                for (int d = 0; d < kAhead; ++d) {
+                    const uint32_t kb = kb0 + d;
+                    if (kb >= kblocks) break;
+                    const __half sc = QT == UOCR_QT_F16 ? __ushort_as_half(0) : my_scales[kb];
+                    const uint32_t kbg = kbase + kb, slot = kbg % kAStages, use = kbg / kAStages;
+                    // gate/up: both 32-wide sub-blocks of this thread's matrix; down: the group's sub-block
+                    uint32_t regs[2][8];
+                    if (GATEUP) { convert_sub<QT>(v[d], 0, sc, regs[0]); convert_sub<QT>(v[d], 1, sc, regs[1]); }
+                    else convert_sub<QT>(v[d], grp, sc, regs[0]);
+                    if (kb + kAhead < kblocks) load_block<QT>(rowp, kb + kAhead, h, v[d]);
+                    if (pending >= 0) publish();
+                    if (use > 0 && !gb_wait(&a_empty[slot], (use - 1) & 1u, abort_flag, p.status)) { alive = false; pending = -1; break; }
+                    __syncwarp();
+                    tc_fence_after();
+                    const uint32_t dst = a_base + slot * Sh::kAStageCols + lane_addr;
+                    if (GATEUP) { tc_st8(dst, regs[0]); tc_st8(dst + 16, regs[1]); }
+                    else tc_st8(dst + (uint32_t)grp * 16, regs[0]);
+                    pending = (int)slot;
                 }
             }
-            tc_ld_wait();
+            if (pending >= 0) publish();
+            // ------------------------------------------------ epilogue: TMEM -> registers -> global
+            const bool have_acc = alive && gb_wait(acc_full, it & 1u, abort_flag, p.status);
+            __syncwarp();
+            if (__all_sync(0xffffffffu, have_acc)) {
+                tc_fence_after();
+                // a warp reads the TMEM lanes 32*(warp % 4)..+31; the four warps of a lane quarter split the 16-column
+                // chunks.  All of a warp's chunks are requested before the first is used.
+                constexpr int kChunks = kTileN / 64;
+                const uint32_t lane_base = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
+                const size_t out_col = (size_t)mtile * kTileM + r;
+                const uint32_t cbase = (uint32_t)(warp >> 2) * 16;
 #pragma unroll
-            for (int i = 0; i < kChunks; ++i) {
-                const uint32_t c0 = cbase + 64 * i;
-                if (c0 < nrows) {
+                for (int i = 0; i < kChunks; ++i) {          // chunk by chunk: the registers of one chunk at a time
+                    const uint32_t c0 = cbase + 64 * i;
+                    if (c0 < nrows) {
+                        uint32_t g[16], u[16];
+                        tc_ld16(lane_base + c0, g);
+                        if (GATEUP) tc_ld16(lane_base + kTileN + c0, u);
+                        tc_ld_wait();
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        if (c0 + j < nrows) {
-                            const float a = __uint_as_float(g[i][j]);
-                            const float o = GATEUP ? silu_fast(a) * __uint_as_float(u[GATEUP ? i : 0][j]) : a;
-                            p.out[(size_t)(row0 + c0 + j) * p.out_ld + out_col] = __float2half_rn(o);
+                        for (int j = 0; j < 16; ++j) {
+                            if (c0 + j < nrows) {
+                                const float a = __uint_as_float(g[j]);
+                                const float o = GATEUP ? silu_fast(a) * __uint_as_float(u[j]) : a;
+                                p.out[(size_t)(row0 + c0 + j) * p.out_ld + out_col] = __float2half_rn(o);
+                            }
                         }
                     }
                 }
+            } else {
+                alive = false;
             }
+            tc_fence_before();
         }
-        tc_fence_before();
     } else if (warp == kTmaWarp) {
-        // ------------------------------------------------ activation tiles by TMA
+        // ------------------------------------------------ activation tiles by TMA (runs ahead into the next tile)
         if (lane == 0) {
-            for (uint32_t kb = 0; kb < kblocks; ++kb) {
-                const int s = kb % kBStages;
-                const uint32_t use = kb / kBStages;
-                if (use > 0 && !gb_wait(&b_empty[s], (use - 1) & 1u, abort_flag, p.status)) break;
-                gb_expect_tx(&b_full[s], Sh::kBTileBytes);
-                tma_load_2d(b_tiles + s * Sh::kBTileBytes, &act_map, (int)(kb * kBlockK), (int)row0, &b_full[s]);
+            uint32_t kbase = 0;
+            bool ok = true;
+            for (uint32_t tile_idx = blockIdx.x; tile_idx < n_tiles && ok; tile_idx += gridDim.x, kbase += kblocks) {
+                const uint32_t row0 = p.tiles[tile_idx].z;
+                for (uint32_t kb = 0; kb < kblocks; ++kb) {
+                    const uint32_t kbg = kbase + kb, use = kbg / kBStages;
+                    const int s = kbg % kBStages;
+                    if (use > 0 && !gb_wait(&b_empty[s], (use - 1) & 1u, abort_flag, p.status)) { ok = false; break; }
+                    gb_expect_tx(&b_full[s], Sh::kBTileBytes);
+                    tma_load_2d(b_tiles + s * Sh::kBTileBytes, &act_map, (int)(kb * kBlockK), (int)row0, &b_full[s]);
+                }
             }
         }
     } else {
         // ------------------------------------------------ MMA issue
         if (lane == 0) {
-            const uint32_t idesc = umma_idesc(n_mma);
+            uint32_t kbase = 0;
             bool ok = true;
-            for (uint32_t kb = 0; kb < kblocks && ok; ++kb) {
-                const uint32_t slot = kb % kAStages, bs = kb % kBStages;
-                ok = gb_wait(&a_full[slot], (kb / kAStages) & 1u, abort_flag, p.status);
-                if (ok) ok = gb_wait(&b_full[bs], (kb / kBStages) & 1u, abort_flag, p.status);
-                if (!ok) break;
-                tc_fence_after();
-                const uint32_t b_addr = s2u(b_tiles + bs * Sh::kBTileBytes);
-                const uint32_t a_addr = a_base + slot * Sh::kAStageCols;
+            for (uint32_t tile_idx = blockIdx.x; tile_idx < n_tiles && ok; tile_idx += gridDim.x, kbase += kblocks) {
+                const uint32_t nrows = p.tiles[tile_idx].w;
+                const uint32_t idesc = umma_idesc((nrows + 15u) & ~15u);          // MMA N: multiple of 16
+                // the accumulators of the previous tile have been read: every producer warp publishes its first block
+                // of this tile only after its own epilogue, and the first MMA waits for all sixteen
+                for (uint32_t kb = 0; kb < kblocks && ok; ++kb) {
+                    const uint32_t kbg = kbase + kb, slot = kbg % kAStages, bs = kbg % kBStages;
+                    ok = gb_wait(&a_full[slot], (kbg / kAStages) & 1u, abort_flag, p.status);
+                    if (ok) ok = gb_wait(&b_full[bs], (kbg / kBStages) & 1u, abort_flag, p.status);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint32_t b_addr = s2u(b_tiles + bs * Sh::kBTileBytes);
+                    const uint32_t a_addr = a_base + slot * Sh::kAStageCols;
 #pragma unroll
-                for (int k = 0; k < kBlockK / 16; ++k) {
-                    const uint32_t acc = (kb > 0 || k > 0) ? 1u : 0u;
-                    const uint64_t bd = umma_desc(b_addr + k * 32);
-                    tc_mma_ts(tmem_base, a_addr + k * 8, bd, idesc, acc);
-                    if (GATEUP) tc_mma_ts(tmem_base + kTileN, a_addr + 32 + k * 8, bd, idesc, acc);
+                    for (int k = 0; k < kBlockK / 16; ++k) {
+                        const uint32_t acc = (kb > 0 || k > 0) ? 1u : 0u;
+                        const uint64_t bd = umma_desc(b_addr + k * 32);
+                        tc_mma_ts(tmem_base, a_addr + k * 8, bd, idesc, acc);
+                        if (GATEUP) tc_mma_ts(tmem_base + kTileN, a_addr + 32 + k * 8, bd, idesc, acc);
+                    }
+                    tc_commit(&a_empty[slot]);                // arrives when the MMAs above have read the slot
+                    tc_commit(&b_empty[bs]);
                 }
-                tc_commit(&a_empty[slot]);                // arrives when the MMAs above have read the slot
-                tc_commit(&b_empty[bs]);
+                if (ok) tc_commit(acc_full);
             }
-            if (ok) tc_commit(acc_full);
         }
         __syncwarp();
     }
@@ -534,11 +554,24 @@ router_logits_kernel(const __grid_constant__ CUtensorMap hidden_map, const __gri
 __global__ void tile_plan_kernel(const uint32_t *__restrict__ expert_offsets, uint32_t E, uint32_t expert_base,
                                  uint32_t expert_mod, uint32_t gu_mtiles, uint32_t dn_mtiles, uint4 *__restrict__ tiles_gu,
                                  uint4 *__restrict__ tiles_dn, uint32_t *__restrict__ counts) {
-    __shared__ uint32_t base_gu[257], base_dn[257];
+    // The lists start with the segment that has the most rows (ties: lower index first): the persistent GEMM kernel
+    // deals tiles to its CTAs in list order, so the long segments are under way first and the short ones fill the tail.
+    __shared__ uint32_t base_gu[257], base_dn[257], order[256];
     const uint32_t e = threadIdx.x;
+    if (e < E) {
+        const uint32_t c = expert_offsets[e + 1] - expert_offsets[e];
+        uint32_t rank = 0;
+        for (uint32_t j = 0; j < E; ++j) {
+            const uint32_t cj = expert_offsets[j + 1] - expert_offsets[j];
+            rank += (cj > c || (cj == c && j < e)) ? 1u : 0u;
+        }
+        order[rank] = e;
+    }
+    __syncthreads();
     if (threadIdx.x == 0) {
         uint32_t rg = 0, rd = 0;
-        for (uint32_t i = 0; i < E; ++i) {
+        for (uint32_t k = 0; k < E; ++k) {
+            const uint32_t i = order[k];
             const uint32_t c = expert_offsets[i + 1] - expert_offsets[i];
             base_gu[i] = rg; base_dn[i] = rd;
             rg += (c + kTileNGateUp - 1) / kTileNGateUp;
@@ -798,9 +831,24 @@ bool gemm_path_supported(const DLayer &L) {
            L.S <= 2048 && g_encode.load() != nullptr;
 }
 
+static std::atomic<int> g_gemm_sms[64];
+
+// one CTA per SM at most (the kernel is persistent: CTA b takes tiles b, b + grid, ...)
+static uint32_t gemm_grid(uint32_t max_tiles) {
+    int dev = 0, sms = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return max_tiles;
+    sms = g_gemm_sms[dev].load();
+    if (sms == 0) {
+        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) return max_tiles;
+        g_gemm_sms[dev] = sms;
+    }
+    return max_tiles < (uint32_t)sms ? max_tiles : (uint32_t)sms;
+}
+
 template <bool GU>
 static cudaError_t launch_gemm(int qt, const CUtensorMap &map, const GemmParams &p, uint32_t max_tiles, cudaStream_t st) {
     if (max_tiles == 0) return cudaSuccess;
+    max_tiles = gemm_grid(max_tiles);
     const size_t smem = GemmShape<GU>::kSmemBytes;
     switch (qt) {
         case UOCR_QT_Q4: grouped_gemm_kernel<UOCR_QT_Q4, GU><<<max_tiles, kGemmThreads, smem, st>>>(map, p); break;
