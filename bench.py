@@ -462,15 +462,19 @@ def measure_ep(pkg, torch, dist, rank: int, world: int, flush_l2, steps: int, wa
     result = {"workload": w["workload"].replace("Zipf(1.1)-skewed routing", "Zipf(1.1)-skewed and uniform routing"),
               "tokens_per_step": n_total, "qtype": "q4_0", "n_gpus": world, "parallelism": f"ep{world}", "l2": L2_NOTE}
     exchange = "none (one GPU)"
-    for routing in routings:
-        li = layer_of[routing]
+    pair_counts = {}
+
+    def run_variant(name: str, li: int) -> None:
+        """Time one mapped layer (index li) sharded over the ranks; result[name] gets the figures."""
+        nonlocal exchange
         layer = None
         if world > 1 and exchange_kind == "peer":
             why = ""
             try:
                 layer = pkg.ep.PeerExpertParallelLayer(ctx, li, E, K, H, row_capacity=n_total * K, rank=rank, world=world,
                                                        dist_module=dist)
-                exchange = "peer memory (CUDA IPC over NVLink), fused into gather and combine"
+                exchange = ("peer memory (CUDA IPC over NVLink), fused into gather and combine; counts and row offsets "
+                            "stay on the device")
             except Exception as e:      # e.g. no peer access between the devices: every rank must then take the other path
                 why = str(e)[:200]
             ok = torch.tensor([1 if layer is not None else 0], device="cuda")
@@ -490,6 +494,7 @@ def measure_ep(pkg, torch, dist, rank: int, world: int, flush_l2, steps: int, wa
         times = timed_steps(torch, dist, world, stream, flush_l2, step, steps, warmup)
         launches = (ctx.kernel_launches - launches0) // (steps + warmup)
         plan = layer.last_plan
+        pair_counts[name] = pkg.ep.counts_from_offsets(layer._all_offsets.cpu().numpy()).sum(axis=0)
         e2e_ms = 0.0
         if with_e2e:
             wall = []
@@ -528,7 +533,7 @@ def measure_ep(pkg, torch, dist, rank: int, world: int, flush_l2, steps: int, wa
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms, e2e_ms, max_rows, mismatches = float(t[0]), float(t[1]), float(t[2]), int(t[3])
         if mismatches:
-            raise SystemExit(f"expert-parallel output differs from the single-GPU output on at least one rank ({routing} routing)")
+            raise SystemExit(f"expert-parallel output differs from the single-GPU output on at least one rank ({name})")
         tps = n_total / (ms * 1e-3)
         mean_rows = n_total * K / world
         r = {"tokens_per_s": tps, "ms_per_step": ms, "step_ms_min_max": [min(times), max(times)],
@@ -543,9 +548,19 @@ def measure_ep(pkg, torch, dist, rank: int, world: int, flush_l2, steps: int, wa
             g1 = n_total / (sum(ts[-5:]) / 5 * 1e-3)
             r["single_gpu_tokens_per_s_same_job"] = g1
             r["scaling_efficiency"] = tps / g1 / world
-        result[routing] = r
+        result[name] = r
         if isinstance(layer, pkg.ep.PeerExpertParallelLayer):
             layer.close()                          # every rank together: waits for all ranks' kernels before freeing
+
+    for routing in routings:
+        run_variant(routing, layer_of[routing])
+    if world > 1 and "zipf" in routings:
+        # The named configuration shards contiguous expert ranges.  Beside it: the same layer with its experts relabelled
+        # so that the ranks' loads are even (longest-processing-time placement from the pair counts just observed).
+        from oracle import quant
+        order = pkg.ep.balanced_placement(pair_counts["zipf"], world)
+        run_variant("zipf_balanced_placement", ctx.map_layer(quant.permute_experts(L, order)))
+        result["zipf_balanced_placement"]["placement"] = "experts relabelled by ep.balanced_placement(observed pair counts)"
     result["exchange"] = exchange
     ctx.synchronize()
     ctx.close()

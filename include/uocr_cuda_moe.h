@@ -305,6 +305,13 @@ UOCR_CUDA_API int uocr_cuda_moe_ep_peer_scatter(uocr_cuda_context *ctx, uint32_t
                                                 uint32_t n_tokens, const uint32_t *h_dst_row0, char *error, size_t error_size);
 UOCR_CUDA_API int uocr_cuda_moe_ep_peer_experts(uocr_cuda_context *ctx, uint32_t layer, uint32_t n_sources,
                                                 const uint32_t *h_segment_counts, char *error, size_t error_size);
+/* scatter / experts with the counts left on the device: d_all_offsets [world][E + 1] is every rank's d_expert_offsets
+ * in rank order (one all_gather on the device).  The row offsets of both phases are computed by a small kernel, so no
+ * host copy or wait sits between the count exchange and the kernels.  The experts phase sizes its work for the rows
+ * this rank's buffers can hold (min(row_capacity, token_capacity * top_k)); more rows than that raise the status bit. */
+UOCR_CUDA_API int uocr_cuda_moe_ep_peer_scatter_dev(uocr_cuda_context *ctx, uint32_t layer, const void *d_hidden_f16,
+                                                    uint32_t n_tokens, const uint32_t *d_all_offsets, char *error, size_t error_size);
+UOCR_CUDA_API int uocr_cuda_moe_ep_peer_experts_dev(uocr_cuda_context *ctx, uint32_t layer, char *error, size_t error_size);
 UOCR_CUDA_API int uocr_cuda_moe_ep_peer_combine(uocr_cuda_context *ctx, uint32_t layer, const void *d_residual_f16,
                                                 uint32_t n_tokens, void *d_out_f16, char *error, size_t error_size);
 

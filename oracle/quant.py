@@ -205,6 +205,22 @@ def synth_layer(rng: np.random.Generator, *, H: int, E: int, K: int, F: int, S: 
                         None if logit_bias is None else np.ascontiguousarray(logit_bias, dtype=np.float32))
 
 
+def permute_experts(L: LayerWeights, order: np.ndarray) -> LayerWeights:
+    """The same layer with its experts relabelled: slot s of the result holds expert order[s] of L (router row, logit
+    bias, packed weights and scales move together).  Every token's output is unchanged up to the summation order of
+    the softmax denominator (and exact probability ties, which go to the lower label); the reported ids are slots."""
+    order = np.asarray(order, np.int64)
+    assert sorted(order.tolist()) == list(range(L.E))
+    proj = L.F * packed_row_bytes(L.expert_qtype, L.H)
+    nsc = 0 if L.expert_qtype == QTYPE_F16 else L.F * (L.H // GROUP)
+    slab = L.expert_qweight.reshape(L.E, 3 * proj)[order].reshape(-1)
+    scales = None if L.expert_qscale is None else L.expert_qscale.reshape(L.E, 3 * nsc)[order].reshape(-1)
+    return LayerWeights(L.H, L.E, L.K, L.F, L.S, L.scaling, np.ascontiguousarray(L.router.reshape(L.E, L.H)[order]), L.expert_qtype,
+                        np.ascontiguousarray(slab), None if scales is None else np.ascontiguousarray(scales), L.shared_gate,
+                        L.shared_up, L.shared_down, None if L.logit_bias is None else np.ascontiguousarray(L.logit_bias[order]),
+                        dict(L.meta))
+
+
 def synth_activations(rng: np.random.Generator, rows: int, H: int) -> np.ndarray:
     """fp16 N(0,1) activations as uint16 bits [rows, H]."""
     return rng.standard_normal((rows, H), dtype=np.float32).astype("<f2").view(np.uint16)

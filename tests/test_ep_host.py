@@ -165,3 +165,71 @@ def test_peer_scatter_offsets_match_the_owner_side_row_order():
         want = [(s, owner * per + e) for s in range(world) for e in range(per) for _ in range(plan.recv_counts[s, e])]
         assert [buffers[owner][i] for i in range(plan.rows_received)] == want
 
+
+
+def test_balanced_placement_evens_out_skewed_loads():
+    """Longest-processing-time placement: under a Zipf(1.1) popularity the contiguous ranges leave one rank with almost
+    twice the mean load at 8 ranks; the placement brings every rank within a few percent, is a permutation with
+    E / world experts per rank, and is deterministic."""
+    ep = load_ep()
+    rng = np.random.default_rng(9)
+    ranks = rng.permutation(64).astype(np.float64) + 1.0
+    counts = np.round(98304 * ranks ** -1.1 / np.sum(ranks ** -1.1)).astype(np.int64)
+    for world in (2, 4, 8):
+        contiguous = ep.rank_loads(counts, np.arange(64), world)
+        order = ep.balanced_placement(counts, world)
+        assert sorted(order.tolist()) == list(range(64))
+        assert np.array_equal(order, ep.balanced_placement(counts, world))
+        balanced = ep.rank_loads(counts, order, world)
+        assert balanced.sum() == counts.sum()
+        per = 64 // world
+        # a rank holds E / world experts: the one with the hottest expert cannot get below that expert plus the coldest others
+        floor = counts.max() + np.sort(counts)[: per - 1].sum()
+        assert balanced.max() <= max(1.05 * balanced.mean(), floor)
+        assert balanced.max() <= contiguous.max()
+        for g in range(world):                      # slots of a rank are listed in ascending expert id
+            assert list(order[g * per:(g + 1) * per]) == sorted(order[g * per:(g + 1) * per])
+    with pytest.raises(ValueError):
+        ep.balanced_placement(counts, 3)
+
+
+def test_permuted_experts_give_the_same_layer_output():
+    """Relabelling the experts (how a placement is applied) changes ids, not results: the CPU oracle on the permuted
+    layer selects the same experts (its ids are the slots of the original ids) and returns the same outputs up to the
+    order in which the softmax denominator is summed (expert order, which the relabelling changes)."""
+    from oracle import oracle as orc
+    from oracle import quant
+    port = orc.Port()
+    rng = np.random.default_rng(3)
+    L = quant.synth_layer(rng, H=128, E=8, K=2, F=64, S=64, expert_qtype=quant.QTYPE_Q4_0,
+                          logit_bias=rng.standard_normal(8).astype(np.float32))
+    hidden = quant.synth_activations(rng, 12, 128)
+    order = np.array([5, 2, 7, 0, 3, 6, 1, 4])
+    a, b = port.layer(L, hidden), port.layer(quant.permute_experts(L, order), hidden)
+    slot_of = np.argsort(order)
+    assert np.array_equal(slot_of[a.ids], b.ids)
+    assert np.max(np.abs(a.weights - b.weights)) <= 1e-6 and np.max(np.abs(a.out - b.out)) <= 1e-5
+
+
+def test_device_side_offset_arithmetic_restated():
+    """The row offsets the library computes on the device (ep_offsets_kernel) follow two formulas; restated here in
+    NumPy they must agree with the host helpers the earlier form of the exchange uses."""
+    ep = load_ep()
+    rng = np.random.default_rng(6)
+    world, n_experts = 4, 64
+    per = n_experts // world
+    counts = rng.integers(0, 50, size=(world, n_experts))
+    offsets = np.concatenate([np.zeros((world, 1), np.int64), np.cumsum(counts, axis=1)], axis=1)
+    for rank in range(world):
+        dst = np.empty(n_experts, np.int64)
+        for e in range(n_experts):
+            first = (e // per) * per
+            dst[e] = sum(offsets[g, first + per] - offsets[g, first] for g in range(rank)) + offsets[rank, e] - offsets[rank, first]
+        assert np.array_equal(dst, ep.dst_rows_from_counts(counts, rank))
+        seg = [0]
+        for src in range(world):
+            for le in range(per):
+                seg.append(seg[-1] + offsets[src, rank * per + le + 1] - offsets[src, rank * per + le])
+        plan = ep.plan_from_counts(counts, rank)
+        assert seg[-1] == plan.rows_received
+        assert np.array_equal(np.diff(seg), plan.recv_counts.reshape(-1))

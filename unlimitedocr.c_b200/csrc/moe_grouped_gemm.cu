@@ -979,6 +979,44 @@ cudaError_t launch_combine_peer(const DLayer &L, const Scratch &S, const GemmScr
     return cudaGetLastError();
 }
 
+// Row bookkeeping of the peer-memory exchange, on the device (no host round trip between the count exchange and the
+// scatter).  all_offsets [world][E + 1]: every rank's expert_offsets.  For this rank as a SENDER: dst_row0[e] = row of the
+// owner's "received rows" buffer where its rows for expert e start (the owner's buffer holds, for source 0, 1, ... in
+// turn, the rows of each of its experts in turn).  For this rank as an OWNER: seg_offsets[source * per + local expert]
+// = first row of that segment, seg_offsets[world * per] = rows received.  More rows than the buffers hold raise the
+// status bit; the kernels that use the offsets check every row index again.
+__global__ void ep_offsets_kernel(const uint32_t *__restrict__ all_offsets, uint32_t world, uint32_t rank, uint32_t E,
+                                  unsigned long long row_capacity, uint32_t *__restrict__ dst_row0,
+                                  uint32_t *__restrict__ seg_offsets, uint32_t *__restrict__ status) {
+    const uint32_t per = E / world, tid = threadIdx.x, stride = E + 1;
+    auto cnt = [&](uint32_t g, uint32_t e) { return all_offsets[g * stride + e + 1] - all_offsets[g * stride + e]; };
+    for (uint32_t e = tid; e < E; e += blockDim.x) {
+        const uint32_t owner = e / per, first = owner * per;
+        unsigned long long row = 0;
+        for (uint32_t g = 0; g < rank; ++g) row += all_offsets[g * stride + first + per] - all_offsets[g * stride + first];
+        row += all_offsets[rank * stride + e] - all_offsets[rank * stride + first];
+        dst_row0[e] = row > 0xffffffffull ? 0xffffffffu : (uint32_t)row;
+    }
+    if (tid == 0) {
+        unsigned long long run = 0;
+        for (uint32_t src = 0; src < world; ++src)
+            for (uint32_t le = 0; le < per; ++le) {
+                seg_offsets[src * per + le] = (uint32_t)run;
+                run += cnt(src, rank * per + le);
+            }
+        if (run > row_capacity) { atomicOr(status, kStatusPeerRange); run = row_capacity; }
+        seg_offsets[world * per] = (uint32_t)run;
+    }
+}
+
+cudaError_t launch_ep_offsets(const uint32_t *all_offsets, uint32_t world, uint32_t rank, uint32_t E,
+                              unsigned long long row_capacity, uint32_t *dst_row0, uint32_t *seg_offsets, uint32_t *status,
+                              cudaStream_t st, uint64_t *launches) {
+    ep_offsets_kernel<<<1, 256, 0, st>>>(all_offsets, world, rank, E, row_capacity, dst_row0, seg_offsets, status);
+    ++*launches;
+    return cudaGetLastError();
+}
+
 // ---- dequantisation probe ------------------------------------------------------------------------------------
 // out[row][col] = the fp16 value (widened to f32) the grouped GEMM's producer threads store into tensor memory for
 // weight (row, col): the same load_block / convert_sub pair, one thread per (row, 64-wide K block, half h).

@@ -30,6 +30,9 @@ cudaError_t launch_scatter_peer(const DLayer &L, const Scratch &S, const __half 
 cudaError_t launch_combine_peer(const DLayer &L, const Scratch &S, const GemmScratch &G, const PeerBuffers &done,
                                 uint32_t experts_per_rank, const uint32_t *dst_row0, unsigned long long row_capacity,
                                 const __half *residual, uint32_t n, __half *out, cudaStream_t st, uint64_t *launches);
+cudaError_t launch_ep_offsets(const uint32_t *all_offsets, uint32_t world, uint32_t rank, uint32_t E,
+                              unsigned long long row_capacity, uint32_t *dst_row0, uint32_t *seg_offsets, uint32_t *status,
+                              cudaStream_t st, uint64_t *launches);
 cudaError_t launch_gather_sorted(const DLayer &L, const Scratch &S, const __half *hidden, uint32_t n, __half *rows_out,
                                  cudaStream_t st, uint64_t *launches);
 cudaError_t launch_gemm_experts(const DLayer &L, const Scratch &S, const GemmScratch &G, const uint32_t *seg_offsets,
@@ -1084,6 +1087,44 @@ extern "C" int uocr_cuda_moe_ep_peer_experts(uocr_cuda_context *ctx, uint32_t la
     for (uint32_t i = 0; i < n_sources * per; ++i) rows += h_segment_counts[i];
     if (rows > P.row_capacity) return fail(ctx, error, error_size, "%llu received rows exceed the exchange buffers' %llu rows", (unsigned long long)rows, (unsigned long long)P.row_capacity);
     return uocr_cuda_moe_ep_experts(ctx, layer, P.rank * per, per, n_sources, h_segment_counts, P.recv, P.done, error, error_size);
+}
+
+// The same two phases with the counts left on the device: d_all_offsets [world][E + 1] holds every rank's expert offsets
+// (one all_gather of what the dispatch call wrote).  Nothing is copied to or from the host between the phases.
+extern "C" int uocr_cuda_moe_ep_peer_scatter_dev(uocr_cuda_context *ctx, uint32_t layer, const void *d_hidden, uint32_t n,
+                                                 const uint32_t *d_all_offsets, char *error, size_t error_size) {
+    if (!check_call(ctx, layer, n, error, error_size)) return 0;
+    if (!d_hidden || !d_all_offsets) return fail(ctx, error, error_size, "null expert-parallel scatter argument");
+    const DLayer &L = ctx->layers[layer];
+    if (!peer_ready(ctx, L, error, error_size)) return 0;
+    auto &P = ctx->peer;
+    ArenaLayout a;
+    Scratch s = carve(ctx, L, ctx->token_capacity, &a);
+    const unsigned long long cap_rows = (unsigned long long)ctx->token_capacity * L.K;
+    CU_TRY(ctx, uocr::launch_ep_offsets(d_all_offsets, P.world, P.rank, L.E, P.row_capacity < cap_rows ? P.row_capacity : cap_rows,
+                                        P.d_dst_row0, (uint32_t *)(ctx->arena + a.seg_offsets), ctx->status, ctx->stream, &ctx->launches));
+    CU_TRY(ctx, uocr::launch_scatter_peer(L, s, (const __half *)d_hidden, n, L.E / P.world, P.d_dst_row0, P.recv_all,
+                                          P.row_capacity, ctx->stream, &ctx->launches));
+    return 1;
+}
+
+extern "C" int uocr_cuda_moe_ep_peer_experts_dev(uocr_cuda_context *ctx, uint32_t layer, char *error, size_t error_size) {
+    if (!ctx) return fail(nullptr, error, error_size, "null context");
+    if (layer >= ctx->layers.size()) return fail(ctx, error, error_size, "layer index %u out of range", layer);
+    const DLayer &L = ctx->layers[layer];
+    if (!uocr::gemm_path_supported(L)) return fail(ctx, error, error_size, "layer shape not supported by the tensor-core path");
+    if (!peer_ready(ctx, L, error, error_size)) return 0;
+    if (!ctx->arena) return fail(ctx, error, error_size, "arenas not allocated");
+    auto &P = ctx->peer;
+    ArenaLayout a;
+    Scratch s = carve(ctx, L, ctx->token_capacity, &a);
+    const uocr::GemmScratch g = gemm_scratch(ctx, s, a);
+    const uint32_t per = L.E / P.world;
+    const unsigned long long cap_rows = (unsigned long long)ctx->token_capacity * L.K;
+    const uint32_t bound = (uint32_t)(P.row_capacity < cap_rows ? P.row_capacity : cap_rows);      // rows this rank can hold
+    CU_TRY(ctx, uocr::launch_gemm_experts(L, s, g, (const uint32_t *)(ctx->arena + a.seg_offsets), P.world * per, P.rank * per, per,
+                                          P.recv, bound, g.mid_sorted, P.done, ctx->stream, &ctx->launches));
+    return 1;
 }
 
 extern "C" int uocr_cuda_moe_ep_peer_combine(uocr_cuda_context *ctx, uint32_t layer, const void *d_residual, uint32_t n,

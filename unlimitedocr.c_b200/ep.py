@@ -84,6 +84,32 @@ def dst_rows_from_counts(counts: np.ndarray, rank: int) -> np.ndarray:
     return out.astype(np.uint32)
 
 
+def balanced_placement(pairs_per_expert: np.ndarray, world: int) -> np.ndarray:
+    """Which expert sits in which slot so that the ranks' loads are even.  The library shards contiguous SLOT ranges
+    (rank g owns slots [g*E/G, (g+1)*E/G)); relabelling the experts of a layer (oracle.quant.permute_experts, or the
+    same permutation applied when the model is converted) therefore places them freely.  Longest-processing-time
+    rule: experts in descending order of their observed pair count, each to the rank with the least load that still
+    has a free slot.  Returns order[slot] = expert id; deterministic (ties: lower id first)."""
+    counts = np.asarray(pairs_per_expert, np.int64).reshape(-1)
+    n_experts = counts.shape[0]
+    if n_experts % world != 0:
+        raise ValueError(f"{n_experts} experts do not divide over {world} ranks")
+    per = n_experts // world
+    load = np.zeros(world, np.int64)
+    members: list[list[int]] = [[] for _ in range(world)]
+    for e in sorted(range(n_experts), key=lambda i: (-int(counts[i]), i)):
+        g = min((r for r in range(world) if len(members[r]) < per), key=lambda r: (int(load[r]), r))
+        members[g].append(e)
+        load[g] += counts[e]
+    return np.array([e for g in range(world) for e in sorted(members[g])], np.int64)
+
+
+def rank_loads(pairs_per_expert: np.ndarray, order: np.ndarray, world: int) -> np.ndarray:
+    """Pairs every rank receives when slot s holds expert order[s]."""
+    counts = np.asarray(pairs_per_expert, np.int64).reshape(-1)
+    return counts[np.asarray(order)].reshape(world, -1).sum(axis=1)
+
+
 class ExpertParallelLayer:
     """One mapped MoE layer whose routed experts are sharded over the ranks of a process group.
     The context must run on the stream the collectives use (ctx.set_stream(torch.cuda.current_stream().cuda_stream))."""
@@ -174,17 +200,34 @@ class PeerExpertParallelLayer:
         self._offsets = torch.zeros(n_experts + 1, dtype=torch.int32, device=device)
         self._all_offsets = torch.zeros((world, n_experts + 1), dtype=torch.int32, device=device)
         self._token = torch.zeros(1, dtype=torch.int32, device=device)
-        self.last_plan: ExchangePlan | None = None
 
     def _barrier(self) -> None:
         """Everything every rank has queued so far is done (a tiny all-reduce on the compute stream)."""
         if self.world > 1:
             self.dist.all_reduce(self._token, group=self.group)
 
-    def forward(self, hidden, out, *, residual=None) -> ExchangePlan:
+    def forward(self, hidden, out, *, residual=None) -> None:
+        """One layer call.  Nothing is read back to the host: the per-rank counts stay on the device (one all_gather),
+        the row offsets of the scatter and of the experts phase are computed there (last_plan reads them on demand)."""
         n = hidden.shape[0]
         self.ctx.ep_peer_dispatch(self.layer, hidden, n, self._offsets)
         self.ctx.ep_shared(self.layer, hidden, n)            # on the context's second stream, beside all that follows
+        if self.world == 1:
+            self._all_offsets.copy_(self._offsets.reshape(1, -1))
+        else:
+            self.dist.all_gather(list(self._all_offsets.unbind(0)), self._offsets, group=self.group)
+        self.ctx.ep_peer_scatter_dev(self.layer, hidden, n, self._all_offsets)
+        self._barrier()                                      # every rank's rows are in the owners' buffers
+        self.ctx.ep_peer_experts_dev(self.layer)
+        self._barrier()                                      # every owner's outputs are written
+        self.ctx.ep_peer_combine(self.layer, n, out, residual=residual)
+
+    def forward_host_counts(self, hidden, out, *, residual=None) -> ExchangePlan:
+        """The same call with the counts read back and the row offsets computed on the host (the earlier form, kept for
+        comparison and as the reference of the device-side arithmetic)."""
+        n = hidden.shape[0]
+        self.ctx.ep_peer_dispatch(self.layer, hidden, n, self._offsets)
+        self.ctx.ep_shared(self.layer, hidden, n)
         if self.world == 1:
             all_offsets = self._offsets.reshape(1, -1)
         else:
@@ -192,13 +235,17 @@ class PeerExpertParallelLayer:
             all_offsets = self._all_offsets
         counts = counts_from_offsets(all_offsets.cpu().numpy())
         plan = plan_from_counts(counts, self.rank)
-        self.last_plan = plan
         self.ctx.ep_peer_scatter(self.layer, hidden, n, dst_rows_from_counts(counts, self.rank))
-        self._barrier()                                      # every rank's rows are in the owners' buffers
+        self._barrier()
         self.ctx.ep_peer_experts(self.layer, plan.recv_counts)
-        self._barrier()                                      # every owner's outputs are written
+        self._barrier()
         self.ctx.ep_peer_combine(self.layer, n, out, residual=residual)
         return plan
+
+    @property
+    def last_plan(self) -> ExchangePlan:
+        """Row counts of the last forward call (reads the gathered offsets from the device)."""
+        return plan_from_counts(counts_from_offsets(self._all_offsets.cpu().numpy()), self.rank)
 
     def close(self, *, group_barrier: bool = True) -> None:
         """Unmap the peers' buffers and free this rank's.  A peer's scatter or combine kernel may still be reading or

@@ -55,7 +55,7 @@ EXPORTS = (
     "uocr_cuda_moe_ep_dispatch", "uocr_cuda_moe_ep_experts", "uocr_cuda_moe_ep_shared", "uocr_cuda_moe_ep_combine",
     "uocr_cuda_moe_ep_peer_create", "uocr_cuda_moe_ep_peer_open", "uocr_cuda_moe_ep_peer_destroy",
     "uocr_cuda_moe_ep_peer_dispatch", "uocr_cuda_moe_ep_peer_scatter", "uocr_cuda_moe_ep_peer_experts",
-    "uocr_cuda_moe_ep_peer_combine",
+    "uocr_cuda_moe_ep_peer_combine", "uocr_cuda_moe_ep_peer_scatter_dev", "uocr_cuda_moe_ep_peer_experts_dev",
 )
 
 
@@ -118,6 +118,8 @@ def load_library() -> C.CDLL:
         "uocr_cuda_moe_ep_peer_scatter": (C.c_int, [vp, u32, vp, u32, vp] + err),
         "uocr_cuda_moe_ep_peer_experts": (C.c_int, [vp, u32, u32, vp] + err),
         "uocr_cuda_moe_ep_peer_combine": (C.c_int, [vp, u32, vp, u32, vp] + err),
+        "uocr_cuda_moe_ep_peer_scatter_dev": (C.c_int, [vp, u32, vp, u32, vp] + err),
+        "uocr_cuda_moe_ep_peer_experts_dev": (C.c_int, [vp, u32] + err),
     }
     assert set(sig) == set(EXPORTS)
     for name, (res, args) in sig.items():
@@ -349,6 +351,14 @@ class Context:
     def ep_peer_experts(self, layer: int, segment_counts: np.ndarray) -> None:
         seg = np.ascontiguousarray(segment_counts, np.uint32)
         self._check(self._lib.uocr_cuda_moe_ep_peer_experts(self._h, layer, seg.shape[0], _np_ptr(seg), self._err, _ERR))
+
+    def ep_peer_scatter_dev(self, layer: int, hidden, n_tokens: int, all_offsets) -> None:
+        """all_offsets: device int32 [world, E + 1], every rank's expert offsets; row offsets are computed on the device."""
+        self._check(self._lib.uocr_cuda_moe_ep_peer_scatter_dev(self._h, layer, _dev_ptr(hidden), n_tokens, _dev_ptr(all_offsets),
+                                                                self._err, _ERR))
+
+    def ep_peer_experts_dev(self, layer: int) -> None:
+        self._check(self._lib.uocr_cuda_moe_ep_peer_experts_dev(self._h, layer, self._err, _ERR))
 
     def ep_peer_combine(self, layer: int, n_tokens: int, out, *, residual=None) -> None:
         self._check(self._lib.uocr_cuda_moe_ep_peer_combine(self._h, layer, _dev_ptr(residual), n_tokens, _dev_ptr(out),
