@@ -41,6 +41,18 @@ extern "C" {
 
 typedef struct uocr_cuda_context uocr_cuda_context;
 
+/* The engine's profile store and memory tracker (src/runtime/uocr_profile.h, src/runtime/uocr_memory.h).  This backend
+ * treats them as opaque and reaches them through the engine's own functions, which the engine passes along:
+ * uocr_profile_add_event_ms (src/runtime/uocr_profile.c:118-135) and uocr_memory_reserve / uocr_memory_release
+ * (src/runtime/uocr_memory.h:47-48) have exactly these signatures. */
+typedef struct uocr_profile_state uocr_profile_state;
+typedef struct uocr_memory_tracker uocr_memory_tracker;
+typedef void (*uocr_cuda_profile_add_event_ms_fn)(uocr_profile_state *profile, const char *name, double elapsed_ms);
+typedef int (*uocr_cuda_memory_account_fn)(uocr_memory_tracker *tracker, int category, uint64_t bytes);
+/* values of uocr_memory_category (include/unlimitedocr.h:50-62) this backend accounts under */
+#define UOCR_CUDA_MEMORY_MODEL_VIEWS 0
+#define UOCR_CUDA_MEMORY_MOE_SCRATCH 7
+
 /* One projection matrix [rows][cols], input dimension contiguous.
  * f16: qweight = fp16[rows][cols], qscale unused.
  * q8_0: qweight = int8[rows][cols], qscale = fp16[rows][cols/64].
@@ -105,6 +117,23 @@ UOCR_CUDA_API const char *uocr_cuda_context_last_error(const uocr_cuda_context *
 /* Use an existing cudaStream_t (passed as void*) instead of the context's own; NULL restores it.
  * (The legacy default stream is named by cudaStreamLegacy, not by NULL.) */
 UOCR_CUDA_API int uocr_cuda_context_set_stream(uocr_cuda_context *ctx, void *cuda_stream);
+/* Counterparts of uocr_metal_context_set_profile / _set_memory_tracker (src/backend/metal/uocr_metal.h:177-178).
+ * With a profile store set, every layer call brackets its phases with CUDA events on the stream they run on, and the
+ * durations are added to the store under the names below the next time the context waits for its stream
+ * (uocr_cuda_context_synchronize, the host-buffer calls, destroy).  Names follow the reference's
+ * (src/backend/metal/uocr_metal.m:14447-14496, :13509, :13902): cuda.decode.moe_layer_fused (single-token kernel: router,
+ * shared and routed experts in one launch), cuda.decode.moe_router, cuda.decode.moe_routed_experts, cuda.decode.moe_combine,
+ * cuda.decode.moe_matvec, cuda.prefill.moe_router, cuda.prefill.moe_plan, cuda.prefill.moe_shared_experts,
+ * cuda.prefill.moe_routed_bucketed_f16 / _q8 / _q4, cuda.prefill.moe_combine; uocr_cuda_profile_event_name(i) lists them
+ * (NULL past the end).  NULL switches profiling off.
+ * With a memory tracker set, the bytes of mapped weights are reserved under MODEL_VIEWS and the scratch arena under
+ * MOE_SCRATCH (and released when they are freed); bytes held when the tracker is set are reserved at once. */
+UOCR_CUDA_API void uocr_cuda_context_set_profile(uocr_cuda_context *ctx, uocr_profile_state *profile,
+                                                 uocr_cuda_profile_add_event_ms_fn add_event_ms);
+UOCR_CUDA_API void uocr_cuda_context_set_memory_tracker(uocr_cuda_context *ctx, uocr_memory_tracker *tracker,
+                                                        uocr_cuda_memory_account_fn reserve, uocr_cuda_memory_account_fn release);
+UOCR_CUDA_API const char *uocr_cuda_profile_event_name(uint32_t index);
+
 /* Detail profiling of the single-token stack call, the counterpart of the reference's per-op checkpoints
  * (UOCR_METAL_DECODER_PROFILE_DETAIL, src/backend/metal/uocr_metal.m:29-31, :14251-14297).  d_trace is a device
  * buffer of 128 * n_layers * 16 uint64: the SM clock of CTA c in layer l at point p sits at [(c * n_layers + l) * 16 + p].

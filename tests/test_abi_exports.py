@@ -57,3 +57,15 @@ def test_struct_layouts_match_the_header(pkg):
     assert C.sizeof(pkg.ffi.CMatrix) == 32
     assert pkg.ffi.CLayerDesc.expert_qweight.offset % 8 == 0
     assert C.sizeof(pkg.ffi.CLayerDesc) == 24 + 16 + 8 + 16 + 48 + 3 * 32
+
+
+def test_profile_event_names_follow_the_reference_naming():
+    """The names the backend reports phase durations under (no GPU needed): the reference's event names with the
+    backend prefix swapped (src/backend/metal/uocr_metal.m:14447-14496 `metal.decode.moe_router`,
+    `metal.decode.moe_shared_experts`, `metal.decode.moe_routed_experts`; :13509, :13902 `metal.prefill.moe_routed_bucketed_q8/_q4`)."""
+    import __graft_entry__ as entry
+    names = entry.load_package().ffi.profile_event_names()
+    assert len(names) == len(set(names)) and all(n.startswith(("cuda.decode.moe_", "cuda.prefill.moe_")) for n in names)
+    for wanted in ("cuda.decode.moe_router", "cuda.decode.moe_routed_experts", "cuda.prefill.moe_shared_experts",
+                   "cuda.prefill.moe_routed_bucketed_q4", "cuda.prefill.moe_routed_bucketed_q8", "cuda.prefill.moe_routed_bucketed_f16"):
+        assert wanted in names

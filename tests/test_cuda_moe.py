@@ -775,3 +775,75 @@ def test_large_prefill_configs(pkg, port, n, seed, qname, routing):
     err, cos = closeness(out[sub], want.out)
     assert err <= MAX_ABS and cos >= MIN_COS, (err, cos)
     assert np.all(np.isfinite(out))
+
+
+# ------------------------------------------------------------ engine hooks: profile store, memory tracker, threads
+
+def test_profile_store_and_memory_tracker_hooks(pkg):
+    """The hooks an engine passes its profile store and memory tracker through (here: Python callables standing in
+    for uocr_profile_add_event_ms / uocr_memory_reserve / uocr_memory_release): every regime reports its phases under
+    the documented names with positive durations, and the tracker sees exactly the bytes the context reports."""
+    L, _, _ = make(15, FULL, "q4_0", 1)
+    events, mem = [], {}
+    with pkg.Context() as ctx:
+        ctx.set_memory_tracker(lambda cat, b: mem.__setitem__(cat, mem.get(cat, 0) + b),
+                               lambda cat, b: mem.__setitem__(cat, mem.get(cat, 0) - b))
+        ctx.map_layer(L)
+        assert mem == {0: ctx.model_view_bytes}
+        ctx.allocate_runtime_arenas(256)
+        assert mem == {0: ctx.model_view_bytes, 7: ctx.moe_scratch_bytes} and mem[7] > 0
+        ctx.set_profile(lambda name, ms: events.append((name, ms)))
+        for n in (1, 8, 200):
+            hidden = quant.synth_activations(np.random.default_rng(n), n, FULL["H"])
+            ctx.layer_forward_host(0, hidden, hidden)
+        names = {e[0] for e in events}
+        assert {"cuda.decode.moe_layer_fused", "cuda.decode.moe_router", "cuda.decode.moe_routed_experts", "cuda.decode.moe_combine",
+                "cuda.prefill.moe_router", "cuda.prefill.moe_plan", "cuda.prefill.moe_shared_experts",
+                "cuda.prefill.moe_routed_bucketed_q4", "cuda.prefill.moe_combine"} <= names
+        assert names <= set(pkg.ffi.profile_event_names())
+        assert all(0.0 < ms < 100.0 for _, ms in events)
+        ctx.set_profile(None)
+        seen = len(events)
+        ctx.layer_forward_host(0, hidden, hidden)
+        assert len(events) == seen
+        ctx.release_runtime_arenas()
+        assert mem[7] == 0
+    assert mem == {0: 0, 7: 0}
+
+
+def test_two_contexts_on_two_threads(pkg):
+    """Distinct contexts may be created and used from distinct threads at the same time (the per-engine rule of
+    include/unlimitedocr.h:153-167): both threads get the result a single thread gets."""
+    import threading
+    rng = np.random.default_rng(16)
+    layers = [quant.synth_layer(rng, expert_qtype=quant.QTYPE_Q4_0, **FULL) for _ in range(2)]
+    hidden1 = quant.synth_activations(rng, 1, FULL["H"])
+    hidden9 = quant.synth_activations(rng, 9, FULL["H"])
+
+    def run(out, key):
+        try:
+            torch.cuda.set_device(0)
+            with pkg.Context() as ctx:
+                for L in layers:
+                    ctx.map_layer(L)
+                ctx.allocate_runtime_arenas(16)
+                res = []
+                for _ in range(5):
+                    res.append(ctx.stack_forward_host(0, 2, hidden1).copy())
+                    res.append(ctx.layer_forward_host(1, hidden9, hidden9).copy())
+                out[key] = res
+        except Exception as exc:       # reported by the main thread
+            out[key] = exc
+
+    want = {}
+    run(want, "single")
+    assert not isinstance(want["single"], Exception), want["single"]
+    got = {}
+    threads = [threading.Thread(target=run, args=(got, i)) for i in range(2)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    for i in range(2):
+        assert not isinstance(got[i], Exception), got[i]
+        assert all(np.array_equal(a, b) for a, b in zip(got[i], want["single"]))

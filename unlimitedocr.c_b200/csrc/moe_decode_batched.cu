@@ -532,6 +532,8 @@ cudaError_t init_decode_batched_kernels() {
                                 (int)BtSmem<UOCR_QT_Q8>::kTotal);
 }
 
+static std::atomic<int> g_bt_sms[64];
+
 uint32_t decode_batched_max_tokens() { return kBtMaxTokens; }
 
 // Scratch of a call with n tokens (n <= decode_batched_max_tokens()): the parts of the routed experts and of the shared
@@ -553,13 +555,25 @@ bool decode_batched_supported(const DLayer &L, uint32_t n) {
     return n >= 2 && n <= (uint32_t)kBtMaxTokens && L.K <= 16 && decode_sliced_layer_ok(L) && L.dec_units != nullptr;
 }
 
-static std::atomic<int> g_bt_sms[64];
+// The layer for n tokens in three launches: routing + activation bytes + dispatch plan (results in S), experts, combine.
+// scratch: a region of decode_batched_scratch(n, K).total bytes; ticket: a word that is zero before the first call
+// (every call leaves it zero).
+cudaError_t launch_batched_route(const DLayer &L, const Scratch &S, const __half *hidden, const float *injected, uint32_t n,
+                                 float *logits, float *probs, uint8_t *scratch, uint32_t *ticket, cudaStream_t st, uint64_t *launches) {
+    const BatchedScratchLayout lay = decode_batched_scratch(n, L.K);
+    RouteSmallParams r{};
+    r.hidden = hidden; r.router = L.router; r.bias = L.bias; r.injected = injected; r.n = n; r.K = L.K; r.scaling = L.scaling;
+    r.logits_out = logits; r.probs_out = probs; r.ids = S.top_ids; r.weights = S.top_weights;
+    r.x_limbs = reinterpret_cast<uint32_t *>(scratch + lay.x_limbs); r.x_scales = reinterpret_cast<float *>(scratch + lay.x_scales);
+    r.offsets = S.expert_offsets; r.pair_rows = S.pair_rows; r.inverse = S.inverse; r.active = S.active;
+    r.ticket = ticket; r.status = S.status;
+    if (L.expert_qtype == UOCR_QT_Q4) route_small_kernel<UOCR_QT_Q4><<<n, kRsThreads, 0, st>>>(r);
+    else route_small_kernel<UOCR_QT_Q8><<<n, kRsThreads, 0, st>>>(r);
+    ++*launches;
+    return cudaGetLastError();
+}
 
-// The whole layer for n tokens: routing (results in S), dispatch plan (in S), experts, combine.  scratch: a region of
-// decode_batched_scratch(n, K).total bytes; ticket: a word that is zero before the first call (every call leaves it zero).
-cudaError_t launch_decode_batched(const DLayer &L, const Scratch &S, const __half *hidden, const __half *residual,
-                                  const float *injected, uint32_t n, float *logits, float *probs, uint8_t *scratch,
-                                  uint32_t *ticket, __half *out, cudaStream_t st, uint64_t *launches) {
+cudaError_t launch_batched_experts(const DLayer &L, const Scratch &S, uint32_t n, uint8_t *scratch, cudaStream_t st, uint64_t *launches) {
     int dev = 0;
     cudaError_t err = cudaGetDevice(&dev);
     if (err != cudaSuccess) return err;
@@ -569,19 +583,10 @@ cudaError_t launch_decode_batched(const DLayer &L, const Scratch &S, const __hal
         if (dev >= 0 && dev < 64) g_bt_sms[dev] = sms;
     }
     const BatchedScratchLayout lay = decode_batched_scratch(n, L.K);
-    RouteSmallParams r{};
-    r.hidden = hidden; r.router = L.router; r.bias = L.bias; r.injected = injected; r.n = n; r.K = L.K; r.scaling = L.scaling;
-    r.logits_out = logits; r.probs_out = probs; r.ids = S.top_ids; r.weights = S.top_weights;
-    r.x_limbs = reinterpret_cast<uint32_t *>(scratch + lay.x_limbs); r.x_scales = reinterpret_cast<float *>(scratch + lay.x_scales);
-    r.offsets = S.expert_offsets; r.pair_rows = S.pair_rows; r.inverse = S.inverse; r.active = S.active;
-    r.ticket = ticket; r.status = S.status;
-    const bool q4 = L.expert_qtype == UOCR_QT_Q4;
-    if (q4) route_small_kernel<UOCR_QT_Q4><<<n, kRsThreads, 0, st>>>(r);
-    else route_small_kernel<UOCR_QT_Q8><<<n, kRsThreads, 0, st>>>(r);
-    if ((err = cudaGetLastError()) != cudaSuccess) return err;
-
     BatchedParams p{};
-    p.units = L.dec_units; p.x_limbs = r.x_limbs; p.x_scales = r.x_scales; p.n = n; p.K = L.K;
+    p.units = L.dec_units;
+    p.x_limbs = reinterpret_cast<const uint32_t *>(scratch + lay.x_limbs); p.x_scales = reinterpret_cast<const float *>(scratch + lay.x_scales);
+    p.n = n; p.K = L.K;
     p.active = S.active; p.expert_offsets = S.expert_offsets; p.pair_rows = S.pair_rows;
     p.routed_part = reinterpret_cast<float *>(scratch + lay.routed_part);
     p.shared_part = reinterpret_cast<float *>(scratch + lay.shared_part);
@@ -591,13 +596,20 @@ cudaError_t launch_decode_batched(const DLayer &L, const Scratch &S, const __hal
     const uint64_t max_entry_passes = (pairs < L.E ? pairs : L.E) + pairs / kBtTokens + kBtSharedHalves * ((n + kBtTokens - 1) / kBtTokens);
     const uint64_t max_items = max_entry_passes * kBtParts;
     const uint32_t grid = (uint32_t)(max_items < (uint64_t)sms ? max_items : (uint64_t)sms);
-    if (q4) decode_batched_kernel<UOCR_QT_Q4><<<grid, kBtThreads, BtSmem<UOCR_QT_Q4>::kTotal, st>>>(p);
+    if (L.expert_qtype == UOCR_QT_Q4) decode_batched_kernel<UOCR_QT_Q4><<<grid, kBtThreads, BtSmem<UOCR_QT_Q4>::kTotal, st>>>(p);
     else decode_batched_kernel<UOCR_QT_Q8><<<grid, kBtThreads, BtSmem<UOCR_QT_Q8>::kTotal, st>>>(p);
-    if ((err = cudaGetLastError()) != cudaSuccess) return err;
+    ++*launches;
+    return cudaGetLastError();
+}
+
+cudaError_t launch_batched_combine(const DLayer &L, const Scratch &S, const __half *residual, uint32_t n, uint8_t *scratch, __half *out,
+                                   cudaStream_t st, uint64_t *launches) {
+    const BatchedScratchLayout lay = decode_batched_scratch(n, L.K);
     const size_t work = (size_t)n * (L.H / 4);
-    combine_batched_kernel<<<(unsigned)((work + 255) / 256), 256, 0, st>>>(p.routed_part, p.shared_part, residual, S.inverse,
-                                                                           S.top_weights, n, L.H, L.K, out);
-    *launches += 3;
+    combine_batched_kernel<<<(unsigned)((work + 255) / 256), 256, 0, st>>>(
+        reinterpret_cast<const float *>(scratch + lay.routed_part), reinterpret_cast<const float *>(scratch + lay.shared_part), residual,
+        S.inverse, S.top_weights, n, L.H, L.K, out);
+    ++*launches;
     return cudaGetLastError();
 }
 

@@ -46,9 +46,11 @@ cudaError_t init_decode_batched_kernels();
 uint32_t decode_batched_max_tokens();
 BatchedScratchLayout decode_batched_scratch(uint32_t n, uint32_t K);
 bool decode_batched_supported(const DLayer &L, uint32_t n);
-cudaError_t launch_decode_batched(const DLayer &L, const Scratch &S, const __half *hidden, const __half *residual,
-                                  const float *injected, uint32_t n, float *logits, float *probs, uint8_t *scratch,
-                                  uint32_t *ticket, __half *out, cudaStream_t st, uint64_t *launches);
+cudaError_t launch_batched_route(const DLayer &L, const Scratch &S, const __half *hidden, const float *injected, uint32_t n,
+                                 float *logits, float *probs, uint8_t *scratch, uint32_t *ticket, cudaStream_t st, uint64_t *launches);
+cudaError_t launch_batched_experts(const DLayer &L, const Scratch &S, uint32_t n, uint8_t *scratch, cudaStream_t st, uint64_t *launches);
+cudaError_t launch_batched_combine(const DLayer &L, const Scratch &S, const __half *residual, uint32_t n, uint8_t *scratch, __half *out,
+                                   cudaStream_t st, uint64_t *launches);
 cudaError_t launch_dequant_probe(const DMatrix &m, float *out, cudaStream_t st, uint64_t *launches);
 cudaError_t launch_producer_probe(const DMatrix &m, float *out, cudaStream_t st, uint64_t *launches);
 int decode_grid_size();
@@ -127,8 +129,107 @@ struct uocr_cuda_context {
     bool shared_pending = false;          // an expert-parallel shared-MLP call is running on the second stream
     uint32_t seg_slot = 0;
     uint64_t launches = 0;
+    // engine hooks (the reference backend takes the engine's profile store and memory tracker the same way,
+    // src/backend/metal/uocr_metal.h:177-178): opaque objects plus the engine functions that act on them
+    uocr_profile_state *profile = nullptr;
+    uocr_cuda_profile_add_event_ms_fn profile_add = nullptr;
+    uocr_memory_tracker *mem_tracker = nullptr;
+    uocr_cuda_memory_account_fn mem_reserve = nullptr, mem_release = nullptr;
+    uint64_t tracked_model_bytes = 0, tracked_scratch_bytes = 0;     // what the tracker has been told so far
+    struct ProfSpan { const char *name; cudaEvent_t start, stop; };
+    std::vector<ProfSpan> prof_pending;      // spans whose events have been recorded and not yet read
+    std::vector<cudaEvent_t> prof_free;      // events ready for reuse
     char last_error[1024] = {0};
 };
+
+// ---- profile spans: two CUDA events around a phase; read (and handed to the engine's store) when the context next waits
+static const char *const kProfileEventNames[] = {
+    "cuda.decode.moe_layer_fused",            // single-token kernel: router, shared and routed experts, combine in one launch
+    "cuda.decode.moe_router",                 // few tokens: routing, activation bytes and dispatch plan
+    "cuda.decode.moe_routed_experts",         // few tokens: routed experts and shared MLP (one weight-streaming kernel)
+    "cuda.decode.moe_combine",
+    "cuda.decode.moe_matvec",                 // shapes off the other paths: the matrix-vector kernels
+    "cuda.prefill.moe_router",
+    "cuda.prefill.moe_plan",
+    "cuda.prefill.moe_shared_experts",
+    "cuda.prefill.moe_routed_bucketed_f16",
+    "cuda.prefill.moe_routed_bucketed_q8",
+    "cuda.prefill.moe_routed_bucketed_q4",
+    "cuda.prefill.moe_combine",
+};
+enum ProfileEvent { kPfFused, kPfRouter, kPfRouted, kPfCombine, kPfMatvec, kPfPrefillRouter, kPfPrefillPlan, kPfPrefillShared,
+                    kPfBucketedF16, kPfBucketedQ8, kPfBucketedQ4, kPfPrefillCombine, kPfCount };
+static_assert(sizeof(kProfileEventNames) / sizeof(kProfileEventNames[0]) == kPfCount, "one name per event");
+
+extern "C" const char *uocr_cuda_profile_event_name(uint32_t index) { return index < kPfCount ? kProfileEventNames[index] : nullptr; }
+
+static cudaEvent_t prof_event(uocr_cuda_context *ctx) {
+    if (!ctx->prof_free.empty()) { cudaEvent_t e = ctx->prof_free.back(); ctx->prof_free.pop_back(); return e; }
+    cudaEvent_t e = nullptr;
+    return cudaEventCreate(&e) == cudaSuccess ? e : nullptr;
+}
+
+// waits for the recorded spans and hands their durations to the engine's store
+static void prof_flush(uocr_cuda_context *ctx) {
+    for (auto &sp : ctx->prof_pending) {
+        float ms = 0.f;
+        if (cudaEventSynchronize(sp.stop) == cudaSuccess && cudaEventElapsedTime(&ms, sp.start, sp.stop) == cudaSuccess && ctx->profile_add)
+            ctx->profile_add(ctx->profile, sp.name, (double)ms);
+        ctx->prof_free.push_back(sp.start);
+        ctx->prof_free.push_back(sp.stop);
+    }
+    ctx->prof_pending.clear();
+}
+
+struct ProfScope {      // records the start event now and the stop event when it goes out of scope (same stream)
+    uocr_cuda_context *ctx;
+    cudaStream_t st;
+    int slot = -1;
+    ProfScope(uocr_cuda_context *c, int which, cudaStream_t stream) : ctx(c), st(stream) {
+        if (!ctx->profile_add) return;
+        if (ctx->prof_pending.size() >= 512) prof_flush(ctx);
+        cudaEvent_t a = prof_event(ctx), b = prof_event(ctx);
+        if (!a || !b) return;
+        cudaEventRecord(a, st);
+        ctx->prof_pending.push_back({kProfileEventNames[which], a, b});
+        slot = (int)ctx->prof_pending.size() - 1;
+    }
+    ~ProfScope() { if (slot >= 0) cudaEventRecord(ctx->prof_pending[slot].stop, st); }
+};
+
+static void track_memory(uocr_cuda_context *ctx) {      // brings the engine's tracker up to date with what the context holds
+    if (!ctx->mem_tracker) return;
+    auto sync = [&](int category, uint64_t now, uint64_t &told) {
+        if (now > told && ctx->mem_reserve) ctx->mem_reserve(ctx->mem_tracker, category, now - told);
+        if (now < told && ctx->mem_release) ctx->mem_release(ctx->mem_tracker, category, told - now);
+        told = now;
+    };
+    sync(UOCR_CUDA_MEMORY_MODEL_VIEWS, ctx->weight_bytes, ctx->tracked_model_bytes);
+    sync(UOCR_CUDA_MEMORY_MOE_SCRATCH, ctx->arena_bytes, ctx->tracked_scratch_bytes);
+}
+
+extern "C" void uocr_cuda_context_set_profile(uocr_cuda_context *ctx, uocr_profile_state *profile,
+                                              uocr_cuda_profile_add_event_ms_fn add_event_ms) {
+    if (!ctx) return;
+    prof_flush(ctx);
+    ctx->profile = profile;
+    ctx->profile_add = profile ? add_event_ms : nullptr;
+}
+
+extern "C" void uocr_cuda_context_set_memory_tracker(uocr_cuda_context *ctx, uocr_memory_tracker *tracker,
+                                                     uocr_cuda_memory_account_fn reserve, uocr_cuda_memory_account_fn release) {
+    if (!ctx) return;
+    if (ctx->mem_tracker) {      // hand back what the previous tracker was told
+        const uint64_t m = ctx->weight_bytes, a = ctx->arena_bytes;
+        ctx->weight_bytes = 0; ctx->arena_bytes = 0;
+        track_memory(ctx);
+        ctx->weight_bytes = m; ctx->arena_bytes = a;
+    }
+    ctx->mem_tracker = tracker; ctx->mem_reserve = tracker ? reserve : nullptr; ctx->mem_release = tracker ? release : nullptr;
+    ctx->tracked_model_bytes = 0; ctx->tracked_scratch_bytes = 0;
+    track_memory(ctx);
+}
+
 
 static thread_local char g_create_error[1024];
 
@@ -240,6 +341,7 @@ extern "C" void uocr_cuda_context_release_runtime_arenas(uocr_cuda_context *ctx)
     ctx->arena = nullptr;
     ctx->arena_bytes = 0;
     ctx->token_capacity = 0;
+    track_memory(ctx);
     cudaFreeHost(ctx->h_in); cudaFreeHost(ctx->h_res); cudaFreeHost(ctx->h_out);
     cudaFreeHost(ctx->h_ids); cudaFreeHost(ctx->h_wts);
     ctx->h_in = ctx->h_res = ctx->h_out = nullptr;
@@ -254,6 +356,7 @@ extern "C" void uocr_cuda_context_unmap_model(uocr_cuda_context *ctx) {
     ctx->weight_allocs.clear();
     ctx->layers.clear();
     ctx->weight_bytes = 0;
+    track_memory(ctx);
 }
 
 extern "C" void uocr_cuda_moe_ep_peer_destroy(uocr_cuda_context *ctx);
@@ -262,6 +365,9 @@ extern "C" void uocr_cuda_context_destroy(uocr_cuda_context *ctx) {
     if (!ctx) return;
     cudaSetDevice(ctx->device);
     if (ctx->own_stream) cudaStreamSynchronize(ctx->own_stream);
+    prof_flush(ctx);
+    for (cudaEvent_t e : ctx->prof_free) cudaEventDestroy(e);
+    ctx->prof_free.clear();
     uocr_cuda_moe_ep_peer_destroy(ctx);
     uocr_cuda_context_release_runtime_arenas(ctx);
     uocr_cuda_context_unmap_model(ctx);
@@ -297,6 +403,7 @@ extern "C" int uocr_cuda_context_synchronize(uocr_cuda_context *ctx, char *error
     if (!ctx) return fail(nullptr, error, error_size, "null context");
     CU_TRY(ctx, cudaMemcpyAsync(ctx->h_status, ctx->status, sizeof(uint32_t), cudaMemcpyDeviceToHost, ctx->stream));
     CU_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+    prof_flush(ctx);
     if (*ctx->h_status != 0) {
         const uint32_t st = *ctx->h_status;
         // clears the status word, the decode kernels' barrier counter and accumulators (they are off after an abort)
@@ -457,6 +564,7 @@ extern "C" int uocr_cuda_context_map_moe_layer(uocr_cuda_context *ctx, const uoc
     ctx->layers.push_back(L);
     CU_TRY(ctx, cudaMemcpy(ctx->d_layers, ctx->layers.data(), ctx->layers.size() * sizeof(DLayer), cudaMemcpyHostToDevice));
     if (out_layer_index) *out_layer_index = (uint32_t)ctx->layers.size() - 1;
+    track_memory(ctx);
     return 1;
 }
 
@@ -544,6 +652,7 @@ extern "C" int uocr_cuda_context_allocate_runtime_arenas(uocr_cuda_context *ctx,
     CU_TRY(ctx, cudaMalloc(&ctx->arena, bytes));
     ctx->arena_bytes = bytes;
     ctx->token_capacity = token_capacity;
+    track_memory(ctx);
     const size_t act = (size_t)token_capacity * m.H * 2;
     CU_TRY(ctx, cudaMallocHost(&ctx->h_in, act));
     CU_TRY(ctx, cudaMallocHost(&ctx->h_res, act));
@@ -688,11 +797,13 @@ static int layer_forward(uocr_cuda_context *ctx, uint32_t layer, const __half *d
     float *logits = dbg && dbg->d_router_logits ? dbg->d_router_logits : nullptr;
     float *probs = dbg && dbg->d_router_probs ? dbg->d_router_probs : nullptr;
     if (n == 1 && ctx->fused_decode && ctx->sliced_decode && uocr::decode_sliced_supported(ctx->layers.data(), layer, 1)) {
+        ProfScope span(ctx, kPfFused, ctx->stream);
         CU_TRY(ctx, uocr::launch_decode_sliced(ctx->layers.data(), ctx->d_layers, layer, 1, d_hidden, d_residual, nullptr, 0,
                                                d_injected, d_out, nullptr, decode_accumulators(ctx), &ctx->acc_base, ctx->status,
                                                logits, probs, s.top_ids, s.top_weights, nullptr, take_decode_knobs(ctx), ctx->stream,
                                                &ctx->launches));
     } else if (n == 1 && ctx->fused_decode && uocr::decode_supported(ctx->layers.data(), layer, 1)) {
+        ProfScope span(ctx, kPfFused, ctx->stream);
         CU_TRY(ctx, uocr::launch_decode_stack(ctx->layers.data(), ctx->d_layers, layer, 1, d_hidden, d_residual, 0,
                                               d_injected, d_out, (__half *)(ctx->arena + a.stack0),
                                               (__half *)(ctx->arena + a.stack1), (__half *)(ctx->arena + a.dec_mid),
@@ -702,30 +813,58 @@ static int layer_forward(uocr_cuda_context *ctx, uint32_t layer, const __half *d
     } else if (n >= 2 && ctx->batched_decode && uocr::decode_batched_supported(L, n)) {
         // a few tokens at the model's shapes: routing + plan, ONE weight-streaming kernel for the routed experts and the
         // shared MLP, and the combine
-        CU_TRY(ctx, uocr::launch_decode_batched(L, s, d_hidden, d_residual, d_injected, n, logits, probs, ctx->arena + a.bt_routed,
-                                                batched_ticket(ctx), d_out, ctx->stream, &ctx->launches));
+        uint8_t *scratch = ctx->arena + a.bt_routed;
+        {
+            ProfScope span(ctx, kPfRouter, ctx->stream);
+            CU_TRY(ctx, uocr::launch_batched_route(L, s, d_hidden, d_injected, n, logits, probs, scratch, batched_ticket(ctx), ctx->stream,
+                                                   &ctx->launches));
+        }
+        {
+            ProfScope span(ctx, kPfRouted, ctx->stream);
+            CU_TRY(ctx, uocr::launch_batched_experts(L, s, n, scratch, ctx->stream, &ctx->launches));
+        }
+        ProfScope span(ctx, kPfCombine, ctx->stream);
+        CU_TRY(ctx, uocr::launch_batched_combine(L, s, d_residual, n, scratch, d_out, ctx->stream, &ctx->launches));
     } else if (n >= ctx->gemm_min_tokens && uocr::gemm_path_supported(L)) {
         // The shared MLP needs neither the routing nor the permutation: it runs on a second stream beside the router,
         // the dispatch plan, the gather and the routed experts, whose small kernels leave most SMs idle.
         const uocr::GemmScratch g = gemm_scratch(ctx, s, a);
         CU_TRY(ctx, cudaEventRecord(ctx->fork_event, ctx->stream));
         CU_TRY(ctx, cudaStreamWaitEvent(ctx->side_stream, ctx->fork_event, 0));
-        CU_TRY(ctx, uocr::launch_gemm_shared(L, s, g, d_hidden, n, ctx->side_stream, &ctx->launches));
+        {
+            ProfScope span(ctx, kPfPrefillShared, ctx->side_stream);
+            CU_TRY(ctx, uocr::launch_gemm_shared(L, s, g, d_hidden, n, ctx->side_stream, &ctx->launches));
+        }
         CU_TRY(ctx, cudaEventRecord(ctx->join_event, ctx->side_stream));
-        CU_TRY(ctx, uocr::launch_router(L, d_hidden, d_injected, n, logits, probs, s.top_ids, s.top_weights, ctx->status,
-                                        s.logits, ctx->stream, &ctx->launches));
-        CU_TRY(ctx, uocr::launch_dispatch_plan(s.top_ids, n, L.K, L.E, s.expert_offsets, s.pair_rows, s.inverse,
-                                               s.active, s.plan_counts, ctx->stream, &ctx->launches));
-        CU_TRY(ctx, uocr::launch_gather_sorted(L, s, d_hidden, n, g.x_sorted, ctx->stream, &ctx->launches));
-        CU_TRY(ctx, uocr::launch_gemm_experts(L, s, g, s.expert_offsets, L.E, 0, L.E, g.x_sorted, n * L.K, g.mid_sorted,
-                                              g.down_sorted, ctx->stream, &ctx->launches));
+        {
+            ProfScope span(ctx, kPfPrefillRouter, ctx->stream);
+            CU_TRY(ctx, uocr::launch_router(L, d_hidden, d_injected, n, logits, probs, s.top_ids, s.top_weights, ctx->status,
+                                            s.logits, ctx->stream, &ctx->launches));
+        }
+        {
+            ProfScope span(ctx, kPfPrefillPlan, ctx->stream);
+            CU_TRY(ctx, uocr::launch_dispatch_plan(s.top_ids, n, L.K, L.E, s.expert_offsets, s.pair_rows, s.inverse,
+                                                   s.active, s.plan_counts, ctx->stream, &ctx->launches));
+            CU_TRY(ctx, uocr::launch_gather_sorted(L, s, d_hidden, n, g.x_sorted, ctx->stream, &ctx->launches));
+        }
+        {
+            ProfScope span(ctx, L.expert_qtype == UOCR_QT_Q4 ? kPfBucketedQ4 : (L.expert_qtype == UOCR_QT_Q8 ? kPfBucketedQ8 : kPfBucketedF16),
+                           ctx->stream);
+            CU_TRY(ctx, uocr::launch_gemm_experts(L, s, g, s.expert_offsets, L.E, 0, L.E, g.x_sorted, n * L.K, g.mid_sorted,
+                                                  g.down_sorted, ctx->stream, &ctx->launches));
+        }
         CU_TRY(ctx, cudaStreamWaitEvent(ctx->stream, ctx->join_event, 0));
+        ProfScope span(ctx, kPfPrefillCombine, ctx->stream);
         CU_TRY(ctx, uocr::launch_gemm_combine(L, s, g, g.down_sorted, d_residual, n, d_out, ctx->stream, &ctx->launches));
     } else {
-        CU_TRY(ctx, uocr::launch_router(L, d_hidden, d_injected, n, logits, probs, s.top_ids, s.top_weights, ctx->status,
-                                        s.logits, ctx->stream, &ctx->launches));
-        CU_TRY(ctx, uocr::launch_dispatch_plan(s.top_ids, n, L.K, L.E, s.expert_offsets, s.pair_rows, s.inverse,
-                                               s.active, s.plan_counts, ctx->stream, &ctx->launches));
+        {
+            ProfScope span(ctx, kPfRouter, ctx->stream);
+            CU_TRY(ctx, uocr::launch_router(L, d_hidden, d_injected, n, logits, probs, s.top_ids, s.top_weights, ctx->status,
+                                            s.logits, ctx->stream, &ctx->launches));
+            CU_TRY(ctx, uocr::launch_dispatch_plan(s.top_ids, n, L.K, L.E, s.expert_offsets, s.pair_rows, s.inverse,
+                                                   s.active, s.plan_counts, ctx->stream, &ctx->launches));
+        }
+        ProfScope span(ctx, kPfMatvec, ctx->stream);
         CU_TRY(ctx, uocr::launch_small_batch_layer(L, s, d_hidden, d_residual, n, d_out, ctx->stream, &ctx->launches));
     }
     if (dbg && dbg->d_top_ids)
@@ -769,6 +908,7 @@ static int stack_forward(uocr_cuda_context *ctx, uint32_t first, uint32_t count,
     Scratch s = carve(ctx, ctx->layers[first], n, &a);
     __half *buf[2] = {(__half *)(ctx->arena + a.stack0), (__half *)(ctx->arena + a.stack1)};
     if (stack_uses_sliced_decode(ctx, first, count, n)) {
+        ProfScope span(ctx, kPfFused, ctx->stream);
         CU_TRY(ctx, uocr::launch_decode_sliced(ctx->layers.data(), ctx->d_layers, first, count, d_hidden, d_hidden, h_inline, 1,
                                                nullptr, d_out, host_status, decode_accumulators(ctx), &ctx->acc_base, ctx->status, nullptr,
                                                nullptr, s.top_ids, s.top_weights, ctx->decode_trace, take_decode_knobs(ctx), ctx->stream,
@@ -850,6 +990,7 @@ extern "C" int uocr_cuda_moe_stack_forward_host(uocr_cuda_context *ctx, uint32_t
         *ctx->h_status = 0xffffffffu;
         if (!stack_forward(ctx, first, count, d_in, n, ctx->h_out_dev, error, error_size, h_hidden, ctx->h_status_dev)) return 0;
         CU_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+        prof_flush(ctx);
         if (*(volatile uint32_t *)ctx->h_status != 0) {       // the kernel gave up, or flagged something: read the device word
             if (!uocr_cuda_context_synchronize(ctx, error, error_size)) return 0;
             return fail(ctx, error, error_size, "the decode kernel ended without writing its result");

@@ -43,10 +43,14 @@ class CDebugOutputs(C.Structure):
                 ("d_top_weights", C.c_void_p)]
 
 
+PROFILE_ADD_EVENT_FN = C.CFUNCTYPE(None, C.c_void_p, C.c_char_p, C.c_double)       # uocr_profile_add_event_ms
+MEMORY_ACCOUNT_FN = C.CFUNCTYPE(C.c_int, C.c_void_p, C.c_int, C.c_uint64)          # uocr_memory_reserve / _release
+
 EXPORTS = (
     "uocr_cuda_is_available", "uocr_cuda_backend_name", "uocr_cuda_device_count", "uocr_cuda_context_create",
     "uocr_cuda_context_destroy", "uocr_cuda_context_last_error", "uocr_cuda_context_set_stream",
-    "uocr_cuda_context_set_profile_detail", "uocr_cuda_context_synchronize", "uocr_cuda_context_kernel_launches", "uocr_cuda_context_model_view_bytes",
+    "uocr_cuda_context_set_profile_detail", "uocr_cuda_context_set_profile", "uocr_cuda_context_set_memory_tracker",
+    "uocr_cuda_profile_event_name", "uocr_cuda_context_synchronize", "uocr_cuda_context_kernel_launches", "uocr_cuda_context_model_view_bytes",
     "uocr_cuda_context_moe_scratch_bytes", "uocr_cuda_context_map_moe_layer", "uocr_cuda_context_unmap_model",
     "uocr_cuda_context_moe_layer_count", "uocr_cuda_context_allocate_runtime_arenas",
     "uocr_cuda_context_release_runtime_arenas", "uocr_cuda_moe_scratch_size", "uocr_cuda_moe_router",
@@ -57,6 +61,15 @@ EXPORTS = (
     "uocr_cuda_moe_ep_peer_dispatch", "uocr_cuda_moe_ep_peer_scatter", "uocr_cuda_moe_ep_peer_experts",
     "uocr_cuda_moe_ep_peer_combine", "uocr_cuda_moe_ep_peer_scatter_dev", "uocr_cuda_moe_ep_peer_experts_dev",
 )
+
+
+def profile_event_names() -> list[str]:
+    """Names under which the backend reports phase durations to the engine's profile store."""
+    lib, out, i = load_library(), [], 0
+    while (name := lib.uocr_cuda_profile_event_name(i)) is not None:
+        out.append(name.decode())
+        i += 1
+    return out
 
 
 def library_path() -> Path:
@@ -88,6 +101,9 @@ def load_library() -> C.CDLL:
         "uocr_cuda_context_last_error": (cp, [vp]),
         "uocr_cuda_context_set_stream": (C.c_int, [vp, vp]),
         "uocr_cuda_context_set_profile_detail": (C.c_int, [vp, vp]),
+        "uocr_cuda_context_set_profile": (None, [vp, vp, PROFILE_ADD_EVENT_FN]),
+        "uocr_cuda_context_set_memory_tracker": (None, [vp, vp, MEMORY_ACCOUNT_FN, MEMORY_ACCOUNT_FN]),
+        "uocr_cuda_profile_event_name": (cp, [u32]),
         "uocr_cuda_context_synchronize": (C.c_int, [vp] + err),
         "uocr_cuda_context_kernel_launches": (u64, [vp]),
         "uocr_cuda_context_model_view_bytes": (u64, [vp]),
@@ -231,6 +247,9 @@ class Context:
         self._layer_e[idx.value] = desc.n_experts
         return idx.value
 
+    def release_runtime_arenas(self) -> None:
+        self._lib.uocr_cuda_context_release_runtime_arenas(self._h)
+
     def unmap_model(self) -> None:
         self._lib.uocr_cuda_context_unmap_model(self._h)
 
@@ -244,6 +263,22 @@ class Context:
         if cuda_stream == 0:
             cuda_stream = 1   # cudaStreamLegacy
         self._check(self._lib.uocr_cuda_context_set_stream(self._h, cuda_stream))
+
+    def set_profile(self, add_event_ms) -> None:
+        """add_event_ms(name: str, ms: float) receives the duration of every phase (see the header for the names); None
+        switches it off.  Stands in for the engine's profile store."""
+        if add_event_ms is None:
+            self._profile_cb = None
+            self._lib.uocr_cuda_context_set_profile(self._h, None, PROFILE_ADD_EVENT_FN())
+            return
+        self._profile_cb = PROFILE_ADD_EVENT_FN(lambda _store, name, ms: add_event_ms(name.decode(), ms))
+        self._lib.uocr_cuda_context_set_profile(self._h, 1, self._profile_cb)
+
+    def set_memory_tracker(self, reserve, release) -> None:
+        """reserve(category: int, bytes: int) / release(category, bytes): stand-ins for the engine's memory tracker."""
+        self._mem_cbs = (MEMORY_ACCOUNT_FN(lambda _t, cat, b: (reserve(cat, b), 1)[1]),
+                         MEMORY_ACCOUNT_FN(lambda _t, cat, b: (release(cat, b), 1)[1]))
+        self._lib.uocr_cuda_context_set_memory_tracker(self._h, 1, *self._mem_cbs)
 
     def set_profile_detail(self, trace) -> None:
         """Device buffer (128 * n_layers * 16 int64) that single-token stack calls fill with per-phase SM clocks:
