@@ -428,6 +428,8 @@ def measure_batched_decode(pkg, torch, flush_l2, steps: int, warmup: int) -> dic
                                      "algorithmic_bytes_per_step": nbytes, "achieved_gbs": achieved, "frac": achieved / peak,
                                      "frac_of_nominal_8TBs": achieved / NOMINAL_HBM_GBS, "gpu_launches_per_step": int(launches),
                                      "served_by": ctx.regime_name(0, n)}
+    traffic, source = captured_traffic("decode_batched_kernel__batched_q8.md", "moe_decode_batched.cu")
+    out["tokens"]["8"]["traffic"], out["tokens"]["8"]["traffic_source"] = traffic, source + " (the weight-streaming kernel of the three)"
     return out
 
 
@@ -569,6 +571,40 @@ def measure_ep(pkg, torch, dist, rank: int, world: int, flush_l2, steps: int, wa
 
 # ------------------------------------------------------------------------------------------ decode (headline)
 
+TRACE_POINTS = [("activations_in_smem", 0), ("own_router_logits", 8), ("logits_exchanged", 9), ("expert_chosen", 1),
+                ("weight_fetch_issued", 2), ("first_chunk_in_smem", 3), ("gate_up_chunk0", 10), ("chunk2_arrived", 11),
+                ("gate_up_chunk2", 12), ("last_groups_arrived", 13), ("own_sums", 14), ("all_warps_sums", 15),
+                ("swiglu_products", 4), ("partial_outputs", 5), ("partial_sums_sent", 6), ("layer_output_complete", 7)]
+
+
+def decode_timeline(ctx, torch, d_hidden, d_out, flush_l2, sm_mhz: float) -> dict:
+    """Per-layer timeline of the one-launch decode kernel from its own clock stamps (uocr_cuda_context_set_profile_detail):
+    microseconds since the previous layer's output was complete, mean over CTAs and layers 1..10 and mean over layers of
+    the slowest CTA, for the 84 routed-expert CTAs and the 28 shared-MLP CTAs."""
+    n_cta, n_pts = 128, 16
+    trace = torch.zeros(n_cta * N_LAYERS * n_pts, dtype=torch.int64, device="cuda")
+    ctx.set_profile_detail(trace)
+    for i in range(3):
+        flush_l2(i)
+        ctx.stack_forward(0, N_LAYERS, d_hidden, 1, d_out)
+        torch.cuda.synchronize()
+    ctx.set_profile_detail(None)
+    t = trace.cpu().numpy().reshape(n_cta, N_LAYERS, n_pts).astype(np.float64)
+    if not t[:112, :, 7].all():
+        return {"unavailable": "the decode kernel in use writes no clock stamps"}
+    per_us = sm_mhz
+
+    def table(rows):
+        rel = (t[rows, 1:, :] - t[rows, :-1, 7:8]) / per_us
+        mean, slow = rel.mean((0, 1)), rel.max(0).mean(0)
+        return {name: [round(float(mean[i]), 3), round(float(slow[i]), 3)] for name, i in TRACE_POINTS}
+
+    return {"columns": "[mean, slowest CTA] in us since the previous layer's output was complete", "sm_mhz_assumed": sm_mhz,
+            "routed_ctas": table(slice(0, 84)), "shared_mlp_ctas": table(slice(84, 112)),
+            "kernel_entry_to_first_layer_us": round(float((t[0, 0, 0] - t[127, 0, 0]) / per_us), 3),
+            "kernel_entry_to_exit_us": round(float((t[127, 0, 1] - t[127, 0, 0]) / per_us), 3)}
+
+
 def measure_decode(pkg, torch, dist, rank: int, local_rank: int, world: int, flush_l2, args) -> dict | None:
     """One token through the 11-layer stack (N replicas when launched on N GPUs)."""
     layers, hidden = synth_stack(N_LAYERS, "q4_0", SEED_DECODE)
@@ -606,6 +642,9 @@ def measure_decode(pkg, torch, dist, rank: int, local_rank: int, world: int, flu
     e2e_ms = sum(e2e_times) / len(e2e_times) * 1e3
     assert np.array_equal(host_out, d_out.cpu().numpy().view(np.uint16)), "host and device entry points disagree"
     clocks = sampler.stop() if sampler else None
+    timeline = None
+    if rank == 0 and args.extras == "all":
+        timeline = decode_timeline(ctx, torch, d_hidden, d_out, flush_l2, float((clocks or {}).get("sm_mhz") or 1965.0))
 
     t = torch.tensor([ms_per_step, e2e_ms], dtype=torch.float64, device="cuda")
     if world > 1:
@@ -638,6 +677,8 @@ def measure_decode(pkg, torch, dist, rank: int, local_rank: int, world: int, flu
         "per_layer_us": ms_per_step * 1e3 / N_LAYERS,
         "step_ms_min_max": [min(times_ms), max(times_ms)],
     }
+    if timeline is not None:
+        line["decode_timeline_us"] = timeline
     if not args.no_cpu_baseline:
         from oracle import oracle as orc
         threads = orc.host_threads()

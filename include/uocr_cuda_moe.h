@@ -159,6 +159,65 @@ UOCR_CUDA_API uint64_t uocr_cuda_context_moe_scratch_bytes(const uocr_cuda_conte
 UOCR_CUDA_API int uocr_cuda_context_map_moe_layer(uocr_cuda_context *ctx, const uocr_cuda_moe_layer_desc *h_desc,
                                                   uint32_t *out_layer_index, char *error, size_t error_size);
 UOCR_CUDA_API void uocr_cuda_context_unmap_model(uocr_cuda_context *ctx);
+
+/* One entry of a .uocr file's tensor directory, byte for byte as the file stores it
+ * (uocr_tensor_entry, src/model/uocr_format.h:275-299: packed, 140 bytes, sorted by id). */
+#pragma pack(push, 1)
+typedef struct uocr_cuda_tensor_entry {
+    uint32_t id;                  /* src/model/uocr_tensor_registry.h:22-124 */
+    uint32_t family;
+    int32_t layer;
+    int32_t expert;
+    uint32_t projection;
+    uint32_t usage;               /* 1 = runtime */
+    uint32_t qtype;               /* 1 f16, 3 q8_0, 4 q4_0 */
+    uint32_t flags;               /* bit 0 = row major */
+    uint32_t rank;
+    uint32_t logical_shape[4];
+    uint32_t physical_shape[4];
+    uint64_t payload_offset;      /* from the start of the file */
+    uint64_t payload_size;
+    uint32_t block_size;
+    uint32_t row_size;
+    uint64_t scale_offset;
+    uint64_t scale_size;
+    uint64_t min_offset;
+    uint64_t min_size;
+    uint32_t qtype_reason;
+    uint32_t promotion_reason;
+    uint32_t source_name_offset;
+    uint32_t source_name_size;
+} uocr_cuda_tensor_entry;
+#pragma pack(pop)
+
+/* What the backend needs of an opened model file: the fields of the engine's uocr_model_file
+ * (src/model/uocr_model_file.h:9-28) and of its config record (src/model/uocr_format.h:193-225) that concern the
+ * decoder's MoE layers.  The engine fills it from the file it has already opened and validated:
+ *   data, size, tensors, tensor_count      <- model->data, ->size, ->tensors, ->tensor_count
+ *   routed_experts, moe_top_k              <- model->config->routed_experts, ->moe_top_k
+ *   first_moe_layer, moe_layer_count       <- config->dense_first_layers, config->decoder_layers - dense_first_layers
+ *   routed_scaling_factor                  <- UOCR_MOE_ROUTED_SCALING_FACTOR (src/model/uocr_constants.h:54) */
+typedef struct uocr_cuda_model_file_view {
+    const void *data;
+    uint64_t size;
+    const void *tensors;          /* uocr_cuda_tensor_entry[tensor_count], inside [data, data + size) */
+    uint32_t tensor_count;
+    uint32_t routed_experts;
+    uint32_t moe_top_k;
+    uint32_t first_moe_layer;
+    uint32_t moe_layer_count;
+    float routed_scaling_factor;
+} uocr_cuda_model_file_view;
+
+/* Counterpart of uocr_metal_context_map_model (src/backend/metal/uocr_metal.h:180) for the MoE layers: looks up the
+ * router, the three shared projections and every routed expert's three projections of each requested decoder layer
+ * by tensor id, checks them (runtime usage, row-major rank 2, shapes agree, byte ranges inside the file), checks
+ * that the routed experts form ONE interleaved-contiguous slab of packed weights and one of scales, as the
+ * reference host does before it binds a layer (src/backend/metal/uocr_metal.m:3037-3154, same error texts), and
+ * uploads each layer once.  File layer first_moe_layer + i becomes layer i of this context.  A file that fails
+ * any check leaves the context without layers. */
+UOCR_CUDA_API int uocr_cuda_context_map_model(uocr_cuda_context *ctx, const uocr_cuda_model_file_view *model,
+                                              char *error, size_t error_size);
 UOCR_CUDA_API uint32_t uocr_cuda_context_moe_layer_count(const uocr_cuda_context *ctx);
 
 /* ---- scratch: counterpart of uocr_metal_context_allocate_runtime_arenas / _release_runtime_arenas

@@ -426,6 +426,128 @@ extern "C" int uocr_cuda_context_synchronize(uocr_cuda_context *ctx, char *error
 extern "C" uint64_t uocr_cuda_context_kernel_launches(const uocr_cuda_context *ctx) { return ctx ? ctx->launches : 0; }
 extern "C" uint64_t uocr_cuda_context_model_view_bytes(const uocr_cuda_context *ctx) { return ctx ? ctx->weight_bytes : 0; }
 extern "C" uint64_t uocr_cuda_context_moe_scratch_bytes(const uocr_cuda_context *ctx) { return ctx ? ctx->arena_bytes : 0; }
+// ---- mapping from an opened .uocr model file -----------------------------------------------------------------------
+// The tensor directory is the file's own packed array of 140-byte entries sorted by id (src/model/uocr_format.h:275-299;
+// the loader checks the order, src/model/uocr_model_file.c:885-895), so a tensor is found by binary search as
+// uocr_model_file_find_tensor does.  Ids follow src/model/uocr_tensor_registry.h:22-124.
+static_assert(sizeof(uocr_cuda_tensor_entry) == 140, "the on-disk tensor entry has 140 bytes");
+
+namespace {
+constexpr uint32_t kIdLayerBase = 10000, kIdLayerStride = 1000, kIdRouter = 40, kIdSharedGate = 50, kIdExpertBase = 100;
+constexpr uint32_t kUsageRuntime = 1, kFlagRowMajor = 1;
+
+const uocr_cuda_tensor_entry *find_entry(const uocr_cuda_model_file_view *m, uint32_t id) {
+    const uocr_cuda_tensor_entry *t = (const uocr_cuda_tensor_entry *)m->tensors;
+    uint32_t lo = 0, hi = m->tensor_count;
+    while (lo < hi) {
+        const uint32_t mid = lo + (hi - lo) / 2;
+        if (t[mid].id == id) return &t[mid];
+        if (t[mid].id < id) lo = mid + 1; else hi = mid;
+    }
+    return nullptr;
+}
+
+// One projection of the file checked against what this backend can consume: a runtime, row-major, rank-2 tensor of a
+// known qtype whose byte ranges lie inside the file and are as long as the shape says.
+const char *check_entry(const uocr_cuda_model_file_view *m, const uocr_cuda_tensor_entry *t) {
+    if (!t) return "is missing from the tensor directory";
+    if (t->usage != kUsageRuntime) return "is not a runtime tensor";
+    if (t->rank != 2 || !(t->flags & kFlagRowMajor)) return "is not a row-major matrix";
+    if (t->qtype != UOCR_QT_F16 && t->qtype != UOCR_QT_Q8 && t->qtype != UOCR_QT_Q4) return "has an unsupported qtype";
+    const uint64_t rows = t->logical_shape[0], cols = t->logical_shape[1];
+    if (rows == 0 || cols == 0 || t->physical_shape[0] != rows || t->physical_shape[1] != cols) return "has an invalid shape";
+    if (t->qtype != UOCR_QT_F16 && cols % UOCR_GROUP) return "has a width that is no multiple of the quantisation group";
+    const uint64_t want = t->qtype == UOCR_QT_F16 ? rows * cols * 2 : t->qtype == UOCR_QT_Q8 ? rows * cols : rows * cols / 2;
+    if (t->payload_size != want) return "has a payload size that does not match its shape";
+    if (t->payload_offset > m->size || t->payload_size > m->size - t->payload_offset) return "has a payload outside the file";
+    if (t->payload_offset % 16) return "has a payload that is not 16-byte aligned";
+    if (t->qtype != UOCR_QT_F16) {
+        if (t->scale_size != rows * (cols / UOCR_GROUP) * 2) return "has a scale size that does not match its shape";
+        if (t->scale_offset > m->size || t->scale_size > m->size - t->scale_offset) return "has scales outside the file";
+        if (t->scale_offset % 16) return "has scales that are not 16-byte aligned";
+    }
+    return nullptr;
+}
+
+uocr_cuda_matrix matrix_of(const uocr_cuda_model_file_view *m, const uocr_cuda_tensor_entry *t) {
+    const uint8_t *base = (const uint8_t *)m->data;
+    return uocr_cuda_matrix{(int32_t)t->qtype, t->logical_shape[0], t->logical_shape[1], base + t->payload_offset,
+                            t->qtype == UOCR_QT_F16 ? nullptr : base + t->scale_offset};
+}
+}  // namespace
+
+extern "C" int uocr_cuda_context_map_model(uocr_cuda_context *ctx, const uocr_cuda_model_file_view *m, char *error,
+                                           size_t error_size) {
+    if (!ctx || !m) return fail(ctx, error, error_size, "null context or model view");
+    if (!m->data || !m->tensors || m->tensor_count == 0) return fail(ctx, error, error_size, "model view without data or tensor directory");
+    if ((const uint8_t *)m->tensors < (const uint8_t *)m->data ||
+        (uint64_t)((const uint8_t *)m->tensors - (const uint8_t *)m->data) + (uint64_t)m->tensor_count * sizeof(uocr_cuda_tensor_entry) > m->size)
+        return fail(ctx, error, error_size, "tensor directory lies outside the model file");
+    if (m->moe_layer_count == 0) return fail(ctx, error, error_size, "no MoE layer requested");
+    if (!ctx->layers.empty()) return fail(ctx, error, error_size, "a model is already mapped; call uocr_cuda_context_unmap_model first");
+    const uint32_t E = m->routed_experts, K = m->moe_top_k;
+    if (E == 0 || E > 256 || K == 0 || K > E) return fail(ctx, error, error_size, "invalid router configuration (experts %u, top_k %u)", E, K);
+
+    // every layer is checked before the first one is uploaded, so a refused file leaves the context empty
+    auto one_layer = [&](uint32_t layer, bool upload_it) -> int {
+        const uint32_t lbase = kIdLayerBase + layer * kIdLayerStride;
+        const uocr_cuda_tensor_entry *router = find_entry(m, lbase + kIdRouter);
+        const uocr_cuda_tensor_entry *shared[3], *gate0 = find_entry(m, lbase + kIdExpertBase);
+        const char *why = check_entry(m, router);
+        if (why) return fail(ctx, error, error_size, "layer %u: MoE router %s", layer, why);
+        static const char *kProj[3] = {"gate", "up", "down"};
+        for (int p = 0; p < 3; ++p) {
+            shared[p] = find_entry(m, lbase + kIdSharedGate + p);
+            if ((why = check_entry(m, shared[p]))) return fail(ctx, error, error_size, "layer %u: MoE shared %s %s", layer, kProj[p], why);
+        }
+        if ((why = check_entry(m, gate0))) return fail(ctx, error, error_size, "layer %u: MoE expert 0 gate %s", layer, why);
+        if (router->qtype != UOCR_QT_F16) return fail(ctx, error, error_size, "layer %u: the MoE router must be fp16", layer);
+        const uint32_t H = router->logical_shape[1], F = gate0->logical_shape[0], S = shared[0]->logical_shape[0];
+        if (router->logical_shape[0] != E) return fail(ctx, error, error_size, "layer %u: router has %u rows for %u experts", layer, router->logical_shape[0], E);
+        if (gate0->logical_shape[1] != H) return fail(ctx, error, error_size, "layer %u: expert gate width %u differs from the hidden size %u", layer, gate0->logical_shape[1], H);
+
+        // the expert slab: every expert's gate, up and down follow one another without a gap, packed weights in one
+        // run and scales in another — the rule of src/backend/metal/uocr_metal.m:3037-3154
+        const uint32_t qt = gate0->qtype;
+        const uint64_t proj = gate0->payload_size, proj_scales = qt == UOCR_QT_F16 ? 0 : gate0->scale_size;
+        for (uint32_t e = 0; e < E; ++e)
+            for (uint32_t p = 0; p < 3; ++p) {
+                const uocr_cuda_tensor_entry *t = find_entry(m, lbase + kIdExpertBase + 3 * e + p);
+                if ((why = check_entry(m, t))) return fail(ctx, error, error_size, "layer %u: MoE expert %u %s %s", layer, e, kProj[p], why);
+                const uint32_t rows = p == 2 ? H : F, cols = p == 2 ? F : H;
+                if (t->qtype != qt || t->logical_shape[0] != rows || t->logical_shape[1] != cols)
+                    return fail(ctx, error, error_size, "layer %u: MoE expert %u %s differs in qtype or shape from expert 0", layer, e, kProj[p]);
+                if (t->payload_offset != gate0->payload_offset + (3ull * e + p) * proj)
+                    return fail(ctx, error, error_size, "integrated MoE expert tensors for layer %u are not interleaved-contiguous at expert %u", layer, e);
+                if (qt != UOCR_QT_F16 && t->scale_offset != gate0->scale_offset + (3ull * e + p) * proj_scales)
+                    return fail(ctx, error, error_size, "integrated MoE expert qscale tensors for layer %u are not interleaved-contiguous at expert %u", layer, e);
+            }
+
+        if (!upload_it) return 1;
+        uocr_cuda_moe_layer_desc d{};
+        d.hidden_size = H; d.n_experts = E; d.top_k = K; d.expert_intermediate = F; d.shared_intermediate = S;
+        d.routed_scaling_factor = m->routed_scaling_factor;
+        const uint8_t *base = (const uint8_t *)m->data;
+        d.router_weight_f16 = base + router->payload_offset;
+        d.expert_qtype = (int32_t)qt;
+        d.expert_qweight = base + gate0->payload_offset;
+        d.expert_qscale = qt == UOCR_QT_F16 ? nullptr : base + gate0->scale_offset;
+        d.shared_gate = matrix_of(m, shared[0]);
+        d.shared_up = matrix_of(m, shared[1]);
+        d.shared_down = matrix_of(m, shared[2]);
+        char inner[512] = {0};
+        if (!uocr_cuda_context_map_moe_layer(ctx, &d, nullptr, inner, sizeof inner)) {
+            uocr_cuda_context_unmap_model(ctx);
+            return fail(ctx, error, error_size, "layer %u: %s", layer, inner);
+        }
+        return 1;
+    };
+    for (int pass = 0; pass < 2; ++pass)
+        for (uint32_t layer = m->first_moe_layer; layer < m->first_moe_layer + m->moe_layer_count; ++layer)
+            if (!one_layer(layer, pass == 1)) return 0;
+    return 1;
+}
+
 extern "C" uint32_t uocr_cuda_context_moe_layer_count(const uocr_cuda_context *ctx) {
     return ctx ? (uint32_t)ctx->layers.size() : 0;
 }
@@ -601,14 +723,13 @@ static ArenaLayout layout_arena(uint32_t H, uint32_t E, uint32_t K, uint32_t F, 
     a.d_out = take((uint64_t)n * H * 2);
     a.dec_mid = take(((uint64_t)K * F + S) * 2);            // single-token decode kernel: SwiGLU products
     a.dec_plogits = take((uint64_t)1024 * E * 4);           // and per-CTA partial router logits
-    {   // tensor-core path: sorted activations and tile lists (128 tokens x 128 weight rows per tile)
-        // (gate/up tiles hold 64 tokens, down tiles 128)
+    {   // tensor-core path: sorted activations and tile lists (a tile is 128 tokens x 128 rows of down, or x 64 rows each
+        // of gate and up); the experts phase of an expert-parallel rank sees up to E segments
         const uint64_t ttiles = (pairs + 127) / 128 + E, sttiles = ((uint64_t)n + 127) / 128;
-        const uint64_t ttiles_gu = (pairs + 63) / 64 + E, sttiles_gu = ((uint64_t)n + 63) / 64;
         a.x_sorted = take(pairs * H * 2);
-        a.tiles_gu = take(ttiles_gu * (F / 128 + 1) * 16);
+        a.tiles_gu = take(ttiles * (F / 64 + 1) * 16);
         a.tiles_dn = take(ttiles * (H / 128 + 1) * 16);
-        a.stiles_gu = take(sttiles_gu * (S / 128 + 1) * 16);
+        a.stiles_gu = take(sttiles * (S / 64 + 1) * 16);
         a.stiles_dn = take(sttiles * (H / 128 + 1) * 16);
         a.counts = take(64);
         a.seg_offsets = take(260 * 4);        // expert-parallel experts phase: offsets of the received segments

@@ -38,6 +38,13 @@ class CLayerDesc(C.Structure):
                 ("shared_gate", CMatrix), ("shared_up", CMatrix), ("shared_down", CMatrix)]
 
 
+class CModelFileView(C.Structure):
+    """uocr_cuda_model_file_view: what the backend needs of an opened `.uocr` file."""
+    _fields_ = [("data", C.c_void_p), ("size", C.c_uint64), ("tensors", C.c_void_p), ("tensor_count", C.c_uint32),
+                ("routed_experts", C.c_uint32), ("moe_top_k", C.c_uint32), ("first_moe_layer", C.c_uint32),
+                ("moe_layer_count", C.c_uint32), ("routed_scaling_factor", C.c_float)]
+
+
 class CDebugOutputs(C.Structure):
     _fields_ = [("d_router_logits", C.c_void_p), ("d_router_probs", C.c_void_p), ("d_top_ids", C.c_void_p),
                 ("d_top_weights", C.c_void_p)]
@@ -51,7 +58,7 @@ EXPORTS = (
     "uocr_cuda_context_destroy", "uocr_cuda_context_last_error", "uocr_cuda_context_set_stream",
     "uocr_cuda_context_set_profile_detail", "uocr_cuda_context_set_profile", "uocr_cuda_context_set_memory_tracker",
     "uocr_cuda_profile_event_name", "uocr_cuda_context_synchronize", "uocr_cuda_context_kernel_launches", "uocr_cuda_context_model_view_bytes",
-    "uocr_cuda_context_moe_scratch_bytes", "uocr_cuda_context_map_moe_layer", "uocr_cuda_context_unmap_model",
+    "uocr_cuda_context_moe_scratch_bytes", "uocr_cuda_context_map_moe_layer", "uocr_cuda_context_map_model", "uocr_cuda_context_unmap_model",
     "uocr_cuda_context_moe_layer_count", "uocr_cuda_context_allocate_runtime_arenas",
     "uocr_cuda_context_release_runtime_arenas", "uocr_cuda_moe_scratch_size", "uocr_cuda_moe_router",
     "uocr_cuda_moe_dispatch_plan", "uocr_cuda_moe_dispatch_plan_noalloc", "uocr_cuda_moe_debug_dequantize", "uocr_cuda_moe_regime_name", "uocr_cuda_moe_layer_forward", "uocr_cuda_moe_stack_forward",
@@ -109,6 +116,7 @@ def load_library() -> C.CDLL:
         "uocr_cuda_context_model_view_bytes": (u64, [vp]),
         "uocr_cuda_context_moe_scratch_bytes": (u64, [vp]),
         "uocr_cuda_context_map_moe_layer": (C.c_int, [vp, C.POINTER(CLayerDesc), C.POINTER(u32)] + err),
+        "uocr_cuda_context_map_model": (C.c_int, [vp, C.POINTER(CModelFileView)] + err),
         "uocr_cuda_context_unmap_model": (None, [vp]),
         "uocr_cuda_context_moe_layer_count": (u32, [vp]),
         "uocr_cuda_context_allocate_runtime_arenas": (C.c_int, [vp, u32, u32] + err),
@@ -246,6 +254,19 @@ class Context:
         self._layer_k[idx.value] = desc.top_k
         self._layer_e[idx.value] = desc.n_experts
         return idx.value
+
+    def map_model(self, data_address: int, size: int, tensors_address: int, tensor_count: int, *, routed_experts: int,
+                  top_k: int, first_moe_layer: int, moe_layer_count: int, routed_scaling_factor: float = 1.0) -> int:
+        """Map the MoE layers of an opened `.uocr` file (uocr_cuda_context_map_model).  `data_address` is the address
+        of the file's first byte in host memory (a memory map or a buffer the caller keeps alive during the call),
+        `tensors_address` the address of its tensor directory entries.  Returns the number of layers mapped."""
+        view = CModelFileView(data_address, size, tensors_address, tensor_count, routed_experts, top_k, first_moe_layer,
+                              moe_layer_count, routed_scaling_factor)
+        self._check(self._lib.uocr_cuda_context_map_model(self._h, C.byref(view), self._err, _ERR))
+        for i in range(moe_layer_count):
+            self._layer_k[i] = top_k
+            self._layer_e[i] = routed_experts
+        return int(self._lib.uocr_cuda_context_moe_layer_count(self._h))
 
     def release_runtime_arenas(self) -> None:
         self._lib.uocr_cuda_context_release_runtime_arenas(self._h)
