@@ -1,23 +1,26 @@
 // Many-token MoE layer: expert-grouped GEMMs on the 5th-generation tensor cores.
 //
 // After the dispatch plan the (token, slot) pairs of one expert are contiguous, so each expert is a
-// dense product.  Both products are computed "weights as rows":
-//     gate/up :  [2 x 128 weight rows] x [<=128 tokens]  over K = H,  two accumulators (gate, up) ->
-//                mid[pos][f] = fp16( silu(gate) * up )
-//     down    :  [128 weight rows] x [<=256 tokens]  over K = F (or S) -> down_out[pos][h] = fp16(acc)
+// dense product.  Both products are computed "weights as rows": a tile is 128 tensor-memory lanes of weight rows
+// against up to 192 tokens,
+//     gate/up :  64 gate rows interleaved with the 64 matching up rows, K = H  ->
+//                mid[pos][f] = fp16( silu(gate) * up )   (the two accumulators of an output sit in neighbouring lanes)
+//     down    :  128 weight rows, K = F (or S)  ->  down_out[pos][h] = fp16(acc)
 // With the weights on the M side of the MMA a cold expert with a handful of tokens pads its token
 // count to 16, not to 128, which matters under Zipf-skewed routing.
 //
-// One CTA (576 threads, one per SM: it owns all 512 tensor-memory columns) computes one tile.  Per 64-wide K
-// block (= one scale group of the weight formats, = one 128-byte swizzle row of fp16):
-//   warps 0-15 two threads per weight row and matrix: each loads its share of the row's packed bytes with 128-bit
-//              loads (several K blocks ahead), turns them into fp16( level * scale ) in registers and stores
-//              them with tcgen05.st straight into a ring of tensor-memory slots, the A operand of the MMA:
-//              no dequantised weight ever reaches shared or global memory.  A slot is published one block late,
-//              so the stores' latency hides behind the next conversion.  The same warps run the epilogue
-//              (tcgen05.ld, SwiGLU with the fast exponential, fp16 stores).
-//   warp 16    one thread issues the TMA tile loads (cp.async.bulk.tensor) of the activation tile.
-//   warp 17    one thread issues tcgen05.mma (kind::f16, A from tensor memory, B from shared memory, fp32
+// One persistent CTA per SM (704 threads; it owns all 512 tensor-memory columns: two accumulators of 192 columns and
+// a ring of four 32-column slots for the weight operand) walks its share of the tile list.  Per 64-wide K block
+// (= one scale group of the weight formats, = one 128-byte swizzle row of fp16):
+//   warps 0-15 four threads per lane: each loads its 16 weights' packed bytes with a 128-bit load (several K blocks
+//              ahead), turns them into fp16( level * scale ) in registers and stores them with tcgen05.st straight
+//              into the ring of tensor-memory slots, the A operand of the MMA: no dequantised weight ever reaches
+//              shared or global memory.  A slot is published one block late, so the stores' latency hides behind
+//              the next conversion.  These warps never wait for an accumulator: they run on into the next tile.
+//   warps 16-19 the epilogue of the PREVIOUS tile (tcgen05.ld, SwiGLU with the fast exponential, fp16 stores) while
+//              the tensor core accumulates the current one in the other accumulator.
+//   warp 20    one thread issues the TMA tile loads (cp.async.bulk.tensor) of the activation tile.
+//   warp 21    one thread issues tcgen05.mma (kind::f16, A from tensor memory, B from shared memory, fp32
 //              accumulators in tensor memory) and commits the slots back; the warp also owns the TMEM allocation.
 // Every wait is bounded; on a time-out the CTA raises a status bit, drains and returns.
 #include <cuda.h>
@@ -31,12 +34,13 @@
 
 namespace uocr {
 
-constexpr int kGemmThreads = 576;        // warps 0-15 producers + epilogue, warp 16 TMA, warp 17 MMA
+constexpr int kGemmThreads = 704;        // warps 0-15 converters, 16-19 epilogue, warp 20 TMA, warp 21 MMA
 constexpr int kProducerThreads = 512;
-constexpr int kTmaWarp = 16, kMmaWarp = 17;
-constexpr int kTileM = 128;          // weight rows per tile = TMEM lanes
-constexpr int kTileN = 256;          // tokens per tile of the down product (one accumulator)
-constexpr int kTileNGateUp = 128;    // tokens per tile of the gate/up product (two accumulators)
+constexpr int kEpilogueWarps = 4;
+constexpr int kTmaWarp = 20, kMmaWarp = 21;
+constexpr int kTileM = 128;          // TMEM lanes per tile: 128 rows of down, or 64 rows of gate interleaved with 64 of up
+constexpr int kTileN = 192;          // tokens per tile: a tcgen05.mma costs about 106 cycles whatever its N up to 192 (measured),
+                                     // and two accumulators of 192 columns leave 128 columns for the weight operand
 constexpr int kBlockK = 64;          // fp16 elements per K block = 128 bytes = one swizzle row
 constexpr int kTileBytes = kTileM * kBlockK * 2;   // 16 KB: one operand tile of one stage
 constexpr long long kGemmSpinLimit = 400000000LL;    // cycles (~0.2 s): no legitimate wait comes near
@@ -77,13 +81,18 @@ __device__ __forceinline__ bool gb_try(uint64_t *bar, uint32_t parity) {
         : "=r"(ok) : "r"(s2u(bar)), "r"(parity) : "memory");
     return ok != 0;
 }
-// Bounded wait; also gives up as soon as another role of the CTA has raised the abort flag.
+// Bounded wait; also gives up as soon as another role of the CTA has raised the abort flag.  RELAXED waits sleep between
+// polls: the roles that run ahead of the tensor core (converters, activation loader) or behind it (epilogue) spend much
+// of their time waiting, and a warp that polls in a tight loop takes issue slots from the one thread whose instruction
+// stream feeds the tensor core.
+template <bool RELAXED = false>
 __device__ __forceinline__ bool gb_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag, uint32_t *status) {
     if (gb_try(bar, parity)) return true;
     const long long t0 = clock64();
     uint32_t polls = 0;
     while (!gb_try(bar, parity)) {
-        if ((++polls & 255u) == 0u) {
+        if (RELAXED) __nanosleep(128);
+        if ((++polls & (RELAXED ? 15u : 255u)) == 0u) {
             if (*abort_flag) return false;
             if (clock64() - t0 > kGemmSpinLimit) {
                 *abort_flag = 1;
@@ -154,47 +163,38 @@ __device__ __forceinline__ void bytes_to_h2(uint32_t bytes, __half2 bias, __half
     hi = h2_as_u32(__hmul2(__hsub2(*reinterpret_cast<const __half2 *>(&b), bias), scale));
 }
 
-// Packed bytes one thread holds per 64-wide K block: it owns K positions [16h, 16h+16) of both 32-wide
-// sub-blocks (h = 0 / 1).  kAhead: how many K blocks of packed bytes a thread keeps in flight from global memory.
+// Packed bytes of one row and one 64-wide K block (one scale group), as 16-byte vectors.  kAhead: how many K blocks
+// of packed bytes a thread keeps in flight from global memory.
 template <int QT> struct PackedBlock;
-template <> struct PackedBlock<UOCR_QT_Q4> { static constexpr int kVecs = 1; static constexpr int kAhead = 4; };
-template <> struct PackedBlock<UOCR_QT_Q8> { static constexpr int kVecs = 2; static constexpr int kAhead = 3; };
-template <> struct PackedBlock<UOCR_QT_F16> { static constexpr int kVecs = 4; static constexpr int kAhead = 2; };
+template <> struct PackedBlock<UOCR_QT_Q4> { static constexpr int kVecs = 2; static constexpr int kAhead = 3; };
+template <> struct PackedBlock<UOCR_QT_Q8> { static constexpr int kVecs = 4; static constexpr int kAhead = 2; };
+template <> struct PackedBlock<UOCR_QT_F16> { static constexpr int kVecs = 8; static constexpr int kAhead = 1; };
 
-// Q4_0: bytes 16h..16h+15 of the group's 32 (low nibbles: sub-block 0, high nibbles: sub-block 1).
-// Q8_0: bytes 32j + 16h .. +15 for sub-block j.   fp16: halves 32j + 16h .. +15 for sub-block j.
 template <int QT>
-__device__ __forceinline__ void load_block(const uint8_t *row, uint32_t kb, int h, uint4 (&v)[PackedBlock<QT>::kVecs]) {
-    const uint4 *p = reinterpret_cast<const uint4 *>(row);
-    if constexpr (QT == UOCR_QT_Q4) {
-        v[0] = __ldg(p + (size_t)kb * 2 + h);
-    } else if constexpr (QT == UOCR_QT_Q8) {
-        v[0] = __ldg(p + (size_t)kb * 4 + h);
-        v[1] = __ldg(p + (size_t)kb * 4 + 2 + h);
-    } else {
-        v[0] = __ldg(p + (size_t)kb * 8 + 2 * h);
-        v[1] = __ldg(p + (size_t)kb * 8 + 2 * h + 1);
-        v[2] = __ldg(p + (size_t)kb * 8 + 4 + 2 * h);
-        v[3] = __ldg(p + (size_t)kb * 8 + 4 + 2 * h + 1);
-    }
+__device__ __forceinline__ void load_block(const uint8_t *row, uint32_t kb, uint4 (&v)[PackedBlock<QT>::kVecs]) {
+    const uint4 *p = reinterpret_cast<const uint4 *>(row) + (size_t)kb * PackedBlock<QT>::kVecs;
+#pragma unroll
+    for (int i = 0; i < PackedBlock<QT>::kVecs; ++i) v[i] = __ldg(p + i);
 }
 
-// 16 weights of sub-block j -> 8 registers of two fp16 each, in K order
+// The 16 weights at K positions [32 j + 16 h, +16) of the block -> 8 registers of two fp16 each, in K order.
+// Q4_0: bytes 16h..16h+15 of the group's 32 (low nibbles: sub-block j = 0, high nibbles: j = 1).
+// Q8_0: bytes 32j + 16h .. +15.   fp16: halves 32j + 16h .. +15.
 template <int QT>
-__device__ __forceinline__ void convert_sub(const uint4 (&v)[PackedBlock<QT>::kVecs], int j, __half scale, uint32_t (&out)[8]) {
+__device__ __forceinline__ void convert_sub(const uint4 (&v)[PackedBlock<QT>::kVecs], int j, int h, __half scale, uint32_t (&out)[8]) {
     if constexpr (QT == UOCR_QT_F16) {
-        const uint4 a = j ? v[2] : v[0], b = j ? v[3] : v[1];
+        const uint4 a = v[4 * j + 2 * h], b = v[4 * j + 2 * h + 1];
         out[0] = a.x; out[1] = a.y; out[2] = a.z; out[3] = a.w; out[4] = b.x; out[5] = b.y; out[6] = b.z; out[7] = b.w;
     } else if constexpr (QT == UOCR_QT_Q8) {
         const __half2 s2 = __half2half2(scale), bias = __float2half2_rn(1152.f);   // 1024 + 128
-        const uint4 q = j ? v[1] : v[0];
+        const uint4 q = v[2 * j + h];
         bytes_to_h2(q.x ^ 0x80808080u, bias, s2, out[0], out[1]);
         bytes_to_h2(q.y ^ 0x80808080u, bias, s2, out[2], out[3]);
         bytes_to_h2(q.z ^ 0x80808080u, bias, s2, out[4], out[5]);
         bytes_to_h2(q.w ^ 0x80808080u, bias, s2, out[6], out[7]);
     } else {
         const __half2 s2 = __half2half2(scale), bias = __float2half2_rn(1032.f);    // 1024 + 8
-        const uint4 q = v[0];
+        const uint4 q = v[h];
         const int sh = 4 * j;
         bytes_to_h2((q.x >> sh) & 0x0F0F0F0Fu, bias, s2, out[0], out[1]);
         bytes_to_h2((q.y >> sh) & 0x0F0F0F0Fu, bias, s2, out[2], out[3]);
@@ -223,49 +223,70 @@ __device__ __forceinline__ void tc_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint
 __device__ __forceinline__ float silu_fast(float v) { return __fdividef(v, 1.0f + __expf(-v)); }
 
 // ------------------------------------------------------------------------------ kernel
-// Tensor-memory columns: the accumulators first, then kAStages slots of the weight operand (one 32-wide K
-// sub-block of every weight tile per slot).  Two CTAs share an SM, so a CTA may hold at most 256 columns.
-template <bool GATEUP> struct GemmShape {
-    static constexpr int kATiles = GATEUP ? 2 : 1;                     // weight tiles (gate and up, or down)
-    static constexpr int kTileN = GATEUP ? kTileNGateUp : uocr::kTileN;   // tokens per tile = columns per accumulator
-    static constexpr int kAStages = 4;
-    static constexpr int kAccCols = kATiles * kTileN;                  // 256
-    static constexpr int kAStageCols = kATiles * 32;                   // 32 columns = one 64-wide K block per weight tile
+// One tile = 128 tensor-memory lanes x up to 192 tokens.  down: lane r is weight row 128*mtile + r.  gate/up: the two
+// matrices are interleaved, lane 2i is gate row 64*mtile + i and lane 2i+1 is up row 64*mtile + i, so the SwiGLU
+// partner of an accumulator sits in the neighbouring lane of the same warp and the epilogue needs one shuffle.
+// Tensor-memory columns: two accumulators of 192 columns (tile i+1 accumulates while tile i is read out), then
+// kAStages slots of 32 columns (one 64-wide K block of the 128 lanes).
+#ifndef UOCR_GEMM_ABLATE
+#define UOCR_GEMM_ABLATE 0      // development builds only: 1 no tensor-memory stores, 2 no activation loads, 4 no epilogue work, 8 no MMAs,
+                                // 16 no epilogue stores, 32 no SwiGLU arithmetic in the epilogue
+#endif
+#ifdef UOCR_GEMM_TRACE
+// Development build only: cycles every role of the kernel spends waiting, summed over CTAs ([gate/up or down][counter]).
+__device__ unsigned long long g_gemm_trace[2][16];
+#define GT_BEGIN(var) const long long var = clock64()
+#define GT_ADD(slot, var) gt_local[slot] += (unsigned long long)(clock64() - var)
+#else
+#define GT_BEGIN(var)
+#define GT_ADD(slot, var)
+#endif
+
+struct GemmShape {
+    static constexpr int kTileN = uocr::kTileN;                        // tokens per tile = columns per accumulator
+    static constexpr int kAccBufs = 2;
+    static constexpr int kStages = 4;                                  // ring depth, the same for both operands
+    static constexpr int kAccCols = kAccBufs * kTileN;                 // 384
+    static constexpr int kAStageCols = 32;
     static constexpr int kTmemCols = 512;
-    static_assert(kAccCols + kAStages * kAStageCols <= kTmemCols, "tensor memory budget");
-    static constexpr int kBStages = GATEUP ? 6 : 4;
-    static constexpr int kBTileBytes = kTileN * kBlockK * 2;           // 16 or 32 KB
-    static constexpr int kMaxKBlocks = 32;                             // K <= 2048
-    static constexpr int kScaleBytes = 2 * kATiles * kTileM * kMaxKBlocks * 2;    // two tiles' worth: [tile parity][matrix][row][k block]
-    static constexpr int kSmemBytes = kBStages * kBTileBytes + kScaleBytes + 1024 /*alignment*/ + 256 /*barriers*/;
+    static_assert(kAccCols + kStages * kAStageCols <= kTmemCols, "tensor memory budget");
+    static constexpr int kBTileBytes = kTileN * kBlockK * 2;           // 24 KB
+    static constexpr int kBarrierBytes = 256;
+    static constexpr int kEpiStageBytes = 1024;                        // per epilogue warp: 16 tokens x 32 output columns of fp16
+    static constexpr int kSmemBytes = kStages * kBTileBytes + kBarrierBytes + kEpilogueWarps * kEpiStageBytes + 1024 /*alignment*/;
 };
 
 template <int QT, bool GATEUP>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap act_map, GemmParams p) {
-    using Sh = GemmShape<GATEUP>;
-    constexpr int kAStages = Sh::kAStages, kBStages = Sh::kBStages, kTileN = Sh::kTileN;
+    using Sh = GemmShape;
+    constexpr int kStages = Sh::kStages, kTileN = Sh::kTileN;
     // Persistent: the grid has at most one CTA per SM, and CTA b takes tiles b, b + gridDim.x, ... of the list (hottest
-    // expert first).  Barriers and tensor memory are set up once; the rings' phases run on across tiles, and the
-    // activation loader works ahead into the next tile while the other warps finish the current one.
+    // expert first).  Barriers and tensor memory are set up once.  The CTA's K blocks form ONE running sequence across
+    // its tiles (block q of the sequence uses ring stage q % 4); every role walks that sequence on its own: the
+    // activation loader and the converters work ahead into the next tiles while the tensor core finishes the current
+    // one and the epilogue warps read out the one before.  Nothing synchronises the roles at a tile boundary.
     const uint32_t n_tiles = *p.tile_count;
     if (blockIdx.x >= n_tiles) return;
     const uint32_t kblocks = p.k_dim / kBlockK;
+    const uint32_t my_tiles = (n_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x;
+    const uint32_t total_blocks = my_tiles * kblocks;
 
     extern __shared__ uint8_t smem_dyn[];
     uint8_t *b_tiles = reinterpret_cast<uint8_t *>(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
-    __half *s_scales = reinterpret_cast<__half *>(b_tiles + kBStages * Sh::kBTileBytes);   // [tile parity][kATiles][128][kMaxKBlocks]
-    uint64_t *bars = reinterpret_cast<uint64_t *>(b_tiles + kBStages * Sh::kBTileBytes + Sh::kScaleBytes);
-    uint64_t *a_full = bars, *a_empty = a_full + kAStages, *b_full = a_empty + kAStages, *b_empty = b_full + kBStages,
-             *acc_full = b_empty + kBStages;
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_full + 1);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(b_tiles + kStages * Sh::kBTileBytes);
+    // full[s]: the stage's weights are in tensor memory (one arrival per converter warp of the owning group) and its
+    // activation tile has landed (the loader's arrival + byte count); empty[s]: the MMAs that read it have finished
+    uint64_t *full = bars, *empty = full + kStages, *acc_full = empty + kStages, *acc_empty = acc_full + Sh::kAccBufs;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_empty + Sh::kAccBufs);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+    static_assert((2 * kStages + 2 * Sh::kAccBufs) * 8 + 8 <= Sh::kBarrierBytes, "barrier block");
+    uint8_t *epi_stage = b_tiles + kStages * Sh::kBTileBytes + Sh::kBarrierBytes;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     if (tid == 0) {
-        for (int s = 0; s < kAStages; ++s) { gb_init(&a_full[s], kProducerThreads / 32); gb_init(&a_empty[s], 1); }
-        for (int s = 0; s < kBStages; ++s) { gb_init(&b_full[s], 1); gb_init(&b_empty[s], 1); }
-        gb_init(acc_full, 1);
+        for (int s = 0; s < kStages; ++s) { gb_init(&full[s], kTileM / 32 + 1); gb_init(&empty[s], 1); }
+        for (int s = 0; s < Sh::kAccBufs; ++s) { gb_init(&acc_full[s], 1); gb_init(&acc_empty[s], kEpilogueWarps); }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -279,157 +300,287 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap act_map, GemmParams p) {
     const uint32_t tmem_base = *tmem_slot;
     const uint32_t a_base = tmem_base + Sh::kAccCols;       // first column of the weight-operand slots
 
-    if (warp < 16) {
-        // ------------------------------------------------ weight rows -> fp16 -> tensor memory, then the epilogue
-        // Two groups of 256 threads.  gate/up: group g converts matrix g (gate / up).  down: group g converts
-        // the g-th 32-wide sub-block of every K block.  Inside a group, thread (r, h) owns row r and the K
-        // positions [16h, 16h+16) of a sub-block.
-        const int grp = tid >> 8, r = tid & 127, h = (tid >> 7) & 1;
+    if (warp < kProducerThreads / 32) {
+        // ------------------------------------------------ weight rows -> fp16 -> tensor memory
+        // Four groups of four warps.  Group g owns the blocks q = g, g + 4, ... of the CTA's sequence, hence ring stage g,
+        // and converts each of them whole: thread r of the group turns the 64 weights of lane r's row into 32
+        // tensor-memory columns.  The groups work on different K blocks at the same time, so the latencies inside one
+        // block's conversion overlap with the other groups' arithmetic.  A thread keeps the packed bytes and the scale
+        // of its next kAhead blocks in registers; that prefetch runs across tile boundaries.
+        constexpr int kGroups = kProducerThreads / kTileM;
+        static_assert(kGroups == kStages, "one ring stage per converter group");
+        const int grp = tid >> 7, r = tid & 127;
         constexpr int kAhead = PackedBlock<QT>::kAhead, kVecs = PackedBlock<QT>::kVecs;
-        const int sm = GATEUP ? grp : 0;                              // which matrix's scales this thread uses
-        // this thread's TMEM lane, its 8 columns inside a 16-column sub-block, and its matrix inside a slot
-        const uint32_t lane_addr = ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)h * 8 + (GATEUP ? (uint32_t)grp * 32 : 0u);
-        bool alive = true;
-        uint32_t kbase = 0, it = 0;                                   // K blocks and tiles this CTA has gone through
-#pragma unroll 1
-        for (uint32_t tile_idx = blockIdx.x; tile_idx < n_tiles && alive; tile_idx += gridDim.x, kbase += kblocks, ++it) {
-            const uint4 tile = p.tiles[tile_idx];
-            const uint32_t expert = tile.x, mtile = tile.y, row0 = tile.z, nrows = tile.w;
-            const size_t grow = (size_t)mtile * kTileM + r;               // row of the matrix
-            const uint8_t *rowp = ((GATEUP && grp) ? p.w1 : p.w0) + (size_t)expert * p.expert_stride_bytes + grow * p.row_bytes;
-            // the first packed blocks are requested before the scales are waited for: one memory latency, not two
-            uint4 v[kAhead][kVecs];
-#pragma unroll
-            for (int d = 0; d < kAhead; ++d)
-                if ((uint32_t)d < kblocks) load_block<QT>(rowp, d, h, v[d]);
-            // The row's scales go to shared memory once ([matrix][row][k block], one buffer per tile parity, so the
-            // previous tile's readers need not be waited for): the K loop never waits on a 2-byte global load.  A row's
-            // scales are contiguous: 4-byte loads, all issued before the first store.
-            __half *tile_scales = s_scales + (size_t)(it & 1u) * (Sh::kATiles * kTileM * Sh::kMaxKBlocks);
-            if (QT != UOCR_QT_F16 && h == 0 && (GATEUP || grp == 0)) {
-                // (K is a multiple of 128, so a row holds an even number of scales and starts on a 4-byte boundary)
-                const uint32_t *sc = reinterpret_cast<const uint32_t *>((sm == 0 ? p.s0 : p.s1) + (size_t)expert * p.expert_scale_stride + grow * kblocks);
-                uint32_t *dst = reinterpret_cast<uint32_t *>(tile_scales + ((size_t)sm * kTileM + r) * Sh::kMaxKBlocks);
-                uint32_t t[Sh::kMaxKBlocks / 2];
-#pragma unroll
-                for (int i = 0; i < Sh::kMaxKBlocks / 2; ++i) t[i] = (uint32_t)(2 * i) < kblocks ? __ldg(sc + i) : 0u;
-#pragma unroll
-                for (int i = 0; i < Sh::kMaxKBlocks / 2; ++i)
-                    if ((uint32_t)(2 * i) < kblocks) dst[i] = t[i];
+        const uint32_t dst = a_base + (uint32_t)grp * Sh::kAStageCols + ((uint32_t)((warp & 3) * 32) << 16);
+        const bool second = GATEUP && (r & 1);                        // this lane holds a row of the up matrix
+        const uint8_t *wbase = second ? p.w1 : p.w0;
+        const __half *sbase = second ? p.s1 : p.s0;
+#ifdef UOCR_GEMM_TRACE
+        unsigned long long gt_local[5] = {0, 0, 0, 0, 0};
+        GT_BEGIN(gt_all);
+#endif
+        // prefetch cursor: tile and K block of the next block to request
+        uint32_t pf_tile = blockIdx.x, pf_kb = (uint32_t)grp;
+        const uint8_t *pf_row = nullptr;
+        const unsigned short *pf_sc = nullptr;
+        auto pf_enter_tile = [&]() {
+            if (pf_tile < n_tiles) {
+                const uint4 tile = p.tiles[pf_tile];
+                const size_t grow = GATEUP ? (size_t)tile.y * (kTileM / 2) + (r >> 1) : (size_t)tile.y * kTileM + r;   // row of the matrix
+                pf_row = wbase + (size_t)tile.x * p.expert_stride_bytes + grow * p.row_bytes;
+                if (QT != UOCR_QT_F16)
+                    pf_sc = reinterpret_cast<const unsigned short *>(sbase + (size_t)tile.x * p.expert_scale_stride + grow * kblocks);
             }
-            asm volatile("bar.sync 1, %0;" ::"n"(kProducerThreads) : "memory");     // scales visible to every thread of a row
-            const __half *my_scales = tile_scales + ((size_t)sm * kTileM + r) * Sh::kMaxKBlocks;
-            int pending = -1;       // slot whose tensor-memory stores are in flight: published one block later, so that
-                                    // the stores' latency hides behind the next block's conversion
-            auto publish = [&]() {
-                tc_st_wait();
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) gb_arrive(&a_full[pending]);              // one arrival per warp: its stores have all landed
-            };
-            for (uint32_t kb0 = 0; kb0 < kblocks && alive; kb0 += kAhead) {
+        };
+        auto pf_settle = [&]() {                                      // carry the K block index over into the next tiles
+            bool moved = false;
+            while (pf_kb >= kblocks) { pf_kb -= kblocks; pf_tile += gridDim.x; moved = true; }
+            if (moved) pf_enter_tile();
+        };
+        auto pf_fetch = [&](uint4 (&vv)[kVecs], unsigned short &sc) {
+            if (pf_tile < n_tiles) {
+                load_block<QT>(pf_row, pf_kb, vv);
+                if (QT != UOCR_QT_F16) sc = __ldg(pf_sc + pf_kb);
+            }
+            pf_kb += kGroups;
+            pf_settle();
+        };
+        pf_enter_tile();
+        pf_settle();
+        uint4 v[kAhead][kVecs];
+        unsigned short scv[kAhead];
 #pragma unroll
-                for (int d = 0; d < kAhead; ++d) {
-                    const uint32_t kb = kb0 + d;
-                    if (kb >= kblocks) break;
-                    const __half sc = QT == UOCR_QT_F16 ? __ushort_as_half(0) : my_scales[kb];
-                    const uint32_t kbg = kbase + kb, slot = kbg % kAStages, use = kbg / kAStages;
-                    // gate/up: both 32-wide sub-blocks of this thread's matrix; down: the group's sub-block
-                    uint32_t regs[2][8];
-                    if (GATEUP) { convert_sub<QT>(v[d], 0, sc, regs[0]); convert_sub<QT>(v[d], 1, sc, regs[1]); }
-                    else convert_sub<QT>(v[d], grp, sc, regs[0]);
-                    if (kb + kAhead < kblocks) load_block<QT>(rowp, kb + kAhead, h, v[d]);
-                    if (pending >= 0) publish();
-                    if (use > 0 && !gb_wait(&a_empty[slot], (use - 1) & 1u, abort_flag, p.status)) { alive = false; pending = -1; break; }
+        for (int d = 0; d < kAhead; ++d) { scv[d] = 0; pf_fetch(v[d], scv[d]); }
+
+        bool alive = true, pending = false;     // pending: this group's stage holds stores that are not published yet
+        auto publish = [&]() {
+            GT_BEGIN(gt_p);
+            tc_st_wait();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) gb_arrive(&full[grp]);                      // one arrival per warp: its stores have all landed
+            GT_ADD(3, gt_p);
+        };
+        uint32_t use = 0;                                             // how many blocks this group has stored so far
+#pragma unroll 1
+        for (uint32_t q0 = (uint32_t)grp; q0 < total_blocks && alive; q0 += kGroups * kAhead) {
+#pragma unroll
+            for (int d = 0; d < kAhead; ++d) {
+                if (q0 + (uint32_t)d * kGroups >= total_blocks) break;
+                const __half sc = __ushort_as_half(scv[d]);
+                // the first half of the block is converted before the previous block is published and the stage waited
+                // for, so that the previous stores' latency hides behind arithmetic
+                uint32_t regs[2][8];
+                convert_sub<QT>(v[d], 0, 0, sc, regs[0]);
+                convert_sub<QT>(v[d], 0, 1, sc, regs[1]);
+                if (pending) publish();
+                GT_BEGIN(gt_w);
+                if (use > 0 && !gb_wait<true>(&empty[grp], (use - 1) & 1u, abort_flag, p.status)) { alive = false; pending = false; break; }
+                GT_ADD(0, gt_w);
+                __syncwarp();
+                tc_fence_after();
+                GT_BEGIN(gt_s);
+                if (!(UOCR_GEMM_ABLATE & 1)) { tc_st8(dst, regs[0]); tc_st8(dst + 8u, regs[1]); }
+                else if (regs[0][0] == 0x12345u && regs[1][7] == 0x54321u) *abort_flag = 2;
+                GT_ADD(4, gt_s);
+                convert_sub<QT>(v[d], 1, 0, sc, regs[0]);
+                convert_sub<QT>(v[d], 1, 1, sc, regs[1]);
+                pf_fetch(v[d], scv[d]);                                // the registers are free: request the block kAhead rounds on
+                if (!(UOCR_GEMM_ABLATE & 1)) { tc_st8(dst + 16u, regs[0]); tc_st8(dst + 24u, regs[1]); }
+                else if (regs[0][0] == 0x12345u && regs[1][7] == 0x54321u) *abort_flag = 2;
+                pending = true;
+                ++use;
+            }
+        }
+        if (pending) publish();
+#ifdef UOCR_GEMM_TRACE
+        GT_ADD(2, gt_all);
+        if (tid == 0) {
+            atomicAdd(&g_gemm_trace[GATEUP][0], gt_local[0]);     // converters: waiting for a free slot
+            atomicAdd(&g_gemm_trace[GATEUP][2], gt_local[2]);     // converters: whole loop
+            atomicAdd(&g_gemm_trace[GATEUP][13], gt_local[3]);    // converters: publishing (wait for the stores, arrive)
+            atomicAdd(&g_gemm_trace[GATEUP][14], gt_local[4]);    // converters: issuing the first two stores of a block
+        }
+#endif
+    } else if (warp < kTmaWarp) {
+        // ------------------------------------------------ epilogue: TMEM -> registers -> global, one tile behind the MMAs
+        // Warp q of the four reads the TMEM lanes 32 q .. 32 q + 31 (the hardware ties a warp to the lane quarter
+        // warp % 4), sixteen token columns at a time.
+        const uint32_t q = (uint32_t)(warp & 3);
+        const bool odd = (lane & 1) != 0;
+        uint32_t it = 0;
+#ifdef UOCR_GEMM_TRACE
+        unsigned long long gt_local[3] = {0, 0, 0};
+        GT_BEGIN(gt_all);
+#endif
+        uint4 tile = p.tiles[blockIdx.x];
+#pragma unroll 1
+        for (uint32_t tile_idx = blockIdx.x; tile_idx < n_tiles; tile_idx += gridDim.x, ++it) {
+            const uint32_t mtile = tile.y, row0 = tile.z, nrows = tile.w, buf = it & 1u;
+            if (tile_idx + gridDim.x < n_tiles) tile = p.tiles[tile_idx + gridDim.x];       // the next tile's entry, requested early
+            GT_BEGIN(gt_w);
+            const bool have_acc = gb_wait<true>(&acc_full[buf], (it >> 1) & 1u, abort_flag, p.status);
+            GT_ADD(0, gt_w);
+            __syncwarp();
+            if (!__all_sync(0xffffffffu, have_acc)) break;
+            tc_fence_after();
+            const uint32_t src = tmem_base + buf * (uint32_t)kTileN + ((q * 32u) << 16);
+            const uint32_t last_chunk = (nrows - 1u) / 16u;
+#pragma unroll 1
+            for (uint32_t c = (UOCR_GEMM_ABLATE & 4) ? last_chunk : 0u; c <= last_chunk; ++c) {
+                uint32_t a[16];
+                GT_BEGIN(gt_l);
+                tc_ld16(src + 16u * c, a);
+                tc_ld_wait();
+                GT_ADD(2, gt_l);
+                if (c == last_chunk) {
+                    // the accumulator has been read: the tensor core may start the tile after the next in it
+                    tc_fence_before();
                     __syncwarp();
-                    tc_fence_after();
-                    const uint32_t dst = a_base + slot * Sh::kAStageCols + lane_addr;
-                    if (GATEUP) { tc_st8(dst, regs[0]); tc_st8(dst + 16, regs[1]); }
-                    else tc_st8(dst + (uint32_t)grp * 16, regs[0]);
-                    pending = (int)slot;
+                    if (lane == 0) gb_arrive(&acc_empty[buf]);
+                }
+                // Two-byte stores scattered over sixteen token rows cost the load/store unit about as much as sixteen
+                // 16-byte ones, so the chunk is transposed through a 1 KB staging tile of this warp: neighbouring lanes
+                // pair their values into 32-bit words, and every token row then leaves as 16-byte stores.
+                const uint32_t t0 = 16u * c;
+                uint32_t *stage32 = reinterpret_cast<uint32_t *>(epi_stage + (size_t)(warp - kProducerThreads / 32) * Sh::kEpiStageBytes);
+                if (GATEUP) {
+                    // even lanes hold gate rows, odd lanes the matching up rows: the even lane computes the pair's output
+                    // for the even tokens, the odd lane for the odd ones (one exchange per token pair)
+                    uint32_t o[8];
+#pragma unroll
+                    for (int jj = 0; jj < 8; ++jj) {
+                        const uint32_t recv = __shfl_xor_sync(0xffffffffu, odd ? a[2 * jj] : a[2 * jj + 1], 1);
+                        const float g = __uint_as_float(odd ? recv : a[2 * jj]);
+                        const float u = __uint_as_float(odd ? a[2 * jj + 1] : recv);
+                        o[jj] = (uint32_t)__half_as_ushort(__float2half_rn((UOCR_GEMM_ABLATE & 32) ? g : silu_fast(g) * u));
+                    }
+                    // lanes l and l ^ 2 hold neighbouring output columns of the same tokens: pair them up
+                    const bool hi2 = (lane & 2) != 0;
+#pragma unroll
+                    for (int m = 0; m < 4; ++m) {
+                        const uint32_t recv = __shfl_xor_sync(0xffffffffu, hi2 ? o[2 * m] : o[2 * m + 1], 2);
+                        const uint32_t word = hi2 ? (recv | (o[2 * m + 1] << 16)) : (o[2 * m] | (recv << 16));
+                        const uint32_t token = 2u * (2u * m + (hi2 ? 1u : 0u)) + (odd ? 1u : 0u);
+                        stage32[token * 8u + ((uint32_t)lane >> 2)] = word;          // [16 tokens][8 words]
+                    }
+                    __syncwarp();
+                    const uint32_t token = (uint32_t)lane >> 1, part = (uint32_t)lane & 1u;
+                    const uint4 vec = *reinterpret_cast<const uint4 *>(stage32 + token * 8u + part * 4u);
+                    if (!(UOCR_GEMM_ABLATE & 16) && t0 + token < nrows)
+                        *reinterpret_cast<uint4 *>(p.out + (size_t)(row0 + t0 + token) * p.out_ld + (size_t)mtile * (kTileM / 2) + q * 16u + part * 8u) = vec;
+                    __syncwarp();
+                } else {
+#pragma unroll
+                    for (int m = 0; m < 8; ++m) {
+                        const uint32_t v0 = (uint32_t)__half_as_ushort(__float2half_rn(__uint_as_float(a[2 * m])));
+                        const uint32_t v1 = (uint32_t)__half_as_ushort(__float2half_rn(__uint_as_float(a[2 * m + 1])));
+                        const uint32_t recv = __shfl_xor_sync(0xffffffffu, odd ? v0 : v1, 1);
+                        const uint32_t word = odd ? (recv | (v1 << 16)) : (v0 | (recv << 16));
+                        stage32[(2u * m + (odd ? 1u : 0u)) * 16u + ((uint32_t)lane >> 1)] = word;    // [16 tokens][16 words]
+                    }
+                    __syncwarp();
+#pragma unroll
+                    for (int pass = 0; pass < 2; ++pass) {
+                        const uint32_t token = 8u * pass + ((uint32_t)lane >> 2), part = (uint32_t)lane & 3u;
+                        const uint4 vec = *reinterpret_cast<const uint4 *>(stage32 + token * 16u + part * 4u);
+                        if (!(UOCR_GEMM_ABLATE & 16) && t0 + token < nrows)
+                            *reinterpret_cast<uint4 *>(p.out + (size_t)(row0 + t0 + token) * p.out_ld + (size_t)mtile * kTileM + q * 32u + part * 8u) = vec;
+                    }
+                    __syncwarp();
                 }
             }
-            if (pending >= 0) publish();
-            // ------------------------------------------------ epilogue: TMEM -> registers -> global
-            const bool have_acc = alive && gb_wait(acc_full, it & 1u, abort_flag, p.status);
-            __syncwarp();
-            if (__all_sync(0xffffffffu, have_acc)) {
-                tc_fence_after();
-                // a warp reads the TMEM lanes 32*(warp % 4)..+31; the four warps of a lane quarter split the 16-column
-                // chunks.  All of a warp's chunks are requested before the first is used.
-                constexpr int kChunks = kTileN / 64;
-                const uint32_t lane_base = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
-                const size_t out_col = (size_t)mtile * kTileM + r;
-                const uint32_t cbase = (uint32_t)(warp >> 2) * 16;
-#pragma unroll
-                for (int i = 0; i < kChunks; ++i) {          // chunk by chunk: the registers of one chunk at a time
-                    const uint32_t c0 = cbase + 64 * i;
-                    if (c0 < nrows) {
-                        uint32_t g[16], u[16];
-                        tc_ld16(lane_base + c0, g);
-                        if (GATEUP) tc_ld16(lane_base + kTileN + c0, u);
-                        tc_ld_wait();
-#pragma unroll
-                        for (int j = 0; j < 16; ++j) {
-                            if (c0 + j < nrows) {
-                                const float a = __uint_as_float(g[j]);
-                                const float o = GATEUP ? silu_fast(a) * __uint_as_float(u[j]) : a;
-                                p.out[(size_t)(row0 + c0 + j) * p.out_ld + out_col] = __float2half_rn(o);
-                            }
-                        }
+        }
+#ifdef UOCR_GEMM_TRACE
+        GT_ADD(1, gt_all);
+        if (warp == kProducerThreads / 32 && lane == 0) {
+            atomicAdd(&g_gemm_trace[GATEUP][3], gt_local[0]);     // epilogue: waiting for an accumulator
+            atomicAdd(&g_gemm_trace[GATEUP][4], gt_local[1]);     // epilogue: whole loop
+            atomicAdd(&g_gemm_trace[GATEUP][15], gt_local[2]);    // epilogue: tensor-memory loads
+        }
+#endif
+    } else if (warp == kTmaWarp) {
+        // ------------------------------------------------ activation tiles by TMA (runs ahead into the next tiles)
+        if (lane == 0) {
+            uint32_t q = 0;
+            bool ok = true;
+#ifdef UOCR_GEMM_TRACE
+            unsigned long long gt_local[1] = {0};
+#endif
+            uint32_t row0 = p.tiles[blockIdx.x].z;
+            for (uint32_t tile_idx = blockIdx.x; tile_idx < n_tiles && ok; tile_idx += gridDim.x) {
+                const uint32_t cur_row0 = row0;
+                if (tile_idx + gridDim.x < n_tiles) row0 = p.tiles[tile_idx + gridDim.x].z;
+                for (uint32_t kb = 0; kb < kblocks; ++kb, ++q) {
+                    const uint32_t s = q % kStages, use = q / kStages;
+                    GT_BEGIN(gt_w);
+                    if (use > 0 && !gb_wait<true>(&empty[s], (use - 1) & 1u, abort_flag, p.status)) { ok = false; break; }
+                    GT_ADD(0, gt_w);
+                    if (!(UOCR_GEMM_ABLATE & 2)) {
+                        gb_expect_tx(&full[s], Sh::kBTileBytes);
+                        tma_load_2d(b_tiles + s * Sh::kBTileBytes, &act_map, (int)(kb * kBlockK), (int)cur_row0, &full[s]);
+                    } else {
+                        gb_arrive(&full[s]);
                     }
                 }
-            } else {
-                alive = false;
             }
-            tc_fence_before();
-        }
-    } else if (warp == kTmaWarp) {
-        // ------------------------------------------------ activation tiles by TMA (runs ahead into the next tile)
-        if (lane == 0) {
-            uint32_t kbase = 0;
-            bool ok = true;
-            for (uint32_t tile_idx = blockIdx.x; tile_idx < n_tiles && ok; tile_idx += gridDim.x, kbase += kblocks) {
-                const uint32_t row0 = p.tiles[tile_idx].z;
-                for (uint32_t kb = 0; kb < kblocks; ++kb) {
-                    const uint32_t kbg = kbase + kb, use = kbg / kBStages;
-                    const int s = kbg % kBStages;
-                    if (use > 0 && !gb_wait(&b_empty[s], (use - 1) & 1u, abort_flag, p.status)) { ok = false; break; }
-                    gb_expect_tx(&b_full[s], Sh::kBTileBytes);
-                    tma_load_2d(b_tiles + s * Sh::kBTileBytes, &act_map, (int)(kb * kBlockK), (int)row0, &b_full[s]);
-                }
-            }
+#ifdef UOCR_GEMM_TRACE
+            atomicAdd(&g_gemm_trace[GATEUP][5], gt_local[0]);         // loader: waiting for a free activation stage
+#endif
         }
     } else {
         // ------------------------------------------------ MMA issue
+        // One thread feeds the tensor core; its own instruction stream is on the critical path (a tcgen05.mma costs about
+        // 106 cycles of it whatever N is, measured), so a K block is one wait, four MMAs and one commit.
         if (lane == 0) {
-            uint32_t kbase = 0;
+            uint32_t q = 0, it = 0;
             bool ok = true;
-            for (uint32_t tile_idx = blockIdx.x; tile_idx < n_tiles && ok; tile_idx += gridDim.x, kbase += kblocks) {
-                const uint32_t nrows = p.tiles[tile_idx].w;
+            const uint64_t b_desc0 = umma_desc(s2u(b_tiles));
+#ifdef UOCR_GEMM_TRACE
+            unsigned long long gt_local[6] = {0, 0, 0, 0, 0, 0};
+            GT_BEGIN(gt_all);
+#endif
+            uint32_t nrows_next = p.tiles[blockIdx.x].w;
+            for (uint32_t tile_idx = blockIdx.x; tile_idx < n_tiles && ok; tile_idx += gridDim.x, ++it) {
+                const uint32_t nrows = nrows_next, buf = it & 1u;
+                if (tile_idx + gridDim.x < n_tiles) nrows_next = p.tiles[tile_idx + gridDim.x].w;
                 const uint32_t idesc = umma_idesc((nrows + 15u) & ~15u);          // MMA N: multiple of 16
-                // the accumulators of the previous tile have been read: every producer warp publishes its first block
-                // of this tile only after its own epilogue, and the first MMA waits for all sixteen
-                for (uint32_t kb = 0; kb < kblocks && ok; ++kb) {
-                    const uint32_t kbg = kbase + kb, slot = kbg % kAStages, bs = kbg % kBStages;
-                    ok = gb_wait(&a_full[slot], (kbg / kAStages) & 1u, abort_flag, p.status);
-                    if (ok) ok = gb_wait(&b_full[bs], (kbg / kBStages) & 1u, abort_flag, p.status);
+                // the accumulator buffer is free once the epilogue has read the tile before the previous one out of it
+                GT_BEGIN(gt_e);
+                if (it >= 2 && !gb_wait(&acc_empty[buf], ((it >> 1) - 1u) & 1u, abort_flag, p.status)) break;
+                GT_ADD(2, gt_e);
+#ifdef UOCR_GEMM_TRACE
+                gt_local[4] += (unsigned long long)kblocks * ((nrows + 15u) & ~15u);      // MMA work: K blocks x token columns
+                gt_local[5] += kblocks;
+#endif
+                tc_fence_after();
+                const uint32_t acc_addr = tmem_base + buf * (uint32_t)kTileN;
+                for (uint32_t kb = 0; kb < kblocks; ++kb, ++q) {
+                    const uint32_t s = q % kStages;
+                    GT_BEGIN(gt_a);
+                    ok = gb_wait(&full[s], (q / kStages) & 1u, abort_flag, p.status);
+                    GT_ADD(0, gt_a);
                     if (!ok) break;
                     tc_fence_after();
-                    const uint32_t b_addr = s2u(b_tiles + bs * Sh::kBTileBytes);
-                    const uint32_t a_addr = a_base + slot * Sh::kAStageCols;
+                    // (the descriptor's address field counts 16-byte units: a stage and a K step are plain additions)
+                    const uint64_t bd = b_desc0 + (uint64_t)(s * (uint32_t)(Sh::kBTileBytes >> 4));
+                    const uint32_t a_addr = a_base + s * Sh::kAStageCols;
 #pragma unroll
-                    for (int k = 0; k < kBlockK / 16; ++k) {
-                        const uint32_t acc = (kb > 0 || k > 0) ? 1u : 0u;
-                        const uint64_t bd = umma_desc(b_addr + k * 32);
-                        tc_mma_ts(tmem_base, a_addr + k * 8, bd, idesc, acc);
-                        if (GATEUP) tc_mma_ts(tmem_base + kTileN, a_addr + 32 + k * 8, bd, idesc, acc);
-                    }
-                    tc_commit(&a_empty[slot]);                // arrives when the MMAs above have read the slot
-                    tc_commit(&b_empty[bs]);
+                    for (int k = 0; k < kBlockK / 16; ++k)
+                        if (!(UOCR_GEMM_ABLATE & 8)) tc_mma_ts(acc_addr, a_addr + k * 8, bd + (uint64_t)(k * 2), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                    tc_commit(&empty[s]);                     // arrives when the MMAs above have read the stage
                 }
-                if (ok) tc_commit(acc_full);
+                if (ok) tc_commit(&acc_full[buf]);
             }
+#ifdef UOCR_GEMM_TRACE
+            GT_ADD(3, gt_all);
+            atomicAdd(&g_gemm_trace[GATEUP][6], gt_local[0]);         // MMA issue: waiting for a full stage
+            atomicAdd(&g_gemm_trace[GATEUP][8], gt_local[2]);         // MMA issue: waiting for a free accumulator
+            atomicAdd(&g_gemm_trace[GATEUP][9], gt_local[3]);         // MMA issue: whole loop
+            atomicAdd(&g_gemm_trace[GATEUP][10], gt_local[4]);        // K blocks x columns issued
+            atomicAdd(&g_gemm_trace[GATEUP][11], 1ull);               // CTAs
+            atomicAdd(&g_gemm_trace[GATEUP][12], gt_local[5]);        // K blocks
+#endif
         }
         __syncwarp();
     }
@@ -546,8 +697,8 @@ router_logits_kernel(const __grid_constant__ CUtensorMap hidden_map, const __gri
 }
 
 // --------------------------------------------------------------------- helper kernels
-// Tile lists of the routed GEMMs: for every expert with pairs, gate/up tiles of (64 tokens, 128 weight rows)
-// and down tiles of (128 tokens, 128 weight rows).  Entries are {expert, weight-row tile, first sorted
+// Tile lists of the routed GEMMs: for every expert with pairs, gate/up tiles of (192 tokens, 64 + 64 weight rows)
+// and down tiles of (192 tokens, 128 weight rows).  Entries are {expert, weight-row tile, first sorted
 // position, rows}; counts[0/1] are the list lengths.
 // Segment e uses the weights of expert expert_base + e % expert_mod (single GPU: base 0, mod E; expert-parallel
 // ranks receive one segment per (source rank, local expert)).
@@ -574,7 +725,7 @@ __global__ void tile_plan_kernel(const uint32_t *__restrict__ expert_offsets, ui
             const uint32_t i = order[k];
             const uint32_t c = expert_offsets[i + 1] - expert_offsets[i];
             base_gu[i] = rg; base_dn[i] = rd;
-            rg += (c + kTileNGateUp - 1) / kTileNGateUp;
+            rg += (c + kTileN - 1) / kTileN;
             rd += (c + kTileN - 1) / kTileN;
         }
         counts[0] = rg * gu_mtiles;
@@ -583,8 +734,8 @@ __global__ void tile_plan_kernel(const uint32_t *__restrict__ expert_offsets, ui
     __syncthreads();
     if (e < E) {
         const uint32_t lo = expert_offsets[e], cnt = expert_offsets[e + 1] - lo;
-        for (uint32_t t = 0; t * kTileNGateUp < cnt; ++t) {
-            const uint32_t r0 = lo + t * kTileNGateUp, nr = min((uint32_t)kTileNGateUp, cnt - t * kTileNGateUp);
+        for (uint32_t t = 0; t * kTileN < cnt; ++t) {
+            const uint32_t r0 = lo + t * kTileN, nr = min((uint32_t)kTileN, cnt - t * kTileN);
             for (uint32_t m = 0; m < gu_mtiles; ++m) tiles_gu[(size_t)(base_gu[e] + t) * gu_mtiles + m] = make_uint4(expert_base + e % expert_mod, m, r0, nr);
         }
         for (uint32_t t = 0; t * kTileN < cnt; ++t) {
@@ -597,11 +748,11 @@ __global__ void tile_plan_kernel(const uint32_t *__restrict__ expert_offsets, ui
 // Tile lists of the shared MLP (one "expert", all n tokens).
 __global__ void shared_tile_plan_kernel(uint32_t n, uint32_t gu_mtiles, uint32_t dn_mtiles, uint4 *__restrict__ tiles_gu,
                                         uint4 *__restrict__ tiles_dn, uint32_t *__restrict__ counts) {
-    const uint32_t tg = (n + kTileNGateUp - 1) / kTileNGateUp, td = (n + kTileN - 1) / kTileN;
+    const uint32_t tg = (n + kTileN - 1) / kTileN, td = tg;
     const uint32_t stride = gridDim.x * blockDim.x, i0 = blockIdx.x * blockDim.x + threadIdx.x;
     for (uint32_t i = i0; i < tg * gu_mtiles; i += stride) {
-        const uint32_t t = i / gu_mtiles, m = i % gu_mtiles, r0 = t * kTileNGateUp;
-        tiles_gu[i] = make_uint4(0, m, r0, min((uint32_t)kTileNGateUp, n - r0));
+        const uint32_t t = i / gu_mtiles, m = i % gu_mtiles, r0 = t * kTileN;
+        tiles_gu[i] = make_uint4(0, m, r0, min((uint32_t)kTileN, n - r0));
     }
     for (uint32_t i = i0; i < td * dn_mtiles; i += stride) {
         const uint32_t t = i / dn_mtiles, m = i % dn_mtiles, r0 = t * kTileN;
@@ -783,7 +934,7 @@ cudaError_t init_gemm_kernels() {
 #define UOCR_SET_SMEM(QT, GU)                                                                                    \
     if (err == cudaSuccess)                                                                                      \
         err = cudaFuncSetAttribute(grouped_gemm_kernel<QT, GU>, cudaFuncAttributeMaxDynamicSharedMemorySize,     \
-                                   GemmShape<GU>::kSmemBytes);
+                                   GemmShape::kSmemBytes);
     UOCR_SET_SMEM(UOCR_QT_Q4, true) UOCR_SET_SMEM(UOCR_QT_Q4, false)
     UOCR_SET_SMEM(UOCR_QT_Q8, true) UOCR_SET_SMEM(UOCR_QT_Q8, false)
     UOCR_SET_SMEM(UOCR_QT_F16, true) UOCR_SET_SMEM(UOCR_QT_F16, false)
@@ -849,7 +1000,7 @@ template <bool GU>
 static cudaError_t launch_gemm(int qt, const CUtensorMap &map, const GemmParams &p, uint32_t max_tiles, cudaStream_t st) {
     if (max_tiles == 0) return cudaSuccess;
     max_tiles = gemm_grid(max_tiles);
-    const size_t smem = GemmShape<GU>::kSmemBytes;
+    const size_t smem = GemmShape::kSmemBytes;
     switch (qt) {
         case UOCR_QT_Q4: grouped_gemm_kernel<UOCR_QT_Q4, GU><<<max_tiles, kGemmThreads, smem, st>>>(map, p); break;
         case UOCR_QT_Q8: grouped_gemm_kernel<UOCR_QT_Q8, GU><<<max_tiles, kGemmThreads, smem, st>>>(map, p); break;
@@ -886,15 +1037,14 @@ cudaError_t launch_gemm_experts(const DLayer &L, const Scratch &S, const GemmScr
                                 uint32_t rows_bound, __half *mid, __half *rows_out, cudaStream_t st, uint64_t *launches) {
     const uint32_t H = L.H, F = L.F;
     if (rows_bound == 0) return cudaSuccess;
-    const uint32_t ttiles_gu = (rows_bound + kTileNGateUp - 1) / kTileNGateUp + n_seg;
-    const uint32_t ttiles_dn = (rows_bound + kTileN - 1) / kTileN + n_seg;
+    const uint32_t ttiles = (rows_bound + kTileN - 1) / kTileN + n_seg;     // token tiles: an upper bound known on the host
     cudaError_t err;
-    tile_plan_kernel<<<1, 256, 0, st>>>(seg_offsets, n_seg, expert_base, expert_mod, F / kTileM, H / kTileM, G.tiles_gu,
+    tile_plan_kernel<<<1, 256, 0, st>>>(seg_offsets, n_seg, expert_base, expert_mod, F / (kTileM / 2), H / kTileM, G.tiles_gu,
                                         G.tiles_dn, G.counts);
     ++*launches;
     if ((err = cudaGetLastError()) != cudaSuccess) return err;
     CUtensorMap map_x, map_mid;
-    if ((err = make_map_rows(&map_x, rows_in, rows_bound, H, kTileNGateUp)) != cudaSuccess) return err;
+    if ((err = make_map_rows(&map_x, rows_in, rows_bound, H, kTileN)) != cudaSuccess) return err;
     if ((err = make_map_rows(&map_mid, mid, rows_bound, F, kTileN)) != cudaSuccess) return err;
     const int qt = L.expert_qtype;
     GemmParams p = base_params(S);
@@ -903,12 +1053,12 @@ cudaError_t launch_gemm_experts(const DLayer &L, const Scratch &S, const GemmScr
     p.expert_stride_bytes = L.expert_stride_bytes; p.expert_scale_stride = L.expert_scale_stride;
     p.row_bytes = packed_row_bytes_of(qt, H); p.k_dim = H;
     p.tiles = G.tiles_gu; p.tile_count = G.counts; p.out = mid; p.out_ld = F;
-    if ((err = launch_gemm<true>(qt, map_x, p, ttiles_gu * (F / kTileM), st)) != cudaSuccess) return err;
+    if ((err = launch_gemm<true>(qt, map_x, p, ttiles * (F / (kTileM / 2)), st)) != cudaSuccess) return err;
     p.w0 = L.expert_w + L.down_offset_bytes; p.w1 = nullptr;
     p.s0 = L.expert_s ? L.expert_s + L.down_scale_offset : nullptr; p.s1 = nullptr;
     p.row_bytes = packed_row_bytes_of(qt, F); p.k_dim = F;
     p.tiles = G.tiles_dn; p.tile_count = G.counts + 1; p.out = rows_out; p.out_ld = H;
-    if ((err = launch_gemm<false>(qt, map_mid, p, ttiles_dn * (H / kTileM), st)) != cudaSuccess) return err;
+    if ((err = launch_gemm<false>(qt, map_mid, p, ttiles * (H / kTileM), st)) != cudaSuccess) return err;
     *launches += 2;
     return cudaSuccess;
 }
@@ -917,22 +1067,22 @@ cudaError_t launch_gemm_experts(const DLayer &L, const Scratch &S, const GemmScr
 cudaError_t launch_gemm_shared(const DLayer &L, const Scratch &S, const GemmScratch &G, const __half *hidden, uint32_t n,
                                cudaStream_t st, uint64_t *launches) {
     const uint32_t H = L.H, Sd = L.S;
-    const uint32_t sttiles_gu = (n + kTileNGateUp - 1) / kTileNGateUp, sttiles_dn = (n + kTileN - 1) / kTileN;
+    const uint32_t sttiles = (n + kTileN - 1) / kTileN;
     cudaError_t err;
-    shared_tile_plan_kernel<<<8, 256, 0, st>>>(n, Sd / kTileM, H / kTileM, G.stiles_gu, G.stiles_dn, G.counts + 2);
+    shared_tile_plan_kernel<<<8, 256, 0, st>>>(n, Sd / (kTileM / 2), H / kTileM, G.stiles_gu, G.stiles_dn, G.counts + 2);
     ++*launches;
     CUtensorMap map_hidden, map_smid;
-    if ((err = make_map_rows(&map_hidden, hidden, n, H, kTileNGateUp)) != cudaSuccess) return err;
+    if ((err = make_map_rows(&map_hidden, hidden, n, H, kTileN)) != cudaSuccess) return err;
     if ((err = make_map_rows(&map_smid, G.shared_mid, n, Sd, kTileN)) != cudaSuccess) return err;
     GemmParams p = base_params(S);
     p.w0 = L.shared_gate.w; p.w1 = L.shared_up.w; p.s0 = L.shared_gate.s; p.s1 = L.shared_up.s;
     p.row_bytes = L.shared_gate.row_bytes; p.k_dim = H;
     p.tiles = G.stiles_gu; p.tile_count = G.counts + 2; p.out = G.shared_mid; p.out_ld = Sd;
-    if ((err = launch_gemm<true>(L.shared_gate.qtype, map_hidden, p, sttiles_gu * (Sd / kTileM), st)) != cudaSuccess) return err;
+    if ((err = launch_gemm<true>(L.shared_gate.qtype, map_hidden, p, sttiles * (Sd / (kTileM / 2)), st)) != cudaSuccess) return err;
     p.w0 = L.shared_down.w; p.w1 = nullptr; p.s0 = L.shared_down.s; p.s1 = nullptr;
     p.row_bytes = L.shared_down.row_bytes; p.k_dim = Sd;
     p.tiles = G.stiles_dn; p.tile_count = G.counts + 3; p.out = G.shared_out; p.out_ld = H;
-    if ((err = launch_gemm<false>(L.shared_down.qtype, map_smid, p, sttiles_dn * (H / kTileM), st)) != cudaSuccess) return err;
+    if ((err = launch_gemm<false>(L.shared_down.qtype, map_smid, p, sttiles * (H / kTileM), st)) != cudaSuccess) return err;
     *launches += 2;
     return cudaSuccess;
 }
@@ -1019,23 +1169,22 @@ cudaError_t launch_ep_offsets(const uint32_t *all_offsets, uint32_t world, uint3
 
 // ---- dequantisation probe ------------------------------------------------------------------------------------
 // out[row][col] = the fp16 value (widened to f32) the grouped GEMM's producer threads store into tensor memory for
-// weight (row, col): the same load_block / convert_sub pair, one thread per (row, 64-wide K block, half h).
+// weight (row, col): the same load_block / convert_sub pair, one thread per (row, 64-wide K block).
 template <int QT>
 __global__ void producer_probe_kernel(const uint8_t *__restrict__ w, const __half *__restrict__ s, uint32_t rows, uint32_t cols,
                                       uint32_t row_bytes, float *__restrict__ out) {
     const uint32_t kblocks = cols / kBlockK;
     const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (idx >= (size_t)rows * kblocks * 2) return;
-    const int h = (int)(idx & 1);
-    const uint32_t kb = (uint32_t)((idx >> 1) % kblocks), row = (uint32_t)((idx >> 1) / kblocks);
+    if (idx >= (size_t)rows * kblocks) return;
+    const uint32_t kb = (uint32_t)(idx % kblocks), row = (uint32_t)(idx / kblocks);
     uint4 v[PackedBlock<QT>::kVecs];
-    load_block<QT>(w + (size_t)row * row_bytes, kb, h, v);
+    load_block<QT>(w + (size_t)row * row_bytes, kb, v);
     const __half sc = QT == UOCR_QT_F16 ? __ushort_as_half(0) : s[(size_t)row * kblocks + kb];
 #pragma unroll
-    for (int j = 0; j < 2; ++j) {
+    for (int q4 = 0; q4 < 4; ++q4) {
         uint32_t regs[8];
-        convert_sub<QT>(v, j, sc, regs);
-        float *dst = out + (size_t)row * cols + (size_t)kb * kBlockK + 32 * j + 16 * h;
+        convert_sub<QT>(v, q4 >> 1, q4 & 1, sc, regs);
+        float *dst = out + (size_t)row * cols + (size_t)kb * kBlockK + 16 * q4;
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
             const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&regs[i]));
@@ -1046,7 +1195,7 @@ __global__ void producer_probe_kernel(const uint8_t *__restrict__ w, const __hal
 }
 
 cudaError_t launch_producer_probe(const DMatrix &m, float *out, cudaStream_t st, uint64_t *launches) {
-    const size_t work = (size_t)m.rows * (m.cols / kBlockK) * 2;
+    const size_t work = (size_t)m.rows * (m.cols / kBlockK);
     const unsigned blocks = (unsigned)((work + 255) / 256);
     switch (m.qtype) {
         case UOCR_QT_Q4: producer_probe_kernel<UOCR_QT_Q4><<<blocks, 256, 0, st>>>(m.w, m.s, m.rows, m.cols, m.row_bytes, out); break;
@@ -1057,4 +1206,21 @@ cudaError_t launch_producer_probe(const DMatrix &m, float *out, cudaStream_t st,
     return cudaGetLastError();
 }
 
+#ifdef UOCR_GEMM_TRACE
+cudaError_t read_gemm_trace(unsigned long long *out32, bool reset) {
+    cudaError_t err = cudaMemcpyFromSymbol(out32, g_gemm_trace, sizeof(unsigned long long) * 32);
+    if (err == cudaSuccess && reset) {
+        static const unsigned long long zero[32] = {0};
+        err = cudaMemcpyToSymbol(g_gemm_trace, zero, sizeof zero);
+    }
+    return err;
+}
+#endif
+
 }  // namespace uocr
+
+#ifdef UOCR_GEMM_TRACE
+extern "C" __attribute__((visibility("default"))) int uocr_cuda_debug_gemm_trace(unsigned long long *out32, int reset) {
+    return uocr::read_gemm_trace(out32, reset != 0) == cudaSuccess ? 1 : 0;
+}
+#endif
