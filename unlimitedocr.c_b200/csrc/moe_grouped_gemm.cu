@@ -219,6 +219,26 @@ __device__ __forceinline__ void tc_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint
         ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
 }
 
+// The same MMA and the commit, issued by one elected lane of a warp whose lanes all run the issuing loop.  Measured on
+// this part: with the loop inside an `if (lane == 0)` branch an MMA costs the issuing thread 106 - 164 cycles whatever its
+// N; with warp-uniform control flow and `elect.sync` it costs 91 cycles up to N = 128, 96 at N = 192 and 128 at N = 256,
+// i.e. the tensor core's own rate.
+__device__ __forceinline__ void tc_mma_ts_elect(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "elect.sync _|q, 0xffffffff;\n\t"
+        "@q tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tc_commit_elect(uint64_t *bar) {
+    asm volatile(
+        "{\n\t.reg .pred q;\n\t"
+        "elect.sync _|q, 0xffffffff;\n\t"
+        "@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}"
+        ::"r"(s2u(bar)) : "memory");
+}
+
 // silu with the fast exponential and reciprocal (about 2 ulp; the result is rounded to fp16 anyway)
 __device__ __forceinline__ float silu_fast(float v) { return __fdividef(v, 1.0f + __expf(-v)); }
 
@@ -530,9 +550,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap act_map, GemmParams p) {
         }
     } else {
         // ------------------------------------------------ MMA issue
-        // One thread feeds the tensor core; its own instruction stream is on the critical path (a tcgen05.mma costs about
-        // 106 cycles of it whatever N is, measured), so a K block is one wait, four MMAs and one commit.
-        if (lane == 0) {
+        // The warp's instruction stream is on the critical path of the tensor core, so a K block is one wait, four MMAs
+        // and one commit, and all 32 lanes run the loop: only the MMA and commit instructions themselves are predicated
+        // on an elected lane (see tc_mma_ts_elect).
+        {
             uint32_t q = 0, it = 0;
             bool ok = true;
             const uint64_t b_desc0 = umma_desc(s2u(b_tiles));
@@ -547,7 +568,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap act_map, GemmParams p) {
                 const uint32_t idesc = umma_idesc((nrows + 15u) & ~15u);          // MMA N: multiple of 16
                 // the accumulator buffer is free once the epilogue has read the tile before the previous one out of it
                 GT_BEGIN(gt_e);
-                if (it >= 2 && !gb_wait(&acc_empty[buf], ((it >> 1) - 1u) & 1u, abort_flag, p.status)) break;
+                if (it >= 2) ok = __all_sync(0xffffffffu, gb_wait(&acc_empty[buf], ((it >> 1) - 1u) & 1u, abort_flag, p.status));
+                if (!ok) break;
                 GT_ADD(2, gt_e);
 #ifdef UOCR_GEMM_TRACE
                 gt_local[4] += (unsigned long long)kblocks * ((nrows + 15u) & ~15u);      // MMA work: K blocks x token columns
@@ -558,7 +580,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap act_map, GemmParams p) {
                 for (uint32_t kb = 0; kb < kblocks; ++kb, ++q) {
                     const uint32_t s = q % kStages;
                     GT_BEGIN(gt_a);
-                    ok = gb_wait(&full[s], (q / kStages) & 1u, abort_flag, p.status);
+                    ok = __all_sync(0xffffffffu, gb_wait(&full[s], (q / kStages) & 1u, abort_flag, p.status));
                     GT_ADD(0, gt_a);
                     if (!ok) break;
                     tc_fence_after();
@@ -567,19 +589,21 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap act_map, GemmParams p) {
                     const uint32_t a_addr = a_base + s * Sh::kAStageCols;
 #pragma unroll
                     for (int k = 0; k < kBlockK / 16; ++k)
-                        if (!(UOCR_GEMM_ABLATE & 8)) tc_mma_ts(acc_addr, a_addr + k * 8, bd + (uint64_t)(k * 2), idesc, (kb > 0 || k > 0) ? 1u : 0u);
-                    tc_commit(&empty[s]);                     // arrives when the MMAs above have read the stage
+                        if (!(UOCR_GEMM_ABLATE & 8)) tc_mma_ts_elect(acc_addr, a_addr + k * 8, bd + (uint64_t)(k * 2), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                    tc_commit_elect(&empty[s]);               // arrives when the MMAs above have read the stage
                 }
-                if (ok) tc_commit(&acc_full[buf]);
+                if (ok) tc_commit_elect(&acc_full[buf]);
             }
 #ifdef UOCR_GEMM_TRACE
             GT_ADD(3, gt_all);
-            atomicAdd(&g_gemm_trace[GATEUP][6], gt_local[0]);         // MMA issue: waiting for a full stage
-            atomicAdd(&g_gemm_trace[GATEUP][8], gt_local[2]);         // MMA issue: waiting for a free accumulator
-            atomicAdd(&g_gemm_trace[GATEUP][9], gt_local[3]);         // MMA issue: whole loop
-            atomicAdd(&g_gemm_trace[GATEUP][10], gt_local[4]);        // K blocks x columns issued
-            atomicAdd(&g_gemm_trace[GATEUP][11], 1ull);               // CTAs
-            atomicAdd(&g_gemm_trace[GATEUP][12], gt_local[5]);        // K blocks
+            if (lane == 0) {
+                atomicAdd(&g_gemm_trace[GATEUP][6], gt_local[0]);         // MMA issue: waiting for a full stage
+                atomicAdd(&g_gemm_trace[GATEUP][8], gt_local[2]);         // MMA issue: waiting for a free accumulator
+                atomicAdd(&g_gemm_trace[GATEUP][9], gt_local[3]);         // MMA issue: whole loop
+                atomicAdd(&g_gemm_trace[GATEUP][10], gt_local[4]);        // K blocks x columns issued
+                atomicAdd(&g_gemm_trace[GATEUP][11], 1ull);               // CTAs
+                atomicAdd(&g_gemm_trace[GATEUP][12], gt_local[5]);        // K blocks
+            }
 #endif
         }
         __syncwarp();
