@@ -91,7 +91,7 @@ __device__ __forceinline__ bool gb_wait(uint64_t *bar, uint32_t parity, volatile
     const long long t0 = clock64();
     uint32_t polls = 0;
     while (!gb_try(bar, parity)) {
-        if (RELAXED) __nanosleep(128);
+        if (RELAXED) __nanosleep(40);
         if ((++polls & (RELAXED ? 15u : 255u)) == 0u) {
             if (*abort_flag) return false;
             if (clock64() - t0 > kGemmSpinLimit) {
@@ -372,15 +372,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap act_map, GemmParams p) {
 #pragma unroll
         for (int d = 0; d < kAhead; ++d) { scv[d] = 0; pf_fetch(v[d], scv[d]); }
 
-        bool alive = true, pending = false;     // pending: this group's stage holds stores that are not published yet
-        auto publish = [&]() {
-            GT_BEGIN(gt_p);
-            tc_st_wait();
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) gb_arrive(&full[grp]);                      // one arrival per warp: its stores have all landed
-            GT_ADD(3, gt_p);
-        };
+        bool alive = true;
         uint32_t use = 0;                                             // how many blocks this group has stored so far
 #pragma unroll 1
         for (uint32_t q0 = (uint32_t)grp; q0 < total_blocks && alive; q0 += kGroups * kAhead) {
@@ -388,14 +380,13 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap act_map, GemmParams p) {
             for (int d = 0; d < kAhead; ++d) {
                 if (q0 + (uint32_t)d * kGroups >= total_blocks) break;
                 const __half sc = __ushort_as_half(scv[d]);
-                // the first half of the block is converted before the previous block is published and the stage waited
-                // for, so that the previous stores' latency hides behind arithmetic
+                // the first half of the block is converted before the stage is waited for: when the tensor core frees
+                // the stage, half of the work that stands between "free" and "full again" is already done
                 uint32_t regs[2][8];
                 convert_sub<QT>(v[d], 0, 0, sc, regs[0]);
                 convert_sub<QT>(v[d], 0, 1, sc, regs[1]);
-                if (pending) publish();
                 GT_BEGIN(gt_w);
-                if (use > 0 && !gb_wait<true>(&empty[grp], (use - 1) & 1u, abort_flag, p.status)) { alive = false; pending = false; break; }
+                if (use > 0 && !gb_wait<true>(&empty[grp], (use - 1) & 1u, abort_flag, p.status)) { alive = false; break; }
                 GT_ADD(0, gt_w);
                 __syncwarp();
                 tc_fence_after();
@@ -405,14 +396,20 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap act_map, GemmParams p) {
                 GT_ADD(4, gt_s);
                 convert_sub<QT>(v[d], 1, 0, sc, regs[0]);
                 convert_sub<QT>(v[d], 1, 1, sc, regs[1]);
-                pf_fetch(v[d], scv[d]);                                // the registers are free: request the block kAhead rounds on
                 if (!(UOCR_GEMM_ABLATE & 1)) { tc_st8(dst + 16u, regs[0]); tc_st8(dst + 24u, regs[1]); }
                 else if (regs[0][0] == 0x12345u && regs[1][7] == 0x54321u) *abort_flag = 2;
-                pending = true;
+                {   // publish at once: the other three groups keep the arithmetic units busy while these stores land
+                    GT_BEGIN(gt_p);
+                    tc_st_wait();
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) gb_arrive(&full[grp]);              // one arrival per warp: its stores have all landed
+                    GT_ADD(3, gt_p);
+                }
+                pf_fetch(v[d], scv[d]);                                // the registers are free: request the block kAhead rounds on
                 ++use;
             }
         }
-        if (pending) publish();
 #ifdef UOCR_GEMM_TRACE
         GT_ADD(2, gt_all);
         if (tid == 0) {
