@@ -131,7 +131,7 @@ def test_layers_from_a_file_equal_layers_from_descriptors(pkg, port, tmp_path, e
         assert map_file(from_file, path, TINY, 1, 2) == 2
         for l in (1, 2):
             from_desc.map_layer(layers[l])
-        assert from_file.model_view_bytes() == from_desc.model_view_bytes()
+        assert from_file.model_view_bytes == from_desc.model_view_bytes
         got = run_stack(from_file, 2, hidden, n)
         want = run_stack(from_desc, 2, hidden, n)
     for a, b in zip(got, want):
@@ -169,7 +169,7 @@ def test_files_the_reference_host_refuses_are_refused(pkg, tmp_path):
     with pkg.Context() as ctx:
         with pytest.raises(pkg.UocrCudaError, match="layer 2 are not interleaved-contiguous at expert 5"):
             map_file(ctx, gap, TINY, 1, 2)
-        assert ctx.layer_count() == 0                      # layer 1 was fine, but nothing stays mapped
+        assert ctx.layer_count == 0                      # layer 1 was fine, but nothing stays mapped
         with pytest.raises(pkg.UocrCudaError, match="layer 3: MoE router is missing"):
             map_file(ctx, good, TINY, 1, 3)
         with pytest.raises(pkg.UocrCudaError, match="router has 8 rows for 16 experts"):
@@ -185,7 +185,7 @@ def test_files_the_reference_host_refuses_are_refused(pkg, tmp_path):
         with pytest.raises(pkg.UocrCudaError, match="outside the file"):
             ctx.map_model(data.ctypes.data, data.size - 8192, data.ctypes.data + entries, count, routed_experts=8, top_k=2,
                           first_moe_layer=1, moe_layer_count=2)
-        assert ctx.layer_count() == 0
+        assert ctx.layer_count == 0
         assert map_file(ctx, good, TINY, 1, 2) == 2
         with pytest.raises(pkg.UocrCudaError, match="already mapped"):
             map_file(ctx, good, TINY, 1, 2)
