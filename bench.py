@@ -315,7 +315,11 @@ def make_flush(torch):
 
 
 def timed_steps(torch, dist, world, stream, flush_l2, fn, steps: int, warmup: int) -> list[float]:
-    """W untimed steps, then K steps each between two CUDA events on the launching stream (ms per step)."""
+    """W untimed steps, then K steps each between two CUDA events on the launching stream (ms per step).
+    On several GPUs every step starts behind a barrier of all ranks that is ordered on the stream (a one-element
+    all-reduce), not one that blocks the host: with a host-blocking barrier the host could not run ahead of the GPU and
+    its launch latency (and the scheduling noise of N processes on one host) would sit between the two events."""
+    token = torch.zeros(1, dtype=torch.int32, device="cuda") if world > 1 else None
     for i in range(warmup):
         flush_l2(i)
         fn()
@@ -328,7 +332,7 @@ def timed_steps(torch, dist, world, stream, flush_l2, fn, steps: int, warmup: in
     for i in range(steps):
         flush_l2(i)
         if world > 1:
-            dist.barrier()                     # every rank starts the step together; the barrier is not timed
+            dist.all_reduce(token)             # every rank starts the step together; the barrier is not timed
         starts[i].record(stream)
         fn()
         ends[i].record(stream)
@@ -466,8 +470,9 @@ def measure_ep(pkg, torch, dist, rank: int, world: int, flush_l2, steps: int, wa
     exchange = "none (one GPU)"
     pair_counts = {}
 
-    def run_variant(name: str, li: int) -> None:
-        """Time one mapped layer (index li) sharded over the ranks; result[name] gets the figures."""
+    def run_variant(name: str, li: int, collectives: bool = False) -> None:
+        """Time one mapped layer (index li) sharded over the ranks; result[name] gets the figures.  collectives: the
+        peer-memory form with torch.distributed collectives between its phases instead of the device-side flags."""
         nonlocal exchange
         layer = None
         if world > 1 and exchange_kind == "peer":
@@ -475,8 +480,8 @@ def measure_ep(pkg, torch, dist, rank: int, world: int, flush_l2, steps: int, wa
             try:
                 layer = pkg.ep.PeerExpertParallelLayer(ctx, li, E, K, H, row_capacity=n_total * K, rank=rank, world=world,
                                                        dist_module=dist)
-                exchange = ("peer memory (CUDA IPC over NVLink), fused into gather and combine; counts and row offsets "
-                            "stay on the device")
+                exchange = ("peer memory (CUDA IPC over NVLink), fused into gather and combine; counts, row offsets and the "
+                            "synchronisation of the ranks (flags in peer memory) stay on the device")
             except Exception as e:      # e.g. no peer access between the devices: every rank must then take the other path
                 why = str(e)[:200]
             ok = torch.tensor([1 if layer is not None else 0], device="cuda")
@@ -491,12 +496,15 @@ def measure_ep(pkg, torch, dist, rank: int, world: int, flush_l2, steps: int, wa
                 exchange = "nccl all_to_all_single"
             layer = pkg.ep.ExpertParallelLayer(ctx, li, E, K, H, rank=rank, world=world, dist_module=dist if world > 1 else None)
             layer.reserve(n_local, n_total * K)
-        step = lambda: layer.forward(d_h, d_out, residual=d_r)
+        peer_form = isinstance(layer, pkg.ep.PeerExpertParallelLayer)
+        if collectives and not peer_form:
+            return
+        step = (lambda: layer.forward_collectives(d_h, d_out, residual=d_r)) if collectives else (lambda: layer.forward(d_h, d_out, residual=d_r))
         launches0 = ctx.kernel_launches
         times = timed_steps(torch, dist, world, stream, flush_l2, step, steps, warmup)
         launches = (ctx.kernel_launches - launches0) // (steps + warmup)
         plan = layer.last_plan
-        pair_counts[name] = pkg.ep.counts_from_offsets(layer._all_offsets.cpu().numpy()).sum(axis=0)
+        pair_counts[name] = layer.gathered_counts().sum(axis=0)
         e2e_ms = 0.0
         if with_e2e:
             wall = []
@@ -563,6 +571,10 @@ def measure_ep(pkg, torch, dist, rank: int, world: int, flush_l2, steps: int, wa
         order = pkg.ep.balanced_placement(pair_counts["zipf"], world)
         run_variant("zipf_balanced_placement", ctx.map_layer(quant.permute_experts(L, order)))
         result["zipf_balanced_placement"]["placement"] = "experts relabelled by ep.balanced_placement(observed pair counts)"
+        run_variant("zipf_synchronised_by_collectives", layer_of["zipf"], collectives=True)
+        if "zipf_synchronised_by_collectives" in result:
+            result["zipf_synchronised_by_collectives"]["note"] = ("the same peer-memory exchange with one all_gather of the counts and two "
+                                                                  "all-reduce barriers of torch.distributed per call instead of flags in peer memory")
     result["exchange"] = exchange
     ctx.synchronize()
     ctx.close()

@@ -400,6 +400,19 @@ UOCR_CUDA_API int uocr_cuda_moe_ep_peer_experts(uocr_cuda_context *ctx, uint32_t
 UOCR_CUDA_API int uocr_cuda_moe_ep_peer_scatter_dev(uocr_cuda_context *ctx, uint32_t layer, const void *d_hidden_f16,
                                                     uint32_t n_tokens, const uint32_t *d_all_offsets, char *error, size_t error_size);
 UOCR_CUDA_API int uocr_cuda_moe_ep_peer_experts_dev(uocr_cuda_context *ctx, uint32_t layer, char *error, size_t error_size);
+/* The whole expert-parallel layer call with the ranks synchronised ON THE DEVICE: router, plan, count exchange, scatter,
+ * experts and combine are queued in one go; between them the ranks signal one another through flags in peer memory
+ * (a release store of the call's number into every peer, a bounded wait on the own flags) instead of host-side
+ * collectives.  Every rank of the group must issue the call, in the same order on every rank.  A peer that does not
+ * reach the call within about two seconds makes the waiting kernels give up; the next uocr_cuda_context_synchronize
+ * then fails with a message, and nothing is left hanging. */
+UOCR_CUDA_API int uocr_cuda_moe_ep_peer_forward(uocr_cuda_context *ctx, uint32_t layer, const void *d_hidden,
+                                                const void *d_residual, uint32_t n_tokens, void *d_out, char *error,
+                                                size_t error_size);
+/* Every rank's expert offsets of the last uocr_cuda_moe_ep_peer_forward call, h_all_offsets [world][n_experts + 1]
+ * (waits for the stream; meant for load statistics). */
+UOCR_CUDA_API int uocr_cuda_moe_ep_peer_last_offsets(uocr_cuda_context *ctx, uint32_t n_experts, uint32_t *h_all_offsets,
+                                                     char *error, size_t error_size);
 UOCR_CUDA_API int uocr_cuda_moe_ep_peer_combine(uocr_cuda_context *ctx, uint32_t layer, const void *d_residual_f16,
                                                 uint32_t n_tokens, void *d_out_f16, char *error, size_t error_size);
 

@@ -49,7 +49,7 @@ def main():
         # the same layer with the exchange over peer memory (CUDA IPC mappings of the other ranks' buffers)
         peer = pkg.ep.PeerExpertParallelLayer(ctx, 0, dims["E"], dims["K"], dims["H"], row_capacity=n_total * dims["K"],
                                               rank=rank, world=world, dist_module=dist)
-        for call in (peer.forward, peer.forward_host_counts, peer.forward):      # row offsets computed on the device / on the host
+        for call in (peer.forward, peer.forward_collectives, peer.forward_host_counts, peer.forward):   # ranks synchronised on the device / by collectives / offsets on the host
             out2 = torch.zeros_like(mine)
             call(mine, out2, residual=r_all[lo:hi].contiguous())
             ctx.synchronize()

@@ -78,7 +78,7 @@ def test_peer_memory_phases_on_one_gpu_equal_the_layer_call(pkg):
         want = torch.zeros_like(d_h)
         ctx.layer_forward(0, d_h, n, want, residual=d_r)
         layer = pkg.ep.PeerExpertParallelLayer(ctx, 0, FULL["E"], FULL["K"], FULL["H"], row_capacity=n * FULL["K"])
-        for call in (layer.forward, layer.forward_host_counts, layer.forward):      # offsets computed on the device / on the host
+        for call in (layer.forward, layer.forward_collectives, layer.forward_host_counts, layer.forward):   # ranks synchronised on the device / by collectives / offsets on the host
             got = torch.zeros_like(d_h)
             call(d_h, got, residual=d_r)
             ctx.synchronize()

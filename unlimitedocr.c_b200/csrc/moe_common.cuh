@@ -168,6 +168,11 @@ __device__ __forceinline__ float silu_fast_f32(float v) { return __fdividef(v, 1
 // One buffer per rank of an expert-parallel group on one node (this rank's own and the peers' mapped ones).
 constexpr int kMaxPeers = 16;
 struct PeerBuffers { __half *p[kMaxPeers]; };
+// the ranks' synchronisation regions (see ep_exchange_counts_kernel): offsets of every source rank, then three rows of flags
+struct PeerSync { uint32_t *p[kMaxPeers]; };
+constexpr uint32_t kSyncStride = 260;                          // words per source rank (E + 1 <= 257)
+constexpr uint32_t kSyncFlagWords = kMaxPeers * kSyncStride;   // word offset of the flags
+constexpr size_t kSyncBytes = (size_t)(kSyncFlagWords + 3 * kMaxPeers) * 4;
 
 // Run-time settings of the single-token decode kernel (a context reads them from the environment when it is created).
 struct SlicedKnobs {

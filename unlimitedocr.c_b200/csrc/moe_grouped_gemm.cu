@@ -728,41 +728,45 @@ __global__ void tile_plan_kernel(const uint32_t *__restrict__ expert_offsets, ui
                                  uint4 *__restrict__ tiles_dn, uint32_t *__restrict__ counts) {
     // The lists start with the segment that has the most rows (ties: lower index first): the persistent GEMM kernel
     // deals tiles to its CTAs in list order, so the long segments are under way first and the short ones fill the tail.
-    __shared__ uint32_t base_gu[257], base_dn[257], order[256];
-    const uint32_t e = threadIdx.x;
-    if (e < E) {
-        const uint32_t c = expert_offsets[e + 1] - expert_offsets[e];
+    // One CTA; the entries are then written by all its threads, entry i finding its segment by binary search.
+    __shared__ uint32_t order[256], first_tile[257];         // segments by rank; token tiles before the segment of rank k
+    const uint32_t tid = threadIdx.x;
+    if (tid < E) {
+        const uint32_t c = expert_offsets[tid + 1] - expert_offsets[tid];
         uint32_t rank = 0;
         for (uint32_t j = 0; j < E; ++j) {
             const uint32_t cj = expert_offsets[j + 1] - expert_offsets[j];
-            rank += (cj > c || (cj == c && j < e)) ? 1u : 0u;
+            rank += (cj > c || (cj == c && j < tid)) ? 1u : 0u;
         }
-        order[rank] = e;
+        order[rank] = tid;
     }
     __syncthreads();
-    if (threadIdx.x == 0) {
-        uint32_t rg = 0, rd = 0;
+    if (tid == 0) {
+        uint32_t run = 0;
         for (uint32_t k = 0; k < E; ++k) {
             const uint32_t i = order[k];
-            const uint32_t c = expert_offsets[i + 1] - expert_offsets[i];
-            base_gu[i] = rg; base_dn[i] = rd;
-            rg += (c + kTileN - 1) / kTileN;
-            rd += (c + kTileN - 1) / kTileN;
+            first_tile[k] = run;
+            run += (expert_offsets[i + 1] - expert_offsets[i] + kTileN - 1) / kTileN;
         }
-        counts[0] = rg * gu_mtiles;
-        counts[1] = rd * dn_mtiles;
+        first_tile[E] = run;
+        counts[0] = run * gu_mtiles;
+        counts[1] = run * dn_mtiles;
     }
     __syncthreads();
-    if (e < E) {
-        const uint32_t lo = expert_offsets[e], cnt = expert_offsets[e + 1] - lo;
-        for (uint32_t t = 0; t * kTileN < cnt; ++t) {
-            const uint32_t r0 = lo + t * kTileN, nr = min((uint32_t)kTileN, cnt - t * kTileN);
-            for (uint32_t m = 0; m < gu_mtiles; ++m) tiles_gu[(size_t)(base_gu[e] + t) * gu_mtiles + m] = make_uint4(expert_base + e % expert_mod, m, r0, nr);
+    const uint32_t token_tiles = first_tile[E];
+    for (uint32_t i = tid; i < token_tiles * (gu_mtiles + dn_mtiles); i += blockDim.x) {
+        const bool gu = i < token_tiles * gu_mtiles;
+        const uint32_t mtiles = gu ? gu_mtiles : dn_mtiles, j = gu ? i : i - token_tiles * gu_mtiles;
+        const uint32_t tt = j / mtiles, m = j % mtiles;       // token tile of the whole list, weight-row tile
+        uint32_t lo = 0, hi = E;                              // the rank k with first_tile[k] <= tt < first_tile[k + 1]
+        while (hi - lo > 1) {
+            const uint32_t mid = (lo + hi) / 2;
+            if (first_tile[mid] <= tt) lo = mid; else hi = mid;
         }
-        for (uint32_t t = 0; t * kTileN < cnt; ++t) {
-            const uint32_t r0 = lo + t * kTileN, nr = min((uint32_t)kTileN, cnt - t * kTileN);
-            for (uint32_t m = 0; m < dn_mtiles; ++m) tiles_dn[(size_t)(base_dn[e] + t) * dn_mtiles + m] = make_uint4(expert_base + e % expert_mod, m, r0, nr);
-        }
+        const uint32_t e = order[lo], t = tt - first_tile[lo];
+        const uint32_t seg0 = expert_offsets[e], cnt = expert_offsets[e + 1] - seg0;
+        const uint4 entry = make_uint4(expert_base + e % expert_mod, m, seg0 + t * kTileN, min((uint32_t)kTileN, cnt - t * kTileN));
+        (gu ? tiles_gu : tiles_dn)[j] = entry;
     }
 }
 
@@ -1060,7 +1064,7 @@ cudaError_t launch_gemm_experts(const DLayer &L, const Scratch &S, const GemmScr
     if (rows_bound == 0) return cudaSuccess;
     const uint32_t ttiles = (rows_bound + kTileN - 1) / kTileN + n_seg;     // token tiles: an upper bound known on the host
     cudaError_t err;
-    tile_plan_kernel<<<1, 256, 0, st>>>(seg_offsets, n_seg, expert_base, expert_mod, F / (kTileM / 2), H / kTileM, G.tiles_gu,
+    tile_plan_kernel<<<1, 1024, 0, st>>>(seg_offsets, n_seg, expert_base, expert_mod, F / (kTileM / 2), H / kTileM, G.tiles_gu,
                                         G.tiles_dn, G.counts);
     ++*launches;
     if ((err = cudaGetLastError()) != cudaSuccess) return err;
@@ -1184,6 +1188,92 @@ cudaError_t launch_ep_offsets(const uint32_t *all_offsets, uint32_t world, uint3
                               unsigned long long row_capacity, uint32_t *dst_row0, uint32_t *seg_offsets, uint32_t *status,
                               cudaStream_t st, uint64_t *launches) {
     ep_offsets_kernel<<<1, 256, 0, st>>>(all_offsets, world, rank, E, row_capacity, dst_row0, seg_offsets, status);
+    ++*launches;
+    return cudaGetLastError();
+}
+
+// ---- synchronisation of the expert-parallel ranks on the device ----------------------------------------------------
+// Every rank owns a small "sync" region that the other ranks write over NVLink: for each source rank its expert offsets
+// of the current call ([kMaxPeers][kSyncStride] words), then three rows of flags ([3][kMaxPeers] words: counts written,
+// rows landed, outputs written) that hold the number of the call that last set them.  A rank signals by a release store
+// of the call number into every peer's flag and waits (bounded, in its own memory) until all its own flags have reached
+// that number, so no host library call stands between the phases.  Every rank runs these kernels on its own GPU.
+constexpr uint32_t kStatusPeerSync = 64u;
+constexpr long long kPeerSpinLimit = 4000000000LL;      // cycles (~2 s)
+
+__device__ __forceinline__ void st_release_sys(uint32_t *p, uint32_t v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t *p) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+// thread g < world: tell rank g that this rank has reached `call` in phase `which`, then wait for rank g to have told us
+__device__ __forceinline__ void peer_signal_and_wait(const PeerSync &sync, uint32_t world, uint32_t rank, uint32_t which,
+                                                     uint32_t call, uint32_t *status) {
+    const uint32_t g = threadIdx.x;
+    if (g >= world) return;
+    __threadfence_system();
+    st_release_sys(sync.p[g] + kSyncFlagWords + which * kMaxPeers + rank, call);
+    const uint32_t *mine = sync.p[rank] + kSyncFlagWords + which * kMaxPeers + g;
+    const long long t0 = clock64();
+    while ((int)(ld_acquire_sys(mine) - call) < 0) {
+        __nanosleep(100);
+        if (clock64() - t0 > kPeerSpinLimit) { atomicOr(status, kStatusPeerSync); break; }
+    }
+}
+
+// Publishes this rank's expert offsets to every rank, waits for everybody's, and derives the rows of the exchange (the
+// arithmetic of ep_offsets_kernel on the gathered offsets).
+__global__ void ep_exchange_counts_kernel(const uint32_t *__restrict__ my_offsets, PeerSync sync, uint32_t world, uint32_t rank,
+                                          uint32_t E, uint32_t call, unsigned long long row_capacity,
+                                          uint32_t *__restrict__ dst_row0, uint32_t *__restrict__ seg_offsets,
+                                          uint32_t *__restrict__ status) {
+    const uint32_t tid = threadIdx.x, per = E / world;
+    for (uint32_t g = 0; g < world; ++g) {
+        volatile uint32_t *dst = sync.p[g] + rank * kSyncStride;
+        for (uint32_t i = tid; i <= E; i += blockDim.x) dst[i] = my_offsets[i];
+    }
+    __syncthreads();                      // (the signalling threads fence at system scope before their release stores)
+    peer_signal_and_wait(sync, world, rank, 0, call, status);
+    __syncthreads();
+    const volatile uint32_t *all = sync.p[rank];
+    for (uint32_t e = tid; e < E; e += blockDim.x) {
+        const uint32_t owner = e / per, first = owner * per;
+        unsigned long long row = 0;
+        for (uint32_t g = 0; g < rank; ++g) row += all[g * kSyncStride + first + per] - all[g * kSyncStride + first];
+        row += all[rank * kSyncStride + e] - all[rank * kSyncStride + first];
+        dst_row0[e] = row > 0xffffffffull ? 0xffffffffu : (uint32_t)row;
+    }
+    if (tid == 0) {
+        unsigned long long run = 0;
+        for (uint32_t src = 0; src < world; ++src)
+            for (uint32_t le = 0; le < per; ++le) {
+                seg_offsets[src * per + le] = (uint32_t)run;
+                run += all[src * kSyncStride + rank * per + le + 1] - all[src * kSyncStride + rank * per + le];
+            }
+        if (run > row_capacity) { atomicOr(status, kStatusPeerRange); run = row_capacity; }
+        seg_offsets[world * per] = (uint32_t)run;
+    }
+}
+
+__global__ void ep_signal_wait_kernel(PeerSync sync, uint32_t world, uint32_t rank, uint32_t which, uint32_t call,
+                                      uint32_t *__restrict__ status) {
+    peer_signal_and_wait(sync, world, rank, which, call, status);
+}
+
+cudaError_t launch_ep_exchange_counts(const uint32_t *my_offsets, const PeerSync &sync, uint32_t world, uint32_t rank, uint32_t E,
+                                      uint32_t call, unsigned long long row_capacity, uint32_t *dst_row0, uint32_t *seg_offsets,
+                                      uint32_t *status, cudaStream_t st, uint64_t *launches) {
+    ep_exchange_counts_kernel<<<1, 256, 0, st>>>(my_offsets, sync, world, rank, E, call, row_capacity, dst_row0, seg_offsets, status);
+    ++*launches;
+    return cudaGetLastError();
+}
+
+cudaError_t launch_ep_signal_wait(const PeerSync &sync, uint32_t world, uint32_t rank, uint32_t which, uint32_t call,
+                                  uint32_t *status, cudaStream_t st, uint64_t *launches) {
+    ep_signal_wait_kernel<<<1, 32, 0, st>>>(sync, world, rank, which, call, status);
     ++*launches;
     return cudaGetLastError();
 }

@@ -30,6 +30,11 @@ cudaError_t launch_scatter_peer(const DLayer &L, const Scratch &S, const __half 
 cudaError_t launch_combine_peer(const DLayer &L, const Scratch &S, const GemmScratch &G, const PeerBuffers &done,
                                 uint32_t experts_per_rank, const uint32_t *dst_row0, unsigned long long row_capacity,
                                 const __half *residual, uint32_t n, __half *out, cudaStream_t st, uint64_t *launches);
+cudaError_t launch_ep_exchange_counts(const uint32_t *my_offsets, const PeerSync &sync, uint32_t world, uint32_t rank, uint32_t E,
+                                      uint32_t call, unsigned long long row_capacity, uint32_t *dst_row0, uint32_t *seg_offsets,
+                                      uint32_t *status, cudaStream_t st, uint64_t *launches);
+cudaError_t launch_ep_signal_wait(const PeerSync &sync, uint32_t world, uint32_t rank, uint32_t which, uint32_t call,
+                                  uint32_t *status, cudaStream_t st, uint64_t *launches);
 cudaError_t launch_ep_offsets(const uint32_t *all_offsets, uint32_t world, uint32_t rank, uint32_t E,
                               unsigned long long row_capacity, uint32_t *dst_row0, uint32_t *seg_offsets, uint32_t *status,
                               cudaStream_t st, uint64_t *launches);
@@ -121,6 +126,8 @@ struct uocr_cuda_context {
         uint64_t row_capacity = 0;
         __half *recv = nullptr, *done = nullptr;        // this rank's buffers
         uocr::PeerBuffers recv_all{}, done_all{};      // every rank's (own pointers + mapped peers)
+        uocr::PeerSync sync{};                         // every rank's synchronisation region (it follows the received rows)
+        uint32_t call = 0;                             // number of the last device-synchronised layer call
         uint32_t *d_dst_row0 = nullptr;                // [256] device copy of the scatter offsets of the current call
         bool opened = false;
     } peer;
@@ -417,6 +424,7 @@ extern "C" int uocr_cuda_context_synchronize(uocr_cuda_context *ctx, char *error
                     : (st & 4u) ? "a bulk copy of the decode kernel timed out"
                     : (st & 8u) ? "a pipeline wait of the grouped GEMM kernel timed out"
                     : (st & 16u) ? "the decode kernel met a non-finite or out-of-range partial output"
+                    : (st & 64u) ? "a rank of the expert-parallel group did not reach the call in time (wait for a peer's flag ran out)"
                     : (st & 32u) ? "a row index left the expert-parallel exchange buffers (inconsistent counts between the ranks)"
                                 : "kernel reported an internal error");
     }
@@ -1252,7 +1260,10 @@ extern "C" int uocr_cuda_moe_ep_peer_create(uocr_cuda_context *ctx, uint32_t hid
     CU_TRY(ctx, cudaSetDevice(ctx->device));
     auto &P = ctx->peer;
     const size_t bytes = (size_t)row_capacity * hidden_size * 2;
-    CU_TRY(ctx, cudaMalloc(&P.recv, bytes));
+    // the synchronisation region shares the allocation (and so the IPC handle) of the received rows
+    const size_t sync_off = (bytes + 255) & ~(size_t)255;
+    CU_TRY(ctx, cudaMalloc(&P.recv, sync_off + uocr::kSyncBytes));
+    CU_TRY(ctx, cudaMemset((uint8_t *)P.recv + sync_off, 0, uocr::kSyncBytes));
     CU_TRY(ctx, cudaMalloc(&P.done, bytes));
     CU_TRY(ctx, cudaMalloc(&P.d_dst_row0, 256 * sizeof(uint32_t)));
     P.hidden = hidden_size; P.row_capacity = row_capacity;
@@ -1283,6 +1294,8 @@ extern "C" int uocr_cuda_moe_ep_peer_open(uocr_cuda_context *ctx, uint32_t world
         CU_TRY(ctx, cudaIpcOpenMemHandle(&b, h[2 * g + 1], cudaIpcMemLazyEnablePeerAccess));
         P.done_all.p[g] = (__half *)b;
     }
+    const size_t sync_off = ((size_t)P.row_capacity * P.hidden * 2 + 255) & ~(size_t)255;
+    for (uint32_t g = 0; g < world; ++g) P.sync.p[g] = (uint32_t *)((uint8_t *)P.recv_all.p[g] + sync_off);
     P.opened = true;
     return 1;
 }
@@ -1386,6 +1399,58 @@ extern "C" int uocr_cuda_moe_ep_peer_experts_dev(uocr_cuda_context *ctx, uint32_
     const uint32_t bound = (uint32_t)(P.row_capacity < cap_rows ? P.row_capacity : cap_rows);      // rows this rank can hold
     CU_TRY(ctx, uocr::launch_gemm_experts(L, s, g, (const uint32_t *)(ctx->arena + a.seg_offsets), P.world * per, P.rank * per, per,
                                           P.recv, bound, g.mid_sorted, P.done, ctx->stream, &ctx->launches));
+    return 1;
+}
+
+// One whole expert-parallel layer call with the ranks synchronised on the device: dispatch, count exchange, scatter,
+// "rows landed", experts, "outputs written", combine.  No host library call and no host read in between; every rank of the
+// group must issue the call (the flags carry the call's number).
+extern "C" int uocr_cuda_moe_ep_peer_forward(uocr_cuda_context *ctx, uint32_t layer, const void *d_hidden, const void *d_residual,
+                                             uint32_t n, void *d_out, char *error, size_t error_size) {
+    if (!check_call(ctx, layer, n, error, error_size)) return 0;
+    if (!d_hidden || !d_out) return fail(ctx, error, error_size, "null expert-parallel layer argument");
+    const DLayer &L = ctx->layers[layer];
+    if (!uocr::gemm_path_supported(L)) return fail(ctx, error, error_size, "layer shape not supported by the tensor-core path");
+    if (!peer_ready(ctx, L, error, error_size)) return 0;
+    auto &P = ctx->peer;
+    ArenaLayout a;
+    Scratch s = carve(ctx, L, ctx->token_capacity, &a);
+    const uocr::GemmScratch g = gemm_scratch(ctx, s, a);
+    const uint32_t per = L.E / P.world, call = ++P.call;
+    const unsigned long long cap_rows = (unsigned long long)ctx->token_capacity * L.K;
+    const unsigned long long bound = P.row_capacity < cap_rows ? P.row_capacity : cap_rows;       // rows this rank can hold
+    uint32_t *seg_offsets = (uint32_t *)(ctx->arena + a.seg_offsets);
+    if (!uocr_cuda_moe_ep_shared(ctx, layer, d_hidden, n, error, error_size)) return 0;      // second stream, beside all that follows
+    CU_TRY(ctx, uocr::launch_router(L, (const __half *)d_hidden, nullptr, n, nullptr, nullptr, s.top_ids, s.top_weights,
+                                    ctx->status, s.logits, ctx->stream, &ctx->launches));
+    CU_TRY(ctx, uocr::launch_dispatch_plan(s.top_ids, n, L.K, L.E, s.expert_offsets, s.pair_rows, s.inverse, s.active,
+                                           s.plan_counts, ctx->stream, &ctx->launches));
+    CU_TRY(ctx, uocr::launch_ep_exchange_counts(s.expert_offsets, P.sync, P.world, P.rank, L.E, call, bound, P.d_dst_row0,
+                                                seg_offsets, ctx->status, ctx->stream, &ctx->launches));
+    CU_TRY(ctx, uocr::launch_scatter_peer(L, s, (const __half *)d_hidden, n, per, P.d_dst_row0, P.recv_all, P.row_capacity,
+                                          ctx->stream, &ctx->launches));
+    CU_TRY(ctx, uocr::launch_ep_signal_wait(P.sync, P.world, P.rank, 1, call, ctx->status, ctx->stream, &ctx->launches));
+    CU_TRY(ctx, uocr::launch_gemm_experts(L, s, g, seg_offsets, P.world * per, P.rank * per, per, P.recv, (uint32_t)bound,
+                                          g.mid_sorted, P.done, ctx->stream, &ctx->launches));
+    CU_TRY(ctx, uocr::launch_ep_signal_wait(P.sync, P.world, P.rank, 2, call, ctx->status, ctx->stream, &ctx->launches));
+    if (!join_shared(ctx, error, error_size)) return 0;
+    CU_TRY(ctx, uocr::launch_combine_peer(L, s, g, P.done_all, per, P.d_dst_row0, P.row_capacity, (const __half *)d_residual, n,
+                                          (__half *)d_out, ctx->stream, &ctx->launches));
+    return 1;
+}
+
+// Every rank's expert offsets of the last uocr_cuda_moe_ep_peer_forward call, [world][E + 1], read back from this rank's
+// synchronisation region (waits for the context's stream; for load statistics, not for the call path).
+extern "C" int uocr_cuda_moe_ep_peer_last_offsets(uocr_cuda_context *ctx, uint32_t n_experts, uint32_t *h_all_offsets,
+                                                  char *error, size_t error_size) {
+    if (!ctx || !h_all_offsets) return fail(ctx, error, error_size, "null argument");
+    auto &P = ctx->peer;
+    if (!P.opened) return fail(ctx, error, error_size, "peer exchange not opened");
+    if (n_experts == 0 || n_experts > 256) return fail(ctx, error, error_size, "invalid expert count %u", n_experts);
+    CU_TRY(ctx, cudaSetDevice(ctx->device));
+    CU_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+    CU_TRY(ctx, cudaMemcpy2D(h_all_offsets, (size_t)(n_experts + 1) * 4, P.sync.p[P.rank], (size_t)uocr::kSyncStride * 4,
+                             (size_t)(n_experts + 1) * 4, P.world, cudaMemcpyDeviceToHost));
     return 1;
 }
 

@@ -128,6 +128,10 @@ class ExpertParallelLayer:
         self._all_offsets = None
         self.last_plan: ExchangePlan | None = None
 
+    def gathered_counts(self) -> np.ndarray:
+        """[world, E] pairs per rank and expert of the last forward call (read back from the device)."""
+        return counts_from_offsets(self._all_offsets.cpu().numpy())
+
     def _buffer(self, name: str, rows: int):
         t = self._bufs.get(name)
         if t is None or t.shape[0] < rows:
@@ -207,8 +211,15 @@ class PeerExpertParallelLayer:
             self.dist.all_reduce(self._token, group=self.group)
 
     def forward(self, hidden, out, *, residual=None) -> None:
-        """One layer call.  Nothing is read back to the host: the per-rank counts stay on the device (one all_gather),
-        the row offsets of the scatter and of the experts phase are computed there (last_plan reads them on demand)."""
+        """One layer call, queued in one go: the ranks exchange their counts and signal "rows landed" / "outputs written"
+        to one another through flags in peer memory, inside the library's own kernels; no collective of
+        torch.distributed runs and the host reads nothing."""
+        self.ctx.ep_peer_forward(self.layer, hidden, hidden.shape[0], out, residual=residual)
+        self._device_synced = True
+
+    def forward_collectives(self, hidden, out, *, residual=None) -> None:
+        """The same call with torch.distributed between the phases: one all_gather of the per-rank counts into device
+        memory and two 4-byte all-reduces as barriers (the form the device-side flags replaced; kept for comparison)."""
         n = hidden.shape[0]
         self.ctx.ep_peer_dispatch(self.layer, hidden, n, self._offsets)
         self.ctx.ep_shared(self.layer, hidden, n)            # on the context's second stream, beside all that follows
@@ -221,6 +232,7 @@ class PeerExpertParallelLayer:
         self.ctx.ep_peer_experts_dev(self.layer)
         self._barrier()                                      # every owner's outputs are written
         self.ctx.ep_peer_combine(self.layer, n, out, residual=residual)
+        self._device_synced = False
 
     def forward_host_counts(self, hidden, out, *, residual=None) -> ExchangePlan:
         """The same call with the counts read back and the row offsets computed on the host (the earlier form, kept for
@@ -242,10 +254,20 @@ class PeerExpertParallelLayer:
         self.ctx.ep_peer_combine(self.layer, n, out, residual=residual)
         return plan
 
+    def gathered_counts(self) -> np.ndarray:
+        """[world, E] pairs per rank and expert of the last forward call (read back from the device)."""
+        if getattr(self, "_device_synced", False):
+            return counts_from_offsets(self.ctx.ep_peer_last_offsets(self.world, self.E).astype(np.int64))
+        return counts_from_offsets(self._all_offsets.cpu().numpy())
+
     @property
     def last_plan(self) -> ExchangePlan:
         """Row counts of the last forward call (reads the gathered offsets from the device)."""
-        return plan_from_counts(counts_from_offsets(self._all_offsets.cpu().numpy()), self.rank)
+        if getattr(self, "_device_synced", False):
+            offsets = self.ctx.ep_peer_last_offsets(self.world, self.E).astype(np.int64)
+        else:
+            offsets = self._all_offsets.cpu().numpy()
+        return plan_from_counts(counts_from_offsets(offsets), self.rank)
 
     def close(self, *, group_barrier: bool = True) -> None:
         """Unmap the peers' buffers and free this rank's.  A peer's scatter or combine kernel may still be reading or

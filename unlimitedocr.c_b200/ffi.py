@@ -64,7 +64,7 @@ EXPORTS = (
     "uocr_cuda_moe_dispatch_plan", "uocr_cuda_moe_dispatch_plan_noalloc", "uocr_cuda_moe_debug_dequantize", "uocr_cuda_moe_regime_name", "uocr_cuda_moe_layer_forward", "uocr_cuda_moe_stack_forward",
     "uocr_cuda_moe_layer_forward_host", "uocr_cuda_moe_stack_forward_host",
     "uocr_cuda_moe_ep_dispatch", "uocr_cuda_moe_ep_experts", "uocr_cuda_moe_ep_shared", "uocr_cuda_moe_ep_combine",
-    "uocr_cuda_moe_ep_peer_create", "uocr_cuda_moe_ep_peer_open", "uocr_cuda_moe_ep_peer_destroy",
+    "uocr_cuda_moe_ep_peer_forward", "uocr_cuda_moe_ep_peer_last_offsets", "uocr_cuda_moe_ep_peer_create", "uocr_cuda_moe_ep_peer_open", "uocr_cuda_moe_ep_peer_destroy",
     "uocr_cuda_moe_ep_peer_dispatch", "uocr_cuda_moe_ep_peer_scatter", "uocr_cuda_moe_ep_peer_experts",
     "uocr_cuda_moe_ep_peer_combine", "uocr_cuda_moe_ep_peer_scatter_dev", "uocr_cuda_moe_ep_peer_experts_dev",
 )
@@ -142,6 +142,8 @@ def load_library() -> C.CDLL:
         "uocr_cuda_moe_ep_peer_scatter": (C.c_int, [vp, u32, vp, u32, vp] + err),
         "uocr_cuda_moe_ep_peer_experts": (C.c_int, [vp, u32, u32, vp] + err),
         "uocr_cuda_moe_ep_peer_combine": (C.c_int, [vp, u32, vp, u32, vp] + err),
+        "uocr_cuda_moe_ep_peer_forward": (C.c_int, [vp, u32, vp, vp, u32, vp] + err),
+        "uocr_cuda_moe_ep_peer_last_offsets": (C.c_int, [vp, u32, vp] + err),
         "uocr_cuda_moe_ep_peer_scatter_dev": (C.c_int, [vp, u32, vp, u32, vp] + err),
         "uocr_cuda_moe_ep_peer_experts_dev": (C.c_int, [vp, u32] + err),
     }
@@ -415,6 +417,17 @@ class Context:
 
     def ep_peer_experts_dev(self, layer: int) -> None:
         self._check(self._lib.uocr_cuda_moe_ep_peer_experts_dev(self._h, layer, self._err, _ERR))
+
+    def ep_peer_forward(self, layer: int, hidden, n_tokens: int, out, *, residual=None) -> None:
+        """The whole expert-parallel layer call, the ranks synchronised on the device (uocr_cuda_moe_ep_peer_forward)."""
+        self._check(self._lib.uocr_cuda_moe_ep_peer_forward(self._h, layer, _dev_ptr(hidden), _dev_ptr(residual), n_tokens,
+                                                            _dev_ptr(out), self._err, _ERR))
+
+    def ep_peer_last_offsets(self, world: int, n_experts: int) -> np.ndarray:
+        """Every rank's expert offsets of the last ep_peer_forward call, uint32 [world, n_experts + 1]."""
+        out = np.zeros((world, n_experts + 1), dtype=np.uint32)
+        self._check(self._lib.uocr_cuda_moe_ep_peer_last_offsets(self._h, n_experts, out.ctypes.data, self._err, _ERR))
+        return out
 
     def ep_peer_combine(self, layer: int, n_tokens: int, out, *, residual=None) -> None:
         self._check(self._lib.uocr_cuda_moe_ep_peer_combine(self._h, layer, _dev_ptr(residual), n_tokens, _dev_ptr(out),
