@@ -879,7 +879,14 @@ __global__ void scatter_rows_peer_kernel(const __half *__restrict__ hidden, cons
     }
     const uint4 *src = reinterpret_cast<const uint4 *>(hidden + (size_t)(pair_rows[pos] / K) * H);
     uint4 *dst = reinterpret_cast<uint4 *>(peer.p[e / experts_per_rank] + (size_t)row * H);
-    for (uint32_t i = lane; i < H / 8; i += 32) dst[i] = __ldg(src + i);
+    // all of the row's loads are issued before the first (remote) store
+    uint4 v[8];                                 // H <= 2048: at most eight 16-byte pieces per lane
+#pragma unroll
+    for (uint32_t k = 0; k < 8; ++k)
+        if (lane + 32 * k < H / 8) v[k] = __ldg(src + lane + 32 * k);
+#pragma unroll
+    for (uint32_t k = 0; k < 8; ++k)
+        if (lane + 32 * k < H / 8) dst[lane + 32 * k] = v[k];
 }
 
 __device__ __forceinline__ uint4 ld_volatile_v4(const uint4 *p) {
@@ -902,19 +909,41 @@ __global__ void combine_peer_kernel(PeerBuffers peer, const __half *__restrict__
     float acc[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) acc[i] = 0.f;
-    for (uint32_t s = 0; s < K; ++s) {
-        const uint32_t pos = inverse[t * K + s], e = top_ids[t * K + s];
-        if (pos == 0xffffffffu || e >= E) continue;
-        const unsigned long long row = (unsigned long long)dst_row0[e] + (pos - expert_offsets[e]);
-        if (row >= row_capacity) { atomicOr(status, kStatusPeerRange); continue; }
-        const float w = weights[t * K + s];
-        const uint4 v = ld_volatile_v4(reinterpret_cast<const uint4 *>(peer.p[e / experts_per_rank] + (size_t)row * H + c));
-        const __half2 *h = reinterpret_cast<const __half2 *>(&v);
+    // A remote row takes microseconds to arrive: the loads of up to eight slots are all issued before the first one is
+    // used; the sums still run in slot order, as the single-GPU combine's do.
+    constexpr uint32_t kSlotsInFlight = 8;
+    for (uint32_t s0 = 0; s0 < K; s0 += kSlotsInFlight) {
+        uint4 v[kSlotsInFlight];
+        float w[kSlotsInFlight];
+        bool have[kSlotsInFlight];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const float2 f = __half22float2(h[i]);
-            acc[2 * i] = fmaf(w, f.x, acc[2 * i]);
-            acc[2 * i + 1] = fmaf(w, f.y, acc[2 * i + 1]);
+        for (uint32_t j = 0; j < kSlotsInFlight; ++j) {
+            const uint32_t s = s0 + j;
+            have[j] = false;
+            if (s < K) {
+                const uint32_t pos = inverse[t * K + s], e = top_ids[t * K + s];
+                if (pos != 0xffffffffu && e < E) {
+                    const unsigned long long row = (unsigned long long)dst_row0[e] + (pos - expert_offsets[e]);
+                    if (row >= row_capacity) {
+                        atomicOr(status, kStatusPeerRange);
+                    } else {
+                        have[j] = true;
+                        w[j] = weights[t * K + s];
+                        v[j] = ld_volatile_v4(reinterpret_cast<const uint4 *>(peer.p[e / experts_per_rank] + (size_t)row * H + c));
+                    }
+                }
+            }
+        }
+#pragma unroll
+        for (uint32_t j = 0; j < kSlotsInFlight; ++j) {
+            if (!have[j]) continue;
+            const __half2 *h = reinterpret_cast<const __half2 *>(&v[j]);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float2 f = __half22float2(h[i]);
+                acc[2 * i] = fmaf(w[j], f.x, acc[2 * i]);
+                acc[2 * i + 1] = fmaf(w[j], f.y, acc[2 * i + 1]);
+            }
         }
     }
     {
