@@ -220,6 +220,34 @@ UOCR_CUDA_API int uocr_cuda_context_map_model(uocr_cuda_context *ctx, const uocr
                                               char *error, size_t error_size);
 UOCR_CUDA_API uint32_t uocr_cuda_context_moe_layer_count(const uocr_cuda_context *ctx);
 
+/* ---- the steps either side of the MoE layer.
+ * RMSNorm (uocr_cpu_ref_rmsnorm_f32, src/backend/cpu_ref/uocr_cpu_ref.c:145-169; the GPU form
+ * uocr_rmsnorm_f16_to_f16, src/backend/metal/kernels/norm.metal:12-40): fp16 rows [n][hidden_size] and fp16 weight in,
+ * f32 arithmetic, d_out = fp16( x * 1/sqrt(mean(x^2) + eps) * weight ).  hidden_size must be a multiple of 8. */
+UOCR_CUDA_API int uocr_cuda_rmsnorm(uocr_cuda_context *ctx, const void *d_x, const void *d_weight_f16, float eps,
+                                    uint32_t n_tokens, uint32_t hidden_size, void *d_out, char *error, size_t error_size);
+/* The MoE layer as the decoder runs it (src/backend/metal/uocr_metal.m:14433-14497): d_stream is the residual stream after
+ * attention, the post-attention norm feeds the layer and the stream is added back:
+ * d_out = MoE( RMSNorm(d_stream) * weight ) + d_stream.  The normalised rows live in the context's scratch. */
+UOCR_CUDA_API int uocr_cuda_moe_layer_forward_normed(uocr_cuda_context *ctx, uint32_t layer, const void *d_stream,
+                                                     const void *d_norm_weight_f16, float eps, uint32_t n_tokens, void *d_out,
+                                                     const uocr_cuda_moe_debug_outputs *dbg, char *error, size_t error_size);
+/* The dense SwiGLU MLP of the first decoder layer (uocr_cpu_ref_dense_swiglu_f32, src/backend/cpu_ref/uocr_cpu_ref.c:305-349;
+ * tensors uocr_tensor_id_layer_dense, src/model/uocr_tensor_registry.h:72-86; intermediate width 6848): the kernels of
+ * the shared experts on other matrices.  gate / up [S][H] and down [H][S] with HOST pointers, S <= 8192, H <= 2048, both
+ * multiples of 64; scratch for up to token_capacity tokens is allocated here and freed by uocr_cuda_context_unmap_model.
+ * d_out = fp16( down . fp16( silu(gate x) * up x ) + residual ); calls of at least the tensor-core threshold (and H a
+ * multiple of 128) round the down product to fp16 before the residual is added, as the MoE layer's shared output is. */
+UOCR_CUDA_API int uocr_cuda_context_map_dense_mlp(uocr_cuda_context *ctx, const uocr_cuda_matrix *gate, const uocr_cuda_matrix *up,
+                                                  const uocr_cuda_matrix *down, uint32_t token_capacity, uint32_t *out_index,
+                                                  char *error, size_t error_size);
+UOCR_CUDA_API int uocr_cuda_dense_mlp_forward(uocr_cuda_context *ctx, uint32_t index, const void *d_hidden, const void *d_residual,
+                                              uint32_t n_tokens, void *d_out, char *error, size_t error_size);
+/* d_out = DenseMLP( RMSNorm(d_stream) * weight ) + d_stream */
+UOCR_CUDA_API int uocr_cuda_dense_mlp_forward_normed(uocr_cuda_context *ctx, uint32_t index, const void *d_stream,
+                                                     const void *d_norm_weight_f16, float eps, uint32_t n_tokens, void *d_out,
+                                                     char *error, size_t error_size);
+
 /* ---- scratch: counterpart of uocr_metal_context_allocate_runtime_arenas / _release_runtime_arenas
  * (src/backend/metal/uocr_metal.h:221-226) restricted to the MoE scratch.  Must be called after the
  * layers are mapped and before any forward call with n_tokens <= token_capacity. */

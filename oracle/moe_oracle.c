@@ -197,6 +197,37 @@ int mo_route_from_logits_f32(const float *logits, uint32_t rows, uint32_t E, uin
     return 1;
 }
 
+/* ------------------------------------------------------------ RMSNorm */
+
+/* uocr_cpu_ref_rmsnorm_f32 (src/backend/cpu_ref/uocr_cpu_ref.c:145-169): per row, sum of squares as one serial fmaf
+ * chain, mean, 1 / sqrtf(mean + eps), out = x * inv_rms * weight (in that order). */
+int mo_rmsnorm_f32(const float *x, const float *weight, uint32_t rows, uint32_t cols, float eps, float *out) {
+    if (!x || !weight || !out || rows == 0u || cols == 0u || eps < 0.0f) return 0;
+    for (uint32_t r = 0; r < rows; ++r) {
+        const float *xr = x + (size_t)r * cols;
+        float ss = 0.0f;
+        for (uint32_t c = 0; c < cols; ++c) ss = fmaf(xr[c], xr[c], ss);
+        const float inv = 1.0f / sqrtf(ss / (float)cols + eps);
+        for (uint32_t c = 0; c < cols; ++c) out[(size_t)r * cols + c] = xr[c] * inv * weight[c];
+    }
+    return 1;
+}
+
+/* The GPU path's form of the same step (src/backend/metal/kernels/norm.metal:12-40): fp16 activations and weight,
+ * f32 arithmetic, the result rounded to fp16 once. */
+int mo_rmsnorm_f16(const uint16_t *x_f16, const uint16_t *weight_f16, uint32_t rows, uint32_t cols, float eps, uint16_t *out_f16) {
+    if (!x_f16 || !weight_f16 || !out_f16 || rows == 0u || cols == 0u || eps < 0.0f) return 0;
+    for (uint32_t r = 0; r < rows; ++r) {
+        const uint16_t *xr = x_f16 + (size_t)r * cols;
+        float ss = 0.0f;
+        for (uint32_t c = 0; c < cols; ++c) { const float v = mo_f16_to_f32(xr[c]); ss = fmaf(v, v, ss); }
+        const float inv = 1.0f / sqrtf(ss / (float)cols + eps);
+        for (uint32_t c = 0; c < cols; ++c)
+            out_f16[(size_t)r * cols + c] = mo_f32_to_f16(mo_f16_to_f32(xr[c]) * inv * mo_f16_to_f32(weight_f16[c]));
+    }
+    return 1;
+}
+
 /* ------------------------------------------------------------ dense MLP */
 
 int mo_dense_swiglu_f32(const float *x, const float *gate, const float *up, const float *down, uint32_t rows,

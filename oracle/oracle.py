@@ -91,6 +91,8 @@ class Port:
         lib.mo_router_f32.argtypes = [C.c_void_p, C.c_void_p] + [C.c_uint32] * 4 + [C.c_float] + [C.c_void_p] * 4
         lib.mo_route_from_logits_f32.argtypes = [_f32p] + [C.c_uint32] * 3 + [C.c_float, _f32p, _u32p, _f32p]
         lib.mo_dense_swiglu_f32.argtypes = [_f32p] * 4 + [C.c_uint32] * 3 + [_f32p] * 2
+        lib.mo_rmsnorm_f32.argtypes = [_f32p, _f32p, C.c_uint32, C.c_uint32, C.c_float, _f32p]
+        lib.mo_rmsnorm_f16.argtypes = [_u16p, _u16p, C.c_uint32, C.c_uint32, C.c_float, _u16p]
         lib.mo_layer_f32.argtypes = [C.c_void_p] * 8 + [C.c_uint32] * 6 + [C.c_float] + [C.c_void_p] * 7
         lib.mo_layer_slab.argtypes = [C.POINTER(_Layer), C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint32, C.c_int] + \
             [C.c_void_p] * 7
@@ -145,6 +147,19 @@ class Port:
         out = np.zeros((rows, H), np.float32)
         st = self.lib.mo_dense_swiglu_f32(x, gate, up, down, rows, H, F, mid, out)
         return st, mid, out
+
+    def rmsnorm_f32(self, x: np.ndarray, weight: np.ndarray, eps: float) -> np.ndarray:
+        x = np.ascontiguousarray(x, np.float32)
+        out = np.zeros_like(x)
+        assert self.lib.mo_rmsnorm_f32(x, np.ascontiguousarray(weight, np.float32), x.shape[0], x.shape[1], eps, out) == 1
+        return out
+
+    def rmsnorm_f16(self, x_bits: np.ndarray, weight_bits: np.ndarray, eps: float) -> np.ndarray:
+        """fp16 bits in, fp16 bits out: the GPU path's form (f32 arithmetic, one rounding)."""
+        x_bits = np.ascontiguousarray(x_bits, np.uint16)
+        out = np.zeros_like(x_bits)
+        assert self.lib.mo_rmsnorm_f16(x_bits, np.ascontiguousarray(weight_bits, np.uint16), x_bits.shape[0], x_bits.shape[1], eps, out) == 1
+        return out
 
     # -- model-format call
     def layer(self, L: quant.LayerWeights, hidden: np.ndarray, residual: np.ndarray | None = None, *,
@@ -215,6 +230,7 @@ class Ref:
             [C.c_void_p] * 4
         lib.uocr_cpu_ref_moe_swiglu_f32.argtypes = [C.c_void_p] * 8 + [C.c_uint32] * 6 + [C.c_float] + [C.c_void_p] * 7
         lib.uocr_cpu_ref_dense_swiglu_f32.argtypes = [_f32p] * 4 + [C.c_uint32] * 3 + [_f32p] * 2
+        lib.uocr_cpu_ref_rmsnorm_f32.argtypes = [_f32p, _f32p, C.c_uint32, C.c_uint32, C.c_float, _f32p]
         self.lib = lib
 
     def f16_to_f32(self, bits):
@@ -267,6 +283,12 @@ class Ref:
         out = np.zeros((rows, H), np.float32)
         st = self.lib.uocr_cpu_ref_dense_swiglu_f32(x, gate, up, down, rows, H, F, mid, out)
         return st, mid, out
+
+    def rmsnorm_f32(self, x: np.ndarray, weight: np.ndarray, eps: float) -> np.ndarray:
+        x = np.ascontiguousarray(x, np.float32)
+        out = np.zeros_like(x)
+        assert self.lib.uocr_cpu_ref_rmsnorm_f32(x, np.ascontiguousarray(weight, np.float32), x.shape[0], x.shape[1], eps, out) == 1
+        return out
 
     def layer(self, L: quant.LayerWeights, hidden: np.ndarray, residual: np.ndarray | None = None, *,
               threads: int = 1, f32_weights=None) -> LayerOut:

@@ -1,0 +1,149 @@
+"""The steps either side of the MoE layer: the post-attention RMSNorm that feeds it and the dense SwiGLU MLP of the first
+decoder layer (intermediate width 6848), against the CPU oracle.  fp16 outputs: RMSNorm within one fp16 step of the
+serial-sum CPU result; MLP outputs max-abs <= 2e-2 and cosine >= 0.9995 against the f32 CPU path."""
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+torch = pytest.importorskip("torch")
+
+from oracle import quant  # noqa: E402
+
+FULL = dict(H=1280, E=64, K=6, F=896, S=1792)
+DENSE_INTER = 6848          # UOCR_DENSE_LAYER0_INTERMEDIATE (src/model/uocr_constants.h:51)
+EPS = 1.0e-6                # UOCR_RMS_NORM_EPS (src/model/uocr_constants.h:27)
+MAX_ABS, MIN_COS = 2e-2, 0.9995
+
+
+@pytest.fixture(scope="module")
+def pkg():
+    import __graft_entry__ as entry
+    if not torch.cuda.is_available():
+        pytest.fail("GPU tests need a CUDA device; the library has no CPU path")
+    torch.cuda.set_device(0)
+    return entry.load_package()
+
+
+def dev(bits):
+    return torch.from_numpy(np.ascontiguousarray(bits)).cuda().view(torch.float16)
+
+
+def closeness(got, want):
+    got, want = got.astype(np.float64).reshape(-1), want.astype(np.float64).reshape(-1)
+    return float(np.max(np.abs(got - want))), float(got @ want / np.sqrt((got @ got) * (want @ want)))
+
+
+def f16_steps(a_bits, b_bits):
+    """distance in representable fp16 values between two arrays of fp16 bits (same sign assumed where it matters)"""
+    def key(b):
+        b = b.astype(np.int32)
+        return np.where(b & 0x8000, -(b & 0x7FFF), b & 0x7FFF)
+    return np.abs(key(a_bits) - key(b_bits))
+
+
+@pytest.mark.parametrize("n,H", [(1, 1280), (7, 1280), (300, 1280), (5, 128), (3, 2048)])
+def test_rmsnorm_matches_the_cpu_function(pkg, port, n, H):
+    rng = np.random.default_rng(100 + n)
+    x = (rng.standard_normal((n, H), dtype=np.float32) * rng.uniform(0.2, 6.0)).astype("<f2").view(np.uint16)
+    w = rng.uniform(0.5, 1.5, H).astype("<f2").view(np.uint16)
+    want = port.rmsnorm_f16(x, w, EPS)
+    with pkg.Context() as ctx:
+        ctx.set_stream(torch.cuda.current_stream().cuda_stream)
+        out = torch.zeros((n, H), dtype=torch.float16, device="cuda")
+        ctx.rmsnorm(dev(x), dev(w), EPS, n, H, out)
+        ctx.synchronize()
+        got = out.cpu().numpy().view(np.uint16)
+        with pytest.raises(pkg.UocrCudaError, match="RMSNorm"):
+            ctx.rmsnorm(dev(x), dev(w), -1.0, n, H, out)
+    steps = f16_steps(got, want)
+    assert steps.max() <= 1                       # the tree sum of squares may move the scale by one f32 step
+    assert (steps == 0).mean() >= 0.98
+
+
+@pytest.mark.parametrize("n", [1, 8, 96])
+def test_normed_layer_call(pkg, port, n):
+    """d_out = MoE(RMSNorm(stream) * w) + stream on a full-size Q4_0 layer through all three regimes."""
+    rng = np.random.default_rng(200 + n)
+    L = quant.synth_layer(rng, expert_qtype=quant.QTYPE_Q4_0, **FULL)
+    stream_rows = (rng.standard_normal((n, FULL["H"]), dtype=np.float32) * 2.5).astype("<f2").view(np.uint16)
+    w = rng.uniform(0.5, 1.5, FULL["H"]).astype("<f2").view(np.uint16)
+    x = port.rmsnorm_f16(stream_rows, w, EPS)
+    want = port.layer(L, x, stream_rows)
+    with pkg.Context() as ctx:
+        ctx.map_layer(L)
+        ctx.allocate_runtime_arenas(n)
+        ctx.set_stream(torch.cuda.current_stream().cuda_stream)
+        out = torch.zeros((n, FULL["H"]), dtype=torch.float16, device="cuda")
+        ids = torch.zeros((n, FULL["K"]), dtype=torch.int32, device="cuda")
+        ctx.layer_forward_normed(0, dev(stream_rows), dev(w), EPS, n, out)
+        # the same through the two separate calls
+        xg = torch.zeros_like(out)
+        ctx.rmsnorm(dev(stream_rows), dev(w), EPS, n, FULL["H"], xg)
+        two = torch.zeros_like(out)
+        ctx.layer_forward(0, xg, n, two, residual=dev(stream_rows), top_ids=ids)
+        ctx.synchronize()
+        assert torch.equal(out, two)
+    got_ids = ids.cpu().numpy().view(np.uint32)
+    same = np.all(got_ids == want.ids, axis=1)        # GPU-computed logits on a (possibly one step different) x: near-ties may flip
+    assert same.mean() >= 0.9
+    err, cos = closeness(out.cpu().numpy().astype(np.float32)[same], want.out[same])
+    assert err <= MAX_ABS * max(1.0, float(np.max(np.abs(want.out)))) and cos >= MIN_COS, (err, cos)
+
+
+@pytest.mark.parametrize("qname,n", [("q8_0", 1), ("q8_0", 3), ("q8_0", 64), ("q8_0", 200), ("f16", 2), ("f16", 77), ("q4_0", 5)])
+def test_dense_mlp_of_the_first_layer(pkg, port, qname, n):
+    rng = np.random.default_rng(300 + n)
+    H, S = FULL["H"], DENSE_INTER
+    qt = quant.QTYPE_BY_NAME[qname]
+    gate = quant.make_matrix(qt, rng.standard_normal((S, H), dtype=np.float32) * 0.02)
+    up = quant.make_matrix(qt, rng.standard_normal((S, H), dtype=np.float32) * 0.02)
+    down = quant.make_matrix(qt, rng.standard_normal((H, S), dtype=np.float32) * 0.02)
+    hidden = quant.synth_activations(rng, n, H)
+    resid = quant.synth_activations(rng, n, H)
+    with pkg.Context() as ctx:
+        idx = ctx.map_dense_mlp(gate, up, down, token_capacity=256)
+        ctx.set_stream(torch.cuda.current_stream().cuda_stream)
+        out = torch.zeros((n, H), dtype=torch.float16, device="cuda")
+        ctx.dense_mlp_forward(idx, dev(hidden), n, out, residual=dev(resid))
+        ctx.synchronize()
+        got = out.cpu().numpy().astype(np.float32)
+        with pytest.raises(pkg.UocrCudaError, match="capacity"):
+            ctx.dense_mlp_forward(idx, dev(hidden), 257, out)
+        assert ctx.moe_scratch_bytes > 0
+    rows = np.unique(np.concatenate([[0, n - 1], rng.integers(0, n, size=6)]))          # the CPU chain is serial: a sample of rows
+    x32 = hidden[rows].view("<f2").astype(np.float32)
+    st, _mid, ref = port.dense_swiglu_f32(x32, gate.to_f32(), up.to_f32(), down.to_f32())
+    assert st == 1
+    want = ref + resid[rows].view("<f2").astype(np.float32)
+    err, cos = closeness(got[rows], want)
+    assert err <= MAX_ABS * max(1.0, float(np.max(np.abs(want)))) and cos >= MIN_COS, (qname, n, err, cos)
+
+
+def test_dense_mlp_normed_and_argument_checks(pkg, port):
+    rng = np.random.default_rng(400)
+    H, S, n = FULL["H"], DENSE_INTER, 6
+    gate = quant.make_matrix(quant.QTYPE_Q8_0, rng.standard_normal((S, H), dtype=np.float32) * 0.02)
+    up = quant.make_matrix(quant.QTYPE_Q8_0, rng.standard_normal((S, H), dtype=np.float32) * 0.02)
+    down = quant.make_matrix(quant.QTYPE_Q8_0, rng.standard_normal((H, S), dtype=np.float32) * 0.02)
+    stream_rows = (rng.standard_normal((n, H), dtype=np.float32) * 3.0).astype("<f2").view(np.uint16)
+    w = rng.uniform(0.5, 1.5, H).astype("<f2").view(np.uint16)
+    x = port.rmsnorm_f16(stream_rows, w, EPS)
+    st, _mid, ref = port.dense_swiglu_f32(x.view("<f2").astype(np.float32), gate.to_f32(), up.to_f32(), down.to_f32())
+    want = ref + stream_rows.view("<f2").astype(np.float32)
+    with pkg.Context() as ctx:
+        idx = ctx.map_dense_mlp(gate, up, down, token_capacity=8)
+        ctx.set_stream(torch.cuda.current_stream().cuda_stream)
+        out = torch.zeros((n, H), dtype=torch.float16, device="cuda")
+        ctx.dense_mlp_forward_normed(idx, dev(stream_rows), dev(w), EPS, n, out)
+        ctx.synchronize()
+        err, cos = closeness(out.cpu().numpy().astype(np.float32), want)
+        assert err <= MAX_ABS * max(1.0, float(np.max(np.abs(want)))) and cos >= MIN_COS, (err, cos)
+        bad = quant.make_matrix(quant.QTYPE_Q8_0, rng.standard_normal((S, H + 64), dtype=np.float32) * 0.02)
+        with pytest.raises(pkg.UocrCudaError, match="shape"):
+            ctx.map_dense_mlp(gate, bad, down, token_capacity=8)
+        with pytest.raises(pkg.UocrCudaError, match="out of range"):
+            ctx.dense_mlp_forward(7, dev(stream_rows), n, out)
+        ctx.unmap_model()
+        with pytest.raises(pkg.UocrCudaError, match="out of range"):
+            ctx.dense_mlp_forward(idx, dev(stream_rows), n, out)

@@ -307,3 +307,18 @@ def test_fp16_contract_mode_matches_the_reference_numpy_layer(port, golden_dir):
     # and the mode matters: without the roundings the bits differ far more often
     plain = port.f32_to_f16(port.layer(L, hidden, resid, threads=6).out)
     assert np.mean(plain == want_bits) < np.mean(got_bits == want_bits)
+
+
+def test_rmsnorm_restatement_equals_the_reference_build(port, ref):
+    """uocr_cpu_ref_rmsnorm_f32 compiled from the reference tree against its restatement, bit for bit, and the fp16
+    form (what the GPU computes) against the f32 form on the same values within one fp16 step."""
+    rng = np.random.default_rng(77)
+    for rows, cols, eps in ((1, 1280, 1e-6), (7, 1280, 1e-6), (5, 128, 0.0), (3, 2048, 1e-5)):
+        x = rng.standard_normal((rows, cols), dtype=np.float32) * rng.uniform(0.1, 8.0)
+        w = rng.uniform(0.5, 1.5, cols).astype(np.float32)
+        a, b = port.rmsnorm_f32(x, w, eps), ref.rmsnorm_f32(x, w, eps)
+        assert np.array_equal(a.view(np.uint32), b.view(np.uint32))
+        xb, wb = x.astype("<f2").view(np.uint16), w.astype("<f2").view(np.uint16)
+        got = port.rmsnorm_f16(xb, wb, eps).view("<f2").astype(np.float32)
+        want = ref.rmsnorm_f32(xb.view("<f2").astype(np.float32), wb.view("<f2").astype(np.float32), eps)
+        assert np.array_equal(got, want.astype("<f2").astype(np.float32))

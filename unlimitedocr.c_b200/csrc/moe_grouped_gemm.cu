@@ -1031,6 +1031,8 @@ cudaError_t launch_router_logits(const DLayer &L, const __half *hidden, uint32_t
     return cudaGetLastError();
 }
 
+bool gemm_tensor_maps_ready() { return g_encode.load() != nullptr; }
+
 bool gemm_path_supported(const DLayer &L) {
     return L.H % 128 == 0 && L.F % 128 == 0 && L.S % 128 == 0 && L.E <= 256 && L.H <= 2048 && L.F <= 2048 &&
            L.S <= 2048 && g_encode.load() != nullptr;

@@ -183,6 +183,8 @@ __global__ void combine_kernel(const float *__restrict__ down_out, const float *
     out[idx] = __float2half_rn(acc);
 }
 
+constexpr int kDenseSmemBytes = 4 * 8192 * (int)sizeof(float);
+
 template <int QT>
 static void launch_gate_up(const GroupSource &src, uint32_t n_groups, const __half *hidden, uint32_t H, uint32_t F,
                            const uint8_t *w, const __half *s, uint64_t stride, uint64_t up_off, uint64_t sstride,
@@ -213,8 +215,36 @@ static uint32_t packed_row_bytes(int qt, uint32_t cols) {
 }
 
 cudaError_t init_small_batch_kernels() {
-    // dynamic shared memory stays below 48 KB for every supported shape (4 rows x 2048 f32 = 32 KB)
-    return cudaSuccess;
+    // MoE layers stay below 48 KB of dynamic shared memory (4 rows x 2048 f32 = 32 KB); the dense MLP of the first
+    // decoder layer stages rows of its intermediate width (6848) for the down product: 4 x 8192 f32 = 128 KB
+    cudaError_t err = cudaFuncSetAttribute(down_kernel<UOCR_QT_Q4>, cudaFuncAttributeMaxDynamicSharedMemorySize, kDenseSmemBytes);
+    if (err == cudaSuccess) err = cudaFuncSetAttribute(down_kernel<UOCR_QT_Q8>, cudaFuncAttributeMaxDynamicSharedMemorySize, kDenseSmemBytes);
+    if (err == cudaSuccess) err = cudaFuncSetAttribute(down_kernel<UOCR_QT_F16>, cudaFuncAttributeMaxDynamicSharedMemorySize, kDenseSmemBytes);
+    return err;
+}
+
+// ---- dense SwiGLU MLP (the first decoder layer's MLP; uocr_cpu_ref_dense_swiglu_f32, src/backend/cpu_ref/uocr_cpu_ref.c:305-349) ----
+// A few tokens through gate/up, down and the residual add with the kernels the shared experts use:
+// out = fp16( down . fp16(silu(gate x) * up x) + residual ), f32 sums, one rounding of the result.
+bool dense_small_supported(uint32_t H, uint32_t S) {
+    return (size_t)kMaxM * H * sizeof(float) <= 48 * 1024 && (size_t)kMaxM * S * sizeof(float) <= (size_t)kDenseSmemBytes;
+}
+
+cudaError_t launch_dense_small(const DMatrix &g, const DMatrix &u, const DMatrix &d, const __half *hidden, const __half *residual,
+                               uint32_t n, __half *mid, float *out_f32, __half *out, cudaStream_t st, uint64_t *launches) {
+    const uint32_t H = g.cols, Sd = g.rows;
+    if (!dense_small_supported(H, Sd)) return cudaErrorInvalidValue;
+    GroupSource all{nullptr, nullptr, nullptr, n, 1};
+    const int64_t up_off = (const uint8_t *)u.w - (const uint8_t *)g.w;
+    const int64_t sup_off = g.s ? (u.s - g.s) : 0;
+    if (up_off <= 0 || (g.s && sup_off <= 0)) return cudaErrorInvalidValue;      // up follows gate in one allocation
+    UOCR_QT_SWITCH(g.qtype, (launch_gate_up<QT>(all, 1, hidden, H, Sd, g.w, g.s, 0, (uint64_t)up_off, 0, (uint64_t)sup_off,
+                                                g.row_bytes, mid, st)));
+    UOCR_QT_SWITCH(d.qtype, (launch_down<QT>(all, 1, mid, H, Sd, d.w, d.s, 0, 0, d.row_bytes, out_f32, st)));
+    const size_t total = (size_t)n * H;
+    combine_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(nullptr, out_f32, residual, nullptr, nullptr, n, H, 0, 0, out);
+    *launches += 3;
+    return cudaGetLastError();
 }
 
 cudaError_t launch_small_batch_layer(const DLayer &L, const Scratch &S, const __half *hidden, const __half *residual,

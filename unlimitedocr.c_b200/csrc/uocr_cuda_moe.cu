@@ -15,6 +15,13 @@
 namespace uocr {
 cudaError_t init_router_kernels();
 cudaError_t init_small_batch_kernels();
+bool dense_small_supported(uint32_t H, uint32_t S);
+bool gemm_tensor_maps_ready();
+cudaError_t launch_dense_small(const DMatrix &g, const DMatrix &u, const DMatrix &d, const __half *hidden, const __half *residual,
+                               uint32_t n, __half *mid, float *out_f32, __half *out, cudaStream_t st, uint64_t *launches);
+cudaError_t launch_rmsnorm(const __half *x, const __half *w, uint32_t rows, uint32_t cols, float eps, __half *out, cudaStream_t st,
+                           uint64_t *launches);
+cudaError_t launch_add_rows(const __half *a, const __half *residual, size_t count, __half *out, cudaStream_t st, uint64_t *launches);
 cudaError_t init_decode_kernels();
 cudaError_t init_decode_sliced_kernels();
 cudaError_t init_gemm_kernels();
@@ -92,6 +99,18 @@ struct uocr_cuda_context {
     cudaStream_t own_stream = nullptr;
     cudaStream_t stream = nullptr;
     std::vector<DLayer> layers;
+    // dense SwiGLU MLPs (the first decoder layer's MLP) with their own scratch, sized when they are mapped
+    struct DenseMlp {
+        DMatrix gate{}, up{}, down{};
+        uint32_t H = 0, S = 0, capacity = 0;
+        __half *x_norm = nullptr, *mid = nullptr;      // [capacity][H], [capacity][S]
+        float *out_f32 = nullptr;                      // [capacity][H] (the tensor-core path keeps fp16 rows in it)
+        uint4 *tiles_gu = nullptr, *tiles_dn = nullptr;
+        uint32_t *counts = nullptr;
+        void *scratch = nullptr;
+        uint64_t scratch_bytes = 0;
+    };
+    std::vector<DenseMlp> dense;
     DLayer *d_layers = nullptr;        // device copy of `layers`
     bool fused_decode = true;          // single-token calls use the persistent decode kernel when it fits
     uint32_t gemm_min_tokens = 5;      // calls with at least this many tokens take the tensor-core path
@@ -108,6 +127,7 @@ struct uocr_cuda_context {
     // arena
     uint8_t *arena = nullptr;
     uint64_t arena_bytes = 0;
+    uint64_t dense_scratch_bytes = 0;     // scratch of the mapped dense MLPs (reported with the arena)
     uint32_t token_capacity = 0;
     uint32_t *status = nullptr;        // device status word
     uint32_t *h_status = nullptr;      // pinned mirror
@@ -212,7 +232,7 @@ static void track_memory(uocr_cuda_context *ctx) {      // brings the engine's t
         told = now;
     };
     sync(UOCR_CUDA_MEMORY_MODEL_VIEWS, ctx->weight_bytes, ctx->tracked_model_bytes);
-    sync(UOCR_CUDA_MEMORY_MOE_SCRATCH, ctx->arena_bytes, ctx->tracked_scratch_bytes);
+    sync(UOCR_CUDA_MEMORY_MOE_SCRATCH, ctx->arena_bytes + ctx->dense_scratch_bytes, ctx->tracked_scratch_bytes);
 }
 
 extern "C" void uocr_cuda_context_set_profile(uocr_cuda_context *ctx, uocr_profile_state *profile,
@@ -227,10 +247,10 @@ extern "C" void uocr_cuda_context_set_memory_tracker(uocr_cuda_context *ctx, uoc
                                                      uocr_cuda_memory_account_fn reserve, uocr_cuda_memory_account_fn release) {
     if (!ctx) return;
     if (ctx->mem_tracker) {      // hand back what the previous tracker was told
-        const uint64_t m = ctx->weight_bytes, a = ctx->arena_bytes;
-        ctx->weight_bytes = 0; ctx->arena_bytes = 0;
+        const uint64_t m = ctx->weight_bytes, a = ctx->arena_bytes, d = ctx->dense_scratch_bytes;
+        ctx->weight_bytes = 0; ctx->arena_bytes = 0; ctx->dense_scratch_bytes = 0;
         track_memory(ctx);
-        ctx->weight_bytes = m; ctx->arena_bytes = a;
+        ctx->weight_bytes = m; ctx->arena_bytes = a; ctx->dense_scratch_bytes = d;
     }
     ctx->mem_tracker = tracker; ctx->mem_reserve = tracker ? reserve : nullptr; ctx->mem_release = tracker ? release : nullptr;
     ctx->tracked_model_bytes = 0; ctx->tracked_scratch_bytes = 0;
@@ -362,6 +382,9 @@ extern "C" void uocr_cuda_context_unmap_model(uocr_cuda_context *ctx) {
     for (void *p : ctx->weight_allocs) cudaFree(p);
     ctx->weight_allocs.clear();
     ctx->layers.clear();
+    for (auto &d : ctx->dense) cudaFree(d.scratch);
+    ctx->dense.clear();
+    ctx->dense_scratch_bytes = 0;
     ctx->weight_bytes = 0;
     track_memory(ctx);
 }
@@ -433,7 +456,7 @@ extern "C" int uocr_cuda_context_synchronize(uocr_cuda_context *ctx, char *error
 
 extern "C" uint64_t uocr_cuda_context_kernel_launches(const uocr_cuda_context *ctx) { return ctx ? ctx->launches : 0; }
 extern "C" uint64_t uocr_cuda_context_model_view_bytes(const uocr_cuda_context *ctx) { return ctx ? ctx->weight_bytes : 0; }
-extern "C" uint64_t uocr_cuda_context_moe_scratch_bytes(const uocr_cuda_context *ctx) { return ctx ? ctx->arena_bytes : 0; }
+extern "C" uint64_t uocr_cuda_context_moe_scratch_bytes(const uocr_cuda_context *ctx) { return ctx ? ctx->arena_bytes + ctx->dense_scratch_bytes : 0; }
 // ---- mapping from an opened .uocr model file -----------------------------------------------------------------------
 // The tensor directory is the file's own packed array of 140-byte entries sorted by id (src/model/uocr_format.h:275-299;
 // the loader checks the order, src/model/uocr_model_file.c:885-895), so a tensor is found by binary search as
@@ -1001,6 +1024,135 @@ static int layer_forward(uocr_cuda_context *ctx, uint32_t layer, const __half *d
     if (dbg && dbg->d_top_weights)
         CU_TRY(ctx, cudaMemcpyAsync(dbg->d_top_weights, s.top_weights, (size_t)n * L.K * 4, cudaMemcpyDeviceToDevice, ctx->stream));
     return 1;
+}
+
+// ---- the steps either side of the MoE layer ------------------------------------------------------------------------
+extern "C" int uocr_cuda_rmsnorm(uocr_cuda_context *ctx, const void *d_x, const void *d_weight_f16, float eps, uint32_t n,
+                                 uint32_t hidden_size, void *d_out, char *error, size_t error_size) {
+    if (!ctx) return fail(nullptr, error, error_size, "null context");
+    if (!d_x || !d_weight_f16 || !d_out || n == 0 || hidden_size == 0 || hidden_size % 8 || !(eps >= 0.0f))
+        return fail(ctx, error, error_size, "invalid RMSNorm argument (null pointer, zero size, width not a multiple of 8 or negative eps)");
+    CU_TRY(ctx, cudaSetDevice(ctx->device));
+    CU_TRY(ctx, uocr::launch_rmsnorm((const __half *)d_x, (const __half *)d_weight_f16, n, hidden_size, eps, (__half *)d_out, ctx->stream,
+                                     &ctx->launches));
+    return 1;
+}
+
+extern "C" int uocr_cuda_moe_layer_forward_normed(uocr_cuda_context *ctx, uint32_t layer, const void *d_stream,
+                                                  const void *d_norm_weight_f16, float eps, uint32_t n, void *d_out,
+                                                  const uocr_cuda_moe_debug_outputs *dbg, char *error, size_t error_size) {
+    if (!check_call(ctx, layer, n, error, error_size)) return 0;
+    if (!d_stream || !d_norm_weight_f16 || !d_out) return fail(ctx, error, error_size, "null argument");
+    const DLayer &L = ctx->layers[layer];
+    ArenaLayout a;
+    carve(ctx, L, ctx->token_capacity, &a);
+    __half *x = (__half *)(ctx->arena + a.d_in);          // the staging rows of the host-buffer calls: free during a device call
+    if (!uocr_cuda_rmsnorm(ctx, d_stream, d_norm_weight_f16, eps, n, L.H, x, error, error_size)) return 0;
+    return uocr_cuda_moe_layer_forward(ctx, layer, x, d_stream, nullptr, n, d_out, dbg, error, error_size);
+}
+
+extern "C" int uocr_cuda_context_map_dense_mlp(uocr_cuda_context *ctx, const uocr_cuda_matrix *gate, const uocr_cuda_matrix *up,
+                                               const uocr_cuda_matrix *down, uint32_t token_capacity, uint32_t *out_index,
+                                               char *error, size_t error_size) {
+    if (!ctx || !gate || !up || !down) return fail(ctx, error, error_size, "null context or matrix");
+    const uint32_t S = gate->rows, H = gate->cols;
+    if (H == 0 || S == 0 || H % UOCR_GROUP || S % UOCR_GROUP) return fail(ctx, error, error_size, "dense MLP widths must be positive multiples of 64 (hidden %u, intermediate %u)", H, S);
+    if (H > 2048 || S > 8192) return fail(ctx, error, error_size, "dense MLP widths above 2048 (hidden) / 8192 (intermediate) are not supported");
+    if (token_capacity == 0) return fail(ctx, error, error_size, "token capacity must be positive");
+    if (!check_matrix(ctx, *gate, S, H, "dense gate", error, error_size) || !check_matrix(ctx, *up, S, H, "dense up", error, error_size) ||
+        !check_matrix(ctx, *down, H, S, "dense down", error, error_size))
+        return 0;
+    if (gate->qtype != up->qtype) return fail(ctx, error, error_size, "dense gate and up projections must share one qtype");
+    CU_TRY(ctx, cudaSetDevice(ctx->device));
+    uocr_cuda_context::DenseMlp D;
+    D.H = H; D.S = S; D.capacity = token_capacity;
+    {   // gate and up in one allocation (gate first), as the kernels address "up" as a positive offset from "gate"
+        const int q = gate->qtype;
+        const uint64_t wb = packed_bytes(q, S, H), sb = q == UOCR_QT_F16 ? 0 : (uint64_t)S * (H / UOCR_GROUP) * 2;
+        uint8_t *dw = nullptr, *ds = nullptr;
+        CU_TRY(ctx, cudaMalloc(&dw, 2 * wb + kUploadPad));
+        ctx->weight_allocs.push_back(dw);
+        CU_TRY(ctx, cudaMemcpy(dw, gate->qweight, wb, cudaMemcpyHostToDevice));
+        CU_TRY(ctx, cudaMemcpy(dw + wb, up->qweight, wb, cudaMemcpyHostToDevice));
+        if (sb) {
+            CU_TRY(ctx, cudaMalloc(&ds, 2 * sb + kUploadPad));
+            ctx->weight_allocs.push_back(ds);
+            CU_TRY(ctx, cudaMemcpy(ds, gate->qscale, sb, cudaMemcpyHostToDevice));
+            CU_TRY(ctx, cudaMemcpy(ds + sb, up->qscale, sb, cudaMemcpyHostToDevice));
+        }
+        ctx->weight_bytes += 2 * (wb + sb);
+        const uint32_t rb = (uint32_t)(wb / S);
+        D.gate = DMatrix{dw, (const __half *)ds, S, H, rb, q};
+        D.up = DMatrix{dw + wb, ds ? (const __half *)(ds + sb) : nullptr, S, H, rb, q};
+    }
+    {
+        const int q = down->qtype;
+        const uint64_t wb = packed_bytes(q, H, S), sb = q == UOCR_QT_F16 ? 0 : (uint64_t)H * (S / UOCR_GROUP) * 2;
+        void *pw = nullptr, *ps = nullptr;
+        if (!upload(ctx, down->qweight, wb, &pw, error, error_size)) return 0;
+        if (sb && !upload(ctx, down->qscale, sb, &ps, error, error_size)) return 0;
+        D.down = DMatrix{(const uint8_t *)pw, (const __half *)ps, H, S, (uint32_t)(wb / H), q};
+    }
+    // scratch: normalised input, SwiGLU products, output rows, the two tile lists of the tensor-core path and their counts
+    auto up256 = [](uint64_t v) { return (v + 255) & ~(uint64_t)255; };
+    const uint64_t token_tiles = (token_capacity + 127) / 128 + 1;
+    const uint64_t o_x = 0, o_mid = o_x + up256((uint64_t)token_capacity * H * 2), o_out = o_mid + up256((uint64_t)token_capacity * S * 2),
+                   o_tg = o_out + up256((uint64_t)token_capacity * H * 4), o_td = o_tg + up256(token_tiles * (S / 64 + 1) * 16),
+                   o_cnt = o_td + up256(token_tiles * (H / 128 + 1) * 16), total = o_cnt + 256;
+    uint8_t *base = nullptr;
+    CU_TRY(ctx, cudaMalloc(&base, total));
+    D.scratch = base; D.scratch_bytes = total;
+    D.x_norm = (__half *)(base + o_x); D.mid = (__half *)(base + o_mid); D.out_f32 = (float *)(base + o_out);
+    D.tiles_gu = (uint4 *)(base + o_tg); D.tiles_dn = (uint4 *)(base + o_td); D.counts = (uint32_t *)(base + o_cnt);
+    ctx->dense.push_back(D);
+    ctx->dense_scratch_bytes += total;
+    if (out_index) *out_index = (uint32_t)ctx->dense.size() - 1;
+    track_memory(ctx);
+    return 1;
+}
+
+static int dense_forward(uocr_cuda_context *ctx, uint32_t index, const __half *d_hidden, const __half *d_residual, uint32_t n,
+                         __half *d_out, char *error, size_t error_size) {
+    auto &D = ctx->dense[index];
+    if (n >= ctx->gemm_min_tokens && D.H % 128 == 0 && uocr::gemm_tensor_maps_ready()) {
+        // tensor-core path: the two grouped GEMMs of a shared MLP on all n tokens (one "expert"), fp16 output rows, then
+        // the residual add (two roundings, like the shared output of the MoE layer in this regime)
+        DLayer L{};
+        L.H = D.H; L.S = D.S; L.shared_gate = D.gate; L.shared_up = D.up; L.shared_down = D.down;
+        Scratch s{};
+        s.status = ctx->status;
+        uocr::GemmScratch g{};
+        g.shared_mid = D.mid; g.shared_out = (__half *)D.out_f32; g.stiles_gu = D.tiles_gu; g.stiles_dn = D.tiles_dn;
+        g.counts = D.counts - 2;                          // the shared MLP's two counters are entries 2 and 3
+        CU_TRY(ctx, uocr::launch_gemm_shared(L, s, g, d_hidden, n, ctx->stream, &ctx->launches));
+        CU_TRY(ctx, uocr::launch_add_rows((const __half *)D.out_f32, d_residual, (size_t)n * D.H, d_out, ctx->stream, &ctx->launches));
+        return 1;
+    }
+    if (!uocr::dense_small_supported(D.H, D.S)) return fail(ctx, error, error_size, "dense MLP shape not supported by the matrix-vector path");
+    CU_TRY(ctx, uocr::launch_dense_small(D.gate, D.up, D.down, d_hidden, d_residual, n, D.mid, D.out_f32, d_out, ctx->stream, &ctx->launches));
+    return 1;
+}
+
+extern "C" int uocr_cuda_dense_mlp_forward(uocr_cuda_context *ctx, uint32_t index, const void *d_hidden, const void *d_residual,
+                                           uint32_t n, void *d_out, char *error, size_t error_size) {
+    if (!ctx) return fail(nullptr, error, error_size, "null context");
+    if (index >= ctx->dense.size()) return fail(ctx, error, error_size, "dense MLP index %u out of range (%zu mapped)", index, ctx->dense.size());
+    if (!d_hidden || !d_out || n == 0) return fail(ctx, error, error_size, "null or empty dense MLP argument");
+    if (n > ctx->dense[index].capacity) return fail(ctx, error, error_size, "n_tokens %u exceeds the dense MLP's capacity %u", n, ctx->dense[index].capacity);
+    CU_TRY(ctx, cudaSetDevice(ctx->device));
+    return dense_forward(ctx, index, (const __half *)d_hidden, (const __half *)d_residual, n, (__half *)d_out, error, error_size);
+}
+
+extern "C" int uocr_cuda_dense_mlp_forward_normed(uocr_cuda_context *ctx, uint32_t index, const void *d_stream,
+                                                  const void *d_norm_weight_f16, float eps, uint32_t n, void *d_out, char *error,
+                                                  size_t error_size) {
+    if (!ctx) return fail(nullptr, error, error_size, "null context");
+    if (index >= ctx->dense.size()) return fail(ctx, error, error_size, "dense MLP index %u out of range (%zu mapped)", index, ctx->dense.size());
+    if (!d_stream || !d_norm_weight_f16 || !d_out || n == 0) return fail(ctx, error, error_size, "null or empty dense MLP argument");
+    auto &D = ctx->dense[index];
+    if (n > D.capacity) return fail(ctx, error, error_size, "n_tokens %u exceeds the dense MLP's capacity %u", n, D.capacity);
+    if (!uocr_cuda_rmsnorm(ctx, d_stream, d_norm_weight_f16, eps, n, D.H, D.x_norm, error, error_size)) return 0;
+    return dense_forward(ctx, index, D.x_norm, (const __half *)d_stream, n, (__half *)d_out, error, error_size);
 }
 
 extern "C" const char *uocr_cuda_moe_regime_name(const uocr_cuda_context *ctx, uint32_t layer, uint32_t n) {

@@ -61,7 +61,8 @@ EXPORTS = (
     "uocr_cuda_context_moe_scratch_bytes", "uocr_cuda_context_map_moe_layer", "uocr_cuda_context_map_model", "uocr_cuda_context_unmap_model",
     "uocr_cuda_context_moe_layer_count", "uocr_cuda_context_allocate_runtime_arenas",
     "uocr_cuda_context_release_runtime_arenas", "uocr_cuda_moe_scratch_size", "uocr_cuda_moe_router",
-    "uocr_cuda_moe_dispatch_plan", "uocr_cuda_moe_dispatch_plan_noalloc", "uocr_cuda_moe_debug_dequantize", "uocr_cuda_moe_regime_name", "uocr_cuda_moe_layer_forward", "uocr_cuda_moe_stack_forward",
+    "uocr_cuda_moe_dispatch_plan", "uocr_cuda_moe_dispatch_plan_noalloc", "uocr_cuda_moe_debug_dequantize", "uocr_cuda_moe_regime_name", "uocr_cuda_rmsnorm", "uocr_cuda_moe_layer_forward_normed", "uocr_cuda_context_map_dense_mlp",
+    "uocr_cuda_dense_mlp_forward", "uocr_cuda_dense_mlp_forward_normed", "uocr_cuda_moe_layer_forward", "uocr_cuda_moe_stack_forward",
     "uocr_cuda_moe_layer_forward_host", "uocr_cuda_moe_stack_forward_host",
     "uocr_cuda_moe_ep_dispatch", "uocr_cuda_moe_ep_experts", "uocr_cuda_moe_ep_shared", "uocr_cuda_moe_ep_combine",
     "uocr_cuda_moe_ep_peer_forward", "uocr_cuda_moe_ep_peer_last_offsets", "uocr_cuda_moe_ep_peer_create", "uocr_cuda_moe_ep_peer_open", "uocr_cuda_moe_ep_peer_destroy",
@@ -118,6 +119,11 @@ def load_library() -> C.CDLL:
         "uocr_cuda_context_map_moe_layer": (C.c_int, [vp, C.POINTER(CLayerDesc), C.POINTER(u32)] + err),
         "uocr_cuda_context_map_model": (C.c_int, [vp, C.POINTER(CModelFileView)] + err),
         "uocr_cuda_context_unmap_model": (None, [vp]),
+        "uocr_cuda_rmsnorm": (C.c_int, [vp, vp, vp, C.c_float, u32, u32, vp] + err),
+        "uocr_cuda_moe_layer_forward_normed": (C.c_int, [vp, u32, vp, vp, C.c_float, u32, vp, C.POINTER(CDebugOutputs)] + err),
+        "uocr_cuda_context_map_dense_mlp": (C.c_int, [vp, C.POINTER(CMatrix), C.POINTER(CMatrix), C.POINTER(CMatrix), u32, C.POINTER(u32)] + err),
+        "uocr_cuda_dense_mlp_forward": (C.c_int, [vp, u32, vp, vp, u32, vp] + err),
+        "uocr_cuda_dense_mlp_forward_normed": (C.c_int, [vp, u32, vp, vp, C.c_float, u32, vp] + err),
         "uocr_cuda_context_moe_layer_count": (u32, [vp]),
         "uocr_cuda_context_allocate_runtime_arenas": (C.c_int, [vp, u32, u32] + err),
         "uocr_cuda_context_release_runtime_arenas": (None, [vp]),
@@ -269,6 +275,38 @@ class Context:
             self._layer_k[i] = top_k
             self._layer_e[i] = routed_experts
         return int(self._lib.uocr_cuda_context_moe_layer_count(self._h))
+
+    # -- the steps either side of the MoE layer
+    def rmsnorm(self, x, weight, eps: float, n_tokens: int, hidden_size: int, out) -> None:
+        self._check(self._lib.uocr_cuda_rmsnorm(self._h, _dev_ptr(x), _dev_ptr(weight), eps, n_tokens, hidden_size, _dev_ptr(out),
+                                                self._err, _ERR))
+
+    def layer_forward_normed(self, layer: int, stream_rows, norm_weight, eps: float, n_tokens: int, out) -> None:
+        """out = MoE(RMSNorm(stream_rows) * norm_weight) + stream_rows (uocr_cuda_moe_layer_forward_normed)."""
+        self._check(self._lib.uocr_cuda_moe_layer_forward_normed(self._h, layer, _dev_ptr(stream_rows), _dev_ptr(norm_weight), eps,
+                                                                 n_tokens, _dev_ptr(out), None, self._err, _ERR))
+
+    def map_dense_mlp(self, gate: Any, up: Any, down: Any, token_capacity: int) -> int:
+        """gate / up / down: objects with qtype, rows, cols, qweight, qscale (host arrays), e.g. oracle.quant.Matrix."""
+        keep, cm = [], []
+        for m in (gate, up, down):
+            w = np.ascontiguousarray(m.qweight)
+            sc = None if m.qscale is None else np.ascontiguousarray(m.qscale)
+            keep += [w, sc]
+            cm.append(CMatrix(m.qtype, m.rows, m.cols, w.ctypes.data, None if sc is None else sc.ctypes.data))
+        idx = C.c_uint32(0xFFFFFFFF)
+        self._check(self._lib.uocr_cuda_context_map_dense_mlp(self._h, C.byref(cm[0]), C.byref(cm[1]), C.byref(cm[2]), token_capacity,
+                                                              C.byref(idx), self._err, _ERR))
+        del keep
+        return idx.value
+
+    def dense_mlp_forward(self, index: int, hidden, n_tokens: int, out, *, residual=None) -> None:
+        self._check(self._lib.uocr_cuda_dense_mlp_forward(self._h, index, _dev_ptr(hidden), _dev_ptr(residual), n_tokens,
+                                                          _dev_ptr(out), self._err, _ERR))
+
+    def dense_mlp_forward_normed(self, index: int, stream_rows, norm_weight, eps: float, n_tokens: int, out) -> None:
+        self._check(self._lib.uocr_cuda_dense_mlp_forward_normed(self._h, index, _dev_ptr(stream_rows), _dev_ptr(norm_weight), eps,
+                                                                 n_tokens, _dev_ptr(out), self._err, _ERR))
 
     def release_runtime_arenas(self) -> None:
         self._lib.uocr_cuda_context_release_runtime_arenas(self._h)
