@@ -396,6 +396,47 @@ def measure_prefill(pkg, torch, flush_l2, qtype_name: str, steps: int, warmup: i
     return out
 
 
+# ------------------------------------------------------------------------------------------ dense MLP of layer 0 (one GPU)
+
+def measure_dense_mlp(pkg, torch, flush_l2, steps: int, warmup: int) -> dict:
+    """The first decoder layer's dense SwiGLU MLP (hidden 1280, intermediate 6848, Q8_0 as the mixed profiles store it),
+    with its RMSNorm prologue: one token (weight bytes against the HBM roofline) and 4096 tokens (tensor roofline)."""
+    from oracle import quant
+    H, S = FULL["H"], 6848
+    rng = np.random.default_rng(5)
+    mats = [quant.make_matrix(quant.QTYPE_Q8_0, rng.standard_normal(shape, dtype=np.float32) * 0.02) for shape in ((S, H), (S, H), (H, S))]
+    weight_bytes = 3 * (S * H + S * H // 64 * 2)
+    peak_hbm, kind_hbm = measured_peaks()
+    peak_tc, kind_tc = measured_tensor_peak()
+    stream = torch.cuda.current_stream()
+    out = {"workload": "dense SwiGLU MLP of decoder layer 0: hidden 1280, intermediate 6848, Q8_0, RMSNorm prologue, seed 5", "l2": L2_NOTE,
+           "tokens": {}}
+    with pkg.Context() as ctx:
+        idx = ctx.map_dense_mlp(*mats, token_capacity=4096)
+        ctx.set_stream(stream.cuda_stream)
+        w = torch.from_numpy(rng.uniform(0.5, 1.5, H).astype("<f2").view(np.uint16)).cuda().view(torch.float16)
+        for n in (1, 4096):
+            x = torch.from_numpy(quant.synth_activations(rng, n, H)).cuda().view(torch.float16)
+            y = torch.zeros_like(x)
+            launches0 = ctx.kernel_launches
+            times = timed_steps(torch, None, 1, stream, flush_l2, lambda: ctx.dense_mlp_forward_normed(idx, x, w, 1e-6, n, y), steps, warmup)
+            launches = (ctx.kernel_launches - launches0) // (steps + warmup)
+            ms = sum(times) / len(times)
+            r = {"us_per_step": ms * 1e3, "gpu_launches_per_step": int(launches)}
+            if n == 1:
+                gbs = weight_bytes / (ms * 1e-3) / 1e9
+                r["roofline"] = {"bound": "hbm", "achieved": gbs, "peak": peak_hbm, "peak_kind": f"of {kind_hbm}", "unit": "GB/s",
+                                 "frac": gbs / peak_hbm, "algorithmic_bytes_per_step": weight_bytes}
+            else:
+                tf = 2.0 * 3 * S * H * n / (ms * 1e-3) / 1e12
+                r["tokens_per_s"] = n / (ms * 1e-3)
+                r["roofline"] = {"bound": "tensor", "achieved": tf, "peak": peak_tc, "peak_kind": f"of {kind_tc}", "unit": "TFLOP/s",
+                                 "frac": tf / peak_tc, "algorithmic_flops_per_step": 2.0 * 3 * S * H * n}
+            out["tokens"][str(n)] = r
+        ctx.synchronize()
+    return out
+
+
 # ------------------------------------------------------------------------------------------ batched decode (one GPU)
 
 def measure_batched_decode(pkg, torch, flush_l2, steps: int, warmup: int) -> dict:
@@ -755,6 +796,7 @@ def main() -> None:
             if world == 1:
                 extras["prefill"] = {q: measure_prefill(pkg, torch, flush_l2, q, short, 3) for q in ("q4_0", "f16")}
                 extras["batched_decode"] = measure_batched_decode(pkg, torch, flush_l2, short, 3)
+                extras["dense_mlp"] = measure_dense_mlp(pkg, torch, flush_l2, short, 3)
             extras["ep"] = measure_ep(pkg, torch, dist, rank, world, flush_l2, short, 3, args.exchange, routings)
             if rank == 0:
                 line.update(extras)
