@@ -193,6 +193,16 @@ struct BatchedParams {
     uint32_t *status;
 };
 
+#ifdef UOCR_BT_TRACE
+// Development build only: cycles warp 0 of every CTA spends in each phase of an item, summed over CTAs.
+__device__ unsigned long long g_bt_trace[16];
+#define BT_T0(var) const long long var = clock64()
+#define BT_ADD(slot, var) bt_local[slot] += (unsigned long long)(clock64() - var)
+#else
+#define BT_T0(var)
+#define BT_ADD(slot, var)
+#endif
+
 template <int QT> struct BtSmem {
     static constexpr int kChunkBytes = SlBlob<QT>::kGuBytes / kBtChunks;
     static constexpr int kRing = 0;
@@ -316,7 +326,12 @@ __global__ void __launch_bounds__(kBtThreads, 1) decode_batched_kernel(const __g
     // ---- consumers
     const int rb = warp & 7, nh = warp >> 3;       // gate / up: row block, and which n-blocks (nh, nh + 2) of the pass
     uint32_t seq = 0, slices_done = 0;
+#ifdef UOCR_BT_TRACE
+    unsigned long long bt_local[10] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
+    BT_T0(bt_all);
+#endif
     for (uint32_t item = blockIdx.x; item < n_items; item += gridDim.x) {
+        BT_T0(bt_p1);
         const BtItem it = resolve(item);
         const bool shared = it.expert >= (uint32_t)kSlE;
         const uint32_t T = it.T, NB = (T + 3u) / 4u;
@@ -347,38 +362,49 @@ __global__ void __launch_bounds__(kBtThreads, 1) decode_batched_kernel(const __g
             }
         }
         bt_sync();
+        BT_ADD(0, bt_p1);
+#ifdef UOCR_BT_TRACE
+        bt_local[8] += 1; bt_local[9] += T;
+#endif
 
         for (int sl = 0; sl < kBtSlices; ++sl, ++slices_done) {
+            BT_T0(bt_dw);
             const uint8_t *blob = prm.units + (size_t)(first_unit + sl) * Bl::kBytes;
             const uint32_t sb = slices_done & 1u;
             // the slice's 64 columns of `down` for this warp's five 16-row blocks, and the rows' scales, into registers
             uint4 dwn[kBtBlocksPerWarp][2];
             __half dslo[kBtBlocksPerWarp], dshi[kBtBlocksPerWarp];
-            {
-                const uint4 *dn = reinterpret_cast<const uint4 *>(blob + Bl::kDn);
-                const __half *dsc = reinterpret_cast<const __half *>(blob + Bl::kDnSc);
-#pragma unroll
-                for (int bi = 0; bi < kBtBlocksPerWarp; ++bi) {
-                    const int blk = warp + 16 * bi;
-                    if (QT == UOCR_QT_Q8) {
-                        dwn[bi][0] = __ldg(dn + (blk * 2) * 32 + lane);
-                        dwn[bi][1] = __ldg(dn + (blk * 2 + 1) * 32 + lane);
-                    } else {
-                        dwn[bi][0] = __ldg(dn + blk * 32 + lane);
-                    }
-                    dslo[bi] = dsc[16 * blk + g];
-                    dshi[bi] = dsc[16 * blk + 8 + g];
+            // (requested one 16-row block per chunk of the gate / up loop below: twenty 512-byte loads per warp at once
+            // only queue up in front of the load unit, while spread over the loop they travel beside its arithmetic)
+            const uint4 *dn = reinterpret_cast<const uint4 *>(blob + Bl::kDn);
+            const __half *dsc = reinterpret_cast<const __half *>(blob + Bl::kDnSc);
+            auto fetch_down_block = [&](int bi) {
+                const int blk = warp + 16 * bi;
+                if (QT == UOCR_QT_Q8) {
+                    dwn[bi][0] = __ldg(dn + (blk * 2) * 32 + lane);
+                    dwn[bi][1] = __ldg(dn + (blk * 2 + 1) * 32 + lane);
+                } else {
+                    dwn[bi][0] = __ldg(dn + blk * 32 + lane);
                 }
-            }
+                dslo[bi] = dsc[16 * blk + g];
+                dshi[bi] = dsc[16 * blk + 8 + g];
+            };
+            static_assert(kBtBlocksPerWarp == kBtChunks, "one down block is requested per gate / up chunk");
+            BT_ADD(1, bt_dw);
+            BT_T0(bt_gu);
             // 2. gate / up: rows 8 rb .. + 7 of both matrices x the tokens of n-blocks nh and nh + 2
             float ag[2] = {0.f, 0.f}, au[2] = {0.f, 0.f};
             const __half *scg = s_sc + sb * (Bl::kGuScBytes / 2) + (8 * rb + g) * kSlGroups;
             const __half *scu = scg + 64 * kSlGroups;
             bool got = true;
+#pragma unroll
             for (int c = 0; c < kBtChunks; ++c, ++seq) {
                 const uint32_t s = seq % kBtStages;
+                BT_T0(bt_w);
                 got = mbar_wait(&full[s], (seq / kBtStages) & 1u, prm.status, s_flag) && got;
                 if (c == 0) got = mbar_wait(&sc_full[sb], (slices_done >> 1) & 1u, prm.status, s_flag) && got;
+                BT_ADD(2, bt_w);
+                fetch_down_block(c);
                 const uint4 *w4 = s_ring4 + (size_t)s * (Sm::kChunkBytes / 16);
                 if ((uint32_t)nh < NB) {
 #pragma unroll
@@ -409,6 +435,8 @@ __global__ void __launch_bounds__(kBtThreads, 1) decode_batched_kernel(const __g
             }
             __syncwarp();
             if (lane == 0) bt_arrive(&sc_empty[sb]);
+            BT_ADD(3, bt_gu);
+            BT_T0(bt_sw);
             // 3. SwiGLU in registers: lane (g, t) holds gate and up of column 8 rb + g for token 4 nb + t
 #pragma unroll
             for (int i = 0; i < 2; ++i) {
@@ -427,6 +455,8 @@ __global__ void __launch_bounds__(kBtThreads, 1) decode_batched_kernel(const __g
                 if (p == 0) s_ms[tok] = QT == UOCR_QT_Q4 ? M.scale * kQ4LevelScale : M.scale;
             }
             bt_sync();
+            BT_ADD(4, bt_sw);
+            BT_T0(bt_dn);
             // 4. down: this warp's 80 rows x the slice's 64 columns x every token of the pass
             for (uint32_t nb = 0; nb < NB; ++nb) {
                 const uint4 mbf = *reinterpret_cast<const uint4 *>(s_midf + (((4 * nb + (g >> 1)) * 2 + (g & 1)) * 4 + t) * 4);
@@ -457,9 +487,18 @@ __global__ void __launch_bounds__(kBtThreads, 1) decode_batched_kernel(const __g
                     }
                 }
             }
+            BT_ADD(5, bt_dn);
+            BT_T0(bt_fs);
             bt_sync();
+            BT_ADD(6, bt_fs);
         }
     }
+#ifdef UOCR_BT_TRACE
+    BT_ADD(7, bt_all);
+    if (tid == 0)
+        for (int i = 0; i < 10; ++i) atomicAdd(&g_bt_trace[i], bt_local[i]);
+    if (tid == 0) atomicAdd(&g_bt_trace[10], 1ull);
+#endif
 }
 
 // ---------------------------------------------------------------- 3. combine
@@ -614,3 +653,11 @@ cudaError_t launch_batched_combine(const DLayer &L, const Scratch &S, const __ha
 }
 
 }  // namespace uocr
+
+#ifdef UOCR_BT_TRACE
+extern "C" __attribute__((visibility("default"))) int uocr_cuda_debug_bt_trace(unsigned long long *out16, int reset) {
+    if (cudaMemcpyFromSymbol(out16, uocr::g_bt_trace, sizeof(unsigned long long) * 16) != cudaSuccess) return 0;
+    if (reset) { static const unsigned long long zero[16] = {0}; if (cudaMemcpyToSymbol(uocr::g_bt_trace, zero, sizeof zero) != cudaSuccess) return 0; }
+    return 1;
+}
+#endif
