@@ -437,6 +437,36 @@ def measure_dense_mlp(pkg, torch, flush_l2, steps: int, warmup: int) -> dict:
     return out
 
 
+# ------------------------------------------------------------------------------------------ LM head (one GPU)
+
+def measure_lm_head(pkg, torch, flush_l2, steps: int, warmup: int) -> dict:
+    """The vocabulary projection fused with the argmax, one token: [129280, 1280] in Q4_0 and Q8_0 (83 / 165 MB per
+    decoded token), weight bytes against the HBM roofline."""
+    from oracle import quant
+    V, H = 129280, FULL["H"]
+    rng = np.random.default_rng(6)
+    w = rng.standard_normal((V, H), dtype=np.float32) * 0.02
+    peak, kind = measured_peaks()
+    stream = torch.cuda.current_stream()
+    out = {"workload": "LM head fused with argmax: vocabulary 129280, hidden 1280, one token, seed 6", "l2": L2_NOTE, "qtype": {}}
+    x = torch.from_numpy(quant.synth_activations(rng, 1, H)).cuda().view(torch.float16)
+    ids = torch.zeros(1, dtype=torch.int32, device="cuda")
+    for qname in ("q4_0", "q8_0"):
+        m = quant.make_matrix(quant.QTYPE_BY_NAME[qname], w)
+        nbytes = int(m.qweight.size + (0 if m.qscale is None else m.qscale.size * 2))
+        with pkg.Context() as ctx:
+            ctx.map_lm_head(m)
+            ctx.set_stream(stream.cuda_stream)
+            times = timed_steps(torch, None, 1, stream, flush_l2, lambda: ctx.lm_head_argmax(x, 1, ids), steps, warmup)
+            ctx.synchronize()
+        ms = sum(times) / len(times)
+        gbs = nbytes / (ms * 1e-3) / 1e9
+        out["qtype"][qname] = {"us_per_token": ms * 1e3, "gpu_launches_per_step": 1,
+                               "roofline": {"bound": "hbm", "achieved": gbs, "peak": peak, "peak_kind": f"of {kind}", "unit": "GB/s",
+                                            "frac": gbs / peak, "algorithmic_bytes_per_step": nbytes}}
+    return out
+
+
 # ------------------------------------------------------------------------------------------ batched decode (one GPU)
 
 def measure_batched_decode(pkg, torch, flush_l2, steps: int, warmup: int) -> dict:
@@ -797,6 +827,7 @@ def main() -> None:
                 extras["prefill"] = {q: measure_prefill(pkg, torch, flush_l2, q, short, 3) for q in ("q4_0", "f16")}
                 extras["batched_decode"] = measure_batched_decode(pkg, torch, flush_l2, short, 3)
                 extras["dense_mlp"] = measure_dense_mlp(pkg, torch, flush_l2, short, 3)
+                extras["lm_head"] = measure_lm_head(pkg, torch, flush_l2, short, 3)
             extras["ep"] = measure_ep(pkg, torch, dist, rank, world, flush_l2, short, 3, args.exchange, routings)
             if rank == 0:
                 line.update(extras)

@@ -248,6 +248,17 @@ UOCR_CUDA_API int uocr_cuda_dense_mlp_forward_normed(uocr_cuda_context *ctx, uin
                                                      const void *d_norm_weight_f16, float eps, uint32_t n_tokens, void *d_out,
                                                      char *error, size_t error_size);
 
+/* ---- LM head: the vocabulary projection fused with the argmax (uocr_lm_head_argmax_q4_0_to_f16 / _q8_0,
+ * src/backend/metal/kernels/lm_head_q4.metal:25-100; host metal_run_lm_head_argmax_*; docs/plan_q4.md:493-517), the
+ * largest single weight reader of a decode step after the MoE layers.  weight [vocab][hidden] with HOST pointers in
+ * any of the three formats.  d_token_ids[t] = the row with the largest dot product with d_hidden[t] (fp16 rows after the
+ * final norm), ties to the lowest id, NaN rows skipped (0xffffffff if every row is NaN); d_scores (optional) the winning
+ * logits.  At most four tokens per call share one pass over the weights. */
+UOCR_CUDA_API int uocr_cuda_context_map_lm_head(uocr_cuda_context *ctx, const uocr_cuda_matrix *weight, char *error,
+                                                size_t error_size);
+UOCR_CUDA_API int uocr_cuda_lm_head_argmax(uocr_cuda_context *ctx, const void *d_hidden, uint32_t n_tokens,
+                                           uint32_t *d_token_ids, float *d_scores, char *error, size_t error_size);
+
 /* ---- scratch: counterpart of uocr_metal_context_allocate_runtime_arenas / _release_runtime_arenas
  * (src/backend/metal/uocr_metal.h:221-226) restricted to the MoE scratch.  Must be called after the
  * layers are mapped and before any forward call with n_tokens <= token_capacity. */

@@ -345,6 +345,35 @@ int mo_dequant_matrix(const mo_matrix *m, float *dst) {
     return 1;
 }
 
+/* LM head: logits[t][v] = row v of the matrix . x[t] (fp16 activations, f32 fmaf chain over the dequantised row), and
+ * per token the argmax with ties to the lowest id and NaN rows skipped: the contract of the reference's fused kernels
+ * (src/backend/metal/kernels/lm_head_q4.metal:25-100: strict '>' over ascending rows, '!isnan(total)').  ids[t] is
+ * 0xffffffff when every row is NaN.  logits_out (optional) receives all logits [rows][m->rows]. */
+int mo_lm_head_argmax(const mo_matrix *m, const uint16_t *x_f16, uint32_t rows, uint32_t *ids, float *scores, float *logits_out) {
+    if (!mo_matrix_ok(m) || !x_f16 || !ids || rows == 0u) return 0;
+    const uint32_t C = m->cols, R = m->rows;
+    float *w = (float *)malloc(sizeof(float) * C * 2u);
+    if (!w) return 0;
+    float *x = w + C;
+    for (uint32_t t = 0; t < rows; ++t) { ids[t] = 0xffffffffu; if (scores) scores[t] = -INFINITY; }
+    float *best = (float *)malloc(sizeof(float) * rows);
+    if (!best) { free(w); return 0; }
+    for (uint32_t r = 0; r < R; ++r) {
+        mo_dequant_row(m, r, w);
+        for (uint32_t t = 0; t < rows; ++t) {
+            for (uint32_t c = 0; c < C; ++c) x[c] = mo_f16_to_f32(x_f16[(size_t)t * C + c]);
+            const float v = mo_dot(x, w, C);
+            if (logits_out) logits_out[(size_t)t * R + r] = v;
+            if (v != v) continue;
+            if (ids[t] == 0xffffffffu || v > best[t]) { best[t] = v; ids[t] = r; }
+        }
+    }
+    if (scores) for (uint32_t t = 0; t < rows; ++t) if (ids[t] != 0xffffffffu) scores[t] = best[t];
+    free(best);
+    free(w);
+    return 1;
+}
+
 /* y[rows x m->rows] = x[rows x m->cols] . m^T, each output one fmaf chain.
  * Weight rows are dequantised once (four at a time) and swept over all x rows. */
 static void mo_matmul_nt(const mo_matrix *m, const float *x, uint32_t rows, float *y, float *scratch4) {

@@ -98,6 +98,7 @@ class Port:
             [C.c_void_p] * 7
         lib.mo_dispatch_plan.argtypes = [_u32p] + [C.c_uint32] * 3 + [_u32p] * 3
         lib.mo_dequant_matrix.argtypes = [C.POINTER(_Matrix), _f32p]
+        lib.mo_lm_head_argmax.argtypes = [C.POINTER(_Matrix), _u16p, C.c_uint32, _u32p, _f32p, C.c_void_p]
         self.lib = lib
 
     # -- conversions
@@ -147,6 +148,17 @@ class Port:
         out = np.zeros((rows, H), np.float32)
         st = self.lib.mo_dense_swiglu_f32(x, gate, up, down, rows, H, F, mid, out)
         return st, mid, out
+
+    def lm_head_argmax(self, m: quant.Matrix, x_bits: np.ndarray, want_logits: bool = False):
+        """(ids uint32 [rows], scores f32 [rows], logits f32 [rows, vocab] or None): the LM head's argmax per token."""
+        x_bits = np.ascontiguousarray(x_bits, np.uint16)
+        rows = x_bits.shape[0]
+        ids = np.zeros(rows, np.uint32)
+        scores = np.zeros(rows, np.float32)
+        logits = np.zeros((rows, m.rows), np.float32) if want_logits else None
+        cm = _cmatrix(m)
+        assert self.lib.mo_lm_head_argmax(C.byref(cm), x_bits, rows, ids, scores, _ptr(logits)) == 1
+        return ids, scores, logits
 
     def rmsnorm_f32(self, x: np.ndarray, weight: np.ndarray, eps: float) -> np.ndarray:
         x = np.ascontiguousarray(x, np.float32)

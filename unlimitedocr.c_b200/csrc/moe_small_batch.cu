@@ -289,6 +289,111 @@ cudaError_t launch_small_batch_layer(const DLayer &L, const Scratch &S, const __
     return cudaGetLastError();
 }
 
+// ---- LM head: fused logits + argmax ---------------------------------------------------------------------------------
+// ids[t] = argmax over the vocabulary rows v of ( row v . x[t] ), ties to the lowest id, NaN rows skipped: the contract of
+// the reference's fused kernels (src/backend/metal/kernels/lm_head_q4.metal:25-100, lm_head_q8.metal), which stream the
+// whole [vocab][hidden] matrix once per decoded token (83 MB in Q4_0, 165 MB in Q8_0: the largest single reader of a
+// decode step after the MoE layers).  One warp per row, rows dealt round-robin over a grid of a few CTAs per SM; up to
+// four tokens share one pass over the weights.  Every CTA leaves its best (score, id) per token; the CTA that takes the
+// last ticket picks the winner.
+constexpr int kLmThreads = 256;
+
+__device__ __forceinline__ bool lm_better(float s, uint32_t id, float best, uint32_t best_id) {
+    return id != 0xffffffffu && (best_id == 0xffffffffu || s > best || (s == best && id < best_id));
+}
+
+template <int QT, int M>
+__global__ void __launch_bounds__(kLmThreads)
+lm_head_argmax_kernel(const __half *__restrict__ hidden, uint32_t n, uint32_t H, const uint8_t *__restrict__ w, const __half *__restrict__ sc,
+                      uint32_t vocab, uint32_t row_bytes, float *__restrict__ part_scores, uint32_t *__restrict__ part_ids,
+                      uint32_t *__restrict__ ticket, uint32_t *__restrict__ ids_out, float *__restrict__ scores_out) {
+    extern __shared__ float xs[];            // [M][H]
+    __shared__ float s_score[kLmThreads / 32][M];
+    __shared__ uint32_t s_id[kLmThreads / 32][M];
+    __shared__ bool s_last;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    for (uint32_t k = tid; k < (uint32_t)M * H; k += kLmThreads) xs[k] = k < n * H ? __half2float(hidden[k]) : 0.f;    // slots beyond n: zeros
+    __syncthreads();
+    const uint32_t groups = H / UOCR_GROUP;
+    float best[M];
+    uint32_t best_id[M];
+#pragma unroll
+    for (int m = 0; m < M; ++m) { best[m] = 0.f; best_id[m] = 0xffffffffu; }
+    const uint32_t warps = gridDim.x * (kLmThreads / 32);
+    for (uint32_t row = blockIdx.x * (kLmThreads / 32) + warp; row < vocab; row += warps) {
+        float acc[M];
+#pragma unroll
+        for (int m = 0; m < M; ++m) acc[m] = 0.f;
+        row_dot<QT, M>(w + (size_t)row * row_bytes, sc ? sc + (size_t)row * groups : nullptr, H, xs, (int)H, lane, acc);
+#pragma unroll
+        for (int m = 0; m < M; ++m) {
+            const float v = warp_sum(acc[m]);
+            if (v == v && lm_better(v, row, best[m], best_id[m])) { best[m] = v; best_id[m] = row; }     // rows ascend per warp
+        }
+    }
+    if (lane == 0) {
+#pragma unroll
+        for (int m = 0; m < M; ++m) { s_score[warp][m] = best[m]; s_id[warp][m] = best_id[m]; }
+    }
+    __syncthreads();
+    if (tid < M) {
+        float b = 0.f;
+        uint32_t bi = 0xffffffffu;
+        for (int wv = 0; wv < kLmThreads / 32; ++wv)
+            if (lm_better(s_score[wv][tid], s_id[wv][tid], b, bi)) { b = s_score[wv][tid]; bi = s_id[wv][tid]; }
+        part_scores[(size_t)blockIdx.x * M + tid] = b;
+        part_ids[(size_t)blockIdx.x * M + tid] = bi;
+    }
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) s_last = atomicAdd(ticket, 1u) == gridDim.x - 1;
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    // the last CTA: one warp per token scans every CTA's entry
+    if ((uint32_t)warp < n) {
+        float b = 0.f;
+        uint32_t bi = 0xffffffffu;
+        for (uint32_t c = lane; c < gridDim.x; c += 32) {
+            const float s2 = __ldcg(part_scores + (size_t)c * M + warp);
+            const uint32_t i2 = __ldcg(part_ids + (size_t)c * M + warp);
+            if (lm_better(s2, i2, b, bi)) { b = s2; bi = i2; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float s2 = __shfl_xor_sync(0xffffffffu, b, o);
+            const uint32_t i2 = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (lm_better(s2, i2, b, bi)) { b = s2; bi = i2; }
+        }
+        if (lane == 0) {
+            ids_out[warp] = bi;
+            if (scores_out) scores_out[warp] = bi == 0xffffffffu ? -INFINITY : b;
+        }
+    }
+    if (tid == 0) *ticket = 0;               // ready for the next call on the stream
+}
+
+uint32_t lm_head_max_tokens() { return kMaxM; }
+
+cudaError_t launch_lm_head_argmax(const DMatrix &m, const __half *hidden, uint32_t n, uint32_t grid, float *part_scores,
+                                  uint32_t *part_ids, uint32_t *ticket, uint32_t *ids_out, float *scores_out, cudaStream_t st,
+                                  uint64_t *launches) {
+    if (n == 0 || n > (uint32_t)kMaxM || (size_t)kMaxM * m.cols * sizeof(float) > 48 * 1024) return cudaErrorInvalidValue;
+    const size_t smem = sizeof(float) * (n <= 1 ? 1 : (n == 2 ? 2 : kMaxM)) * m.cols;
+#define UOCR_LM_LAUNCH(MM)                                                                                                       \
+    UOCR_QT_SWITCH(m.qtype, (lm_head_argmax_kernel<QT, MM><<<grid, kLmThreads, smem, st>>>(hidden, n, m.cols, m.w, m.s, m.rows, m.row_bytes, \
+                                                                                           part_scores, part_ids, ticket, ids_out, scores_out)))
+    if (n == 1) { UOCR_LM_LAUNCH(1); }
+    else if (n == 2) { UOCR_LM_LAUNCH(2); }
+    else {
+        // three tokens run in the four-token instantiation: the fourth slot holds zeros and writes nothing
+        UOCR_LM_LAUNCH(kMaxM);
+    }
+#undef UOCR_LM_LAUNCH
+    ++*launches;
+    return cudaGetLastError();
+}
+
 // ---- dequantisation probe ------------------------------------------------------------------------------------
 // out[row][col] = the f32 value the matrix-vector kernels give weight (row, col): the row is multiplied, through the
 // same row_dot() the layer kernels use, with a one-hot activation vector per column, which leaves level * scale.

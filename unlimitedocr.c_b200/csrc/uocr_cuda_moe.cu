@@ -16,6 +16,10 @@ namespace uocr {
 cudaError_t init_router_kernels();
 cudaError_t init_small_batch_kernels();
 bool dense_small_supported(uint32_t H, uint32_t S);
+uint32_t lm_head_max_tokens();
+cudaError_t launch_lm_head_argmax(const DMatrix &m, const __half *hidden, uint32_t n, uint32_t grid, float *part_scores,
+                                  uint32_t *part_ids, uint32_t *ticket, uint32_t *ids_out, float *scores_out, cudaStream_t st,
+                                  uint64_t *launches);
 bool gemm_tensor_maps_ready();
 cudaError_t launch_dense_small(const DMatrix &g, const DMatrix &u, const DMatrix &d, const __half *hidden, const __half *residual,
                                uint32_t n, __half *mid, float *out_f32, __half *out, cudaStream_t st, uint64_t *launches);
@@ -111,6 +115,13 @@ struct uocr_cuda_context {
         uint64_t scratch_bytes = 0;
     };
     std::vector<DenseMlp> dense;
+    // the LM head (vocabulary projection) and the scratch of its fused argmax
+    struct {
+        DMatrix w{};
+        bool mapped = false;
+        uint32_t grid = 0;
+        void *scratch = nullptr;       // [grid][4] scores, [grid][4] ids, ticket
+    } lm_head;
     DLayer *d_layers = nullptr;        // device copy of `layers`
     bool fused_decode = true;          // single-token calls use the persistent decode kernel when it fits
     uint32_t gemm_min_tokens = 5;      // calls with at least this many tokens take the tensor-core path
@@ -385,6 +396,8 @@ extern "C" void uocr_cuda_context_unmap_model(uocr_cuda_context *ctx) {
     for (auto &d : ctx->dense) cudaFree(d.scratch);
     ctx->dense.clear();
     ctx->dense_scratch_bytes = 0;
+    cudaFree(ctx->lm_head.scratch);
+    ctx->lm_head = {};
     ctx->weight_bytes = 0;
     track_memory(ctx);
 }
@@ -1153,6 +1166,47 @@ extern "C" int uocr_cuda_dense_mlp_forward_normed(uocr_cuda_context *ctx, uint32
     if (n > D.capacity) return fail(ctx, error, error_size, "n_tokens %u exceeds the dense MLP's capacity %u", n, D.capacity);
     if (!uocr_cuda_rmsnorm(ctx, d_stream, d_norm_weight_f16, eps, n, D.H, D.x_norm, error, error_size)) return 0;
     return dense_forward(ctx, index, D.x_norm, (const __half *)d_stream, n, (__half *)d_out, error, error_size);
+}
+
+// ---- LM head: fused logits + argmax ----------------------------------------------------------------------------------
+extern "C" int uocr_cuda_context_map_lm_head(uocr_cuda_context *ctx, const uocr_cuda_matrix *weight, char *error, size_t error_size) {
+    if (!ctx || !weight) return fail(ctx, error, error_size, "null context or matrix");
+    if (ctx->lm_head.mapped) return fail(ctx, error, error_size, "an LM head is already mapped; call uocr_cuda_context_unmap_model first");
+    const uint32_t V = weight->rows, H = weight->cols;
+    if (V == 0 || H == 0 || H % UOCR_GROUP || H > 2048) return fail(ctx, error, error_size, "LM head shape [%u, %u] not supported (hidden: multiple of 64, at most 2048)", V, H);
+    if (!check_matrix(ctx, *weight, V, H, "LM head", error, error_size)) return 0;
+    CU_TRY(ctx, cudaSetDevice(ctx->device));
+    const int q = weight->qtype;
+    const uint64_t wb = packed_bytes(q, V, H), sb = q == UOCR_QT_F16 ? 0 : (uint64_t)V * (H / UOCR_GROUP) * 2;
+    void *pw = nullptr, *ps = nullptr;
+    if (!upload(ctx, weight->qweight, wb, &pw, error, error_size)) return 0;
+    if (sb && !upload(ctx, weight->qscale, sb, &ps, error, error_size)) return 0;
+    ctx->lm_head.w = DMatrix{(const uint8_t *)pw, (const __half *)ps, V, H, (uint32_t)(wb / V), q};
+    int sms = 0;
+    CU_TRY(ctx, cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, ctx->device));
+    ctx->lm_head.grid = (uint32_t)sms * 8u;                // 8 CTAs of 256 threads per SM: every SM's 64 warp slots stream rows
+    const size_t bytes = (size_t)ctx->lm_head.grid * 4 * 8 + 256;
+    CU_TRY(ctx, cudaMalloc(&ctx->lm_head.scratch, bytes));
+    CU_TRY(ctx, cudaMemset(ctx->lm_head.scratch, 0, bytes));
+    ctx->lm_head.mapped = true;
+    track_memory(ctx);
+    return 1;
+}
+
+extern "C" int uocr_cuda_lm_head_argmax(uocr_cuda_context *ctx, const void *d_hidden, uint32_t n, uint32_t *d_token_ids,
+                                        float *d_scores, char *error, size_t error_size) {
+    if (!ctx) return fail(nullptr, error, error_size, "null context");
+    if (!ctx->lm_head.mapped) return fail(ctx, error, error_size, "no LM head mapped");
+    if (!d_hidden || !d_token_ids || n == 0) return fail(ctx, error, error_size, "null or empty LM head argument");
+    if (n > uocr::lm_head_max_tokens()) return fail(ctx, error, error_size, "the fused LM head takes at most %u tokens per call", uocr::lm_head_max_tokens());
+    CU_TRY(ctx, cudaSetDevice(ctx->device));
+    auto &Lm = ctx->lm_head;
+    float *part_scores = (float *)Lm.scratch;
+    uint32_t *part_ids = (uint32_t *)(part_scores + (size_t)Lm.grid * 4);
+    uint32_t *ticket = part_ids + (size_t)Lm.grid * 4;
+    CU_TRY(ctx, uocr::launch_lm_head_argmax(Lm.w, (const __half *)d_hidden, n, Lm.grid, part_scores, part_ids, ticket, d_token_ids,
+                                            d_scores, ctx->stream, &ctx->launches));
+    return 1;
 }
 
 extern "C" const char *uocr_cuda_moe_regime_name(const uocr_cuda_context *ctx, uint32_t layer, uint32_t n) {

@@ -62,7 +62,7 @@ EXPORTS = (
     "uocr_cuda_context_moe_layer_count", "uocr_cuda_context_allocate_runtime_arenas",
     "uocr_cuda_context_release_runtime_arenas", "uocr_cuda_moe_scratch_size", "uocr_cuda_moe_router",
     "uocr_cuda_moe_dispatch_plan", "uocr_cuda_moe_dispatch_plan_noalloc", "uocr_cuda_moe_debug_dequantize", "uocr_cuda_moe_regime_name", "uocr_cuda_rmsnorm", "uocr_cuda_moe_layer_forward_normed", "uocr_cuda_context_map_dense_mlp",
-    "uocr_cuda_dense_mlp_forward", "uocr_cuda_dense_mlp_forward_normed", "uocr_cuda_moe_layer_forward", "uocr_cuda_moe_stack_forward",
+    "uocr_cuda_dense_mlp_forward", "uocr_cuda_dense_mlp_forward_normed", "uocr_cuda_context_map_lm_head", "uocr_cuda_lm_head_argmax", "uocr_cuda_moe_layer_forward", "uocr_cuda_moe_stack_forward",
     "uocr_cuda_moe_layer_forward_host", "uocr_cuda_moe_stack_forward_host",
     "uocr_cuda_moe_ep_dispatch", "uocr_cuda_moe_ep_experts", "uocr_cuda_moe_ep_shared", "uocr_cuda_moe_ep_combine",
     "uocr_cuda_moe_ep_peer_forward", "uocr_cuda_moe_ep_peer_last_offsets", "uocr_cuda_moe_ep_peer_create", "uocr_cuda_moe_ep_peer_open", "uocr_cuda_moe_ep_peer_destroy",
@@ -124,6 +124,8 @@ def load_library() -> C.CDLL:
         "uocr_cuda_context_map_dense_mlp": (C.c_int, [vp, C.POINTER(CMatrix), C.POINTER(CMatrix), C.POINTER(CMatrix), u32, C.POINTER(u32)] + err),
         "uocr_cuda_dense_mlp_forward": (C.c_int, [vp, u32, vp, vp, u32, vp] + err),
         "uocr_cuda_dense_mlp_forward_normed": (C.c_int, [vp, u32, vp, vp, C.c_float, u32, vp] + err),
+        "uocr_cuda_context_map_lm_head": (C.c_int, [vp, C.POINTER(CMatrix)] + err),
+        "uocr_cuda_lm_head_argmax": (C.c_int, [vp, vp, u32, vp, vp] + err),
         "uocr_cuda_context_moe_layer_count": (u32, [vp]),
         "uocr_cuda_context_allocate_runtime_arenas": (C.c_int, [vp, u32, u32] + err),
         "uocr_cuda_context_release_runtime_arenas": (None, [vp]),
@@ -307,6 +309,17 @@ class Context:
     def dense_mlp_forward_normed(self, index: int, stream_rows, norm_weight, eps: float, n_tokens: int, out) -> None:
         self._check(self._lib.uocr_cuda_dense_mlp_forward_normed(self._h, index, _dev_ptr(stream_rows), _dev_ptr(norm_weight), eps,
                                                                  n_tokens, _dev_ptr(out), self._err, _ERR))
+
+    def map_lm_head(self, weight: Any) -> None:
+        """weight: object with qtype, rows (vocabulary), cols (hidden), qweight, qscale (host arrays)."""
+        w = np.ascontiguousarray(weight.qweight)
+        sc = None if weight.qscale is None else np.ascontiguousarray(weight.qscale)
+        cm = CMatrix(weight.qtype, weight.rows, weight.cols, w.ctypes.data, None if sc is None else sc.ctypes.data)
+        self._check(self._lib.uocr_cuda_context_map_lm_head(self._h, C.byref(cm), self._err, _ERR))
+
+    def lm_head_argmax(self, hidden, n_tokens: int, token_ids, scores=None) -> None:
+        self._check(self._lib.uocr_cuda_lm_head_argmax(self._h, _dev_ptr(hidden), n_tokens, _dev_ptr(token_ids), _dev_ptr(scores),
+                                                       self._err, _ERR))
 
     def release_runtime_arenas(self) -> None:
         self._lib.uocr_cuda_context_release_runtime_arenas(self._h)
