@@ -293,8 +293,8 @@ cudaError_t launch_small_batch_layer(const DLayer &L, const Scratch &S, const __
 // ids[t] = argmax over the vocabulary rows v of ( row v . x[t] ), ties to the lowest id, NaN rows skipped: the contract of
 // the reference's fused kernels (src/backend/metal/kernels/lm_head_q4.metal:25-100, lm_head_q8.metal), which stream the
 // whole [vocab][hidden] matrix once per decoded token (83 MB in Q4_0, 165 MB in Q8_0: the largest single reader of a
-// decode step after the MoE layers).  One warp per row, rows dealt round-robin over a grid of a few CTAs per SM; up to
-// four tokens share one pass over the weights.  Every CTA leaves its best (score, id) per token; the CTA that takes the
+// decode step after the MoE layers).  Eight lanes per row, four rows per warp and pass, the passes dealt round-robin over a
+// grid of a few CTAs per SM; up to four tokens share one pass over the weights.  Every CTA leaves its best (score, id) per token; the CTA that takes the
 // last ticket picks the winner.
 constexpr int kLmThreads = 256;
 
@@ -319,16 +319,62 @@ lm_head_argmax_kernel(const __half *__restrict__ hidden, uint32_t n, uint32_t H,
     uint32_t best_id[M];
 #pragma unroll
     for (int m = 0; m < M; ++m) { best[m] = 0.f; best_id[m] = 0xffffffffu; }
-    const uint32_t warps = gridDim.x * (kLmThreads / 32);
-    for (uint32_t row = blockIdx.x * (kLmThreads / 32) + warp; row < vocab; row += warps) {
+    // Eight lanes per row, four rows per warp and pass: a lane's 16-byte pieces of its row (every eighth one, so the eight
+    // lanes read 128 contiguous bytes at a time) and their scales are all requested before the first is used, which keeps
+    // several kilobytes per warp in flight instead of one load per lane.
+    constexpr int kLanesPerRow = 8, kRowsPerPass = 32 / kLanesPerRow, kBatch = 5;
+    constexpr int kW = ChunkTraits<QT>::kWeights, kChunksPerGroup = UOCR_GROUP / kW;
+    const int sub = lane & (kLanesPerRow - 1), rsel = lane / kLanesPerRow;
+    const uint32_t chunks = H / kW;
+    const uint32_t pass_rows = gridDim.x * (kLmThreads / 32) * kRowsPerPass;
+    for (uint32_t row0 = (blockIdx.x * (kLmThreads / 32) + warp) * kRowsPerPass; row0 < vocab; row0 += pass_rows) {
+        const uint32_t row = row0 + rsel;
+        const bool valid = row < vocab;
         float acc[M];
 #pragma unroll
         for (int m = 0; m < M; ++m) acc[m] = 0.f;
-        row_dot<QT, M>(w + (size_t)row * row_bytes, sc ? sc + (size_t)row * groups : nullptr, H, xs, (int)H, lane, acc);
+        if (valid) {
+            const uint4 *w4 = reinterpret_cast<const uint4 *>(w + (size_t)row * row_bytes);
+            const __half *srow = sc ? sc + (size_t)row * groups : nullptr;
+            for (uint32_t base = 0; base < chunks; base += kLanesPerRow * kBatch) {
+                uint4 q[kBatch];
+                __half scl[kBatch];
+#pragma unroll
+                for (int i = 0; i < kBatch; ++i) {
+                    const uint32_t c = base + sub + kLanesPerRow * i;
+                    if (c < chunks) {
+                        q[i] = __ldg(w4 + c);
+                        if (QT != UOCR_QT_F16) scl[i] = srow[c / kChunksPerGroup];
+                    }
+                }
+#pragma unroll
+                for (int i = 0; i < kBatch; ++i) {
+                    const uint32_t c = base + sub + kLanesPerRow * i;
+                    if (c < chunks) {
+                        if (QT == UOCR_QT_Q4) chunk_dot_q4<M>(q[i], xs, (int)H, (int)c, __half2float(scl[i]), acc);
+                        else if (QT == UOCR_QT_Q8) chunk_dot_q8<M>(q[i], xs, (int)H, (int)c, __half2float(scl[i]), acc);
+                        else chunk_dot_f16<M>(q[i], xs, (int)H, (int)c, acc);
+                    }
+                }
+            }
+        }
 #pragma unroll
         for (int m = 0; m < M; ++m) {
-            const float v = warp_sum(acc[m]);
-            if (v == v && lm_better(v, row, best[m], best_id[m])) { best[m] = v; best_id[m] = row; }     // rows ascend per warp
+            float v = acc[m];
+            v += __shfl_xor_sync(0xffffffffu, v, 1);
+            v += __shfl_xor_sync(0xffffffffu, v, 2);
+            v += __shfl_xor_sync(0xffffffffu, v, 4);
+            if (valid && v == v && lm_better(v, row, best[m], best_id[m])) { best[m] = v; best_id[m] = row; }
+        }
+    }
+    // the four row groups of the warp
+#pragma unroll
+    for (int m = 0; m < M; ++m) {
+#pragma unroll
+        for (int o = kLanesPerRow; o < 32; o <<= 1) {
+            const float s2 = __shfl_xor_sync(0xffffffffu, best[m], o);
+            const uint32_t i2 = __shfl_xor_sync(0xffffffffu, best_id[m], o);
+            if (lm_better(s2, i2, best[m], best_id[m])) { best[m] = s2; best_id[m] = i2; }
         }
     }
     if (lane == 0) {
