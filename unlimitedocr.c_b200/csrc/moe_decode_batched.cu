@@ -35,11 +35,16 @@ namespace uocr {
 constexpr int kBtConsumers = 512;                              // 16 warps compute
 constexpr int kBtThreads = kBtConsumers + 32;                  // + one warp that issues the bulk copies
 constexpr int kBtTokens = 16;                                  // tokens per pass
-constexpr int kBtSlices = 2;                                   // consecutive slices per item
-constexpr int kBtParts = kSlRoutedPerSlot / kBtSlices;         // 7 items per (expert, pass)
+// An item covers SLICES consecutive 64-wide slices of its expert (template parameter of the kernel): two for calls of more
+// than 16 tokens (7 parts per expert and pass), one for smaller calls (14 parts), whose ~150 two-slice items would leave most
+// CTAs idle during a second wave.  The partial-output buffers are sized for 14 parts.
+constexpr int kBtMaxParts = kSlRoutedPerSlot;                  // 14
+constexpr int kBtSmallCallTokens = 16;
+__host__ __device__ constexpr int bt_slices_for(uint32_t n) { return n <= (uint32_t)kBtSmallCallTokens ? 1 : 2; }
 constexpr int kBtSharedHalves = kSlS / 64 / kSlRoutedPerSlot;  // the shared MLP as 2 pseudo-experts of 14 slices
 constexpr int kBtEntries = kSlE + kBtSharedHalves;             // 66
 constexpr int kBtStages = 4;
+constexpr int kBtDownChunks = 3;                               // ring chunks that carry a slice's `down` fragments and scales
 constexpr int kBtChunks = 5;                                   // chunks of four groups per slice
 constexpr int kBtMaxTokens = 64;
 constexpr int kBtBlocksPerWarp = kSlH / 16 / 16;               // 5 blocks of 16 `down` rows per warp
@@ -188,8 +193,8 @@ struct BatchedParams {
     const uint32_t *active;           // [0] = number of experts with at least one pair, then their ids
     const uint32_t *expert_offsets;   // [E + 1]
     const uint32_t *pair_rows;        // pairs grouped by expert
-    float *routed_part;               // [kBtParts][n * K][H], row = position in pair_rows
-    float *shared_part;               // [kBtSharedHalves * kBtParts][n][H]
+    float *routed_part;               // [parts][n * K][H], row = position in pair_rows
+    float *shared_part;               // [kBtSharedHalves * parts][n][H]
     uint32_t *status;
 };
 
@@ -205,6 +210,8 @@ __device__ unsigned long long g_bt_trace[16];
 
 template <int QT> struct BtSmem {
     static constexpr int kChunkBytes = SlBlob<QT>::kGuBytes / kBtChunks;
+    static constexpr int kDownBytes = SlBlob<QT>::kDnBytes + kSlH * 2;      // `down` fragments and their scales: three chunks of the ring
+    static_assert(kDownBytes > 2 * kChunkBytes && kDownBytes <= 3 * kChunkBytes && kDownBytes % 16 == 0, "down region = three ring chunks");
     static constexpr int kRing = 0;
     static constexpr int kSc = kRing + kBtStages * kChunkBytes;             // two buffers of gate / up scales
     static constexpr int kXf = kSc + 2 * SlBlob<QT>::kGuScBytes;            // activation bytes [16 tok][20][2][16 words]
@@ -229,8 +236,9 @@ struct BtItem {
     uint32_t expert, part, row0, p0, T;
 };
 
-template <int QT>
+template <int QT, int SLICES>
 __global__ void __launch_bounds__(kBtThreads, 1) decode_batched_kernel(const __grid_constant__ BatchedParams prm) {
+    constexpr int kBtSlices = SLICES, kBtParts = kSlRoutedPerSlot / SLICES;
     using Bl = SlBlob<QT>;
     using Sm = BtSmem<QT>;
     constexpr int H = kSlH;
@@ -317,6 +325,15 @@ __global__ void __launch_bounds__(kBtThreads, 1) decode_batched_kernel(const __g
                             bulk_g2s(smem + Sm::kSc + sb * Bl::kGuScBytes, blob + Bl::kGuSc, Bl::kGuScBytes, &sc_full[sb]);
                         }
                     }
+                    // then the slice's `down` fragments and their scales (contiguous in the blob), through the same ring
+                    for (int d = 0; d < kBtDownChunks; ++d, ++seq) {
+                        const uint32_t s = seq % kBtStages;
+                        if (seq >= (uint32_t)kBtStages && !mbar_wait(&empty[s], ((seq / kBtStages) - 1u) & 1u, prm.status, s_flag)) return;
+                        const uint32_t off = (uint32_t)d * Sm::kChunkBytes;
+                        const uint32_t bytes = min((uint32_t)Sm::kChunkBytes, (uint32_t)Sm::kDownBytes - off);
+                        mbar_expect_tx(&full[s], bytes);
+                        bulk_g2s(smem + Sm::kRing + s * Sm::kChunkBytes, blob + Bl::kDn + off, bytes, &full[s]);
+                    }
                 }
             }
         }
@@ -374,22 +391,6 @@ __global__ void __launch_bounds__(kBtThreads, 1) decode_batched_kernel(const __g
             // the slice's 64 columns of `down` for this warp's five 16-row blocks, and the rows' scales, into registers
             uint4 dwn[kBtBlocksPerWarp][2];
             __half dslo[kBtBlocksPerWarp], dshi[kBtBlocksPerWarp];
-            // (requested one 16-row block per chunk of the gate / up loop below: twenty 512-byte loads per warp at once
-            // only queue up in front of the load unit, while spread over the loop they travel beside its arithmetic)
-            const uint4 *dn = reinterpret_cast<const uint4 *>(blob + Bl::kDn);
-            const __half *dsc = reinterpret_cast<const __half *>(blob + Bl::kDnSc);
-            auto fetch_down_block = [&](int bi) {
-                const int blk = warp + 16 * bi;
-                if (QT == UOCR_QT_Q8) {
-                    dwn[bi][0] = __ldg(dn + (blk * 2) * 32 + lane);
-                    dwn[bi][1] = __ldg(dn + (blk * 2 + 1) * 32 + lane);
-                } else {
-                    dwn[bi][0] = __ldg(dn + blk * 32 + lane);
-                }
-                dslo[bi] = dsc[16 * blk + g];
-                dshi[bi] = dsc[16 * blk + 8 + g];
-            };
-            static_assert(kBtBlocksPerWarp == kBtChunks, "one down block is requested per gate / up chunk");
             BT_ADD(1, bt_dw);
             BT_T0(bt_gu);
             // 2. gate / up: rows 8 rb .. + 7 of both matrices x the tokens of n-blocks nh and nh + 2
@@ -404,7 +405,6 @@ __global__ void __launch_bounds__(kBtThreads, 1) decode_batched_kernel(const __g
                 got = mbar_wait(&full[s], (seq / kBtStages) & 1u, prm.status, s_flag) && got;
                 if (c == 0) got = mbar_wait(&sc_full[sb], (slices_done >> 1) & 1u, prm.status, s_flag) && got;
                 BT_ADD(2, bt_w);
-                fetch_down_block(c);
                 const uint4 *w4 = s_ring4 + (size_t)s * (Sm::kChunkBytes / 16);
                 if ((uint32_t)nh < NB) {
 #pragma unroll
@@ -435,6 +435,32 @@ __global__ void __launch_bounds__(kBtThreads, 1) decode_batched_kernel(const __g
             }
             __syncwarp();
             if (lane == 0) bt_arrive(&sc_empty[sb]);
+            // the slice's `down` fragments arrive through the ring as three more chunks (32 blocks of 16 rows per chunk):
+            // this warp's five blocks and their scales go to registers, and the stages are handed back at once
+            {
+                const uint32_t s0 = seq % kBtStages, s1 = (seq + 1) % kBtStages, s2 = (seq + 2) % kBtStages;
+                got = mbar_wait(&full[s0], (seq / kBtStages) & 1u, prm.status, s_flag) && got;
+                got = mbar_wait(&full[s1], ((seq + 1) / kBtStages) & 1u, prm.status, s_flag) && got;
+                got = mbar_wait(&full[s2], ((seq + 2) / kBtStages) & 1u, prm.status, s_flag) && got;
+                const uint32_t stage_of[3] = {s0, s1, s2};
+                constexpr int kBlockVecs = QT == UOCR_QT_Q8 ? 64 : 32;          // 16-byte vectors per 16-row block
+                constexpr int kBlocksPerChunk = Sm::kChunkBytes / 16 / kBlockVecs;   // 32
+                const __half *dsc = reinterpret_cast<const __half *>(smem + Sm::kRing + s2 * Sm::kChunkBytes +
+                                                                    (Bl::kDnBytes - 2 * Sm::kChunkBytes));
+#pragma unroll
+                for (int bi = 0; bi < kBtBlocksPerWarp; ++bi) {
+                    const int blk = warp + 16 * bi;
+                    const uint4 *src = s_ring4 + (size_t)stage_of[blk / kBlocksPerChunk] * (Sm::kChunkBytes / 16) +
+                                       (size_t)(blk % kBlocksPerChunk) * kBlockVecs;
+                    dwn[bi][0] = src[lane];
+                    if (QT == UOCR_QT_Q8) dwn[bi][1] = src[32 + lane];
+                    dslo[bi] = dsc[16 * blk + g];
+                    dshi[bi] = dsc[16 * blk + 8 + g];
+                }
+                __syncwarp();
+                if (lane == 0) { bt_arrive(&empty[s0]); bt_arrive(&empty[s1]); bt_arrive(&empty[s2]); }
+                seq += kBtDownChunks;
+            }
             BT_ADD(3, bt_gu);
             BT_T0(bt_sw);
             // 3. SwiGLU in registers: lane (g, t) holds gate and up of column 8 rb + g for token 4 nb + t
@@ -506,47 +532,54 @@ __global__ void __launch_bounds__(kBtThreads, 1) decode_batched_kernel(const __g
 __global__ void __launch_bounds__(256) combine_batched_kernel(const float *__restrict__ routed_part, const float *__restrict__ shared_part,
                                                               const __half *__restrict__ residual, const uint32_t *__restrict__ inverse,
                                                               const float *__restrict__ weights, uint32_t n, uint32_t H, uint32_t K,
-                                                              __half *__restrict__ out) {
+                                                              uint32_t parts, __half *__restrict__ out) {
     const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;       // one thread per 4 outputs
     const uint32_t per_row = H / 4;
     if (idx >= (size_t)n * per_row) return;
     const uint32_t tkn = (uint32_t)(idx / per_row), c = (uint32_t)(idx % per_row) * 4;
     const size_t routed_stride = (size_t)n * K * H, shared_stride = (size_t)n * H;
-    // the shared parts first in flight, summed last (the order of the CPU path: routed slots, then shared, then residual)
-    float4 sh[kBtSharedHalves * kBtParts];
-#pragma unroll
-    for (int p = 0; p < kBtSharedHalves * kBtParts; ++p)
-        sh[p] = *reinterpret_cast<const float4 *>(shared_part + p * shared_stride + (size_t)tkn * H + c);
+    // Parts are read seven at a time (all seven loads of up to three slots in flight together) and added in part order.
+    constexpr int kChunk = 7;
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
-    // three slots at a time: their 21 loads are issued before the first is used
     for (uint32_t s0 = 0; s0 < K; s0 += 3) {
         uint32_t pos[3];
         float w[3];
-        float4 v[3][kBtParts];
+        float4 sum[3];
 #pragma unroll
         for (int j = 0; j < 3; ++j) {
             pos[j] = s0 + j < K ? inverse[tkn * K + s0 + j] : 0xffffffffu;
             w[j] = s0 + j < K ? weights[tkn * K + s0 + j] : 0.f;
+            sum[j] = make_float4(0.f, 0.f, 0.f, 0.f);
         }
+        for (uint32_t p0 = 0; p0 < parts; p0 += kChunk) {
+            float4 v[3][kChunk];
 #pragma unroll
-        for (int j = 0; j < 3; ++j)
+            for (int j = 0; j < 3; ++j)
 #pragma unroll
-            for (int p = 0; p < kBtParts; ++p)
-                v[j][p] = pos[j] != 0xffffffffu ? *reinterpret_cast<const float4 *>(routed_part + p * routed_stride + (size_t)pos[j] * H + c)
-                                                 : make_float4(0.f, 0.f, 0.f, 0.f);
+                for (int p = 0; p < kChunk; ++p)
+                    v[j][p] = pos[j] != 0xffffffffu ? *reinterpret_cast<const float4 *>(routed_part + (p0 + p) * routed_stride + (size_t)pos[j] * H + c)
+                                                     : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int j = 0; j < 3; ++j)
+#pragma unroll
+                for (int p = 0; p < kChunk; ++p) { sum[j].x += v[j][p].x; sum[j].y += v[j][p].y; sum[j].z += v[j][p].z; sum[j].w += v[j][p].w; }
+        }
 #pragma unroll
         for (int j = 0; j < 3; ++j) {
             if (pos[j] == 0xffffffffu) continue;
-            float4 sum = v[j][0];
-#pragma unroll
-            for (int p = 1; p < kBtParts; ++p) { sum.x += v[j][p].x; sum.y += v[j][p].y; sum.z += v[j][p].z; sum.w += v[j][p].w; }
-            acc[0] = fmaf(w[j], sum.x, acc[0]); acc[1] = fmaf(w[j], sum.y, acc[1]);
-            acc[2] = fmaf(w[j], sum.z, acc[2]); acc[3] = fmaf(w[j], sum.w, acc[3]);
+            acc[0] = fmaf(w[j], sum[j].x, acc[0]); acc[1] = fmaf(w[j], sum[j].y, acc[1]);
+            acc[2] = fmaf(w[j], sum[j].z, acc[2]); acc[3] = fmaf(w[j], sum[j].w, acc[3]);
         }
     }
-    float4 ssum = sh[0];
+    // the shared MLP's parts (the order of the CPU path: routed slots, then shared, then residual)
+    float4 ssum = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (uint32_t p0 = 0; p0 < (uint32_t)kBtSharedHalves * parts; p0 += kChunk) {
+        float4 sh[kChunk];
 #pragma unroll
-    for (int p = 1; p < kBtSharedHalves * kBtParts; ++p) { ssum.x += sh[p].x; ssum.y += sh[p].y; ssum.z += sh[p].z; ssum.w += sh[p].w; }
+        for (int p = 0; p < kChunk; ++p) sh[p] = *reinterpret_cast<const float4 *>(shared_part + (p0 + p) * shared_stride + (size_t)tkn * H + c);
+#pragma unroll
+        for (int p = 0; p < kChunk; ++p) { ssum.x += sh[p].x; ssum.y += sh[p].y; ssum.z += sh[p].z; ssum.w += sh[p].w; }
+    }
     acc[0] += ssum.x; acc[1] += ssum.y; acc[2] += ssum.z; acc[3] += ssum.w;
     if (residual) {
         const uint2 rv = *reinterpret_cast<const uint2 *>(residual + (size_t)tkn * H + c);
@@ -564,11 +597,13 @@ __global__ void __launch_bounds__(256) combine_batched_kernel(const float *__res
 bool decode_sliced_layer_ok(const DLayer &L);
 
 cudaError_t init_decode_batched_kernels() {
-    cudaError_t err = cudaFuncSetAttribute(decode_batched_kernel<UOCR_QT_Q4>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                           (int)BtSmem<UOCR_QT_Q4>::kTotal);
-    if (err != cudaSuccess) return err;
-    return cudaFuncSetAttribute(decode_batched_kernel<UOCR_QT_Q8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                (int)BtSmem<UOCR_QT_Q8>::kTotal);
+    cudaError_t err = cudaSuccess;
+#define UOCR_BT_SMEM(QT, SL)                                                                                              \
+    if (err == cudaSuccess)                                                                                               \
+        err = cudaFuncSetAttribute(decode_batched_kernel<QT, SL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)BtSmem<QT>::kTotal);
+    UOCR_BT_SMEM(UOCR_QT_Q4, 1) UOCR_BT_SMEM(UOCR_QT_Q4, 2) UOCR_BT_SMEM(UOCR_QT_Q8, 1) UOCR_BT_SMEM(UOCR_QT_Q8, 2)
+#undef UOCR_BT_SMEM
+    return err;
 }
 
 static std::atomic<int> g_bt_sms[64];
@@ -581,8 +616,8 @@ BatchedScratchLayout decode_batched_scratch(uint32_t n, uint32_t K) {
     BatchedScratchLayout l{};
     size_t off = 0;
     auto take = [&](size_t bytes) { const size_t o = off; off = (off + bytes + 255) / 256 * 256; return o; };
-    l.routed_part = take((size_t)kBtParts * n * K * kSlH * sizeof(float));
-    l.shared_part = take((size_t)kBtSharedHalves * kBtParts * n * kSlH * sizeof(float));
+    l.routed_part = take((size_t)kBtMaxParts * n * K * kSlH * sizeof(float));
+    l.shared_part = take((size_t)kBtSharedHalves * kBtMaxParts * n * kSlH * sizeof(float));
     l.x_limbs = take((size_t)n * kBtTokenLimbBytes);
     l.x_scales = take((size_t)n * kSlGroups * sizeof(float));
     l.total = off;
@@ -633,10 +668,16 @@ cudaError_t launch_batched_experts(const DLayer &L, const Scratch &S, uint32_t n
     // at most one item per (selected expert or shared half, pass, part); one CTA per SM, items dealt round-robin
     const uint64_t pairs = (uint64_t)n * L.K;
     const uint64_t max_entry_passes = (pairs < L.E ? pairs : L.E) + pairs / kBtTokens + kBtSharedHalves * ((n + kBtTokens - 1) / kBtTokens);
-    const uint64_t max_items = max_entry_passes * kBtParts;
+    const int slices = bt_slices_for(n);
+    const uint64_t max_items = max_entry_passes * (uint64_t)(kSlRoutedPerSlot / slices);
     const uint32_t grid = (uint32_t)(max_items < (uint64_t)sms ? max_items : (uint64_t)sms);
-    if (L.expert_qtype == UOCR_QT_Q4) decode_batched_kernel<UOCR_QT_Q4><<<grid, kBtThreads, BtSmem<UOCR_QT_Q4>::kTotal, st>>>(p);
-    else decode_batched_kernel<UOCR_QT_Q8><<<grid, kBtThreads, BtSmem<UOCR_QT_Q8>::kTotal, st>>>(p);
+    if (L.expert_qtype == UOCR_QT_Q4) {
+        if (slices == 1) decode_batched_kernel<UOCR_QT_Q4, 1><<<grid, kBtThreads, BtSmem<UOCR_QT_Q4>::kTotal, st>>>(p);
+        else decode_batched_kernel<UOCR_QT_Q4, 2><<<grid, kBtThreads, BtSmem<UOCR_QT_Q4>::kTotal, st>>>(p);
+    } else {
+        if (slices == 1) decode_batched_kernel<UOCR_QT_Q8, 1><<<grid, kBtThreads, BtSmem<UOCR_QT_Q8>::kTotal, st>>>(p);
+        else decode_batched_kernel<UOCR_QT_Q8, 2><<<grid, kBtThreads, BtSmem<UOCR_QT_Q8>::kTotal, st>>>(p);
+    }
     ++*launches;
     return cudaGetLastError();
 }
@@ -647,7 +688,7 @@ cudaError_t launch_batched_combine(const DLayer &L, const Scratch &S, const __ha
     const size_t work = (size_t)n * (L.H / 4);
     combine_batched_kernel<<<(unsigned)((work + 255) / 256), 256, 0, st>>>(
         reinterpret_cast<const float *>(scratch + lay.routed_part), reinterpret_cast<const float *>(scratch + lay.shared_part), residual,
-        S.inverse, S.top_weights, n, L.H, L.K, out);
+        S.inverse, S.top_weights, n, L.H, L.K, (uint32_t)(kSlRoutedPerSlot / bt_slices_for(n)), out);
     ++*launches;
     return cudaGetLastError();
 }
