@@ -529,17 +529,28 @@ __global__ void __launch_bounds__(kBtThreads, 1) decode_batched_kernel(const __g
 
 // ---------------------------------------------------------------- 3. combine
 // out[t][h] = fp16( fma chain over slots of w * (sum of the pair's parts) + (sum of the shared parts) + residual )
+// SPLIT threads share one group of four outputs: each adds every SPLIT-th run of seven parts (all seven loads of up to three
+// slots in flight together), the partial sums meet through a shuffle.  Calls with 14 parts use SPLIT = 2, so the chain of
+// dependent loads is as long as with 7 parts.
+template <int SPLIT>
 __global__ void __launch_bounds__(256) combine_batched_kernel(const float *__restrict__ routed_part, const float *__restrict__ shared_part,
                                                               const __half *__restrict__ residual, const uint32_t *__restrict__ inverse,
                                                               const float *__restrict__ weights, uint32_t n, uint32_t H, uint32_t K,
                                                               uint32_t parts, __half *__restrict__ out) {
-    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;       // one thread per 4 outputs
+    const size_t gthread = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t idx = gthread / SPLIT;                                     // one group of 4 outputs
+    const uint32_t half = (uint32_t)(gthread % SPLIT);
     const uint32_t per_row = H / 4;
-    if (idx >= (size_t)n * per_row) return;
-    const uint32_t tkn = (uint32_t)(idx / per_row), c = (uint32_t)(idx % per_row) * 4;
+    const bool live = idx < (size_t)n * per_row;                            // (whole warps stay in the shuffles below)
+    const uint32_t tkn = live ? (uint32_t)(idx / per_row) : 0u, c = live ? (uint32_t)(idx % per_row) * 4 : 0u;
     const size_t routed_stride = (size_t)n * K * H, shared_stride = (size_t)n * H;
-    // Parts are read seven at a time (all seven loads of up to three slots in flight together) and added in part order.
     constexpr int kChunk = 7;
+    auto meet = [](float4 &v) {
+        if (SPLIT == 2) {
+            v.x += __shfl_xor_sync(0xffffffffu, v.x, 1); v.y += __shfl_xor_sync(0xffffffffu, v.y, 1);
+            v.z += __shfl_xor_sync(0xffffffffu, v.z, 1); v.w += __shfl_xor_sync(0xffffffffu, v.w, 1);
+        }
+    };
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
     for (uint32_t s0 = 0; s0 < K; s0 += 3) {
         uint32_t pos[3];
@@ -547,11 +558,11 @@ __global__ void __launch_bounds__(256) combine_batched_kernel(const float *__res
         float4 sum[3];
 #pragma unroll
         for (int j = 0; j < 3; ++j) {
-            pos[j] = s0 + j < K ? inverse[tkn * K + s0 + j] : 0xffffffffu;
-            w[j] = s0 + j < K ? weights[tkn * K + s0 + j] : 0.f;
+            pos[j] = live && s0 + j < K ? inverse[tkn * K + s0 + j] : 0xffffffffu;
+            w[j] = live && s0 + j < K ? weights[tkn * K + s0 + j] : 0.f;
             sum[j] = make_float4(0.f, 0.f, 0.f, 0.f);
         }
-        for (uint32_t p0 = 0; p0 < parts; p0 += kChunk) {
+        for (uint32_t p0 = half * kChunk; p0 < parts; p0 += SPLIT * kChunk) {
             float4 v[3][kChunk];
 #pragma unroll
             for (int j = 0; j < 3; ++j)
@@ -566,6 +577,7 @@ __global__ void __launch_bounds__(256) combine_batched_kernel(const float *__res
         }
 #pragma unroll
         for (int j = 0; j < 3; ++j) {
+            meet(sum[j]);
             if (pos[j] == 0xffffffffu) continue;
             acc[0] = fmaf(w[j], sum[j].x, acc[0]); acc[1] = fmaf(w[j], sum[j].y, acc[1]);
             acc[2] = fmaf(w[j], sum[j].z, acc[2]); acc[3] = fmaf(w[j], sum[j].w, acc[3]);
@@ -573,13 +585,16 @@ __global__ void __launch_bounds__(256) combine_batched_kernel(const float *__res
     }
     // the shared MLP's parts (the order of the CPU path: routed slots, then shared, then residual)
     float4 ssum = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (uint32_t p0 = 0; p0 < (uint32_t)kBtSharedHalves * parts; p0 += kChunk) {
+    for (uint32_t p0 = half * kChunk; p0 < (uint32_t)kBtSharedHalves * parts; p0 += SPLIT * kChunk) {
         float4 sh[kChunk];
 #pragma unroll
-        for (int p = 0; p < kChunk; ++p) sh[p] = *reinterpret_cast<const float4 *>(shared_part + (p0 + p) * shared_stride + (size_t)tkn * H + c);
+        for (int p = 0; p < kChunk; ++p)
+            sh[p] = live ? *reinterpret_cast<const float4 *>(shared_part + (p0 + p) * shared_stride + (size_t)tkn * H + c) : make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
         for (int p = 0; p < kChunk; ++p) { ssum.x += sh[p].x; ssum.y += sh[p].y; ssum.z += sh[p].z; ssum.w += sh[p].w; }
     }
+    meet(ssum);
+    if (!live || half != 0) return;
     acc[0] += ssum.x; acc[1] += ssum.y; acc[2] += ssum.z; acc[3] += ssum.w;
     if (residual) {
         const uint2 rv = *reinterpret_cast<const uint2 *>(residual + (size_t)tkn * H + c);
@@ -685,10 +700,15 @@ cudaError_t launch_batched_experts(const DLayer &L, const Scratch &S, uint32_t n
 cudaError_t launch_batched_combine(const DLayer &L, const Scratch &S, const __half *residual, uint32_t n, uint8_t *scratch, __half *out,
                                    cudaStream_t st, uint64_t *launches) {
     const BatchedScratchLayout lay = decode_batched_scratch(n, L.K);
-    const size_t work = (size_t)n * (L.H / 4);
-    combine_batched_kernel<<<(unsigned)((work + 255) / 256), 256, 0, st>>>(
-        reinterpret_cast<const float *>(scratch + lay.routed_part), reinterpret_cast<const float *>(scratch + lay.shared_part), residual,
-        S.inverse, S.top_weights, n, L.H, L.K, (uint32_t)(kSlRoutedPerSlot / bt_slices_for(n)), out);
+    const uint32_t parts = (uint32_t)(kSlRoutedPerSlot / bt_slices_for(n));
+    const float *rp = reinterpret_cast<const float *>(scratch + lay.routed_part), *sp = reinterpret_cast<const float *>(scratch + lay.shared_part);
+    if (parts > 7) {
+        const size_t work = (size_t)n * (L.H / 4) * 2;
+        combine_batched_kernel<2><<<(unsigned)((work + 255) / 256), 256, 0, st>>>(rp, sp, residual, S.inverse, S.top_weights, n, L.H, L.K, parts, out);
+    } else {
+        const size_t work = (size_t)n * (L.H / 4);
+        combine_batched_kernel<1><<<(unsigned)((work + 255) / 256), 256, 0, st>>>(rp, sp, residual, S.inverse, S.top_weights, n, L.H, L.K, parts, out);
+    }
     ++*launches;
     return cudaGetLastError();
 }
