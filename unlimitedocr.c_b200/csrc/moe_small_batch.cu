@@ -15,6 +15,7 @@
 // Rounding contract as the reference's GPU kernels (src/backend/metal/kernels/decode_gemv_q4.metal:34-57,
 // :138-224): fp16 activations, scale applied per group partial, fp16 `mid`, f32 routed sum.
 #include "moe_common.cuh"
+#include "moe_decode_units.cuh"
 
 namespace uocr {
 
@@ -419,12 +420,189 @@ lm_head_argmax_kernel(const __half *__restrict__ hidden, uint32_t n, uint32_t H,
     if (tid == 0) *ticket = 0;               // ready for the next call on the stream
 }
 
+// ---- LM head on the integer tensor-core path (Q4_0 / Q8_0) ---------------------------------------------------------
+// The scalar kernel above spends ~190 instructions per vocabulary row; this one spends ~18.  A warp takes 16 consecutive
+// rows; lane (g, t) of it loads, for each 64-wide group, its 16 bytes (Q8_0; 8 in Q4_0) of rows g and g + 8 straight from
+// the row-major matrix, and two m16n8k32 integer MMAs multiply the group's levels with the activations in
+// block-floating-point form (group_limbs16(): per group a power-of-two scale and 15-bit mantissas split into a low and a
+// high signed byte).  The MMA's eight N columns are (token, limb) for four tokens, so lane (g, t) ends up with the low-
+// and the high-limb sums of rows g, g + 8 for token t and finishes them with one FMA per row and group:
+// (lo + 256 hi) * weight scale * activation scale.  Loads run one batch of four groups ahead of the MMAs, across row
+// blocks.  The argmax bookkeeping and the ticket are those of the scalar kernel.
+constexpr int kLmiThreads = 256, kLmiBatch = 4, kLmiPad = 64, kLmiTokens = 4;
+
+template <int QT> struct LmiFrag;
+template <> struct LmiFrag<UOCR_QT_Q8> { using T = uint4; static constexpr int kGroupBytes = 64; };
+template <> struct LmiFrag<UOCR_QT_Q4> { using T = uint2; static constexpr int kGroupBytes = 32; };
+
+template <int QT>
+struct LmiBatch {
+    typename LmiFrag<QT>::T w[2][kLmiBatch];     // [row g | row g + 8][group of the batch]
+    uint2 s[2];                                  // the four fp16 scales of each row
+};
+
+template <int QT>
+__device__ __forceinline__ void lmi_load(LmiBatch<QT> &B, const uint8_t *__restrict__ w, const __half *__restrict__ sc, uint32_t row_bytes,
+                                         uint32_t groups, uint32_t vocab, uint32_t blk, uint32_t b, int g, int t) {
+    using T = typename LmiFrag<QT>::T;
+    const uint32_t r0 = min(blk * 16u + (uint32_t)g, vocab - 1u), r1 = min(blk * 16u + 8u + (uint32_t)g, vocab - 1u);
+    const size_t col = (size_t)b * kLmiBatch * LmiFrag<QT>::kGroupBytes + (size_t)t * sizeof(T);
+    const uint8_t *p0 = w + (size_t)r0 * row_bytes + col, *p1 = w + (size_t)r1 * row_bytes + col;
+#pragma unroll
+    for (int i = 0; i < kLmiBatch; ++i) {
+        B.w[0][i] = __ldcs(reinterpret_cast<const T *>(p0 + i * LmiFrag<QT>::kGroupBytes));
+        B.w[1][i] = __ldcs(reinterpret_cast<const T *>(p1 + i * LmiFrag<QT>::kGroupBytes));
+    }
+    B.s[0] = __ldg(reinterpret_cast<const uint2 *>(sc + (size_t)r0 * groups + b * kLmiBatch));
+    B.s[1] = __ldg(reinterpret_cast<const uint2 *>(sc + (size_t)r1 * groups + b * kLmiBatch));
+}
+
+__device__ __forceinline__ void lmi_group(int (&c)[4], const uint4 &lo, const uint4 &hi, const uint4 &xb) {           // Q8_0
+    imma_s8(c, lo.x, hi.x, lo.y, hi.y, xb.x, xb.y);
+    imma_s8(c, lo.z, hi.z, lo.w, hi.w, xb.z, xb.w);
+}
+__device__ __forceinline__ void lmi_group(int (&c)[4], const uint2 &lo, const uint2 &hi, const uint4 &xb) {           // Q4_0
+    imma_s8(c, q4_lo16(lo.x), q4_lo16(hi.x), q4_lo16(lo.y), q4_lo16(hi.y), xb.x, xb.y);
+    imma_s8(c, q4_hi16(lo.x), q4_hi16(hi.x), q4_hi16(lo.y), q4_hi16(hi.y), xb.z, xb.w);
+}
+
+template <int QT>
+__global__ void __launch_bounds__(kLmiThreads, 2)
+lm_head_imma_kernel(const __half *__restrict__ hidden, uint32_t n, uint32_t H, const uint8_t *__restrict__ w, const __half *__restrict__ sc,
+                    uint32_t vocab, uint32_t row_bytes, float *__restrict__ part_scores, uint32_t *__restrict__ part_ids,
+                    uint32_t *__restrict__ ticket, uint32_t *__restrict__ ids_out, float *__restrict__ scores_out) {
+    constexpr int M = kLmiTokens;
+    extern __shared__ __align__(16) uint8_t lmi_smem[];
+    __shared__ float s_score[kLmiThreads / 32][M];
+    __shared__ uint32_t s_id[kLmiThreads / 32][M];
+    __shared__ bool s_last;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
+    const uint32_t groups = H / UOCR_GROUP, stride = H + kLmiPad;
+    uint8_t *xl = lmi_smem;                                                  // [2 * token + limb][H + pad] signed bytes
+    float *xsc = reinterpret_cast<float *>(lmi_smem + 2 * M * stride);       // [token][group]
+    // the activations in limb form: 16 lanes per (token, group); word p of a group holds the four columns the MMAs'
+    // B registers want there (limb_column())
+    for (uint32_t task = (uint32_t)tid >> 4; task < (uint32_t)M * groups; task += kLmiThreads / 16) {
+        const uint32_t tok = task / groups, G = task % groups;
+        const int p = lane & 15;
+        float x[4] = {0.f, 0.f, 0.f, 0.f};
+        if (tok < n) {
+            const uint2 raw = *reinterpret_cast<const uint2 *>(hidden + (size_t)tok * H + G * UOCR_GROUP + limb_column<QT>(p));
+            const float2 f01 = __half22float2(*reinterpret_cast<const __half2 *>(&raw.x));
+            const float2 f23 = __half22float2(*reinterpret_cast<const __half2 *>(&raw.y));
+            x[0] = f01.x; x[1] = f01.y; x[2] = f23.x; x[3] = f23.y;
+        }
+        const GroupLimbs L = group_limbs16(x, 0xffffffffu);
+        *reinterpret_cast<uint32_t *>(xl + (2 * tok) * stride + G * UOCR_GROUP + 4 * p) = L.lo;
+        *reinterpret_cast<uint32_t *>(xl + (2 * tok + 1) * stride + G * UOCR_GROUP + 4 * p) = L.hi;
+        if (p == 0) xsc[tok * groups + G] = QT == UOCR_QT_Q4 ? L.scale * kQ4LevelScale : L.scale;
+    }
+    __syncthreads();
+    float best = 0.f;                      // of token t, over the rows this lane has seen
+    uint32_t best_id = 0xffffffffu;
+    const uint32_t nblk = (vocab + 15u) / 16u, nb = groups / kLmiBatch;
+    const uint32_t first = (uint32_t)((uint64_t)blockIdx.x * nblk / gridDim.x), last = (uint32_t)((uint64_t)(blockIdx.x + 1) * nblk / gridDim.x);
+    const uint8_t *xrow = xl + (size_t)g * stride + 16 * t;
+    const float *xs_t = xsc + (size_t)t * groups;
+    LmiBatch<QT> cur, nxt;
+    uint32_t blk = first + (uint32_t)warp;
+    if (blk < last) lmi_load<QT>(cur, w, sc, row_bytes, groups, vocab, blk, 0, g, t);
+    while (blk < last) {
+        float acc0 = 0.f, acc1 = 0.f;
+#pragma unroll 1
+        for (uint32_t b = 0; b < nb; ++b) {
+            const bool wrap = b + 1 == nb;
+            const uint32_t pblk = wrap ? blk + kLmiThreads / 32 : blk, pb = wrap ? 0u : b + 1;
+            if (pblk < last) lmi_load<QT>(nxt, w, sc, row_bytes, groups, vocab, pblk, pb, g, t);
+            const float4 xs4 = *reinterpret_cast<const float4 *>(xs_t + b * kLmiBatch);
+            const float xsv[kLmiBatch] = {xs4.x, xs4.y, xs4.z, xs4.w};
+            const __half *h0 = reinterpret_cast<const __half *>(&cur.s[0]), *h1 = reinterpret_cast<const __half *>(&cur.s[1]);
+#pragma unroll
+            for (int i = 0; i < kLmiBatch; ++i) {
+                const uint4 xb = *reinterpret_cast<const uint4 *>(xrow + (size_t)(b * kLmiBatch + i) * UOCR_GROUP);
+                int c[4] = {0, 0, 0, 0};
+                lmi_group(c, cur.w[0][i], cur.w[1][i], xb);
+                acc0 = fmaf((float)(c[0] + c[1] * 256), __half2float(h0[i]) * xsv[i], acc0);
+                acc1 = fmaf((float)(c[2] + c[3] * 256), __half2float(h1[i]) * xsv[i], acc1);
+            }
+            cur = nxt;
+        }
+        const uint32_t r0 = blk * 16u + (uint32_t)g, r1 = r0 + 8u;
+        if (r0 < vocab && acc0 == acc0 && lm_better(acc0, r0, best, best_id)) { best = acc0; best_id = r0; }
+        if (r1 < vocab && acc1 == acc1 && lm_better(acc1, r1, best, best_id)) { best = acc1; best_id = r1; }
+        blk += kLmiThreads / 32;
+    }
+    // the eight row lanes of a token
+#pragma unroll
+    for (int o = 4; o < 32; o <<= 1) {
+        const float s2 = __shfl_xor_sync(0xffffffffu, best, o);
+        const uint32_t i2 = __shfl_xor_sync(0xffffffffu, best_id, o);
+        if (lm_better(s2, i2, best, best_id)) { best = s2; best_id = i2; }
+    }
+    if (lane < M) { s_score[warp][lane] = best; s_id[warp][lane] = best_id; }
+    __syncthreads();
+    if (tid < M) {
+        float bsc = 0.f;
+        uint32_t bi = 0xffffffffu;
+        for (int wv = 0; wv < kLmiThreads / 32; ++wv)
+            if (lm_better(s_score[wv][tid], s_id[wv][tid], bsc, bi)) { bsc = s_score[wv][tid]; bi = s_id[wv][tid]; }
+        part_scores[(size_t)blockIdx.x * M + tid] = bsc;
+        part_ids[(size_t)blockIdx.x * M + tid] = bi;
+    }
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) s_last = atomicAdd(ticket, 1u) == gridDim.x - 1;
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    if ((uint32_t)warp < n) {               // the last CTA: one warp per token scans every CTA's entry
+        float bsc = 0.f;
+        uint32_t bi = 0xffffffffu;
+        for (uint32_t c = lane; c < gridDim.x; c += 32) {
+            const float s2 = __ldcg(part_scores + (size_t)c * M + warp);
+            const uint32_t i2 = __ldcg(part_ids + (size_t)c * M + warp);
+            if (lm_better(s2, i2, bsc, bi)) { bsc = s2; bi = i2; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float s2 = __shfl_xor_sync(0xffffffffu, bsc, o);
+            const uint32_t i2 = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (lm_better(s2, i2, bsc, bi)) { bsc = s2; bi = i2; }
+        }
+        if (lane == 0) {
+            ids_out[warp] = bi;
+            if (scores_out) scores_out[warp] = bi == 0xffffffffu ? -INFINITY : bsc;
+        }
+    }
+    if (tid == 0) *ticket = 0;
+}
+
+static bool lm_head_imma_ok(const DMatrix &m) {
+    const size_t smem = (size_t)2 * kLmiTokens * (m.cols + kLmiPad) + (size_t)kLmiTokens * (m.cols / UOCR_GROUP) * sizeof(float);
+    return (m.qtype == UOCR_QT_Q4 || m.qtype == UOCR_QT_Q8) && m.s != nullptr && m.cols % (UOCR_GROUP * kLmiBatch) == 0 &&
+           smem <= 48 * 1024 && m.rows >= 16 && m.row_bytes % 16 == 0;
+}
+
 uint32_t lm_head_max_tokens() { return kMaxM; }
 
 cudaError_t launch_lm_head_argmax(const DMatrix &m, const __half *hidden, uint32_t n, uint32_t grid, float *part_scores,
                                   uint32_t *part_ids, uint32_t *ticket, uint32_t *ids_out, float *scores_out, cudaStream_t st,
                                   uint64_t *launches) {
-    if (n == 0 || n > (uint32_t)kMaxM || (size_t)kMaxM * m.cols * sizeof(float) > 48 * 1024) return cudaErrorInvalidValue;
+    if (n == 0 || n > (uint32_t)kMaxM) return cudaErrorInvalidValue;
+    if (lm_head_imma_ok(m)) {
+        // two CTAs per SM (the grid the scratch was sized for holds eight per SM)
+        const uint32_t cg = grid >= 4 ? grid / 4 : grid;
+        const size_t smem_i = (size_t)2 * kLmiTokens * (m.cols + kLmiPad) + (size_t)kLmiTokens * (m.cols / UOCR_GROUP) * sizeof(float);
+        if (m.qtype == UOCR_QT_Q4)
+            lm_head_imma_kernel<UOCR_QT_Q4><<<cg, kLmiThreads, smem_i, st>>>(hidden, n, m.cols, m.w, m.s, m.rows, m.row_bytes, part_scores,
+                                                                             part_ids, ticket, ids_out, scores_out);
+        else
+            lm_head_imma_kernel<UOCR_QT_Q8><<<cg, kLmiThreads, smem_i, st>>>(hidden, n, m.cols, m.w, m.s, m.rows, m.row_bytes, part_scores,
+                                                                             part_ids, ticket, ids_out, scores_out);
+        ++*launches;
+        return cudaGetLastError();
+    }
+    if ((size_t)kMaxM * m.cols * sizeof(float) > 48 * 1024) return cudaErrorInvalidValue;
     const size_t smem = sizeof(float) * (n <= 1 ? 1 : (n == 2 ? 2 : kMaxM)) * m.cols;
 #define UOCR_LM_LAUNCH(MM)                                                                                                       \
     UOCR_QT_SWITCH(m.qtype, (lm_head_argmax_kernel<QT, MM><<<grid, kLmThreads, smem, st>>>(hidden, n, m.cols, m.w, m.s, m.rows, m.row_bytes, \
