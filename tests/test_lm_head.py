@@ -58,6 +58,23 @@ def test_full_vocabulary_argmax(pkg, port, full_weights, qname, n):
         assert abs(got_scores[t] - logits[t, got_ids[t]]) <= 1e-4 * max(1.0, abs(want_scores[t]))
 
 
+@pytest.mark.parametrize("qname", ["q4_0", "q8_0"])
+@pytest.mark.parametrize("V,Hc", [(1000, 1280), (4096, 1280), (64, 256), (2384, 2048)])
+def test_other_shapes(pkg, port, qname, V, Hc):
+    """1000 rows (not a multiple of 16) go through the row-per-lane-group kernel, the others through the bulk-copy ring:
+    with fewer 16-row blocks than CTAs (64 rows), one or two blocks per CTA, and the widest hidden size."""
+    rng = np.random.default_rng(540 + V)
+    m = quant.make_matrix(quant.QTYPE_BY_NAME[qname], rng.standard_normal((V, Hc), dtype=np.float32) * 0.05)
+    x = quant.synth_activations(rng, 3, Hc)
+    got_ids, got_scores = run(pkg, m, x)
+    want_ids, want_scores, logits = port.lm_head_argmax(m, x, want_logits=True)
+    for t in range(3):
+        if got_ids[t] != want_ids[t]:
+            top2 = np.sort(logits[t])[-2:]
+            assert abs(top2[1] - top2[0]) <= 2e-5 * max(1.0, abs(top2[1])), (t, got_ids[t], want_ids[t], top2)
+        assert abs(got_scores[t] - logits[t, got_ids[t]]) <= 1e-4 * max(1.0, abs(want_scores[t]))
+
+
 def test_ties_go_to_the_lowest_id_and_nan_rows_are_skipped(pkg, port):
     rng = np.random.default_rng(520)
     w = rng.standard_normal((4096, H), dtype=np.float32) * 0.02

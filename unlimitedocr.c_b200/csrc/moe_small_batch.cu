@@ -14,8 +14,11 @@
 //
 // Rounding contract as the reference's GPU kernels (src/backend/metal/kernels/decode_gemv_q4.metal:34-57,
 // :138-224): fp16 activations, scale applied per group partial, fp16 `mid`, f32 routed sum.
+#include <stdlib.h>
+
 #include "moe_common.cuh"
 #include "moe_decode_units.cuh"
+#include "moe_sync.cuh"
 
 namespace uocr {
 
@@ -421,41 +424,14 @@ lm_head_argmax_kernel(const __half *__restrict__ hidden, uint32_t n, uint32_t H,
 }
 
 // ---- LM head on the integer tensor-core path (Q4_0 / Q8_0) ---------------------------------------------------------
-// The scalar kernel above spends ~190 instructions per vocabulary row; this one spends ~18.  A warp takes 16 consecutive
-// rows; lane (g, t) of it loads, for each 64-wide group, its 16 bytes (Q8_0; 8 in Q4_0) of rows g and g + 8 straight from
-// the row-major matrix, and two m16n8k32 integer MMAs multiply the group's levels with the activations in
-// block-floating-point form (group_limbs16(): per group a power-of-two scale and 15-bit mantissas split into a low and a
-// high signed byte).  The MMA's eight N columns are (token, limb) for four tokens, so lane (g, t) ends up with the low-
-// and the high-limb sums of rows g, g + 8 for token t and finishes them with one FMA per row and group:
-// (lo + 256 hi) * weight scale * activation scale.  Loads run one batch of four groups ahead of the MMAs, across row
-// blocks.  The argmax bookkeeping and the ticket are those of the scalar kernel.
-constexpr int kLmiThreads = 256, kLmiBatch = 4, kLmiPad = 64, kLmiTokens = 4;
-
-template <int QT> struct LmiFrag;
-template <> struct LmiFrag<UOCR_QT_Q8> { using T = uint4; static constexpr int kGroupBytes = 64; };
-template <> struct LmiFrag<UOCR_QT_Q4> { using T = uint2; static constexpr int kGroupBytes = 32; };
-
-template <int QT>
-struct LmiBatch {
-    typename LmiFrag<QT>::T w[2][kLmiBatch];     // [row g | row g + 8][group of the batch]
-    uint2 s[2];                                  // the four fp16 scales of each row
-};
-
-template <int QT>
-__device__ __forceinline__ void lmi_load(LmiBatch<QT> &B, const uint8_t *__restrict__ w, const __half *__restrict__ sc, uint32_t row_bytes,
-                                         uint32_t groups, uint32_t vocab, uint32_t blk, uint32_t b, int g, int t) {
-    using T = typename LmiFrag<QT>::T;
-    const uint32_t r0 = min(blk * 16u + (uint32_t)g, vocab - 1u), r1 = min(blk * 16u + 8u + (uint32_t)g, vocab - 1u);
-    const size_t col = (size_t)b * kLmiBatch * LmiFrag<QT>::kGroupBytes + (size_t)t * sizeof(T);
-    const uint8_t *p0 = w + (size_t)r0 * row_bytes + col, *p1 = w + (size_t)r1 * row_bytes + col;
-#pragma unroll
-    for (int i = 0; i < kLmiBatch; ++i) {
-        B.w[0][i] = __ldcs(reinterpret_cast<const T *>(p0 + i * LmiFrag<QT>::kGroupBytes));
-        B.w[1][i] = __ldcs(reinterpret_cast<const T *>(p1 + i * LmiFrag<QT>::kGroupBytes));
-    }
-    B.s[0] = __ldg(reinterpret_cast<const uint2 *>(sc + (size_t)r0 * groups + b * kLmiBatch));
-    B.s[1] = __ldg(reinterpret_cast<const uint2 *>(sc + (size_t)r1 * groups + b * kLmiBatch));
-}
+// The scalar kernel above spends ~190 instructions per vocabulary row; this one spends a tenth of that.  A warp takes 16
+// consecutive rows; lane (g, t) of it reads, for each 64-wide group, its 16 bytes (Q8_0; 8 in Q4_0) of two of the rows,
+// and two m16n8k32 integer MMAs multiply the group's levels with the activations in block-floating-point form
+// (group_limbs16(): per group a power-of-two scale and 15-bit mantissas split into a low and a high signed byte).  The
+// MMA's eight N columns are (token, limb) for four tokens, so lane (g, t) ends up with the low- and the high-limb sums of
+// its two rows for token t and finishes them with one FMA per row and group: (lo + 256 hi) * weight scale * activation
+// scale.  The argmax bookkeeping and the ticket are those of the scalar kernel.
+constexpr int kLmiBatch = 4, kLmiPad = 64, kLmiTokens = 4;
 
 __device__ __forceinline__ void lmi_group(int (&c)[4], const uint4 &lo, const uint4 &hi, const uint4 &xb) {           // Q8_0
     imma_s8(c, lo.x, hi.x, lo.y, hi.y, xb.x, xb.y);
@@ -466,85 +442,177 @@ __device__ __forceinline__ void lmi_group(int (&c)[4], const uint2 &lo, const ui
     imma_s8(c, q4_hi16(lo.x), q4_hi16(hi.x), q4_hi16(lo.y), q4_hi16(hi.y), xb.z, xb.w);
 }
 
+// The rows come in by bulk copies.  One warp only issues them: whole 16-row blocks (Q8_0: 20 KB, contiguous in the
+// row-major matrix) into a ring of stages in shared memory, from which eight consumer warps, taking the blocks in turn,
+// read their MMA fragments: ~170 KB per SM are on their way at any time without a register or an instruction slot of
+// the consumers.  (The same MMAs fed by per-lane global loads, one batch of four groups ahead, spent ~50 instructions
+// per group on addresses, predicates and register copies and ran 10 % slower.)
+//   * A bulk copy costs the SM's copy engine ~65 ns whatever its size (measured: a ring of 17 copies per block ran at
+//     56 ns per copy, one of 5 per block at 72 ns), so a block arrives as TWO copies of eight rows, and the scales of
+//     eight consecutive blocks (one per consumer warp) as one copy into a ring of their own.
+//   * The second copy of a block lands one group further along the banks than the first, and MMA row g of a block is
+//     matrix row 8 (g % 2) + g / 2 (+ 4 for the upper half): the two values of g that share an LDS.128 in Q8_0 read from
+//     different copies (no bank conflict although every row starts at a multiple of 128 bytes); in Q4_0, where four
+//     values of g share an LDS.64, a two-way conflict remains.
+//   * The number of stages is a multiple of the number of consumer warps: every stage is then filled for, and emptied
+//     by, one warp only, in order.  With any other count a warp could reach its wait on a stage while the copy of the
+//     block BEFORE the awaited one (another warp's) is still on its way; a parity wait cannot tell that phase from the
+//     awaited one and would let the warp through.  Every warp passes through every stage of the scale ring.
+constexpr int kLmrConsumers = 8, kLmrThreads = (kLmrConsumers + 1) * 32, kLmrMaxStages = 16, kLmrScaleStages = 4;
+constexpr size_t kLmrSmemLimit = 231000;     // dynamic shared memory of the kernel; the rest of the SM's 227 KB is static data
+
+template <int QT> struct LmrCfg;
+template <> struct LmrCfg<UOCR_QT_Q8> { using T = uint4; static constexpr int kGroupBytes = 64; };
+template <> struct LmrCfg<UOCR_QT_Q4> { using T = uint2; static constexpr int kGroupBytes = 32; };
+
+struct LmrLayout {
+    uint32_t region, sc_block, sc_stage, stage_bytes, fixed_bytes;
+};
 template <int QT>
-__global__ void __launch_bounds__(kLmiThreads, 2)
-lm_head_imma_kernel(const __half *__restrict__ hidden, uint32_t n, uint32_t H, const uint8_t *__restrict__ w, const __half *__restrict__ sc,
-                    uint32_t vocab, uint32_t row_bytes, float *__restrict__ part_scores, uint32_t *__restrict__ part_ids,
+__host__ __device__ __forceinline__ LmrLayout lmr_layout(uint32_t H, uint32_t row_bytes) {
+    LmrLayout L;
+    const uint32_t groups = H / UOCR_GROUP;
+    L.region = 8u * row_bytes + 128u;                              // eight rows and room for the second copy's shift along the banks
+    L.sc_block = 16u * groups * 2u;                                // the fp16 scales of one block
+    L.sc_stage = kLmrConsumers * L.sc_block;
+    L.stage_bytes = 2u * L.region;
+    L.fixed_bytes = kLmrScaleStages * L.sc_stage + 2u * kLmiTokens * (H + kLmiPad) + kLmiTokens * groups * 4u +
+                    2u * (kLmrMaxStages + kLmrScaleStages) * 8u + 16u;
+    return L;
+}
+
+template <int QT>
+__global__ void __launch_bounds__(kLmrThreads, 1)
+lm_head_ring_kernel(const __half *__restrict__ hidden, uint32_t n, uint32_t H, const uint8_t *__restrict__ w, const __half *__restrict__ sc,
+                    uint32_t vocab, uint32_t row_bytes, uint32_t stages, float *__restrict__ part_scores, uint32_t *__restrict__ part_ids,
                     uint32_t *__restrict__ ticket, uint32_t *__restrict__ ids_out, float *__restrict__ scores_out) {
-    constexpr int M = kLmiTokens;
-    extern __shared__ __align__(16) uint8_t lmi_smem[];
-    __shared__ float s_score[kLmiThreads / 32][M];
-    __shared__ uint32_t s_id[kLmiThreads / 32][M];
+    using T = typename LmrCfg<QT>::T;
+    constexpr int M = kLmiTokens, kGroupBytes = LmrCfg<QT>::kGroupBytes;
+    extern __shared__ __align__(128) uint8_t lmr_smem[];
+    __shared__ float s_score[kLmrConsumers][M];
+    __shared__ uint32_t s_id[kLmrConsumers][M];
     __shared__ bool s_last;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
     const uint32_t groups = H / UOCR_GROUP, stride = H + kLmiPad;
-    uint8_t *xl = lmi_smem;                                                  // [2 * token + limb][H + pad] signed bytes
-    float *xsc = reinterpret_cast<float *>(lmi_smem + 2 * M * stride);       // [token][group]
-    // the activations in limb form: 16 lanes per (token, group); word p of a group holds the four columns the MMAs'
-    // B registers want there (limb_column())
-    for (uint32_t task = (uint32_t)tid >> 4; task < (uint32_t)M * groups; task += kLmiThreads / 16) {
-        const uint32_t tok = task / groups, G = task % groups;
-        const int p = lane & 15;
-        float x[4] = {0.f, 0.f, 0.f, 0.f};
-        if (tok < n) {
-            const uint2 raw = *reinterpret_cast<const uint2 *>(hidden + (size_t)tok * H + G * UOCR_GROUP + limb_column<QT>(p));
-            const float2 f01 = __half22float2(*reinterpret_cast<const __half2 *>(&raw.x));
-            const float2 f23 = __half22float2(*reinterpret_cast<const __half2 *>(&raw.y));
-            x[0] = f01.x; x[1] = f01.y; x[2] = f23.x; x[3] = f23.y;
-        }
-        const GroupLimbs L = group_limbs16(x, 0xffffffffu);
-        *reinterpret_cast<uint32_t *>(xl + (2 * tok) * stride + G * UOCR_GROUP + 4 * p) = L.lo;
-        *reinterpret_cast<uint32_t *>(xl + (2 * tok + 1) * stride + G * UOCR_GROUP + 4 * p) = L.hi;
-        if (p == 0) xsc[tok * groups + G] = QT == UOCR_QT_Q4 ? L.scale * kQ4LevelScale : L.scale;
+    const LmrLayout L = lmr_layout<QT>(H, row_bytes);
+    uint8_t *sc_ring = lmr_smem + (size_t)stages * L.stage_bytes;            // [scale stage][block of the round][16 rows][groups] fp16
+    uint8_t *xl = sc_ring + kLmrScaleStages * L.sc_stage;                    // [2 * token + limb][H + pad] signed bytes
+    float *xsc = reinterpret_cast<float *>(xl + 2 * M * stride);             // [token][group]
+    uint64_t *full = reinterpret_cast<uint64_t *>(xsc + M * groups), *empty = full + kLmrMaxStages;
+    uint64_t *sc_full = empty + kLmrMaxStages, *sc_empty = sc_full + kLmrScaleStages;
+    int *s_flag = reinterpret_cast<int *>(sc_empty + kLmrScaleStages);
+    uint32_t *status = ticket + 1;           // a copy that never arrived leaves a bit here; the call then reports no token
+    if (tid == 0) {
+        for (uint32_t i = 0; i < stages; ++i) { mbar_init(&full[i], 1); mbar_init(&empty[i], 1); }
+        for (int i = 0; i < kLmrScaleStages; ++i) { mbar_init(&sc_full[i], 1); mbar_init(&sc_empty[i], kLmrConsumers); }
+        s_flag[0] = 0; s_flag[1] = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
+    const uint32_t nblk = vocab / 16u;
+    const uint32_t first = (uint32_t)((uint64_t)blockIdx.x * nblk / gridDim.x), last = (uint32_t)((uint64_t)(blockIdx.x + 1) * nblk / gridDim.x);
+    const uint32_t count = last - first;
     float best = 0.f;                      // of token t, over the rows this lane has seen
     uint32_t best_id = 0xffffffffu;
-    const uint32_t nblk = (vocab + 15u) / 16u, nb = groups / kLmiBatch;
-    const uint32_t first = (uint32_t)((uint64_t)blockIdx.x * nblk / gridDim.x), last = (uint32_t)((uint64_t)(blockIdx.x + 1) * nblk / gridDim.x);
-    const uint8_t *xrow = xl + (size_t)g * stride + 16 * t;
-    const float *xs_t = xsc + (size_t)t * groups;
-    LmiBatch<QT> cur, nxt;
-    uint32_t blk = first + (uint32_t)warp;
-    if (blk < last) lmi_load<QT>(cur, w, sc, row_bytes, groups, vocab, blk, 0, g, t);
-    while (blk < last) {
-        float acc0 = 0.f, acc1 = 0.f;
-#pragma unroll 1
-        for (uint32_t b = 0; b < nb; ++b) {
-            const bool wrap = b + 1 == nb;
-            const uint32_t pblk = wrap ? blk + kLmiThreads / 32 : blk, pb = wrap ? 0u : b + 1;
-            if (pblk < last) lmi_load<QT>(nxt, w, sc, row_bytes, groups, vocab, pblk, pb, g, t);
-            const float4 xs4 = *reinterpret_cast<const float4 *>(xs_t + b * kLmiBatch);
-            const float xsv[kLmiBatch] = {xs4.x, xs4.y, xs4.z, xs4.w};
-            const __half *h0 = reinterpret_cast<const __half *>(&cur.s[0]), *h1 = reinterpret_cast<const __half *>(&cur.s[1]);
-#pragma unroll
-            for (int i = 0; i < kLmiBatch; ++i) {
-                const uint4 xb = *reinterpret_cast<const uint4 *>(xrow + (size_t)(b * kLmiBatch + i) * UOCR_GROUP);
-                int c[4] = {0, 0, 0, 0};
-                lmi_group(c, cur.w[0][i], cur.w[1][i], xb);
-                acc0 = fmaf((float)(c[0] + c[1] * 256), __half2float(h0[i]) * xsv[i], acc0);
-                acc1 = fmaf((float)(c[2] + c[3] * 256), __half2float(h1[i]) * xsv[i], acc1);
+
+    if (warp == kLmrConsumers) {
+        // ---- the copy warp: lanes 0, 1 copy eight rows each; lane 2 the scales of a round of eight blocks
+        uint32_t s = 0, round = 0;
+        for (uint32_t j = 0; j < count; ++j) {
+            const uint32_t blk = first + j;
+            if ((j & (kLmrConsumers - 1)) == 0u) {
+                const uint32_t r = j / kLmrConsumers, ss = r % kLmrScaleStages, sround = r / kLmrScaleStages;
+                if (sround > 0 && !mbar_wait(&sc_empty[ss], (sround - 1u) & 1u, status, s_flag)) break;
+                const uint32_t bytes = min((uint32_t)kLmrConsumers, count - j) * L.sc_block;
+                if (lane == 2) {
+                    mbar_expect_tx(&sc_full[ss], bytes);
+                    bulk_g2s(sc_ring + ss * L.sc_stage, sc + (size_t)blk * 16u * groups, bytes, &sc_full[ss]);
+                }
             }
-            cur = nxt;
+            if (round > 0 && !mbar_wait(&empty[s], (round - 1u) & 1u, status, s_flag)) break;
+            uint8_t *stage = lmr_smem + (size_t)s * L.stage_bytes;
+            if (lane == 0) mbar_expect_tx(&full[s], 16u * row_bytes);
+            __syncwarp();
+            if (lane < 2) bulk_g2s(stage + lane * (L.region + kGroupBytes), w + ((size_t)blk * 16u + 8u * lane) * row_bytes, 8u * row_bytes, &full[s]);
+            if (++s == stages) { s = 0; ++round; }
         }
-        const uint32_t r0 = blk * 16u + (uint32_t)g, r1 = r0 + 8u;
-        if (r0 < vocab && acc0 == acc0 && lm_better(acc0, r0, best, best_id)) { best = acc0; best_id = r0; }
-        if (r1 < vocab && acc1 == acc1 && lm_better(acc1, r1, best, best_id)) { best = acc1; best_id = r1; }
-        blk += kLmiThreads / 32;
-    }
-    // the eight row lanes of a token
+    } else {
+        // ---- consumers: first the activations in limb form, 16 lanes per (token, group); word p of a group holds the
+        // four columns the MMAs' B registers want there (limb_column())
+        for (uint32_t task = (uint32_t)tid >> 4; task < (uint32_t)M * groups; task += kLmrConsumers * 2) {
+            const uint32_t tok = task / groups, G = task % groups;
+            const int p = lane & 15;
+            float x[4] = {0.f, 0.f, 0.f, 0.f};
+            if (tok < n) {
+                const uint2 raw = *reinterpret_cast<const uint2 *>(hidden + (size_t)tok * H + G * UOCR_GROUP + limb_column<QT>(p));
+                const float2 f01 = __half22float2(*reinterpret_cast<const __half2 *>(&raw.x));
+                const float2 f23 = __half22float2(*reinterpret_cast<const __half2 *>(&raw.y));
+                x[0] = f01.x; x[1] = f01.y; x[2] = f23.x; x[3] = f23.y;
+            }
+            const GroupLimbs Lm = group_limbs16(x, 0xffffffffu);
+            *reinterpret_cast<uint32_t *>(xl + (2 * tok) * stride + G * UOCR_GROUP + 4 * p) = Lm.lo;
+            *reinterpret_cast<uint32_t *>(xl + (2 * tok + 1) * stride + G * UOCR_GROUP + 4 * p) = Lm.hi;
+            if (p == 0) xsc[tok * groups + G] = QT == UOCR_QT_Q4 ? Lm.scale * kQ4LevelScale : Lm.scale;
+        }
+        asm volatile("bar.sync 1, %0;" ::"n"(kLmrConsumers * 32) : "memory");
+        const uint8_t *xrow = xl + (size_t)g * stride + 16 * t;
+        const float *xs_t = xsc + (size_t)t * groups;
+        const uint32_t nb = groups / kLmiBatch;
+        // MMA rows g and g + 8 of a block are its matrix rows rho and rho + 4: copy g % 2, row g / 2 (+ 4) of the copy
+        const uint32_t cpy = (uint32_t)g & 1u, rho = 8u * cpy + ((uint32_t)g >> 1);
+        const uint32_t w_off = cpy * (L.region + kGroupBytes) + ((uint32_t)g >> 1) * row_bytes + (uint32_t)t * (uint32_t)sizeof(T);
+        const uint32_t s_off = (uint32_t)warp * L.sc_block + rho * groups * 2u;
+        uint32_t r = 0;                      // this warp's round: its block is j = warp + 8 r
+        for (uint32_t j = (uint32_t)warp; j < count; j += kLmrConsumers, ++r) {
+            const uint32_t s = j % stages, round = j / stages, ss = r % kLmrScaleStages;
+            bool got = mbar_wait(&sc_full[ss], (r / kLmrScaleStages) & 1u, status, s_flag);
+            got = mbar_wait(&full[s], round & 1u, status, s_flag) && got;
+            if (!got) break;
+            const uint8_t *stage = lmr_smem + (size_t)s * L.stage_bytes;
+            const uint8_t *w0p = stage + w_off, *w1p = w0p + 4u * row_bytes;
+            const uint8_t *s0p = sc_ring + ss * L.sc_stage + s_off, *s1p = s0p + 4u * groups * 2u;
+            float acc0 = 0.f, acc1 = 0.f;
+#pragma unroll 1
+            for (uint32_t b = 0; b < nb; ++b) {
+                const uint2 s0 = *reinterpret_cast<const uint2 *>(s0p + b * 8u), s1 = *reinterpret_cast<const uint2 *>(s1p + b * 8u);
+                const float4 xs4 = *reinterpret_cast<const float4 *>(xs_t + b * kLmiBatch);
+                const float xsv[kLmiBatch] = {xs4.x, xs4.y, xs4.z, xs4.w};
+                const __half *h0 = reinterpret_cast<const __half *>(&s0), *h1 = reinterpret_cast<const __half *>(&s1);
 #pragma unroll
-    for (int o = 4; o < 32; o <<= 1) {
-        const float s2 = __shfl_xor_sync(0xffffffffu, best, o);
-        const uint32_t i2 = __shfl_xor_sync(0xffffffffu, best_id, o);
-        if (lm_better(s2, i2, best, best_id)) { best = s2; best_id = i2; }
+                for (int i = 0; i < kLmiBatch; ++i) {
+                    const uint32_t G = b * kLmiBatch + i;
+                    const T w0 = *reinterpret_cast<const T *>(w0p + G * kGroupBytes);
+                    const T w1 = *reinterpret_cast<const T *>(w1p + G * kGroupBytes);
+                    const uint4 xb = *reinterpret_cast<const uint4 *>(xrow + (size_t)G * UOCR_GROUP);
+                    int c[4] = {0, 0, 0, 0};
+                    lmi_group(c, w0, w1, xb);
+                    acc0 = fmaf((float)(c[0] + c[1] * 256), __half2float(h0[i]) * xsv[i], acc0);
+                    acc1 = fmaf((float)(c[2] + c[3] * 256), __half2float(h1[i]) * xsv[i], acc1);
+                }
+            }
+            __syncwarp();
+            if (lane == 0) {
+                asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&empty[s])) : "memory");
+                asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&sc_empty[ss])) : "memory");
+            }
+            const uint32_t r0 = (first + j) * 16u + rho, r1 = r0 + 4u;
+            if (acc0 == acc0 && lm_better(acc0, r0, best, best_id)) { best = acc0; best_id = r0; }
+            if (acc1 == acc1 && lm_better(acc1, r1, best, best_id)) { best = acc1; best_id = r1; }
+        }
+        // the eight row lanes of a token
+#pragma unroll
+        for (int o = 4; o < 32; o <<= 1) {
+            const float s2 = __shfl_xor_sync(0xffffffffu, best, o);
+            const uint32_t i2 = __shfl_xor_sync(0xffffffffu, best_id, o);
+            if (lm_better(s2, i2, best, best_id)) { best = s2; best_id = i2; }
+        }
+        if (lane < M) { s_score[warp][lane] = best; s_id[warp][lane] = best_id; }
     }
-    if (lane < M) { s_score[warp][lane] = best; s_id[warp][lane] = best_id; }
     __syncthreads();
     if (tid < M) {
         float bsc = 0.f;
         uint32_t bi = 0xffffffffu;
-        for (int wv = 0; wv < kLmiThreads / 32; ++wv)
+        for (int wv = 0; wv < kLmrConsumers; ++wv)
             if (lm_better(s_score[wv][tid], s_id[wv][tid], bsc, bi)) { bsc = s_score[wv][tid]; bi = s_id[wv][tid]; }
         part_scores[(size_t)blockIdx.x * M + tid] = bsc;
         part_ids[(size_t)blockIdx.x * M + tid] = bi;
@@ -569,6 +637,7 @@ lm_head_imma_kernel(const __half *__restrict__ hidden, uint32_t n, uint32_t H, c
             const uint32_t i2 = __shfl_xor_sync(0xffffffffu, bi, o);
             if (lm_better(s2, i2, bsc, bi)) { bsc = s2; bi = i2; }
         }
+        if (ld_volatile_u32(status) != 0u) bi = 0xffffffffu;
         if (lane == 0) {
             ids_out[warp] = bi;
             if (scores_out) scores_out[warp] = bi == 0xffffffffu ? -INFINITY : bsc;
@@ -577,28 +646,44 @@ lm_head_imma_kernel(const __half *__restrict__ hidden, uint32_t n, uint32_t H, c
     if (tid == 0) *ticket = 0;
 }
 
-static bool lm_head_imma_ok(const DMatrix &m) {
-    const size_t smem = (size_t)2 * kLmiTokens * (m.cols + kLmiPad) + (size_t)kLmiTokens * (m.cols / UOCR_GROUP) * sizeof(float);
-    return (m.qtype == UOCR_QT_Q4 || m.qtype == UOCR_QT_Q8) && m.s != nullptr && m.cols % (UOCR_GROUP * kLmiBatch) == 0 &&
-           smem <= 48 * 1024 && m.rows >= 16 && m.row_bytes % 16 == 0;
+template <int QT>
+static uint32_t lmr_stages(const DMatrix &m) {
+    const LmrLayout L = lmr_layout<QT>(m.cols, m.row_bytes);
+    if (L.fixed_bytes + (size_t)kLmrConsumers * L.stage_bytes > kLmrSmemLimit) return 0;
+    const uint32_t s = (uint32_t)((kLmrSmemLimit - L.fixed_bytes) / L.stage_bytes);
+    return s >= (uint32_t)kLmrMaxStages ? (uint32_t)kLmrMaxStages : (uint32_t)kLmrConsumers;      // a multiple of the consumer warps
+}
+static bool lm_head_ring_ok(const DMatrix &m) {
+    if (!((m.qtype == UOCR_QT_Q4 || m.qtype == UOCR_QT_Q8) && m.s != nullptr && m.cols % (UOCR_GROUP * kLmiBatch) == 0 &&
+          m.rows >= 16 && m.rows % 16 == 0 && m.row_bytes % 128 == 0)) return false;
+    return (m.qtype == UOCR_QT_Q4 ? lmr_stages<UOCR_QT_Q4>(m) : lmr_stages<UOCR_QT_Q8>(m)) != 0;
 }
 
 uint32_t lm_head_max_tokens() { return kMaxM; }
+
+cudaError_t init_lm_head_kernels() {
+    cudaError_t err = cudaFuncSetAttribute(lm_head_ring_kernel<UOCR_QT_Q4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kLmrSmemLimit);
+    if (err == cudaSuccess) err = cudaFuncSetAttribute(lm_head_ring_kernel<UOCR_QT_Q8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kLmrSmemLimit);
+    return err;
+}
 
 cudaError_t launch_lm_head_argmax(const DMatrix &m, const __half *hidden, uint32_t n, uint32_t grid, float *part_scores,
                                   uint32_t *part_ids, uint32_t *ticket, uint32_t *ids_out, float *scores_out, cudaStream_t st,
                                   uint64_t *launches) {
     if (n == 0 || n > (uint32_t)kMaxM) return cudaErrorInvalidValue;
-    if (lm_head_imma_ok(m)) {
-        // two CTAs per SM (the grid the scratch was sized for holds eight per SM)
-        const uint32_t cg = grid >= 4 ? grid / 4 : grid;
-        const size_t smem_i = (size_t)2 * kLmiTokens * (m.cols + kLmiPad) + (size_t)kLmiTokens * (m.cols / UOCR_GROUP) * sizeof(float);
-        if (m.qtype == UOCR_QT_Q4)
-            lm_head_imma_kernel<UOCR_QT_Q4><<<cg, kLmiThreads, smem_i, st>>>(hidden, n, m.cols, m.w, m.s, m.rows, m.row_bytes, part_scores,
-                                                                             part_ids, ticket, ids_out, scores_out);
-        else
-            lm_head_imma_kernel<UOCR_QT_Q8><<<cg, kLmiThreads, smem_i, st>>>(hidden, n, m.cols, m.w, m.s, m.rows, m.row_bytes, part_scores,
-                                                                             part_ids, ticket, ids_out, scores_out);
+    if (lm_head_ring_ok(m)) {
+        const uint32_t cg = grid >= 8 ? grid / 8 : grid;          // one CTA per SM (the scratch was sized for eight per SM)
+        if (m.qtype == UOCR_QT_Q4) {
+            const uint32_t stg = lmr_stages<UOCR_QT_Q4>(m);
+            const LmrLayout L = lmr_layout<UOCR_QT_Q4>(m.cols, m.row_bytes);
+            lm_head_ring_kernel<UOCR_QT_Q4><<<cg, kLmrThreads, L.fixed_bytes + (size_t)stg * L.stage_bytes, st>>>(
+                hidden, n, m.cols, m.w, m.s, m.rows, m.row_bytes, stg, part_scores, part_ids, ticket, ids_out, scores_out);
+        } else {
+            const uint32_t stg = lmr_stages<UOCR_QT_Q8>(m);
+            const LmrLayout L = lmr_layout<UOCR_QT_Q8>(m.cols, m.row_bytes);
+            lm_head_ring_kernel<UOCR_QT_Q8><<<cg, kLmrThreads, L.fixed_bytes + (size_t)stg * L.stage_bytes, st>>>(
+                hidden, n, m.cols, m.w, m.s, m.rows, m.row_bytes, stg, part_scores, part_ids, ticket, ids_out, scores_out);
+        }
         ++*launches;
         return cudaGetLastError();
     }

@@ -15,6 +15,7 @@
 namespace uocr {
 cudaError_t init_router_kernels();
 cudaError_t init_small_batch_kernels();
+cudaError_t init_lm_head_kernels();
 bool dense_small_supported(uint32_t H, uint32_t S);
 uint32_t lm_head_max_tokens();
 cudaError_t launch_lm_head_argmax(const DMatrix &m, const __half *hidden, uint32_t n, uint32_t grid, float *part_scores,
@@ -340,7 +341,7 @@ extern "C" uocr_cuda_context *uocr_cuda_context_create(const char *resource_path
         (e = cudaMallocHost(&ctx->h_status, 256)) != cudaSuccess ||
         (e = cudaMalloc(&ctx->d_layers, kMaxLayers * sizeof(DLayer))) != cudaSuccess ||
         (e = cudaMallocHost(&ctx->h_seg, kSegSlots * 260 * sizeof(uint32_t))) != cudaSuccess ||
-        (e = uocr::init_router_kernels()) != cudaSuccess || (e = uocr::init_small_batch_kernels()) != cudaSuccess ||
+        (e = uocr::init_router_kernels()) != cudaSuccess || (e = uocr::init_small_batch_kernels()) != cudaSuccess || (e = uocr::init_lm_head_kernels()) != cudaSuccess ||
         (e = uocr::init_decode_kernels()) != cudaSuccess ||
         (e = uocr::init_decode_sliced_kernels()) != cudaSuccess || (e = uocr::init_decode_batched_kernels()) != cudaSuccess ||
         (e = uocr::init_gemm_kernels()) != cudaSuccess) {
