@@ -34,7 +34,7 @@ def build(force: bool = False) -> None:
     """Compile the checkers (``make -C oracle``); the reference build is skipped when its tree is absent."""
     if force or not PORT_LIB.exists() or PORT_LIB.stat().st_mtime < (HERE / "moe_oracle.c").stat().st_mtime:
         subprocess.run(["make", "-C", str(HERE), "libmoe_oracle.so"], check=True, capture_output=True)
-    if force or not REF_LIB.exists() or not (REF_LIB.parent / "libuocr_model_file.so").exists():
+    if force or not all((REF_LIB.parent / name).exists() for name in ("libuocr_cpu_ref.so", "libuocr_model_file.so", "libunlimitedocr_cuda.so")):
         subprocess.run(["make", "-C", str(HERE), "ref"], check=True, capture_output=True)
 
 
