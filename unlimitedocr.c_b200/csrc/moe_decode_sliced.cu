@@ -653,8 +653,9 @@ __global__ void __launch_bounds__(kSlThreads, 1) decode_sliced_kernel(const __gr
         if (last) {
             if (cta == 0) {
                 for (int h = tid; h < H; h += kSlThreads) prm.out[h] = s_x[h];
-                if (prm.host_status != nullptr) {       // ordered after this CTA saw every contribution of the launch
-                    __threadfence();
+                if (prm.host_status != nullptr) {       // ordered after this CTA saw every contribution of the launch, and (the
+                                                        // host may poll the word) after the result has reached host memory
+                    __threadfence_system();
                     __syncthreads();
                     if (tid == 0) *prm.host_status = ld_volatile_u32(status);
                 }

@@ -3,6 +3,7 @@
 // the forward path.
 #include "../../include/uocr_cuda_moe.h"
 
+#include <chrono>
 #include <cmath>
 #include <cstdarg>
 #include <cstdio>
@@ -209,6 +210,14 @@ static cudaEvent_t prof_event(uocr_cuda_context *ctx) {
 }
 
 // waits for the recorded spans and hands their durations to the engine's store
+static inline void cpu_relax() {        // inside a host spin: leave the core's resources to its sibling thread
+#if defined(__x86_64__) || defined(__i386__)
+    __builtin_ia32_pause();
+#elif defined(__aarch64__)
+    asm volatile("yield" ::: "memory");
+#endif
+}
+
 static void prof_flush(uocr_cuda_context *ctx) {
     for (auto &sp : ctx->prof_pending) {
         float ms = 0.f;
@@ -1325,7 +1334,17 @@ extern "C" int uocr_cuda_moe_stack_forward_host(uocr_cuda_context *ctx, uint32_t
         // the result and its status word straight into mapped host memory, so the call issues no copy at all
         *ctx->h_status = 0xffffffffu;
         if (!stack_forward(ctx, first, count, d_in, n, ctx->h_out_dev, error, error_size, h_hidden, ctx->h_status_dev)) return 0;
-        CU_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+        // The kernel writes the status word last, after the result (system-scope fence in between): the host polls it for
+        // up to a millisecond instead of sleeping in the driver, whose wake-up costs several microseconds of a 90 us
+        // step, and falls back to the stream wait (always taken when events have to be read back for the profile).
+        if (ctx->profile == nullptr) {
+            const auto t0 = std::chrono::steady_clock::now();
+            while (*(volatile uint32_t *)ctx->h_status == 0xffffffffu) {
+                if (std::chrono::steady_clock::now() - t0 > std::chrono::milliseconds(1)) break;
+                cpu_relax();
+            }
+        }
+        if (*(volatile uint32_t *)ctx->h_status == 0xffffffffu) CU_TRY(ctx, cudaStreamSynchronize(ctx->stream));
         prof_flush(ctx);
         if (*(volatile uint32_t *)ctx->h_status != 0) {       // the kernel gave up, or flagged something: read the device word
             if (!uocr_cuda_context_synchronize(ctx, error, error_size)) return 0;
