@@ -184,7 +184,7 @@ struct SlicedKnobs {
 };
 
 // Byte offsets inside the scratch region of the batched decode path.
-struct BatchedScratchLayout { size_t routed_part, shared_part, x_limbs, x_scales, total; };
+struct BatchedScratchLayout { size_t acc, x_limbs, x_scales, total; };
 
 // ---- launch interface (implemented in the kernel files, called by the host API) ----------
 struct LaunchCounter { uint64_t *count; };

@@ -8,16 +8,16 @@
 //    token instead of once per expert that uses it.  The CTA that finishes last builds the dispatch plan (a stable
 //    counting sort of the at most 384 pairs).
 // 2. decode_batched_kernel, weight-stationary on the slice-major "unit blobs" of the single-token decode kernel.  A
-//    work item is (expert, 16-token pass, two consecutive 64-wide slices of the intermediate dimension); the shared
+//    work item is (expert, 16-token pass, one or two consecutive 64-wide slices of the intermediate dimension); the shared
 //    MLP counts as two more experts that every token selects.  Items are listed hottest expert first and dealt
 //    round-robin to one CTA per SM.  Per item the pass's activation bytes are copied into shared memory, then per slice
 //    the 128 gate / up rows stream through a four-stage ring of bulk copies (one chunk = four quantisation groups) and
 //    are multiplied with up to 16 tokens (a token occupies two of the MMA's eight columns, so one MMA covers four
 //    tokens); the SwiGLU products never leave the SM: rounded to fp16, rewritten as bytes, multiplied with the
-//    slice's 64 columns of `down` (held in registers).  The slice's partial outputs go to a per-part buffer
-//    ([part][row][H], f32; the item's second slice adds to its first).
-// 3. combine_batched_kernel adds the parts in a fixed order, applies the routing weights in slot order, adds the shared
-//    MLP and the residual and rounds to fp16.  No atomics on data: results are bit-reproducible.
+//    slice's 64 columns of `down` (held in registers).  The products, weighted with the slot's routing weight, are
+//    added to the call's output sums: [token][H] 64-bit integers in 2^-28 fixed point (red.global.add.u64; the routing
+//    kernel clears them).  Integer addition commutes: results are bit-reproducible whatever the order of the items.
+// 3. finalize_batched_kernel converts the sums, adds the residual and rounds to fp16.
 //
 // Rounding contract as the single-token kernel: fp16 activations, scale applied per group partial, fp16 SwiGLU
 // products, f32 routed sum (src/backend/metal/kernels/decode_gemv_q8.metal:166-251).
@@ -68,6 +68,7 @@ struct RouteSmallParams {
     uint32_t *offsets, *pair_rows, *inverse, *active;      // the dispatch plan
     uint32_t *ticket;               // zero between launches
     uint32_t *status;
+    unsigned long long *acc;        // [n][H] fixed-point output sums of the call: this kernel clears its token's row
 };
 
 template <int QT>
@@ -82,6 +83,7 @@ __global__ void __launch_bounds__(kRsThreads) route_small_kernel(const RouteSmal
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const uint32_t token = blockIdx.x, K = prm.K;
     if (tid < UOCR_EXPF_N) s_tab[tid] = c_exp_tab[tid];
+    for (int h = tid; h < H / 2; h += kRsThreads) reinterpret_cast<uint4 *>(prm.acc + (size_t)token * H)[h] = make_uint4(0u, 0u, 0u, 0u);
     if (tid < H / 8) reinterpret_cast<uint4 *>(s_x)[tid] = __ldg(reinterpret_cast<const uint4 *>(prm.hidden + (size_t)token * H) + tid);
     __syncthreads();
 
@@ -193,8 +195,8 @@ struct BatchedParams {
     const uint32_t *active;           // [0] = number of experts with at least one pair, then their ids
     const uint32_t *expert_offsets;   // [E + 1]
     const uint32_t *pair_rows;        // pairs grouped by expert
-    float *routed_part;               // [parts][n * K][H], row = position in pair_rows
-    float *shared_part;               // [kBtSharedHalves * parts][n][H]
+    const float *top_weights;         // [n][K] routing weights
+    unsigned long long *acc;          // [n][H] output sums in 2^-28 fixed point (cleared by the routing kernel)
     uint32_t *status;
 };
 
@@ -220,7 +222,8 @@ template <int QT> struct BtSmem {
     static constexpr int kMidf = kMid + kBtTokens * 64 * 2;                 // their bytes [16 tok][2][16 words]
     static constexpr int kMs = kMidf + kBtTokens * 2 * 64;                  // their scales [16]
     static constexpr int kTok = kMs + 64;                                   // token of each slot of the pass [16]
-    static constexpr int kEntry = kTok + 64;                                // entries (expert ids), most tokens first [66]
+    static constexpr int kWt = kTok + 64;                                   // routing weight of each slot of the pass [16]
+    static constexpr int kEntry = kWt + 64;                                 // entries (expert ids), most tokens first [66]
     static constexpr int kFirst = kEntry + 68 * 4;                          // first (entry, pass) index of each entry [67]
     static constexpr int kBars = kFirst + 68 * 4;                           // full[4], empty[4], sc_full[2], sc_empty[2], flags
     static constexpr int kTotal = kBars + 128;
@@ -231,7 +234,16 @@ __device__ __forceinline__ void bt_arrive(uint64_t *bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
-// one work item: an entry (expert or shared half), a 16-token pass, a part (two slices)
+// Output sums: 64-bit integers in 2^-28 fixed point, added with red.global.add.u64.  Integer addition commutes, so the
+// result does not depend on the order in which the items of a call finish (bit-reproducible), and neither per-part
+// partial outputs nor a pass over them are needed.  A value outside +-2^18 (or a NaN) is left out and flagged.
+constexpr float kBtAccScale = 268435456.f, kBtAccRange = 262144.f;
+__device__ __forceinline__ void bt_add_fixed(unsigned long long *p, float x, uint32_t *status) {
+    if (!(fabsf(x) < kBtAccRange)) { atomicOr(status, kStatusRange); x = 0.f; }
+    asm volatile("red.global.add.u64 [%0], %1;" ::"l"(p), "l"((unsigned long long)__float2ll_rn(x * kBtAccScale)) : "memory");
+}
+
+// one work item: an entry (expert or shared half), a 16-token pass, a part (one or two slices)
 struct BtItem {
     uint32_t expert, part, row0, p0, T;
 };
@@ -251,6 +263,7 @@ __global__ void __launch_bounds__(kBtThreads, 1) decode_batched_kernel(const __g
     uint32_t *s_midf = reinterpret_cast<uint32_t *>(smem + Sm::kMidf);
     float *s_ms = reinterpret_cast<float *>(smem + Sm::kMs);
     uint32_t *s_tok = reinterpret_cast<uint32_t *>(smem + Sm::kTok);
+    float *s_wt = reinterpret_cast<float *>(smem + Sm::kWt);
     uint32_t *s_entry = reinterpret_cast<uint32_t *>(smem + Sm::kEntry);
     uint32_t *s_first = reinterpret_cast<uint32_t *>(smem + Sm::kFirst);
     uint64_t *full = reinterpret_cast<uint64_t *>(smem + Sm::kBars), *empty = full + kBtStages, *sc_full = empty + kBtStages,
@@ -353,10 +366,20 @@ __global__ void __launch_bounds__(kBtThreads, 1) decode_batched_kernel(const __g
         const bool shared = it.expert >= (uint32_t)kSlE;
         const uint32_t T = it.T, NB = (T + 3u) / 4u;
         const uint32_t first_unit = it.expert * kSlRoutedPerSlot + it.part * kBtSlices;
-        float *out_base = shared ? prm.shared_part + (size_t)((it.expert - kSlE) * kBtParts + it.part) * prm.n * H
-                                 : prm.routed_part + (size_t)it.part * prm.n * prm.K * H;
-        if (tid < kBtTokens)
-            s_tok[tid] = (uint32_t)tid < T ? (shared ? it.p0 + tid : prm.pair_rows[it.row0 + it.p0 + tid] / prm.K) : 0xffffffffu;
+        if (tid < kBtTokens) {
+            uint32_t token = 0xffffffffu;
+            float wt = 0.f;
+            if ((uint32_t)tid < T) {
+                if (shared) { token = it.p0 + tid; wt = 1.0f; }
+                else {
+                    const uint32_t pair = prm.pair_rows[it.row0 + it.p0 + tid];
+                    token = pair / prm.K;
+                    wt = prm.top_weights[pair];
+                }
+            }
+            s_tok[tid] = token;
+            s_wt[tid] = wt;
+        }
         bt_sync();
         // 1. the pass's activation bytes and scales (slots beyond T: zeros), all loads of a thread in flight together
         {
@@ -487,29 +510,20 @@ __global__ void __launch_bounds__(kBtThreads, 1) decode_batched_kernel(const __g
             for (uint32_t nb = 0; nb < NB; ++nb) {
                 const uint4 mbf = *reinterpret_cast<const uint4 *>(s_midf + (((4 * nb + (g >> 1)) * 2 + (g & 1)) * 4 + t) * 4);
                 const uint32_t tokc = 4u * nb + t;
-                const float ms = s_ms[tokc];
-                float *dst = out_base + (size_t)(it.row0 + it.p0 + tokc) * H;
-                float prev[kBtBlocksPerWarp][2];
-                if (sl != 0 && tokc < T) {                    // the first slice's values of this thread: all loads in flight together
-#pragma unroll
-                    for (int bi = 0; bi < kBtBlocksPerWarp; ++bi) {
-                        const uint32_t r = 16u * (warp + 16 * bi) + g;
-                        prev[bi][0] = dst[r];
-                        prev[bi][1] = dst[r + 8];
-                    }
-                }
+                // the slot's routing weight rides in the scale; the products go straight into the call's output sums
+                const float ms = s_ms[tokc] * s_wt[tokc];
+                unsigned long long *dst = prm.acc + (size_t)(tokc < T ? s_tok[tokc] : 0u) * H;
 #pragma unroll
                 for (int bi = 0; bi < kBtBlocksPerWarp; ++bi) {
                     int ca[4] = {0, 0, 0, 0}, cb[4] = {0, 0, 0, 0};
                     if (QT == UOCR_QT_Q8) group_imma(ca, cb, dwn[bi][0], dwn[bi][1], mbf);
                     else group_imma(ca, cb, make_uint2(dwn[bi][0].x, dwn[bi][0].y), make_uint2(dwn[bi][0].z, dwn[bi][0].w), mbf);
                     if (tokc < T) {
-                        float v0 = (float)(ca[0] + cb[0] + (ca[1] + cb[1]) * 256) * (__half2float(dslo[bi]) * ms);
-                        float v1 = (float)(ca[2] + cb[2] + (ca[3] + cb[3]) * 256) * (__half2float(dshi[bi]) * ms);
-                        if (sl != 0) { v0 += prev[bi][0]; v1 += prev[bi][1]; }     // same thread, same address as for the first slice
+                        const float v0 = (float)(ca[0] + cb[0] + (ca[1] + cb[1]) * 256) * (__half2float(dslo[bi]) * ms);
+                        const float v1 = (float)(ca[2] + cb[2] + (ca[3] + cb[3]) * 256) * (__half2float(dshi[bi]) * ms);
                         const uint32_t r = 16u * (warp + 16 * bi) + g;
-                        dst[r] = v0;
-                        dst[r + 8] = v1;
+                        bt_add_fixed(dst + r, v0, prm.status);
+                        bt_add_fixed(dst + r + 8, v1, prm.status);
                     }
                 }
             }
@@ -528,84 +542,24 @@ __global__ void __launch_bounds__(kBtThreads, 1) decode_batched_kernel(const __g
 }
 
 // ---------------------------------------------------------------- 3. combine
-// out[t][h] = fp16( fma chain over slots of w * (sum of the pair's parts) + (sum of the shared parts) + residual )
-// SPLIT threads share one group of four outputs: each adds every SPLIT-th run of seven parts (all seven loads of up to three
-// slots in flight together), the partial sums meet through a shuffle.  Calls with 14 parts use SPLIT = 2, so the chain of
-// dependent loads is as long as with 7 parts.
-template <int SPLIT>
-__global__ void __launch_bounds__(256) combine_batched_kernel(const float *__restrict__ routed_part, const float *__restrict__ shared_part,
-                                                              const __half *__restrict__ residual, const uint32_t *__restrict__ inverse,
-                                                              const float *__restrict__ weights, uint32_t n, uint32_t H, uint32_t K,
-                                                              uint32_t parts, __half *__restrict__ out) {
-    const size_t gthread = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    const size_t idx = gthread / SPLIT;                                     // one group of 4 outputs
-    const uint32_t half = (uint32_t)(gthread % SPLIT);
-    const uint32_t per_row = H / 4;
-    const bool live = idx < (size_t)n * per_row;                            // (whole warps stay in the shuffles below)
-    const uint32_t tkn = live ? (uint32_t)(idx / per_row) : 0u, c = live ? (uint32_t)(idx % per_row) * 4 : 0u;
-    const size_t routed_stride = (size_t)n * K * H, shared_stride = (size_t)n * H;
-    constexpr int kChunk = 7;
-    auto meet = [](float4 &v) {
-        if (SPLIT == 2) {
-            v.x += __shfl_xor_sync(0xffffffffu, v.x, 1); v.y += __shfl_xor_sync(0xffffffffu, v.y, 1);
-            v.z += __shfl_xor_sync(0xffffffffu, v.z, 1); v.w += __shfl_xor_sync(0xffffffffu, v.w, 1);
-        }
-    };
-    float acc[4] = {0.f, 0.f, 0.f, 0.f};
-    for (uint32_t s0 = 0; s0 < K; s0 += 3) {
-        uint32_t pos[3];
-        float w[3];
-        float4 sum[3];
-#pragma unroll
-        for (int j = 0; j < 3; ++j) {
-            pos[j] = live && s0 + j < K ? inverse[tkn * K + s0 + j] : 0xffffffffu;
-            w[j] = live && s0 + j < K ? weights[tkn * K + s0 + j] : 0.f;
-            sum[j] = make_float4(0.f, 0.f, 0.f, 0.f);
-        }
-        for (uint32_t p0 = half * kChunk; p0 < parts; p0 += SPLIT * kChunk) {
-            float4 v[3][kChunk];
-#pragma unroll
-            for (int j = 0; j < 3; ++j)
-#pragma unroll
-                for (int p = 0; p < kChunk; ++p)
-                    v[j][p] = pos[j] != 0xffffffffu ? *reinterpret_cast<const float4 *>(routed_part + (p0 + p) * routed_stride + (size_t)pos[j] * H + c)
-                                                     : make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-            for (int j = 0; j < 3; ++j)
-#pragma unroll
-                for (int p = 0; p < kChunk; ++p) { sum[j].x += v[j][p].x; sum[j].y += v[j][p].y; sum[j].z += v[j][p].z; sum[j].w += v[j][p].w; }
-        }
-#pragma unroll
-        for (int j = 0; j < 3; ++j) {
-            meet(sum[j]);
-            if (pos[j] == 0xffffffffu) continue;
-            acc[0] = fmaf(w[j], sum[j].x, acc[0]); acc[1] = fmaf(w[j], sum[j].y, acc[1]);
-            acc[2] = fmaf(w[j], sum[j].z, acc[2]); acc[3] = fmaf(w[j], sum[j].w, acc[3]);
-        }
-    }
-    // the shared MLP's parts (the order of the CPU path: routed slots, then shared, then residual)
-    float4 ssum = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (uint32_t p0 = half * kChunk; p0 < (uint32_t)kBtSharedHalves * parts; p0 += SPLIT * kChunk) {
-        float4 sh[kChunk];
-#pragma unroll
-        for (int p = 0; p < kChunk; ++p)
-            sh[p] = live ? *reinterpret_cast<const float4 *>(shared_part + (p0 + p) * shared_stride + (size_t)tkn * H + c) : make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-        for (int p = 0; p < kChunk; ++p) { ssum.x += sh[p].x; ssum.y += sh[p].y; ssum.z += sh[p].z; ssum.w += sh[p].w; }
-    }
-    meet(ssum);
-    if (!live || half != 0) return;
-    acc[0] += ssum.x; acc[1] += ssum.y; acc[2] += ssum.z; acc[3] += ssum.w;
+// out[t][h] = fp16( output sum + residual ): the weighted sum over slots and the shared MLP's output are already in the sum
+__global__ void __launch_bounds__(256) finalize_batched_kernel(const unsigned long long *__restrict__ acc, const __half *__restrict__ residual,
+                                                               uint32_t n, uint32_t H, __half *__restrict__ out) {
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;       // one group of 4 outputs
+    if (idx >= (size_t)n * (H / 4)) return;
+    const ulonglong2 a01 = *reinterpret_cast<const ulonglong2 *>(acc + idx * 4), a23 = *reinterpret_cast<const ulonglong2 *>(acc + idx * 4 + 2);
+    float v[4] = {(float)(long long)a01.x * (1.0f / kBtAccScale), (float)(long long)a01.y * (1.0f / kBtAccScale),
+                  (float)(long long)a23.x * (1.0f / kBtAccScale), (float)(long long)a23.y * (1.0f / kBtAccScale)};
     if (residual) {
-        const uint2 rv = *reinterpret_cast<const uint2 *>(residual + (size_t)tkn * H + c);
+        const uint2 rv = *reinterpret_cast<const uint2 *>(residual + idx * 4);
         const float2 r01 = __half22float2(*reinterpret_cast<const __half2 *>(&rv.x));
         const float2 r23 = __half22float2(*reinterpret_cast<const __half2 *>(&rv.y));
-        acc[0] += r01.x; acc[1] += r01.y; acc[2] += r23.x; acc[3] += r23.y;
+        v[0] += r01.x; v[1] += r01.y; v[2] += r23.x; v[3] += r23.y;
     }
     uint2 o;
-    *reinterpret_cast<__half2 *>(&o.x) = __floats2half2_rn(acc[0], acc[1]);
-    *reinterpret_cast<__half2 *>(&o.y) = __floats2half2_rn(acc[2], acc[3]);
-    *reinterpret_cast<uint2 *>(out + (size_t)tkn * H + c) = o;
+    *reinterpret_cast<__half2 *>(&o.x) = __floats2half2_rn(v[0], v[1]);
+    *reinterpret_cast<__half2 *>(&o.y) = __floats2half2_rn(v[2], v[3]);
+    *reinterpret_cast<uint2 *>(out + idx * 4) = o;
 }
 
 // ---------------------------------------------------------------- host side
@@ -631,8 +585,8 @@ BatchedScratchLayout decode_batched_scratch(uint32_t n, uint32_t K) {
     BatchedScratchLayout l{};
     size_t off = 0;
     auto take = [&](size_t bytes) { const size_t o = off; off = (off + bytes + 255) / 256 * 256; return o; };
-    l.routed_part = take((size_t)kBtMaxParts * n * K * kSlH * sizeof(float));
-    l.shared_part = take((size_t)kBtSharedHalves * kBtMaxParts * n * kSlH * sizeof(float));
+    (void)K;
+    l.acc = take((size_t)n * kSlH * sizeof(unsigned long long));
     l.x_limbs = take((size_t)n * kBtTokenLimbBytes);
     l.x_scales = take((size_t)n * kSlGroups * sizeof(float));
     l.total = off;
@@ -656,6 +610,7 @@ cudaError_t launch_batched_route(const DLayer &L, const Scratch &S, const __half
     r.x_limbs = reinterpret_cast<uint32_t *>(scratch + lay.x_limbs); r.x_scales = reinterpret_cast<float *>(scratch + lay.x_scales);
     r.offsets = S.expert_offsets; r.pair_rows = S.pair_rows; r.inverse = S.inverse; r.active = S.active;
     r.ticket = ticket; r.status = S.status;
+    r.acc = reinterpret_cast<unsigned long long *>(scratch + lay.acc);
     if (L.expert_qtype == UOCR_QT_Q4) route_small_kernel<UOCR_QT_Q4><<<n, kRsThreads, 0, st>>>(r);
     else route_small_kernel<UOCR_QT_Q8><<<n, kRsThreads, 0, st>>>(r);
     ++*launches;
@@ -677,8 +632,8 @@ cudaError_t launch_batched_experts(const DLayer &L, const Scratch &S, uint32_t n
     p.x_limbs = reinterpret_cast<const uint32_t *>(scratch + lay.x_limbs); p.x_scales = reinterpret_cast<const float *>(scratch + lay.x_scales);
     p.n = n; p.K = L.K;
     p.active = S.active; p.expert_offsets = S.expert_offsets; p.pair_rows = S.pair_rows;
-    p.routed_part = reinterpret_cast<float *>(scratch + lay.routed_part);
-    p.shared_part = reinterpret_cast<float *>(scratch + lay.shared_part);
+    p.top_weights = S.top_weights;
+    p.acc = reinterpret_cast<unsigned long long *>(scratch + lay.acc);
     p.status = S.status;
     // at most one item per (selected expert or shared half, pass, part); one CTA per SM, items dealt round-robin
     const uint64_t pairs = (uint64_t)n * L.K;
@@ -699,16 +654,11 @@ cudaError_t launch_batched_experts(const DLayer &L, const Scratch &S, uint32_t n
 
 cudaError_t launch_batched_combine(const DLayer &L, const Scratch &S, const __half *residual, uint32_t n, uint8_t *scratch, __half *out,
                                    cudaStream_t st, uint64_t *launches) {
+    (void)S;
     const BatchedScratchLayout lay = decode_batched_scratch(n, L.K);
-    const uint32_t parts = (uint32_t)(kSlRoutedPerSlot / bt_slices_for(n));
-    const float *rp = reinterpret_cast<const float *>(scratch + lay.routed_part), *sp = reinterpret_cast<const float *>(scratch + lay.shared_part);
-    if (parts > 7) {
-        const size_t work = (size_t)n * (L.H / 4) * 2;
-        combine_batched_kernel<2><<<(unsigned)((work + 255) / 256), 256, 0, st>>>(rp, sp, residual, S.inverse, S.top_weights, n, L.H, L.K, parts, out);
-    } else {
-        const size_t work = (size_t)n * (L.H / 4);
-        combine_batched_kernel<1><<<(unsigned)((work + 255) / 256), 256, 0, st>>>(rp, sp, residual, S.inverse, S.top_weights, n, L.H, L.K, parts, out);
-    }
+    const size_t work = (size_t)n * (L.H / 4);
+    finalize_batched_kernel<<<(unsigned)((work + 255) / 256), 256, 0, st>>>(reinterpret_cast<const unsigned long long *>(scratch + lay.acc), residual, n,
+                                                                            L.H, out);
     ++*launches;
     return cudaGetLastError();
 }
