@@ -2,7 +2,7 @@
 """Benchmark of the MoE-layer hot path.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
-                    [--workload decode|prefill|ep|batched] [--extras all|none]
+                    [--workload decode|prefill|ep|batched|lm_head] [--extras all|none]
 
 Prints ONE JSON line on rank 0.  Workloads (seeded synthetic inputs of the benchmark plan's shapes):
   decode   (default, the headline)  one token through 11 stacked MoE layers (hidden 1280, 64 experts top-6 + shared
@@ -776,7 +776,7 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=None)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "ep", "batched"])
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "ep", "batched", "lm_head"])
     ap.add_argument("--extras", default="all", choices=["all", "none"],
                     help="decode workload: also time short passes of the other workloads and append them to the line")
     ap.add_argument("--qtype", default="q4_0", choices=["q4_0", "f16", "q8_0"], help="prefill workload: weight format")
@@ -794,6 +794,10 @@ def main() -> None:
         args.steps = 50 if kind == "decode" else 20
 
     if args.impl == "reference":
+        if kind == "lm_head":
+            if rank == 0:
+                print(json.dumps({"impl": "reference", "unavailable": "the reference has no CPU function for the fused LM head + argmax (Metal kernels only)"}))
+            return
         if kind in ("decode", "batched"):
             run_reference_arm(args, rank, world)
         else:
@@ -852,6 +856,17 @@ def main() -> None:
             L, hidden, resid = synth_token_layer(w["seed"], 1024, args.qtype)
             cps, ckind, sample = cpu_tokens_per_s(L, hidden, resid, orc.host_threads())
             line["cpu_baseline"] = {"value": cps, "unit": "tokens/s", "cores": orc.host_threads(), "kind": ckind, "sample": sample}
+    elif kind == "lm_head":
+        if world > 1:
+            raise SystemExit("the LM-head workload runs on one GPU")
+        r = measure_lm_head(pkg, torch, flush_l2, args.steps, max(args.warmup, 3))
+        q4 = r["qtype"]["q4_0"]
+        line = {"metric": "lm_head_argmax_us_per_token", "value": q4["us_per_token"], "unit": "us/token (Q4_0)", "n_gpus": 1,
+                "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": q4["us_per_token"] / 1e3,
+                "higher_is_better": False, "scaling": "weak", "vs_baseline": None,
+                "dtype": "int8 x int8 -> int32 on block-floating fp16 activations and Q4_0 / Q8_0 weights", "data": "synthetic",
+                "config": {"workload": r["workload"], "tokens_per_step": 1, "qtype": "q4_0", "l2": L2_NOTE},
+                "gpu_launches": 2 * args.steps, "roofline": dict(q4["roofline"], traffic=None), "lm_head": r}
     elif kind == "batched":
         if world > 1:
             raise SystemExit("the batched-decode workload runs on one GPU")
