@@ -219,6 +219,19 @@ typedef struct uocr_cuda_model_file_view {
 UOCR_CUDA_API int uocr_cuda_context_map_model(uocr_cuda_context *ctx, const uocr_cuda_model_file_view *model,
                                               char *error, size_t error_size);
 UOCR_CUDA_API uint32_t uocr_cuda_context_moe_layer_count(const uocr_cuda_context *ctx);
+/* The tensors either side of the MoE layers, from the same file, after uocr_cuda_context_map_model: the dense SwiGLU MLP
+ * of decoder layer 0 (uocr_tensor_id_layer_dense_mlp, src/model/uocr_tensor_registry.h:72-86; scratch for token_capacity
+ * tokens), the LM head (UOCR_TENSOR_ID_LM_HEAD, :12), the post-attention norm weight of every decoder layer below
+ * first_moe_layer + moe_layer_count (uocr_tensor_id_layer_post_attn_norm, :54-56) and the final norm
+ * (UOCR_TENSOR_ID_FINAL_NORM, :13).  A tensor the file does not hold is skipped; one it holds is checked like the MoE
+ * tensors (runtime, row-major, byte ranges inside the file) and refused with a message otherwise, before anything is
+ * uploaded.  The getters return -1 / NULL for what was not mapped; the norm weights are device fp16[hidden_size], ready
+ * for uocr_cuda_moe_layer_forward_normed / uocr_cuda_dense_mlp_forward_normed / uocr_cuda_rmsnorm. */
+UOCR_CUDA_API int uocr_cuda_context_map_model_neighbours(uocr_cuda_context *ctx, const uocr_cuda_model_file_view *model,
+                                                         uint32_t token_capacity, char *error, size_t error_size);
+UOCR_CUDA_API int uocr_cuda_context_file_dense_mlp_index(const uocr_cuda_context *ctx);
+UOCR_CUDA_API const void *uocr_cuda_context_post_attn_norm_weight(const uocr_cuda_context *ctx, uint32_t decoder_layer);
+UOCR_CUDA_API const void *uocr_cuda_context_final_norm_weight(const uocr_cuda_context *ctx);
 
 /* ---- the steps either side of the MoE layer.
  * RMSNorm (uocr_cpu_ref_rmsnorm_f32, src/backend/cpu_ref/uocr_cpu_ref.c:145-169; the GPU form

@@ -133,7 +133,15 @@ def model_files(tmp_path_factory):
     L = quant.synth_layer(rng, expert_qtype=quant.QTYPE_Q4_0, shared_qtype=quant.QTYPE_Q8_0, **FULL)
     folder = tmp_path_factory.mktemp("engine")
     good, gap = folder / "moe.uocr", folder / "gap.uocr"
-    info = uocr_file.write_moe_model(str(good), {l: L for l in MOE_LAYERS})
+    # what the file holds either side of the MoE layers: layer 0's dense MLP (intermediate 6848), a (shortened) LM head, norms
+    H = FULL["H"]
+    dense = tuple(quant.make_matrix(quant.QTYPE_Q8_0, rng.standard_normal(shape, dtype=np.float32) * 0.02)
+                  for shape in ((6848, H), (6848, H), (H, 6848)))
+    head = quant.make_matrix(quant.QTYPE_Q4_0, rng.standard_normal((4096, H), dtype=np.float32) * 0.02)
+    norm = rng.uniform(0.5, 1.5, H).astype("<f2").view(np.uint16)
+    info = uocr_file.write_moe_model(str(good), {l: L for l in MOE_LAYERS}, dense=dense, lm_head=head,
+                                     post_attn_norms={l: norm for l in range(12)}, final_norm=norm)
+    info["neighbour_bytes"] = sum(m.qweight.size + m.qscale.size * 2 for m in dense + (head,)) + 13 * H * 2
     uocr_file.write_moe_model(str(gap), {l: L for l in MOE_LAYERS}, break_slab_at=(3, 17))
     return str(good), str(gap), info, L
 
@@ -151,7 +159,7 @@ def test_engine_open_with_the_cuda_backend(engine_lib, model_files):
         assert engine_lib.uocr_engine_memory_report(eng, C.byref(rep)) == UOCR_OK
         layer_bytes = L.expert_qweight.size + L.expert_qscale.size * 2
         # the engine's own view of the file's tensor data plus the device copy of every layer
-        assert rep.category_live_bytes[MEMORY_MODEL_VIEWS] >= 2 * 11 * layer_bytes
+        assert rep.category_live_bytes[MEMORY_MODEL_VIEWS] >= 2 * (11 * layer_bytes + info["neighbour_bytes"])
         assert rep.category_live_bytes[MEMORY_MOE_SCRATCH] > 0
         assert rep.total_live_bytes >= rep.category_live_bytes[MEMORY_MODEL_VIEWS] + rep.category_live_bytes[MEMORY_MOE_SCRATCH]
         # the ABI smoke request (no generated tokens) is served; generation is refused by the engine as for cpu-ref

@@ -191,3 +191,112 @@ def test_files_the_reference_host_refuses_are_refused(pkg, tmp_path):
             map_file(ctx, good, TINY, 1, 2)
         ctx.unmap_model()
         assert map_file(ctx, good, TINY, 2, 1) == 1
+
+
+# ------------------------------------------------------------------------------ the tensors either side of the layers
+EPS = 1.0e-6                # UOCR_RMS_NORM_EPS (src/model/uocr_constants.h:27)
+
+
+def neighbour_tensors(seed, qname="q8_0", S=256, V=512):
+    rng = np.random.default_rng(seed)
+    H, qt = TINY["H"], QT[qname]
+    dense = tuple(quant.make_matrix(qt, rng.standard_normal(shape, dtype=np.float32) * 0.05) for shape in ((S, H), (S, H), (H, S)))
+    head = quant.make_matrix(qt, rng.standard_normal((V, H), dtype=np.float32) * 0.05)
+    norms = {l: rng.uniform(0.5, 1.5, H).astype("<f2").view(np.uint16) for l in (0, 1, 2)}
+    final = rng.uniform(0.5, 1.5, H).astype("<f2").view(np.uint16)
+    return dense, head, norms, final
+
+
+def test_reference_loader_accepts_a_file_with_the_neighbouring_tensors(ref_loader, tmp_path):
+    dense, head, norms, final = neighbour_tensors(20)
+    path = tmp_path / "full.uocr"
+    info = uocr_file.write_moe_model(str(path), tiny_layers(21, "q4_0", "q8_0"), dense=dense, lm_head=head, post_attn_norms=norms,
+                                     final_norm=final)
+    mf, err = RefModelFile(), ctypes.create_string_buffer(512)
+    assert ref_loader.uocr_model_file_open(str(path).encode(), ctypes.byref(mf), err, 512) == 0, err.value
+    try:
+        assert mf.tensor_count == info["tensor_count"]
+        for tid in (uocr_file.TENSOR_ID_LM_HEAD, uocr_file.TENSOR_ID_FINAL_NORM, uocr_file.tensor_id_post_attn_norm(2),
+                    uocr_file.tensor_id_dense(uocr_file.PROJ_DOWN)):
+            assert ref_loader.uocr_model_file_find_tensor(ctypes.byref(mf), tid)
+    finally:
+        ref_loader.uocr_model_file_close(ctypes.byref(mf))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("qname", ["q8_0", "q4_0", "f16"])
+def test_neighbours_from_a_file_equal_the_same_tensors_from_memory(pkg, tmp_path, qname):
+    """Dense MLP of layer 0, LM head, post-attention norms and final norm mapped from the file: every call through them
+    gives bit for bit what the same tensors mapped from host arrays give."""
+    dense, head, norms, final = neighbour_tensors(22, qname)
+    layers = tiny_layers(23, "q4_0", "q8_0")
+    path = tmp_path / "full.uocr"
+    uocr_file.write_moe_model(str(path), layers, dense=dense, lm_head=head, post_attn_norms=norms, final_norm=final)
+    H, n = TINY["H"], 5
+    rng = np.random.default_rng(24)
+    stream_rows = (rng.standard_normal((n, H), dtype=np.float32) * 2.0).astype("<f2").view(np.uint16)
+    dev = lambda bits: torch.from_numpy(np.ascontiguousarray(bits)).cuda().view(torch.float16)
+    data = np.fromfile(path, dtype=np.uint8)
+    entries, n_entries = uocr_file.read_directory(data)
+    with pkg.Context() as from_file, pkg.Context() as from_mem:
+        assert map_file(from_file, path, TINY, 1, 2) == 2
+        got = from_file.map_model_neighbours(data.ctypes.data, data.size, data.ctypes.data + entries, n_entries, token_capacity=16,
+                                             first_moe_layer=1, moe_layer_count=2)
+        assert got["dense_mlp"] == 0 and sorted(got["post_attn_norm"]) == [0, 1, 2] and got["final_norm"]
+        with pytest.raises(pkg.UocrCudaError, match="already mapped"):
+            from_file.map_model_neighbours(data.ctypes.data, data.size, data.ctypes.data + entries, n_entries, token_capacity=16,
+                                           first_moe_layer=1, moe_layer_count=2)
+        for l in (1, 2):
+            from_mem.map_layer(layers[l])
+        idx = from_mem.map_dense_mlp(*dense, token_capacity=16)
+        from_mem.map_lm_head(head)
+        assert from_file.model_view_bytes == from_mem.model_view_bytes + 4 * H * 2          # + three layer norms and the final norm
+        outs = []
+        for ctx, dense_idx, w0, w1, wf in ((from_file, got["dense_mlp"], got["post_attn_norm"][0], got["post_attn_norm"][1], got["final_norm"]),
+                                           (from_mem, idx, dev(norms[0]), dev(norms[1]), dev(final))):
+            ctx.allocate_runtime_arenas(n)
+            ctx.set_stream(torch.cuda.current_stream().cuda_stream)
+            a, b, c = (torch.zeros((n, H), dtype=torch.float16, device="cuda") for _ in range(3))
+            ids = torch.zeros(4, dtype=torch.int32, device="cuda")
+            ctx.dense_mlp_forward_normed(dense_idx, dev(stream_rows), w0, EPS, n, a)           # decoder layer 0
+            ctx.layer_forward_normed(0, a, w1, EPS, n, b)                                     # decoder layer 1
+            ctx.rmsnorm(b, wf, EPS, n, H, c)                                                  # final norm
+            ctx.lm_head_argmax(c, 4, ids)
+            ctx.synchronize()
+            outs.append((a.cpu().numpy().view(np.uint16), b.cpu().numpy().view(np.uint16), ids.cpu().numpy()))
+    for x, y in zip(*outs):
+        assert np.array_equal(x, y)
+
+
+@pytest.mark.gpu
+def test_neighbour_tensors_that_do_not_fit_are_refused(pkg, tmp_path):
+    dense, head, norms, final = neighbour_tensors(25)
+    layers = tiny_layers(26, "q4_0", "q8_0")
+
+    def try_map(path, match):
+        data = np.fromfile(path, dtype=np.uint8)
+        entries, n_entries = uocr_file.read_directory(data)
+        with pkg.Context() as ctx:
+            with pytest.raises(pkg.UocrCudaError, match="map the MoE layers first"):
+                ctx.map_model_neighbours(data.ctypes.data, data.size, data.ctypes.data + entries, n_entries, token_capacity=8,
+                                         first_moe_layer=1, moe_layer_count=2)
+            map_file(ctx, path, TINY, 1, 2)
+            if match is None:
+                got = ctx.map_model_neighbours(data.ctypes.data, data.size, data.ctypes.data + entries, n_entries, token_capacity=8,
+                                               first_moe_layer=1, moe_layer_count=2)
+                return got
+            with pytest.raises(pkg.UocrCudaError, match=match):
+                ctx.map_model_neighbours(data.ctypes.data, data.size, data.ctypes.data + entries, n_entries, token_capacity=8,
+                                         first_moe_layer=1, moe_layer_count=2)
+            assert ctx.moe_scratch_bytes == 0 and ctx.layer_count == 2          # nothing of the neighbours stays behind
+
+    bare = tmp_path / "bare.uocr"
+    uocr_file.write_moe_model(str(bare), layers)
+    assert try_map(bare, None) == {"dense_mlp": None, "post_attn_norm": {}, "final_norm": None}      # nothing there: nothing mapped
+    short_norm = tmp_path / "short.uocr"
+    uocr_file.write_moe_model(str(short_norm), layers, post_attn_norms={1: norms[1][:64]})
+    try_map(short_norm, "layer 1: post-attention norm does not have the hidden size")
+    wide = tmp_path / "wide.uocr"
+    bad_head = quant.make_matrix(quant.QTYPE_Q8_0, np.random.default_rng(27).standard_normal((64, 2 * TINY["H"]), dtype=np.float32))
+    uocr_file.write_moe_model(str(wide), layers, lm_head=bad_head, dense=dense)
+    try_map(wide, "LM head")

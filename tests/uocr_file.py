@@ -29,7 +29,9 @@ SECTION_CONFIG, SECTION_TENSOR_DIRECTORY, SECTION_TOKENIZER, SECTION_PROVENANCE,
 TOKENIZER_MAGIC, PROVENANCE_MAGIC, TENSOR_DIR_MAGIC = 0x4B4F5455, 0x564F5250, 0x52494454
 USAGE_RUNTIME = 1
 FLAG_ROW_MAJOR = 1
+FAMILY_LM_HEAD, FAMILY_FINAL_NORM, FAMILY_LAYER_NORM, FAMILY_LAYER_DENSE_MLP = 2, 3, 5, 6
 FAMILY_MOE_ROUTER, FAMILY_MOE_EXPERT, FAMILY_MOE_SHARED = 7, 8, 9
+TENSOR_ID_LM_HEAD, TENSOR_ID_FINAL_NORM = 2, 3
 PROJ_WEIGHT, PROJ_GATE, PROJ_UP, PROJ_DOWN = 1, 20, 21, 22
 
 HEADER = struct.Struct("<4s7IQQ32s32s")                     # 112 bytes
@@ -54,6 +56,14 @@ def tensor_id_layer(layer: int, local: int) -> int:
     return 10000 + layer * 1000 + local
 
 
+def tensor_id_post_attn_norm(layer: int) -> int:
+    return tensor_id_layer(layer, 2)
+
+
+def tensor_id_dense(projection: int) -> int:
+    return tensor_id_layer(0, 30 + projection - PROJ_GATE)
+
+
 def tensor_id_router(layer: int) -> int:
     return tensor_id_layer(layer, 40)
 
@@ -71,9 +81,9 @@ def align_up(v: int, a: int) -> int:
 
 
 class _Tensor:
-    def __init__(self, tid, family, layer, expert, projection, qtype, rows, cols, payload, scales):
+    def __init__(self, tid, family, layer, expert, projection, qtype, rows, cols, payload, scales, rank=2):
         self.id, self.family, self.layer, self.expert, self.projection = tid, family, layer, expert, projection
-        self.qtype, self.rows, self.cols = qtype, rows, cols
+        self.qtype, self.rows, self.cols, self.rank = qtype, rows, cols, rank
         self.payload = np.ascontiguousarray(payload).view(np.uint8).reshape(-1)
         self.scales = None if scales is None else np.ascontiguousarray(scales).view(np.uint8).reshape(-1)
         self.payload_offset = 0
@@ -83,7 +93,7 @@ class _Tensor:
         quantised = self.qtype != quant.QTYPE_F16
         row_size = 0 if not quantised else quant.packed_row_bytes(self.qtype, self.cols)
         return TENSOR_ENTRY.pack(self.id, self.family, self.layer, self.expert, self.projection, USAGE_RUNTIME, self.qtype,
-                                 FLAG_ROW_MAJOR, 2, self.rows, self.cols, 0, 0, self.rows, self.cols, 0, 0,
+                                 FLAG_ROW_MAJOR, self.rank, self.rows, self.cols, 0, 0, self.rows, self.cols, 0, 0,
                                  self.payload_offset, self.payload.size, quant.GROUP if quantised else 0, row_size,
                                  self.scale_offset if quantised else 0, self.scales.size if quantised else 0, 0, 0, 0, 0, 0, 0)
 
@@ -111,15 +121,35 @@ def _layer_tensors(layer: int, L: quant.LayerWeights) -> list[list[_Tensor]]:
     return groups
 
 
-def write_moe_model(path: str, layers: dict[int, quant.LayerWeights], *, break_slab_at: tuple[int, int] | None = None) -> dict:
+def _vector(tid, family, layer, values) -> _Tensor:
+    v = np.ascontiguousarray(values).view(np.uint16).reshape(-1)           # fp16 bits
+    return _Tensor(tid, family, layer, -1, PROJ_WEIGHT, quant.QTYPE_F16, v.size, 0, v, None, rank=1)
+
+
+def write_moe_model(path: str, layers: dict[int, quant.LayerWeights], *, break_slab_at: tuple[int, int] | None = None,
+                    dense: tuple | None = None, lm_head=None, post_attn_norms: dict | None = None, final_norm=None) -> dict:
     """Write a model file with the MoE tensors of `layers` (decoder layer index -> weights).
 
     `break_slab_at=(layer, expert)` inserts 16 bytes of padding before that expert's gate projection, which leaves a
     file the loader accepts but whose expert slab is no longer contiguous (the case every backend has to refuse).
+    Optional neighbours of the MoE layers: `dense` = (gate, up, down) matrices of decoder layer 0's MLP, `lm_head` a
+    [vocabulary][hidden] matrix, `post_attn_norms` = {decoder layer: fp16 bits [hidden]}, `final_norm` fp16 bits [hidden].
     Returns {"file_size", "tensor_count", "qprofile"}."""
     groups: list[list[_Tensor]] = []
     for layer in sorted(layers):
         groups.extend(_layer_tensors(layer, layers[layer]))
+    if lm_head is not None:
+        groups.append([_Tensor(TENSOR_ID_LM_HEAD, FAMILY_LM_HEAD, -1, -1, PROJ_WEIGHT, lm_head.qtype, lm_head.rows, lm_head.cols,
+                               lm_head.qweight, lm_head.qscale)])
+    if final_norm is not None:
+        groups.append([_vector(TENSOR_ID_FINAL_NORM, FAMILY_FINAL_NORM, -1, final_norm)])
+    for layer, values in (post_attn_norms or {}).items():
+        groups.append([_vector(tensor_id_post_attn_norm(layer), FAMILY_LAYER_NORM, layer, values)])
+    if dense is not None:
+        for proj, m in zip((PROJ_GATE, PROJ_UP, PROJ_DOWN), dense):
+            groups.append([_Tensor(tensor_id_dense(proj), FAMILY_LAYER_DENSE_MLP, 0, -1, proj, m.qtype, m.rows, m.cols, m.qweight,
+                                   m.qscale)])
+    groups.sort(key=lambda g: g[0].id)
     tensors = [t for g in groups for t in g]
     assert [t.id for t in tensors] == sorted(t.id for t in tensors)
     qtypes = {t.qtype for t in tensors}

@@ -117,6 +117,10 @@ struct uocr_cuda_context {
         uint64_t scratch_bytes = 0;
     };
     std::vector<DenseMlp> dense;
+    // tensors either side of the MoE layers mapped from a model file (uocr_cuda_context_map_model_neighbours)
+    int file_dense_index = -1;                          // index of the file's layer-0 dense MLP in `dense`, or -1
+    std::vector<const __half *> post_attn_norms;        // [decoder layer] device fp16[H], null where the file has none
+    const __half *final_norm = nullptr;
     // the LM head (vocabulary projection) and the scratch of its fused argmax
     struct {
         DMatrix w{};
@@ -408,6 +412,9 @@ extern "C" void uocr_cuda_context_unmap_model(uocr_cuda_context *ctx) {
     ctx->dense_scratch_bytes = 0;
     cudaFree(ctx->lm_head.scratch);
     ctx->lm_head = {};
+    ctx->file_dense_index = -1;
+    ctx->post_attn_norms.clear();
+    ctx->final_norm = nullptr;
     ctx->weight_bytes = 0;
     track_memory(ctx);
 }
@@ -605,6 +612,93 @@ extern "C" int uocr_cuda_context_map_model(uocr_cuda_context *ctx, const uocr_cu
 extern "C" uint32_t uocr_cuda_context_moe_layer_count(const uocr_cuda_context *ctx) {
     return ctx ? (uint32_t)ctx->layers.size() : 0;
 }
+
+// ---- the tensors either side of the MoE layers, from the same file ------------------------------------------------
+static int upload(uocr_cuda_context *ctx, const void *host, uint64_t bytes, void **out, char *error, size_t error_size);
+
+namespace {
+constexpr uint32_t kIdLmHead = 2, kIdFinalNorm = 3, kIdPostAttnNorm = 2, kIdDenseGate = 30;
+
+// a norm weight: a runtime fp16 vector whose bytes lie inside the file
+const char *check_norm_entry(const uocr_cuda_model_file_view *m, const uocr_cuda_tensor_entry *t, uint32_t H) {
+    if (t->usage != kUsageRuntime) return "is not a runtime tensor";
+    if (t->qtype != UOCR_QT_F16 || t->rank != 1) return "is not an fp16 vector";
+    if (t->logical_shape[0] != H || t->payload_size != (uint64_t)H * 2) return "does not have the hidden size";
+    if (t->payload_offset > m->size || t->payload_size > m->size - t->payload_offset) return "has a payload outside the file";
+    return nullptr;
+}
+}  // namespace
+
+extern "C" int uocr_cuda_context_map_model_neighbours(uocr_cuda_context *ctx, const uocr_cuda_model_file_view *m,
+                                                      uint32_t token_capacity, char *error, size_t error_size) {
+    if (!ctx || !m) return fail(ctx, error, error_size, "null context or model view");
+    if (ctx->layers.empty()) return fail(ctx, error, error_size, "map the MoE layers first (uocr_cuda_context_map_model)");
+    if (ctx->file_dense_index >= 0 || ctx->final_norm || !ctx->post_attn_norms.empty() || ctx->lm_head.mapped)
+        return fail(ctx, error, error_size, "the neighbouring tensors are already mapped; call uocr_cuda_context_unmap_model first");
+    if (!m->data || !m->tensors || m->tensor_count == 0) return fail(ctx, error, error_size, "model view without data or tensor directory");
+    CU_TRY(ctx, cudaSetDevice(ctx->device));
+    const uint32_t H = ctx->layers[0].H;
+    const uint8_t *base = (const uint8_t *)m->data;
+    const char *why = nullptr;
+    static const char *kProj[3] = {"gate", "up", "down"};
+
+    // check everything that is present before anything is uploaded
+    const uocr_cuda_tensor_entry *dense[3], *head = find_entry(m, kIdLmHead), *fnorm = find_entry(m, kIdFinalNorm);
+    int dense_present = 0;
+    for (int p = 0; p < 3; ++p) dense_present += (dense[p] = find_entry(m, kIdLayerBase + kIdDenseGate + p)) != nullptr;
+    if (dense_present != 0 && dense_present != 3) return fail(ctx, error, error_size, "layer 0: the dense MLP is incomplete (%d of 3 projections)", dense_present);
+    if (dense_present == 3) {
+        if (token_capacity == 0) return fail(ctx, error, error_size, "the dense MLP needs a token capacity");
+        for (int p = 0; p < 3; ++p)
+            if ((why = check_entry(m, dense[p]))) return fail(ctx, error, error_size, "layer 0: dense MLP %s %s", kProj[p], why);
+        const uint32_t S = dense[0]->logical_shape[0];
+        if (dense[0]->logical_shape[1] != H || dense[1]->logical_shape[0] != S || dense[1]->logical_shape[1] != H ||
+            dense[2]->logical_shape[0] != H || dense[2]->logical_shape[1] != S)
+            return fail(ctx, error, error_size, "layer 0: dense MLP shapes do not fit the hidden size %u", H);
+    }
+    if (head && (why = check_entry(m, head))) return fail(ctx, error, error_size, "LM head %s", why);
+    if (head && head->logical_shape[1] != H) return fail(ctx, error, error_size, "LM head width %u differs from the hidden size %u", head->logical_shape[1], H);
+    if (fnorm && (why = check_norm_entry(m, fnorm, H))) return fail(ctx, error, error_size, "final norm %s", why);
+    const uint32_t decoder_layers = m->first_moe_layer + m->moe_layer_count;
+    std::vector<const uocr_cuda_tensor_entry *> norms(decoder_layers, nullptr);
+    for (uint32_t l = 0; l < decoder_layers; ++l) {
+        norms[l] = find_entry(m, kIdLayerBase + l * kIdLayerStride + kIdPostAttnNorm);
+        if (norms[l] && (why = check_norm_entry(m, norms[l], H))) return fail(ctx, error, error_size, "layer %u: post-attention norm %s", l, why);
+    }
+
+    char inner[512] = {0};
+    if (dense_present == 3) {
+        const uocr_cuda_matrix g = matrix_of(m, dense[0]), u = matrix_of(m, dense[1]), d = matrix_of(m, dense[2]);
+        uint32_t index = 0;
+        if (!uocr_cuda_context_map_dense_mlp(ctx, &g, &u, &d, token_capacity, &index, inner, sizeof inner))
+            return fail(ctx, error, error_size, "layer 0: dense MLP: %s", inner);
+        ctx->file_dense_index = (int)index;
+    }
+    if (head) {
+        const uocr_cuda_matrix w = matrix_of(m, head);
+        if (!uocr_cuda_context_map_lm_head(ctx, &w, inner, sizeof inner)) return fail(ctx, error, error_size, "LM head: %s", inner);
+    }
+    ctx->post_attn_norms.assign(decoder_layers, nullptr);
+    for (uint32_t l = 0; l < decoder_layers; ++l)
+        if (norms[l]) {
+            void *d = nullptr;
+            if (!upload(ctx, base + norms[l]->payload_offset, norms[l]->payload_size, &d, error, error_size)) return 0;
+            ctx->post_attn_norms[l] = (const __half *)d;
+        }
+    if (fnorm) {
+        void *d = nullptr;
+        if (!upload(ctx, base + fnorm->payload_offset, fnorm->payload_size, &d, error, error_size)) return 0;
+        ctx->final_norm = (const __half *)d;
+    }
+    track_memory(ctx);
+    return 1;
+}
+
+extern "C" int uocr_cuda_context_file_dense_mlp_index(const uocr_cuda_context *ctx) { return ctx ? ctx->file_dense_index : -1; }
+extern "C" const void *uocr_cuda_context_post_attn_norm_weight(const uocr_cuda_context *ctx, uint32_t decoder_layer) {
+    return ctx && decoder_layer < ctx->post_attn_norms.size() ? ctx->post_attn_norms[decoder_layer] : nullptr;
+}
+extern "C" const void *uocr_cuda_context_final_norm_weight(const uocr_cuda_context *ctx) { return ctx ? ctx->final_norm : nullptr; }
 
 // ----------------------------------------------------------------------------- map model
 static int upload(uocr_cuda_context *ctx, const void *host, uint64_t bytes, void **out, char *error, size_t error_size) {

@@ -49,6 +49,11 @@ struct uocr_cuda_context *uocr_cuda_engine_attach(const uocr_model_file *file, u
         if (uocr_cuda_context_moe_layer_count(ctx) != 0u) {
             const uint64_t tokens = (uint64_t)(max_batch != 0u ? max_batch : 1u) * (uint64_t)(max_prompt_tokens != 0u ? max_prompt_tokens : 1u);
             const uint32_t capacity = tokens > 65536u ? 65536u : (uint32_t)tokens;
+            /* what the file holds either side of the MoE layers: layer 0's dense MLP, the LM head, the norm weights */
+            if (!uocr_cuda_context_map_model_neighbours(ctx, &view, capacity, error, error_size)) {
+                uocr_cuda_context_destroy(ctx);
+                return NULL;
+            }
             if (!uocr_cuda_context_allocate_runtime_arenas(ctx, max_batch != 0u ? max_batch : 1u, capacity, error, error_size)) {
                 uocr_cuda_context_destroy(ctx);
                 return NULL;

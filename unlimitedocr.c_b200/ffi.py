@@ -59,7 +59,8 @@ EXPORTS = (
     "uocr_cuda_context_set_profile_detail", "uocr_cuda_context_set_profile", "uocr_cuda_context_set_memory_tracker",
     "uocr_cuda_profile_event_name", "uocr_cuda_context_synchronize", "uocr_cuda_context_kernel_launches", "uocr_cuda_context_model_view_bytes",
     "uocr_cuda_context_moe_scratch_bytes", "uocr_cuda_context_map_moe_layer", "uocr_cuda_context_map_model", "uocr_cuda_context_unmap_model",
-    "uocr_cuda_context_moe_layer_count", "uocr_cuda_context_allocate_runtime_arenas",
+    "uocr_cuda_context_moe_layer_count", "uocr_cuda_context_map_model_neighbours", "uocr_cuda_context_file_dense_mlp_index",
+    "uocr_cuda_context_post_attn_norm_weight", "uocr_cuda_context_final_norm_weight", "uocr_cuda_context_allocate_runtime_arenas",
     "uocr_cuda_context_release_runtime_arenas", "uocr_cuda_moe_scratch_size", "uocr_cuda_moe_router",
     "uocr_cuda_moe_dispatch_plan", "uocr_cuda_moe_dispatch_plan_noalloc", "uocr_cuda_moe_debug_dequantize", "uocr_cuda_moe_regime_name", "uocr_cuda_rmsnorm", "uocr_cuda_moe_layer_forward_normed", "uocr_cuda_context_map_dense_mlp",
     "uocr_cuda_dense_mlp_forward", "uocr_cuda_dense_mlp_forward_normed", "uocr_cuda_context_map_lm_head", "uocr_cuda_lm_head_argmax", "uocr_cuda_moe_layer_forward", "uocr_cuda_moe_stack_forward",
@@ -127,6 +128,10 @@ def load_library() -> C.CDLL:
         "uocr_cuda_context_map_lm_head": (C.c_int, [vp, C.POINTER(CMatrix)] + err),
         "uocr_cuda_lm_head_argmax": (C.c_int, [vp, vp, u32, vp, vp] + err),
         "uocr_cuda_context_moe_layer_count": (u32, [vp]),
+        "uocr_cuda_context_map_model_neighbours": (C.c_int, [vp, C.POINTER(CModelFileView), u32] + err),
+        "uocr_cuda_context_file_dense_mlp_index": (C.c_int, [vp]),
+        "uocr_cuda_context_post_attn_norm_weight": (vp, [vp, u32]),
+        "uocr_cuda_context_final_norm_weight": (vp, [vp]),
         "uocr_cuda_context_allocate_runtime_arenas": (C.c_int, [vp, u32, u32] + err),
         "uocr_cuda_context_release_runtime_arenas": (None, [vp]),
         "uocr_cuda_moe_scratch_size": (u64, [u32] * 6),
@@ -277,6 +282,22 @@ class Context:
             self._layer_k[i] = top_k
             self._layer_e[i] = routed_experts
         return int(self._lib.uocr_cuda_context_moe_layer_count(self._h))
+
+    def map_model_neighbours(self, data_address: int, size: int, tensors_address: int, tensor_count: int, *, token_capacity: int,
+                             first_moe_layer: int, moe_layer_count: int) -> dict:
+        """Map what the file holds either side of the MoE layers (uocr_cuda_context_map_model_neighbours): the dense MLP of
+        decoder layer 0, the LM head, the post-attention norm weights and the final norm.  Returns
+        {"dense_mlp": index or None, "lm_head": bool, "post_attn_norm": {layer: device address}, "final_norm": address or None}."""
+        view = CModelFileView(data_address, size, tensors_address, tensor_count, 0, 0, first_moe_layer, moe_layer_count, 1.0)
+        self._check(self._lib.uocr_cuda_context_map_model_neighbours(self._h, C.byref(view), token_capacity, self._err, _ERR))
+        idx = int(self._lib.uocr_cuda_context_file_dense_mlp_index(self._h))
+        norms = {}
+        for layer in range(first_moe_layer + moe_layer_count):
+            p = self._lib.uocr_cuda_context_post_attn_norm_weight(self._h, layer)
+            if p:
+                norms[layer] = int(p)
+        fin = self._lib.uocr_cuda_context_final_norm_weight(self._h)
+        return {"dense_mlp": None if idx < 0 else idx, "post_attn_norm": norms, "final_norm": int(fin) if fin else None}
 
     # -- the steps either side of the MoE layer
     def rmsnorm(self, x, weight, eps: float, n_tokens: int, hidden_size: int, out) -> None:
