@@ -91,7 +91,7 @@ def test_normed_layer_call(pkg, port, n):
     assert err <= MAX_ABS * max(1.0, float(np.max(np.abs(want.out)))) and cos >= MIN_COS, (err, cos)
 
 
-@pytest.mark.parametrize("qname,n", [("q8_0", 1), ("q8_0", 3), ("q8_0", 64), ("q8_0", 200), ("f16", 2), ("f16", 77), ("q4_0", 5)])
+@pytest.mark.parametrize("qname,n", [("q8_0", 1), ("q4_0", 1), ("f16", 1), ("q8_0", 3), ("q8_0", 64), ("q8_0", 200), ("f16", 2), ("f16", 77), ("q4_0", 5)])
 def test_dense_mlp_of_the_first_layer(pkg, port, qname, n):
     rng = np.random.default_rng(300 + n)
     H, S = FULL["H"], DENSE_INTER

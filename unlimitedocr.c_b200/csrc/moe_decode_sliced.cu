@@ -83,6 +83,7 @@ constexpr int kSlBlocksPerWarp = kSlH / 16 / 16;            // 5 blocks of 16 ou
 
 struct SlicedParams {
     static constexpr bool kInline = false;
+    static constexpr bool kDense = false;
     const DLayer *layers;
     uint32_t first, count;
     const __half *hidden_in;
@@ -109,6 +110,12 @@ struct SlicedParams {
 struct SlicedParamsInline : SlicedParams {
     static constexpr bool kInline = true;
     uint4 inline_x[kSlH * 2 / 16];  // fp16 activations
+};
+// A dense SwiGLU MLP (the first decoder layer's) through the same kernel: `layers` points at ONE pseudo layer whose
+// dec_units hold gridDim.x units of 64 intermediate columns each; every CTA works like a shared-MLP CTA on unit blockIdx.x,
+// nothing is routed.  Units beyond the MLP's width hold zeros (the grid is a multiple of the cluster size).
+struct SlicedParamsDense : SlicedParams {
+    static constexpr bool kDense = true;
 };
 
 __device__ __forceinline__ void red_add_u64(unsigned long long *p, unsigned long long v) {
@@ -206,9 +213,10 @@ __global__ void __launch_bounds__(kSlThreads, 1) decode_sliced_kernel(const __gr
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t = lane & 3;                              // MMA row group = B column / lane in quad
     const uint32_t G = gridDim.x, cta = blockIdx.x;
-    const bool routed = cta < (uint32_t)kSlRouted;
+    const bool routed = !Params::kDense && cta < (uint32_t)kSlRouted;
     const uint32_t slot = routed ? cta / kSlRoutedPerSlot : (uint32_t)K;
-    const uint32_t fg = routed ? cta % kSlRoutedPerSlot : cta - kSlRouted;     // 64-wide slice of F (of S)
+    const uint32_t fg = Params::kDense ? cta : routed ? cta % kSlRoutedPerSlot : cta - kSlRouted;     // 64-wide slice of F (of S)
+    constexpr uint32_t kSharedUnit0 = Params::kDense ? 0u : (uint32_t)(kSlE * kSlRoutedPerSlot);         // first unit of the non-routed CTAs
     uint32_t *status = prm.status;
     const uint32_t crank = cluster_rank(), csize = cluster_size();
     const uint32_t R = prm.replicas;                                    // accumulator replicas (1, 2 or 4)
@@ -333,7 +341,7 @@ __global__ void __launch_bounds__(kSlThreads, 1) decode_sliced_kernel(const __gr
     // ---- prologue: everything the first layer can fetch before its activations are arranged
     uint32_t copy_phase = 0;
     if (routed) load_router(s_layers[0]);
-    else fetch_unit(s_layers[0].dec_units + (size_t)(kSlE * kSlRoutedPerSlot + fg) * Bl::kBytes);
+    else fetch_unit(s_layers[0].dec_units + (size_t)(kSharedUnit0 + fg) * Bl::kBytes);
     if (!routed) build_x_frags();      // routed CTAs arrange their activations while their weights are on the way
     __syncthreads();
 
@@ -596,7 +604,7 @@ __global__ void __launch_bounds__(kSlThreads, 1) decode_sliced_kernel(const __gr
         }
         if (!last) {
             if (routed) load_router(s_layers[li + 1]);
-            else fetch_unit(s_layers[li + 1].dec_units + (size_t)(kSlE * kSlRoutedPerSlot + fg) * Bl::kBytes);
+            else fetch_unit(s_layers[li + 1].dec_units + (size_t)(kSharedUnit0 + fg) * Bl::kBytes);
         }
 
         // ---- the layer's output = next layer's input: every accumulator row once all G CTAs have added to it,
@@ -767,9 +775,9 @@ cudaError_t build_decode_units(const DLayer &L, uint8_t *out, cudaStream_t st) {
 }
 
 template <int QT>
-static void launch_config(cudaLaunchConfig_t *cfg, cudaLaunchAttribute *attrs, int cluster, cudaStream_t st) {
+static void launch_config(cudaLaunchConfig_t *cfg, cudaLaunchAttribute *attrs, int cluster, cudaStream_t st, uint32_t grid = kSlUnits) {
     *cfg = cudaLaunchConfig_t{};
-    cfg->gridDim = dim3(kSlUnits); cfg->blockDim = dim3(kSlThreads);
+    cfg->gridDim = dim3(grid); cfg->blockDim = dim3(kSlThreads);
     cfg->dynamicSmemBytes = SlSmem<QT>::kTotal; cfg->stream = st;
     attrs[0].id = cudaLaunchAttributeClusterDimension;
     attrs[0].val.clusterDim.x = (unsigned)cluster; attrs[0].val.clusterDim.y = 1; attrs[0].val.clusterDim.z = 1;
@@ -784,6 +792,9 @@ static cudaError_t prepare_sliced(int *ok) {
                                            (int)SlSmem<QT>::kTotal);
     if (err != cudaSuccess) return err;
     err = cudaFuncSetAttribute(decode_sliced_kernel<QT, SlicedParamsInline>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               (int)SlSmem<QT>::kTotal);
+    if (err != cudaSuccess) return err;
+    err = cudaFuncSetAttribute(decode_sliced_kernel<QT, SlicedParamsDense>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                (int)SlSmem<QT>::kTotal);
     if (err != cudaSuccess) return err;
     cudaLaunchConfig_t cfg;
@@ -822,10 +833,10 @@ bool decode_sliced_supported(const DLayer *layers, uint32_t first, uint32_t coun
 }
 
 template <int QT, class Params>
-static cudaError_t launch_one(const Params &prm, int cluster, cudaStream_t st) {
+static cudaError_t launch_one(const Params &prm, int cluster, cudaStream_t st, uint32_t grid = kSlUnits) {
     cudaLaunchConfig_t cfg;
     cudaLaunchAttribute attrs[2];
-    launch_config<QT>(&cfg, attrs, cluster, st);
+    launch_config<QT>(&cfg, attrs, cluster, st, grid);
     return cudaLaunchKernelEx(&cfg, decode_sliced_kernel<QT, Params>, prm);
 }
 
@@ -866,6 +877,62 @@ cudaError_t launch_decode_sliced(const DLayer *h_layers, const DLayer *d_layers,
     }
     if (err != cudaSuccess) return err;
     *acc_base = (*acc_base + count) % kSlAccBuffers;
+    ++*launches;
+    return cudaSuccess;
+}
+
+// ---- a dense SwiGLU MLP of the model's hidden size through the same kernel, one token --------------------------------
+// Units of 64 intermediate columns, padded with all-zero units to a multiple of the cluster size; every unit needs an SM
+// of its own (the CTAs wait for one another), so the width is limited by the device.
+uint32_t decode_dense_units(uint32_t hidden, uint32_t inter, int gate_qtype, int up_qtype, int down_qtype) {
+    int dev = 0, sms = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64 || g_sliced_cluster[dev] == 0) return 0;
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
+    if (hidden != (uint32_t)kSlH || inter == 0 || inter % 64 != 0) return 0;
+    if ((gate_qtype != UOCR_QT_Q4 && gate_qtype != UOCR_QT_Q8) || up_qtype != gate_qtype || down_qtype != gate_qtype) return 0;
+    const uint32_t units = (inter / 64 + kSlCluster - 1) / kSlCluster * kSlCluster;
+    return units <= (uint32_t)sms ? units : 0;
+}
+
+size_t decode_dense_units_bytes(int qtype, uint32_t units) {
+    return (size_t)units * (qtype == UOCR_QT_Q4 ? SlBlob<UOCR_QT_Q4>::kBytes : SlBlob<UOCR_QT_Q8>::kBytes);
+}
+
+// out: decode_dense_units_bytes() of device memory
+cudaError_t build_dense_units(const DMatrix &gate, const DMatrix &up, const DMatrix &down, uint32_t units, uint8_t *out, cudaStream_t st) {
+    cudaError_t err = cudaMemsetAsync(out, 0, decode_dense_units_bytes(gate.qtype, units), st);
+    if (err != cudaSuccess) return err;
+    RepackSrc src{};
+    src.gate_w = gate.w; src.up_w = up.w; src.down_w = down.w;
+    src.gate_s = gate.s; src.up_s = up.s; src.down_s = down.s;
+    src.inter = gate.rows;
+    if (gate.qtype == UOCR_QT_Q4) repack_units_kernel<UOCR_QT_Q4><<<gate.rows / 64, 256, 0, st>>>(src, out);
+    else repack_units_kernel<UOCR_QT_Q8><<<gate.rows / 64, 256, 0, st>>>(src, out);
+    return cudaGetLastError();
+}
+
+// d_layer: device copy of a DLayer whose dec_units point at the units; out = fp16( MLP(hidden) + residual ).  Accumulators,
+// their rotation and the knobs as for launch_decode_sliced.
+cudaError_t launch_decode_dense(const DLayer *d_layer, int qtype, uint32_t units, const __half *hidden, const __half *residual,
+                                __half *out, unsigned long long *acc, uint32_t *acc_base, uint32_t *status, const SlicedKnobs &knobs,
+                                cudaStream_t st, uint64_t *launches) {
+    int dev = 0;
+    cudaError_t err = cudaGetDevice(&dev);
+    if (err != cudaSuccess) return err;
+    if (dev < 0 || dev >= 64 || g_sliced_cluster[dev] == 0 || units == 0 || units % kSlCluster != 0) return cudaErrorNotSupported;
+    SlicedParamsDense prm{};
+    prm.layers = d_layer; prm.first = 0; prm.count = 1;
+    prm.hidden_in = hidden; prm.residual0 = residual; prm.chain_residual = 0;
+    prm.out = out; prm.acc = acc; prm.acc_base = *acc_base;
+    prm.replicas = (knobs.replicas == 1 || knobs.replicas == 2 || knobs.replicas == 4) ? knobs.replicas : 1u;
+    prm.status = status;
+    prm.spin_limit = knobs.spin_limit_cycles > 0 ? knobs.spin_limit_cycles : kSpinLimit;
+    prm.expect_extra = knobs.expect_extra;
+    prm.poll_sleep_ns = knobs.poll_sleep_ns;
+    err = qtype == UOCR_QT_Q4 ? launch_one<UOCR_QT_Q4, SlicedParamsDense>(prm, g_sliced_cluster[dev], st, units)
+                              : launch_one<UOCR_QT_Q8, SlicedParamsDense>(prm, g_sliced_cluster[dev], st, units);
+    if (err != cudaSuccess) return err;
+    *acc_base = (*acc_base + 1) % kSlAccBuffers;
     ++*launches;
     return cudaSuccess;
 }

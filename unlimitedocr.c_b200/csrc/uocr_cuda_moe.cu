@@ -84,6 +84,12 @@ cudaError_t launch_decode_sliced(const DLayer *h_layers, const DLayer *d_layers,
                                  uint32_t *acc_base, uint32_t *status,
                                  float *dbg_logits, float *dbg_probs, uint32_t *ids_out, float *wts_out,
                                  unsigned long long *trace, const SlicedKnobs &knobs, cudaStream_t st, uint64_t *launches);
+uint32_t decode_dense_units(uint32_t hidden, uint32_t inter, int gate_qtype, int up_qtype, int down_qtype);
+size_t decode_dense_units_bytes(int qtype, uint32_t units);
+cudaError_t build_dense_units(const DMatrix &gate, const DMatrix &up, const DMatrix &down, uint32_t units, uint8_t *out, cudaStream_t st);
+cudaError_t launch_decode_dense(const DLayer *d_layer, int qtype, uint32_t units, const __half *hidden, const __half *residual,
+                                __half *out, unsigned long long *acc, uint32_t *acc_base, uint32_t *status, const SlicedKnobs &knobs,
+                                cudaStream_t st, uint64_t *launches);
 cudaError_t launch_decode_stack(const DLayer *h_layers, const DLayer *d_layers, uint32_t first, uint32_t count,
                                 const __half *hidden, const __half *residual0, int chain_residual,
                                 const float *injected, __half *out, __half *hbuf0, __half *hbuf1, __half *mid,
@@ -113,6 +119,8 @@ struct uocr_cuda_context {
         float *out_f32 = nullptr;                      // [capacity][H] (the tensor-core path keeps fp16 rows in it)
         uint4 *tiles_gu = nullptr, *tiles_dn = nullptr;
         uint32_t *counts = nullptr;
+        uint32_t units = 0;                            // one-token path through the decode kernel: 64-column units (0: not built)
+        DLayer *d_layer = nullptr;                     // device copy of the pseudo layer that points at the units
         void *scratch = nullptr;
         uint64_t scratch_bytes = 0;
     };
@@ -1221,6 +1229,26 @@ extern "C" int uocr_cuda_context_map_dense_mlp(uocr_cuda_context *ctx, const uoc
     D.scratch = base; D.scratch_bytes = total;
     D.x_norm = (__half *)(base + o_x); D.mid = (__half *)(base + o_mid); D.out_f32 = (float *)(base + o_out);
     D.tiles_gu = (uint4 *)(base + o_tg); D.tiles_dn = (uint4 *)(base + o_td); D.counts = (uint32_t *)(base + o_cnt);
+    // One token: the single-token decode kernel on a slice-major copy of the three matrices (every CTA a 64-column unit)
+    if (ctx->fused_decode && ctx->sliced_decode) {
+        const uint32_t units = uocr::decode_dense_units(H, S, D.gate.qtype, D.up.qtype, D.down.qtype);
+        if (units != 0) {
+            const size_t bytes = uocr::decode_dense_units_bytes(D.gate.qtype, units);
+            uint8_t *blob = nullptr;
+            CU_TRY(ctx, cudaMalloc(&blob, bytes));
+            ctx->weight_allocs.push_back(blob);
+            CU_TRY(ctx, uocr::build_dense_units(D.gate, D.up, D.down, units, blob, ctx->stream));
+            DLayer pseudo{};
+            pseudo.H = H; pseudo.S = S; pseudo.expert_qtype = D.gate.qtype; pseudo.dec_units = blob;
+            void *dl = nullptr;
+            CU_TRY(ctx, cudaMalloc(&dl, sizeof(DLayer)));
+            ctx->weight_allocs.push_back(dl);
+            CU_TRY(ctx, cudaMemcpyAsync(dl, &pseudo, sizeof(DLayer), cudaMemcpyHostToDevice, ctx->stream));
+            CU_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+            ctx->weight_bytes += bytes;
+            D.units = units; D.d_layer = (DLayer *)dl;
+        }
+    }
     ctx->dense.push_back(D);
     ctx->dense_scratch_bytes += total;
     if (out_index) *out_index = (uint32_t)ctx->dense.size() - 1;
@@ -1243,6 +1271,11 @@ static int dense_forward(uocr_cuda_context *ctx, uint32_t index, const __half *d
         g.counts = D.counts - 2;                          // the shared MLP's two counters are entries 2 and 3
         CU_TRY(ctx, uocr::launch_gemm_shared(L, s, g, d_hidden, n, ctx->stream, &ctx->launches));
         CU_TRY(ctx, uocr::launch_add_rows((const __half *)D.out_f32, d_residual, (size_t)n * D.H, d_out, ctx->stream, &ctx->launches));
+        return 1;
+    }
+    if (n == 1 && D.units != 0) {
+        CU_TRY(ctx, uocr::launch_decode_dense(D.d_layer, D.gate.qtype, D.units, d_hidden, d_residual, d_out, decode_accumulators(ctx),
+                                              &ctx->acc_base, ctx->status, take_decode_knobs(ctx), ctx->stream, &ctx->launches));
         return 1;
     }
     if (!uocr::dense_small_supported(D.H, D.S)) return fail(ctx, error, error_size, "dense MLP shape not supported by the matrix-vector path");
