@@ -726,8 +726,26 @@ def measure_decode(pkg, torch, dist, rank: int, local_rank: int, world: int, flu
     assert np.array_equal(host_out, d_out.cpu().numpy().view(np.uint16)), "host and device entry points disagree"
     clocks = sampler.stop() if sampler else None
     timeline = None
+    per_layer = None
     if rank == 0 and args.extras == "all":
         timeline = decode_timeline(ctx, torch, d_hidden, d_out, flush_l2, float((clocks or {}).get("sm_mhz") or 1965.0))
+        # The same token as eleven separate calls, each with its post-attention RMSNorm, the way a decoder whose attention
+        # sits between the MoE layers has to make them (uocr_cuda_moe_layer_forward_normed; the attention itself is not here).
+        norm_w = torch.ones(FULL["H"], dtype=torch.float16, device="cuda")
+        ping, pong = d_hidden.clone(), torch.zeros_like(d_hidden)
+
+        def layer_calls():
+            a, b = ping, pong
+            for l in range(N_LAYERS):
+                ctx.layer_forward_normed(l, a, norm_w, 1.0e-6, 1, b)
+                a, b = b, a
+
+        l0 = ctx.kernel_launches
+        pl_ms = timed_steps(torch, None, 1, stream, flush_l2, layer_calls, max(5, min(args.steps, 20)), 3)
+        per_layer = {"workload": "the decode token as 11 calls of RMSNorm + MoE layer (one call per decoder layer)",
+                     "us_per_token": sum(pl_ms) / len(pl_ms) * 1e3,
+                     "gpu_launches_per_token": (ctx.kernel_launches - l0) // (max(5, min(args.steps, 20)) + 3)}
+        ctx.synchronize()
 
     t = torch.tensor([ms_per_step, e2e_ms], dtype=torch.float64, device="cuda")
     if world > 1:
@@ -762,6 +780,8 @@ def measure_decode(pkg, torch, dist, rank: int, local_rank: int, world: int, flu
     }
     if timeline is not None:
         line["decode_timeline_us"] = timeline
+    if per_layer is not None:
+        line["decode_per_layer_calls"] = per_layer
     if not args.no_cpu_baseline:
         from oracle import oracle as orc
         threads = orc.host_threads()

@@ -139,6 +139,15 @@ def test_dense_mlp_normed_and_argument_checks(pkg, port):
         ctx.synchronize()
         err, cos = closeness(out.cpu().numpy().astype(np.float32), want)
         assert err <= MAX_ABS * max(1.0, float(np.max(np.abs(want)))) and cos >= MIN_COS, (err, cos)
+        # one token: the norm runs inside the single-token kernel; bit for bit the norm kernel followed by the plain call
+        one, xg, two = (torch.zeros((1, H), dtype=torch.float16, device="cuda") for _ in range(3))
+        ctx.dense_mlp_forward_normed(idx, dev(stream_rows[:1]), dev(w), EPS, 1, one)
+        ctx.rmsnorm(dev(stream_rows[:1]), dev(w), EPS, 1, H, xg)
+        ctx.dense_mlp_forward(idx, xg, 1, two, residual=dev(stream_rows[:1]))
+        ctx.synchronize()
+        assert torch.equal(one, two)
+        err, cos = closeness(one.cpu().numpy().astype(np.float32), want[:1])
+        assert err <= MAX_ABS * max(1.0, float(np.max(np.abs(want)))) and cos >= MIN_COS, (err, cos)
         bad = quant.make_matrix(quant.QTYPE_Q8_0, rng.standard_normal((S, H + 64), dtype=np.float32) * 0.02)
         with pytest.raises(pkg.UocrCudaError, match="shape"):
             ctx.map_dense_mlp(gate, bad, down, token_capacity=8)

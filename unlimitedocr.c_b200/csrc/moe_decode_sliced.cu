@@ -103,6 +103,10 @@ struct SlicedParams {
     long long spin_limit;         // cycles a wait for other CTAs may take before the kernel gives up
     uint32_t poll_sleep_ns;       // pause between two polls of the layer accumulator (0: none)
     uint32_t expect_extra;        // test hook: contributions the poll expects beyond the CTAs there are (0 in production)
+    const __half *router0;        // router matrix and unit blobs of the first layer of the launch (the same pointers as in
+    const uint8_t *units0;        // layers[first]): every CTA starts its first fetch from them before it has read the layer table
+    const __half *norm_weight;    // optional fp16[H]: the first layer's input is RMSNorm(hidden_in) * norm_weight (residual0 stays as given)
+    float norm_eps;
 };
 // The same with the first layer's input (and, with chain_residual, its residual) carried in the launch parameters:
 // a host-buffer call then needs no copy.  A kernel instantiation of its own, so that calls on device buffers keep a
@@ -233,31 +237,6 @@ __global__ void __launch_bounds__(kSlThreads, 1) decode_sliced_kernel(const __gr
     }
     // every CTA of the cluster has initialised its barriers before any peer arrives on them
     asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-    {
-        const uint32_t words = prm.count * (uint32_t)(sizeof(DLayer) / 4);
-        const uint32_t *src = reinterpret_cast<const uint32_t *>(prm.layers + prm.first);
-        uint32_t *dst = reinterpret_cast<uint32_t *>(s_layers);
-        for (uint32_t i = tid; i < words; i += kSlThreads) dst[i] = src[i];
-        for (int i = tid; i < kSlGroups * 8 * 16; i += kSlThreads) s_xf[i] = 0u;      // the columns no group writes
-        for (int i = tid; i < 4 * 8 * 16; i += kSlThreads) s_midf[i] = 0u;
-    }
-    // the first layer's input, and its residual in registers
-    float res0[3] = {0.f, 0.f, 0.f};
-    {
-        const __half *xin = prm.hidden_in, *rin = prm.residual0;
-        if constexpr (Params::kInline) {
-            xin = reinterpret_cast<const __half *>(prm.inline_x);
-            rin = prm.chain_residual ? xin : nullptr;
-        }
-        for (int h = tid; h < H; h += kSlThreads) s_x[h] = xin[h];
-        if (rin != nullptr) {
-#pragma unroll
-            for (int i = 0; i < 3; ++i)
-                if (tid + i * kSlThreads < H) res0[i] = __half2float(rin[tid + i * kSlThreads]);
-        }
-    }
-    __syncthreads();
-
     // ---- helpers --------------------------------------------------------------------------------------
     // mantissa bytes and offset corrections of the activations in s_x
     // (by warps 0 and 2 .. 10: warp 1 of a routed CTA is busy with the exact routing at that time)
@@ -322,14 +301,73 @@ __global__ void __launch_bounds__(kSlThreads, 1) decode_sliced_kernel(const __gr
     auto fetch_unit = [&](const uint8_t *blob) { fetch_gate_up(blob); fetch_down(blob); };
     // This CTA's quarter of the router matrix (experts 16 crank .. +15, fp16 [E][H]) as MMA A fragments: warp w holds
     // columns 80 w .. 80 w + 79 (five k steps), lane (g, t) the columns 4t .. 4t + 3 of each step for rows g and g + 8.
-    auto load_router = [&](const DLayer &L) {
-        const __half *r0 = L.router + (size_t)(16 * crank + g) * H + 80 * warp + 4 * t;
+    auto load_router = [&](const __half *router) {
+        const __half *r0 = router + (size_t)(16 * crank + g) * H + 80 * warp + 4 * t;
 #pragma unroll
         for (int i = 0; i < 5; ++i) {
             rtr[i][0] = __ldg(reinterpret_cast<const uint2 *>(r0 + 16 * i));
             rtr[i][1] = __ldg(reinterpret_cast<const uint2 *>(r0 + 8 * H + 16 * i));
         }
     };
+    // ---- everything the first layer can fetch before its activations are arranged, asked for before anything else is read
+    if (routed) load_router(prm.router0);
+    else fetch_unit(prm.units0 + (size_t)(kSharedUnit0 + fg) * Bl::kBytes);
+    {
+        const uint32_t words = prm.count * (uint32_t)(sizeof(DLayer) / 4);
+        const uint32_t *src = reinterpret_cast<const uint32_t *>(prm.layers + prm.first);
+        uint32_t *dst = reinterpret_cast<uint32_t *>(s_layers);
+        for (uint32_t i = tid; i < words; i += kSlThreads) dst[i] = src[i];
+        for (int i = tid; i < kSlGroups * 8 * 16; i += kSlThreads) s_xf[i] = 0u;      // the columns no group writes
+        for (int i = tid; i < 4 * 8 * 16; i += kSlThreads) s_midf[i] = 0u;
+    }
+    // the first layer's input, and its residual in registers
+    float res0[3] = {0.f, 0.f, 0.f};
+    {
+        const __half *xin = prm.hidden_in, *rin = prm.residual0;
+        if constexpr (Params::kInline) {
+            xin = reinterpret_cast<const __half *>(prm.inline_x);
+            rin = prm.chain_residual ? xin : nullptr;
+        }
+        for (int h = tid; h < H; h += kSlThreads) s_x[h] = xin[h];
+        if (rin != nullptr) {
+#pragma unroll
+            for (int i = 0; i < 3; ++i)
+                if (tid + i * kSlThreads < H) res0[i] = __half2float(rin[tid + i * kSlThreads]);
+        }
+    }
+    __syncthreads();
+    if (prm.norm_weight != nullptr) {
+        // The post-attention RMSNorm in front of the layer, with the arithmetic of rmsnorm_kernel (128 threads take every
+        // 128th pair, a shuffle tree per warp, the four warp sums added in order), so that a call with the norm folded in
+        // equals the norm kernel followed by the plain call bit for bit.
+        float *s_norm = s_rp;
+        if (tid < 128) {
+            const __half2 *xr = reinterpret_cast<const __half2 *>(s_x);
+            float ss = 0.f;
+            for (int i = tid; i < H / 2; i += 128) {
+                const float2 v = __half22float2(xr[i]);
+                ss = fmaf(v.x, v.x, ss);
+                ss = fmaf(v.y, v.y, ss);
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+            if (lane == 0) s_norm[warp] = ss;
+        }
+        __syncthreads();
+        float total = 0.f;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) total += s_norm[i];
+        const float inv = 1.0f / sqrtf(total / (float)H + prm.norm_eps);
+        const __half2 *wr = reinterpret_cast<const __half2 *>(prm.norm_weight);
+        __half2 *xw = reinterpret_cast<__half2 *>(s_x);
+        __syncthreads();          // every thread has read the four sums before s_rp is used again
+        for (int i = tid; i < H / 2; i += kSlThreads) {
+            const float2 v = __half22float2(xw[i]), gw = __half22float2(wr[i]);
+            xw[i] = __floats2half2_rn(v.x * inv * gw.x, v.y * inv * gw.y);
+        }
+        __syncthreads();
+    }
+
     uint32_t lg_phase = 0;
 
 #define UOCR_SL_TRACE(point)                                                                              \
@@ -338,10 +376,7 @@ __global__ void __launch_bounds__(kSlThreads, 1) decode_sliced_kernel(const __gr
             prm.trace[((size_t)cta * prm.count + li) * kSlTracePoints + (point)] = clock64();             \
     } while (0)
 
-    // ---- prologue: everything the first layer can fetch before its activations are arranged
     uint32_t copy_phase = 0;
-    if (routed) load_router(s_layers[0]);
-    else fetch_unit(s_layers[0].dec_units + (size_t)(kSharedUnit0 + fg) * Bl::kBytes);
     if (!routed) build_x_frags();      // routed CTAs arrange their activations while their weights are on the way
     __syncthreads();
 
@@ -603,7 +638,7 @@ __global__ void __launch_bounds__(kSlThreads, 1) decode_sliced_kernel(const __gr
             __threadfence();
         }
         if (!last) {
-            if (routed) load_router(s_layers[li + 1]);
+            if (routed) load_router(s_layers[li + 1].router);
             else fetch_unit(s_layers[li + 1].dec_units + (size_t)(kSharedUnit0 + fg) * Bl::kBytes);
         }
 
@@ -851,7 +886,8 @@ cudaError_t launch_decode_sliced(const DLayer *h_layers, const DLayer *d_layers,
                                  const float *injected,
                                  __half *out, uint32_t *host_status, unsigned long long *acc, uint32_t *acc_base, uint32_t *status,
                                  float *dbg_logits, float *dbg_probs, uint32_t *ids_out, float *wts_out,
-                                 unsigned long long *trace, const SlicedKnobs &knobs, cudaStream_t st, uint64_t *launches) {
+                                 unsigned long long *trace, const SlicedKnobs &knobs, cudaStream_t st, uint64_t *launches,
+                                 const __half *norm_weight, float norm_eps) {
     int dev = 0;
     cudaError_t err = cudaGetDevice(&dev);
     if (err != cudaSuccess) return err;
@@ -867,6 +903,8 @@ cudaError_t launch_decode_sliced(const DLayer *h_layers, const DLayer *d_layers,
     prm.expect_extra = knobs.expect_extra;
     prm.poll_sleep_ns = knobs.poll_sleep_ns;
     prm.dbg_logits = dbg_logits; prm.dbg_probs = dbg_probs; prm.ids_out = ids_out; prm.wts_out = wts_out; prm.trace = trace;
+    prm.norm_weight = h_inline != nullptr ? nullptr : norm_weight; prm.norm_eps = norm_eps;
+    prm.router0 = h_layers[first].router; prm.units0 = h_layers[first].dec_units;
     const bool q4 = h_layers[first].expert_qtype == UOCR_QT_Q4;
     if (h_inline != nullptr) {
         memcpy(prm.inline_x, h_inline, sizeof(prm.inline_x));
@@ -911,11 +949,11 @@ cudaError_t build_dense_units(const DMatrix &gate, const DMatrix &up, const DMat
     return cudaGetLastError();
 }
 
-// d_layer: device copy of a DLayer whose dec_units point at the units; out = fp16( MLP(hidden) + residual ).  Accumulators,
+// d_layer: device copy of a DLayer whose dec_units point at the units (unit_blobs, the same address); out = fp16( MLP(hidden) + residual ).  Accumulators,
 // their rotation and the knobs as for launch_decode_sliced.
-cudaError_t launch_decode_dense(const DLayer *d_layer, int qtype, uint32_t units, const __half *hidden, const __half *residual,
+cudaError_t launch_decode_dense(const DLayer *d_layer, const uint8_t *unit_blobs, int qtype, uint32_t units, const __half *hidden, const __half *residual,
                                 __half *out, unsigned long long *acc, uint32_t *acc_base, uint32_t *status, const SlicedKnobs &knobs,
-                                cudaStream_t st, uint64_t *launches) {
+                                cudaStream_t st, uint64_t *launches, const __half *norm_weight, float norm_eps) {
     int dev = 0;
     cudaError_t err = cudaGetDevice(&dev);
     if (err != cudaSuccess) return err;
@@ -929,6 +967,8 @@ cudaError_t launch_decode_dense(const DLayer *d_layer, int qtype, uint32_t units
     prm.spin_limit = knobs.spin_limit_cycles > 0 ? knobs.spin_limit_cycles : kSpinLimit;
     prm.expect_extra = knobs.expect_extra;
     prm.poll_sleep_ns = knobs.poll_sleep_ns;
+    prm.norm_weight = norm_weight; prm.norm_eps = norm_eps;
+    prm.router0 = nullptr; prm.units0 = unit_blobs;
     err = qtype == UOCR_QT_Q4 ? launch_one<UOCR_QT_Q4, SlicedParamsDense>(prm, g_sliced_cluster[dev], st, units)
                               : launch_one<UOCR_QT_Q8, SlicedParamsDense>(prm, g_sliced_cluster[dev], st, units);
     if (err != cudaSuccess) return err;

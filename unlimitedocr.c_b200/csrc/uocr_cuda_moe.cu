@@ -83,13 +83,14 @@ cudaError_t launch_decode_sliced(const DLayer *h_layers, const DLayer *d_layers,
                                  const float *injected, __half *out, uint32_t *host_status, unsigned long long *acc,
                                  uint32_t *acc_base, uint32_t *status,
                                  float *dbg_logits, float *dbg_probs, uint32_t *ids_out, float *wts_out,
-                                 unsigned long long *trace, const SlicedKnobs &knobs, cudaStream_t st, uint64_t *launches);
+                                 unsigned long long *trace, const SlicedKnobs &knobs, cudaStream_t st, uint64_t *launches,
+                                 const __half *norm_weight = nullptr, float norm_eps = 0.f);
 uint32_t decode_dense_units(uint32_t hidden, uint32_t inter, int gate_qtype, int up_qtype, int down_qtype);
 size_t decode_dense_units_bytes(int qtype, uint32_t units);
 cudaError_t build_dense_units(const DMatrix &gate, const DMatrix &up, const DMatrix &down, uint32_t units, uint8_t *out, cudaStream_t st);
-cudaError_t launch_decode_dense(const DLayer *d_layer, int qtype, uint32_t units, const __half *hidden, const __half *residual,
+cudaError_t launch_decode_dense(const DLayer *d_layer, const uint8_t *unit_blobs, int qtype, uint32_t units, const __half *hidden, const __half *residual,
                                 __half *out, unsigned long long *acc, uint32_t *acc_base, uint32_t *status, const SlicedKnobs &knobs,
-                                cudaStream_t st, uint64_t *launches);
+                                cudaStream_t st, uint64_t *launches, const __half *norm_weight = nullptr, float norm_eps = 0.f);
 cudaError_t launch_decode_stack(const DLayer *h_layers, const DLayer *d_layers, uint32_t first, uint32_t count,
                                 const __half *hidden, const __half *residual0, int chain_residual,
                                 const float *injected, __half *out, __half *hbuf0, __half *hbuf1, __half *mid,
@@ -121,6 +122,7 @@ struct uocr_cuda_context {
         uint32_t *counts = nullptr;
         uint32_t units = 0;                            // one-token path through the decode kernel: 64-column units (0: not built)
         DLayer *d_layer = nullptr;                     // device copy of the pseudo layer that points at the units
+        const uint8_t *unit_blobs = nullptr;
         void *scratch = nullptr;
         uint64_t scratch_bytes = 0;
     };
@@ -1065,9 +1067,11 @@ static uocr::GemmScratch gemm_scratch(uocr_cuda_context *ctx, const Scratch &s, 
     return g;
 }
 
+// norm_weight: only for a call that takes the single-token decode kernel (the caller checks): the kernel then normalises
+// d_hidden itself
 static int layer_forward(uocr_cuda_context *ctx, uint32_t layer, const __half *d_hidden, const __half *d_residual,
                          const float *d_injected, uint32_t n, __half *d_out, const uocr_cuda_moe_debug_outputs *dbg,
-                         char *error, size_t error_size) {
+                         char *error, size_t error_size, const __half *norm_weight = nullptr, float norm_eps = 0.f) {
     const DLayer &L = ctx->layers[layer];
     ArenaLayout a;
     Scratch s = carve(ctx, L, n, &a);
@@ -1078,7 +1082,7 @@ static int layer_forward(uocr_cuda_context *ctx, uint32_t layer, const __half *d
         CU_TRY(ctx, uocr::launch_decode_sliced(ctx->layers.data(), ctx->d_layers, layer, 1, d_hidden, d_residual, nullptr, 0,
                                                d_injected, d_out, nullptr, decode_accumulators(ctx), &ctx->acc_base, ctx->status,
                                                logits, probs, s.top_ids, s.top_weights, nullptr, take_decode_knobs(ctx), ctx->stream,
-                                               &ctx->launches));
+                                               &ctx->launches, norm_weight, norm_eps));
     } else if (n == 1 && ctx->fused_decode && uocr::decode_supported(ctx->layers.data(), layer, 1)) {
         ProfScope span(ctx, kPfFused, ctx->stream);
         CU_TRY(ctx, uocr::launch_decode_stack(ctx->layers.data(), ctx->d_layers, layer, 1, d_hidden, d_residual, 0,
@@ -1169,6 +1173,13 @@ extern "C" int uocr_cuda_moe_layer_forward_normed(uocr_cuda_context *ctx, uint32
     if (!check_call(ctx, layer, n, error, error_size)) return 0;
     if (!d_stream || !d_norm_weight_f16 || !d_out) return fail(ctx, error, error_size, "null argument");
     const DLayer &L = ctx->layers[layer];
+    if (n == 1 && ctx->fused_decode && ctx->sliced_decode && uocr::decode_sliced_supported(ctx->layers.data(), layer, 1)) {
+        // one token: the decode kernel normalises its input itself (same arithmetic as the norm kernel), one launch
+        if (!(eps >= 0.f)) return fail(ctx, error, error_size, "RMSNorm: eps must not be negative");
+        CU_TRY(ctx, cudaSetDevice(ctx->device));
+        return layer_forward(ctx, layer, (const __half *)d_stream, (const __half *)d_stream, nullptr, 1, (__half *)d_out, dbg, error,
+                             error_size, (const __half *)d_norm_weight_f16, eps);
+    }
     ArenaLayout a;
     carve(ctx, L, ctx->token_capacity, &a);
     __half *x = (__half *)(ctx->arena + a.d_in);          // the staging rows of the host-buffer calls: free during a device call
@@ -1246,7 +1257,7 @@ extern "C" int uocr_cuda_context_map_dense_mlp(uocr_cuda_context *ctx, const uoc
             CU_TRY(ctx, cudaMemcpyAsync(dl, &pseudo, sizeof(DLayer), cudaMemcpyHostToDevice, ctx->stream));
             CU_TRY(ctx, cudaStreamSynchronize(ctx->stream));
             ctx->weight_bytes += bytes;
-            D.units = units; D.d_layer = (DLayer *)dl;
+            D.units = units; D.d_layer = (DLayer *)dl; D.unit_blobs = blob;
         }
     }
     ctx->dense.push_back(D);
@@ -1257,7 +1268,7 @@ extern "C" int uocr_cuda_context_map_dense_mlp(uocr_cuda_context *ctx, const uoc
 }
 
 static int dense_forward(uocr_cuda_context *ctx, uint32_t index, const __half *d_hidden, const __half *d_residual, uint32_t n,
-                         __half *d_out, char *error, size_t error_size) {
+                         __half *d_out, char *error, size_t error_size, const __half *norm_weight = nullptr, float norm_eps = 0.f) {
     auto &D = ctx->dense[index];
     if (n >= ctx->gemm_min_tokens && D.H % 128 == 0 && uocr::gemm_tensor_maps_ready()) {
         // tensor-core path: the two grouped GEMMs of a shared MLP on all n tokens (one "expert"), fp16 output rows, then
@@ -1274,8 +1285,9 @@ static int dense_forward(uocr_cuda_context *ctx, uint32_t index, const __half *d
         return 1;
     }
     if (n == 1 && D.units != 0) {
-        CU_TRY(ctx, uocr::launch_decode_dense(D.d_layer, D.gate.qtype, D.units, d_hidden, d_residual, d_out, decode_accumulators(ctx),
-                                              &ctx->acc_base, ctx->status, take_decode_knobs(ctx), ctx->stream, &ctx->launches));
+        CU_TRY(ctx, uocr::launch_decode_dense(D.d_layer, D.unit_blobs, D.gate.qtype, D.units, d_hidden, d_residual, d_out, decode_accumulators(ctx),
+                                              &ctx->acc_base, ctx->status, take_decode_knobs(ctx), ctx->stream, &ctx->launches, norm_weight,
+                                              norm_eps));
         return 1;
     }
     if (!uocr::dense_small_supported(D.H, D.S)) return fail(ctx, error, error_size, "dense MLP shape not supported by the matrix-vector path");
@@ -1301,6 +1313,12 @@ extern "C" int uocr_cuda_dense_mlp_forward_normed(uocr_cuda_context *ctx, uint32
     if (!d_stream || !d_norm_weight_f16 || !d_out || n == 0) return fail(ctx, error, error_size, "null or empty dense MLP argument");
     auto &D = ctx->dense[index];
     if (n > D.capacity) return fail(ctx, error, error_size, "n_tokens %u exceeds the dense MLP's capacity %u", n, D.capacity);
+    if (n == 1 && D.units != 0) {      // one token: the decode kernel normalises its input itself, one launch
+        if (!(eps >= 0.f)) return fail(ctx, error, error_size, "RMSNorm: eps must not be negative");
+        CU_TRY(ctx, cudaSetDevice(ctx->device));
+        return dense_forward(ctx, index, (const __half *)d_stream, (const __half *)d_stream, 1, (__half *)d_out, error, error_size,
+                             (const __half *)d_norm_weight_f16, eps);
+    }
     if (!uocr_cuda_rmsnorm(ctx, d_stream, d_norm_weight_f16, eps, n, D.H, D.x_norm, error, error_size)) return 0;
     return dense_forward(ctx, index, D.x_norm, (const __half *)d_stream, n, (__half *)d_out, error, error_size);
 }
