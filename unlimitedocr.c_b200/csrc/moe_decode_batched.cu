@@ -38,7 +38,6 @@ constexpr int kBtTokens = 16;                                  // tokens per pas
 // An item covers SLICES consecutive 64-wide slices of its expert (template parameter of the kernel): two for calls of more
 // than 16 tokens (7 parts per expert and pass), one for smaller calls (14 parts), whose ~150 two-slice items would leave most
 // CTAs idle during a second wave.  The partial-output buffers are sized for 14 parts.
-constexpr int kBtMaxParts = kSlRoutedPerSlot;                  // 14
 constexpr int kBtSmallCallTokens = 16;
 __host__ __device__ constexpr int bt_slices_for(uint32_t n) { return n <= (uint32_t)kBtSmallCallTokens ? 1 : 2; }
 constexpr int kBtSharedHalves = kSlS / 64 / kSlRoutedPerSlot;  // the shared MLP as 2 pseudo-experts of 14 slices

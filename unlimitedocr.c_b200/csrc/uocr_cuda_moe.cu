@@ -893,7 +893,7 @@ static ArenaLayout layout_arena(uint32_t H, uint32_t E, uint32_t K, uint32_t F, 
         a.seg_offsets = take(260 * 4);        // expert-parallel experts phase: offsets of the received segments
         a.plan_counts = take((pairs / 2048 + 2) * E * 4);
     }
-    {   // batched decode path (calls of up to 64 tokens): per-part partial outputs, the tokens' activation bytes
+    {   // batched decode path (calls of up to 64 tokens): the call's fixed-point output sums, the tokens' activation bytes
         const uint32_t nb = n < uocr::decode_batched_max_tokens() ? n : uocr::decode_batched_max_tokens();
         a.bt_routed = take(uocr::decode_batched_scratch(nb, K).total);
     }
