@@ -241,7 +241,8 @@ UOCR_CUDA_API int uocr_cuda_rmsnorm(uocr_cuda_context *ctx, const void *d_x, con
                                     uint32_t n_tokens, uint32_t hidden_size, void *d_out, char *error, size_t error_size);
 /* The MoE layer as the decoder runs it (src/backend/metal/uocr_metal.m:14433-14497): d_stream is the residual stream after
  * attention, the post-attention norm feeds the layer and the stream is added back:
- * d_out = MoE( RMSNorm(d_stream) * weight ) + d_stream.  The normalised rows live in the context's scratch. */
+ * d_out = MoE( RMSNorm(d_stream) * weight ) + d_stream.  The normalised rows live in the context's scratch; a one-token
+ * call on the single-token decode kernel normalises inside that kernel (one launch, the same arithmetic, bit-equal). */
 UOCR_CUDA_API int uocr_cuda_moe_layer_forward_normed(uocr_cuda_context *ctx, uint32_t layer, const void *d_stream,
                                                      const void *d_norm_weight_f16, float eps, uint32_t n_tokens, void *d_out,
                                                      const uocr_cuda_moe_debug_outputs *dbg, char *error, size_t error_size);
@@ -256,7 +257,9 @@ UOCR_CUDA_API int uocr_cuda_context_map_dense_mlp(uocr_cuda_context *ctx, const 
                                                   char *error, size_t error_size);
 UOCR_CUDA_API int uocr_cuda_dense_mlp_forward(uocr_cuda_context *ctx, uint32_t index, const void *d_hidden, const void *d_residual,
                                               uint32_t n_tokens, void *d_out, char *error, size_t error_size);
-/* d_out = DenseMLP( RMSNorm(d_stream) * weight ) + d_stream */
+/* d_out = DenseMLP( RMSNorm(d_stream) * weight ) + d_stream.  One token at the model's hidden size in Q4_0 / Q8_0 runs on the
+ * single-token decode kernel without routing (units of 64 intermediate columns on a slice-major copy of the three
+ * matrices, norm inside the kernel); 2 - 4 tokens on the shared experts' matrix-vector kernels; more on the grouped GEMM. */
 UOCR_CUDA_API int uocr_cuda_dense_mlp_forward_normed(uocr_cuda_context *ctx, uint32_t index, const void *d_stream,
                                                      const void *d_norm_weight_f16, float eps, uint32_t n_tokens, void *d_out,
                                                      char *error, size_t error_size);
