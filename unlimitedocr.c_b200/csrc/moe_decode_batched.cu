@@ -50,7 +50,7 @@ constexpr int kBtBlocksPerWarp = kSlH / 16 / 16;               // 5 blocks of 16
 constexpr int kBtTokenLimbBytes = kSlGroups * 2 * 64;          // 2560: a token's activation bytes [20][2][16 words]
 
 // ---------------------------------------------------------------- 1. routing, activation bytes, dispatch plan
-constexpr int kRsThreads = 256;
+constexpr int kRsThreads = 512;                                 // 16 warps: four experts' logits each
 
 struct RouteSmallParams {
     const __half *hidden;           // [n][H]
@@ -89,8 +89,8 @@ __global__ void __launch_bounds__(kRsThreads) route_small_kernel(const RouteSmal
     if (prm.injected != nullptr) {
         if (tid < E) s_logits[tid] = prm.injected[(size_t)token * E + tid] + (prm.bias ? prm.bias[tid] : 0.f);
     } else {
-        // warp w: experts 8w .. 8w + 7, four at a time; lane: the 16-byte chunks lane, lane + 32, ... of every row, all
-        // 20 loads of a batch in flight before the first is used
+        // warp w: experts 4w .. 4w + 3; lane: the 16-byte chunks lane, lane + 32, ... of every row, all 20 loads in
+        // flight before the first is used
         float xv[5][8];
 #pragma unroll
         for (int i = 0; i < 5; ++i) {
@@ -99,31 +99,28 @@ __global__ void __launch_bounds__(kRsThreads) route_small_kernel(const RouteSmal
 #pragma unroll
             for (int k = 0; k < 4; ++k) { const float2 f = __half22float2(xh[k]); xv[i][2 * k] = f.x; xv[i][2 * k + 1] = f.y; }
         }
+        uint4 wv[4][5];
 #pragma unroll
-        for (int b = 0; b < 2; ++b) {
-            uint4 wv[4][5];
+        for (int j = 0; j < 4; ++j)
 #pragma unroll
-            for (int j = 0; j < 4; ++j)
+            for (int i = 0; i < 5; ++i)
+                wv[j][i] = __ldg(reinterpret_cast<const uint4 *>(prm.router + (size_t)(4 * warp + j) * H) + lane + 32 * i);
 #pragma unroll
-                for (int i = 0; i < 5; ++i)
-                    wv[j][i] = __ldg(reinterpret_cast<const uint4 *>(prm.router + (size_t)(8 * warp + 4 * b + j) * H) + lane + 32 * i);
+        for (int j = 0; j < 4; ++j) {
+            float acc = 0.f;
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                float acc = 0.f;
+            for (int i = 0; i < 5; ++i) {
+                const __half2 *wh = reinterpret_cast<const __half2 *>(&wv[j][i]);
 #pragma unroll
-                for (int i = 0; i < 5; ++i) {
-                    const __half2 *wh = reinterpret_cast<const __half2 *>(&wv[j][i]);
-#pragma unroll
-                    for (int k = 0; k < 4; ++k) {
-                        const float2 f = __half22float2(wh[k]);
-                        acc = fmaf(f.x, xv[i][2 * k], acc);
-                        acc = fmaf(f.y, xv[i][2 * k + 1], acc);
-                    }
+                for (int k = 0; k < 4; ++k) {
+                    const float2 f = __half22float2(wh[k]);
+                    acc = fmaf(f.x, xv[i][2 * k], acc);
+                    acc = fmaf(f.y, xv[i][2 * k + 1], acc);
                 }
-                acc = warp_sum(acc);
-                const int e = 8 * warp + 4 * b + j;
-                if (lane == 0) s_logits[e] = prm.bias ? acc + prm.bias[e] : acc;
             }
+            acc = warp_sum(acc);
+            const int e = 4 * warp + j;
+            if (lane == 0) s_logits[e] = prm.bias ? acc + prm.bias[e] : acc;
         }
     }
     __syncthreads();
@@ -134,8 +131,8 @@ __global__ void __launch_bounds__(kRsThreads) route_small_kernel(const RouteSmal
                                         prm.weights + (size_t)token * K);
         if (bad && lane == 0) atomicOr(prm.status, 1u);
     } else {
-        // the token's activations as bytes: 16 lanes per group, warps 1 .. 7 (14 half-warps) over the 20 groups
-        for (int Gi = (warp - 1) * 2 + (lane >> 4); Gi < kSlGroups; Gi += 14) {
+        // the token's activations as bytes: 16 lanes per group, warps 1 .. 15 (30 half-warps) over the 20 groups
+        for (int Gi = (warp - 1) * 2 + (lane >> 4); Gi < kSlGroups; Gi += 30) {
             const int p = lane & 15;
             float xv[4];
             load_word_values<QT>(s_x + Gi * 64, p, xv);
@@ -156,30 +153,55 @@ __global__ void __launch_bounds__(kRsThreads) route_small_kernel(const RouteSmal
     const uint32_t pairs = prm.n * K;
     for (uint32_t p = tid; p < pairs; p += kRsThreads) s_ids[p] = __ldcg(prm.ids + p);
     __syncthreads();
-    if (tid < E) {
-        uint32_t c = 0;
-        for (uint32_t p = 0; p < pairs; ++p) c += s_ids[p] == (uint32_t)tid ? 1u : 0u;
-        s_cnt[tid] = c;
+    // Counting sort of the pairs by expert, stable (ascending pair index inside an expert).  Warp w owns experts 4w .. 4w + 3
+    // and walks the pairs 32 at a time: a ballot per expert gives the count of the chunk and, in the second pass, the
+    // position of every matching lane.
+    const uint32_t chunks = (pairs + 31u) / 32u;
+    uint32_t cnt[4] = {0u, 0u, 0u, 0u};
+    for (uint32_t c = 0; c < chunks; ++c) {
+        const uint32_t p = 32u * c + (uint32_t)lane, id = p < pairs ? s_ids[p] : 0xffffffffu;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) cnt[j] += (uint32_t)__popc(__ballot_sync(0xffffffffu, id == (uint32_t)(4 * warp + j)));
     }
+    if (lane < 4) s_cnt[4 * warp + lane] = lane == 0 ? cnt[0] : lane == 1 ? cnt[1] : lane == 2 ? cnt[2] : cnt[3];
     __syncthreads();
-    if (tid == 0) {
-        uint32_t run = 0, na = 0;
-        for (int e = 0; e < E; ++e) {
-            const uint32_t c = s_cnt[e];
-            s_cnt[e] = run;
-            prm.offsets[e] = run;
-            if (c) prm.active[1 + na++] = (uint32_t)e;
-            run += c;
+    if (warp == 0) {
+        // exclusive prefix sums of the 64 counts and of the "has pairs" flags: lane l takes experts 2l and 2l + 1
+        const uint32_t c0 = s_cnt[2 * lane], c1 = s_cnt[2 * lane + 1];
+        uint32_t sum = c0 + c1, act = (c0 ? 1u : 0u) + (c1 ? 1u : 0u);
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const uint32_t s2 = __shfl_up_sync(0xffffffffu, sum, o), a2 = __shfl_up_sync(0xffffffffu, act, o);
+            if (lane >= o) { sum += s2; act += a2; }
         }
-        prm.offsets[E] = run;
-        prm.active[0] = na;
-        *prm.ticket = 0u;
+        const uint32_t base = sum - c0 - c1, abase = act - (c0 ? 1u : 0u) - (c1 ? 1u : 0u);
+        prm.offsets[2 * lane] = base;
+        prm.offsets[2 * lane + 1] = base + c0;
+        if (c0) prm.active[1 + abase] = (uint32_t)(2 * lane);
+        if (c1) prm.active[1 + abase + (c0 ? 1u : 0u)] = (uint32_t)(2 * lane + 1);
+        __syncwarp();
+        s_cnt[2 * lane] = base;
+        s_cnt[2 * lane + 1] = base + c0;
+        if (lane == 31) {
+            prm.offsets[E] = sum;
+            prm.active[0] = act;
+            *prm.ticket = 0u;
+        }
     }
     __syncthreads();
-    if (tid < E) {                              // expert e lists its pairs in ascending order: the stable sort
-        uint32_t pos = s_cnt[tid];
-        for (uint32_t p = 0; p < pairs; ++p)
-            if (s_ids[p] == (uint32_t)tid) { prm.pair_rows[pos] = p; prm.inverse[p] = pos; ++pos; }
+    uint32_t run[4] = {s_cnt[4 * warp], s_cnt[4 * warp + 1], s_cnt[4 * warp + 2], s_cnt[4 * warp + 3]};
+    for (uint32_t c = 0; c < chunks; ++c) {
+        const uint32_t p = 32u * c + (uint32_t)lane, id = p < pairs ? s_ids[p] : 0xffffffffu;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const uint32_t m = __ballot_sync(0xffffffffu, id == (uint32_t)(4 * warp + j));
+            if (id == (uint32_t)(4 * warp + j)) {
+                const uint32_t pos = run[j] + (uint32_t)__popc(m & ((1u << lane) - 1u));
+                prm.pair_rows[pos] = p;
+                prm.inverse[p] = pos;
+            }
+            run[j] += (uint32_t)__popc(m);
+        }
     }
     for (uint32_t p = tid; p < pairs; p += kRsThreads)
         if (s_ids[p] >= (uint32_t)E) prm.inverse[p] = 0xffffffffu;
