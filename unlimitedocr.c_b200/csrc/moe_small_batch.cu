@@ -643,7 +643,8 @@ lm_head_ring_kernel(const __half *__restrict__ hidden, uint32_t n, uint32_t H, c
             if (scores_out) scores_out[warp] = bi == 0xffffffffu ? -INFINITY : bsc;
         }
     }
-    if (tid == 0) *ticket = 0;
+    __syncthreads();                           // every token's warp has read the status word
+    if (tid == 0) { *ticket = 0; *status = 0u; }      // the failed call has reported "no token"; the next call starts clean
 }
 
 template <int QT>
