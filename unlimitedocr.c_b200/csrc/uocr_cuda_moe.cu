@@ -1243,7 +1243,10 @@ extern "C" int uocr_cuda_context_map_dense_mlp(uocr_cuda_context *ctx, const uoc
     // One token: the single-token decode kernel on a slice-major copy of the three matrices (every CTA a 64-column unit)
     if (ctx->fused_decode && ctx->sliced_decode) {
         const uint32_t units = uocr::decode_dense_units(H, S, D.gate.qtype, D.up.qtype, D.down.qtype);
-        if (units != 0) {
+        // every unit is a CTA that waits for the others: only grids no larger than the MoE decode kernel's own (112 CTAs in
+        // clusters of four, whose co-residency is verified when the context is created) are launched this way
+        constexpr uint32_t kCoResidentCtas = 112;
+        if (units != 0 && units <= kCoResidentCtas) {
             const size_t bytes = uocr::decode_dense_units_bytes(D.gate.qtype, units);
             uint8_t *blob = nullptr;
             CU_TRY(ctx, cudaMalloc(&blob, bytes));
