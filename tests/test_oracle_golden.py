@@ -322,3 +322,33 @@ def test_rmsnorm_restatement_equals_the_reference_build(port, ref):
         got = port.rmsnorm_f16(xb, wb, eps).view("<f2").astype(np.float32)
         want = ref.rmsnorm_f32(xb.view("<f2").astype(np.float32), wb.view("<f2").astype(np.float32), eps)
         assert np.array_equal(got, want.astype("<f2").astype(np.float32))
+
+
+@pytest.mark.parametrize("qname", ["q4_0", "q8_0", "f16"])
+def test_lm_head_restatement_against_numpy(port, qname):
+    """The fused LM head's contract (src/backend/metal/kernels/lm_head_q4.metal:25-100: strict '>' over ascending rows, NaN
+    totals skipped) restated once more in NumPy on the dequantised matrix: logits within f32 summation noise, the same
+    winner unless the two best NumPy logits are closer than that noise, ties to the lowest row, a NaN row never wins."""
+    rng = np.random.default_rng(900)
+    V, H, n = 700, 256, 5
+    w = rng.standard_normal((V, H), dtype=np.float32) * 0.05
+    w[300] = w[40]                                      # an exact twin: the lower id must win whenever it is the best
+    m = quant.make_matrix(quant.QTYPE_BY_NAME[qname], w)
+    x = quant.synth_activations(rng, n, H)
+    ids, scores, logits = port.lm_head_argmax(m, x, want_logits=True)
+    ref = x.view("<f2").astype(np.float64) @ m.to_f32().astype(np.float64).T
+    assert np.max(np.abs(logits - ref)) <= 1e-4 * max(1.0, float(np.max(np.abs(ref))))
+    assert np.array_equal(logits[:, 300], logits[:, 40])
+    for t in range(n):
+        order = np.argsort(-ref[t], kind="stable")
+        if ids[t] != order[0]:
+            assert abs(ref[t, order[0]] - ref[t, order[1]]) <= 1e-4 and ids[t] == order[1]
+        assert ids[t] != 300 and scores[t] == logits[t, ids[t]]
+        assert ids[t] == int(np.flatnonzero(logits[t] == logits[t].max())[0])         # first of the equal maxima
+    if qname == "f16":                                   # a NaN weight: that row's logit is NaN and it never wins
+        bits = m.qweight.view(np.uint16).reshape(V, H).copy()
+        bits[int(ids[0]), 3] = 0x7E00
+        m_nan = quant.Matrix(quant.QTYPE_F16, V, H, bits.view(np.uint8).reshape(-1), None)
+        ids2, _, logits2 = port.lm_head_argmax(m_nan, x, want_logits=True)
+        assert np.isnan(logits2[0, ids[0]]) and ids2[0] != ids[0]
+        assert ids2[0] == int(np.nanargmax(logits2[0]))
