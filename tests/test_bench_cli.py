@@ -41,3 +41,11 @@ def test_repo_arm_refuses_to_run_without_a_device():
     res = run_bench("--steps", "1", "--warmup", "1")
     assert res.returncode != 0
     assert "needs a CUDA device" in (res.stderr + res.stdout)
+
+
+def test_reference_arm_on_a_rank_other_than_zero_does_nothing():
+    import os
+    env = dict(os.environ, RANK="1", LOCAL_RANK="1", WORLD_SIZE="2")
+    res = subprocess.run([sys.executable, str(ROOT / "bench.py"), "--impl", "reference", "--gpus", "2", "--steps", "1", "--warmup", "1"],
+                         capture_output=True, text=True, timeout=120, cwd=str(ROOT), env=env)
+    assert res.returncode == 0 and res.stdout.strip() == ""
